@@ -1,0 +1,330 @@
+"""Generate the golden fixtures in this folder by running the reference implementation.
+
+Usage (only where the reference checkout is available; the fixtures are committed so the
+test-suite never needs it):
+
+    python tests/golden/make_golden.py /path/to/compressed-tensors
+
+The reference is imported from ``<checkout>/src`` with a stub for its build-generated
+``version`` module, in eager mode (``TORCHDYNAMO_DISABLE=1``).  Every fixture is a dict of
+small tensors holding seeded inputs and the reference's outputs for them.
+"""
+import itertools
+import os
+import sys
+import types
+
+os.environ.setdefault("TORCHDYNAMO_DISABLE", "1")
+os.environ.setdefault("HF_HUB_OFFLINE", "1")
+
+REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+_v = types.ModuleType("compressed_tensors.version")
+_v.__version__ = _v.version = "0.0.0"
+_v.__all__ = ["__version__", "version"]
+sys.modules["compressed_tensors.version"] = _v
+sys.path.insert(0, os.path.join(REF, "src"))
+
+import torch  # noqa: E402
+
+import compressed_tensors  # noqa: E402
+
+assert compressed_tensors.__file__.startswith(REF), compressed_tensors.__file__
+
+from compressed_tensors.compressors.quantized_compressors.fp4_quantized import (  # noqa: E402
+    NVFP4PackedCompressor,
+    pack_fp4_to_uint8,
+    unpack_fp4_from_uint8,
+)
+from compressed_tensors.compressors.quantized_compressors.naive_quantized import (  # noqa: E402
+    NaiveQuantizationCompressor,
+)
+from compressed_tensors.compressors.quantized_compressors.pack_quantized import (  # noqa: E402
+    PackedQuantizationCompressor,
+    pack_to_int32,
+    unpack_from_int32,
+)
+from compressed_tensors.compressors.sparse_compressors.sparse_24_bitmask import (  # noqa: E402
+    get_24_bytemasks,
+    sparse24_bitmask_compress,
+    sparse24_bitmask_decompress,
+)
+from compressed_tensors.compressors.sparse_compressors.sparse_bitmask import (  # noqa: E402
+    bitmask_compress,
+    bitmask_decompress,
+)
+from compressed_tensors.quantization import QuantizationArgs  # noqa: E402
+from compressed_tensors.quantization.lifecycle.forward import (  # noqa: E402
+    dequantize,
+    fake_quantize,
+    quantize,
+)
+from compressed_tensors.quantization.utils.helpers import (  # noqa: E402
+    calculate_qparams,
+    compute_dynamic_scales_and_zp,
+    generate_gparam,
+)
+from compressed_tensors.transform import TransformArgs, TransformScheme  # noqa: E402
+from compressed_tensors.transform.factory.hadamard import HadamardFactory  # noqa: E402
+from compressed_tensors.transform.factory.random_hadamard import RandomHadamardFactory  # noqa: E402
+from compressed_tensors.transform.utils.hadamard import (  # noqa: E402
+    deterministic_hadamard_matrix,
+    random_hadamard_matrix,
+)
+
+OUT = os.path.dirname(os.path.abspath(__file__))
+
+
+def weights(gen, rows, cols, dtype, std=0.02):
+    """N(0, std) weights with a few rows of awkward values (zeros, signed zero, ties, extremes)."""
+    w = (torch.randn(rows, cols, generator=gen) * std).to(dtype)
+    w[0, : cols // 2] = 0.0
+    w[1, ::3] = -0.0
+    w[2] = torch.linspace(-1.0, 1.0, cols).to(dtype)  # many exact ties after scaling
+    w[3, :8] = torch.tensor([3.0, -3.0, 1e-6, -1e-6, 0.5, -0.5, 100.0, -100.0]).to(dtype)
+    w[4] = 0.0  # an all-zero row: scale clamps to eps / 0.125
+    return w
+
+
+def group_minmax(x, g):
+    v = x.unflatten(-1, (x.shape[-1] // g, g))
+    return torch.amin(v, dim=-1), torch.amax(v, dim=-1)
+
+
+def gen_int():
+    """int4/int8, symmetric/asymmetric, tensor/channel/group, bf16/fp16/fp32."""
+    out = {}
+    gen = torch.Generator().manual_seed(0)
+    cases = [
+        ("w4_sym_g128_bf16", 4, True, "group", 128, torch.bfloat16),
+        ("w4_asym_g128_bf16", 4, False, "group", 128, torch.bfloat16),
+        ("w4_sym_g32_bf16", 4, True, "group", 32, torch.bfloat16),
+        ("w8_sym_g128_bf16", 8, True, "group", 128, torch.bfloat16),
+        ("w8_sym_channel_bf16", 8, True, "channel", None, torch.bfloat16),
+        ("w8_asym_channel_bf16", 8, False, "channel", None, torch.bfloat16),
+        ("w4_sym_tensor_bf16", 4, True, "tensor", None, torch.bfloat16),
+        ("w4_sym_g128_fp32", 4, True, "group", 128, torch.float32),
+        ("w4_asym_g64_fp16", 4, False, "group", 64, torch.float16),
+        ("w4_sym_channel_fp32", 4, True, "channel", None, torch.float32),
+    ]
+    for name, bits, sym, strategy, g, dtype in cases:
+        x = weights(gen, 16, 256, dtype)
+        args = QuantizationArgs(num_bits=bits, symmetric=sym, strategy=strategy, group_size=g)
+        if strategy == "group":
+            mn, mx = group_minmax(x, g)
+        elif strategy == "channel":
+            mn, mx = torch.amin(x, dim=-1, keepdim=True), torch.amax(x, dim=-1, keepdim=True)
+        else:
+            mn, mx = torch.aminmax(x)
+        scale, zp = calculate_qparams(mn, mx, args)
+        q8 = quantize(x, scale, zp, args, dtype=torch.int8)
+        packed = pack_to_int32(q8, bits)
+        d = {
+            "x": x, "min": mn, "max": mx, "scale": scale, "zp": zp,
+            "q_int8": q8,
+            "q_float": quantize(x, scale, zp, args),
+            "packed": packed,
+            "unpacked": unpack_from_int32(packed, bits, x.shape),
+            "dequant": dequantize(q8, scale, zp, args),
+            "dequant_noargs": dequantize(q8, scale, zp) if strategy != "tensor" else dequantize(q8, scale, zp, args),
+            "fake": fake_quantize(x, scale, zp, args),
+            "bits": torch.tensor(bits), "sym": torch.tensor(sym), "group": torch.tensor(g or 0),
+        }
+        comp = PackedQuantizationCompressor()
+        cd = comp.compress_weight(x, scale, args, zero_point=zp)
+        for k, v in cd.items():
+            d["c_" + k] = v
+        cd["weight_scale"] = scale
+        d["decompressed"] = comp.decompress_weight(cd, args)
+        out[name] = d
+    # activation ordering: groups assigned by a permuted column map
+    x = weights(gen, 16, 256, torch.bfloat16)
+    g = 64
+    perm = torch.randperm(256, generator=gen)
+    g_idx = torch.empty(256, dtype=torch.int32)
+    g_idx[perm] = (torch.arange(256) // g).to(torch.int32)
+    args = QuantizationArgs(num_bits=4, symmetric=True, strategy="group", group_size=g, actorder="group")
+    xs = x.index_select(-1, torch.argsort(g_idx))
+    mn, mx = group_minmax(xs, g)
+    scale, zp = calculate_qparams(mn, mx, args)
+    q8 = quantize(x, scale, zp, args, dtype=torch.int8, g_idx=g_idx)
+    out["w4_sym_g64_actorder"] = {
+        "x": x, "scale": scale, "zp": zp, "g_idx": g_idx, "q_int8": q8,
+        "dequant": dequantize(q8, scale, zp, args, g_idx=g_idx),
+        "fake": fake_quantize(x, scale, zp, args, g_idx=g_idx),
+        "bits": torch.tensor(4), "sym": torch.tensor(True), "group": torch.tensor(g),
+    }
+    # exact words asserted by the reference's own pack test
+    for bits, vals in ((4, [-8, -7, -6, -5, -4, -3, -2, -1]), (8, [1, 2, 3, 4]), (4, [1, 2, 3]), (2, list(range(-2, 2)) * 5)):
+        v = torch.tensor([vals], dtype=torch.int8)
+        out[f"pack_known_{bits}_{len(vals)}"] = {"value": v, "packed": pack_to_int32(v, bits), "bits": torch.tensor(bits)}
+    # packing of zero points along dim 0
+    zp = torch.randint(-8, 8, (20, 6), generator=gen, dtype=torch.int8)
+    pz = pack_to_int32(zp, 4, packed_dim=0)
+    out["pack_dim0"] = {"value": zp, "packed": pz.contiguous(), "unpacked": unpack_from_int32(pz, 4, zp.shape, packed_dim=0)}
+    torch.save(out, os.path.join(OUT, "int_quant.pt"))
+
+
+def gen_fp8():
+    out = {}
+    gen = torch.Generator().manual_seed(1)
+    args_c = QuantizationArgs(num_bits=8, type="float", symmetric=True, strategy="channel")
+    args_t = QuantizationArgs(num_bits=8, type="float", symmetric=True, strategy="tensor")
+    args_tok = QuantizationArgs(num_bits=8, type="float", symmetric=True, strategy="token", dynamic=True)
+    args_b = QuantizationArgs(num_bits=8, type="float", symmetric=True, strategy="block", block_structure=[16, 64])
+    for dtype, sdt, tag in ((torch.bfloat16, None, "bf16"), (torch.bfloat16, torch.float32, "bf16_f32scale"),
+                            (torch.float16, None, "fp16"), (torch.float32, None, "fp32")):
+        x = weights(gen, 32, 256, dtype)
+        xs = x if sdt is None else x.to(sdt)
+        mn, mx = torch.amin(xs, dim=-1, keepdim=True), torch.amax(xs, dim=-1, keepdim=True)
+        scale, zp = calculate_qparams(mn, mx, args_c)
+        q = quantize(x, scale, zp, args_c, dtype=torch.float8_e4m3fn)
+        out["channel_" + tag] = {
+            "x": x, "scale": scale, "zp": zp, "q": q, "q_float": quantize(x, scale, zp, args_c),
+            "dequant": dequantize(q, scale, zp, args_c), "dequant_noargs": dequantize(q, scale),
+            "fake": fake_quantize(x, scale, zp, args_c),
+        }
+        c = NaiveQuantizationCompressor()
+        cd = c.compress_weight(x, scale, args_c, zero_point=zp)
+        out["channel_" + tag]["c_weight"] = cd["weight"]
+        cd["weight_scale"] = scale
+        out["channel_" + tag]["decompressed"] = c.decompress_weight(cd, args_c)
+    x = weights(gen, 32, 256, torch.bfloat16)
+    scale, zp = calculate_qparams(*torch.aminmax(x), args_t)
+    q = quantize(x, scale, zp, args_t, dtype=torch.float8_e4m3fn)
+    out["tensor_bf16"] = {"x": x, "scale": scale, "zp": zp, "q": q, "dequant": dequantize(q, scale, zp, args_t),
+                          "fake": fake_quantize(x, scale, zp, args_t)}
+    # dynamic per token, with outlier channels
+    act = torch.randn(2, 24, 256, generator=gen)
+    idx = torch.randperm(256, generator=gen)[:3]
+    act[..., idx] *= 20
+    act[0, 0] = 0.0
+    act = act.to(torch.bfloat16)
+    scale, zp = compute_dynamic_scales_and_zp(act, args_tok, module=None)
+    q = quantize(act, scale, zp, args_tok, dtype=torch.float8_e4m3fn)
+    out["token_bf16"] = {"x": act, "scale": scale, "zp": zp, "q": q, "dequant": dequantize(q, scale, zp, args_tok),
+                         "fake": fake_quantize(act, scale, zp, args_tok)}
+    # 2-D input under TOKEN collapses to one scale for the whole tensor
+    s2, z2 = compute_dynamic_scales_and_zp(act[0], args_tok, module=None)
+    out["token_2d"] = {"x": act[0], "scale": s2, "zp": z2}
+    # block strategy
+    x = weights(gen, 32, 256, torch.bfloat16)
+    xb = x.reshape(2, 16, 4, 64).transpose(1, 2)
+    mn, mx = torch.amin(xb, dim=(-1, -2)), torch.amax(xb, dim=(-1, -2))
+    scale, zp = calculate_qparams(mn, mx, args_b)
+    q = quantize(x, scale, zp, args_b, dtype=torch.float8_e4m3fn)
+    out["block_bf16"] = {"x": x, "scale": scale, "zp": zp, "q": q, "dequant": dequantize(q, scale, zp, args_b),
+                         "fake": fake_quantize(x, scale, zp, args_b)}
+    # e4m3 rounding probe: every bf16 value in a range, unit scale
+    allv = torch.arange(0x3000, 0x4400, dtype=torch.int32).to(torch.int16).view(torch.bfloat16).reshape(1, -1)
+    allv = torch.cat([allv, -allv], dim=0)
+    one = torch.ones(1, dtype=torch.bfloat16)
+    out["e4m3_probe"] = {"x": allv, "scale": one, "q": quantize(allv, one, None, args_t, dtype=torch.float8_e4m3fn)}
+    torch.save(out, os.path.join(OUT, "fp8_quant.pt"))
+
+
+def gen_nvfp4():
+    out = {}
+    gen = torch.Generator().manual_seed(2)
+    args = QuantizationArgs(num_bits=4, type="float", symmetric=True, strategy="tensor_group", group_size=16)
+    for tag, rows, cols in (("a", 24, 256), ("b", 8, 64)):
+        x = weights(gen, rows, cols, torch.bfloat16)
+        x[3, :8] = x[3, :8] / 50  # keep the global scale dominated by the N(0, .02) body
+        mn, mx = torch.aminmax(x)
+        gs = generate_gparam(mn, mx)
+        gmn, gmx = group_minmax(x, 16)
+        scale, zp = calculate_qparams(gmn, gmx, args, global_scale=gs)
+        q = quantize(x, scale, zp, args, global_scale=gs)
+        packed = pack_fp4_to_uint8(q)
+        unpacked = unpack_fp4_from_uint8(packed, rows, cols)
+        comp = NVFP4PackedCompressor()
+        cd = comp.compress_weight(x, scale, gs, args, zero_point=zp)
+        out[tag] = {
+            "x": x, "min": mn.reshape(1), "max": mx.reshape(1), "global_scale": gs, "gmin": gmn, "gmax": gmx,
+            "scale": scale, "zp": zp, "q": q, "packed": packed, "unpacked": unpacked,
+            "dequant": dequantize(unpacked, scale, global_scale=gs, dtype=torch.bfloat16),
+            "fake": fake_quantize(x, scale, zp, args, global_scale=gs),
+            "c_weight_packed": cd["weight_packed"],
+            "decompressed": comp.decompress_weight({"weight_packed": packed, "weight_scale": scale,
+                                                    "weight_global_scale": gs}, args),
+        }
+    # threshold probe for the e2m1 cast: a fine sweep of fp32 values through unit scales
+    sweep = torch.cat([torch.linspace(-7, 7, 1121), torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, -0.25, -0.0, 0.0, -1e-3])])
+    sweep = torch.nn.functional.pad(sweep, (0, 1136 - sweep.numel())).reshape(1, -1)
+    one = torch.ones(1, 1136 // 16, dtype=torch.float8_e4m3fn)
+    gs1 = torch.ones(1)
+    q = quantize(sweep, one, None, args, global_scale=gs1)
+    out["e2m1_probe"] = {"x": sweep, "scale": one, "global_scale": gs1, "q": q, "packed": pack_fp4_to_uint8(q)}
+    torch.save(out, os.path.join(OUT, "nvfp4.pt"))
+
+
+def gen_sparse():
+    out = {}
+    gen = torch.Generator().manual_seed(3)
+    for dtype, tag in ((torch.bfloat16, "bf16"), (torch.float16, "fp16"), (torch.float32, "fp32"), (torch.float8_e4m3fn, "e4m3")):
+        for cols in (64, 13):
+            x = torch.randn(12, cols, generator=gen) * 0.5
+            x[torch.rand(12, cols, generator=gen) < 0.5] = 0.0
+            x[1, ::2] = -0.0
+            x[5] = 0.0
+            x = x.to(dtype)
+            values, bitmask, row_offsets = bitmask_compress(x)
+            out[f"bitmask_{tag}_{cols}"] = {
+                "x": x, "values": values, "bitmask": bitmask, "row_offsets": row_offsets,
+                "dense": bitmask_decompress(values, bitmask, list(x.shape)),
+            }
+    for dtype, tag in ((torch.bfloat16, "bf16"), (torch.float32, "fp32"), (torch.int8, "int8"), (torch.float8_e4m3fn, "e4m3")):
+        if dtype == torch.int8:
+            x = torch.randint(-128, 128, (16, 64), generator=gen, dtype=torch.int8)
+        else:
+            x = torch.randn(16, 64, generator=gen)
+            x[0] = torch.round(x[0] * 2) / 2  # many ties
+            x[1] = 0.0
+            x[2, ::2] = 1.0
+            x = x.to(dtype)
+        mask = get_24_bytemasks(x)
+        values, bitmask = sparse24_bitmask_compress(x)
+        out[f"s24_{tag}"] = {"x": x, "mask": mask, "values": values, "bitmask": bitmask,
+                             "dense": sparse24_bitmask_decompress(values, bitmask, list(x.shape))}
+    # keep-mask for every weak ordering of four magnitudes (dense ranks 0..3)
+    pats = [p for p in itertools.product(range(4), repeat=4) if set(p) == set(range(len(set(p))))]
+    ranks = torch.tensor(pats, dtype=torch.float32)
+    out["s24_rank_patterns"] = {"ranks": ranks.to(torch.int8), "mask": get_24_bytemasks(ranks),
+                                "mask_int8": get_24_bytemasks(ranks.to(torch.int8)),
+                                "mask_bf16": get_24_bytemasks(ranks.to(torch.bfloat16))}
+    torch.save(out, os.path.join(OUT, "sparse.pt"))
+
+
+def gen_hadamard():
+    out = {}
+    for n in (16, 64, 128, 256):
+        out[f"det_{n}"] = {"H": deterministic_hadamard_matrix(n, torch.float64).to(torch.int8)}
+        g = torch.Generator().manual_seed(42)
+        out[f"rand_{n}_seed42"] = {"H": random_hadamard_matrix(n, torch.float64, gen=g).to(torch.int8)}
+    gen = torch.Generator().manual_seed(4)
+    for tag, fac_cls, seed in (("hadamard", HadamardFactory, None), ("random", RandomHadamardFactory, 7)):
+        for location, inverse in (("weight_input", False), ("weight_input", True), ("weight_output", False), ("weight_output", True)):
+            for dtype in (torch.bfloat16, torch.float32):
+                o, i = (16, 256) if location == "weight_input" else (256, 16)
+                lin = torch.nn.Linear(i, o, bias=False, dtype=dtype)
+                lin.weight.data = weights(gen, o, i, dtype)
+                scheme = TransformScheme(type=tag if tag == "hadamard" else "random-hadamard", head_dim=128,
+                                         apply=[TransformArgs(targets=["Linear"], location=location, inverse=inverse)])
+                fac = fac_cls("t", scheme, seed=seed)
+                tr = fac.create_transform(lin, scheme.apply[0])
+                w0 = lin.weight.data.clone()
+                with torch.no_grad():
+                    w1 = tr(lin.weight)
+                name = f"{tag}_{location}_{'inv' if inverse else 'fwd'}_{str(dtype).split('.')[-1]}"
+                out[name] = {"w": w0, "out": w1.detach(), "matrix": tr.weight.detach().to(torch.int8)}
+    torch.save(out, os.path.join(OUT, "hadamard.pt"))
+
+
+if __name__ == "__main__":
+    gen_int()
+    gen_fp8()
+    gen_nvfp4()
+    gen_sparse()
+    gen_hadamard()
+    for f in sorted(os.listdir(OUT)):
+        if f.endswith(".pt"):
+            print(f, os.path.getsize(os.path.join(OUT, f)))
