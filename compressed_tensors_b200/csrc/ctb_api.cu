@@ -1,0 +1,54 @@
+// Library-wide host state: version, thread-local error text, launch counter, device properties.
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+
+#include "ctb_common.cuh"
+
+namespace ctb {
+
+static thread_local char g_err[512] = "";
+static std::atomic<int64_t> g_launches{0};
+
+void set_error(const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+
+int fail(int status, const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return status;
+}
+
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
+int after_launch(const char *what) {
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(CTB_ECUDA, "%s: %s", what, cudaGetErrorString(e));
+    return CTB_OK;
+}
+
+int sm_count() {
+    // one cached value per device index
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+}  // namespace ctb
+
+extern "C" const char *ctb_version(void) { return "ctb200 0.1.0 (sm_100a)"; }
+extern "C" const char *ctb_last_error_string(void) { return ctb::g_err; }
+extern "C" int64_t ctb_launch_count(void) { return ctb::g_launches.load(); }

@@ -1,0 +1,304 @@
+// Per-chunk (8 consecutive elements of one row) load / store / arithmetic used by the quantize,
+// dequantize and fused kernels.  Every function restates one step of
+// quantization/lifecycle/forward.py:455-514 (_quantize / _dequantize) with the intermediate
+// roundings torch performs made explicit.
+#pragma once
+
+#include "ctb_common.cuh"
+
+namespace ctb {
+
+// storage format of one side of a kernel
+enum Fmt : int {
+    F_BF16 = 0,
+    F_F16 = 1,
+    F_F32 = 2,
+    F_I8 = 3,
+    F_E4M3 = 4,
+    F_PACK4 = 5,  // int4 codes, 8 per int32 word, offset binary (pack_to_int32, num_bits=4)
+    F_PACK8 = 6,  // int8 codes, 4 per int32 word, offset binary (pack_to_int32, num_bits=8)
+    F_FP4X2 = 7,  // e2m1 codes, 2 per byte, even element in the low nibble
+    F_NONE = 8
+};
+
+enum QKind : int { QK_INT = 0, QK_FP8 = 1, QK_FP4 = 2 };
+
+#ifdef __CUDACC__
+
+// bytes one 8-element chunk occupies in a format
+__host__ __device__ constexpr int chunk_bytes(int f) {
+    return f == F_F32 ? 32 : (f == F_BF16 || f == F_F16) ? 16 : (f == F_I8 || f == F_E4M3 || f == F_PACK8) ? 8 : 4;
+}
+
+// raw register image of one chunk (enough for the widest format)
+struct Raw8 {
+    uint4 a, b;
+};
+
+template <int F>
+__device__ __forceinline__ Raw8 load_raw(const void *base, int64_t chunk) {
+    Raw8 r;
+    const char *p = (const char *)base + chunk * chunk_bytes(F);
+    if constexpr (F == F_F32) {
+        r.a = ld_stream(p);
+        r.b = ld_stream(p + 16);
+    } else if constexpr (F == F_BF16 || F == F_F16) {
+        r.a = ld_stream(p);
+    } else if constexpr (F == F_I8 || F == F_E4M3 || F == F_PACK8) {
+        uint2 t = ld_stream8(p);
+        r.a.x = t.x;
+        r.a.y = t.y;
+    } else {
+        r.a.x = ld_stream4(p);
+    }
+    return r;
+}
+
+__device__ __forceinline__ float2 half2_bits_to_float2(uint32_t u) {
+    __half2 h = *reinterpret_cast<__half2 *>(&u);
+    return __half22float2(h);
+}
+
+template <int F>
+__device__ __forceinline__ void decode8(const Raw8 &r, float (&v)[8]) {
+    if constexpr (F == F_F32) {
+        v[0] = __uint_as_float(r.a.x); v[1] = __uint_as_float(r.a.y);
+        v[2] = __uint_as_float(r.a.z); v[3] = __uint_as_float(r.a.w);
+        v[4] = __uint_as_float(r.b.x); v[5] = __uint_as_float(r.b.y);
+        v[6] = __uint_as_float(r.b.z); v[7] = __uint_as_float(r.b.w);
+    } else if constexpr (F == F_BF16) {
+        const uint32_t w[4] = {r.a.x, r.a.y, r.a.z, r.a.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            v[2 * i] = __uint_as_float(w[i] << 16);
+            v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+        }
+    } else if constexpr (F == F_F16) {
+        const uint32_t w[4] = {r.a.x, r.a.y, r.a.z, r.a.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float2 f = half2_bits_to_float2(w[i]);
+            v[2 * i] = f.x;
+            v[2 * i + 1] = f.y;
+        }
+    } else if constexpr (F == F_I8 || F == F_PACK8) {
+        const uint32_t w[2] = {r.a.x, r.a.y};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            uint32_t b = (w[i >> 2] >> (8 * (i & 3))) & 0xFFu;
+            if constexpr (F == F_PACK8) b ^= 0x80u;  // stored as value + 128
+            v[i] = (float)(int)(int8_t)b;
+        }
+    } else if constexpr (F == F_E4M3) {
+        const uint32_t w[2] = {r.a.x, r.a.y};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            __half2_raw h = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)((w[i >> 1] >> (16 * (i & 1))) & 0xFFFFu), __NV_E4M3);
+            float2 f = __half22float2(__half2(h));
+            v[2 * i] = f.x;
+            v[2 * i + 1] = f.y;
+        }
+    } else if constexpr (F == F_PACK4) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = (float)((int)((r.a.x >> (4 * i)) & 0xFu) - 8);
+    } else if constexpr (F == F_FP4X2) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            __half2_raw h = __nv_cvt_fp4x2_to_halfraw2((__nv_fp4x2_storage_t)((r.a.x >> (8 * i)) & 0xFFu), __NV_E2M1);
+            float2 f = __half22float2(__half2(h));
+            v[2 * i] = f.x;      // low nibble = even element; nibble 0x8 decodes to -0.0
+            v[2 * i + 1] = f.y;
+        }
+    }
+}
+
+// store 8 plain values (already exactly representable in the target float dtype, or to be rounded to it)
+template <int F>
+__device__ __forceinline__ void store8_float(void *base, int64_t chunk, const float (&v)[8]) {
+    char *p = (char *)base + chunk * chunk_bytes(F);
+    if constexpr (F == F_F32) {
+        st_stream(p, make_uint4(__float_as_uint(v[0]), __float_as_uint(v[1]), __float_as_uint(v[2]), __float_as_uint(v[3])));
+        st_stream(p + 16, make_uint4(__float_as_uint(v[4]), __float_as_uint(v[5]), __float_as_uint(v[6]), __float_as_uint(v[7])));
+    } else if constexpr (F == F_BF16) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+            w[i] = *reinterpret_cast<uint32_t *>(&h);
+        }
+        st_stream(p, make_uint4(w[0], w[1], w[2], w[3]));
+    } else if constexpr (F == F_F16) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+            w[i] = *reinterpret_cast<uint32_t *>(&h);
+        }
+        st_stream(p, make_uint4(w[0], w[1], w[2], w[3]));
+    }
+}
+
+// Final rounding of 8 clamped values to the quantized grid (quantization/quant_args.py:384-408
+// round_to_quantized_type) fused with the store in format F.
+//   INT : torch.round (half to even)                      -> I8 / PACK4 / PACK8 / float dtype
+//   FP8 : Tensor.to(float8_e4m3fn), NaN keeps its sign   -> E4M3 / float dtype
+//   FP4 : FP4_E2M1_DATA.cast_to_fp4 (quant_args.py:55-68) -> FP4X2 / float dtype
+// In FP4 an input that is exactly +-0 encodes as +0 while a negative value that rounds to zero
+// keeps its sign (nibble 0x8), because the reference multiplies by torch.sign(x).
+template <int QK, int F>
+__device__ __forceinline__ void encode_store8(void *base, int64_t chunk, float (&v)[8]) {
+    char *p = (char *)base + chunk * chunk_bytes(F);
+    if constexpr (QK == QK_INT) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = rintf(v[i]);
+        if constexpr (F == F_PACK4) {
+            uint32_t w = 0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) w |= (uint32_t)(((int)v[i] + 8) & 0xF) << (4 * i);
+            st_stream4(p, w);
+        } else if constexpr (F == F_I8 || F == F_PACK8) {
+            uint32_t w[2] = {0u, 0u};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                uint32_t b = (uint32_t)((int)v[i]) & 0xFFu;
+                if constexpr (F == F_PACK8) b ^= 0x80u;
+                w[i >> 2] |= b << (8 * (i & 3));
+            }
+            st_stream8(p, make_uint2(w[0], w[1]));
+        } else {
+            store8_float<F>(base, chunk, v);
+        }
+    } else if constexpr (QK == QK_FP8) {
+        uint32_t w[2] = {0u, 0u};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            uint32_t c = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(v[2 * i], v[2 * i + 1]), __NV_SATFINITE, __NV_E4M3);
+            if (v[2 * i] != v[2 * i]) c = (c & 0xFF00u) | 0x7Fu | ((__float_as_uint(v[2 * i]) >> 24) & 0x80u);
+            if (v[2 * i + 1] != v[2 * i + 1]) c = (c & 0x00FFu) | 0x7F00u | ((__float_as_uint(v[2 * i + 1]) >> 16) & 0x8000u);
+            w[i >> 1] |= c << (16 * (i & 1));
+        }
+        if constexpr (F == F_E4M3) {
+            st_stream8(p, make_uint2(w[0], w[1]));
+        } else {
+            Raw8 r;
+            r.a.x = w[0];
+            r.a.y = w[1];
+            decode8<F_E4M3>(r, v);
+            store8_float<F>(base, chunk, v);
+        }
+    } else {
+        uint32_t w = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            uint32_t c = (uint32_t)__nv_cvt_float2_to_fp4x2(make_float2(v[2 * i], v[2 * i + 1]), __NV_E2M1, cudaRoundNearest);
+            if (v[2 * i] == 0.0f) c &= 0xF7u;      // exact zero in -> +0 out
+            if (v[2 * i + 1] == 0.0f) c &= 0x7Fu;
+            w |= c << (8 * i);
+        }
+        if constexpr (F == F_FP4X2) {
+            st_stream4(p, w);
+        } else {
+            Raw8 r;
+            r.a.x = w;
+            float q[8];
+            decode8<F_FP4X2>(r, q);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = (v[i] != v[i]) ? v[i] : q[i];  // NaN stays NaN
+            store8_float<F>(base, chunk, v);
+        }
+    }
+}
+
+// Values (not codes) of the quantized grid for 8 clamped inputs: what round_to_quantized_type
+// returns before any cast.  Used by fake-quantize, which feeds them straight to the dequantize step.
+template <int QK>
+__device__ __forceinline__ void round8(float (&v)[8]) {
+    if constexpr (QK == QK_INT) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = rintf(v[i]);
+    } else if constexpr (QK == QK_FP8) {
+        Raw8 r;
+        r.a.x = r.a.y = 0u;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            uint32_t c = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(v[2 * i], v[2 * i + 1]), __NV_SATFINITE, __NV_E4M3);
+            if (i < 2) r.a.x |= c << (16 * (i & 1)); else r.a.y |= c << (16 * (i & 1));
+        }
+        float q[8];
+        decode8<F_E4M3>(r, q);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = (v[i] != v[i]) ? v[i] : q[i];
+    } else {
+        Raw8 r;
+        r.a.x = 0u;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            uint32_t c = (uint32_t)__nv_cvt_float2_to_fp4x2(make_float2(v[2 * i], v[2 * i + 1]), __NV_E2M1, cudaRoundNearest);
+            if (v[2 * i] == 0.0f) c &= 0xF7u;
+            if (v[2 * i + 1] == 0.0f) c &= 0x7Fu;
+            r.a.x |= c << (8 * i);
+        }
+        float q[8];
+        decode8<F_FP4X2>(r, q);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = (v[i] != v[i]) ? v[i] : q[i];
+    }
+}
+
+// qparam for a chunk, as fp32
+struct QP {
+    float s;   // effective scale (scale or scale / global_scale)
+    float r;   // 1 / s, correctly rounded
+    float zp;  // zero point value (0 when absent)
+    bool slow; // scale outside the range where the reciprocal path is proven exact
+};
+
+__device__ __forceinline__ QP load_qp(const void *scale, int sdt, const void *zp, int zdt, const float *gs, int64_t qi) {
+    QP q;
+    q.s = load_f32(scale, sdt, qi);
+    if (gs != nullptr) q.s = __fdiv_rn(q.s, __ldg(gs));  // forward.py:468-469 scale.to(f32) / global_scale
+    q.r = __frcp_rn(q.s);
+    q.zp = (zp != nullptr) ? load_f32(zp, zdt, qi) : 0.0f;
+    float a = fabsf(q.s);
+    q.slow = !(a >= 1.0e-30f && a <= 1.0e30f);
+    return q;
+}
+
+// x / scale rounded to the compute dtype T (forward.py:471 `scaled = x / scale`).
+//  T = bf16: both operands carry 8 significant bits, so the exact quotient is at least 2^-17
+//            (relative) away from every bf16 rounding boundary while x * rcp(s) is within 2^-23
+//            of it: rounding the product gives the same bf16 as rounding the IEEE quotient.
+//  otherwise: correctly rounded fp32 quotient (Markstein correction), then the rounding to T.
+template <int T>
+__device__ __forceinline__ float scaled_div(float x, const QP &q) {
+    if (q.slow) return round_to<T>(__fdiv_rn(x, q.s));
+    if constexpr (T == CTB_BF16) return round_to<T>(x * q.r);
+    else return round_to<T>(div_by_rcp(x, q.s, q.r));
+}
+
+// forward.py:471-481: scale, add zero point, clamp.  zp_x is zero_point.to(x.dtype).
+template <int T>
+__device__ __forceinline__ void quant_prepare8(float (&v)[8], const QP &q, bool has_zp, float zp_x, float qmin, float qmax) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        float t = scaled_div<T>(v[i], q);
+        if (has_zp) t = round_to<T>(t + zp_x);
+        v[i] = clamp_nan(t, qmin, qmax);
+    }
+}
+
+// forward.py:504-512: x_q.to(scale.dtype), subtract zero point, multiply by scale; all in Ts.
+template <int TS>
+__device__ __forceinline__ void dequant8(float (&v)[8], const QP &q, bool has_zp) {
+    float z = round_to<TS>(q.zp);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        float t = round_to<TS>(v[i]);
+        if (has_zp) t = round_to<TS>(t - z);
+        v[i] = round_to<TS>(t * q.s);
+    }
+}
+
+#endif  // __CUDACC__
+
+}  // namespace ctb

@@ -1,0 +1,362 @@
+// Block Hadamard rotation of Linear weights (transform/factory/hadamard.py:104-121 with
+// transform/utils/matrix.py:65-134) and the fused calibrate + quantize + pack kernels.
+//
+// Wh = diag(signs) @ H_n with H_n the Sylvester matrix, H[i][j] = (-1)^popcount(i & j)
+// (transform/utils/hadamard.py:33-89).  For a Linear weight W:
+//   weight_input,  forward: out[r, i] = signs[i] * FWHT(W[r, block])[i]
+//   weight_input,  inverse: out[r, i] = FWHT(signs * W[r, block])[i]
+//   weight_output, forward: out[i, c] = FWHT over the block's rows of (signs[row] * W[row, c])
+//   weight_output, inverse: out[i, c] = signs[i] * FWHT over rows of W[:, c]
+// each divided by sqrt(n) and rounded to the dtype of W.  The reference computes in float64; sums of
+// at most 256 bf16/fp16 values are exact in float64 whatever the order, so the float64 butterfly
+// below reproduces its matmul bit for bit.  The float32 mode trades that for speed.
+#include "ctb_codec.cuh"
+
+namespace ctb {
+
+constexpr int kThreads = 256;
+
+template <typename A>
+__device__ __forceinline__ A shfl_xor(A v, int o) {
+    if constexpr (sizeof(A) == 8) {
+        int lo = __double2loint(v), hi = __double2hiint(v);
+        lo = __shfl_xor_sync(0xFFFFFFFFu, lo, o);
+        hi = __shfl_xor_sync(0xFFFFFFFFu, hi, o);
+        return __hiloint2double(hi, lo);
+    } else {
+        return __shfl_xor_sync(0xFFFFFFFFu, v, o);
+    }
+}
+
+// in-register butterfly over the 8 elements a lane holds (index bits 0..2 of the block position)
+template <typename A>
+__device__ __forceinline__ void fwht8(A (&v)[8]) {
+#pragma unroll
+    for (int h = 1; h < 8; h <<= 1)
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if ((i & h) == 0) {
+                A a = v[i], b = v[i | h];
+                v[i] = a + b;
+                v[i | h] = a - b;
+            }
+}
+
+// cross-lane stages: lane bit k of the L lanes that share a block is index bit 3+k
+template <typename A>
+__device__ __forceinline__ void fwht_lanes(A (&v)[8], int L, int lane_in_block) {
+    for (int o = 1; o < L; o <<= 1) {
+        const bool upper = (lane_in_block & o) != 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            A other = shfl_xor<A>(v[i], o);
+            v[i] = upper ? (other - v[i]) : (v[i] + other);
+        }
+    }
+}
+
+struct HArgs {
+    const void *x;
+    const int8_t *signs;
+    void *out;        // rotated tensor (plain rotation) or quantized output (fused)
+    void *out_scale;  // fused only
+    const float *gs;  // fused fp4 only
+    int64_t chunks;   // rows * cols / 8
+    int n;            // Hadamard size (0 = no rotation, fused calibrate+quantize only)
+    int L;            // lanes per Hadamard block = n / 8
+    int inverse;
+    int GL;           // lanes per quantization group = col_group / 8 (fused)
+    int xdt;
+    float qmin, qmax, half_range;
+};
+
+// rotate the 8 values of this lane in place; returns them rounded to the dtype XF of the tensor
+template <typename A, int XF>
+__device__ __forceinline__ void rotate8(const HArgs &a, int64_t c, float (&v)[8]) {
+    const int lane_in_block = (int)(c & (a.L - 1));
+    float sg[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sg[i] = a.signs ? (float)a.signs[lane_in_block * 8 + i] : 1.0f;
+    A t[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) t[i] = (A)(a.inverse ? v[i] * sg[i] : v[i]);
+    fwht8<A>(t);
+    fwht_lanes<A>(t, a.L, lane_in_block);
+    if constexpr (sizeof(A) == 8) {
+        const double s = sqrt((double)a.n);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = (float)(t[i] / s);  // float64 quotient, then the cast chain of .to(dtype)
+    } else {
+        const float s = 1.0f / sqrtf((float)a.n);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = t[i] * s;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        if (!a.inverse) v[i] *= sg[i];
+        v[i] = round_to<XF == F_BF16 ? CTB_BF16 : XF == F_F16 ? CTB_F16 : CTB_F32>(v[i]);
+    }
+}
+
+// weight_input rotation: one 8-element chunk per lane
+template <typename A, int XF>
+__global__ void __launch_bounds__(kThreads) hadamard_cols_kernel(const HArgs a) {
+    const int64_t padded = (a.chunks + 31) & ~(int64_t)31;
+    for (int64_t c = (int64_t)blockIdx.x * kThreads + threadIdx.x; c < padded; c += (int64_t)gridDim.x * kThreads) {
+        float v[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        const bool live = c < a.chunks;
+        if (live) {
+            Raw8 r = load_raw<XF>(a.x, c);
+            decode8<XF>(r, v);
+        }
+        rotate8<A, XF>(a, c, v);
+        if (live) store8_float<XF>(a.out, c, v);
+    }
+}
+
+// weight_output rotation: a [n rows x 32 cols] tile per block, butterflies over rows in shared memory
+template <typename A>
+__global__ void __launch_bounds__(kThreads) hadamard_rows_kernel(const void *x, int dt, int64_t rows, int64_t cols, int n, const int8_t *signs,
+                                                                  int inverse, void *out) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    A *tile = reinterpret_cast<A *>(smem_raw);  // [n][33]
+    const int64_t col_tiles = (cols + 31) / 32, tiles = (rows / n) * col_tiles;
+    const A scale = (A)sqrt((double)n);
+    for (int64_t t = blockIdx.x; t < tiles; t += gridDim.x) {
+        const int64_t r0 = (t / col_tiles) * n, c0 = (t % col_tiles) * 32;
+        for (int i = threadIdx.x; i < n * 32; i += kThreads) {
+            int r = i >> 5, c = i & 31;
+            A v = 0;
+            if (c0 + c < cols) {
+                v = (A)load_f32(x, dt, (r0 + r) * cols + c0 + c);
+                if (!inverse && signs) v *= (A)signs[r];
+            }
+            tile[r * 33 + c] = v;
+        }
+        __syncthreads();
+        for (int h = 1; h < n; h <<= 1) {
+            for (int i = threadIdx.x; i < (n / 2) * 32; i += kThreads) {
+                int p = i >> 5, c = i & 31;
+                int r = ((p & ~(h - 1)) << 1) | (p & (h - 1));  // row with bit h clear
+                A u = tile[r * 33 + c], w = tile[(r | h) * 33 + c];
+                tile[r * 33 + c] = u + w;
+                tile[(r | h) * 33 + c] = u - w;
+            }
+            __syncthreads();
+        }
+        for (int i = threadIdx.x; i < n * 32; i += kThreads) {
+            int r = i >> 5, c = i & 31;
+            if (c0 + c < cols) {
+                A v = tile[r * 33 + c] / scale;
+                float f = (float)v;
+                if (inverse && signs) f *= (float)signs[r];
+                store_f32(out, dt, (r0 + r) * cols + c0 + c, f);
+            }
+        }
+        __syncthreads();
+    }
+}
+
+}  // namespace ctb
+
+// ------------------------------------------------------------------ fused calibrate + quantize + pack
+
+namespace ctb {
+
+// symmetric scale of one group from its absolute maximum, helpers.py:99-122, in the dtype M of the
+// tensor; returns the effective fp32 scale used by the quantize step and stores the qparam.
+template <int M, int QK>
+__device__ __forceinline__ float group_scale(float amax, const float *gs, float half_range, void *out_scale, int64_t gi, bool writer) {
+    if constexpr (QK == QK_FP4) {
+        float sc = __ldg(gs) * round_to<M>(__fdiv_rn(amax, 6.0f));
+        sc = clamp_nan(sc, -448.0f, 448.0f);
+        uint8_t b = f32_to_e4m3(sc);
+        if ((b & 0x7F) == 0) b = 0x20;  // zero scale -> 0.125
+        if (writer) ((uint8_t *)out_scale)[gi] = b;
+        return __fdiv_rn(e4m3_to_f32(b), __ldg(gs));  // forward.py:468-469
+    } else {
+        float sc = fmaxf(round_to<M>(__fdiv_rn(amax, half_range)), 1.1920928955078125e-07f);
+        if (writer) store_f32(out_scale, M, gi, sc);
+        return sc;
+    }
+}
+
+// groups of 8*GL consecutive elements (GL lanes, power of two <= 32), optional Hadamard in front.
+// A = float / double selects the rotation precision; ROT = false skips the rotation.
+template <typename A, bool ROT, int XF, int QK, int FOUT>
+__global__ void __launch_bounds__(kThreads) absmax_quant_group_kernel(const HArgs a) {
+    constexpr int M = XF == F_BF16 ? CTB_BF16 : XF == F_F16 ? CTB_F16 : CTB_F32;
+    constexpr int T = QK == QK_FP4 ? CTB_F32 : M;
+    const int64_t padded = (a.chunks + 31) & ~(int64_t)31;
+    for (int64_t c = (int64_t)blockIdx.x * kThreads + threadIdx.x; c < padded; c += (int64_t)gridDim.x * kThreads) {
+        float v[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        const bool live = c < a.chunks;
+        if (live) {
+            Raw8 r = load_raw<XF>(a.x, c);
+            decode8<XF>(r, v);
+        }
+        if constexpr (ROT) rotate8<A, XF>(a, c, v);
+        float amax = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+        for (int o = a.GL >> 1; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+        QP q;
+        q.s = group_scale<M, QK>(amax, a.gs, a.half_range, a.out_scale, c / a.GL, live && (c & (a.GL - 1)) == 0);
+        q.r = __frcp_rn(q.s);
+        q.zp = 0.0f;
+        q.slow = !(fabsf(q.s) >= 1.0e-30f && fabsf(q.s) <= 1.0e30f);
+        // the zero point calculate_qparams returns is all zeros; adding it matters only for the sign of an
+        // fp8 zero (-0.0 + 0.0 = +0.0)
+        quant_prepare8<T>(v, q, QK == QK_FP8, 0.0f, a.qmin, a.qmax);
+        if (live) encode_store8<QK, FOUT>(a.out, c, v);
+    }
+}
+
+// one block per row (CHANNEL / TOKEN): first sweep finds the row's absolute maximum, second sweep
+// re-reads the row (it is still in L1/L2) and quantizes it.
+template <int XF, int QK, int FOUT>
+__global__ void __launch_bounds__(kThreads) absmax_quant_row_kernel(const HArgs a, int64_t rows, int64_t cpr) {
+    constexpr int M = XF == F_BF16 ? CTB_BF16 : XF == F_F16 ? CTB_F16 : CTB_F32;
+    __shared__ float red[kThreads / 32];
+    for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+        float amax = 0.0f;
+        for (int64_t c = threadIdx.x; c < cpr; c += kThreads) {
+            const uint4 *p = reinterpret_cast<const uint4 *>((const char *)a.x + (r * cpr + c) * chunk_bytes(XF));
+            Raw8 raw;
+            raw.a = p[0];
+            if constexpr (XF == F_F32) raw.b = p[1];
+            float v[8];
+            decode8<XF>(raw, v);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+        }
+        for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+        __syncthreads();
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < kThreads / 32; ++i) amax = fmaxf(amax, red[i]);
+        QP q;
+        q.s = group_scale<M, QK>(amax, a.gs, a.half_range, a.out_scale, r, threadIdx.x == 0);
+        q.r = __frcp_rn(q.s);
+        q.zp = 0.0f;
+        q.slow = !(fabsf(q.s) >= 1.0e-30f && fabsf(q.s) <= 1.0e30f);
+        for (int64_t c = threadIdx.x; c < cpr; c += kThreads) {
+            Raw8 raw = load_raw<XF>(a.x, r * cpr + c);
+            float v[8];
+            decode8<XF>(raw, v);
+            quant_prepare8<M>(v, q, QK == QK_FP8, 0.0f, a.qmin, a.qmax);
+            encode_store8<QK, FOUT>(a.out, r * cpr + c, v);
+        }
+    }
+}
+
+}  // namespace ctb
+
+// ------------------------------------------------------------------ entry points
+
+using namespace ctb;
+
+static bool pow2(int64_t v) { return v > 0 && (v & (v - 1)) == 0; }
+
+extern "C" int ctb_hadamard(const void *x, int32_t dtype, int64_t rows, int64_t cols, int32_t n, const int8_t *signs, int32_t inverse,
+                            int32_t side, int32_t precision, void *out, void *stream) {
+    if (!x || !out) return fail(CTB_EINVAL_NULL, "null buffer");
+    if (!is_float_dtype(dtype)) return fail(CTB_EINVAL_DTYPE, "weights must be bf16, f16 or f32");
+    if (!pow2(n)) return fail(CTB_EUNSUPPORTED, "only Sylvester sizes (powers of two) are built");
+    if (precision != CTB_F64 && precision != CTB_F32) return fail(CTB_EINVAL_DTYPE, "precision must be F64 or F32");
+    if (rows < 0 || cols < 0) return fail(CTB_EINVAL_SHAPE, "negative shape");
+    if (rows == 0 || cols == 0) return CTB_OK;
+    cudaStream_t st = as_stream(stream);
+    if (side == 0) {
+        if (cols % n) return fail(CTB_EINVAL_SHAPE, "columns %lld are not a multiple of the Hadamard size %d", (long long)cols, n);
+        if (n >= 8 && n <= 256 && aligned16(x) && aligned16(out)) {
+            HArgs a{};
+            a.x = x; a.signs = signs; a.out = out; a.chunks = rows * cols / 8; a.n = n; a.L = n / 8; a.inverse = inverse; a.xdt = dtype;
+            int grid = grid_for(a.chunks, kThreads, 8);
+#define CTB_HC(A_)                                                                                   \
+    if (dtype == CTB_BF16) hadamard_cols_kernel<A_, F_BF16><<<grid, kThreads, 0, st>>>(a);            \
+    else if (dtype == CTB_F16) hadamard_cols_kernel<A_, F_F16><<<grid, kThreads, 0, st>>>(a);         \
+    else hadamard_cols_kernel<A_, F_F32><<<grid, kThreads, 0, st>>>(a);
+            if (precision == CTB_F64) { CTB_HC(double) } else { CTB_HC(float) }
+            return after_launch("hadamard_cols_kernel");
+        }
+        return fail(CTB_EUNSUPPORTED, "weight_input rotation needs 8 <= n <= 256 and 16-byte aligned buffers");
+    }
+    if (side != 1) return fail(CTB_EINVAL_SHAPE, "side must be 0 (weight_input) or 1 (weight_output)");
+    if (rows % n) return fail(CTB_EINVAL_SHAPE, "rows %lld are not a multiple of the Hadamard size %d", (long long)rows, n);
+    if (n > 512) return fail(CTB_EUNSUPPORTED, "weight_output rotation is built for n <= 512");
+    int64_t tiles = (rows / n) * cdiv(cols, 32);
+    int grid = grid_for(tiles, 1, 2);
+    if (precision == CTB_F64) {
+        size_t smem = (size_t)n * 33 * sizeof(double);
+        cudaFuncSetAttribute(hadamard_rows_kernel<double>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        hadamard_rows_kernel<double><<<grid, kThreads, smem, st>>>(x, dtype, rows, cols, n, signs, inverse, out);
+    } else {
+        size_t smem = (size_t)n * 33 * sizeof(float);
+        cudaFuncSetAttribute(hadamard_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        hadamard_rows_kernel<float><<<grid, kThreads, smem, st>>>(x, dtype, rows, cols, n, signs, inverse, out);
+    }
+    return after_launch("hadamard_rows_kernel");
+}
+
+extern "C" int ctb_absmax_quantize(const ctb_qdesc *d, const void *x, const float *gs, void *out_scale, void *out, int32_t n,
+                                   const int8_t *signs, int32_t precision, void *stream) {
+    if (!d || !x || !out_scale || !out) return fail(CTB_EINVAL_NULL, "null descriptor or buffer");
+    if (d->x_dtype != CTB_BF16) return fail(CTB_EUNSUPPORTED, "fused calibration is built for bf16 tensors");
+    if (d->rows < 0 || d->cols <= 0 || d->col_group <= 0 || d->cols % d->col_group) return fail(CTB_EINVAL_SHAPE, "tensor column shape must be divisble by the given group_size");
+    if (d->row_group != 1) return fail(CTB_EUNSUPPORTED, "fused calibration does not take 2-D blocks");
+    if (d->cols % 8 || d->col_group % 8 || !aligned16(x) || !aligned16(out)) return fail(CTB_EINVAL_ALIGN, "needs cols %% 8 == 0, group %% 8 == 0 and 16-byte aligned buffers");
+    const int qk = d->qtype == CTB_QINT ? QK_INT : (d->num_bits == 8 ? QK_FP8 : QK_FP4);
+    if (qk == QK_FP4 && (!gs || d->scale_dtype != CTB_E4M3)) return fail(CTB_EINVAL_DTYPE, "fp4 needs a global scale and e4m3 group scales");
+    if (qk != QK_FP4 && d->scale_dtype != d->x_dtype) return fail(CTB_EINVAL_DTYPE, "scales are produced in the dtype of the tensor");
+    int fout = F_NONE;
+    if (d->codec == CTB_CODE_PACK32 && qk == QK_INT && d->num_bits == 4) fout = F_PACK4;
+    else if (d->codec == CTB_CODE_PACK32 && qk == QK_INT && d->num_bits == 8) fout = F_PACK8;
+    else if (d->codec == CTB_CODE_DTYPE && qk == QK_INT && d->q_dtype == CTB_I8) fout = F_I8;
+    else if (d->codec == CTB_CODE_DTYPE && qk == QK_FP8 && d->q_dtype == CTB_E4M3) fout = F_E4M3;
+    else if (d->codec == CTB_CODE_FP4X2 && qk == QK_FP4) fout = F_FP4X2;
+    else return fail(CTB_EUNSUPPORTED, "fused calibration writes PACK32 (4/8 bit), int8, e4m3 or FP4X2");
+    if (d->rows == 0) return CTB_OK;
+    HArgs a{};
+    a.x = x; a.signs = signs; a.out = out; a.out_scale = out_scale; a.gs = gs;
+    a.chunks = d->rows * d->cols / 8; a.n = n; a.L = n > 0 ? n / 8 : 1; a.inverse = 0; a.xdt = d->x_dtype;
+    if (qk == QK_INT) { a.qmax = (float)(1 << d->num_bits) / 2 - 1; a.qmin = -(float)(1 << d->num_bits) / 2; }
+    else if (qk == QK_FP8) { a.qmax = 448.0f; a.qmin = -448.0f; }
+    else { a.qmax = 6.0f; a.qmin = -6.0f; }
+    a.half_range = (a.qmax - a.qmin) / 2.0f;
+    cudaStream_t st = as_stream(stream);
+    const int64_t GL = d->col_group / 8;
+    if (n > 0) {
+        if (!pow2(n) || n < 8 || n > 256 || d->cols % n) return fail(CTB_EINVAL_SHAPE, "Hadamard size must be a power of two in 8..256 dividing the columns");
+        if (precision != CTB_F64 && precision != CTB_F32) return fail(CTB_EINVAL_DTYPE, "precision must be F64 or F32");
+        if (!(pow2(GL) && GL <= 32)) return fail(CTB_EUNSUPPORTED, "with a rotation in front the group must be a power of two <= 256");
+        if (fout != F_PACK4) return fail(CTB_EUNSUPPORTED, "the fused rotation is built for int4 PACK32 output");
+        a.GL = (int)GL;
+        int grid = grid_for(a.chunks, kThreads, 8);
+        if (precision == CTB_F64) absmax_quant_group_kernel<double, true, F_BF16, QK_INT, F_PACK4><<<grid, kThreads, 0, st>>>(a);
+        else absmax_quant_group_kernel<float, true, F_BF16, QK_INT, F_PACK4><<<grid, kThreads, 0, st>>>(a);
+        return after_launch("absmax_quant_group_kernel");
+    }
+    if (pow2(GL) && GL <= 32 && d->scale_row_stride == d->cols / d->col_group) {
+        a.GL = (int)GL;
+        int grid = grid_for(a.chunks, kThreads, 8);
+#define CTB_AQ(QK_, FOUT_) absmax_quant_group_kernel<float, false, F_BF16, QK_, FOUT_><<<grid, kThreads, 0, st>>>(a)
+        if (fout == F_PACK4) CTB_AQ(QK_INT, F_PACK4);
+        else if (fout == F_PACK8) CTB_AQ(QK_INT, F_PACK8);
+        else if (fout == F_I8) CTB_AQ(QK_INT, F_I8);
+        else if (fout == F_E4M3) CTB_AQ(QK_FP8, F_E4M3);
+        else CTB_AQ(QK_FP4, F_FP4X2);
+        return after_launch("absmax_quant_group_kernel");
+    }
+    if (d->col_group == d->cols && d->scale_row_stride == 1 && qk != QK_FP4) {
+        int grid = grid_for(d->rows, 1, 8);
+        const int64_t cpr = d->cols / 8;
+        if (fout == F_E4M3) absmax_quant_row_kernel<F_BF16, QK_FP8, F_E4M3><<<grid, kThreads, 0, st>>>(a, d->rows, cpr);
+        else if (fout == F_I8) absmax_quant_row_kernel<F_BF16, QK_INT, F_I8><<<grid, kThreads, 0, st>>>(a, d->rows, cpr);
+        else if (fout == F_PACK8) absmax_quant_row_kernel<F_BF16, QK_INT, F_PACK8><<<grid, kThreads, 0, st>>>(a, d->rows, cpr);
+        else absmax_quant_row_kernel<F_BF16, QK_INT, F_PACK4><<<grid, kThreads, 0, st>>>(a, d->rows, cpr);
+        return after_launch("absmax_quant_row_kernel");
+    }
+    return fail(CTB_EUNSUPPORTED, "fused calibration takes groups of 8..256 (power of two) or whole rows");
+}

@@ -1,0 +1,141 @@
+// Stand-alone packing entry points (the fused kernels in ctb_quant.cu cover the hot path; these exist so
+// that pack_to_int32 / unpack_from_int32 / pack_fp4_to_uint8 / unpack_fp4_from_uint8 / pack_bitmasks /
+// unpack_bitmasks keep working as separate calls with identical results).
+#include "ctb_codec.cuh"
+
+namespace ctb {
+
+constexpr int kThreads = 256;
+
+// compressors/quantized_compressors/pack_quantized.py:186-246; one thread per output word
+__global__ void __launch_bounds__(kThreads) pack_int32_kernel(const int8_t *v, int64_t rows, int64_t cols, int64_t rs, int64_t cs, int bits, int32_t *out) {
+    const int pf = 32 / bits, offset = 1 << (bits - 1);
+    const int64_t pc = (cols + pf - 1) / pf, n = rows * pc;
+    for (int64_t u = (int64_t)blockIdx.x * kThreads + threadIdx.x; u < n; u += (int64_t)gridDim.x * kThreads) {
+        int64_t r = u / pc, c0 = (u - r * pc) * pf;
+        uint32_t w = 0;
+        for (int k = 0; k < pf && c0 + k < cols; ++k)
+            w += (uint32_t)(uint8_t)(v[r * rs + (c0 + k) * cs] + offset) << (bits * k);  // :220, :241-242 (pad fields stay 0)
+        out[u] = (int32_t)w;
+    }
+}
+
+// pack_quantized.py:249-309; one thread per output element
+__global__ void __launch_bounds__(kThreads) unpack_int32_kernel(const int32_t *w, int64_t rows, int64_t cols, int64_t rs, int64_t cs, int bits, int8_t *out) {
+    const int pf = 32 / bits;
+    const int32_t mask = (1 << bits) - 1, offset = (1 << bits) / 2;
+    const int64_t n = rows * cols;
+    for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += (int64_t)gridDim.x * kThreads) {
+        int64_t r = i / cols, c = i - r * cols;
+        int32_t word = w[r * rs + (c / pf) * cs];
+        out[i] = (int8_t)(((word >> (bits * (int)(c % pf))) & mask) - offset);
+    }
+}
+
+// compressors/quantized_compressors/fp4_quantized.py:135-178; nearest grid magnitude (first minimum wins,
+// like torch.argmin), sign from signbit; one thread per output byte
+__device__ __forceinline__ uint32_t nearest_e2m1(float x, int dt) {
+    const float grid[8] = {0.0f, 0.5f, 1.0f, 1.5f, 2.0f, 3.0f, 4.0f, 6.0f};
+    float a = fabsf(x);
+    int best = 0;
+    float bd = round_to_rt(dt, fabsf(round_to_rt(dt, a - grid[0])));
+#pragma unroll
+    for (int k = 1; k < 8; ++k) {
+        float d = round_to_rt(dt, fabsf(round_to_rt(dt, a - grid[k])));
+        if (d < bd) { bd = d; best = k; }
+    }
+    return (uint32_t)best | ((__float_as_uint(x) >> 31) << 3);
+}
+
+__global__ void __launch_bounds__(kThreads) pack_fp4_kernel(const void *x, int dt, int64_t nbytes, uint8_t *out) {
+    for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < nbytes; i += (int64_t)gridDim.x * kThreads)
+        out[i] = (uint8_t)(nearest_e2m1(load_f32(x, dt, 2 * i), dt) | (nearest_e2m1(load_f32(x, dt, 2 * i + 1), dt) << 4));
+}
+
+// fp4_quantized.py:187-221
+__global__ void __launch_bounds__(kThreads) unpack_fp4_kernel(const uint8_t *a, int64_t nbytes, void *out, int odt) {
+    const float grid[8] = {0.0f, 0.5f, 1.0f, 1.5f, 2.0f, 3.0f, 4.0f, 6.0f};
+    for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < nbytes; i += (int64_t)gridDim.x * kThreads) {
+        uint32_t b = a[i];
+        float lo = grid[b & 7], hi = grid[(b >> 4) & 7];
+        store_f32(out, odt, 2 * i, (b & 0x08) ? -lo : lo);
+        store_f32(out, odt, 2 * i + 1, (b & 0x80) ? -hi : hi);
+    }
+}
+
+// utils/helpers.py:302-313; one thread per output byte
+__global__ void __launch_bounds__(kThreads) pack_bitmasks_kernel(const uint8_t *m, int64_t rows, int64_t cols, uint8_t *out) {
+    const int64_t pc = (cols + 7) / 8, n = rows * pc;
+    for (int64_t u = (int64_t)blockIdx.x * kThreads + threadIdx.x; u < n; u += (int64_t)gridDim.x * kThreads) {
+        int64_t r = u / pc, c0 = (u - r * pc) * 8;
+        uint32_t b = 0;
+        for (int j = 0; j < 8 && c0 + j < cols; ++j) b |= (m[r * cols + c0 + j] != 0 ? 1u : 0u) << j;
+        out[u] = (uint8_t)b;
+    }
+}
+
+// utils/helpers.py:316-339
+__global__ void __launch_bounds__(kThreads) unpack_bitmasks_kernel(const uint8_t *p, int64_t rows, int64_t cols, uint8_t *out) {
+    const int64_t pc = (cols + 7) / 8, n = rows * cols;
+    for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += (int64_t)gridDim.x * kThreads) {
+        int64_t r = i / cols, c = i - r * cols;
+        out[i] = (p[r * pc + (c >> 3)] >> (c & 7)) & 1u;
+    }
+}
+
+}  // namespace ctb
+
+using namespace ctb;
+
+extern "C" int ctb_pack_int32(const int8_t *value, int64_t rows, int64_t cols, int64_t rs, int64_t cs, int32_t bits, int32_t *out, void *stream) {
+    if (!value || !out) return fail(CTB_EINVAL_NULL, "null buffer");
+    if (bits > 8) return fail(CTB_EINVAL_SHAPE, "Packing is only supported for less than 8 bits");
+    if (bits < 1) return fail(CTB_EINVAL_SHAPE, "num_bits must be at least 1, got %d", bits);
+    if (rows < 0 || cols < 0) return fail(CTB_EINVAL_SHAPE, "negative shape");
+    int64_t n = rows * cdiv(cols, 32 / bits);
+    if (n == 0) return CTB_OK;
+    pack_int32_kernel<<<grid_for(n, kThreads, 8), kThreads, 0, as_stream(stream)>>>(value, rows, cols, rs, cs, bits, out);
+    return after_launch("pack_int32_kernel");
+}
+
+extern "C" int ctb_unpack_int32(const int32_t *words, int64_t rows, int64_t cols, int64_t rs, int64_t cs, int32_t bits, int8_t *out, void *stream) {
+    if (!words || !out) return fail(CTB_EINVAL_NULL, "null buffer");
+    if (bits > 8) return fail(CTB_EINVAL_SHAPE, "Unpacking is only supported for less than 8 bits");
+    if (bits < 1) return fail(CTB_EINVAL_SHAPE, "num_bits must be at least 1, got %d", bits);
+    if (rows < 0 || cols < 0) return fail(CTB_EINVAL_SHAPE, "negative shape");
+    if (rows * cols == 0) return CTB_OK;
+    unpack_int32_kernel<<<grid_for(rows * cols, kThreads, 8), kThreads, 0, as_stream(stream)>>>(words, rows, cols, rs, cs, bits, out);
+    return after_launch("unpack_int32_kernel");
+}
+
+extern "C" int ctb_pack_fp4(const void *x, int32_t dtype, int64_t m, int64_t n, uint8_t *out, void *stream) {
+    if (!x || !out) return fail(CTB_EINVAL_NULL, "null buffer");
+    if (n % 2 != 0) return fail(CTB_EINVAL_SHAPE, "tensor must have an even number of columns for nvfp4 compression");
+    if (!is_float_dtype(dtype)) return fail(CTB_EINVAL_DTYPE, "fp4 values must be held in bf16, f16 or f32");
+    if (m * n == 0) return CTB_OK;
+    pack_fp4_kernel<<<grid_for(m * n / 2, kThreads, 8), kThreads, 0, as_stream(stream)>>>(x, dtype, m * n / 2, out);
+    return after_launch("pack_fp4_kernel");
+}
+
+extern "C" int ctb_unpack_fp4(const uint8_t *packed, int64_t m, int64_t n, void *out, int32_t odt, void *stream) {
+    if (!packed || !out) return fail(CTB_EINVAL_NULL, "null buffer");
+    if (n % 2 != 0) return fail(CTB_EINVAL_SHAPE, "odd column count");
+    if (!is_float_dtype(odt)) return fail(CTB_EINVAL_DTYPE, "output must be bf16, f16 or f32");
+    if (m * n == 0) return CTB_OK;
+    unpack_fp4_kernel<<<grid_for(m * n / 2, kThreads, 8), kThreads, 0, as_stream(stream)>>>(packed, m * n / 2, out, odt);
+    return after_launch("unpack_fp4_kernel");
+}
+
+extern "C" int ctb_pack_bitmasks(const uint8_t *bytemask, int64_t rows, int64_t cols, uint8_t *out, void *stream) {
+    if (!bytemask || !out) return fail(CTB_EINVAL_NULL, "null buffer");
+    if (rows * cols == 0) return CTB_OK;
+    pack_bitmasks_kernel<<<grid_for(rows * cdiv(cols, 8), kThreads, 8), kThreads, 0, as_stream(stream)>>>(bytemask, rows, cols, out);
+    return after_launch("pack_bitmasks_kernel");
+}
+
+extern "C" int ctb_unpack_bitmasks(const uint8_t *packed, int64_t rows, int64_t cols, uint8_t *out, void *stream) {
+    if (!packed || !out) return fail(CTB_EINVAL_NULL, "null buffer");
+    if (rows * cols == 0) return CTB_OK;
+    unpack_bitmasks_kernel<<<grid_for(rows * cols, kThreads, 8), kThreads, 0, as_stream(stream)>>>(packed, rows, cols, out);
+    return after_launch("unpack_bitmasks_kernel");
+}

@@ -1,0 +1,228 @@
+// Quantization parameters: tile min/max (quantization/utils/helpers.py:149-205), calculate_qparams
+// (:67-146) and generate_gparam (:414-434).
+#include <algorithm>
+#include <cfloat>
+
+#include "ctb_codec.cuh"
+
+namespace ctb {
+
+constexpr int kThreads = 256;
+
+__device__ __forceinline__ void warp_minmax(float &mn, float &mx, int width) {
+    for (int o = width >> 1; o > 0; o >>= 1) {
+        mn = fminf(mn, __shfl_xor_sync(0xFFFFFFFFu, mn, o));
+        mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+    }
+}
+
+__device__ __forceinline__ void block_minmax(float &mn, float &mx) {
+    __shared__ float smn[kThreads / 32], smx[kThreads / 32];
+    warp_minmax(mn, mx, 32);
+    int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+    __syncthreads();  // protects reuse of the shared arrays across calls
+    if (l == 0) { smn[w] = mn; smx[w] = mx; }
+    __syncthreads();
+    mn = (l < kThreads / 32) ? smn[l] : FLT_MAX;
+    mx = (l < kThreads / 32) ? smx[l] : -FLT_MAX;
+    mn = (threadIdx.x < 32) ? mn : FLT_MAX;
+    warp_minmax(mn, mx, 32);  // every warp ends with the block result in all lanes of warp 0
+}
+
+template <int F>
+__device__ __forceinline__ void chunk_minmax(const void *x, int64_t chunk, float &mn, float &mx) {
+    float v[8];
+    Raw8 r = load_raw<F>(x, chunk);
+    decode8<F>(r, v);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { mn = fminf(mn, v[i]); mx = fmaxf(mx, v[i]); }
+}
+
+// (a) groups of 8*L consecutive elements inside a row, L a power of two <= 32: one chunk per lane,
+//     L lanes cooperate through shuffles.  Flat indexing: group g covers chunks [g*L, (g+1)*L).
+template <int F>
+__global__ void __launch_bounds__(kThreads) minmax_group_kernel(const void *x, int64_t chunks, int L, int dt, void *out_min, void *out_max) {
+    const int64_t stride = (int64_t)gridDim.x * kThreads;
+    const int64_t padded = (chunks + 31) & ~(int64_t)31;  // whole warps stay in the loop for the shuffles
+    for (int64_t c = (int64_t)blockIdx.x * kThreads + threadIdx.x; c < padded; c += stride) {
+        float mn = FLT_MAX, mx = -FLT_MAX;
+        if (c < chunks) chunk_minmax<F>(x, c, mn, mx);
+        warp_minmax(mn, mx, L);
+        if (c < chunks && (c & (L - 1)) == 0) {
+            store_f32(out_min, dt, c / L, mn);
+            store_f32(out_max, dt, c / L, mx);
+        }
+    }
+}
+
+// (b) one block per [row_group x col_group] tile, any shape and alignment (scalar loads)
+__global__ void __launch_bounds__(kThreads) minmax_tile_kernel(const void *x, int dt, int64_t rows, int64_t cols, int64_t rg, int64_t cg,
+                                                                void *out_min, void *out_max) {
+    const int64_t tiles_c = cols / cg, tiles = (rows / rg) * tiles_c;
+    for (int64_t t = blockIdx.x; t < tiles; t += gridDim.x) {
+        int64_t r0 = (t / tiles_c) * rg, c0 = (t % tiles_c) * cg;
+        float mn = FLT_MAX, mx = -FLT_MAX;
+        for (int64_t i = threadIdx.x; i < rg * cg; i += kThreads) {
+            float v = load_f32(x, dt, (r0 + i / cg) * cols + c0 + i % cg);
+            mn = fminf(mn, v);
+            mx = fmaxf(mx, v);
+        }
+        block_minmax(mn, mx);
+        if (threadIdx.x == 0) { store_f32(out_min, dt, t, mn); store_f32(out_max, dt, t, mx); }
+    }
+}
+
+// (b') one block per row, 128-bit loads (CHANNEL / TOKEN: the tile is a whole row)
+template <int F>
+__global__ void __launch_bounds__(kThreads) minmax_row_kernel(const void *x, int dt, int64_t rows, int64_t cpr, void *out_min, void *out_max) {
+    for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+        float mn = FLT_MAX, mx = -FLT_MAX;
+        for (int64_t c = threadIdx.x; c < cpr; c += kThreads) chunk_minmax<F>(x, r * cpr + c, mn, mx);
+        block_minmax(mn, mx);
+        if (threadIdx.x == 0) { store_f32(out_min, dt, r, mn); store_f32(out_max, dt, r, mx); }
+    }
+}
+
+// (c) one tile = the whole tensor: per-block partials into the workspace, then a one-block finish
+template <int F>
+__global__ void __launch_bounds__(kThreads) minmax_flat_kernel(const void *x, int dt, int64_t n, float *partial) {
+    float mn = FLT_MAX, mx = -FLT_MAX;
+    const int64_t chunks = n / 8;
+    for (int64_t c = (int64_t)blockIdx.x * kThreads + threadIdx.x; c < chunks; c += (int64_t)gridDim.x * kThreads)
+        chunk_minmax<F>(x, c, mn, mx);
+    if (blockIdx.x == 0)
+        for (int64_t i = chunks * 8 + threadIdx.x; i < n; i += kThreads) {  // ragged tail
+            float v = load_f32(x, dt, i);
+            mn = fminf(mn, v);
+            mx = fmaxf(mx, v);
+        }
+    block_minmax(mn, mx);
+    if (threadIdx.x == 0) { partial[2 * blockIdx.x] = mn; partial[2 * blockIdx.x + 1] = mx; }
+}
+
+__global__ void __launch_bounds__(kThreads) minmax_finish_kernel(const float *partial, int n, int dt, void *out_min, void *out_max) {
+    float mn = FLT_MAX, mx = -FLT_MAX;
+    for (int i = threadIdx.x; i < n; i += kThreads) { mn = fminf(mn, partial[2 * i]); mx = fmaxf(mx, partial[2 * i + 1]); }
+    block_minmax(mn, mx);
+    if (threadIdx.x == 0) { store_f32(out_min, dt, 0, mn); store_f32(out_max, dt, 0, mx); }
+}
+
+// helpers.py:67-146, one thread per (min, max) pair
+__global__ void __launch_bounds__(kThreads) qparams_kernel(const void *mins, const void *maxs, int M, int64_t n, int qtype, int bits, int symmetric,
+                                                            const float *gs, void *out_scale, void *out_zp, int zdt) {
+    const float eps = 1.1920928955078125e-07f;  // torch.finfo(torch.float32).eps
+    float qmin, qmax;
+    if (qtype == CTB_QINT) { qmax = (float)(1 << bits) / 2 - 1; qmin = -(float)(1 << bits) / 2; }
+    else if (bits == 8) { qmax = 448.0f; qmin = -448.0f; }
+    else { qmax = 6.0f; qmin = -6.0f; }
+    const float bit_range = qmax - qmin;
+    const bool fp4 = qtype == CTB_QFLOAT && bits == 4;
+    for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += (int64_t)gridDim.x * kThreads) {
+        float mn = fminf(load_f32(mins, M, i), 0.0f);  // :87-88 zero stays representable
+        float mx = fmaxf(load_f32(maxs, M, i), 0.0f);
+        float zp = 0.0f;
+        if (symmetric) {
+            float mvp = fmaxf(fabsf(mn), fabsf(mx));
+            if (fp4 && gs != nullptr) {
+                // :103-120  e4m3(clamp(global_scale * (amax / 6))) with 0 replaced by 0.125
+                float sc = gs[0] * round_to_rt(M, __fdiv_rn(mvp, 6.0f));
+                sc = clamp_nan(sc, -448.0f, 448.0f);
+                uint8_t b = f32_to_e4m3(sc);
+                if ((b & 0x7F) == 0) b = 0x20;
+                ((uint8_t *)out_scale)[i] = b;
+            } else {
+                float sc = round_to_rt(M, __fdiv_rn(mvp, bit_range / 2.0f));  // :110
+                store_f32(out_scale, M, i, fmaxf(sc, eps));                  // :122
+            }
+        } else {
+            float sc = round_to_rt(M, __fdiv_rn(round_to_rt(M, mx - mn), bit_range));  // :131
+            sc = round_to_rt(M, fmaxf(sc, eps));
+            zp = round_to_rt(M, qmin - round_to_rt(M, __fdiv_rn(mn, sc)));             // :133
+            zp = clamp_nan(zp, qmin, qmax);
+            store_f32(out_scale, M, i, sc);
+        }
+        if (qtype == CTB_QINT) zp = rintf(zp);  // :138-139
+        store_f32(out_zp, zdt, i, zp);
+    }
+}
+
+// helpers.py:414-434
+__global__ void gparam_kernel(const void *mn_p, const void *mx_p, int M, float *out) {
+    float mn = fminf(load_f32(mn_p, M, 0), 0.0f), mx = fmaxf(load_f32(mx_p, M, 0), 0.0f);
+    out[0] = round_to_rt(M, __fdiv_rn(2688.0f, fmaxf(fabsf(mn), fabsf(mx))));
+}
+
+static int flat_blocks() { return sm_count() * 4; }
+
+}  // namespace ctb
+
+using namespace ctb;
+
+extern "C" int64_t ctb_minmax_workspace_bytes(int64_t rows, int64_t cols, int64_t row_group, int64_t col_group) {
+    if (row_group == rows && col_group == cols) return (int64_t)flat_blocks() * 2 * sizeof(float);
+    return 0;
+}
+
+extern "C" int ctb_minmax(const void *x, int32_t dt, int64_t rows, int64_t cols, int64_t rg, int64_t cg, void *out_min, void *out_max,
+                          void *workspace, void *stream) {
+    if (!x || !out_min || !out_max) return fail(CTB_EINVAL_NULL, "null buffer");
+    if (!is_float_dtype(dt)) return fail(CTB_EINVAL_DTYPE, "min/max needs bf16, f16 or f32");
+    if (rows <= 0 || cols <= 0 || rg <= 0 || cg <= 0 || rows % rg || cols % cg) return fail(CTB_EINVAL_SHAPE, "tiles must divide the tensor");
+    cudaStream_t st = as_stream(stream);
+    const int F = dt == CTB_BF16 ? F_BF16 : dt == CTB_F16 ? F_F16 : F_F32;
+    const bool vec = aligned16(x) && cols % 8 == 0;
+    if (rg == rows && cg == cols) {  // whole tensor
+        if (!workspace) return fail(CTB_EINVAL_NULL, "whole-tensor min/max needs the workspace");
+        if (!aligned16(x)) return fail(CTB_EINVAL_ALIGN, "x must be 16-byte aligned");
+        int blocks = (int)std::min<int64_t>(flat_blocks(), std::max<int64_t>(1, cdiv(rows * cols / 8, kThreads)));
+        float *part = (float *)workspace;
+        if (F == F_BF16) minmax_flat_kernel<F_BF16><<<blocks, kThreads, 0, st>>>(x, dt, rows * cols, part);
+        else if (F == F_F16) minmax_flat_kernel<F_F16><<<blocks, kThreads, 0, st>>>(x, dt, rows * cols, part);
+        else minmax_flat_kernel<F_F32><<<blocks, kThreads, 0, st>>>(x, dt, rows * cols, part);
+        int rc = after_launch("minmax_flat_kernel");
+        if (rc) return rc;
+        minmax_finish_kernel<<<1, kThreads, 0, st>>>(part, blocks, dt, out_min, out_max);
+        return after_launch("minmax_finish_kernel");
+    }
+    if (vec && rg == 1 && cg % 8 == 0) {
+        int64_t L = cg / 8;
+        if (L <= 32 && (L & (L - 1)) == 0) {
+            int64_t chunks = rows * cols / 8;
+            int grid = grid_for(chunks, kThreads, 8);
+            if (F == F_BF16) minmax_group_kernel<F_BF16><<<grid, kThreads, 0, st>>>(x, chunks, (int)L, dt, out_min, out_max);
+            else if (F == F_F16) minmax_group_kernel<F_F16><<<grid, kThreads, 0, st>>>(x, chunks, (int)L, dt, out_min, out_max);
+            else minmax_group_kernel<F_F32><<<grid, kThreads, 0, st>>>(x, chunks, (int)L, dt, out_min, out_max);
+            return after_launch("minmax_group_kernel");
+        }
+        if (cg == cols) {
+            int grid = grid_for(rows, 1, 8);
+            if (F == F_BF16) minmax_row_kernel<F_BF16><<<grid, kThreads, 0, st>>>(x, dt, rows, cols / 8, out_min, out_max);
+            else if (F == F_F16) minmax_row_kernel<F_F16><<<grid, kThreads, 0, st>>>(x, dt, rows, cols / 8, out_min, out_max);
+            else minmax_row_kernel<F_F32><<<grid, kThreads, 0, st>>>(x, dt, rows, cols / 8, out_min, out_max);
+            return after_launch("minmax_row_kernel");
+        }
+    }
+    int grid = grid_for((rows / rg) * (cols / cg), 1, 8);
+    minmax_tile_kernel<<<grid, kThreads, 0, st>>>(x, dt, rows, cols, rg, cg, out_min, out_max);
+    return after_launch("minmax_tile_kernel");
+}
+
+extern "C" int ctb_calculate_qparams(const void *mins, const void *maxs, int32_t dtype, int64_t n, int32_t qtype, int32_t bits,
+                                     int32_t symmetric, const float *gs, void *out_scale, void *out_zp, int32_t zdt, void *stream) {
+    if (!mins || !maxs || !out_scale || !out_zp) return fail(CTB_EINVAL_NULL, "null buffer");
+    if (!is_float_dtype(dtype)) return fail(CTB_EINVAL_DTYPE, "min/max must be bf16, f16 or f32");
+    if (qtype == CTB_QFLOAT && bits == 4 && !symmetric) return fail(CTB_EUNSUPPORTED, "Asymmetric Quantization is not supported for FP4");
+    if (qtype == CTB_QFLOAT && bits != 4 && bits != 8) return fail(CTB_EUNSUPPORTED, "Range calculation only supported for 4 and 8 bits");
+    if (qtype == CTB_QINT && (bits < 1 || bits > 8)) return fail(CTB_EUNSUPPORTED, "int quantization supports 1..8 bits");
+    if (zdt != CTB_I8 && zdt != CTB_E4M3) return fail(CTB_EINVAL_DTYPE, "zero point dtype must be int8 or e4m3");
+    if (n <= 0) return CTB_OK;
+    qparams_kernel<<<grid_for(n, kThreads, 4), kThreads, 0, as_stream(stream)>>>(mins, maxs, dtype, n, qtype, bits, symmetric, gs, out_scale, out_zp, zdt);
+    return after_launch("qparams_kernel");
+}
+
+extern "C" int ctb_generate_gparam(const void *mn, const void *mx, int32_t dtype, float *out, void *stream) {
+    if (!mn || !mx || !out) return fail(CTB_EINVAL_NULL, "null buffer");
+    if (!is_float_dtype(dtype)) return fail(CTB_EINVAL_DTYPE, "min/max must be bf16, f16 or f32");
+    gparam_kernel<<<1, 1, 0, as_stream(stream)>>>(mn, mx, dtype, out);
+    return after_launch("gparam_kernel");
+}

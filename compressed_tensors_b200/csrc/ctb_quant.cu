@@ -1,0 +1,341 @@
+// quantize / dequantize / fake_quantize (quantization/lifecycle/forward.py:45-189, :455-514)
+// with pack_to_int32 / pack_fp4_to_uint8 and their inverses fused on the quantized side.
+//
+// Two tiers:
+//   vec8    : 8 consecutive elements per step, 128-bit streaming loads, formats and compute
+//             dtypes fixed at compile time; needs cols % 8 == 0, col_group % 8 == 0, no g_idx and
+//             16-byte aligned buffers.  Bound by HBM: every input byte is read once and every
+//             output byte written once.
+//   generic : one output unit (element, packed word or fp4 byte) per thread, everything decided
+//             at run time; covers ragged shapes, any num_bits, g_idx column maps.
+#include "ctb_codec.cuh"
+
+namespace ctb {
+
+struct QArgs {
+    const void *in;
+    const void *scale;
+    const void *zp;
+    const int32_t *g_idx;
+    const float *gs;
+    void *out;
+    int64_t rows, cols, col_group, row_group, srs;
+    int64_t chunks;  // rows * cols / 8
+    int64_t cpr;     // chunks per row
+    int gshift;      // >= 0: qparam index = (8 * chunk) >> gshift; < 0: general indexing
+    float qmin, qmax;
+    int sdt, zdt;    // scale / zero-point dtypes
+    int xdt;         // dense-side dtype
+    int T, TS;       // compute dtypes of the quantize and the dequantize half
+    int qk;          // QKind
+    int bits;
+    int fin, fout;   // Fmt of both sides (generic tier)
+};
+
+constexpr int kThreads = 256;
+constexpr int kUnroll = 4;
+
+__device__ __forceinline__ int64_t qp_index_chunk(const QArgs &a, int64_t chunk) {
+    if (a.gshift >= 0) return (chunk << 3) >> a.gshift;
+    int64_t row = chunk / a.cpr;
+    int64_t col = (chunk - row * a.cpr) << 3;
+    return (row / a.row_group) * a.srs + col / a.col_group;
+}
+
+// MODE 0 quantize, 1 dequantize, 2 fake quantize
+template <int MODE, int T, int TS, int QK, int FIN, int FOUT>
+__global__ void __launch_bounds__(kThreads) qdq_vec8_kernel(const QArgs a) {
+    const bool has_zp = a.zp != nullptr;
+    const int64_t stride = (int64_t)gridDim.x * kThreads * kUnroll;
+    for (int64_t base = (int64_t)blockIdx.x * kThreads * kUnroll + threadIdx.x; base < a.chunks; base += stride) {
+        Raw8 raw[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            int64_t c = base + (int64_t)u * kThreads;
+            if (c < a.chunks) raw[u] = load_raw<FIN>(a.in, c);
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            int64_t c = base + (int64_t)u * kThreads;
+            if (c >= a.chunks) continue;
+            QP q = load_qp(a.scale, a.sdt, a.zp, a.zdt, a.gs, qp_index_chunk(a, c));
+            float v[8];
+            decode8<FIN>(raw[u], v);
+            if constexpr (MODE == 0) {
+                quant_prepare8<T>(v, q, has_zp, q.zp, a.qmin, a.qmax);
+                encode_store8<QK, FOUT>(a.out, c, v);
+            } else if constexpr (MODE == 1) {
+                dequant8<TS>(v, q, has_zp);
+                store8_float<FOUT>(a.out, c, v);
+            } else {
+                quant_prepare8<T>(v, q, has_zp, q.zp, a.qmin, a.qmax);
+                round8<QK>(v);
+                dequant8<TS>(v, q, has_zp);
+                store8_float<FOUT>(a.out, c, v);
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------ generic tier
+
+__device__ __forceinline__ float quant_scalar(const QArgs &a, float x, float s, bool has_zp, float zp) {
+    float t = round_to_rt(a.T, __fdiv_rn(x, s));
+    if (has_zp) t = round_to_rt(a.T, t + zp);
+    t = clamp_nan(t, a.qmin, a.qmax);
+    if (a.qk == QK_INT) return rintf(t);
+    if (a.qk == QK_FP8) return (t != t) ? t : e4m3_to_f32(f32_to_e4m3(t));
+    // FP4_E2M1_DATA.cast_to_fp4, quant_args.py:55-68
+    if (t != t) return t;
+    float sign = (t > 0.0f) ? 1.0f : ((t < 0.0f) ? -1.0f : 0.0f);
+    float m = fabsf(t), r;
+    if (m <= 0.25f) r = 0.0f;
+    else if (m < 0.75f) r = 0.5f;
+    else if (m <= 1.25f) r = 1.0f;
+    else if (m < 1.75f) r = 1.5f;
+    else if (m <= 2.5f) r = 2.0f;
+    else if (m < 3.5f) r = 3.0f;
+    else if (m <= 5.0f) r = 4.0f;
+    else r = 6.0f;
+    return r * sign;
+}
+
+__device__ __forceinline__ float dequant_scalar(const QArgs &a, float q, float s, bool has_zp, float zp) {
+    float t = round_to_rt(a.TS, q);
+    if (has_zp) t = round_to_rt(a.TS, t - round_to_rt(a.TS, zp));
+    return round_to_rt(a.TS, t * s);
+}
+
+__device__ __forceinline__ uint32_t e2m1_nibble(float v) {
+    // index of the grid magnitude (exact for grid values) with the sign bit of v
+    float m = fabsf(v);
+    uint32_t idx = m < 0.25f ? 0 : m < 0.75f ? 1 : m < 1.25f ? 2 : m < 1.75f ? 3 : m < 2.5f ? 4 : m < 3.5f ? 5 : m < 5.0f ? 6 : 7;
+    return idx | ((__float_as_uint(v) >> 31) << 3);
+}
+
+__device__ __forceinline__ float e2m1_value(uint32_t nib) {
+    const float mag[8] = {0.0f, 0.5f, 1.0f, 1.5f, 2.0f, 3.0f, 4.0f, 6.0f};
+    float m = mag[nib & 7];
+    return (nib & 8) ? -m : m;
+}
+
+__device__ __forceinline__ int fmt_dtype(int f) {
+    return f == F_BF16 ? CTB_BF16 : f == F_F16 ? CTB_F16 : f == F_F32 ? CTB_F32 : f == F_I8 ? CTB_I8 : CTB_E4M3;
+}
+
+// load the quantized-side value of element (row, col) for the generic dequantize
+__device__ __forceinline__ float load_code(const QArgs &a, int64_t row, int64_t col) {
+    if (a.fin == F_PACK4 || a.fin == F_PACK8) {
+        int pf = 32 / a.bits;
+        int64_t pc = (a.cols + pf - 1) / pf;
+        int32_t w = ((const int32_t *)a.in)[row * pc + col / pf];
+        int32_t u = (w >> (a.bits * (int)(col % pf))) & ((1 << a.bits) - 1);
+        return (float)(u - (1 << (a.bits - 1)));
+    }
+    if (a.fin == F_FP4X2) {
+        uint8_t b = ((const uint8_t *)a.in)[(row * a.cols + col) >> 1];
+        return e2m1_value((col & 1) ? (b >> 4) : (b & 0xF));
+    }
+    return load_f32(a.in, fmt_dtype(a.fin), row * a.cols + col);
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(kThreads) qdq_generic_kernel(const QArgs a) {
+    const bool has_zp = a.zp != nullptr;
+    const bool pack32 = (MODE == 0) && (a.fout == F_PACK4 || a.fout == F_PACK8);
+    const bool fp4x2 = (MODE == 0) && (a.fout == F_FP4X2);
+    const int per = pack32 ? 32 / a.bits : (fp4x2 ? 2 : 1);
+    const int64_t upr = (a.cols + per - 1) / per;  // units per row
+    const int64_t units = a.rows * upr;
+    for (int64_t u = (int64_t)blockIdx.x * kThreads + threadIdx.x; u < units; u += (int64_t)gridDim.x * kThreads) {
+        int64_t row = u / upr, c0 = (u - row * upr) * per;
+        uint32_t word = 0;
+        for (int k = 0; k < per; ++k) {
+            int64_t col = c0 + k;
+            if (col >= a.cols) break;
+            int64_t g = a.g_idx ? (int64_t)a.g_idx[col] : col / a.col_group;
+            int64_t qi = (row / a.row_group) * a.srs + g;
+            float s = load_f32(a.scale, a.sdt, qi);
+            if (a.gs) s = __fdiv_rn(s, a.gs[0]);
+            float zp = has_zp ? load_f32(a.zp, a.zdt, qi) : 0.0f;
+            int64_t i = row * a.cols + col;
+            if (MODE == 1) {
+                float v = dequant_scalar(a, load_code(a, row, col), s, has_zp, zp);
+                store_f32(a.out, fmt_dtype(a.fout), i, v);
+                continue;
+            }
+            float q = quant_scalar(a, load_f32(a.in, a.xdt, i), s, has_zp, zp);
+            if (MODE == 2) {
+                store_f32(a.out, fmt_dtype(a.fout), i, dequant_scalar(a, q, s, has_zp, zp));
+            } else if (pack32) {
+                // pack_quantized.py:219-242: (value + offset).to(uint8) << (bits * k)
+                word |= (uint32_t)(uint8_t)((int)q + (1 << (a.bits - 1))) << (a.bits * k);
+            } else if (fp4x2) {
+                word |= e2m1_nibble(q) << (4 * k);
+            } else {
+                store_f32(a.out, fmt_dtype(a.fout), i, q);
+            }
+        }
+        if (pack32) ((int32_t *)a.out)[u] = (int32_t)word;
+        if (fp4x2) ((uint8_t *)a.out)[u] = (uint8_t)word;
+    }
+}
+
+}  // namespace ctb
+
+// ------------------------------------------------------------------ host dispatch
+
+namespace ctb {
+
+static int dtype_to_fmt(int dt) {
+    switch (dt) {
+    case CTB_BF16: return F_BF16;
+    case CTB_F16: return F_F16;
+    case CTB_F32: return F_F32;
+    case CTB_I8: return F_I8;
+    case CTB_E4M3: return F_E4M3;
+    default: return F_NONE;
+    }
+}
+
+// format of the quantized side
+static int code_fmt(const ctb_qdesc *d) {
+    if (d->codec == CTB_CODE_PACK32) return d->num_bits == 4 ? F_PACK4 : F_PACK8;  // other widths: generic only
+    if (d->codec == CTB_CODE_FP4X2) return F_FP4X2;
+    return dtype_to_fmt(d->q_dtype);
+}
+
+static int validate(const ctb_qdesc *d, const void *in, const void *scale, const void *out, int mode) {
+    if (!d || !in || !scale || !out) return fail(CTB_EINVAL_NULL, "null descriptor or buffer");
+    if (d->rows < 0 || d->cols < 0) return fail(CTB_EINVAL_SHAPE, "negative shape");
+    if (d->col_group <= 0 || d->row_group <= 0) return fail(CTB_EINVAL_SHAPE, "group sizes must be positive");
+    // forward.py:277-282 / :215-224: columns (rows) must divide into whole groups (blocks)
+    if (d->cols % d->col_group != 0)
+        return fail(CTB_EINVAL_SHAPE, "tensor column shape must be divisble by the given group_size %lld but got %lld",
+                    (long long)d->col_group, (long long)d->cols);
+    if (d->rows % d->row_group != 0)
+        return fail(CTB_EINVAL_SHAPE, "Tensor height %lld is not divisible by block_height %lld.",
+                    (long long)d->rows, (long long)d->row_group);
+    if (!is_float_dtype(d->x_dtype)) return fail(CTB_EINVAL_DTYPE, "dense side must be bf16, f16 or f32");
+    if (!(is_float_dtype(d->scale_dtype) || d->scale_dtype == CTB_E4M3)) return fail(CTB_EINVAL_DTYPE, "unsupported scale dtype");
+    if (d->qtype == CTB_QINT) {
+        if (d->num_bits < 1 || d->num_bits > 8) return fail(CTB_EUNSUPPORTED, "int quantization supports 1..8 bits");
+    } else if (d->qtype == CTB_QFLOAT) {
+        if (d->num_bits != 8 && d->num_bits != 4) return fail(CTB_EUNSUPPORTED, "Only num_bits in (4, 8) are supported");
+    } else {
+        return fail(CTB_EINVAL_DTYPE, "Invalid quantization type %d", d->qtype);
+    }
+    if (d->codec == CTB_CODE_PACK32 && d->qtype != CTB_QINT) return fail(CTB_EINVAL_DTYPE, "PACK32 needs an int type");
+    if (d->codec == CTB_CODE_FP4X2) {
+        if (!(d->qtype == CTB_QFLOAT && d->num_bits == 4)) return fail(CTB_EINVAL_DTYPE, "FP4X2 needs the fp4 type");
+        if (d->cols % 2) return fail(CTB_EINVAL_SHAPE, "tensor must have an even number of columns for nvfp4 compression");
+    }
+    if (d->codec == CTB_CODE_DTYPE && dtype_to_fmt(d->q_dtype) == F_NONE) return fail(CTB_EINVAL_DTYPE, "unsupported q_dtype");
+    if (mode == 2 && !is_float_dtype(d->q_dtype)) return fail(CTB_EINVAL_DTYPE, "fake quantize writes a float dtype");
+    return CTB_OK;
+}
+
+template <int MODE, int T, int TS, int QK, int FIN, int FOUT>
+static int launch_vec8(const QArgs &a, cudaStream_t st) {
+    int grid = grid_for(a.chunks, (int64_t)kThreads * kUnroll, 8);
+    qdq_vec8_kernel<MODE, T, TS, QK, FIN, FOUT><<<grid, kThreads, 0, st>>>(a);
+    return after_launch("qdq_vec8_kernel");
+}
+
+// the combinations built for the vec8 tier; anything else runs on the generic tier
+#define CTB_TRY(MODE, T_, TS_, QK_, FIN_, FOUT_)                                                        \
+    if (mode == MODE && (MODE == 1 || a.T == T_) && (MODE == 0 || a.TS == TS_) && a.qk == QK_ &&        \
+        a.fin == FIN_ && a.fout == FOUT_)                                                                \
+        return launch_vec8<MODE, T_, TS_, QK_, FIN_, FOUT_>(a, st);
+
+static int dispatch_vec8(int mode, const QArgs &a, cudaStream_t st, bool *handled) {
+    *handled = true;
+    constexpr int B = CTB_BF16, H = CTB_F16, S = CTB_F32;
+    // quantize
+    CTB_TRY(0, B, S, QK_INT, F_BF16, F_PACK4) CTB_TRY(0, B, S, QK_INT, F_BF16, F_PACK8)
+    CTB_TRY(0, B, S, QK_INT, F_BF16, F_I8) CTB_TRY(0, B, S, QK_INT, F_BF16, F_BF16)
+    CTB_TRY(0, S, S, QK_INT, F_BF16, F_PACK4) CTB_TRY(0, S, S, QK_INT, F_BF16, F_I8)
+    CTB_TRY(0, S, S, QK_INT, F_F32, F_PACK4) CTB_TRY(0, S, S, QK_INT, F_F32, F_I8) CTB_TRY(0, S, S, QK_INT, F_F32, F_F32)
+    CTB_TRY(0, H, S, QK_INT, F_F16, F_PACK4) CTB_TRY(0, H, S, QK_INT, F_F16, F_I8)
+    CTB_TRY(0, B, S, QK_FP8, F_BF16, F_E4M3) CTB_TRY(0, B, S, QK_FP8, F_BF16, F_BF16)
+    CTB_TRY(0, S, S, QK_FP8, F_BF16, F_E4M3) CTB_TRY(0, S, S, QK_FP8, F_F32, F_E4M3)
+    CTB_TRY(0, H, S, QK_FP8, F_F16, F_E4M3)
+    CTB_TRY(0, S, S, QK_FP4, F_BF16, F_FP4X2) CTB_TRY(0, S, S, QK_FP4, F_BF16, F_BF16)
+    // dequantize
+    CTB_TRY(1, S, B, QK_INT, F_PACK4, F_BF16) CTB_TRY(1, S, B, QK_INT, F_PACK8, F_BF16)
+    CTB_TRY(1, S, B, QK_INT, F_I8, F_BF16) CTB_TRY(1, S, B, QK_FP8, F_E4M3, F_BF16)
+    CTB_TRY(1, S, S, QK_INT, F_PACK4, F_F32) CTB_TRY(1, S, S, QK_INT, F_I8, F_F32)
+    CTB_TRY(1, S, S, QK_FP8, F_E4M3, F_F32) CTB_TRY(1, S, S, QK_FP8, F_E4M3, F_BF16)
+    CTB_TRY(1, S, H, QK_INT, F_PACK4, F_F16) CTB_TRY(1, S, H, QK_FP8, F_E4M3, F_F16)
+    CTB_TRY(1, S, S, QK_FP4, F_FP4X2, F_BF16) CTB_TRY(1, S, S, QK_FP4, F_BF16, F_BF16)
+    // fake quantize
+    CTB_TRY(2, B, B, QK_INT, F_BF16, F_BF16) CTB_TRY(2, B, B, QK_FP8, F_BF16, F_BF16)
+    CTB_TRY(2, S, S, QK_FP4, F_BF16, F_BF16) CTB_TRY(2, S, S, QK_FP8, F_BF16, F_F32)
+    CTB_TRY(2, S, S, QK_INT, F_F32, F_F32)
+    *handled = false;
+    return CTB_OK;
+}
+
+static int run(int mode, const ctb_qdesc *d, const void *in, const void *scale, const void *zp,
+               const int32_t *g_idx, const float *gs, void *out, void *stream) {
+    int rc = validate(d, in, scale, out, mode);
+    if (rc) return rc;
+    if (d->rows == 0 || d->cols == 0) return CTB_OK;
+    QArgs a{};
+    a.in = in; a.scale = scale; a.zp = zp; a.g_idx = g_idx; a.gs = gs; a.out = out;
+    a.rows = d->rows; a.cols = d->cols; a.col_group = d->col_group; a.row_group = d->row_group;
+    a.srs = d->scale_row_stride;
+    a.sdt = d->scale_dtype; a.zdt = d->zp_dtype; a.xdt = d->x_dtype; a.bits = d->num_bits;
+    a.qk = d->qtype == CTB_QINT ? QK_INT : (d->num_bits == 8 ? QK_FP8 : QK_FP4);
+    if (a.qk == QK_INT) { a.qmax = (float)(1 << d->num_bits) / 2 - 1; a.qmin = -(float)(1 << d->num_bits) / 2; }
+    else if (a.qk == QK_FP8) { a.qmax = 448.0f; a.qmin = -448.0f; }
+    else { a.qmax = 6.0f; a.qmin = -6.0f; }
+    int sdt_eff = gs ? CTB_F32 : d->scale_dtype;      // scale.to(global_scale.dtype) / global_scale
+    if (sdt_eff == CTB_E4M3) return fail(CTB_EINVAL_DTYPE, "an e4m3 scale needs a global_scale");
+    a.T = promote(d->x_dtype, sdt_eff);
+    a.TS = sdt_eff;
+    int dense = dtype_to_fmt(d->x_dtype), code = code_fmt(d);
+    if (mode == 0) { a.fin = dense; a.fout = code; }
+    else if (mode == 1) { a.fin = code; a.fout = dense; }
+    else { a.fin = dense; a.fout = dtype_to_fmt(d->q_dtype); }
+    cudaStream_t st = as_stream(stream);
+
+    bool pack_other = d->codec == CTB_CODE_PACK32 && d->num_bits != 4 && d->num_bits != 8;
+    bool vec_ok = !g_idx && !pack_other && d->cols % 8 == 0 && d->col_group % 8 == 0 && aligned16(in) && aligned16(out);
+    if (vec_ok) {
+        a.chunks = d->rows * d->cols / 8;
+        a.cpr = d->cols / 8;
+        a.gshift = -1;
+        bool flat = d->row_group == 1 && (d->scale_row_stride == d->cols / d->col_group);
+        if (flat && (d->col_group & (d->col_group - 1)) == 0) {
+            int sh = 0;
+            while ((1LL << sh) < d->col_group) ++sh;
+            a.gshift = sh;
+        }
+        bool handled = false;
+        rc = dispatch_vec8(mode, a, st, &handled);
+        if (handled) return rc;
+    }
+    int per = (mode == 0 && d->codec == CTB_CODE_PACK32) ? 32 / d->num_bits : ((mode == 0 && d->codec == CTB_CODE_FP4X2) ? 2 : 1);
+    int64_t units = d->rows * cdiv(d->cols, per);
+    int grid = grid_for(units, kThreads, 8);
+    if (mode == 0) qdq_generic_kernel<0><<<grid, kThreads, 0, st>>>(a);
+    else if (mode == 1) qdq_generic_kernel<1><<<grid, kThreads, 0, st>>>(a);
+    else qdq_generic_kernel<2><<<grid, kThreads, 0, st>>>(a);
+    return after_launch("qdq_generic_kernel");
+}
+
+}  // namespace ctb
+
+extern "C" int ctb_quantize(const ctb_qdesc *desc, const void *x, const void *scale, const void *zero_point,
+                            const int32_t *g_idx, const float *global_scale, void *out, void *stream) {
+    return ctb::run(0, desc, x, scale, zero_point, g_idx, global_scale, out, stream);
+}
+extern "C" int ctb_dequantize(const ctb_qdesc *desc, const void *q, const void *scale, const void *zero_point,
+                              const int32_t *g_idx, const float *global_scale, void *out, void *stream) {
+    return ctb::run(1, desc, q, scale, zero_point, g_idx, global_scale, out, stream);
+}
+extern "C" int ctb_fake_quantize(const ctb_qdesc *desc, const void *x, const void *scale, const void *zero_point,
+                                 const int32_t *g_idx, const float *global_scale, void *out, void *stream) {
+    return ctb::run(2, desc, x, scale, zero_point, g_idx, global_scale, out, stream);
+}

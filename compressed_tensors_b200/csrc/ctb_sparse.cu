@@ -1,0 +1,423 @@
+// Sparse codecs: 2:4 keep-mask and compaction (compressors/sparse_compressors/sparse_24_bitmask.py),
+// unstructured bitmask compress / decompress (compressors/sparse_compressors/sparse_bitmask.py).
+//
+// Layout facts shared with the reference: values are row-major, bitmask byte k of a row holds
+// columns 8k..8k+7 with column 8k+j in bit j (numpy.packbits, bitorder="little"), row_offsets is the
+// int64 exclusive prefix of the per-row counts.
+#include "ctb_codec.cuh"
+
+namespace ctb {
+
+constexpr int kThreads = 256;
+
+__constant__ uint8_t c_lut24[256] = {
+#include "sparse24_lut.inc"
+};
+
+// element classes by storage size; `nz_mask` selects the bits that make an element non-zero
+// (sign bit excluded for float types so that -0.0 counts as zero, sparse_bitmask.py:137)
+struct ElemInfo {
+    int esize;
+    uint32_t nz_mask;
+    int is_int8;  // magnitudes ranked through the int8 view (int8 and e4m3 tensors)
+};
+
+static bool elem_info(int dt, ElemInfo *e) {
+    switch (dt) {
+    case CTB_BF16: case CTB_F16: *e = {2, 0x7FFFu, 0}; return true;
+    case CTB_F32: *e = {4, 0x7FFFFFFFu, 0}; return true;
+    case CTB_E4M3: *e = {1, 0x7Fu, 1}; return true;
+    case CTB_I8: case CTB_U8: *e = {1, 0xFFu, 1}; return true;
+    default: return false;
+    }
+}
+
+// 8 consecutive elements as raw bit patterns
+template <int ES>
+__device__ __forceinline__ void load8_bits(const void *x, int64_t unit, uint32_t (&b)[8]) {
+    if constexpr (ES == 2) {
+        uint4 v = ld_stream((const char *)x + unit * 16);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { b[2 * i] = w[i] & 0xFFFFu; b[2 * i + 1] = w[i] >> 16; }
+    } else if constexpr (ES == 1) {
+        uint2 v = ld_stream8((const char *)x + unit * 8);
+        const uint32_t w[2] = {v.x, v.y};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) b[i] = (w[i >> 2] >> (8 * (i & 3))) & 0xFFu;
+    } else {
+        uint4 v0 = ld_stream((const char *)x + unit * 32), v1 = ld_stream((const char *)x + unit * 32 + 16);
+        b[0] = v0.x; b[1] = v0.y; b[2] = v0.z; b[3] = v0.w;
+        b[4] = v1.x; b[5] = v1.y; b[6] = v1.z; b[7] = v1.w;
+    }
+}
+
+__device__ __forceinline__ uint32_t load_bits(const void *x, int es, int64_t i) {
+    return es == 1 ? ((const uint8_t *)x)[i] : es == 2 ? ((const uint16_t *)x)[i] : ((const uint32_t *)x)[i];
+}
+__device__ __forceinline__ void store_bits(void *x, int es, int64_t i, uint32_t v) {
+    if (es == 1) ((uint8_t *)x)[i] = (uint8_t)v;
+    else if (es == 2) ((uint16_t *)x)[i] = (uint16_t)v;
+    else ((uint32_t *)x)[i] = v;
+}
+
+// sparse_24_bitmask.py:244-256: magnitude used for ranking.  Float types: |x| orders like its
+// magnitude bits.  int8 view (int8 / e4m3 tensors): torch's int8 abs, where abs(-128) wraps to -128.
+__device__ __forceinline__ int32_t rank_key(uint32_t bits, uint32_t nz_mask, int is_int8) {
+    if (is_int8) {
+        int32_t v = (int32_t)(int8_t)bits;
+        return (int32_t)(int8_t)(v < 0 ? -v : v);
+    }
+    return (int32_t)(bits & nz_mask);
+}
+
+// keep-mask (4 bits) of one run of four magnitudes: the positions abs().topk(2) returns on CPU
+__device__ __forceinline__ uint32_t keep24(int32_t k0, int32_t k1, int32_t k2, int32_t k3, const uint8_t *lut) {
+    // c_i = how many of the other three are strictly smaller than k_i
+    uint32_t c0 = (k1 < k0) + (k2 < k0) + (k3 < k0);
+    uint32_t c1 = (k0 < k1) + (k2 < k1) + (k3 < k1);
+    uint32_t c2 = (k0 < k2) + (k1 < k2) + (k3 < k2);
+    uint32_t c3 = (k0 < k3) + (k1 < k3) + (k2 < k3);
+    return lut[c0 | (c1 << 2) | (c2 << 4) | (c3 << 6)];
+}
+
+__device__ __forceinline__ void stage_lut(uint8_t *s) {
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) s[i] = c_lut24[i];
+    __syncthreads();
+}
+
+// get_24_bytemasks on the flat view: one thread per run of 4
+__global__ void __launch_bounds__(kThreads) sparse24_mask_kernel(const void *x, int es, uint32_t nzm, int is_int8, int64_t groups, uint8_t *out) {
+    __shared__ uint8_t lut[256];
+    stage_lut(lut);
+    for (int64_t g = (int64_t)blockIdx.x * kThreads + threadIdx.x; g < groups; g += (int64_t)gridDim.x * kThreads) {
+        int32_t k[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) k[j] = rank_key(load_bits(x, es, 4 * g + j), nzm, is_int8);
+        uint32_t m = keep24(k[0], k[1], k[2], k[3], lut);
+        *reinterpret_cast<uint32_t *>(out + 4 * g) = (m & 1) | ((m >> 1 & 1) << 8) | ((m >> 2 & 1) << 16) | ((m >> 3 & 1) << 24);
+    }
+}
+
+// sparse24_bitmask_compress, cols % 8 == 0: one thread per 8 elements = 2 runs = 4 kept values and
+// one bitmask byte; four neighbouring lanes merge their bytes into one 32-bit store.
+template <int ES>
+__global__ void __launch_bounds__(kThreads) sparse24_compress_kernel(const void *x, uint32_t nzm, int is_int8, int64_t units, void *values, uint8_t *bitmask) {
+    __shared__ uint8_t lut[256];
+    stage_lut(lut);
+    const int64_t padded = (units + 31) & ~(int64_t)31;
+    for (int64_t u = (int64_t)blockIdx.x * kThreads + threadIdx.x; u < padded; u += (int64_t)gridDim.x * kThreads) {
+        uint32_t b[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        const bool live = u < units;
+        if (live) load8_bits<ES>(x, u, b);
+        int32_t k[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) k[j] = rank_key(b[j], nzm, is_int8);
+        uint32_t m = keep24(k[0], k[1], k[2], k[3], lut) | (keep24(k[4], k[5], k[6], k[7], lut) << 4);
+        // the four kept elements in column order: per run, the lower and the upper of its two set bits
+        uint32_t kept[4];
+#pragma unroll
+        for (int g = 0; g < 2; ++g) {
+            uint32_t mm = (m >> (4 * g)) & 0xFu;
+            kept[2 * g] = (mm & 1) ? b[4 * g] : ((mm & 2) ? b[4 * g + 1] : b[4 * g + 2]);
+            kept[2 * g + 1] = (mm & 8) ? b[4 * g + 3] : ((mm & 4) ? b[4 * g + 2] : b[4 * g + 1]);
+        }
+        if (live) {
+            if constexpr (ES == 2) st_stream8((char *)values + u * 8, make_uint2(kept[0] | (kept[1] << 16), kept[2] | (kept[3] << 16)));
+            else if constexpr (ES == 1) st_stream4((char *)values + u * 4, kept[0] | (kept[1] << 8) | (kept[2] << 16) | (kept[3] << 24));
+            else st_stream((char *)values + u * 16, make_uint4(kept[0], kept[1], kept[2], kept[3]));
+        }
+        // gather 4 mask bytes; whole quads are live or dead together only when units % 4 == 0
+        uint32_t w = m << (8 * (threadIdx.x & 3));
+        w |= __shfl_xor_sync(0xFFFFFFFFu, w, 1);
+        w |= __shfl_xor_sync(0xFFFFFFFFu, w, 2);
+        if ((threadIdx.x & 3) == 0 && live) {
+            if (u + 3 < units) *reinterpret_cast<uint32_t *>(bitmask + u) = w;
+            else
+                for (int64_t t = u; t < units; ++t) bitmask[t] = (uint8_t)(w >> (8 * (t - u)));
+        }
+    }
+}
+
+}  // namespace ctb
+
+// ------------------------------------------------------------------ unstructured bitmask codec
+
+namespace ctb {
+
+// 8-bit keep mask of unit `u` (8 elements of one row; cols % 8 == 0 fast path) plus the raw bits
+template <int ES>
+__device__ __forceinline__ uint32_t unit_mask(const void *x, int64_t unit, uint32_t nzm, uint32_t (&b)[8]) {
+    load8_bits<ES>(x, unit, b);
+    uint32_t m = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) m |= ((b[j] & nzm) != 0 ? 1u : 0u) << j;
+    return m;
+}
+
+// mask of up to 8 elements starting at column c0 of `row`, scalar loads (ragged / unaligned rows);
+// `pred` (optional bytemask) replaces the non-zero test
+__device__ __forceinline__ uint32_t unit_mask_scalar(const void *x, const uint8_t *pred, int es, uint32_t nzm, int64_t row, int64_t c0, int64_t cols, uint32_t (&b)[8]) {
+    uint32_t m = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        b[j] = 0;
+        if (c0 + j < cols) {
+            int64_t i = row * cols + c0 + j;
+            b[j] = load_bits(x, es, i);
+            bool keep = pred ? (pred[i] != 0) : ((b[j] & nzm) != 0);
+            m |= (keep ? 1u : 0u) << j;
+        }
+    }
+    return m;
+}
+
+__device__ __forceinline__ int block_sum(int v) {
+    __shared__ int part[kThreads / 32];
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = v;
+    __syncthreads();
+    int t = 0;
+#pragma unroll
+    for (int i = 0; i < kThreads / 32; ++i) t += part[i];
+    return t;
+}
+
+// exclusive prefix of v over the block, and the block total
+__device__ __forceinline__ int block_excl_scan(int v, int &total) {
+    __shared__ int wsum[kThreads / 32];
+    int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    int inc = v;
+    for (int o = 1; o < 32; o <<= 1) {
+        int t = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+        if (lane >= o) inc += t;
+    }
+    __syncthreads();
+    if (lane == 31) wsum[w] = inc;
+    __syncthreads();
+    int base = 0;
+    total = 0;
+#pragma unroll
+    for (int i = 0; i < kThreads / 32; ++i) {
+        if (i < w) base += wsum[i];
+        total += wsum[i];
+    }
+    return base + inc - v;
+}
+
+// pass 1: bitmask bytes and per-row counts.  One block per row.
+template <int ES, bool VEC>
+__global__ void __launch_bounds__(kThreads) bm_count_kernel(const void *x, const uint8_t *pred, int es, uint32_t nzm, int64_t rows, int64_t cols, uint8_t *bitmask, int64_t *row_counts) {
+    const int64_t upr = (cols + 7) / 8;
+    for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+        int cnt = 0;
+        for (int64_t u = threadIdx.x; u < upr; u += kThreads) {
+            uint32_t b[8];
+            uint32_t m = VEC ? unit_mask<ES>(x, r * upr + u, nzm, b) : unit_mask_scalar(x, pred, es, nzm, r, u * 8, cols, b);
+            if (bitmask) bitmask[r * upr + u] = (uint8_t)m;
+            cnt += __popc(m);
+        }
+        cnt = block_sum(cnt);
+        if (threadIdx.x == 0) row_counts[r] = cnt;
+    }
+}
+
+// per-row counts straight from a bitmask (decompress)
+__global__ void __launch_bounds__(kThreads) bm_popcount_kernel(const uint8_t *bitmask, int64_t rows, int64_t cols, int64_t *row_counts) {
+    const int64_t upr = (cols + 7) / 8;
+    const int tail = (int)(cols & 7);
+    for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+        int cnt = 0;
+        for (int64_t u = threadIdx.x; u < upr; u += kThreads) {
+            uint32_t m = bitmask[r * upr + u];
+            if (tail && u == upr - 1) m &= (1u << tail) - 1;  // unpackbits(count=cols) ignores pad bits
+            cnt += __popc(m);
+        }
+        cnt = block_sum(cnt);
+        if (threadIdx.x == 0) row_counts[r] = cnt;
+    }
+}
+
+// pass 2: in-place exclusive scan of the row counts (single block), total to *nnz
+__global__ void __launch_bounds__(1024) row_scan_kernel(int64_t *counts, int64_t rows, int64_t *nnz) {
+    __shared__ int64_t wsum[32];
+    __shared__ int64_t carry_s;
+    if (threadIdx.x == 0) carry_s = 0;
+    __syncthreads();
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    for (int64_t base = 0; base < rows; base += 1024) {
+        int64_t i = base + threadIdx.x;
+        int64_t v = i < rows ? counts[i] : 0, inc = v;
+        for (int o = 1; o < 32; o <<= 1) {
+            int64_t t = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+            if (lane >= o) inc += t;
+        }
+        if (lane == 31) wsum[w] = inc;
+        __syncthreads();
+        int64_t off = carry_s;
+        for (int k = 0; k < w; ++k) off += wsum[k];
+        if (i < rows) counts[i] = off + inc - v;
+        __syncthreads();
+        if (threadIdx.x == 1023) carry_s = off + inc;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0 && nnz) *nnz = carry_s;
+}
+
+// pass 3 (compress): compact each row's kept elements to values[row_offsets[r] ...], staged through
+// shared memory so that global stores are contiguous.  One block per row, 2048 elements per round.
+template <int ES, bool VEC>
+__global__ void __launch_bounds__(kThreads) bm_scatter_kernel(const void *x, const uint8_t *pred, int es, uint32_t nzm, int64_t rows, int64_t cols, const int64_t *row_offsets, void *values) {
+    __shared__ uint32_t stage[kThreads * 8];
+    const int64_t upr = (cols + 7) / 8;
+    for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+        int64_t out = row_offsets[r];
+        for (int64_t u0 = 0; u0 < upr; u0 += kThreads) {
+            int64_t u = u0 + threadIdx.x;
+            uint32_t b[8], m = 0;
+            if (u < upr) m = VEC ? unit_mask<ES>(x, r * upr + u, nzm, b) : unit_mask_scalar(x, pred, es, nzm, r, u * 8, cols, b);
+            int total, pos = block_excl_scan(__popc(m), total);
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if ((m >> j) & 1) stage[pos++] = b[j];
+            __syncthreads();
+            for (int i = threadIdx.x; i < total; i += kThreads) store_bits(values, es, out + i, stage[i]);
+            out += total;
+            __syncthreads();
+        }
+    }
+}
+
+// decompress: zeros, then values scattered to the set bits.  One block per row; every thread owns
+// 8 output elements per round and writes them with one vector store when the row layout allows.
+template <int ES, bool VEC>
+__global__ void __launch_bounds__(kThreads) bm_expand_kernel(const void *values, const uint8_t *bitmask, int es, int64_t rows, int64_t cols, const int64_t *row_offsets, void *out) {
+    const int64_t upr = (cols + 7) / 8;
+    const int tail = (int)(cols & 7);
+    for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+        int64_t in = row_offsets[r];
+        for (int64_t u0 = 0; u0 < upr; u0 += kThreads) {
+            int64_t u = u0 + threadIdx.x;
+            uint32_t m = 0;
+            if (u < upr) {
+                m = bitmask[r * upr + u];
+                if (tail && u == upr - 1) m &= (1u << tail) - 1;
+            }
+            int total, pos = block_excl_scan(__popc(m), total);
+            uint32_t b[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) b[j] = ((m >> j) & 1) ? load_bits(values, es, in + pos++) : 0u;
+            if (u < upr) {
+                if constexpr (VEC && ES == 2) {
+                    st_stream((char *)out + (r * upr + u) * 16, make_uint4(b[0] | (b[1] << 16), b[2] | (b[3] << 16), b[4] | (b[5] << 16), b[6] | (b[7] << 16)));
+                } else if constexpr (VEC && ES == 1) {
+                    st_stream8((char *)out + (r * upr + u) * 8, make_uint2(b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24), b[4] | (b[5] << 8) | (b[6] << 16) | (b[7] << 24)));
+                } else if constexpr (VEC && ES == 4) {
+                    st_stream((char *)out + (r * upr + u) * 32, make_uint4(b[0], b[1], b[2], b[3]));
+                    st_stream((char *)out + (r * upr + u) * 32 + 16, make_uint4(b[4], b[5], b[6], b[7]));
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        if (u * 8 + j < cols) store_bits(out, es, r * cols + u * 8 + j, b[j]);
+                }
+            }
+            in += total;
+        }
+    }
+}
+
+}  // namespace ctb
+
+// ------------------------------------------------------------------ entry points
+
+using namespace ctb;
+
+extern "C" int ctb_sparse24_mask(const void *x, int32_t dtype, int64_t numel, uint8_t *out, void *stream) {
+    if (!x || !out) return fail(CTB_EINVAL_NULL, "null buffer");
+    ElemInfo e;
+    if (!elem_info(dtype, &e)) return fail(CTB_EINVAL_DTYPE, "unsupported dtype for 2:4 masks");
+    if (numel % 4 != 0) return fail(CTB_EINVAL_SHAPE, "Tensor size must be a multiple of 4 for TWO_FOUR sparsity");
+    if (numel == 0) return CTB_OK;
+    sparse24_mask_kernel<<<grid_for(numel / 4, kThreads, 8), kThreads, 0, as_stream(stream)>>>(x, e.esize, e.nz_mask, e.is_int8, numel / 4, out);
+    return after_launch("sparse24_mask_kernel");
+}
+
+extern "C" int ctb_sparse24_compress(const void *x, int32_t dtype, int64_t rows, int64_t cols, void *values, uint8_t *bitmask, void *stream) {
+    if (!x || !values || !bitmask) return fail(CTB_EINVAL_NULL, "null buffer");
+    ElemInfo e;
+    if (!elem_info(dtype, &e)) return fail(CTB_EINVAL_DTYPE, "unsupported dtype for 2:4 compression");
+    if ((rows * cols) % 4 != 0) return fail(CTB_EINVAL_SHAPE, "Tensor size must be a multiple of 4 for TWO_FOUR sparsity");
+    if (cols % 8 != 0) return fail(CTB_EUNSUPPORTED, "fused 2:4 compression needs cols %% 8 == 0; use ctb_sparse24_mask + ctb_masked_compress");
+    if (!aligned16(x) || !aligned16(values)) return fail(CTB_EINVAL_ALIGN, "buffers must be 16-byte aligned");
+    int64_t units = rows * cols / 8;
+    if (units == 0) return CTB_OK;
+    int grid = grid_for(units, kThreads, 8);
+    cudaStream_t st = as_stream(stream);
+    if (e.esize == 2) sparse24_compress_kernel<2><<<grid, kThreads, 0, st>>>(x, e.nz_mask, e.is_int8, units, values, bitmask);
+    else if (e.esize == 1) sparse24_compress_kernel<1><<<grid, kThreads, 0, st>>>(x, e.nz_mask, e.is_int8, units, values, bitmask);
+    else sparse24_compress_kernel<4><<<grid, kThreads, 0, st>>>(x, e.nz_mask, e.is_int8, units, values, bitmask);
+    return after_launch("sparse24_compress_kernel");
+}
+
+static int compress_impl(const void *x, const uint8_t *pred, int32_t dtype, int64_t rows, int64_t cols, void *values, uint8_t *bitmask,
+                         int64_t *row_offsets, int64_t *nnz, void *stream) {
+    if (!x || !values || !bitmask || !row_offsets || !nnz) return fail(CTB_EINVAL_NULL, "null buffer");
+    ElemInfo e;
+    if (!elem_info(dtype, &e)) return fail(CTB_EINVAL_DTYPE, "unsupported dtype for bitmask compression");
+    if (rows < 0 || cols < 0) return fail(CTB_EINVAL_SHAPE, "negative shape");
+    cudaStream_t st = as_stream(stream);
+    if (rows == 0 || cols == 0) {
+        cudaMemsetAsync(nnz, 0, sizeof(int64_t), st);
+        if (rows) cudaMemsetAsync(row_offsets, 0, sizeof(int64_t) * rows, st);
+        return CTB_OK;
+    }
+    const bool vec = !pred && cols % 8 == 0 && aligned16(x);
+    int grid = grid_for(rows, 1, 8);
+    int rc;
+#define CTB_BM(KERNEL, ...)                                                                              \
+    if (vec && e.esize == 2) KERNEL<2, true><<<grid, kThreads, 0, st>>>(__VA_ARGS__);                     \
+    else if (vec && e.esize == 1) KERNEL<1, true><<<grid, kThreads, 0, st>>>(__VA_ARGS__);                \
+    else if (vec && e.esize == 4) KERNEL<4, true><<<grid, kThreads, 0, st>>>(__VA_ARGS__);                \
+    else KERNEL<0, false><<<grid, kThreads, 0, st>>>(__VA_ARGS__);
+    CTB_BM(bm_count_kernel, x, pred, e.esize, e.nz_mask, rows, cols, bitmask, row_offsets)
+    if ((rc = after_launch("bm_count_kernel"))) return rc;
+    row_scan_kernel<<<1, 1024, 0, st>>>(row_offsets, rows, nnz);
+    if ((rc = after_launch("row_scan_kernel"))) return rc;
+    CTB_BM(bm_scatter_kernel, x, pred, e.esize, e.nz_mask, rows, cols, row_offsets, values)
+    return after_launch("bm_scatter_kernel");
+}
+
+extern "C" int ctb_bitmask_compress(const void *x, int32_t dtype, int64_t rows, int64_t cols, void *values, uint8_t *bitmask,
+                                    int64_t *row_offsets, int64_t *nnz, void *stream) {
+    return compress_impl(x, nullptr, dtype, rows, cols, values, bitmask, row_offsets, nnz, stream);
+}
+
+extern "C" int ctb_masked_compress(const void *x, const uint8_t *bytemask, int32_t dtype, int64_t rows, int64_t cols, void *values,
+                                   uint8_t *bitmask, int64_t *row_offsets, int64_t *nnz, void *stream) {
+    if (!bytemask) return fail(CTB_EINVAL_NULL, "null mask");
+    return compress_impl(x, bytemask, dtype, rows, cols, values, bitmask, row_offsets, nnz, stream);
+}
+
+extern "C" int ctb_bitmask_decompress(const void *values, const uint8_t *bitmask, int32_t dtype, int64_t rows, int64_t cols, void *out,
+                                      void *workspace, void *stream) {
+    if (!bitmask || !out || !workspace) return fail(CTB_EINVAL_NULL, "null buffer");
+    ElemInfo e;
+    if (!elem_info(dtype, &e)) return fail(CTB_EINVAL_DTYPE, "unsupported dtype for bitmask decompression");
+    if (rows <= 0 || cols <= 0) return rows < 0 || cols < 0 ? fail(CTB_EINVAL_SHAPE, "negative shape") : CTB_OK;
+    if (!values) return fail(CTB_EINVAL_NULL, "null values");
+    cudaStream_t st = as_stream(stream);
+    int64_t *offs = (int64_t *)workspace;
+    int grid = grid_for(rows, 1, 8);
+    int rc;
+    bm_popcount_kernel<<<grid, kThreads, 0, st>>>(bitmask, rows, cols, offs);
+    if ((rc = after_launch("bm_popcount_kernel"))) return rc;
+    row_scan_kernel<<<1, 1024, 0, st>>>(offs, rows, nullptr);
+    if ((rc = after_launch("row_scan_kernel"))) return rc;
+    const bool vec = cols % 8 == 0 && aligned16(out);
+    if (vec && e.esize == 2) bm_expand_kernel<2, true><<<grid, kThreads, 0, st>>>(values, bitmask, e.esize, rows, cols, offs, out);
+    else if (vec && e.esize == 1) bm_expand_kernel<1, true><<<grid, kThreads, 0, st>>>(values, bitmask, e.esize, rows, cols, offs, out);
+    else if (vec && e.esize == 4) bm_expand_kernel<4, true><<<grid, kThreads, 0, st>>>(values, bitmask, e.esize, rows, cols, offs, out);
+    else bm_expand_kernel<0, false><<<grid, kThreads, 0, st>>>(values, bitmask, e.esize, rows, cols, offs, out);
+    return after_launch("bm_expand_kernel");
+}

@@ -1,0 +1,208 @@
+/*
+ * ctb200 -- C ABI of the B200 (sm_100a) tensor codec that stands in for the torch-CPU
+ * codec path of compressed-tensors.
+ *
+ * Conventions shared by every entry point
+ *   - plain C: raw device pointers, explicit sizes, dtype codes, a CUDA stream handle
+ *     (`void *stream` is a cudaStream_t; NULL = the legacy default stream);
+ *   - returns a ctb_status (0 = ok); never throws, never traps, never synchronises the
+ *     host and, unless a function says otherwise, never allocates;
+ *   - inputs are read-only, outputs are fully overwritten, buffers must not overlap;
+ *   - tensors are dense row-major; leading dimensions are flattened so that every
+ *     operand is a [rows, cols] matrix;
+ *   - ctb_last_error_string() returns a thread-local description of the last failure.
+ *
+ * Citations name the reference function each entry point replaces, by path inside the
+ * reference project (src/compressed_tensors/...):line.
+ */
+#ifndef CTB200_H
+#define CTB200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum ctb_status {
+    CTB_OK = 0,
+    CTB_EINVAL_SHAPE = 1,  /* sizes that the reference rejects too (ValueError there) */
+    CTB_EINVAL_DTYPE = 2,
+    CTB_EINVAL_ALIGN = 3,
+    CTB_EINVAL_NULL = 4,
+    CTB_ETIMEOUT = 5,      /* a bounded device-side wait gave up */
+    CTB_ECUDA = 6,         /* a CUDA runtime call failed; see ctb_last_error_string() */
+    CTB_EUNSUPPORTED = 7   /* valid in the reference, not built here (NotImplementedError) */
+} ctb_status;
+
+typedef enum ctb_dtype {
+    CTB_BF16 = 0,
+    CTB_F16 = 1,
+    CTB_F32 = 2,
+    CTB_F64 = 3,
+    CTB_I8 = 4,
+    CTB_E4M3 = 5, /* float8_e4m3fn */
+    CTB_U8 = 6,
+    CTB_I32 = 7,
+    CTB_I64 = 8
+} ctb_dtype;
+
+typedef enum ctb_qtype { CTB_QINT = 0, CTB_QFLOAT = 1 } ctb_qtype;
+
+/* What a quantize / dequantize call stores or loads on the quantized side. */
+typedef enum ctb_codec {
+    CTB_CODE_DTYPE = 0,  /* one element per value in `q_dtype` (a float dtype, I8 or E4M3) */
+    CTB_CODE_PACK32 = 1, /* int codes packed 32/num_bits per int32 word (pack_to_int32 layout) */
+    CTB_CODE_FP4X2 = 2   /* e2m1 codes, two per byte, even column in the low nibble */
+} ctb_codec;
+
+/*
+ * Geometry of one quantization problem.  The qparam (scale / zero point) that applies to
+ * element (r, c) is  (r / row_group) * scale_row_stride + c / col_group, or, when a g_idx
+ * column map is given,  (r / row_group) * scale_row_stride + g_idx[c].
+ *   TENSOR:  col_group = cols, scale_row_stride = 0, row_group = 1
+ *   CHANNEL / TOKEN: col_group = cols, scale_row_stride = 1
+ *   GROUP / TENSOR_GROUP: col_group = group_size, scale_row_stride = cols / group_size
+ *   BLOCK [bh, bw]: row_group = bh, col_group = bw, scale_row_stride = cols / bw
+ */
+typedef struct ctb_qdesc {
+    int64_t rows, cols;
+    int64_t col_group, row_group, scale_row_stride;
+    int32_t qtype;     /* ctb_qtype */
+    int32_t num_bits;  /* int: 1..8, float: 8 (e4m3) or 4 (e2m1) */
+    int32_t x_dtype;   /* dtype of the dense side (input of quantize, output of dequantize) */
+    int32_t scale_dtype;
+    int32_t zp_dtype;  /* I8 or E4M3; ignored when zero_point is NULL */
+    int32_t q_dtype;   /* dtype of the quantized side when codec == CTB_CODE_DTYPE */
+    int32_t codec;     /* ctb_codec */
+    int32_t reserved;
+} ctb_qdesc;
+
+const char *ctb_version(void);
+const char *ctb_last_error_string(void);
+/* Number of kernels this library has launched in the calling process (all threads). */
+int64_t ctb_launch_count(void);
+
+/* ---- quantize / dequantize / fake_quantize ------------------------------------------
+ * quantization/lifecycle/forward.py:45-81 quantize, :455-487 _quantize and
+ * quantization/quant_args.py:384-408 round_to_quantized_type:
+ *   q = round(clamp(x / scale' + zero_point, qmin, qmax)),  scale' = scale or scale / global_scale,
+ * every intermediate rounded to the dtype torch's promotion rules give it.
+ * With codec PACK32 the codes go straight into pack_to_int32 words
+ * (compressors/quantized_compressors/pack_quantized.py:88-145 compress_weight, :186-246);
+ * with codec FP4X2 into pack_fp4_to_uint8 bytes
+ * (compressors/quantized_compressors/fp4_quantized.py:84-106, :135-178).
+ * g_idx (int32 [cols]) and global_scale (fp32 [1], device) may be NULL. */
+int ctb_quantize(const ctb_qdesc *desc, const void *x, const void *scale, const void *zero_point,
+                 const int32_t *g_idx, const float *global_scale, void *out, void *stream);
+
+/* forward.py:85-153 dequantize, :491-514 _dequantize:  x = (q - zero_point) * scale'.
+ * `q` is read through desc->codec (PACK32 = unpack_from_int32 fused in front,
+ * pack_quantized.py:147-183; FP4X2 = unpack_fp4_from_uint8, fp4_quantized.py:108-123, :187-221);
+ * the result is written in desc->x_dtype.  zero_point is always one int8/e4m3 per qparam. */
+int ctb_dequantize(const ctb_qdesc *desc, const void *q, const void *scale, const void *zero_point,
+                   const int32_t *g_idx, const float *global_scale, void *out, void *stream);
+
+/* forward.py:157-189 fake_quantize: quantize then dequantize without leaving registers.
+ * Input dtype desc->x_dtype, output dtype desc->q_dtype (a float dtype). */
+int ctb_fake_quantize(const ctb_qdesc *desc, const void *x, const void *scale, const void *zero_point,
+                      const int32_t *g_idx, const float *global_scale, void *out, void *stream);
+
+/* ---- quantization parameters ----------------------------------------------------------
+ * quantization/utils/helpers.py:149-205 compute_dynamic_scales_and_zp (the amin/amax part):
+ * min and max over every [row_group x col_group] tile of x, written in x's dtype as
+ * [rows/row_group, cols/col_group].  A tile that spans several thread blocks is combined
+ * through `workspace` (device memory, ctb_minmax_workspace_bytes() bytes, contents ignored). */
+int64_t ctb_minmax_workspace_bytes(int64_t rows, int64_t cols, int64_t row_group, int64_t col_group);
+int ctb_minmax(const void *x, int32_t x_dtype, int64_t rows, int64_t cols, int64_t row_group,
+               int64_t col_group, void *out_min, void *out_max, void *workspace, void *stream);
+
+/* helpers.py:67-146 calculate_qparams over n (min, max) pairs of dtype `dtype`.
+ * Scale is written in `dtype`, or in e4m3 for fp4 with a global scale (:103-120);
+ * zero point in zp_dtype (I8 for int types, E4M3 for float types). */
+int ctb_calculate_qparams(const void *min_vals, const void *max_vals, int32_t dtype, int64_t n,
+                          int32_t qtype, int32_t num_bits, int32_t symmetric,
+                          const float *global_scale, void *out_scale, void *out_zero_point,
+                          int32_t zp_dtype, void *stream);
+
+/* helpers.py:414-434 generate_gparam: 448*6 / max(|min|, |max|) computed in `dtype`, stored as fp32[1]. */
+int ctb_generate_gparam(const void *min_val, const void *max_val, int32_t dtype, float *out,
+                        void *stream);
+
+/* ---- stand-alone packing ---------------------------------------------------------------
+ * pack_quantized.py:186-246 pack_to_int32.  value is int8 [rows, cols] addressed with element
+ * strides (row_stride, col_stride) so that packed_dim=0 is the same call on the transposed view;
+ * out is int32 [rows, ceil(cols / (32/num_bits))] contiguous.  Pad fields are zero. */
+int ctb_pack_int32(const int8_t *value, int64_t rows, int64_t cols, int64_t row_stride,
+                   int64_t col_stride, int32_t num_bits, int32_t *out, void *stream);
+/* pack_quantized.py:249-309 unpack_from_int32.  words int32 [rows, ceil(cols/pf)] addressed with
+ * element strides; out int8 [rows, cols] contiguous. */
+int ctb_unpack_int32(const int32_t *words, int64_t rows, int64_t cols, int64_t row_stride,
+                     int64_t col_stride, int32_t num_bits, int8_t *out, void *stream);
+/* fp4_quantized.py:135-178 pack_fp4_to_uint8: x [m, n] of `dtype` holding e2m1 grid values
+ * -> uint8 [m, n/2]; odd n is CTB_EINVAL_SHAPE. */
+int ctb_pack_fp4(const void *x, int32_t dtype, int64_t m, int64_t n, uint8_t *out, void *stream);
+/* fp4_quantized.py:187-221 unpack_fp4_from_uint8 -> [m, n] of out_dtype. */
+int ctb_unpack_fp4(const uint8_t *packed, int64_t m, int64_t n, void *out, int32_t out_dtype,
+                   void *stream);
+/* utils/helpers.py:302-313 pack_bitmasks: bool/uint8 [rows, cols] -> uint8 [rows, ceil(cols/8)],
+ * column 8k+j in bit j of byte k. */
+int ctb_pack_bitmasks(const uint8_t *bytemask, int64_t rows, int64_t cols, uint8_t *out, void *stream);
+/* utils/helpers.py:316-339 unpack_bitmasks -> uint8 0/1 [rows, cols]. */
+int ctb_unpack_bitmasks(const uint8_t *packed, int64_t rows, int64_t cols, uint8_t *out, void *stream);
+
+/* ---- sparse codecs ---------------------------------------------------------------------
+ * compressors/sparse_compressors/sparse_24_bitmask.py:227-260 get_24_bytemasks: keep-mask of the
+ * two largest magnitudes in every run of 4 consecutive elements (flat view), ties resolved as
+ * torch.topk does on CPU.  dtype: BF16 / F16 / F32 / I8 / E4M3 (ranked through its int8 view). */
+int ctb_sparse24_mask(const void *x, int32_t dtype, int64_t numel, uint8_t *out_bytemask, void *stream);
+/* sparse_24_bitmask.py:162-203 sparse24_bitmask_compress for cols % 8 == 0:
+ * values [rows, cols/2] (same dtype as x) and bitmask uint8 [rows, ceil(cols/8)] in one pass. */
+int ctb_sparse24_compress(const void *x, int32_t dtype, int64_t rows, int64_t cols, void *out_values,
+                          uint8_t *out_bitmask, void *stream);
+/* compressors/sparse_compressors/sparse_bitmask.py:131-149 bitmask_compress.
+ * out_values needs room for rows*cols elements; the first *out_nnz (device int64) are valid,
+ * row-major.  out_row_offsets is int64 [rows] (exclusive prefix of per-row counts).
+ * Elements equal to zero (+0.0 and -0.0) are dropped; NaN is kept. */
+int ctb_bitmask_compress(const void *x, int32_t dtype, int64_t rows, int64_t cols, void *out_values,
+                         uint8_t *out_bitmask, int64_t *out_row_offsets, int64_t *out_nnz,
+                         void *stream);
+/* The same compaction with the keep-mask given explicitly (uint8 0/1 [rows, cols]): the reference's
+ * `tensor[bytemasks]` + pack_bitmasks (sparse_24_bitmask.py:192-203) for shapes the fused 2:4 kernel
+ * does not take (cols % 8 != 0). */
+int ctb_masked_compress(const void *x, const uint8_t *bytemask, int32_t dtype, int64_t rows, int64_t cols,
+                        void *out_values, uint8_t *out_bitmask, int64_t *out_row_offsets,
+                        int64_t *out_nnz, void *stream);
+/* sparse_bitmask.py:152-169 bitmask_decompress and sparse_24_bitmask.py:206-224
+ * sparse24_bitmask_decompress: zeros, then values scattered row-major to the set bits.
+ * `workspace` is device scratch of rows*8 bytes (per-row start offsets are rebuilt from the
+ * bitmask; the reference does not consult row_offsets either). */
+int ctb_bitmask_decompress(const void *values, const uint8_t *bitmask, int32_t dtype, int64_t rows,
+                           int64_t cols, void *out, void *workspace, void *stream);
+
+/* ---- Hadamard rotation -------------------------------------------------------------------
+ * transform/factory/hadamard.py:104-121 HadamardTransform.forward with
+ * transform/utils/matrix.py:65-134 apply_transform_weight for torch.nn.Linear weights:
+ *   side 0 (weight_input):  out = W @ Wh^T per n-column block,
+ *   side 1 (weight_output): out = Wh^T @ W per n-row block,
+ * Wh = diag(signs) @ H_n (Sylvester; signs int8 +-1 [n] or NULL = all +1; transform/utils/
+ * hadamard.py:33-89), transposed when `inverse`; result / sqrt(n) cast to the dtype of W.
+ * precision: CTB_F64 accumulates like the reference's offline path; CTB_F32 is the fast mode. */
+int ctb_hadamard(const void *x, int32_t dtype, int64_t rows, int64_t cols, int32_t n,
+                 const int8_t *signs, int32_t inverse, int32_t side, int32_t precision, void *out,
+                 void *stream);
+
+/* ---- fused calibrate + quantize + pack (single pass over the dense tensor) -------------------
+ * Symmetric min-max calibration (helpers.py:67-146 with the group's own amin/amax) followed by
+ * ctb_quantize with the scales it produced.  out_scale is written in desc->scale_dtype, which
+ * must equal desc->x_dtype; zero points are all zero and not written.
+ * With n > 0 the weight_input Hadamard rotation of ctb_hadamard (side 0) is applied in front,
+ * rounding to x_dtype in between exactly as the two separate calls would. */
+int ctb_absmax_quantize(const ctb_qdesc *desc, const void *x, const float *global_scale,
+                        void *out_scale, void *out, int32_t hadamard_n, const int8_t *signs,
+                        int32_t precision, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CTB200_H */
