@@ -1,0 +1,300 @@
+#!/usr/bin/env python
+"""Benchmark of the tensor-codec hot path on B200.
+
+Workload (BASELINE.json configs[4]): every Linear weight of a Llama-3-8B-shaped model (32 layers,
+bf16, N(0, 0.02), synthetic), random-Hadamard rotation (block 128) fused with W4A16 int4 group-128
+quantize + pack_to_int32, then unpack + dequantize.  Layers are dealt to the ranks in contiguous
+blocks (strong scaling: the model is fixed, ranks split it); no collective is on the data path.
+
+One "step" = compress every weight of the shard, then decompress every weight of the shard.
+value = bf16 bytes through both directions (2 x weight bytes, all ranks) / max-over-ranks device time.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+METRIC = "bf16 weight GB/s through quantize+pack / unpack+dequant"
+UNIT = "GB/s"
+WORKLOAD = "llama3-8b-linears hadamard128+w4a16-g128 compress+decompress"
+SEED = 0
+ALG_BYTES_PER_ELEM = 2 + 0.5 + 2 / 128  # bf16 in, 4 bits out, one bf16 scale per 128 (either direction)
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return float(json.load(open(p))["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            pass
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        out, _ = self.proc.communicate(timeout=10)
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0])); mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        # "under load": the upper half of the samples (idle samples before/after the region sit low)
+        hi = sorted(sm)[len(sm) // 2:]
+        return {"sm_mhz": statistics.median(hi), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def make_weights(layers, device, shapes):
+    ws = []
+    for layer in layers:
+        for j, (_, o, i) in enumerate(shapes):
+            g = torch.Generator(device=device).manual_seed(SEED * 1000003 + layer * 16 + j)
+            ws.append((torch.randn(o, i, generator=g, device=device, dtype=torch.float32) * 0.02).to(torch.bfloat16))
+    return ws
+
+
+def make_signs():
+    g = torch.Generator().manual_seed(SEED)
+    return (torch.randint(0, 2, (128,), generator=g) * 2 - 1).to(torch.int8)
+
+
+def time_region(fn, steps, stream):
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record(stream)
+    for _ in range(steps):
+        fn()
+    end.record(stream)
+    end.synchronize()
+    return start.elapsed_time(end) / 1e3  # seconds
+
+
+def cpu_pass(ws, signs):
+    """One pass of the path on the host through the oracle port (rotate, calibrate, quantize, pack, unpack, dequantize)."""
+    from oracle import ref as orc
+    out = 0
+    for w in ws:
+        rot = orc.hadamard(w, 128, signs=signs)
+        mn, mx = orc.minmax(rot, 1, 128)
+        scale, zp = orc.calculate_qparams(mn, mx, qtype=orc.QINT, bits=4, symmetric=True)
+        kw = dict(qtype=orc.QINT, bits=4, col_group=128, row_group=1, scale_row_stride=w.shape[1] // 128)
+        words = orc.pack_int32(orc.quantize(rot, scale, zp, out_dtype=torch.int8, **kw), 4)
+        deq = orc.dequantize(orc.unpack_int32(words, 4, w.shape), scale, None, out_dtype=torch.bfloat16, **kw)
+        out += deq.numel()
+    return out
+
+
+def cpu_sample():
+    """Bounded sample of the workload for the CPU arm: q_proj, k_proj and gate_proj of one layer."""
+    g = torch.Generator().manual_seed(SEED)
+    return [(torch.randn(o, i, generator=g) * 0.02).to(torch.bfloat16) for o, i in ((4096, 4096), (1024, 4096), (14336, 4096))]
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import ref as orc
+    orc.build()
+    cores = os.cpu_count() or 1
+    orc.set_threads(cores)
+    ws, signs = cpu_sample(), make_signs()
+    elems = sum(w.numel() for w in ws)
+    for _ in range(args.warmup):
+        cpu_pass(ws, signs)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_pass(ws, signs)
+    dt = (time.perf_counter() - t0) / args.steps
+    val = 2 * 2 * elems / dt / 1e9
+    sample = "q_proj 4096x4096 + k_proj 1024x4096 + gate_proj 14336x4096 of one layer per step"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic", "config": {"workload": WORKLOAD, "sample": sample},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--precision", default="f64", choices=["f64", "f32"], help="accumulation of the Hadamard rotation")
+    ap.add_argument("--layers", type=int, default=32, help="decoder layers of the model (32 = Llama-3-8B)")
+    ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch.distributed as dist
+    from compressed_tensors_b200 import _lib, ops, parallel
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    model = parallel.LLAMA3_8B
+    shapes = parallel.linear_shapes(model)
+    my_layers = parallel.partition_layers(args.layers, world, rank)
+    weights = make_weights(my_layers, dev, shapes)
+    signs = make_signs().to(dev)
+    precision = torch.float64 if args.precision == "f64" else torch.float32
+    codec = parallel.ShardCodec(weights, group_size=128, hadamard_n=128, signs=signs, precision=precision, use_graphs=not args.no_graphs)
+    stream = torch.cuda.current_stream()
+    my_elems = codec.numel
+    total_elems = sum(o * i for _, o, i in shapes) * args.layers
+
+    def step():
+        codec.compress()
+        codec.decompress()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    launches0 = _lib.launch_count()
+    sampler = ClockSampler(local) if rank == 0 else None
+    t = time_region(step, args.steps, stream)
+    barrier()
+    clocks = sampler.stop() if sampler else None
+    launches = _lib.launch_count() - launches0
+    if codec.use_graphs:
+        launches = 2 * codec.launches_per_pass * args.steps  # replayed from CUDA graphs
+    # phase timings for the roofline (same region, compress and decompress timed apart)
+    tc = time_region(codec.compress, args.steps, stream)
+    td = time_region(codec.decompress, args.steps, stream)
+    barrier()
+    times = torch.tensor([t, tc, td], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    t, tc, td = (float(v) for v in times.cpu())
+
+    # ---- end to end: host buffers in, host buffers out, copies inside the timed region
+    e2e = None
+    if not args.no_e2e:
+        host_w = [torch.empty(w.shape, dtype=w.dtype, pin_memory=True).copy_(w) for w in weights]
+        plain = parallel.ShardCodec(weights, group_size=128, hadamard_n=128, signs=signs, precision=precision, use_graphs=False)
+        plain._compress()
+        host_p = [torch.empty(p.shape, dtype=p.dtype, pin_memory=True) for p in plain.packed]
+        host_s = [torch.empty(s.shape, dtype=s.dtype, pin_memory=True) for s in plain.scales]
+        host_r = [torch.empty(w.shape, dtype=w.dtype, pin_memory=True) for w in weights]
+        torch.cuda.synchronize()
+
+        def e2e_step():
+            for i, hw in enumerate(host_w):
+                w = hw.to(dev, non_blocking=True)
+                p, s = ops.absmax_quantize(w, qtype=ops.QINT, bits=4, col_group=128, codec="pack32", hadamard_n=128, signs=signs, precision=precision)
+                host_p[i].copy_(p, non_blocking=True)
+                host_s[i].copy_(s, non_blocking=True)
+            for i, hw in enumerate(host_w):
+                p, s = host_p[i].to(dev, non_blocking=True), host_s[i].to(dev, non_blocking=True)
+                cols = hw.shape[1]
+                r = ops.dequantize(p, s, None, qtype=ops.QINT, bits=4, col_group=128, scale_row_stride=cols // 128,
+                                   out_dtype=torch.bfloat16, codec="pack32", cols=cols)
+                host_r[i].copy_(r, non_blocking=True)
+            torch.cuda.synchronize()
+
+        e2e_step()
+        barrier()
+        k = max(1, min(args.steps, 3))
+        t0 = time.perf_counter()
+        for _ in range(k):
+            e2e_step()
+        te = torch.tensor([(time.perf_counter() - t0) / k], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        packed_bytes = sum(p.numel() * 4 for p in host_p) + sum(s.numel() * 2 for s in host_s)
+        e2e = {"value": 2 * 2 * total_elems / float(te) / 1e9, "unit": UNIT,
+               "h2d_bytes_per_step": 2 * my_elems + packed_bytes, "d2h_bytes_per_step": packed_bytes + 2 * my_elems,
+               "ms_per_step": float(te) * 1e3, "bytes_are": "per rank"}
+        del host_w, host_p, host_s, host_r, plain
+
+    if rank == 0:
+        peak, peak_kind = peaks()
+        ms = t / args.steps * 1e3
+        # dominant kernel: the fused rotate+calibrate+quantize+pack launches of the compress phase.
+        # per-rank algorithmic bytes of one compress pass / per-rank device time of that pass
+        rank_elems = total_elems / world
+        achieved = ALG_BYTES_PER_ELEM * rank_elems / (tc / args.steps) / 1e9
+        out = {
+            "metric": METRIC, "value": 2 * 2 * total_elems / (t / args.steps) / 1e9, "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "layers": args.layers, "tensors_per_rank": len(weights), "partition": f"layers/{world}",
+                       "hadamard_accumulate": args.precision, "l2": "inputs larger than L2 (no flush needed)",
+                       "cuda_graphs": codec.use_graphs},
+            "compress_gbs": 2 * total_elems / (tc / args.steps) / 1e9, "decompress_gbs": 2 * total_elems / (td / args.steps) / 1e9,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "kernel": "absmax_quant_group_kernel", "peak_kind": peak_kind,
+                         "decompress_frac": ALG_BYTES_PER_ELEM * rank_elems / (td / args.steps) / 1e9 / peak},
+            "clocks": clocks, "gpu_launches": int(launches), "e2e": e2e,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            from oracle import ref as orc
+            orc.build()
+            cores = os.cpu_count() or 1
+            orc.set_threads(cores)
+            ws, sg = cpu_sample(), make_signs()
+            cpu_pass(ws, sg)
+            t0 = time.perf_counter()
+            reps = 2
+            for _ in range(reps):
+                cpu_pass(ws, sg)
+            dt = (time.perf_counter() - t0) / reps
+            out["cpu_baseline"] = {"value": 2 * 2 * sum(w.numel() for w in ws) / dt / 1e9, "unit": UNIT, "cores": cores, "kind": "port",
+                                   "sample": "q_proj + k_proj + gate_proj of one layer, 2 passes"}
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

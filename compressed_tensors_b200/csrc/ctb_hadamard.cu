@@ -94,6 +94,7 @@ __device__ __forceinline__ void rotate8(const HArgs &a, int64_t c, float (&v)[8]
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         if (!a.inverse) v[i] *= sg[i];
+        v[i] += 0.0f;  // an exact zero comes out of the reference's matmul as +0.0, whatever the signs
         v[i] = round_to<XF == F_BF16 ? CTB_BF16 : XF == F_F16 ? CTB_F16 : CTB_F32>(v[i]);
     }
 }
@@ -150,6 +151,7 @@ __global__ void __launch_bounds__(kThreads) hadamard_rows_kernel(const void *x, 
                 A v = tile[r * 33 + c] / scale;
                 float f = (float)v;
                 if (inverse && signs) f *= (float)signs[r];
+                f += 0.0f;  // exact zeros are +0.0 in the reference's matmul
                 store_f32(out, dt, (r0 + r) * cols + c0 + c, f);
             }
         }

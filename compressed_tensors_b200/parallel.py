@@ -1,0 +1,132 @@
+"""Partitioning of a whole-model compress / decompress over the GPUs of one node.
+
+The reference walks the state dict one tensor at a time on one CPU
+(compressors/quantized_compressors/base.py:69-134, model_compressors/model_compressor.py:453-617).
+Every weight is an independent unit of work, so the walk shards with no data-path collective:
+decoder layers are dealt to ranks in contiguous blocks and each rank runs the fused kernels on its
+own tensors.  A collective is needed only when ONE tensor's reduction is split across ranks (the
+NVFP4 global scale / TENSOR strategy); `allreduce_amax` covers that case with a 4-byte
+all-reduce(max), which is exact and order independent, so results do not depend on the world size.
+"""
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+__all__ = ["LLAMA3_8B", "ModelShape", "linear_shapes", "partition_layers", "allreduce_amax", "ShardCodec"]
+
+
+@dataclass(frozen=True)
+class ModelShape:
+    layers: int
+    hidden: int
+    intermediate: int
+    q_heads: int
+    kv_heads: int
+    head_dim: int
+    vocab: int
+
+
+LLAMA3_8B = ModelShape(layers=32, hidden=4096, intermediate=14336, q_heads=32, kv_heads=8, head_dim=128, vocab=128256)
+
+
+def linear_shapes(m: ModelShape) -> List[Tuple[str, int, int]]:
+    """(name, out_features, in_features) of the Linear weights of one decoder layer."""
+    kv = m.kv_heads * m.head_dim
+    q = m.q_heads * m.head_dim
+    return [
+        ("self_attn.q_proj", q, m.hidden),
+        ("self_attn.k_proj", kv, m.hidden),
+        ("self_attn.v_proj", kv, m.hidden),
+        ("self_attn.o_proj", m.hidden, q),
+        ("mlp.gate_proj", m.intermediate, m.hidden),
+        ("mlp.up_proj", m.intermediate, m.hidden),
+        ("mlp.down_proj", m.hidden, m.intermediate),
+    ]
+
+
+def partition_layers(num_layers: int, world_size: int, rank: int) -> range:
+    """Contiguous block of layers owned by `rank`; the first `num_layers % world_size` ranks get one more."""
+    if world_size <= 0 or not (0 <= rank < world_size):
+        raise ValueError(f"bad rank {rank} for world size {world_size}")
+    base, extra = divmod(num_layers, world_size)
+    start = rank * base + min(rank, extra)
+    return range(start, start + base + (1 if rank < extra else 0))
+
+
+def allreduce_amax(min_val: torch.Tensor, max_val: torch.Tensor, group=None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Combine per-rank (min, max) of a tensor that is split across ranks.  No-op without a process group."""
+    import torch.distributed as dist
+
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
+        return min_val, max_val
+    # one message: [max, -min] reduced with MAX (fp32 holds bf16/fp16/fp32 extrema exactly)
+    buf = torch.stack([max_val.float().reshape(()), -min_val.float().reshape(())])
+    dist.all_reduce(buf, op=dist.ReduceOp.MAX, group=group)
+    return (-buf[1]).to(min_val.dtype).reshape(min_val.shape), buf[0].to(max_val.dtype).reshape(max_val.shape)
+
+
+class ShardCodec:
+    """Pre-planned compress / decompress of one rank's weights: random-Hadamard rotation (block
+    `hadamard_n`, weight_input) fused with W4A16 group quantize + pack_to_int32, and the inverse
+    unpack + dequantize.  Output buffers are allocated once; `use_graphs` replays the launches from
+    CUDA graphs so that a shard of many small tensors is not bound by launch latency."""
+
+    def __init__(self, weights: Sequence[torch.Tensor], *, group_size: int = 128, hadamard_n: int = 128,
+                 signs: Optional[torch.Tensor] = None, precision=torch.float64, use_graphs: bool = False):
+        from . import ops
+
+        self.ops = ops
+        self.weights = list(weights)
+        self.group_size, self.hadamard_n, self.precision = group_size, hadamard_n, precision
+        dev = self.weights[0].device
+        self.signs = None if signs is None else signs.to(device=dev, dtype=torch.int8)
+        self.packed: List[Optional[torch.Tensor]] = [None] * len(self.weights)
+        self.scales: List[Optional[torch.Tensor]] = [None] * len(self.weights)
+        self.restored: List[Optional[torch.Tensor]] = [None] * len(self.weights)
+        self._graphs: Dict[str, torch.cuda.CUDAGraph] = {}
+        self.use_graphs = use_graphs
+
+    # ------------------------------------------------------------------ plain launches
+    def _compress(self) -> None:
+        for i, w in enumerate(self.weights):
+            self.packed[i], self.scales[i] = self.ops.absmax_quantize(
+                w, qtype=self.ops.QINT, bits=4, col_group=self.group_size, codec="pack32",
+                hadamard_n=self.hadamard_n, signs=self.signs, precision=self.precision)
+
+    def _decompress(self) -> None:
+        for i, w in enumerate(self.weights):
+            cols = w.shape[1]
+            self.restored[i] = self.ops.dequantize(
+                self.packed[i], self.scales[i], None, qtype=self.ops.QINT, bits=4, col_group=self.group_size,
+                scale_row_stride=cols // self.group_size, out_dtype=w.dtype, codec="pack32", cols=cols)
+
+    # ------------------------------------------------------------------ graph replay
+    def _run(self, name: str, fn) -> None:
+        if not self.use_graphs:
+            fn()
+            return
+        g = self._graphs.get(name)
+        if g is None:
+            fn()  # warm-up outside capture (first call may initialise library state)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                fn()
+            self._graphs[name] = g
+        g.replay()
+
+    def compress(self) -> None:
+        self._run("compress", self._compress)
+
+    def decompress(self) -> None:
+        self._run("decompress", self._decompress)
+
+    # ------------------------------------------------------------------ accounting
+    @property
+    def numel(self) -> int:
+        return sum(w.numel() for w in self.weights)
+
+    @property
+    def launches_per_pass(self) -> int:
+        return len(self.weights)
