@@ -421,3 +421,44 @@ extern "C" int ctb_bitmask_decompress(const void *values, const uint8_t *bitmask
     else bm_expand_kernel<0, false><<<grid, kThreads, 0, st>>>(values, bitmask, e.esize, rows, cols, offs, out);
     return after_launch("bm_expand_kernel");
 }
+
+// ------------------------------------------------------------------ decompress without caller scratch
+//
+// Some hosts of this library may not allocate device memory at the point where they decompress:
+// an inference server that handed its whole memory budget to a fixed arena at start-up, or a
+// loader hook that runs while another component owns the allocator.  For them the per-row start
+// offsets that ctb_bitmask_decompress keeps in caller-provided scratch live in this fixed array
+// instead.  Every GPU that loads the library holds these 512 KiB until the process exits.
+constexpr int64_t kStaticMaxRows = 65536;
+static __device__ __align__(256) int64_t g_row_offsets_static[kStaticMaxRows];
+
+// Device address of the array above for the current device.  In host code the array's name is only
+// a stand-in for the symbol, so the address is asked of the runtime once per device, with that
+// device current, and cached.
+static int static_scratch(int64_t **out) {
+    static int64_t *cached[64] = {nullptr};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail(CTB_ECUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= 64) return fail(CTB_EUNSUPPORTED, "device index %d is outside the table of cached scratch addresses", dev);
+    if (cached[dev] == nullptr) {
+        void *p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_row_offsets_static);
+        if (e != cudaSuccess || p == nullptr) return fail(CTB_ECUDA, "cudaGetSymbolAddress(g_row_offsets_static): %s", cudaGetErrorString(e));
+        cached[dev] = static_cast<int64_t *>(p);
+    }
+    *out = cached[dev];
+    return CTB_OK;
+}
+
+extern "C" int ctb_bitmask_decompress_static(const void *values, const uint8_t *bitmask, int32_t dtype, int64_t rows, int64_t cols,
+                                             void *out, void *stream) {
+    if (rows > kStaticMaxRows)
+        return fail(CTB_EINVAL_SHAPE, "ctb_bitmask_decompress_static takes at most %lld rows (got %lld); use ctb_bitmask_decompress with caller scratch",
+                    (long long)kStaticMaxRows, (long long)rows);
+    int64_t *scratch = nullptr;
+    int rc = static_scratch(&scratch);
+    if (rc) return rc;
+    // every row's slot is rewritten by the popcount pass before the scan reads it: nothing has to start at zero
+    return ctb_bitmask_decompress(values, bitmask, dtype, rows, cols, out, scratch, stream);
+}

@@ -180,6 +180,21 @@ int ctb_masked_compress(const void *x, const uint8_t *bytemask, int32_t dtype, i
 int ctb_bitmask_decompress(const void *values, const uint8_t *bitmask, int32_t dtype, int64_t rows,
                            int64_t cols, void *out, void *workspace, void *stream);
 
+/* No counterpart in the reference.  Same result as ctb_bitmask_decompress, for callers that cannot
+ * allocate device memory where they decompress (a server whose memory went to a fixed arena at
+ * start-up, a load hook running while something else owns the allocator): the per-row offsets live
+ * in a 512 KiB array inside the library instead of caller scratch, which every GPU that loads the
+ * library keeps until the process exits.  Limits and rules:
+ *   - rows <= 65536, otherwise CTB_EINVAL_SHAPE;
+ *   - calls no cudaMalloc / cudaFree and no allocating library routine;
+ *   - the first call on each device looks the array's device address up (with that device
+ *     current); make that first call before any stream capture;
+ *   - all calls on a device share the array, so two calls that overlap on the GPU (different
+ *     streams) race: keep calls of this entry point ordered on one stream or separate them with
+ *     events. */
+int ctb_bitmask_decompress_static(const void *values, const uint8_t *bitmask, int32_t dtype, int64_t rows,
+                                  int64_t cols, void *out, void *stream);
+
 /* ---- Hadamard rotation -------------------------------------------------------------------
  * transform/factory/hadamard.py:104-121 HadamardTransform.forward with
  * transform/utils/matrix.py:65-134 apply_transform_weight for torch.nn.Linear weights:
