@@ -114,3 +114,13 @@ def i64(v) -> ctypes.c_int64:
 
 def i32(v) -> ctypes.c_int32:
     return ctypes.c_int32(int(v))
+
+
+def on_gpu(t):
+    """Host plumbing for callers that hand in CPU tensors (the reference's compressors accept any
+    device): copy to the current CUDA device.  The arithmetic still runs only in the CUDA kernels."""
+    if t is None or t.is_cuda:
+        return t
+    if not torch.cuda.is_available():
+        raise RuntimeError("compressed_tensors_b200 needs a CUDA device (no CPU fallback)")
+    return t.cuda()

@@ -65,6 +65,7 @@ struct HArgs {
     int n;            // Hadamard size (0 = no rotation, fused calibrate+quantize only)
     int L;            // lanes per Hadamard block = n / 8
     int inverse;
+    int normalize;    // divide by sqrt(n) (the reference's HadamardTransform) or leave the raw product
     int GL;           // lanes per quantization group = col_group / 8 (fused)
     int xdt;
     float qmin, qmax, half_range;
@@ -83,11 +84,11 @@ __device__ __forceinline__ void rotate8(const HArgs &a, int64_t c, float (&v)[8]
     fwht8<A>(t);
     fwht_lanes<A>(t, a.L, lane_in_block);
     if constexpr (sizeof(A) == 8) {
-        const double s = sqrt((double)a.n);
+        const double s = a.normalize ? sqrt((double)a.n) : 1.0;
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[i] = (float)(t[i] / s);  // float64 quotient, then the cast chain of .to(dtype)
     } else {
-        const float s = 1.0f / sqrtf((float)a.n);
+        const float s = a.normalize ? 1.0f / sqrtf((float)a.n) : 1.0f;
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[i] = t[i] * s;
     }
@@ -118,11 +119,11 @@ __global__ void __launch_bounds__(kThreads) hadamard_cols_kernel(const HArgs a) 
 // weight_output rotation: a [n rows x 32 cols] tile per block, butterflies over rows in shared memory
 template <typename A>
 __global__ void __launch_bounds__(kThreads) hadamard_rows_kernel(const void *x, int dt, int64_t rows, int64_t cols, int n, const int8_t *signs,
-                                                                  int inverse, void *out) {
+                                                                  int inverse, int normalize, void *out) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     A *tile = reinterpret_cast<A *>(smem_raw);  // [n][33]
     const int64_t col_tiles = (cols + 31) / 32, tiles = (rows / n) * col_tiles;
-    const A scale = (A)sqrt((double)n);
+    const A scale = normalize ? (A)sqrt((double)n) : (A)1;
     for (int64_t t = blockIdx.x; t < tiles; t += gridDim.x) {
         const int64_t r0 = (t / col_tiles) * n, c0 = (t % col_tiles) * 32;
         for (int i = threadIdx.x; i < n * 32; i += kThreads) {
@@ -262,7 +263,7 @@ using namespace ctb;
 static bool pow2(int64_t v) { return v > 0 && (v & (v - 1)) == 0; }
 
 extern "C" int ctb_hadamard(const void *x, int32_t dtype, int64_t rows, int64_t cols, int32_t n, const int8_t *signs, int32_t inverse,
-                            int32_t side, int32_t precision, void *out, void *stream) {
+                            int32_t side, int32_t precision, int32_t normalize, void *out, void *stream) {
     if (!x || !out) return fail(CTB_EINVAL_NULL, "null buffer");
     if (!is_float_dtype(dtype)) return fail(CTB_EINVAL_DTYPE, "weights must be bf16, f16 or f32");
     if (!pow2(n)) return fail(CTB_EUNSUPPORTED, "only Sylvester sizes (powers of two) are built");
@@ -274,7 +275,7 @@ extern "C" int ctb_hadamard(const void *x, int32_t dtype, int64_t rows, int64_t 
         if (cols % n) return fail(CTB_EINVAL_SHAPE, "columns %lld are not a multiple of the Hadamard size %d", (long long)cols, n);
         if (n >= 8 && n <= 256 && aligned16(x) && aligned16(out)) {
             HArgs a{};
-            a.x = x; a.signs = signs; a.out = out; a.chunks = rows * cols / 8; a.n = n; a.L = n / 8; a.inverse = inverse; a.xdt = dtype;
+            a.x = x; a.signs = signs; a.out = out; a.chunks = rows * cols / 8; a.n = n; a.L = n / 8; a.inverse = inverse; a.normalize = normalize; a.xdt = dtype;
             int grid = grid_for(a.chunks, kThreads, 8);
 #define CTB_HC(A_)                                                                                   \
     if (dtype == CTB_BF16) hadamard_cols_kernel<A_, F_BF16><<<grid, kThreads, 0, st>>>(a);            \
@@ -293,11 +294,11 @@ extern "C" int ctb_hadamard(const void *x, int32_t dtype, int64_t rows, int64_t 
     if (precision == CTB_F64) {
         size_t smem = (size_t)n * 33 * sizeof(double);
         cudaFuncSetAttribute(hadamard_rows_kernel<double>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        hadamard_rows_kernel<double><<<grid, kThreads, smem, st>>>(x, dtype, rows, cols, n, signs, inverse, out);
+        hadamard_rows_kernel<double><<<grid, kThreads, smem, st>>>(x, dtype, rows, cols, n, signs, inverse, normalize, out);
     } else {
         size_t smem = (size_t)n * 33 * sizeof(float);
         cudaFuncSetAttribute(hadamard_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        hadamard_rows_kernel<float><<<grid, kThreads, smem, st>>>(x, dtype, rows, cols, n, signs, inverse, out);
+        hadamard_rows_kernel<float><<<grid, kThreads, smem, st>>>(x, dtype, rows, cols, n, signs, inverse, normalize, out);
     }
     return after_launch("hadamard_rows_kernel");
 }
@@ -322,7 +323,7 @@ extern "C" int ctb_absmax_quantize(const ctb_qdesc *d, const void *x, const floa
     if (d->rows == 0) return CTB_OK;
     HArgs a{};
     a.x = x; a.signs = signs; a.out = out; a.out_scale = out_scale; a.gs = gs;
-    a.chunks = d->rows * d->cols / 8; a.n = n; a.L = n > 0 ? n / 8 : 1; a.inverse = 0; a.xdt = d->x_dtype;
+    a.chunks = d->rows * d->cols / 8; a.n = n; a.L = n > 0 ? n / 8 : 1; a.inverse = 0; a.normalize = 1; a.xdt = d->x_dtype;
     if (qk == QK_INT) { a.qmax = (float)(1 << d->num_bits) / 2 - 1; a.qmin = -(float)(1 << d->num_bits) / 2; }
     else if (qk == QK_FP8) { a.qmax = 448.0f; a.qmin = -448.0f; }
     else { a.qmax = 6.0f; a.qmin = -6.0f; }

@@ -285,7 +285,7 @@ def bitmask_decompress(values, bitmask, shape):
     return out
 
 
-def hadamard(x, n, signs=None, inverse=False, side=0, precision=torch.float64):
+def hadamard(x, n, signs=None, inverse=False, side=0, precision=torch.float64, normalize=True):
     """transform/factory/hadamard.py:104 HadamardTransform.forward for a Linear weight
     (side 0 = weight_input, 1 = weight_output)."""
     require_cuda(x, signs)
@@ -294,7 +294,7 @@ def hadamard(x, n, signs=None, inverse=False, side=0, precision=torch.float64):
     s = None if signs is None else _c(signs.to(torch.int8))
     out = torch.empty_like(x)
     check(lib().ctb_hadamard(ptr(x), i32(DT[x.dtype]), i64(rows), i64(cols), i32(n), ptr(s), i32(int(inverse)), i32(side),
-                             i32(DT[precision]), ptr(out), stream_of(x)))
+                             i32(DT[precision]), i32(int(normalize)), ptr(out), stream_of(x)))
     return out
 
 

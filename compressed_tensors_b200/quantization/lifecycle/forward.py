@@ -1,0 +1,118 @@
+"""quantize / dequantize / fake_quantize with the reference's signatures
+(quantization/lifecycle/forward.py:45-189).  The host part only works out how the scale tensor
+lines up with the input (strategy -> group geometry) and which dtype the reference would return;
+all arithmetic runs in the ctb200 kernels."""
+from typing import Optional, Tuple
+
+import torch
+
+from ... import ops
+from ..quant_args import QuantizationArgs, QuantizationStrategy
+from ..utils.helpers import qtype_code
+
+__all__ = ["quantize", "dequantize", "fake_quantize", "infer_dequant_args"]
+
+_FLOATS = (torch.bfloat16, torch.float16, torch.float32)
+
+
+def _promote(a: torch.dtype, b: torch.dtype) -> torch.dtype:
+    return a if a == b else torch.float32
+
+
+def _geometry(x: torch.Tensor, scale: torch.Tensor, args: QuantizationArgs) -> Tuple[int, int, int]:
+    """(col_group, row_group, scale_row_stride) for x viewed as [rows, cols]."""
+    cols = x.shape[-1]
+    rows = x.numel() // cols if cols else 0
+    strategy = args.strategy
+    if strategy == QuantizationStrategy.BLOCK:
+        if x.ndim != 2:
+            raise NotImplementedError("block quantization is built for 2-D tensors")
+        bh, bw = args.block_structure
+        if rows % bh != 0:  # forward.py:215-219
+            raise ValueError(f"Tensor height {rows} is not divisible by block_height {bh}. Block quantization requires exact division.")
+        if cols % bw != 0:  # forward.py:220-224
+            raise ValueError(f"Tensor width {cols} is not divisible by block_width {bw}. Block quantization requires exact division.")
+        return bw, bh, cols // bw
+    if strategy in (QuantizationStrategy.GROUP, QuantizationStrategy.TENSOR_GROUP):
+        g = args.group_size
+        if cols >= g and cols % g != 0:  # forward.py:277-282
+            raise ValueError(f"tensor column shape must be divisble by the given group_size {g} but got {cols}")
+        if cols < g:
+            raise ValueError(f"group_size {g} exceeds the {cols} columns of the tensor")
+        groups = cols // g
+        if scale.numel() == rows * groups:
+            return g, 1, groups
+        if scale.numel() == groups:  # one row of scales shared by every row
+            return g, 1, 0
+        raise ValueError(f"scale of shape {tuple(scale.shape)} does not match {rows} rows x {groups} groups")
+    # TENSOR / CHANNEL / TOKEN: the scale broadcasts against x
+    if scale.numel() == 1:
+        return cols, 1, 0
+    if scale.numel() == rows and (scale.ndim == 0 or scale.shape[-1] == 1):
+        return cols, 1, 1
+    raise NotImplementedError(f"strategy {strategy} with a scale of shape {tuple(scale.shape)} against input {tuple(x.shape)} is not built")
+
+
+def infer_dequant_args(x_q: torch.Tensor, scale: torch.Tensor) -> QuantizationArgs:
+    """Strategy inference of dequantize() when args is None (forward.py:106-138)."""
+    if scale.ndim in (0, 1):
+        return QuantizationArgs(strategy=QuantizationStrategy.TENSOR)
+    if scale.ndim == 2:
+        if scale.shape[1] == 1:
+            return QuantizationArgs(strategy=QuantizationStrategy.CHANNEL)
+        if scale.shape[0] == 1 or scale.shape[0] == x_q.shape[0]:
+            return QuantizationArgs(strategy=QuantizationStrategy.GROUP, group_size=int(x_q.shape[1] / scale.shape[1]))
+        rows, cols = x_q.shape[-2], x_q.shape[-1]
+        return QuantizationArgs(strategy=QuantizationStrategy.BLOCK, block_structure=[rows // scale.shape[0], cols // scale.shape[1]])
+    raise ValueError(f"Could not infer a quantization strategy from scale with {scale.ndim} dimmensions. Expected 0 or 2 dimmensions.")
+
+
+def _common(x, scale, args, g_idx, global_scale):
+    if x.dtype not in _FLOATS + (torch.int8, torch.float8_e4m3fn):
+        raise TypeError(f"unsupported input dtype {x.dtype}")
+    col_group, row_group, srs = _geometry(x, scale, args)
+    grouped = args.strategy in (QuantizationStrategy.GROUP, QuantizationStrategy.TENSOR_GROUP)
+    use_gidx = None
+    if grouped and g_idx is not None and not bool((g_idx == -1).any()):  # forward.py:286 is_column_order
+        use_gidx = g_idx
+    kw = dict(qtype=qtype_code(args), bits=args.num_bits, col_group=col_group, row_group=row_group, scale_row_stride=srs,
+              g_idx=use_gidx, global_scale=global_scale)
+    sdt = torch.float32 if global_scale is not None else scale.dtype
+    return kw, grouped, sdt
+
+
+@torch.no_grad()
+def quantize(x: torch.Tensor, scale: torch.Tensor, zero_point: Optional[torch.Tensor], args: QuantizationArgs,
+             dtype: Optional[torch.dtype] = None, g_idx: Optional[torch.Tensor] = None,
+             global_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """forward.py:45-81.  Result dtype: `dtype` if given, else the input dtype for GROUP / TENSOR_GROUP
+    and the promoted (input, scale) dtype for the other strategies, as in the reference."""
+    kw, grouped, sdt = _common(x, scale, args, g_idx, global_scale)
+    out_dtype = dtype if dtype is not None else (x.dtype if grouped else _promote(x.dtype, sdt))
+    return ops.quantize(x, scale, zero_point, out_dtype=out_dtype, **kw)
+
+
+@torch.no_grad()
+def dequantize(x_q: torch.Tensor, scale: torch.Tensor, zero_point: Optional[torch.Tensor] = None,
+               args: Optional[QuantizationArgs] = None, dtype: Optional[torch.dtype] = None,
+               g_idx: Optional[torch.Tensor] = None, global_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """forward.py:85-153.  `dtype` defaults to the scale dtype and, as in the reference, only the
+    GROUP / TENSOR_GROUP path applies it; the other strategies return the scale's compute dtype."""
+    if args is None:
+        args = infer_dequant_args(x_q, scale)
+    if dtype is None:
+        dtype = scale.dtype
+    kw, grouped, sdt = _common(x_q, scale, args, g_idx, global_scale)
+    out_dtype = dtype if grouped else sdt
+    if out_dtype not in _FLOATS:
+        raise TypeError(f"dequantize cannot produce {out_dtype}")
+    return ops.dequantize(x_q, scale, zero_point, out_dtype=out_dtype, **kw)
+
+
+@torch.no_grad()
+def fake_quantize(x: torch.Tensor, scale: torch.Tensor, zero_point: Optional[torch.Tensor], args: QuantizationArgs,
+                  g_idx: Optional[torch.Tensor] = None, global_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """forward.py:157-189: quantize then dequantize in one kernel."""
+    kw, grouped, sdt = _common(x, scale, args, g_idx, global_scale)
+    out_dtype = x.dtype if grouped else sdt
+    return ops.fake_quantize(x, scale, zero_point, out_dtype=out_dtype, **kw)

@@ -1,0 +1,57 @@
+"""`hadamard` transform factory (transform/factory/hadamard.py of the reference)."""
+import math
+from typing import Optional
+
+import torch
+from torch.nn import Module, Parameter
+
+from ... import ops
+from ..transform_args import TransformArgs, TransformLocation
+from ..transform_scheme import TransformScheme
+from ..utils.hadamard import deterministic_hadamard_matrix
+from ..utils.matrix import get_transform_size
+from .base import TransformBase, TransformFactory
+
+__all__ = ["HadamardFactory", "HadamardTransform"]
+
+
+@TransformFactory.register("hadamard")
+class HadamardFactory(TransformFactory):
+    def __init__(self, name: str, scheme: TransformScheme, seed: Optional[int] = None):
+        super().__init__(name, scheme, seed)
+        self._weights = {}
+
+    def create_transform(self, module: Module, args: TransformArgs) -> "HadamardTransform":
+        size = get_transform_size(module, args.location, self.scheme.head_dim)
+        # offline transforms are built in float64, like the reference (hadamard.py:57)
+        precision = self.scheme.precision if args.is_online() else torch.float64
+        key = (size, precision)
+        if key not in self._weights:  # one matrix per size, shared by every module (hadamard.py:64)
+            self._weights[key] = self._create_weight(size, torch.device("cpu"), torch.device("cpu"), precision)
+        if self.scheme.randomize:
+            raise NotImplementedError("randomize=True (row/column permutation of the Hadamard matrix) is not built")
+        return HadamardTransform(self._weights[key], None, self.scheme, args, type(module))
+
+    def _create_weight(self, size: int, device, construct_device, precision: torch.dtype) -> Parameter:
+        return Parameter(deterministic_hadamard_matrix(size, precision, construct_device), requires_grad=False)
+
+
+class HadamardTransform(TransformBase):
+    """Holds the +-1 matrix for inspection / serialisation; forward() runs the CUDA butterfly, which
+    needs only the matrix's first column (the random signs)."""
+
+    def __init__(self, weight: Parameter, perm, scheme: TransformScheme, args: TransformArgs, module_type: type):
+        super().__init__()
+        self.weight, self.perm, self.scheme, self.args, self.module_type = weight, perm, scheme, args, module_type
+        self._signs = weight.data[:, 0].to(torch.int8)  # weight = diag(signs) @ H, column 0 of H is all ones
+        self._scale = math.sqrt(weight.size(0))
+
+    def forward(self, value: torch.Tensor) -> torch.Tensor:
+        """hadamard.py:104-121: (apply_transform_weight(W_h, value.to(W_h.dtype)) / sqrt(n)).to(value.dtype)."""
+        if self.module_type != torch.nn.Linear:
+            raise NotImplementedError(f"Applying transforms to {self.module_type} {self.args.location} is not supported")
+        location = TransformLocation(self.args.location)
+        side = 0 if location == TransformLocation.WEIGHT_INPUT else 1
+        acc = torch.float64 if self.weight.dtype == torch.float64 else torch.float32
+        return ops.hadamard(value, self.weight.size(0), signs=self._signs.to(value.device), inverse=bool(self.args.inverse),
+                            side=side, precision=acc)

@@ -202,10 +202,11 @@ int ctb_bitmask_decompress_static(const void *values, const uint8_t *bitmask, in
  *   side 1 (weight_output): out = Wh^T @ W per n-row block,
  * Wh = diag(signs) @ H_n (Sylvester; signs int8 +-1 [n] or NULL = all +1; transform/utils/
  * hadamard.py:33-89), transposed when `inverse`; result / sqrt(n) cast to the dtype of W.
- * precision: CTB_F64 accumulates like the reference's offline path; CTB_F32 is the fast mode. */
+ * precision: CTB_F64 accumulates like the reference's offline path; CTB_F32 is the fast mode.
+ * normalize = 0 leaves out the division by sqrt(n) (apply_transform_weight on its own, matrix.py:65). */
 int ctb_hadamard(const void *x, int32_t dtype, int64_t rows, int64_t cols, int32_t n,
-                 const int8_t *signs, int32_t inverse, int32_t side, int32_t precision, void *out,
-                 void *stream);
+                 const int8_t *signs, int32_t inverse, int32_t side, int32_t precision,
+                 int32_t normalize, void *out, void *stream);
 
 /* ---- fused calibrate + quantize + pack (single pass over the dense tensor) -------------------
  * Symmetric min-max calibration (helpers.py:67-146 with the group's own amin/amax) followed by

@@ -1,0 +1,249 @@
+"""The reference-facing Python API (same names and signatures as compressed-tensors) on the GPU,
+against the reference's own outputs in tests/golden/."""
+import pytest
+import torch
+
+from tests.helpers import assert_bit_equal
+
+pytestmark = pytest.mark.gpu
+
+
+def dev(t):
+    return None if t is None else t.cuda()
+
+
+def int_args(d, name):
+    from compressed_tensors_b200.quantization import QuantizationArgs
+
+    bits, sym, group = int(d["bits"]), bool(d["sym"]), int(d["group"])
+    if "tensor" in name:
+        return QuantizationArgs(num_bits=bits, symmetric=sym, strategy="tensor")
+    if "channel" in name:
+        return QuantizationArgs(num_bits=bits, symmetric=sym, strategy="channel")
+    return QuantizationArgs(num_bits=bits, symmetric=sym, strategy="group", group_size=group)
+
+
+@pytest.mark.parametrize("name", ["w4_sym_g128_bf16", "w4_asym_g128_bf16", "w8_sym_channel_bf16", "w8_asym_channel_bf16",
+                                  "w4_sym_tensor_bf16", "w4_sym_g128_fp32", "w4_asym_g64_fp16", "w4_sym_channel_fp32"])
+def test_quantize_dequantize_pack_compressor(golden, name):
+    from compressed_tensors_b200.compressors import PackedQuantizationCompressor, pack_to_int32, unpack_from_int32
+    from compressed_tensors_b200.quantization import calculate_qparams, dequantize, fake_quantize, quantize
+
+    d = golden("int_quant")[name]
+    args = int_args(d, name)
+    x, scale, zp = dev(d["x"]), dev(d["scale"]), dev(d["zp"])
+    s, z = calculate_qparams(dev(d["min"]), dev(d["max"]), args)
+    assert_bit_equal(s.cpu(), d["scale"]), assert_bit_equal(z.cpu(), d["zp"])
+    q8 = quantize(x, scale, zp, args, dtype=torch.int8)
+    assert_bit_equal(q8.cpu(), d["q_int8"])
+    assert_bit_equal(quantize(x, scale, zp, args).cpu(), d["q_float"], "dtype=None result dtype and values")
+    assert_bit_equal(dequantize(q8, scale, zp, args).cpu(), d["dequant"])
+    if "tensor" not in name:
+        assert_bit_equal(dequantize(q8, scale, zp).cpu(), d["dequant_noargs"], "strategy inferred from the scale shape")
+    assert_bit_equal(fake_quantize(x, scale, zp, args).cpu(), d["fake"])
+    assert_bit_equal(pack_to_int32(q8, args.num_bits).cpu(), d["packed"])
+    assert_bit_equal(unpack_from_int32(dev(d["packed"]), args.num_bits, x.shape).cpu(), d["unpacked"])
+    comp = PackedQuantizationCompressor()
+    cd = comp.compress_weight(x, scale, args, zero_point=zp)
+    assert_bit_equal(cd["weight_packed"].cpu(), d["c_weight_packed"])
+    assert cd["weight_shape"].dtype == torch.int64 and cd["weight_shape"].tolist() == list(x.shape)
+    if "c_weight_zero_point" in d:
+        assert_bit_equal(cd["weight_zero_point"].cpu(), d["c_weight_zero_point"])
+    cd["weight_scale"] = scale
+    assert_bit_equal(comp.decompress_weight(cd, args).cpu(), d["decompressed"])
+    with pytest.raises(ValueError, match="global_scale is not supported"):
+        comp.compress_weight(x, scale, args, zero_point=zp, global_scale=torch.ones(1))
+
+
+def test_actorder(golden):
+    from compressed_tensors_b200.quantization import QuantizationArgs, dequantize, fake_quantize, quantize
+
+    d = golden("int_quant")["w4_sym_g64_actorder"]
+    args = QuantizationArgs(num_bits=4, symmetric=True, strategy="group", group_size=64, actorder="group")
+    x, scale, zp, g_idx = dev(d["x"]), dev(d["scale"]), dev(d["zp"]), dev(d["g_idx"])
+    q8 = quantize(x, scale, zp, args, dtype=torch.int8, g_idx=g_idx)
+    assert_bit_equal(q8.cpu(), d["q_int8"])
+    assert_bit_equal(dequantize(q8, scale, zp, args, g_idx=g_idx).cpu(), d["dequant"])
+    assert_bit_equal(fake_quantize(x, scale, zp, args, g_idx=g_idx).cpu(), d["fake"])
+    # g_idx of all -1 means "column order" (forward.py:286)
+    q_plain = quantize(x, scale, zp, args, dtype=torch.int8, g_idx=torch.full_like(g_idx, -1))
+    assert_bit_equal(q_plain.cpu(), quantize(x, scale, zp, args, dtype=torch.int8).cpu())
+
+
+def test_fp8_api(golden):
+    from compressed_tensors_b200.compressors import BaseCompressor
+    from compressed_tensors_b200.quantization import (QuantizationArgs, compute_dynamic_scales_and_zp, dequantize,
+                                                      fake_quantize, quantize)
+
+    g = golden("fp8_quant")
+    args_c = QuantizationArgs(num_bits=8, type="float", symmetric=True, strategy="channel")
+    args_tok = QuantizationArgs(num_bits=8, type="float", symmetric=True, strategy="token", dynamic=True)
+    args_b = QuantizationArgs(num_bits=8, type="float", symmetric=True, strategy="block", block_structure=[16, 64])
+    for tag in ("channel_bf16", "channel_bf16_f32scale", "channel_fp16", "channel_fp32"):
+        d = g[tag]
+        x, scale, zp = dev(d["x"]), dev(d["scale"]), dev(d["zp"])
+        q = quantize(x, scale, zp, args_c, dtype=torch.float8_e4m3fn)
+        assert_bit_equal(q.cpu(), d["q"], tag)
+        assert_bit_equal(quantize(x, scale, zp, args_c).cpu(), d["q_float"], tag)
+        assert_bit_equal(dequantize(q, scale, zp, args_c).cpu(), d["dequant"], tag)
+        assert_bit_equal(dequantize(q, scale).cpu(), d["dequant_noargs"], tag)
+        assert_bit_equal(fake_quantize(x, scale, zp, args_c).cpu(), d["fake"], tag)
+        comp = BaseCompressor.load_from_registry("float-quantized")
+        cd = comp.compress_weight(x, scale, args_c, zero_point=zp)
+        assert_bit_equal(cd["weight"].cpu(), d["c_weight"], tag)
+        cd["weight_scale"] = scale
+        assert_bit_equal(comp.decompress_weight(cd, args_c).cpu(), d["decompressed"], tag)
+    d = g["token_bf16"]
+    x = dev(d["x"])
+    scale, zp = compute_dynamic_scales_and_zp(x, args_tok, module=None)
+    assert_bit_equal(scale.cpu(), d["scale"]), assert_bit_equal(zp.cpu(), d["zp"])
+    assert_bit_equal(quantize(x, scale, zp, args_tok, dtype=torch.float8_e4m3fn).cpu(), d["q"])
+    assert_bit_equal(fake_quantize(x, scale, zp, args_tok).cpu(), d["fake"])
+    d2 = g["token_2d"]
+    s2, z2 = compute_dynamic_scales_and_zp(dev(d2["x"]), args_tok, module=None)
+    assert_bit_equal(s2.cpu(), d2["scale"], "2-D TOKEN input collapses to one scale")
+    d = g["block_bf16"]
+    x, scale, zp = dev(d["x"]), dev(d["scale"]), dev(d["zp"])
+    q = quantize(x, scale, zp, args_b, dtype=torch.float8_e4m3fn)
+    assert_bit_equal(q.cpu(), d["q"])
+    assert_bit_equal(dequantize(q, scale, zp, args_b).cpu(), d["dequant"])
+    with pytest.raises(ValueError, match="not divisible by block_height"):
+        quantize(x[:30], scale, zp, args_b)
+
+
+def test_nvfp4_api(golden):
+    from compressed_tensors_b200.compressors import NVFP4PackedCompressor, pack_fp4_to_uint8, unpack_fp4_from_uint8
+    from compressed_tensors_b200.quantization import (QuantizationArgs, calculate_qparams, compute_dynamic_scales_and_zp,
+                                                      dequantize, fake_quantize, generate_gparam, quantize)
+
+    args = QuantizationArgs(num_bits=4, type="float", symmetric=True, strategy="tensor_group", group_size=16)
+    for tag in ("a", "b"):
+        d = golden("nvfp4")[tag]
+        x, scale, zp, gs = dev(d["x"]), dev(d["scale"]), dev(d["zp"]), dev(d["global_scale"])
+        assert_bit_equal(generate_gparam(dev(d["min"]), dev(d["max"])).cpu(), d["global_scale"])
+        s, z = calculate_qparams(dev(d["gmin"]), dev(d["gmax"]), args, global_scale=gs)
+        assert_bit_equal(s.cpu(), d["scale"]), assert_bit_equal(z.cpu(), d["zp"])
+        s, _ = compute_dynamic_scales_and_zp(x, args, module=None, global_scale=gs)
+        assert_bit_equal(s.cpu(), d["scale"], "dynamic local scales")
+        q = quantize(x, scale, zp, args, global_scale=gs)
+        assert_bit_equal(q.cpu(), d["q"])
+        packed = pack_fp4_to_uint8(q)
+        assert_bit_equal(packed.cpu(), d["packed"])
+        assert_bit_equal(unpack_fp4_from_uint8(packed, *x.shape).cpu(), d["unpacked"])
+        assert_bit_equal(dequantize(dev(d["unpacked"]), scale, global_scale=gs, dtype=torch.bfloat16).cpu(), d["dequant"])
+        assert_bit_equal(fake_quantize(x, scale, zp, args, global_scale=gs).cpu(), d["fake"])
+        comp = NVFP4PackedCompressor()
+        cd = comp.compress_weight(x, scale, gs, args, zero_point=zp)
+        assert_bit_equal(cd["weight_packed"].cpu(), d["c_weight_packed"])
+        out = comp.decompress_weight({"weight_packed": cd["weight_packed"], "weight_scale": scale, "weight_global_scale": gs}, args)
+        assert_bit_equal(out.cpu(), d["decompressed"])
+    with pytest.raises(ValueError, match="even number of columns"):
+        pack_fp4_to_uint8(torch.zeros(2, 3, device="cuda"))
+
+
+def test_sparse_api(golden):
+    from compressed_tensors_b200.compressors import (BitmaskCompressor, BitmaskTensor, Sparse24BitMaskCompressor, Sparse24BitMaskTensor,
+                                                     bitmask_compress, bitmask_decompress, get_24_bytemasks,
+                                                     sparse24_bitmask_compress, sparse24_bitmask_decompress)
+    from compressed_tensors_b200.utils import pack_bitmasks, unpack_bitmasks
+
+    g = golden("sparse")
+    for tag in ("bf16", "fp16", "fp32", "e4m3"):
+        for cols in (64, 13):
+            d = g[f"bitmask_{tag}_{cols}"]
+            values, bitmask, row_offsets = bitmask_compress(dev(d["x"]))
+            assert_bit_equal(values.cpu(), d["values"]), assert_bit_equal(bitmask.cpu(), d["bitmask"])
+            assert_bit_equal(row_offsets.cpu(), d["row_offsets"])
+            assert_bit_equal(bitmask_decompress(values, bitmask, d["x"].shape).cpu(), d["dense"])
+            assert_bit_equal(pack_bitmasks(unpack_bitmasks(bitmask, list(d["x"].shape))).cpu(), d["bitmask"])
+    # compressor round trip from a CPU tensor, results on the CPU like the reference
+    d = g["bitmask_bf16_64"]
+    comp = BitmaskCompressor()
+    sd = comp.compress({"layer.weight": d["x"]})
+    assert set(sd) == {"layer.shape", "layer.compressed", "layer.bitmask", "layer.row_offsets"}
+    assert all(not v.is_cuda for v in sd.values())
+    assert_bit_equal(sd["layer.compressed"], d["values"])
+    (name, dense), = list(comp.decompress(sd))
+    assert name == "layer.weight"
+    assert_bit_equal(dense.cpu(), d["dense"])
+    assert BitmaskTensor.from_dense(d["x"]).curr_memory_size_bytes() == sum(v.numel() * v.element_size() for k, v in sd.items() if "shape" not in k)
+    for tag in ("bf16", "fp32", "int8", "e4m3"):
+        d = g[f"s24_{tag}"]
+        assert_bit_equal(get_24_bytemasks(dev(d["x"])).cpu(), d["mask"])
+        values, bitmask = sparse24_bitmask_compress(dev(d["x"]))
+        assert_bit_equal(values.cpu(), d["values"]), assert_bit_equal(bitmask.cpu(), d["bitmask"])
+        assert_bit_equal(sparse24_bitmask_decompress(values, bitmask, d["x"].shape).cpu(), d["dense"])
+    d = g["s24_bf16"]
+    comp = Sparse24BitMaskCompressor()
+    sd = comp.compress({"m.weight": d["x"]})
+    assert set(sd) == {"m.shape", "m.compressed", "m.bitmask"} and tuple(sd["m.shape"].shape) == (2, 1)
+    (name, dense), = list(comp.decompress(sd))
+    assert name == "m.weight"
+    assert_bit_equal(dense.cpu(), d["dense"])
+    with pytest.raises(ValueError, match="multiple of 4"):
+        get_24_bytemasks(torch.zeros(3, 3, device="cuda"))
+    meta_v, meta_b = sparse24_bitmask_compress(torch.empty(8, 16, device="meta"))
+    assert meta_v.shape == (8, 8) and meta_b.shape == (8, 2)
+    assert Sparse24BitMaskTensor.from_dense(d["x"]).curr_memory_size_bytes() > 0
+
+
+def test_transform_factories(golden):
+    from compressed_tensors_b200.transform import (HadamardFactory, RandomHadamardFactory, TransformArgs, TransformConfig, TransformScheme,
+                                                   apply_transform_config)
+
+    g = golden("hadamard")
+    for tag, fac_cls, seed in (("hadamard", HadamardFactory, None), ("random", RandomHadamardFactory, 7)):
+        for location in ("weight_input", "weight_output"):
+            for inverse in (False, True):
+                name = f"{tag}_{location}_{'inv' if inverse else 'fwd'}_bfloat16"
+                d = g[name]
+                o, i = d["w"].shape
+                lin = torch.nn.Linear(i, o, bias=False, dtype=torch.bfloat16, device="cuda")
+                lin.weight.data = dev(d["w"])
+                scheme = TransformScheme(type=tag if tag == "hadamard" else "random-hadamard", head_dim=128,
+                                         apply=[TransformArgs(targets=["Linear"], location=location, inverse=inverse)])
+                fac = fac_cls("t", scheme, seed=seed)
+                tr = fac.create_transform(lin, scheme.apply[0])
+                assert torch.equal(tr.weight.data.to(torch.int8), d["matrix"]), name
+                assert_bit_equal(tr(lin.weight.data).cpu(), d["out"], name)
+    # config-level entry point, seed 7, fused into the weight
+    d = g["random_weight_input_fwd_bfloat16"]
+    model = torch.nn.Sequential(torch.nn.Linear(256, 16, bias=False, dtype=torch.bfloat16, device="cuda"))
+    model[0].weight.data = dev(d["w"])
+    cfg = TransformConfig(config_groups={"r": TransformScheme(type="random-hadamard", head_dim=128,
+                                                              apply=[TransformArgs(targets=["Linear"], location="weight_input")])})
+    apply_transform_config(model, cfg, seed=7)
+    assert_bit_equal(model[0].weight.data.cpu(), d["out"])
+
+
+def test_model_compressor_round_trip():
+    """compress == compress_model, decompress_model restores fake-quantized weights, on a toy model."""
+    from compressed_tensors_b200.compressors import ModelCompressor
+    from compressed_tensors_b200.quantization import (QuantizationConfig, apply_quantization_config, calibrate_weight_qparams,
+                                                      fake_quantize)
+
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Linear(256, 128, bias=False), torch.nn.ReLU(), torch.nn.Linear(128, 32, bias=True))
+    model = model.to(torch.bfloat16).cuda()
+    cfg = QuantizationConfig(config_groups={"W4A16": ["Linear"]}, format="pack-quantized")
+    apply_quantization_config(model, cfg)
+    expect = {}
+    for name, m in model.named_modules():
+        if isinstance(m, torch.nn.Linear):
+            calibrate_weight_qparams(m)
+            expect[name] = fake_quantize(m.weight.data, m.weight_scale.data, m.weight_zero_point.data, m.quantization_scheme.weights).cpu()
+    mc = ModelCompressor(quantization_config=cfg)
+    sd = mc.compress(model)
+    assert "0.weight_packed" in sd and "0.weight_shape" in sd and "0.weight_scale" in sd and "0.weight" not in sd
+    assert "0.weight_zero_point" not in sd, "symmetric zero points are dropped"
+    assert "2.bias" in sd and all(not v.is_cuda for v in sd.values())
+    assert sd["0.weight_packed"].dtype == torch.int32 and tuple(sd["0.weight_packed"].shape) == (128, 32)
+    mc.compress_model(model)
+    assert not hasattr(model[0], "weight")
+    for k in ("0.weight_packed", "0.weight_scale", "2.weight_packed", "2.bias"):
+        assert_bit_equal(dict(model.state_dict())[k].cpu(), sd[k], k)
+    mc.decompress_model(model)
+    for name, want in expect.items():
+        assert_bit_equal(dict(model.named_modules())[name].weight.data.cpu(), want, name)
+    y = model(torch.randn(2, 256, dtype=torch.bfloat16, device="cuda"))
+    assert y.shape == (2, 32)
