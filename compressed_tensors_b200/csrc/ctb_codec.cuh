@@ -245,6 +245,51 @@ __device__ __forceinline__ void round8(float (&v)[8]) {
     }
 }
 
+// ---- packed bf16x2 fast paths for int4 <-> bf16 with a bf16 scale ---------------------------------
+
+__device__ __forceinline__ uint32_t bf162_as_u32(__nv_bfloat162 v) { return *reinterpret_cast<uint32_t *>(&v); }
+__device__ __forceinline__ __nv_bfloat162 u32_as_bf162(uint32_t v) { return *reinterpret_cast<__nv_bfloat162 *>(&v); }
+
+// int4 code byte (two nibbles) from a packed pair of bf16 values already divided by the scale
+__device__ __forceinline__ uint32_t int4_pair_code(__nv_bfloat162 q) {
+    const __nv_bfloat162 lo = u32_as_bf162(0xC100C100u);     // -8, -8
+    const __nv_bfloat162 hi = u32_as_bf162(0x40E040E0u);     //  7,  7
+    const __nv_bfloat162 magic = u32_as_bf162(0x43484348u);  // 200, 200
+    q = __hmin2(__hmax2(q, lo), hi);
+    uint32_t m = bf162_as_u32(__hadd2(q, magic));
+    return (m & 0xFu) | ((m >> 12) & 0xF0u);  // bits 8.. are don't-care for the caller's byte permute
+}
+
+
+// 8 bf16 inputs (4 packed words) -> one pack_to_int32 word of int4 codes, compute dtype bf16:
+//   q = bf16_rn(x * rcp(s)) [+ zero point, rounded to bf16]; clamp to [-8, 7]; round half to even.
+// `zp2` is the zero point replicated in both halves (bf16x2), ignored unless has_zp.
+__device__ __forceinline__ uint32_t quant_int4_word_bf16(const uint32_t (&w)[4], float r, bool has_zp, __nv_bfloat162 zp2) {
+    uint32_t b[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float f0 = __uint_as_float(w[k] << 16), f1 = __uint_as_float(w[k] & 0xFFFF0000u);
+        __nv_bfloat162 q = __floats2bfloat162_rn(f0 * r, f1 * r);
+        if (has_zp) q = __hadd2(q, zp2);
+        b[k] = int4_pair_code(q);
+    }
+    return __byte_perm(__byte_perm(b[0], b[1], 0x0040), __byte_perm(b[2], b[3], 0x0040), 0x5410);
+}
+
+// one pack_to_int32 word of int4 codes -> 8 bf16 outputs (4 packed words), compute dtype bf16:
+//   (code - zero_point) * scale, both steps exact-or-single-rounded in bf16x2 arithmetic.
+// 0x4300 | nibble is the bf16 number 128 + nibble, so subtracting 136 + zp gives code - zp exactly.
+__device__ __forceinline__ uint4 dequant_int4_word_bf16(uint32_t word, __nv_bfloat162 s2, __nv_bfloat162 bias2) {
+    uint32_t t[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) t[k] = ((word >> (4 * k)) & 0x000F000Fu) | 0x43004300u;  // low half: nibble k, high half: nibble k + 4
+    uint32_t p[4] = {__byte_perm(t[0], t[1], 0x5410), __byte_perm(t[2], t[3], 0x5410),   // (n0, n1), (n2, n3)
+                     __byte_perm(t[0], t[1], 0x7632), __byte_perm(t[2], t[3], 0x7632)};  // (n4, n5), (n6, n7)
+#pragma unroll
+    for (int k = 0; k < 4; ++k) p[k] = bf162_as_u32(__hmul2(__hsub2(u32_as_bf162(p[k]), bias2), s2));
+    return make_uint4(p[0], p[1], p[2], p[3]);
+}
+
 // qparam for a chunk, as fp32
 struct QP {
     float s;   // effective scale (scale or scale / global_scale)

@@ -59,6 +59,19 @@ __global__ void __launch_bounds__(kThreads) qdq_vec8_kernel(const QArgs a) {
             int64_t c = base + (int64_t)u * kThreads;
             if (c >= a.chunks) continue;
             QP q = load_qp(a.scale, a.sdt, a.zp, a.zdt, a.gs, qp_index_chunk(a, c));
+            // int4 <-> bf16 with a bf16 scale: packed bf16x2 arithmetic, a few instructions per element
+            if constexpr (MODE == 1 && FIN == F_PACK4 && FOUT == F_BF16 && TS == CTB_BF16) {
+                uint4 o = dequant_int4_word_bf16(raw[u].a.x, __float2bfloat162_rn(q.s), __float2bfloat162_rn(136.0f + q.zp));
+                st_stream((char *)a.out + c * 16, o);
+                continue;
+            }
+            if constexpr (MODE == 0 && FIN == F_BF16 && FOUT == F_PACK4 && T == CTB_BF16 && QK == QK_INT) {
+                if (!q.slow) {
+                    const uint32_t w[4] = {raw[u].a.x, raw[u].a.y, raw[u].a.z, raw[u].a.w};
+                    st_stream4((char *)a.out + c * 4, quant_int4_word_bf16(w, q.r, has_zp, __float2bfloat162_rn(q.zp)));
+                    continue;
+                }
+            }
             float v[8];
             decode8<FIN>(raw[u], v);
             if constexpr (MODE == 0) {

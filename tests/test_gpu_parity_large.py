@@ -1,0 +1,197 @@
+"""Parity of the CUDA path against the CPU oracle on seeded inputs at sizes the oracle finishes in
+seconds, plus size-independent properties at the benchmark's full tensor sizes."""
+import pytest
+import torch
+
+from tests.helpers import assert_bit_equal
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from compressed_tensors_b200 import ops as o
+    return o
+
+
+@pytest.fixture(scope="module")
+def orc():
+    from oracle import ref
+    ref.build()
+    return ref
+
+
+def weights(rows, cols, seed=0, std=0.02):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(rows, cols, generator=g) * std).to(torch.bfloat16)
+
+
+def signs128(seed=0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randint(0, 2, (128,), generator=g) * 2 - 1).to(torch.int8)
+
+
+def oracle_w4(orc, w, group=128):
+    mn, mx = orc.minmax(w, 1, group)
+    scale, zp = orc.calculate_qparams(mn, mx, qtype=orc.QINT, bits=4, symmetric=True)
+    kw = dict(qtype=orc.QINT, bits=4, col_group=group, row_group=1, scale_row_stride=w.shape[1] // group)
+    words = orc.pack_int32(orc.quantize(w, scale, zp, out_dtype=torch.int8, **kw), 4)
+    deq = orc.dequantize(orc.unpack_int32(words, 4, w.shape), scale, None, out_dtype=torch.bfloat16, **kw)
+    return scale, words, deq
+
+
+def test_w4a16_group128_matches_oracle(ops, orc):
+    """BASELINE config 1 math on a 1024x4096 slice: scales, packed words and dequantized values bit-exact."""
+    w = weights(1024, 4096)
+    scale, words, deq = oracle_w4(orc, w)
+    got_words, got_scale = ops.absmax_quantize(w.cuda(), qtype=ops.QINT, bits=4, col_group=128, codec="pack32")
+    assert_bit_equal(got_scale.cpu(), scale, "scales")
+    assert_bit_equal(got_words.cpu(), words, "packed words")
+    given = ops.quantize(w.cuda(), scale.cuda(), None, qtype=ops.QINT, bits=4, col_group=128, scale_row_stride=32, codec="pack32")
+    assert_bit_equal(given.cpu(), words, "packed words from given scales")
+    got = ops.dequantize(got_words, got_scale, None, qtype=ops.QINT, bits=4, col_group=128, scale_row_stride=32,
+                         out_dtype=torch.bfloat16, codec="pack32", cols=4096)
+    assert_bit_equal(got.cpu(), deq, "dequantized")
+
+
+def test_w4a16_asymmetric_matches_oracle(ops, orc):
+    w = weights(256, 1024, seed=5) + 0.01
+    w = w.to(torch.bfloat16)
+    mn, mx = orc.minmax(w, 1, 128)
+    scale, zp = orc.calculate_qparams(mn, mx, qtype=orc.QINT, bits=4, symmetric=False)
+    kw = dict(qtype=orc.QINT, bits=4, col_group=128, row_group=1, scale_row_stride=8)
+    words = orc.pack_int32(orc.quantize(w, scale, zp, out_dtype=torch.int8, **kw), 4)
+    deq = orc.dequantize(orc.unpack_int32(words, 4, w.shape), scale, zp, out_dtype=torch.bfloat16, **kw)
+    gw = ops.quantize(w.cuda(), scale.cuda(), zp.cuda(), codec="pack32", **{k: v for k, v in kw.items()})
+    assert_bit_equal(gw.cpu(), words, "asymmetric packed words")
+    gd = ops.dequantize(gw, scale.cuda(), zp.cuda(), out_dtype=torch.bfloat16, codec="pack32", cols=1024, **kw)
+    assert_bit_equal(gd.cpu(), deq, "asymmetric dequantized")
+
+
+def test_rotate_quantize_exact_mode_matches_oracle(ops, orc):
+    """float64-accumulated rotation fused with int4 g128: bit-exact against rotate -> calibrate -> quantize -> pack."""
+    w, sg = weights(512, 4096, seed=1), signs128(1)
+    rot = orc.hadamard(w, 128, signs=sg)
+    scale, words, _ = oracle_w4(orc, rot)
+    assert_bit_equal(ops.hadamard(w.cuda(), 128, signs=sg.cuda(), precision=torch.float64).cpu(), rot, "rotated weights")
+    gw, gs = ops.absmax_quantize(w.cuda(), qtype=ops.QINT, bits=4, col_group=128, codec="pack32", hadamard_n=128,
+                                 signs=sg.cuda(), precision=torch.float64)
+    assert_bit_equal(gs.cpu(), scale, "scales")
+    assert_bit_equal(gw.cpu(), words, "packed words")
+
+
+def test_rotate_quantize_fast_mode_staged(ops, orc):
+    """float32-accumulated rotation (the fast mode).  Stage 1: rotated weights within the stated tolerance of
+    the float64 result (norm-wise rel-err <= 1e-3, all but a few parts per million identical, none off by more
+    than 4 bf16 steps).  Stage 2: the fused kernel equals the ORACLE's calibrate+quantize+pack applied to that
+    rotated tensor, bit for bit."""
+    from tests.helpers import bf16_ulp_distance
+
+    w, sg = weights(512, 4096, seed=2), signs128(2)
+    exact = orc.hadamard(w, 128, signs=sg)
+    fast = ops.hadamard(w.cuda(), 128, signs=sg.cuda(), precision=torch.float32).cpu()
+    err = (fast.double() - exact.double()).norm() / exact.double().norm()
+    assert err <= 1e-3, float(err)
+    differ = (fast.view(torch.int16) != exact.view(torch.int16)).sum().item()
+    assert differ <= 50e-6 * exact.numel(), differ
+    assert bf16_ulp_distance(fast, exact) <= 4
+    scale, words, _ = oracle_w4(orc, fast)
+    gw, gs = ops.absmax_quantize(w.cuda(), qtype=ops.QINT, bits=4, col_group=128, codec="pack32", hadamard_n=128,
+                                 signs=sg.cuda(), precision=torch.float32)
+    assert_bit_equal(gs.cpu(), scale, "scales from our rotated tensor")
+    assert_bit_equal(gw.cpu(), words, "packed words from our rotated tensor")
+
+
+def test_fp8_channel_and_token_match_oracle(ops, orc):
+    w = weights(512, 4096, seed=3)
+    mn, mx = orc.minmax(w, 1, 4096)
+    scale, zp = orc.calculate_qparams(mn, mx, qtype=orc.QFLOAT, bits=8, symmetric=True)
+    kw = dict(qtype=orc.QFLOAT, bits=8, col_group=4096, row_group=1, scale_row_stride=1)
+    q = orc.quantize(w, scale, zp, out_dtype=torch.float8_e4m3fn, **kw)
+    deq = orc.dequantize(q, scale, zp, out_dtype=torch.bfloat16, **kw)
+    gq, gs = ops.absmax_quantize(w.cuda(), qtype=ops.QFLOAT, bits=8, col_group=4096, codec="dtype", out_dtype=torch.float8_e4m3fn)
+    assert_bit_equal(gs.cpu(), scale.reshape(gs.shape), "per-channel scales")
+    assert_bit_equal(gq.cpu(), q, "e4m3 codes")
+    assert_bit_equal(ops.dequantize(gq, gs, None, out_dtype=torch.bfloat16, **kw).cpu().view(torch.int16),
+                     orc.dequantize(q, scale, None, out_dtype=torch.bfloat16, **kw).view(torch.int16), "dequantized")
+    # activations with outlier channels, fp32 scales
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(1, 256, 4096, generator=g)
+    x[..., torch.randperm(4096, generator=g)[:41]] *= 20
+    x = x.to(torch.bfloat16)
+    mn, mx = orc.minmax(x.float(), 1, 4096)
+    s32, z32 = orc.calculate_qparams(mn, mx, qtype=orc.QFLOAT, bits=8, symmetric=True)
+    q = orc.quantize(x, s32, z32, out_dtype=torch.float8_e4m3fn, **kw)
+    assert_bit_equal(ops.quantize(x.cuda(), s32.cuda(), z32.cuda(), out_dtype=torch.float8_e4m3fn, **kw).cpu(), q, "fp32-scale codes")
+    assert_bit_equal(ops.dequantize(q.cuda(), s32.cuda(), z32.cuda(), out_dtype=torch.float32, **kw).cpu(),
+                     orc.dequantize(q, s32, z32, out_dtype=torch.float32, **kw), "fp32-scale dequantized")
+    assert deq.dtype == torch.bfloat16
+
+
+def test_nvfp4_matches_oracle(ops, orc):
+    w = weights(512, 4096, seed=6)
+    mn, mx = orc.minmax(w, 512, 4096)
+    gs = orc.generate_gparam(mn, mx)
+    gmn, gmx = orc.minmax(w, 1, 16)
+    scale, _ = orc.calculate_qparams(gmn, gmx, qtype=orc.QFLOAT, bits=4, symmetric=True, global_scale=gs)
+    kw = dict(qtype=orc.QFLOAT, bits=4, col_group=16, row_group=1, scale_row_stride=256, global_scale=gs)
+    packed = orc.pack_fp4(orc.quantize(w, scale, None, out_dtype=torch.bfloat16, **kw))
+    deq = orc.dequantize(orc.unpack_fp4(packed, 512, 4096), scale, None, out_dtype=torch.bfloat16, **kw)
+    dmn, dmx = ops.minmax(w.cuda(), 512, 4096)
+    dgs = ops.generate_gparam(dmn, dmx)
+    assert_bit_equal(dgs.cpu(), gs, "global scale")
+    gp, gsc = ops.absmax_quantize(w.cuda(), qtype=ops.QFLOAT, bits=4, col_group=16, codec="fp4x2", global_scale=dgs)
+    assert_bit_equal(gsc.cpu(), scale, "e4m3 group scales")
+    assert_bit_equal(gp.cpu(), packed, "packed e2m1 bytes")
+    kwd = dict(kw, global_scale=dgs)
+    assert_bit_equal(ops.dequantize(gp, gsc, None, out_dtype=torch.bfloat16, codec="fp4x2", **kwd).cpu(), deq, "dequantized")
+
+
+def test_sparse_codecs_match_oracle(ops, orc):
+    g = torch.Generator().manual_seed(7)
+    w = weights(256, 2048, seed=7)
+    w[torch.rand(256, 2048, generator=g) < 0.5] = 0
+    values, bitmask, row_offsets = orc.bitmask_compress(w)
+    gv, gb, gr = ops.bitmask_compress(w.cuda())
+    assert_bit_equal(gv.cpu(), values), assert_bit_equal(gb.cpu(), bitmask), assert_bit_equal(gr.cpu(), row_offsets)
+    assert_bit_equal(ops.bitmask_decompress(gv, gb, w.shape).cpu(), orc.bitmask_decompress(values, bitmask, w.shape))
+    for t in (weights(256, 2048, seed=8), weights(256, 2048, seed=9).to(torch.float8_e4m3fn)):
+        mask = orc.sparse24_mask(t)
+        pruned = torch.where(mask, t.float(), torch.zeros(())).to(t.dtype)
+        v, b = orc.sparse24_compress(pruned)
+        dv, db = ops.sparse24_compress(pruned.cuda())
+        assert_bit_equal(dv.cpu(), v), assert_bit_equal(db.cpu(), b)
+        assert_bit_equal(ops.sparse24_mask(t.cuda()).cpu(), mask, "keep mask on unpruned values")
+        assert_bit_equal(ops.bitmask_decompress(dv, db, t.shape).cpu(), orc.bitmask_decompress(v, b, t.shape))
+    # ops run twice give identical bits (no race in the compaction)
+    gv2, gb2, gr2 = ops.bitmask_compress(w.cuda())
+    assert_bit_equal(gv2.cpu(), gv.cpu()), assert_bit_equal(gr2.cpu(), gr.cpu())
+
+
+@pytest.mark.parametrize("shape", [(14336, 4096), (4096, 14336), (1024, 4096)])
+def test_full_size_round_trip_properties(ops, shape):
+    """At the benchmark's tensor sizes: compress -> decompress -> compress is a fixed point (same words, same
+    scales), the dequantized tensor equals fake-quantize of the rotated tensor, and the reconstruction error is
+    bounded by half a quantization step per element."""
+    g = torch.Generator(device="cuda").manual_seed(11)
+    w = (torch.randn(shape, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    sg = signs128(3).cuda()
+    words, scale = ops.absmax_quantize(w, qtype=ops.QINT, bits=4, col_group=128, codec="pack32", hadamard_n=128, signs=sg,
+                                       precision=torch.float64)
+    kw = dict(qtype=ops.QINT, bits=4, col_group=128, scale_row_stride=shape[1] // 128)
+    deq = ops.dequantize(words, scale, None, out_dtype=torch.bfloat16, codec="pack32", cols=shape[1], **kw)
+    rot = ops.hadamard(w, 128, signs=sg, precision=torch.float64)
+    fake = ops.fake_quantize(rot, scale, None, out_dtype=torch.bfloat16, **kw)
+    assert torch.equal(deq.view(torch.int16), fake.view(torch.int16)), "decompress == fake_quantize(rotated)"
+    again = ops.quantize(deq, scale, None, codec="pack32", **kw)
+    assert torch.equal(again, words), "re-quantizing the dequantized tensor with the same scales is the identity"
+    step = scale.float().repeat_interleave(128, dim=1)
+    assert bool(((deq.float() - rot.float()).abs() <= 0.56 * step + 1e-9).all())
+    # rotation is orthogonal: the inverse rotation restores the weights to bf16 accuracy
+    back = ops.hadamard(rot, 128, signs=sg, inverse=True, precision=torch.float64)
+    rel = (back.float() - w.float()).norm() / w.float().norm()
+    assert float(rel) < 5e-3
+    # words checksum is reproducible run to run
+    words2, _ = ops.absmax_quantize(w, qtype=ops.QINT, bits=4, col_group=128, codec="pack32", hadamard_n=128, signs=sg,
+                                    precision=torch.float64)
+    assert int(words.to(torch.int64).sum()) == int(words2.to(torch.int64).sum())
