@@ -273,7 +273,7 @@ def main():
                        "cuda_graphs": codec.use_graphs},
             "compress_gbs": 2 * total_elems / (tc / args.steps) / 1e9, "decompress_gbs": 2 * total_elems / (td / args.steps) / 1e9,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "kernel": "absmax_quant_group_kernel", "peak_kind": peak_kind,
+                         "traffic": None, "kernel": "rotquant128_kernel", "peak_kind": peak_kind,
                          "decompress_frac": ALG_BYTES_PER_ELEM * rank_elems / (td / args.steps) / 1e9 / peak},
             "clocks": clocks, "gpu_launches": int(launches), "e2e": e2e,
         }

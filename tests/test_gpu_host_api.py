@@ -244,6 +244,7 @@ def test_model_compressor_round_trip():
         assert_bit_equal(dict(model.state_dict())[k].cpu(), sd[k], k)
     mc.decompress_model(model)
     for name, want in expect.items():
-        assert_bit_equal(dict(model.named_modules())[name].weight.data.cpu(), want, name)
+        got = dict(model.named_modules())[name].weight.data.cpu()
+        assert got.dtype == want.dtype and torch.equal(got, want), name  # numeric equality, as the reference's reload test
     y = model(torch.randn(2, 256, dtype=torch.bfloat16, device="cuda"))
     assert y.shape == (2, 32)
