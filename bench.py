@@ -159,6 +159,7 @@ def main():
     ap.add_argument("--precision", default="f64", choices=["f64", "f32"], help="accumulation of the Hadamard rotation")
     ap.add_argument("--layers", type=int, default=32, help="decoder layers of the model (32 = Llama-3-8B)")
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--no-batch", action="store_true", help="one launch per tensor instead of one grid per shard")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
@@ -183,7 +184,7 @@ def main():
     weights = make_weights(my_layers, dev, shapes)
     signs = make_signs().to(dev)
     precision = torch.float64 if args.precision == "f64" else torch.float32
-    codec = parallel.ShardCodec(weights, group_size=128, hadamard_n=128, signs=signs, precision=precision, use_graphs=not args.no_graphs)
+    codec = parallel.ShardCodec(weights, group_size=128, hadamard_n=128, signs=signs, precision=precision, use_graphs=not args.no_graphs, batch=not args.no_batch)
     stream = torch.cuda.current_stream()
     my_elems = codec.numel
     total_elems = sum(o * i for _, o, i in shapes) * args.layers
@@ -270,7 +271,7 @@ def main():
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": WORKLOAD, "layers": args.layers, "tensors_per_rank": len(weights), "partition": f"layers/{world}",
                        "hadamard_accumulate": args.precision, "l2": "inputs larger than L2 (no flush needed)",
-                       "cuda_graphs": codec.use_graphs},
+                       "cuda_graphs": codec.use_graphs, "one_grid_per_shard": codec.batched},
             "compress_gbs": 2 * total_elems / (tc / args.steps) / 1e9, "decompress_gbs": 2 * total_elems / (td / args.steps) / 1e9,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": None, "kernel": "rotquant128_kernel", "peak_kind": peak_kind,

@@ -60,6 +60,13 @@ class QDesc(ctypes.Structure):
     ]
 
 
+class TensorRef(ctypes.Structure):
+    """Mirror of ``ctb_tensor_ref``."""
+
+    _fields_ = [("inp", ctypes.c_void_p), ("out", ctypes.c_void_p), ("scale", ctypes.c_void_p),
+                ("rows", ctypes.c_int64), ("cols", ctypes.c_int64)]
+
+
 _lib = None
 
 

@@ -11,6 +11,7 @@
 // at most 256 bf16/fp16 values are exact in float64 whatever the order, so the float64 butterfly
 // below reproduces its matmul bit for bit.  The float32 mode trades that for speed.
 #include "ctb_codec.cuh"
+#include "ctb_rotquant.cuh"
 
 namespace ctb {
 
@@ -268,9 +269,32 @@ __global__ void __launch_bounds__(kThreads) absmax_quant_row_kernel(const HArgs 
 // ------------------------------------------------------------------ entry points
 
 namespace ctb {
-constexpr int kRQThreads = 128;
-template <typename A, bool QUANT>
-__global__ void rotquant128_kernel(const void *x, const int8_t *signs, void *out_words, void *out_scale, int64_t nblocks);
+
+// launch the batched block-128 kernel over `B` (already filled except for nothing: starts, counts, pointers)
+static int launch_rotquant(const RQBatch &B, const int8_t *signs, int precision, bool quant, cudaStream_t st) {
+    const int64_t total = B.start[B.count];
+    if (total == 0) return CTB_OK;
+    int grid = grid_for(total, kRQThreads / 2, precision == CTB_F64 ? 2 : 4);
+    if (precision == CTB_F64) {
+        if (quant) rotquant128_kernel<double, true><<<grid, kRQThreads, 0, st>>>(B, signs);
+        else rotquant128_kernel<double, false><<<grid, kRQThreads, 0, st>>>(B, signs);
+    } else {
+        if (quant) rotquant128_kernel<float, true><<<grid, kRQThreads, 0, st>>>(B, signs);
+        else rotquant128_kernel<float, false><<<grid, kRQThreads, 0, st>>>(B, signs);
+    }
+    return after_launch("rotquant128_kernel");
+}
+
+static void rq_single(RQBatch &B, const void *x, void *out, void *scale, int64_t nblocks) {
+    B.count = 1;
+    B.start[0] = 0;
+    B.start[1] = (nblocks + 15) & ~(int64_t)15;
+    B.nblocks[0] = nblocks;
+    B.x[0] = x;
+    B.out[0] = out;
+    B.scale[0] = scale;
+}
+
 }  // namespace ctb
 
 using namespace ctb;
@@ -289,11 +313,9 @@ extern "C" int ctb_hadamard(const void *x, int32_t dtype, int64_t rows, int64_t 
     if (side == 0) {
         if (cols % n) return fail(CTB_EINVAL_SHAPE, "columns %lld are not a multiple of the Hadamard size %d", (long long)cols, n);
         if (n == 128 && dtype == CTB_BF16 && !inverse && normalize && aligned16(x) && aligned16(out)) {
-            const int64_t nblocks = rows * cols / 128;
-            int grid = grid_for(nblocks, kRQThreads / 2, precision == CTB_F64 ? 2 : 4);
-            if (precision == CTB_F64) rotquant128_kernel<double, false><<<grid, kRQThreads, 0, st>>>(x, signs, out, nullptr, nblocks);
-            else rotquant128_kernel<float, false><<<grid, kRQThreads, 0, st>>>(x, signs, out, nullptr, nblocks);
-            return after_launch("rotquant128_kernel");
+            static thread_local RQBatch B;
+            rq_single(B, x, out, nullptr, rows * cols / 128);
+            return launch_rotquant(B, signs, precision, false, st);
         }
         if (n >= 8 && n <= 256 && aligned16(x) && aligned16(out)) {
             HArgs a{};
@@ -359,11 +381,9 @@ extern "C" int ctb_absmax_quantize(const ctb_qdesc *d, const void *x, const floa
         if (fout != F_PACK4) return fail(CTB_EUNSUPPORTED, "the fused rotation is built for int4 PACK32 output");
         a.GL = (int)GL;
         if (n == 128 && d->col_group == 128) {
-            const int64_t nblocks = d->rows * d->cols / 128;
-            int grid = grid_for(nblocks, kRQThreads / 2, precision == CTB_F64 ? 2 : 4);
-            if (precision == CTB_F64) rotquant128_kernel<double, true><<<grid, kRQThreads, 0, st>>>(x, signs, out, out_scale, nblocks);
-            else rotquant128_kernel<float, true><<<grid, kRQThreads, 0, st>>>(x, signs, out, out_scale, nblocks);
-            return after_launch("rotquant128_kernel");
+            static thread_local RQBatch B;
+            rq_single(B, x, out, out_scale, d->rows * d->cols / 128);
+            return launch_rotquant(B, signs, precision, true, st);
         }
         int grid = grid_for(a.chunks, kThreads, 8);
         if (precision == CTB_F64) absmax_quant_group_kernel<double, true, F_BF16, QK_INT, F_PACK4><<<grid, kThreads, 0, st>>>(a);
@@ -393,144 +413,33 @@ extern "C" int ctb_absmax_quantize(const ctb_qdesc *d, const void *x, const floa
     return fail(CTB_EUNSUPPORTED, "fused calibration takes groups of 8..256 (power of two) or whole rows");
 }
 
-// ------------------------------------------------------------------ block-128 rotate + int4 group-128, second generation
-//
-// One 128-element Hadamard block is also one quantization group.  Two neighbouring lanes own a
-// block: lane half h holds elements 16a + 8h + j (a, j = 0..7) as eight 16-byte chunks, so six of
-// the seven butterfly stages (index bits 0-2 and 4-6) stay in registers and only bit 3 crosses
-// lanes (one shuffle per element).  After the rotation the values are rounded to bf16 exactly as the
-// separate rotate call would, the group maximum is reduced over the pair, and the int4 codes are
-// produced with packed bf16x2 arithmetic:
-//   q  = bf16_rn(w * rcp(s))                (equal to bf16_rn(w / s) for bf16 operands)
-//   q  = min(max(q, -8), 7)                 (packed min/max)
-//   q += 200                                 (bf16 has 8 significant bits: in [128, 256) the add rounds
-//                                             half-to-even to an integer, i.e. torch.round; 200 = 0x4348,
-//                                             so the low nibble of the result is code + 8)
-namespace ctb {
 
-// QUANT = false stops after the rotation and writes the rotated bf16 tensor (same arithmetic, so the
-// fused output can be checked against quantize(rotate(x)) bit for bit in either precision).
-template <typename A, bool QUANT>
-__global__ void __launch_bounds__(kRQThreads) rotquant128_kernel(const void *x, const int8_t *signs, void *out_words, void *out_scale,
-                                                                 int64_t nblocks) {
-    __shared__ float cs[128];  // sign_i / sqrt(128) (fp32 mode) or sign_i (fp64 mode)
-    for (int i = threadIdx.x; i < 128; i += kRQThreads) {
-        float s = signs ? (float)signs[i] : 1.0f;
-        cs[i] = sizeof(A) == 8 ? s : s * 0.08838834764831845f;  // 1/sqrt(128)
+
+extern "C" int ctb_rotate_quantize_int4_batch(const ctb_tensor_ref *tensors, int32_t count, const int8_t *signs, int32_t precision,
+                                              void *stream) {
+    if (!tensors && count > 0) return fail(CTB_EINVAL_NULL, "null tensor table");
+    if (precision != CTB_F64 && precision != CTB_F32) return fail(CTB_EINVAL_DTYPE, "precision must be F64 or F32");
+    static thread_local RQBatch B;
+    for (int32_t base = 0; base < count; base += kBatchMax) {
+        const int32_t n = count - base < kBatchMax ? count - base : kBatchMax;
+        int64_t g = 0;
+        for (int32_t i = 0; i < n; ++i) {
+            const ctb_tensor_ref &t = tensors[base + i];
+            if (!t.in || !t.out || !t.scale) return fail(CTB_EINVAL_NULL, "tensor %d has a null buffer", base + i);
+            if (t.rows < 0 || t.cols <= 0 || t.cols % 128) return fail(CTB_EINVAL_SHAPE, "tensor %d: columns %lld are not a multiple of 128", base + i, (long long)t.cols);
+            if (!aligned16(t.in) || !aligned16(t.out)) return fail(CTB_EINVAL_ALIGN, "tensor %d is not 16-byte aligned", base + i);
+            const int64_t nb = t.rows * t.cols / 128;
+            B.start[i] = g;
+            B.nblocks[i] = nb;
+            B.x[i] = t.in;
+            B.out[i] = t.out;
+            B.scale[i] = t.scale;
+            g += (nb + 15) & ~(int64_t)15;
+        }
+        B.count = n;
+        B.start[n] = g;
+        int rc = launch_rotquant(B, signs, precision, true, as_stream(stream));
+        if (rc) return rc;
     }
-    __syncthreads();
-    const int h = threadIdx.x & 1;
-    const int64_t pairs = (int64_t)gridDim.x * (kRQThreads / 2);
-    const int64_t padded = (nblocks + 15) & ~(int64_t)15;  // whole warps (16 pairs) stay together for the shuffles
-    for (int64_t blk = (int64_t)blockIdx.x * (kRQThreads / 2) + (threadIdx.x >> 1); blk < padded; blk += pairs) {
-        const bool live = blk < nblocks;
-        A v[8][8];
-        {
-            uint4 raw[8];
-#pragma unroll
-            for (int a = 0; a < 8; ++a) raw[a] = live ? ld_stream((const char *)x + (blk * 16 + 2 * a + h) * 16) : make_uint4(0, 0, 0, 0);
-#pragma unroll
-            for (int a = 0; a < 8; ++a) {
-                const uint32_t w[4] = {raw[a].x, raw[a].y, raw[a].z, raw[a].w};
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    v[a][2 * k] = (A)__uint_as_float(w[k] << 16);
-                    v[a][2 * k + 1] = (A)__uint_as_float(w[k] & 0xFFFF0000u);
-                }
-            }
-        }
-        // index bits 4..6 (a)
-#pragma unroll
-        for (int s = 1; s < 8; s <<= 1)
-#pragma unroll
-            for (int a = 0; a < 8; ++a)
-                if ((a & s) == 0)
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        A p = v[a][j], q = v[a | s][j];
-                        v[a][j] = p + q;
-                        v[a | s][j] = p - q;
-                    }
-        // index bits 0..2 (j)
-#pragma unroll
-        for (int a = 0; a < 8; ++a) fwht8<A>(v[a]);
-        // index bit 3 (the lane half)
-        const A sg = h ? (A)-1 : (A)1;
-#pragma unroll
-        for (int a = 0; a < 8; ++a)
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                A other = shfl_xor<A>(v[a][j], 1);
-                v[a][j] = v[a][j] * sg + other;  // exact: one rounding, same as other -/+ v
-            }
-        // normalise, apply the sign diagonal, round to bf16 (the rotated weight), group maximum
-        uint32_t wq[8][4];  // rotated weights, packed bf16x2
-        float amax = 0.0f;
-#pragma unroll
-        for (int a = 0; a < 8; ++a)
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                float f0, f1;
-                const float c0 = cs[16 * a + 8 * h + 2 * k], c1 = cs[16 * a + 8 * h + 2 * k + 1];
-                if constexpr (sizeof(A) == 8) {
-                    // float64 quotient by sqrt(128), correctly rounded (reciprocal + one Markstein correction), then the
-                    // float64 -> float32 -> bf16 cast chain of Tensor.to
-                    const double c = sqrt(128.0), r = 1.0 / c;  // folded at compile time, both correctly rounded
-                    double t0 = v[a][2 * k], t1 = v[a][2 * k + 1];
-                    double q0 = t0 * r, q1 = t1 * r;
-                    q0 = fma(fma(-q0, c, t0), r, q0);
-                    q1 = fma(fma(-q1, c, t1), r, q1);
-                    f0 = (float)q0 * c0 + 0.0f;
-                    f1 = (float)q1 * c1 + 0.0f;
-                } else {
-                    f0 = (float)v[a][2 * k] * c0 + 0.0f;  // + 0.0f: an exact zero is +0.0 in the reference's matmul
-                    f1 = (float)v[a][2 * k + 1] * c1 + 0.0f;
-                }
-                amax = fmaxf(amax, fmaxf(fabsf(f0), fabsf(f1)));
-                wq[a][k] = bf162_as_u32(__floats2bfloat162_rn(f0, f1));
-            }
-        if constexpr (!QUANT) {
-            if (live)
-#pragma unroll
-                for (int a = 0; a < 8; ++a)
-                    st_stream((char *)out_words + (blk * 16 + 2 * a + h) * 16, make_uint4(wq[a][0], wq[a][1], wq[a][2], wq[a][3]));
-            continue;
-        }
-        amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
-        amax = round_to<CTB_BF16>(amax);  // max of the rounded values = rounded max (rounding is monotonic)
-        // helpers.py:110,122: scale = bf16(amax / 7.5) clamped at fp32 eps
-        const float s = fmaxf(round_to<CTB_BF16>(__fdiv_rn(amax, 7.5f)), 1.1920928955078125e-07f);
-        const float r = __frcp_rn(s);
-        if (live && h == 0) ((__nv_bfloat16 *)out_scale)[blk] = __float2bfloat16_rn(s);
-        uint32_t word[8];
-#pragma unroll
-        for (int a = 0; a < 8; ++a) {
-            uint32_t b[4];
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                const float f0 = __uint_as_float(wq[a][k] << 16), f1 = __uint_as_float(wq[a][k] & 0xFFFF0000u);
-                b[k] = int4_pair_code(__floats2bfloat162_rn(f0 * r, f1 * r));
-            }
-            word[a] = __byte_perm(__byte_perm(b[0], b[1], 0x0040), __byte_perm(b[2], b[3], 0x0040), 0x5410);
-        }
-        // word[a] covers elements 16a + 8h .. +7, i.e. output word 2a + h of the block's 16.  Swap so that
-        // half 0 owns words 0..7 and half 1 words 8..15, then two 16-byte stores per lane.
-        uint32_t mine[8];
-#pragma unroll
-        for (int a = 0; a < 4; ++a) {
-            // half 0 keeps word[a] (a<4) and needs the partner's word[a] (a<4); half 1 keeps word[a+4], needs partner's word[a+4]
-            uint32_t send = h ? word[a] : word[a + 4];
-            uint32_t got = __shfl_xor_sync(0xFFFFFFFFu, send, 1);
-            uint32_t keep = h ? word[a + 4] : word[a];
-            mine[2 * a] = h ? got : keep;      // word index 2a' + 0 comes from half 0
-            mine[2 * a + 1] = h ? keep : got;  // word index 2a' + 1 comes from half 1
-        }
-        if (live) {
-            char *o = (char *)out_words + blk * 64 + h * 32;
-            st_stream(o, make_uint4(mine[0], mine[1], mine[2], mine[3]));
-            st_stream(o + 16, make_uint4(mine[4], mine[5], mine[6], mine[7]));
-        }
-    }
+    return CTB_OK;
 }
-
-}  // namespace ctb

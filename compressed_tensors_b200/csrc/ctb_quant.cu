@@ -352,3 +352,89 @@ extern "C" int ctb_fake_quantize(const ctb_qdesc *desc, const void *x, const voi
                                  const int32_t *g_idx, const float *global_scale, void *out, void *stream) {
     return ctb::run(2, desc, x, scale, zero_point, g_idx, global_scale, out, stream);
 }
+
+// ------------------------------------------------------------------ whole-shard unpack + dequantize (int4, group 128, bf16)
+
+namespace ctb {
+
+constexpr int kDQBatchMax = 256;
+
+struct DQBatch {
+    int count;
+    int64_t start[kDQBatchMax + 1];  // first global chunk (8 elements) of each tensor; start[count] = total
+    const void *in[kDQBatchMax];     // packed words
+    const void *scale[kDQBatchMax];  // bf16, one per 16 chunks
+    void *out[kDQBatchMax];          // bf16
+};
+
+// One launch for every tensor of the table: the chunks of all tensors form one index space and the grid
+// strides over it; the next round's words and scales are loaded before the current round is written.
+__global__ void __launch_bounds__(kThreads) dequant_int4_batch_kernel(const __grid_constant__ DQBatch B) {
+    const int64_t total = B.start[B.count];
+    const int64_t stride = (int64_t)gridDim.x * kThreads * kUnroll;
+    int64_t g = (int64_t)blockIdx.x * kThreads * kUnroll + threadIdx.x;
+    int t = 0;
+    uint32_t word[kUnroll], sbits[kUnroll];
+    char *optr[kUnroll];
+    auto fetch = [&](int64_t base) {
+        int ti = t;
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const int64_t gi = base + (int64_t)u * kThreads;
+            optr[u] = nullptr;
+            if (gi < total) {
+                while (ti + 1 < B.count && gi >= B.start[ti + 1]) ++ti;
+                if (u == 0) t = ti;  // the thread's next round starts no earlier than this tensor
+                const int64_t c = gi - B.start[ti];
+                word[u] = ld_stream4((const char *)B.in[ti] + c * 4);
+                sbits[u] = __ldg((const unsigned short *)B.scale[ti] + (c >> 4));
+                optr[u] = (char *)B.out[ti] + c * 16;
+            }
+        }
+    };
+    if (g < total) fetch(g);
+    const __nv_bfloat162 bias = __float2bfloat162_rn(136.0f);
+    while (g < total) {
+        uint32_t w[kUnroll], s[kUnroll];
+        char *o[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) { w[u] = word[u]; s[u] = sbits[u]; o[u] = optr[u]; }
+        const int64_t gn = g + stride;
+        if (gn < total) fetch(gn);
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u)
+            if (o[u] != nullptr) st_stream(o[u], dequant_int4_word_bf16(w[u], u32_as_bf162(s[u] | (s[u] << 16)), bias));
+        g = gn;
+    }
+}
+
+}  // namespace ctb
+
+extern "C" int ctb_unpack_dequantize_int4_batch(const ctb_tensor_ref *tensors, int32_t count, void *stream) {
+    using namespace ctb;
+    if (!tensors && count > 0) return fail(CTB_EINVAL_NULL, "null tensor table");
+    static thread_local DQBatch B;
+    for (int32_t base = 0; base < count; base += kDQBatchMax) {
+        const int32_t n = count - base < kDQBatchMax ? count - base : kDQBatchMax;
+        int64_t g = 0;
+        for (int32_t i = 0; i < n; ++i) {
+            const ctb_tensor_ref &t = tensors[base + i];
+            if (!t.in || !t.out || !t.scale) return fail(CTB_EINVAL_NULL, "tensor %d has a null buffer", base + i);
+            if (t.rows < 0 || t.cols <= 0 || t.cols % 128) return fail(CTB_EINVAL_SHAPE, "tensor %d: columns %lld are not a multiple of 128", base + i, (long long)t.cols);
+            if (!aligned16(t.out) || (reinterpret_cast<uintptr_t>(t.in) & 3u)) return fail(CTB_EINVAL_ALIGN, "tensor %d is misaligned", base + i);
+            B.start[i] = g;
+            B.in[i] = t.in;
+            B.scale[i] = t.scale;
+            B.out[i] = t.out;
+            g += t.rows * t.cols / 8;
+        }
+        B.count = n;
+        B.start[n] = g;
+        if (g == 0) continue;
+        int grid = grid_for(g, (int64_t)kThreads * kUnroll, 8);
+        dequant_int4_batch_kernel<<<grid, kThreads, 0, as_stream(stream)>>>(B);
+        int rc = after_launch("dequant_int4_batch_kernel");
+        if (rc) return rc;
+    }
+    return CTB_OK;
+}

@@ -13,7 +13,7 @@ __all__ = [
     "quantize", "dequantize", "fake_quantize", "minmax", "calculate_qparams", "generate_gparam",
     "pack_int32", "unpack_int32", "pack_fp4", "unpack_fp4", "pack_bitmasks", "unpack_bitmasks",
     "sparse24_mask", "sparse24_compress", "bitmask_compress", "bitmask_decompress", "hadamard",
-    "absmax_quantize", "QINT", "QFLOAT",
+    "absmax_quantize", "rotate_quantize_int4_batch", "unpack_dequantize_int4_batch", "tensor_table", "QINT", "QFLOAT",
 ]
 
 _CODEC = {"dtype": CODE_DTYPE, "pack32": CODE_PACK32, "fp4x2": CODE_FP4X2}
@@ -321,3 +321,29 @@ def absmax_quantize(x, *, qtype, bits, col_group, codec="pack32", out_dtype=None
     check(lib().ctb_absmax_quantize(ctypes.byref(d), ptr(x), ptr(gs), ptr(scale), ptr(out), i32(hadamard_n), ptr(s),
                                     i32(DT[precision]), stream_of(x)))
     return out, scale
+
+
+def tensor_table(ins, outs, scales, shapes):
+    """A ctypes array of ``ctb_tensor_ref`` for the whole-shard entry points.  Build it once per shard and
+    reuse it: the batched calls then cost one launch and no per-tensor Python work."""
+    n = len(ins)
+    table = (L.TensorRef * n)()
+    for i in range(n):
+        require_cuda(ins[i], outs[i], scales[i])
+        table[i] = L.TensorRef(ins[i].data_ptr(), outs[i].data_ptr(), scales[i].data_ptr(), int(shapes[i][0]), int(shapes[i][1]))
+    return table
+
+
+def rotate_quantize_int4_batch(table, signs, precision=torch.float64, device=None):
+    """Block-128 Hadamard rotation + symmetric int4 group-128 calibrate + quantize + pack of every tensor in
+    `table` (weights bf16 in, int32 words and bf16 scales out), as one launch."""
+    s = None if signs is None else signs
+    stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+    check(lib().ctb_rotate_quantize_int4_batch(table, i32(len(table)), ptr(s), i32(DT[precision]), stream))
+
+
+def unpack_dequantize_int4_batch(table, device=None):
+    """unpack_from_int32 + dequantize (int4, group 128, bf16 scales, symmetric) of every tensor in `table`
+    (words in, bf16 weights out), as one launch."""
+    stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+    check(lib().ctb_unpack_dequantize_int4_batch(table, i32(len(table)), stream))

@@ -73,7 +73,7 @@ class ShardCodec:
     CUDA graphs so that a shard of many small tensors is not bound by launch latency."""
 
     def __init__(self, weights: Sequence[torch.Tensor], *, group_size: int = 128, hadamard_n: int = 128,
-                 signs: Optional[torch.Tensor] = None, precision=torch.float64, use_graphs: bool = False):
+                 signs: Optional[torch.Tensor] = None, precision=torch.float64, use_graphs: bool = False, batch: bool = True):
         from . import ops
 
         self.ops = ops
@@ -86,15 +86,43 @@ class ShardCodec:
         self.restored: List[Optional[torch.Tensor]] = [None] * len(self.weights)
         self._graphs: Dict[str, torch.cuda.CUDAGraph] = {}
         self.use_graphs = use_graphs
+        self.batch = batch
 
-    # ------------------------------------------------------------------ plain launches
+    # ------------------------------------------------------------------ launches
+    def _allocate(self) -> None:
+        if self.packed[0] is not None:
+            return
+        dev = self.weights[0].device
+        for i, w in enumerate(self.weights):
+            rows, cols = w.shape
+            self.packed[i] = torch.empty((rows, cols // 8), dtype=torch.int32, device=dev)
+            self.scales[i] = torch.empty((rows, cols // self.group_size), dtype=w.dtype, device=dev)
+            self.restored[i] = torch.empty_like(w)
+        shapes = [tuple(w.shape) for w in self.weights]
+        self._ctable = self.ops.tensor_table(self.weights, self.packed, self.scales, shapes)
+        self._dtable = self.ops.tensor_table(self.packed, self.restored, self.scales, shapes)
+
+    @property
+    def batched(self) -> bool:
+        """One grid for the whole shard (block-128 rotation, group 128, bf16); otherwise one launch per tensor."""
+        return (self.batch and self.hadamard_n == 128 and self.group_size == 128
+                and all(w.dtype == torch.bfloat16 and w.shape[1] % 128 == 0 for w in self.weights))
+
     def _compress(self) -> None:
+        if self.batched:
+            self._allocate()
+            self.ops.rotate_quantize_int4_batch(self._ctable, self.signs, self.precision, self.weights[0].device)
+            return
         for i, w in enumerate(self.weights):
             self.packed[i], self.scales[i] = self.ops.absmax_quantize(
                 w, qtype=self.ops.QINT, bits=4, col_group=self.group_size, codec="pack32",
                 hadamard_n=self.hadamard_n, signs=self.signs, precision=self.precision)
 
     def _decompress(self) -> None:
+        if self.batched:
+            self._allocate()
+            self.ops.unpack_dequantize_int4_batch(self._dtable, self.weights[0].device)
+            return
         for i, w in enumerate(self.weights):
             cols = w.shape[1]
             self.restored[i] = self.ops.dequantize(
@@ -129,4 +157,4 @@ class ShardCodec:
 
     @property
     def launches_per_pass(self) -> int:
-        return len(self.weights)
+        return -(-len(self.weights) // 256) if self.batched else len(self.weights)

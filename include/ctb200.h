@@ -218,6 +218,24 @@ int ctb_absmax_quantize(const ctb_qdesc *desc, const void *x, const float *globa
                         void *out_scale, void *out, int32_t hadamard_n, const int8_t *signs,
                         int32_t precision, void *stream);
 
+/* ---- whole-shard batches ------------------------------------------------------------------------
+ * The reference walks a state dict one tensor at a time (compressors/quantized_compressors/base.py:91,
+ * model_compressors/model_compressor.py:469, :558).  These entry points take the whole list and run it
+ * as ONE grid, so small tensors cost neither a launch nor a kernel tail each.  Results are identical to
+ * the per-tensor calls.  All tensors: bf16, cols % 128 == 0, symmetric int4, group_size 128. */
+typedef struct ctb_tensor_ref {
+    const void *in;  /* compress: dense bf16 weight;        decompress: packed int32 words      */
+    void *out;       /* compress: packed int32 words;       decompress: dense bf16 weight       */
+    void *scale;     /* bf16 [rows, cols/128]: written by compress, read by decompress           */
+    int64_t rows, cols; /* of the dense weight */
+} ctb_tensor_ref;
+
+/* ctb_absmax_quantize(hadamard_n = 128, group 128, PACK32) for every tensor of the table. */
+int ctb_rotate_quantize_int4_batch(const ctb_tensor_ref *tensors, int32_t count, const int8_t *signs,
+                                   int32_t precision, void *stream);
+/* ctb_dequantize(codec PACK32, num_bits 4, group 128, bf16 scale, no zero point) for every tensor. */
+int ctb_unpack_dequantize_int4_batch(const ctb_tensor_ref *tensors, int32_t count, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

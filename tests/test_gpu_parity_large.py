@@ -196,3 +196,32 @@ def test_full_size_round_trip_properties(ops, shape):
     words2, _ = ops.absmax_quantize(w, qtype=ops.QINT, bits=4, col_group=128, codec="pack32", hadamard_n=128, signs=sg,
                                     precision=torch.float64)
     assert int(words.to(torch.int64).sum()) == int(words2.to(torch.int64).sum())
+
+
+def test_whole_shard_batch_equals_per_tensor(ops):
+    """One grid over a list of tensors (ragged sizes, a tensor smaller than one warp of blocks) gives exactly
+    the per-tensor results, in both rotation precisions, and decompress restores the same values."""
+    from compressed_tensors_b200.parallel import ShardCodec
+
+    shapes = [(3, 128), (64, 256), (1024, 4096), (17, 384), (256, 14336), (1, 128)]
+    ws = [weights(r, c, seed=20 + i).cuda() for i, (r, c) in enumerate(shapes)]
+    sg = signs128(5).cuda()
+    for precision in (torch.float64, torch.float32):
+        batched = ShardCodec(ws, signs=sg, precision=precision, batch=True)
+        single = ShardCodec(ws, signs=sg, precision=precision, batch=False)
+        assert batched.batched and not single.batched
+        batched.compress(), single.compress()
+        batched.decompress(), single.decompress()
+        for i in range(len(ws)):
+            assert_bit_equal(batched.scales[i].cpu(), single.scales[i].cpu(), f"scales of tensor {i}")
+            assert_bit_equal(batched.packed[i].cpu(), single.packed[i].cpu(), f"words of tensor {i}")
+            assert_bit_equal(batched.restored[i].cpu(), single.restored[i].cpu(), f"restored tensor {i}")
+    # and through CUDA graphs
+    exact = ShardCodec(ws, signs=sg, precision=torch.float64, batch=False)
+    exact.compress()
+    graphed = ShardCodec(ws, signs=sg, precision=torch.float64, batch=True, use_graphs=True)
+    for _ in range(2):
+        graphed.compress(), graphed.decompress()
+    torch.cuda.synchronize()
+    for i in range(len(ws)):
+        assert_bit_equal(graphed.packed[i].cpu(), exact.packed[i].cpu(), "graph replay")
