@@ -150,6 +150,90 @@ def run_reference(args):
     }))
 
 
+def per_config_table(dev, peak):
+    """Device-timed throughput of the other BASELINE.json configs (C1-C4) on their named shapes.  Each op runs
+    over a rotating set of distinct input/output buffers whose total exceeds 2x the L2 size, so every launch
+    streams from HBM.  GB/s is bf16 (dense-side) input bytes / time; frac = algorithmic bytes / time / peak."""
+    from compressed_tensors_b200 import ops
+
+    out = {}
+    g = torch.Generator(device=dev).manual_seed(SEED + 1)
+    l2 = 2 * 126 * 1024 * 1024
+
+    def rnd(r, c, std=0.02):
+        return (torch.randn(r, c, generator=g, device=dev) * std).to(torch.bfloat16)
+
+    def run(name, make_args, fn, dense_bytes, alg_bytes, per_set_bytes):
+        nsets = max(2, min(16, -(-l2 // per_set_bytes)))
+        sets = [make_args() for _ in range(nsets)]
+        for a in sets[:2]:
+            fn(*a)
+        torch.cuda.synchronize()
+        reps = 3
+        st, en = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        st.record()
+        for _ in range(reps):
+            for a in sets:
+                fn(*a)
+        en.record()
+        en.synchronize()
+        sec = st.elapsed_time(en) / 1e3 / (reps * nsets)
+        out[name] = {"us": round(sec * 1e6, 2), "dense_gbs": round(dense_bytes / sec / 1e9, 1), "frac": round(alg_bytes / sec / 1e9 / peak, 3)}
+
+    kw4 = dict(qtype=ops.QINT, bits=4, col_group=128)
+    n = 4096 * 4096
+    run("c1_w4a16_calibrate_quantize_pack", lambda: (rnd(4096, 4096),),
+        lambda w: ops.absmax_quantize(w, codec="pack32", **kw4), 2 * n, 2.515625 * n, 2.6 * n)
+    def c1_dq_args():
+        w = rnd(4096, 4096)
+        return ops.absmax_quantize(w, codec="pack32", **kw4)
+    run("c1_w4a16_unpack_dequantize", c1_dq_args,
+        lambda p, sc: ops.dequantize(p, sc, None, scale_row_stride=32, out_dtype=torch.bfloat16, codec="pack32", cols=4096, **kw4),
+        2 * n, 2.515625 * n, 2.6 * n)
+    kw8 = dict(qtype=ops.QFLOAT, bits=8, col_group=4096)
+    run("c2_fp8_weight_channel_calibrate_quantize", lambda: (rnd(4096, 4096),),
+        lambda w: ops.absmax_quantize(w, codec="dtype", out_dtype=torch.float8_e4m3fn, **kw8), 2 * n, 3 * n, 3 * n)
+    na = 8192 * 4096
+    def act():
+        x = torch.randn(1, 8192, 4096, generator=g, device=dev)
+        x[..., torch.randperm(4096, generator=g, device=dev)[:41]] *= 20
+        return (x.to(torch.bfloat16),)
+    run("c2_fp8_activation_token_calibrate_quantize", act,
+        lambda x: ops.absmax_quantize(x, codec="dtype", out_dtype=torch.float8_e4m3fn, **kw8), 2 * na, 3 * na, 3 * na)
+    def c2_dq_args():
+        return ops.absmax_quantize(act()[0], codec="dtype", out_dtype=torch.float8_e4m3fn, **kw8)
+    run("c2_fp8_activation_dequantize", c2_dq_args,
+        lambda q, sc: ops.dequantize(q, sc, None, scale_row_stride=1, out_dtype=torch.bfloat16, **kw8), 2 * na, 3 * na, 3 * na)
+    nm = 14336 * 4096
+    kwf = dict(qtype=ops.QFLOAT, bits=4, col_group=16)
+    def nv(w):
+        mn, mx = ops.minmax(w, w.shape[0], w.shape[1])
+        gs = ops.generate_gparam(mn, mx)
+        return ops.absmax_quantize(w, codec="fp4x2", global_scale=gs, **kwf) + (gs,)
+    run("c3_nvfp4_amax_scales_quantize_pack", lambda: (rnd(14336, 4096),), nv, 2 * nm, 4.5625 * nm, 2.6 * nm)
+    run("c3_nvfp4_unpack_dequantize", lambda: nv(rnd(4096, 14336)),
+        lambda p, sc, gs: ops.dequantize(p, sc, None, scale_row_stride=14336 // 16, out_dtype=torch.bfloat16, codec="fp4x2", global_scale=gs, **kwf),
+        2 * nm, 2.5625 * nm, 2.6 * nm)
+    ns = 4096 * 11008
+    def s24():
+        w = rnd(4096, 11008)
+        keep = ops.sparse24_mask(w)
+        w = torch.where(keep, w, torch.zeros((), dtype=w.dtype, device=dev))
+        q, _ = ops.absmax_quantize(w, qtype=ops.QFLOAT, bits=8, col_group=11008, codec="dtype", out_dtype=torch.float8_e4m3fn)
+        return (q,)
+    run("c4a_sparse24_compress_e4m3", s24, lambda q: ops.sparse24_compress(q), 2 * ns, 1.625 * ns, 1.7 * ns)
+    run("c4a_sparse24_decompress_e4m3", lambda: ops.sparse24_compress(s24()[0]),
+        lambda v, b: ops.bitmask_decompress(v, b, (4096, 11008)), 2 * ns, 1.625 * ns, 1.7 * ns)
+    def unstructured():
+        w = rnd(4096, 4096)
+        w[torch.rand(4096, 4096, generator=g, device=dev) < 0.5] = 0
+        return (w,)
+    run("c4b_bitmask_compress_bf16_50pct", unstructured, lambda w: ops.bitmask_compress(w), 2 * n, (2 + 1 + 0.125) * n, 3.2 * n)
+    run("c4b_bitmask_decompress_bf16_50pct", lambda: ops.bitmask_compress(unstructured()[0])[:2],
+        lambda v, b: ops.bitmask_decompress(v, b, (4096, 4096)), 2 * n, (2 + 1 + 0.125) * n, 3.2 * n)
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -162,6 +246,7 @@ def main():
     ap.add_argument("--no-batch", action="store_true", help="one launch per tensor instead of one grid per shard")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-per-config", action="store_true", help="skip the C1-C4 per-scheme table")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
@@ -278,6 +363,10 @@ def main():
                          "decompress_frac": ALG_BYTES_PER_ELEM * rank_elems / (td / args.steps) / 1e9 / peak},
             "clocks": clocks, "gpu_launches": int(launches), "e2e": e2e,
         }
+        if world == 1 and not args.no_per_config:
+            del codec, weights
+            torch.cuda.empty_cache()
+            out["per_config"] = per_config_table(dev, peak)
         if world == 1 and not args.no_cpu_baseline:
             from oracle import ref as orc
             orc.build()
