@@ -164,21 +164,36 @@ def per_config_table(dev, peak):
         return (torch.randn(r, c, generator=g, device=dev) * std).to(torch.bfloat16)
 
     def run(name, make_args, fn, dense_bytes, alg_bytes, per_set_bytes):
-        nsets = max(2, min(16, -(-l2 // per_set_bytes)))
+        nsets = int(max(2, min(16, -(-l2 // int(per_set_bytes)))))
         sets = [make_args() for _ in range(nsets)]
         for a in sets[:2]:
             fn(*a)
         torch.cuda.synchronize()
         reps = 3
+
+        def sweep():
+            for a in sets:
+                fn(*a)
+
+        mode = "cuda graph"
+        try:  # replay from a CUDA graph so that the host-side call overhead of these 5-50 us kernels is not what is timed
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                sweep()
+            replay = graph.replay
+        except Exception:  # ops that read a count back to the host cannot be captured
+            torch.cuda.synchronize()
+            replay, mode = sweep, "eager (host sync inside)"
+        replay()
+        torch.cuda.synchronize()
         st, en = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         st.record()
         for _ in range(reps):
-            for a in sets:
-                fn(*a)
+            replay()
         en.record()
         en.synchronize()
         sec = st.elapsed_time(en) / 1e3 / (reps * nsets)
-        out[name] = {"us": round(sec * 1e6, 2), "dense_gbs": round(dense_bytes / sec / 1e9, 1), "frac": round(alg_bytes / sec / 1e9 / peak, 3)}
+        out[name] = {"us": round(sec * 1e6, 2), "dense_gbs": round(dense_bytes / sec / 1e9, 1), "frac": round(alg_bytes / sec / 1e9 / peak, 3), "timed": mode}
 
     kw4 = dict(qtype=ops.QINT, bits=4, col_group=128)
     n = 4096 * 4096
@@ -240,7 +255,8 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--precision", default="f64", choices=["f64", "f32"], help="accumulation of the Hadamard rotation")
+    ap.add_argument("--precision", default="f64", choices=["f64", "f32", "tc"],
+                    help="Hadamard rotation: float64 butterfly (bit-identical to the reference), float32 butterfly, or tcgen05 tensor cores with fp32 accumulators")
     ap.add_argument("--layers", type=int, default=32, help="decoder layers of the model (32 = Llama-3-8B)")
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--no-batch", action="store_true", help="one launch per tensor instead of one grid per shard")
@@ -268,7 +284,7 @@ def main():
     my_layers = parallel.partition_layers(args.layers, world, rank)
     weights = make_weights(my_layers, dev, shapes)
     signs = make_signs().to(dev)
-    precision = torch.float64 if args.precision == "f64" else torch.float32
+    precision = {"f64": torch.float64, "f32": torch.float32, "tc": ops.ROT_TENSOR}[args.precision]
     codec = parallel.ShardCodec(weights, group_size=128, hadamard_n=128, signs=signs, precision=precision, use_graphs=not args.no_graphs, batch=not args.no_batch)
     stream = torch.cuda.current_stream()
     my_elems = codec.numel
@@ -359,7 +375,7 @@ def main():
                        "cuda_graphs": codec.use_graphs, "one_grid_per_shard": codec.batched},
             "compress_gbs": 2 * total_elems / (tc / args.steps) / 1e9, "decompress_gbs": 2 * total_elems / (td / args.steps) / 1e9,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "kernel": "rotquant128_kernel", "peak_kind": peak_kind,
+                         "traffic": None, "kernel": "rotquant128_tc_kernel" if args.precision == "tc" else "rotquant128_kernel", "peak_kind": peak_kind,
                          "decompress_frac": ALG_BYTES_PER_ELEM * rank_elems / (td / args.steps) / 1e9 / peak},
             "clocks": clocks, "gpu_launches": int(launches), "e2e": e2e,
         }

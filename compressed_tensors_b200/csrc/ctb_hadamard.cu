@@ -270,6 +270,8 @@ __global__ void __launch_bounds__(kThreads) absmax_quant_row_kernel(const HArgs 
 
 namespace ctb {
 
+int rotquant_tc_launch(const ctb_tensor_ref *tensors, int32_t count, const int8_t *signs, bool quant, int32_t *status, cudaStream_t st);
+
 // launch the batched block-128 kernel over `B` (already filled except for nothing: starts, counts, pointers)
 static int launch_rotquant(const RQBatch &B, const int8_t *signs, int precision, bool quant, cudaStream_t st) {
     const int64_t total = B.start[B.count];
@@ -306,12 +308,17 @@ extern "C" int ctb_hadamard(const void *x, int32_t dtype, int64_t rows, int64_t 
     if (!x || !out) return fail(CTB_EINVAL_NULL, "null buffer");
     if (!is_float_dtype(dtype)) return fail(CTB_EINVAL_DTYPE, "weights must be bf16, f16 or f32");
     if (!pow2(n)) return fail(CTB_EUNSUPPORTED, "only Sylvester sizes (powers of two) are built");
-    if (precision != CTB_F64 && precision != CTB_F32) return fail(CTB_EINVAL_DTYPE, "precision must be F64 or F32");
+    if (precision != CTB_F64 && precision != CTB_F32 && precision != CTB_ROT_TENSOR) return fail(CTB_EINVAL_DTYPE, "precision must be F64, F32 or CTB_ROT_TENSOR");
     if (rows < 0 || cols < 0) return fail(CTB_EINVAL_SHAPE, "negative shape");
     if (rows == 0 || cols == 0) return CTB_OK;
     cudaStream_t st = as_stream(stream);
     if (side == 0) {
         if (cols % n) return fail(CTB_EINVAL_SHAPE, "columns %lld are not a multiple of the Hadamard size %d", (long long)cols, n);
+        if (precision == CTB_ROT_TENSOR) {
+            if (!(n == 128 && dtype == CTB_BF16 && !inverse && normalize)) return fail(CTB_EUNSUPPORTED, "the tensor-core rotation is built for n = 128, bf16, forward, normalised");
+            ctb_tensor_ref t{x, out, nullptr, rows, cols};
+            return rotquant_tc_launch(&t, 1, signs, false, nullptr, st);
+        }
         if (n == 128 && dtype == CTB_BF16 && !inverse && normalize && aligned16(x) && aligned16(out)) {
             static thread_local RQBatch B;
             rq_single(B, x, out, nullptr, rows * cols / 128);
@@ -376,7 +383,12 @@ extern "C" int ctb_absmax_quantize(const ctb_qdesc *d, const void *x, const floa
     const int64_t GL = d->col_group / 8;
     if (n > 0) {
         if (!pow2(n) || n < 8 || n > 256 || d->cols % n) return fail(CTB_EINVAL_SHAPE, "Hadamard size must be a power of two in 8..256 dividing the columns");
-        if (precision != CTB_F64 && precision != CTB_F32) return fail(CTB_EINVAL_DTYPE, "precision must be F64 or F32");
+        if (precision == CTB_ROT_TENSOR) {
+            if (!(n == 128 && d->col_group == 128 && fout == F_PACK4)) return fail(CTB_EUNSUPPORTED, "the tensor-core path is built for n = 128, group 128, int4 PACK32");
+            ctb_tensor_ref t{x, out, out_scale, d->rows, d->cols};
+            return rotquant_tc_launch(&t, 1, signs, true, nullptr, st);
+        }
+        if (precision != CTB_F64 && precision != CTB_F32) return fail(CTB_EINVAL_DTYPE, "precision must be F64, F32 or CTB_ROT_TENSOR");
         if (!(pow2(GL) && GL <= 32)) return fail(CTB_EUNSUPPORTED, "with a rotation in front the group must be a power of two <= 256");
         if (fout != F_PACK4) return fail(CTB_EUNSUPPORTED, "the fused rotation is built for int4 PACK32 output");
         a.GL = (int)GL;
@@ -416,9 +428,10 @@ extern "C" int ctb_absmax_quantize(const ctb_qdesc *d, const void *x, const floa
 
 
 extern "C" int ctb_rotate_quantize_int4_batch(const ctb_tensor_ref *tensors, int32_t count, const int8_t *signs, int32_t precision,
-                                              void *stream) {
+                                              int32_t *device_status, void *stream) {
     if (!tensors && count > 0) return fail(CTB_EINVAL_NULL, "null tensor table");
-    if (precision != CTB_F64 && precision != CTB_F32) return fail(CTB_EINVAL_DTYPE, "precision must be F64 or F32");
+    if (precision == CTB_ROT_TENSOR) return rotquant_tc_launch(tensors, count, signs, true, device_status, as_stream(stream));
+    if (precision != CTB_F64 && precision != CTB_F32) return fail(CTB_EINVAL_DTYPE, "precision must be F64, F32 or CTB_ROT_TENSOR");
     static thread_local RQBatch B;
     for (int32_t base = 0; base < count; base += kBatchMax) {
         const int32_t n = count - base < kBatchMax ? count - base : kBatchMax;

@@ -17,6 +17,11 @@ __all__ = [
 ]
 
 _CODEC = {"dtype": CODE_DTYPE, "pack32": CODE_PACK32, "fp4x2": CODE_FP4X2}
+ROT_TENSOR = "tensor"  # value of `precision` that runs the block-128 rotation on the tensor cores (tcgen05)
+
+
+def _precision_code(precision) -> int:
+    return 100 if precision == ROT_TENSOR else DT[precision]
 
 
 def _c(t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
@@ -294,7 +299,7 @@ def hadamard(x, n, signs=None, inverse=False, side=0, precision=torch.float64, n
     s = None if signs is None else _c(signs.to(torch.int8))
     out = torch.empty_like(x)
     check(lib().ctb_hadamard(ptr(x), i32(DT[x.dtype]), i64(rows), i64(cols), i32(n), ptr(s), i32(int(inverse)), i32(side),
-                             i32(DT[precision]), i32(int(normalize)), ptr(out), stream_of(x)))
+                             i32(_precision_code(precision)), i32(int(normalize)), ptr(out), stream_of(x)))
     return out
 
 
@@ -319,7 +324,7 @@ def absmax_quantize(x, *, qtype, bits, col_group, codec="pack32", out_dtype=None
     gs = _gs(global_scale, x)
     s = None if signs is None else _c(signs.to(torch.int8))
     check(lib().ctb_absmax_quantize(ctypes.byref(d), ptr(x), ptr(gs), ptr(scale), ptr(out), i32(hadamard_n), ptr(s),
-                                    i32(DT[precision]), stream_of(x)))
+                                    i32(_precision_code(precision)), stream_of(x)))
     return out, scale
 
 
@@ -334,12 +339,12 @@ def tensor_table(ins, outs, scales, shapes):
     return table
 
 
-def rotate_quantize_int4_batch(table, signs, precision=torch.float64, device=None):
+def rotate_quantize_int4_batch(table, signs, precision=torch.float64, device=None, status=None):
     """Block-128 Hadamard rotation + symmetric int4 group-128 calibrate + quantize + pack of every tensor in
     `table` (weights bf16 in, int32 words and bf16 scales out), as one launch."""
     s = None if signs is None else signs
     stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
-    check(lib().ctb_rotate_quantize_int4_batch(table, i32(len(table)), ptr(s), i32(DT[precision]), stream))
+    check(lib().ctb_rotate_quantize_int4_batch(table, i32(len(table)), ptr(s), i32(_precision_code(precision)), ptr(status), stream))
 
 
 def unpack_dequantize_int4_batch(table, device=None):

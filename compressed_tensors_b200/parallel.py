@@ -87,6 +87,8 @@ class ShardCodec:
         self._graphs: Dict[str, torch.cuda.CUDAGraph] = {}
         self.use_graphs = use_graphs
         self.batch = batch
+        # set to CTB_ETIMEOUT by the tensor-core kernel if one of its bounded waits gives up
+        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
 
     # ------------------------------------------------------------------ launches
     def _allocate(self) -> None:
@@ -111,7 +113,7 @@ class ShardCodec:
     def _compress(self) -> None:
         if self.batched:
             self._allocate()
-            self.ops.rotate_quantize_int4_batch(self._ctable, self.signs, self.precision, self.weights[0].device)
+            self.ops.rotate_quantize_int4_batch(self._ctable, self.signs, self.precision, self.weights[0].device, self.status)
             return
         for i, w in enumerate(self.weights):
             self.packed[i], self.scales[i] = self.ops.absmax_quantize(

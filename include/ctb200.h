@@ -49,6 +49,11 @@ typedef enum ctb_dtype {
 
 typedef enum ctb_qtype { CTB_QINT = 0, CTB_QFLOAT = 1 } ctb_qtype;
 
+/* Third value of the `precision` argument of the rotation entry points (besides CTB_F64 and CTB_F32):
+ * run the block-128 rotation on the tensor cores (tcgen05, bf16 operands, fp32 accumulators in TMEM).
+ * Needs n = 128, bf16, forward, and tensors that are whole tiles of 128 x 128 elements. */
+#define CTB_ROT_TENSOR 100
+
 /* What a quantize / dequantize call stores or loads on the quantized side. */
 typedef enum ctb_codec {
     CTB_CODE_DTYPE = 0,  /* one element per value in `q_dtype` (a float dtype, I8 or E4M3) */
@@ -231,8 +236,10 @@ typedef struct ctb_tensor_ref {
 } ctb_tensor_ref;
 
 /* ctb_absmax_quantize(hadamard_n = 128, group 128, PACK32) for every tensor of the table. */
+/* device_status (device int32, may be NULL) receives CTB_ETIMEOUT if a bounded wait inside the tensor-core
+ * kernel gives up; it is left untouched otherwise. */
 int ctb_rotate_quantize_int4_batch(const ctb_tensor_ref *tensors, int32_t count, const int8_t *signs,
-                                   int32_t precision, void *stream);
+                                   int32_t precision, int32_t *device_status, void *stream);
 /* ctb_dequantize(codec PACK32, num_bits 4, group 128, bf16 scale, no zero point) for every tensor. */
 int ctb_unpack_dequantize_int4_batch(const ctb_tensor_ref *tensors, int32_t count, void *stream);
 

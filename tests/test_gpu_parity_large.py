@@ -80,16 +80,18 @@ def test_rotate_quantize_exact_mode_matches_oracle(ops, orc):
     assert_bit_equal(gw.cpu(), words, "packed words")
 
 
-def test_rotate_quantize_fast_mode_staged(ops, orc):
-    """float32-accumulated rotation (the fast mode).  Stage 1: rotated weights within the stated tolerance of
-    the float64 result (norm-wise rel-err <= 1e-3, all but a few parts per million identical, none off by more
-    than 4 bf16 steps).  Stage 2: the fused kernel equals the ORACLE's calibrate+quantize+pack applied to that
-    rotated tensor, bit for bit."""
+@pytest.mark.parametrize("mode", ["float32", "tensor"])
+def test_rotate_quantize_fast_modes_staged(ops, orc, mode):
+    """fp32-accumulated rotation: the float32 butterfly and the tcgen05 tensor-core GEMM (bf16 operands, fp32
+    accumulators in TMEM).  Stage 1: rotated weights within the stated tolerance of the float64 result (norm-wise
+    rel-err <= 1e-3, all but a few parts per million identical, none off by more than 4 bf16 steps).  Stage 2: the
+    fused kernel equals the ORACLE's calibrate+quantize+pack applied to that rotated tensor, bit for bit."""
     from tests.helpers import bf16_ulp_distance
 
+    precision = torch.float32 if mode == "float32" else ops.ROT_TENSOR
     w, sg = weights(512, 4096, seed=2), signs128(2)
     exact = orc.hadamard(w, 128, signs=sg)
-    fast = ops.hadamard(w.cuda(), 128, signs=sg.cuda(), precision=torch.float32).cpu()
+    fast = ops.hadamard(w.cuda(), 128, signs=sg.cuda(), precision=precision).cpu()
     err = (fast.double() - exact.double()).norm() / exact.double().norm()
     assert err <= 1e-3, float(err)
     differ = (fast.view(torch.int16) != exact.view(torch.int16)).sum().item()
@@ -97,9 +99,29 @@ def test_rotate_quantize_fast_mode_staged(ops, orc):
     assert bf16_ulp_distance(fast, exact) <= 4
     scale, words, _ = oracle_w4(orc, fast)
     gw, gs = ops.absmax_quantize(w.cuda(), qtype=ops.QINT, bits=4, col_group=128, codec="pack32", hadamard_n=128,
-                                 signs=sg.cuda(), precision=torch.float32)
+                                 signs=sg.cuda(), precision=precision)
     assert_bit_equal(gs.cpu(), scale, "scales from our rotated tensor")
     assert_bit_equal(gw.cpu(), words, "packed words from our rotated tensor")
+
+
+def test_tensor_core_path_batch_and_limits(ops, orc):
+    """The tcgen05 path over a table of tensors (one tensor map spanning all of them) equals its own single-tensor
+    calls; shapes that are not whole 128 x 128 tiles are refused; the device status word stays clear."""
+    from compressed_tensors_b200.parallel import ShardCodec
+
+    sg = signs128(6).cuda()
+    ws = [weights(r, c, seed=40 + i).cuda() for i, (r, c) in enumerate([(128, 128), (1024, 4096), (32, 512), (512, 14336)])]
+    codec = ShardCodec(ws, signs=sg, precision=ops.ROT_TENSOR)
+    codec.compress(), codec.decompress()
+    torch.cuda.synchronize()
+    assert int(codec.status.item()) == 0
+    for i, w in enumerate(ws):
+        gw, gs = ops.absmax_quantize(w, qtype=ops.QINT, bits=4, col_group=128, codec="pack32", hadamard_n=128, signs=sg,
+                                     precision=ops.ROT_TENSOR)
+        assert_bit_equal(codec.packed[i].cpu(), gw.cpu(), f"words {i}")
+        assert_bit_equal(codec.scales[i].cpu(), gs.cpu(), f"scales {i}")
+    with pytest.raises(NotImplementedError):
+        ops.hadamard(weights(3, 128).cuda(), 128, signs=sg, precision=ops.ROT_TENSOR)
 
 
 def test_fp8_channel_and_token_match_oracle(ops, orc):
