@@ -255,7 +255,7 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--precision", default="f64", choices=["f64", "f32", "tc"],
+    ap.add_argument("--precision", default="tc", choices=["f64", "f32", "tc"],
                     help="Hadamard rotation: float64 butterfly (bit-identical to the reference), float32 butterfly, or tcgen05 tensor cores with fp32 accumulators")
     ap.add_argument("--layers", type=int, default=32, help="decoder layers of the model (32 = Llama-3-8B)")
     ap.add_argument("--no-graphs", action="store_true")
@@ -263,6 +263,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-per-config", action="store_true", help="skip the C1-C4 per-scheme table")
+    ap.add_argument("--no-other-modes", action="store_true", help="skip timing the other rotation arithmetics")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
@@ -371,7 +372,8 @@ def main():
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": WORKLOAD, "layers": args.layers, "tensors_per_rank": len(weights), "partition": f"layers/{world}",
-                       "hadamard_accumulate": args.precision, "l2": "inputs larger than L2 (no flush needed)",
+                       "hadamard_accumulate": {"f64": "float64 butterfly (bit-identical to the reference)", "f32": "float32 butterfly",
+                                               "tc": "tcgen05 bf16 x bf16 -> fp32 in TMEM"}[args.precision], "l2": "inputs larger than L2 (no flush needed)",
                        "cuda_graphs": codec.use_graphs, "one_grid_per_shard": codec.batched},
             "compress_gbs": 2 * total_elems / (tc / args.steps) / 1e9, "decompress_gbs": 2 * total_elems / (td / args.steps) / 1e9,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
@@ -379,6 +381,19 @@ def main():
                          "decompress_frac": ALG_BYTES_PER_ELEM * rank_elems / (td / args.steps) / 1e9 / peak},
             "clocks": clocks, "gpu_launches": int(launches), "e2e": e2e,
         }
+        if world == 1 and not args.no_other_modes:
+            # the same compress pass with the other two rotation arithmetics, for the record
+            modes = {}
+            for tag, prec in (("f64", torch.float64), ("f32", torch.float32), ("tc", ops.ROT_TENSOR)):
+                if tag == args.precision:
+                    continue
+                alt = parallel.ShardCodec(weights, group_size=128, hadamard_n=128, signs=signs, precision=prec, use_graphs=False)
+                alt.compress()
+                torch.cuda.synchronize()
+                ta = time_region(alt.compress, 3, stream) / 3
+                modes[tag] = {"compress_gbs": round(2 * total_elems / ta / 1e9, 1), "frac": round(ALG_BYTES_PER_ELEM * total_elems / ta / 1e9 / peak, 3)}
+                del alt
+            out["other_rotation_modes"] = modes
         if world == 1 and not args.no_per_config:
             del codec, weights
             torch.cuda.empty_cache()
