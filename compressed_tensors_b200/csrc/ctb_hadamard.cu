@@ -172,14 +172,15 @@ namespace ctb {
 template <int M, int QK>
 __device__ __forceinline__ float group_scale(float amax, const float *gs, float half_range, void *out_scale, int64_t gi, bool writer) {
     if constexpr (QK == QK_FP4) {
-        float sc = __ldg(gs) * round_to<M>(__fdiv_rn(amax, 6.0f));
+        const float g = __ldg(gs);
+        float sc = g * round_to<M>(div_by_rcp(amax, 6.0f, 0.16666667163372040f));  // RN(1/6); the quotient is correctly rounded
         sc = clamp_nan(sc, -448.0f, 448.0f);
         uint8_t b = f32_to_e4m3(sc);
         if ((b & 0x7F) == 0) b = 0x20;  // zero scale -> 0.125
         if (writer) ((uint8_t *)out_scale)[gi] = b;
-        return __fdiv_rn(e4m3_to_f32(b), __ldg(gs));  // forward.py:468-469
+        return __fdiv_rn(e4m3_to_f32(b), g);  // forward.py:468-469
     } else {
-        float sc = fmaxf(round_to<M>(__fdiv_rn(amax, half_range)), 1.1920928955078125e-07f);
+        float sc = fmaxf(round_to<M>(div_by_rcp(amax, half_range, __frcp_rn(half_range))), 1.1920928955078125e-07f);
         if (writer) store_f32(out_scale, M, gi, sc);
         return sc;
     }
@@ -191,37 +192,89 @@ template <typename A, bool ROT, int XF, int QK, int FOUT>
 __global__ void __launch_bounds__(kThreads) absmax_quant_group_kernel(const HArgs a) {
     constexpr int M = XF == F_BF16 ? CTB_BF16 : XF == F_F16 ? CTB_F16 : CTB_F32;
     constexpr int T = QK == QK_FP4 ? CTB_F32 : M;
-    const int64_t padded = (a.chunks + 31) & ~(int64_t)31;
-    for (int64_t c = (int64_t)blockIdx.x * kThreads + threadIdx.x; c < padded; c += (int64_t)gridDim.x * kThreads) {
-        float v[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        const bool live = c < a.chunks;
-        if (live) {
-            Raw8 r = load_raw<XF>(a.x, c);
-            decode8<XF>(r, v);
+    constexpr int U = ROT ? 1 : 4;  // chunks in flight per thread
+    const int64_t padded = (a.chunks + 31) & ~(int64_t)31;  // whole warps stay in the loop for the shuffles
+    const int64_t stride = (int64_t)gridDim.x * kThreads * U;
+    for (int64_t base = (int64_t)blockIdx.x * kThreads * U + threadIdx.x; base - threadIdx.x + (threadIdx.x & ~31) < padded; base += stride) {
+        Raw8 raw[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int64_t c = base + (int64_t)u * kThreads;
+            if (c < a.chunks) raw[u] = load_raw<XF>(a.x, c);
         }
-        if constexpr (ROT) rotate8<A, XF>(a, c, v);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int64_t c = base + (int64_t)u * kThreads;
+            const bool live = c < a.chunks;
+            float v[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            if (live) decode8<XF>(raw[u], v);
+            if constexpr (ROT) rotate8<A, XF>(a, c, v);
+            float amax = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+            for (int o = a.GL >> 1; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+            QP q;
+            q.s = group_scale<M, QK>(amax, a.gs, a.half_range, a.out_scale, c / a.GL, live && (c & (a.GL - 1)) == 0);
+            q.r = __frcp_rn(q.s);
+            q.zp = 0.0f;
+            q.slow = !(fabsf(q.s) >= 1.0e-30f && fabsf(q.s) <= 1.0e30f);
+            if constexpr (QK == QK_INT && FOUT == F_PACK4 && XF == F_BF16) {
+                if (!q.slow) {  // v[] hold bf16 values exactly, so re-packing them is lossless
+                    uint32_t w[4];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) w[k] = bf162_as_u32(__floats2bfloat162_rn(v[2 * k], v[2 * k + 1]));
+                    if (live) st_stream4((char *)a.out + c * 4, quant_int4_word_bf16(w, q.r, false, __float2bfloat162_rn(0.0f)));
+                    continue;
+                }
+            }
+            // the zero point calculate_qparams returns is all zeros; adding it matters only for the sign of an
+            // fp8 zero (-0.0 + 0.0 = +0.0)
+            quant_prepare8<T>(v, q, QK == QK_FP8, 0.0f, a.qmin, a.qmax);
+            if (live) encode_store8<QK, FOUT>(a.out, c, v);
+        }
+    }
+}
+
+// one warp per row, the whole row in registers (CHANNEL / TOKEN with cols <= 8 * 32 * CPL): a single pass with
+// no shared memory and no block barrier.  CPL = 16-byte chunks per lane.
+template <int CPL, int XF, int QK, int FOUT>
+__global__ void __launch_bounds__(kThreads) absmax_quant_warprow_kernel(const HArgs a, int64_t rows, int cpr) {
+    constexpr int M = XF == F_BF16 ? CTB_BF16 : XF == F_F16 ? CTB_F16 : CTB_F32;
+    const int lane = threadIdx.x & 31;
+    const int64_t warps = (int64_t)gridDim.x * (kThreads / 32);
+    for (int64_t r = (int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5); r < rows; r += warps) {
+        Raw8 raw[CPL];
+#pragma unroll
+        for (int k = 0; k < CPL; ++k) {
+            const int c = k * 32 + lane;
+            if (c < cpr) raw[k] = load_raw<XF>(a.x, r * cpr + c);
+        }
         float amax = 0.0f;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
-        for (int o = a.GL >> 1; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+        for (int k = 0; k < CPL; ++k) {
+            if (k * 32 + lane < cpr) {
+                float v[8];
+                decode8<XF>(raw[k], v);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+            }
+        }
+        for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
         QP q;
-        q.s = group_scale<M, QK>(amax, a.gs, a.half_range, a.out_scale, c / a.GL, live && (c & (a.GL - 1)) == 0);
+        q.s = group_scale<M, QK>(amax, a.gs, a.half_range, a.out_scale, r, lane == 0);
         q.r = __frcp_rn(q.s);
         q.zp = 0.0f;
         q.slow = !(fabsf(q.s) >= 1.0e-30f && fabsf(q.s) <= 1.0e30f);
-        // the zero point calculate_qparams returns is all zeros; adding it matters only for the sign of an
-        // fp8 zero (-0.0 + 0.0 = +0.0)
-        if constexpr (QK == QK_INT && FOUT == F_PACK4 && XF == F_BF16) {
-            if (!q.slow) {  // v[] hold bf16 values exactly, so re-packing them is lossless
-                uint32_t w[4];
 #pragma unroll
-                for (int k = 0; k < 4; ++k) w[k] = bf162_as_u32(__floats2bfloat162_rn(v[2 * k], v[2 * k + 1]));
-                if (live) st_stream4((char *)a.out + c * 4, quant_int4_word_bf16(w, q.r, false, __float2bfloat162_rn(0.0f)));
-                continue;
+        for (int k = 0; k < CPL; ++k) {
+            const int c = k * 32 + lane;
+            if (c < cpr) {
+                float v[8];
+                decode8<XF>(raw[k], v);
+                quant_prepare8<M>(v, q, QK == QK_FP8, 0.0f, a.qmin, a.qmax);
+                encode_store8<QK, FOUT>(a.out, r * cpr + c, v);
             }
         }
-        quant_prepare8<T>(v, q, QK == QK_FP8, 0.0f, a.qmin, a.qmax);
-        if (live) encode_store8<QK, FOUT>(a.out, c, v);
     }
 }
 
@@ -404,7 +457,7 @@ extern "C" int ctb_absmax_quantize(const ctb_qdesc *d, const void *x, const floa
     }
     if (pow2(GL) && GL <= 32 && d->scale_row_stride == d->cols / d->col_group) {
         a.GL = (int)GL;
-        int grid = grid_for(a.chunks, kThreads, 8);
+        int grid = grid_for(a.chunks, kThreads * 4, 8);
 #define CTB_AQ(QK_, FOUT_) absmax_quant_group_kernel<float, false, F_BF16, QK_, FOUT_><<<grid, kThreads, 0, st>>>(a)
         if (fout == F_PACK4) CTB_AQ(QK_INT, F_PACK4);
         else if (fout == F_PACK8) CTB_AQ(QK_INT, F_PACK8);
@@ -414,8 +467,16 @@ extern "C" int ctb_absmax_quantize(const ctb_qdesc *d, const void *x, const floa
         return after_launch("absmax_quant_group_kernel");
     }
     if (d->col_group == d->cols && d->scale_row_stride == 1 && qk != QK_FP4) {
-        int grid = grid_for(d->rows, 1, 8);
         const int64_t cpr = d->cols / 8;
+        if (cpr <= 32 * 32 && (fout == F_E4M3 || fout == F_I8)) {
+            int wgrid = grid_for(d->rows, kThreads / 32, cpr <= 512 ? 4 : 2);
+#define CTB_WR(CPL_)                                                                                                              \
+    if (fout == F_E4M3) absmax_quant_warprow_kernel<CPL_, F_BF16, QK_FP8, F_E4M3><<<wgrid, kThreads, 0, st>>>(a, d->rows, (int)cpr); \
+    else absmax_quant_warprow_kernel<CPL_, F_BF16, QK_INT, F_I8><<<wgrid, kThreads, 0, st>>>(a, d->rows, (int)cpr);
+            if (cpr <= 128) { CTB_WR(4) } else if (cpr <= 256) { CTB_WR(8) } else if (cpr <= 512) { CTB_WR(16) } else { CTB_WR(32) }
+            return after_launch("absmax_quant_warprow_kernel");
+        }
+        int grid = grid_for(d->rows, 1, 8);
         if (fout == F_E4M3) absmax_quant_row_kernel<F_BF16, QK_FP8, F_E4M3><<<grid, kThreads, 0, st>>>(a, d->rows, cpr);
         else if (fout == F_I8) absmax_quant_row_kernel<F_BF16, QK_INT, F_I8><<<grid, kThreads, 0, st>>>(a, d->rows, cpr);
         else if (fout == F_PACK8) absmax_quant_row_kernel<F_BF16, QK_INT, F_PACK8><<<grid, kThreads, 0, st>>>(a, d->rows, cpr);

@@ -361,50 +361,56 @@ constexpr int kDQBatchMax = 256;
 
 struct DQBatch {
     int count;
-    int64_t start[kDQBatchMax + 1];  // first global chunk (8 elements) of each tensor; start[count] = total
-    const void *in[kDQBatchMax];     // packed words
-    const void *scale[kDQBatchMax];  // bf16, one per 16 chunks
-    void *out[kDQBatchMax];          // bf16
+    int64_t ustart[kDQBatchMax + 1];  // first global unit of each tensor (unit = 1024 chunks = 8192 elements); ustart[count] = total
+    int64_t nchunks[kDQBatchMax];     // chunks (8 elements) of each tensor
+    const void *in[kDQBatchMax];      // packed words
+    const void *scale[kDQBatchMax];   // bf16, one per 16 chunks
+    void *out[kDQBatchMax];           // bf16
 };
 
-// One launch for every tensor of the table: the chunks of all tensors form one index space and the grid
-// strides over it; the next round's words and scales are loaded before the current round is written.
+constexpr int kDQUnit = kThreads * kUnroll;  // chunks per block-iteration
+
+// One launch for every tensor of the table.  The units of all tensors form one index space that the grid strides
+// over; the tensor lookup happens once per unit (uniform across the block), addressing inside a unit is 32-bit,
+// and the next unit's words and scales are loaded before the current unit is written.
 __global__ void __launch_bounds__(kThreads) dequant_int4_batch_kernel(const __grid_constant__ DQBatch B) {
-    const int64_t total = B.start[B.count];
-    const int64_t stride = (int64_t)gridDim.x * kThreads * kUnroll;
-    int64_t g = (int64_t)blockIdx.x * kThreads * kUnroll + threadIdx.x;
+    const int64_t total = B.ustart[B.count];
     int t = 0;
     uint32_t word[kUnroll], sbits[kUnroll];
-    char *optr[kUnroll];
-    auto fetch = [&](int64_t base) {
-        int ti = t;
+    bool ok[kUnroll];
+    char *obase = nullptr;
+    auto fetch = [&](int64_t unit) {
+        while (t + 1 < B.count && unit >= B.ustart[t + 1]) ++t;
+        const int64_t cbase = (unit - B.ustart[t]) * kDQUnit;
+        const uint32_t left = (uint32_t)min((int64_t)kDQUnit, B.nchunks[t] - cbase);
+        const char *ip = (const char *)B.in[t] + cbase * 4;
+        const unsigned short *sp = (const unsigned short *)B.scale[t] + (cbase >> 4);
+        obase = (char *)B.out[t] + cbase * 16;
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
-            const int64_t gi = base + (int64_t)u * kThreads;
-            optr[u] = nullptr;
-            if (gi < total) {
-                while (ti + 1 < B.count && gi >= B.start[ti + 1]) ++ti;
-                if (u == 0) t = ti;  // the thread's next round starts no earlier than this tensor
-                const int64_t c = gi - B.start[ti];
-                word[u] = ld_stream4((const char *)B.in[ti] + c * 4);
-                sbits[u] = __ldg((const unsigned short *)B.scale[ti] + (c >> 4));
-                optr[u] = (char *)B.out[ti] + c * 16;
+            const uint32_t c = u * kThreads + threadIdx.x;
+            ok[u] = c < left;
+            if (ok[u]) {
+                word[u] = ld_stream4(ip + c * 4);
+                sbits[u] = __ldg(sp + (c >> 4));
             }
         }
     };
-    if (g < total) fetch(g);
+    int64_t unit = blockIdx.x;
+    if (unit < total) fetch(unit);
     const __nv_bfloat162 bias = __float2bfloat162_rn(136.0f);
-    while (g < total) {
+    while (unit < total) {
         uint32_t w[kUnroll], s[kUnroll];
-        char *o[kUnroll];
+        bool k[kUnroll];
+        char *o = obase;
 #pragma unroll
-        for (int u = 0; u < kUnroll; ++u) { w[u] = word[u]; s[u] = sbits[u]; o[u] = optr[u]; }
-        const int64_t gn = g + stride;
-        if (gn < total) fetch(gn);
+        for (int u = 0; u < kUnroll; ++u) { w[u] = word[u]; s[u] = sbits[u]; k[u] = ok[u]; }
+        const int64_t next = unit + gridDim.x;
+        if (next < total) fetch(next);
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u)
-            if (o[u] != nullptr) st_stream(o[u], dequant_int4_word_bf16(w[u], u32_as_bf162(s[u] | (s[u] << 16)), bias));
-        g = gn;
+            if (k[u]) st_stream(o + (uint32_t)(u * kThreads + threadIdx.x) * 16, dequant_int4_word_bf16(w[u], u32_as_bf162(s[u] | (s[u] << 16)), bias));
+        unit = next;
     }
 }
 
@@ -422,16 +428,17 @@ extern "C" int ctb_unpack_dequantize_int4_batch(const ctb_tensor_ref *tensors, i
             if (!t.in || !t.out || !t.scale) return fail(CTB_EINVAL_NULL, "tensor %d has a null buffer", base + i);
             if (t.rows < 0 || t.cols <= 0 || t.cols % 128) return fail(CTB_EINVAL_SHAPE, "tensor %d: columns %lld are not a multiple of 128", base + i, (long long)t.cols);
             if (!aligned16(t.out) || (reinterpret_cast<uintptr_t>(t.in) & 3u)) return fail(CTB_EINVAL_ALIGN, "tensor %d is misaligned", base + i);
-            B.start[i] = g;
+            B.ustart[i] = g;
+            B.nchunks[i] = t.rows * t.cols / 8;
             B.in[i] = t.in;
             B.scale[i] = t.scale;
             B.out[i] = t.out;
-            g += t.rows * t.cols / 8;
+            g += cdiv(B.nchunks[i], kDQUnit);
         }
         B.count = n;
-        B.start[n] = g;
+        B.ustart[n] = g;
         if (g == 0) continue;
-        int grid = grid_for(g, (int64_t)kThreads * kUnroll, 8);
+        int grid = grid_for(g, 1, 8);
         dequant_int4_batch_kernel<<<grid, kThreads, 0, as_stream(stream)>>>(B);
         int rc = after_launch("dequant_int4_batch_kernel");
         if (rc) return rc;
