@@ -290,6 +290,33 @@ __device__ __forceinline__ uint4 dequant_int4_word_bf16(uint32_t word, __nv_bflo
     return make_uint4(p[0], p[1], p[2], p[3]);
 }
 
+// 8 bf16 inputs (4 packed words) -> 8 e4m3 codes, compute dtype bf16 (bf16 tensor, bf16 scale):
+//   q = bf16_rn(x * rcp(s)) + 0  (the all-zero zero point of a symmetric scheme turns -0.0 into +0.0; folded
+//   into the multiply as fma(x, r, +0.0)), then the saturating round-to-nearest-even e4m3 convert, which
+//   equals the reference's clamp to +-448 followed by Tensor.to(float8_e4m3fn) for every non-NaN input.
+__device__ __forceinline__ uint2 quant_fp8_codes_bf16(const uint32_t (&w)[4], float r) {
+    uint32_t c[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float f0 = __uint_as_float(w[k] << 16), f1 = __uint_as_float(w[k] & 0xFFFF0000u);
+        const uint32_t q = bf162_as_u32(__floats2bfloat162_rn(fmaf(f0, r, 0.0f), fmaf(f1, r, 0.0f)));
+        c[k] = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(__uint_as_float(q << 16), __uint_as_float(q & 0xFFFF0000u)),
+                                                  __NV_SATFINITE, __NV_E4M3);
+    }
+    return make_uint2(c[0] | (c[1] << 16), c[2] | (c[3] << 16));
+}
+
+// 8 values exactly representable in the scale's compute dtype (int8 / e4m3 / e2m1 codes), no zero point:
+// value * scale rounded once to bf16 -- what (x_q.to(scale.dtype) * scale).to(bf16) gives for a bf16 scale,
+// and, with an fp32 effective scale, the fp32 product rounded to bf16 (NVFP4 decompress).
+template <bool F32_PRODUCT>
+__device__ __forceinline__ uint4 dequant8_to_bf16(const float (&v)[8], float s) {
+    uint32_t p[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) p[k] = bf162_as_u32(__floats2bfloat162_rn(v[2 * k] * s, v[2 * k + 1] * s));
+    return make_uint4(p[0], p[1], p[2], p[3]);
+}
+
 // qparam for a chunk, as fp32
 struct QP {
     float s;   // effective scale (scale or scale / global_scale)

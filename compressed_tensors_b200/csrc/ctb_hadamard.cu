@@ -200,6 +200,7 @@ __global__ void __launch_bounds__(kThreads) absmax_quant_group_kernel(const HArg
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const int64_t c = base + (int64_t)u * kThreads;
+            raw[u].a = make_uint4(0, 0, 0, 0);
             if (c < a.chunks) raw[u] = load_raw<XF>(a.x, c);
         }
 #pragma unroll
@@ -218,12 +219,20 @@ __global__ void __launch_bounds__(kThreads) absmax_quant_group_kernel(const HArg
             q.r = __frcp_rn(q.s);
             q.zp = 0.0f;
             q.slow = !(fabsf(q.s) >= 1.0e-30f && fabsf(q.s) <= 1.0e30f);
-            if constexpr (QK == QK_INT && FOUT == F_PACK4 && XF == F_BF16) {
-                if (!q.slow) {  // v[] hold bf16 values exactly, so re-packing them is lossless
+            if constexpr (XF == F_BF16 && ((QK == QK_INT && FOUT == F_PACK4) || (QK == QK_FP8 && FOUT == F_E4M3))) {
+                if (!q.slow) {
                     uint32_t w[4];
+                    if constexpr (ROT) {  // v[] hold bf16 values exactly, so re-packing them is lossless
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) w[k] = bf162_as_u32(__floats2bfloat162_rn(v[2 * k], v[2 * k + 1]));
-                    if (live) st_stream4((char *)a.out + c * 4, quant_int4_word_bf16(w, q.r, false, __float2bfloat162_rn(0.0f)));
+                        for (int k = 0; k < 4; ++k) w[k] = bf162_as_u32(__floats2bfloat162_rn(v[2 * k], v[2 * k + 1]));
+                    } else {
+                        w[0] = raw[u].a.x; w[1] = raw[u].a.y; w[2] = raw[u].a.z; w[3] = raw[u].a.w;
+                    }
+                    if constexpr (QK == QK_INT) {
+                        if (live) st_stream4((char *)a.out + c * 4, quant_int4_word_bf16(w, q.r, false, __float2bfloat162_rn(0.0f)));
+                    } else {
+                        if (live) st_stream8((char *)a.out + c * 8, quant_fp8_codes_bf16(w, q.r));
+                    }
                     continue;
                 }
             }
@@ -269,6 +278,13 @@ __global__ void __launch_bounds__(kThreads) absmax_quant_warprow_kernel(const HA
         for (int k = 0; k < CPL; ++k) {
             const int c = k * 32 + lane;
             if (c < cpr) {
+                if constexpr (QK == QK_FP8 && XF == F_BF16 && FOUT == F_E4M3) {
+                    if (!q.slow) {
+                        const uint32_t w[4] = {raw[k].a.x, raw[k].a.y, raw[k].a.z, raw[k].a.w};
+                        st_stream8((char *)a.out + (r * cpr + c) * 8, quant_fp8_codes_bf16(w, q.r));
+                        continue;
+                    }
+                }
                 float v[8];
                 decode8<XF>(raw[k], v);
                 quant_prepare8<M>(v, q, QK == QK_FP8, 0.0f, a.qmin, a.qmax);
@@ -309,6 +325,13 @@ __global__ void __launch_bounds__(kThreads) absmax_quant_row_kernel(const HArgs 
         q.slow = !(fabsf(q.s) >= 1.0e-30f && fabsf(q.s) <= 1.0e30f);
         for (int64_t c = threadIdx.x; c < cpr; c += kThreads) {
             Raw8 raw = load_raw<XF>(a.x, r * cpr + c);
+            if constexpr (QK == QK_FP8 && XF == F_BF16 && FOUT == F_E4M3) {
+                if (!q.slow) {
+                    const uint32_t w[4] = {raw.a.x, raw.a.y, raw.a.z, raw.a.w};
+                    st_stream8((char *)a.out + (r * cpr + c) * 8, quant_fp8_codes_bf16(w, q.r));
+                    continue;
+                }
+            }
             float v[8];
             decode8<XF>(raw, v);
             quant_prepare8<M>(v, q, QK == QK_FP8, 0.0f, a.qmin, a.qmax);

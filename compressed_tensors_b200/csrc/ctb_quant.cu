@@ -72,8 +72,24 @@ __global__ void __launch_bounds__(kThreads) qdq_vec8_kernel(const QArgs a) {
                     continue;
                 }
             }
+            if constexpr (MODE == 0 && FIN == F_BF16 && FOUT == F_E4M3 && T == CTB_BF16 && QK == QK_FP8) {
+                // symmetric schemes (no zero point, or the all-zero one calculate_qparams returns for them)
+                if (!q.slow && (!has_zp || q.zp == 0.0f)) {
+                    const uint32_t w[4] = {raw[u].a.x, raw[u].a.y, raw[u].a.z, raw[u].a.w};
+                    if (has_zp) {
+                        st_stream8((char *)a.out + c * 8, quant_fp8_codes_bf16(w, q.r));
+                        continue;
+                    }
+                }
+            }
             float v[8];
             decode8<FIN>(raw[u], v);
+            if constexpr (MODE == 1 && FOUT == F_BF16 && (FIN == F_E4M3 || FIN == F_I8 || FIN == F_PACK8 || FIN == F_FP4X2)) {
+                if (!has_zp) {  // codes are exact in the compute dtype: one multiply, one rounding to bf16
+                    st_stream((char *)a.out + c * 16, dequant8_to_bf16<TS == CTB_F32>(v, q.s));
+                    continue;
+                }
+            }
             if constexpr (MODE == 0) {
                 quant_prepare8<T>(v, q, has_zp, q.zp, a.qmin, a.qmax);
                 encode_store8<QK, FOUT>(a.out, c, v);
