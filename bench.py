@@ -238,7 +238,7 @@ def per_config_table(dev, peak):
         return (q,)
     run("c4a_sparse24_compress_e4m3", s24, lambda q: ops.sparse24_compress(q), 2 * ns, 1.625 * ns, 1.7 * ns)
     run("c4a_sparse24_decompress_e4m3", lambda: ops.sparse24_compress(s24()[0]),
-        lambda v, b: ops.bitmask_decompress(v, b, (4096, 11008)), 2 * ns, 1.625 * ns, 1.7 * ns)
+        lambda v, b: ops.sparse24_decompress(v, b, (4096, 11008)), 2 * ns, 1.625 * ns, 1.7 * ns)
     def unstructured():
         w = rnd(4096, 4096)
         w[torch.rand(4096, 4096, generator=g, device=dev) < 0.5] = 0

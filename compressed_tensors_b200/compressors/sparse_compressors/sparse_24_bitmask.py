@@ -38,7 +38,7 @@ def sparse24_bitmask_compress(tensor: Tensor, sparsity_structure: Union[Sparsity
 def sparse24_bitmask_decompress(values: Tensor, bitmasks: Tensor, original_shape: torch.Size) -> Tensor:
     """sparse_24_bitmask.py:206-224."""
     shape = [int(s) for s in original_shape]
-    return ops.bitmask_decompress(values.to(bitmasks.device), bitmasks, shape)
+    return ops.sparse24_decompress(values.to(bitmasks.device), bitmasks, shape)
 
 
 class Sparse24BitMaskTensor:

@@ -68,6 +68,7 @@ struct HArgs {
     int inverse;
     int normalize;    // divide by sqrt(n) (the reference's HadamardTransform) or leave the raw product
     int GL;           // lanes per quantization group = col_group / 8 (fused)
+    int gl_shift;     // log2(GL)
     int xdt;
     float qmin, qmax, half_range;
 };
@@ -215,7 +216,7 @@ __global__ void __launch_bounds__(kThreads) absmax_quant_group_kernel(const HArg
             for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
             for (int o = a.GL >> 1; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
             QP q;
-            q.s = group_scale<M, QK>(amax, a.gs, a.half_range, a.out_scale, c / a.GL, live && (c & (a.GL - 1)) == 0);
+            q.s = group_scale<M, QK>(amax, a.gs, a.half_range, a.out_scale, c >> a.gl_shift, live && (c & (a.GL - 1)) == 0);
             q.r = __frcp_rn(q.s);
             q.zp = 0.0f;
             q.slow = !(fabsf(q.s) >= 1.0e-30f && fabsf(q.s) <= 1.0e30f);
@@ -468,6 +469,8 @@ extern "C" int ctb_absmax_quantize(const ctb_qdesc *d, const void *x, const floa
         if (!(pow2(GL) && GL <= 32)) return fail(CTB_EUNSUPPORTED, "with a rotation in front the group must be a power of two <= 256");
         if (fout != F_PACK4) return fail(CTB_EUNSUPPORTED, "the fused rotation is built for int4 PACK32 output");
         a.GL = (int)GL;
+        a.gl_shift = 0;
+        while ((1 << a.gl_shift) < a.GL) ++a.gl_shift;
         if (n == 128 && d->col_group == 128) {
             static thread_local RQBatch B;
             rq_single(B, x, out, out_scale, d->rows * d->cols / 128);
@@ -480,6 +483,8 @@ extern "C" int ctb_absmax_quantize(const ctb_qdesc *d, const void *x, const floa
     }
     if (pow2(GL) && GL <= 32 && d->scale_row_stride == d->cols / d->col_group) {
         a.GL = (int)GL;
+        a.gl_shift = 0;
+        while ((1 << a.gl_shift) < a.GL) ++a.gl_shift;
         int grid = grid_for(a.chunks, kThreads * 4, 8);
 #define CTB_AQ(QK_, FOUT_) absmax_quant_group_kernel<float, false, F_BF16, QK_, FOUT_><<<grid, kThreads, 0, st>>>(a)
         if (fout == F_PACK4) CTB_AQ(QK_INT, F_PACK4);

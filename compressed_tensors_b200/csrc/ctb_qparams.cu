@@ -49,8 +49,9 @@ __global__ void __launch_bounds__(kThreads) minmax_group_kernel(const void *x, i
         if (c < chunks) chunk_minmax<F>(x, c, mn, mx);
         warp_minmax(mn, mx, L);
         if (c < chunks && (c & (L - 1)) == 0) {
-            store_f32(out_min, dt, c / L, mn);
-            store_f32(out_max, dt, c / L, mx);
+            const int64_t gi = c >> (31 - __clz(L));  // L is a power of two
+            store_f32(out_min, dt, gi, mn);
+            store_f32(out_max, dt, gi, mx);
         }
     }
 }

@@ -10,9 +10,6 @@ namespace ctb {
 
 constexpr int kThreads = 256;
 
-__constant__ uint8_t c_lut24[256] = {
-#include "sparse24_lut.inc"
-};
 
 // element classes by storage size; `nz_mask` selects the bits that make an element non-zero
 // (sign bit excluded for float types so that -0.0 counts as zero, sparse_bitmask.py:137)
@@ -63,48 +60,49 @@ __device__ __forceinline__ void store_bits(void *x, int es, int64_t i, uint32_t 
 
 // sparse_24_bitmask.py:244-256: magnitude used for ranking.  Float types: |x| orders like its
 // magnitude bits.  int8 view (int8 / e4m3 tensors): torch's int8 abs, where abs(-128) wraps to -128.
-__device__ __forceinline__ int32_t rank_key(uint32_t bits, uint32_t nz_mask, int is_int8) {
-    if (is_int8) {
+template <bool IS_INT8>
+__device__ __forceinline__ int32_t rank_key(uint32_t bits, uint32_t nz_mask) {
+    if constexpr (IS_INT8) {
         int32_t v = (int32_t)(int8_t)bits;
         return (int32_t)(int8_t)(v < 0 ? -v : v);
+    } else {
+        return (int32_t)(bits & nz_mask);
     }
-    return (int32_t)(bits & nz_mask);
 }
 
-// keep-mask (4 bits) of one run of four magnitudes: the positions abs().topk(2) returns on CPU
-__device__ __forceinline__ uint32_t keep24(int32_t k0, int32_t k1, int32_t k2, int32_t k3, const uint8_t *lut) {
-    // c_i = how many of the other three are strictly smaller than k_i
-    uint32_t c0 = (k1 < k0) + (k2 < k0) + (k3 < k0);
-    uint32_t c1 = (k0 < k1) + (k2 < k1) + (k3 < k1);
-    uint32_t c2 = (k0 < k2) + (k1 < k2) + (k3 < k2);
-    uint32_t c3 = (k0 < k3) + (k1 < k3) + (k2 < k3);
-    return lut[c0 | (c1 << 2) | (c2 << 4) | (c3 << 6)];
-}
-
-__device__ __forceinline__ void stage_lut(uint8_t *s) {
-    for (int i = threadIdx.x; i < 256; i += blockDim.x) s[i] = c_lut24[i];
-    __syncthreads();
+// keep-mask (4 bits) of one run of four magnitudes: the positions abs().topk(2) returns on CPU.
+// torch's top-k breaks ties towards the higher index ("i beats j" below), with one family of exceptions
+// that comes from the partition step of std::nth_element: when element 0 is strictly the largest and the
+// second place is tied, the winner of the tie is fixed per tie set ({1,2}->1, {1,3}->1, {2,3}->2,
+// {1,2,3}->2).  The rule is checked against torch.topk on all 75 weak orderings of four values (tests/golden).
+__device__ __forceinline__ uint32_t keep24(int32_t k0, int32_t k1, int32_t k2, int32_t k3) {
+    const bool b01 = k0 > k1, b02 = k0 > k2, b03 = k0 > k3, b12 = k1 > k2, b13 = k1 > k3, b23 = k2 > k3;
+    const int w0 = b01 + b02 + b03, w1 = !b01 + b12 + b13, w2 = !b02 + !b12 + b23, w3 = !b03 + !b13 + !b23;
+    uint32_t m = (w0 >= 2 ? 1u : 0u) | (w1 >= 2 ? 2u : 0u) | (w2 >= 2 ? 4u : 0u) | (w3 >= 2 ? 8u : 0u);
+    if (b01 && b02 && b03) {
+        const int32_t mx = max(k1, max(k2, k3));
+        const uint32_t t = (k1 == mx ? 1u : 0u) | (k2 == mx ? 2u : 0u) | (k3 == mx ? 4u : 0u);
+        m = 1u | ((0x44282420u >> (4 * t)) & 0xFu);
+    }
+    return m;
 }
 
 // get_24_bytemasks on the flat view: one thread per run of 4
-__global__ void __launch_bounds__(kThreads) sparse24_mask_kernel(const void *x, int es, uint32_t nzm, int is_int8, int64_t groups, uint8_t *out) {
-    __shared__ uint8_t lut[256];
-    stage_lut(lut);
+template <bool IS_INT8>
+__global__ void __launch_bounds__(kThreads) sparse24_mask_kernel(const void *x, int es, uint32_t nzm, int64_t groups, uint8_t *out) {
     for (int64_t g = (int64_t)blockIdx.x * kThreads + threadIdx.x; g < groups; g += (int64_t)gridDim.x * kThreads) {
         int32_t k[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) k[j] = rank_key(load_bits(x, es, 4 * g + j), nzm, is_int8);
-        uint32_t m = keep24(k[0], k[1], k[2], k[3], lut);
+        for (int j = 0; j < 4; ++j) k[j] = rank_key<IS_INT8>(load_bits(x, es, 4 * g + j), nzm);
+        uint32_t m = keep24(k[0], k[1], k[2], k[3]);
         *reinterpret_cast<uint32_t *>(out + 4 * g) = (m & 1) | ((m >> 1 & 1) << 8) | ((m >> 2 & 1) << 16) | ((m >> 3 & 1) << 24);
     }
 }
 
 // sparse24_bitmask_compress, cols % 8 == 0: one thread per 8 elements = 2 runs = 4 kept values and
 // one bitmask byte; four neighbouring lanes merge their bytes into one 32-bit store.
-template <int ES>
-__global__ void __launch_bounds__(kThreads) sparse24_compress_kernel(const void *x, uint32_t nzm, int is_int8, int64_t units, void *values, uint8_t *bitmask) {
-    __shared__ uint8_t lut[256];
-    stage_lut(lut);
+template <int ES, bool IS_INT8>
+__global__ void __launch_bounds__(kThreads) sparse24_compress_kernel(const void *x, uint32_t nzm, int64_t units, void *values, uint8_t *bitmask) {
     const int64_t padded = (units + 31) & ~(int64_t)31;
     for (int64_t u = (int64_t)blockIdx.x * kThreads + threadIdx.x; u < padded; u += (int64_t)gridDim.x * kThreads) {
         uint32_t b[8] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -112,8 +110,8 @@ __global__ void __launch_bounds__(kThreads) sparse24_compress_kernel(const void 
         if (live) load8_bits<ES>(x, u, b);
         int32_t k[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) k[j] = rank_key(b[j], nzm, is_int8);
-        uint32_t m = keep24(k[0], k[1], k[2], k[3], lut) | (keep24(k[4], k[5], k[6], k[7], lut) << 4);
+        for (int j = 0; j < 8; ++j) k[j] = rank_key<IS_INT8>(b[j], nzm);
+        uint32_t m = keep24(k[0], k[1], k[2], k[3]) | (keep24(k[4], k[5], k[6], k[7]) << 4);
         // the four kept elements in column order: per run, the lower and the upper of its two set bits
         uint32_t kept[4];
 #pragma unroll
@@ -137,6 +135,48 @@ __global__ void __launch_bounds__(kThreads) sparse24_compress_kernel(const void 
                 for (int64_t t = u; t < units; ++t) bitmask[t] = (uint8_t)(w >> (8 * (t - u)));
         }
     }
+}
+
+// Fast expansion of a 2:4 compressed tensor (cols % 8 == 0): every run of four columns keeps exactly two, so
+// the values of byte u of the bitmask start at 4u and no prefix sum is needed.  A bitmask that breaks the
+// two-per-run rule raises *irregular; the generic kernels then redo the tensor (they are launched right
+// behind this one and return at once when the flag is clear).
+template <int ES>
+__global__ void __launch_bounds__(kThreads) sparse24_expand_kernel(const void *values, const uint8_t *bitmask, int64_t units, void *out, int *irregular) {
+    bool bad = false;
+    for (int64_t u = (int64_t)blockIdx.x * kThreads + threadIdx.x; u < units; u += (int64_t)gridDim.x * kThreads) {
+        const uint32_t m = bitmask[u];
+        bad |= (__popc(m & 0xFu) != 2) | (__popc(m >> 4) != 2);
+        uint32_t v[4];
+        if constexpr (ES == 2) {
+            uint2 t = ld_stream8((const char *)values + u * 8);
+            v[0] = t.x & 0xFFFFu; v[1] = t.x >> 16; v[2] = t.y & 0xFFFFu; v[3] = t.y >> 16;
+        } else if constexpr (ES == 1) {
+            uint32_t t = ld_stream4((const char *)values + u * 4);
+            v[0] = t & 0xFFu; v[1] = (t >> 8) & 0xFFu; v[2] = (t >> 16) & 0xFFu; v[3] = t >> 24;
+        } else {
+            uint4 t = ld_stream((const char *)values + u * 16);
+            v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+        }
+        uint32_t b[8];
+#pragma unroll
+        for (int g = 0; g < 2; ++g) {
+            const uint32_t mm = (m >> (4 * g)) & 0xFu;
+            const uint32_t lo = v[2 * g], hi = v[2 * g + 1];
+            // a kept position holds the run's first value if no lower bit is set, else the second
+            b[4 * g + 0] = (mm & 1) ? lo : 0u;
+            b[4 * g + 1] = (mm & 2) ? ((mm & 1) ? hi : lo) : 0u;
+            b[4 * g + 2] = (mm & 4) ? ((mm & 3) ? hi : lo) : 0u;
+            b[4 * g + 3] = (mm & 8) ? hi : 0u;
+        }
+        if constexpr (ES == 2) st_stream((char *)out + u * 16, make_uint4(b[0] | (b[1] << 16), b[2] | (b[3] << 16), b[4] | (b[5] << 16), b[6] | (b[7] << 16)));
+        else if constexpr (ES == 1) st_stream8((char *)out + u * 8, make_uint2(b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24), b[4] | (b[5] << 8) | (b[6] << 16) | (b[7] << 24)));
+        else {
+            st_stream((char *)out + u * 32, make_uint4(b[0], b[1], b[2], b[3]));
+            st_stream((char *)out + u * 32 + 16, make_uint4(b[4], b[5], b[6], b[7]));
+        }
+    }
+    if (__any_sync(0xFFFFFFFFu, bad) && (threadIdx.x & 31) == 0) atomicExch(irregular, 1);
 }
 
 }  // namespace ctb
@@ -224,7 +264,8 @@ __global__ void __launch_bounds__(kThreads) bm_count_kernel(const void *x, const
 }
 
 // per-row counts straight from a bitmask (decompress)
-__global__ void __launch_bounds__(kThreads) bm_popcount_kernel(const uint8_t *bitmask, int64_t rows, int64_t cols, int64_t *row_counts) {
+__global__ void __launch_bounds__(kThreads) bm_popcount_kernel(const uint8_t *bitmask, int64_t rows, int64_t cols, int64_t *row_counts, const int *gate) {
+    if (gate != nullptr && *gate == 0) return;  // the fast 2:4 expansion already produced the tensor
     const int64_t upr = (cols + 7) / 8;
     const int tail = (int)(cols & 7);
     for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
@@ -240,7 +281,8 @@ __global__ void __launch_bounds__(kThreads) bm_popcount_kernel(const uint8_t *bi
 }
 
 // pass 2: in-place exclusive scan of the row counts (single block), total to *nnz
-__global__ void __launch_bounds__(1024) row_scan_kernel(int64_t *counts, int64_t rows, int64_t *nnz) {
+__global__ void __launch_bounds__(1024) row_scan_kernel(int64_t *counts, int64_t rows, int64_t *nnz, const int *gate = nullptr) {
+    if (gate != nullptr && *gate == 0) return;
     __shared__ int64_t wsum[32];
     __shared__ int64_t carry_s;
     if (threadIdx.x == 0) carry_s = 0;
@@ -292,7 +334,9 @@ __global__ void __launch_bounds__(kThreads) bm_scatter_kernel(const void *x, con
 // decompress: zeros, then values scattered to the set bits.  One block per row; every thread owns
 // 8 output elements per round and writes them with one vector store when the row layout allows.
 template <int ES, bool VEC>
-__global__ void __launch_bounds__(kThreads) bm_expand_kernel(const void *values, const uint8_t *bitmask, int es, int64_t rows, int64_t cols, const int64_t *row_offsets, void *out) {
+__global__ void __launch_bounds__(kThreads) bm_expand_kernel(const void *values, const uint8_t *bitmask, int es, int64_t rows, int64_t cols, const int64_t *row_offsets, void *out,
+                                                               const int *gate) {
+    if (gate != nullptr && *gate == 0) return;
     const int64_t upr = (cols + 7) / 8;
     const int tail = (int)(cols & 7);
     for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
@@ -339,7 +383,9 @@ extern "C" int ctb_sparse24_mask(const void *x, int32_t dtype, int64_t numel, ui
     if (!elem_info(dtype, &e)) return fail(CTB_EINVAL_DTYPE, "unsupported dtype for 2:4 masks");
     if (numel % 4 != 0) return fail(CTB_EINVAL_SHAPE, "Tensor size must be a multiple of 4 for TWO_FOUR sparsity");
     if (numel == 0) return CTB_OK;
-    sparse24_mask_kernel<<<grid_for(numel / 4, kThreads, 8), kThreads, 0, as_stream(stream)>>>(x, e.esize, e.nz_mask, e.is_int8, numel / 4, out);
+    int grid = grid_for(numel / 4, kThreads, 8);
+    if (e.is_int8) sparse24_mask_kernel<true><<<grid, kThreads, 0, as_stream(stream)>>>(x, e.esize, e.nz_mask, numel / 4, out);
+    else sparse24_mask_kernel<false><<<grid, kThreads, 0, as_stream(stream)>>>(x, e.esize, e.nz_mask, numel / 4, out);
     return after_launch("sparse24_mask_kernel");
 }
 
@@ -354,9 +400,9 @@ extern "C" int ctb_sparse24_compress(const void *x, int32_t dtype, int64_t rows,
     if (units == 0) return CTB_OK;
     int grid = grid_for(units, kThreads, 8);
     cudaStream_t st = as_stream(stream);
-    if (e.esize == 2) sparse24_compress_kernel<2><<<grid, kThreads, 0, st>>>(x, e.nz_mask, e.is_int8, units, values, bitmask);
-    else if (e.esize == 1) sparse24_compress_kernel<1><<<grid, kThreads, 0, st>>>(x, e.nz_mask, e.is_int8, units, values, bitmask);
-    else sparse24_compress_kernel<4><<<grid, kThreads, 0, st>>>(x, e.nz_mask, e.is_int8, units, values, bitmask);
+    if (e.esize == 2) sparse24_compress_kernel<2, false><<<grid, kThreads, 0, st>>>(x, e.nz_mask, units, values, bitmask);
+    else if (e.esize == 1) sparse24_compress_kernel<1, true><<<grid, kThreads, 0, st>>>(x, e.nz_mask, units, values, bitmask);
+    else sparse24_compress_kernel<4, false><<<grid, kThreads, 0, st>>>(x, e.nz_mask, units, values, bitmask);
     return after_launch("sparse24_compress_kernel");
 }
 
@@ -399,8 +445,8 @@ extern "C" int ctb_masked_compress(const void *x, const uint8_t *bytemask, int32
     return compress_impl(x, bytemask, dtype, rows, cols, values, bitmask, row_offsets, nnz, stream);
 }
 
-extern "C" int ctb_bitmask_decompress(const void *values, const uint8_t *bitmask, int32_t dtype, int64_t rows, int64_t cols, void *out,
-                                      void *workspace, void *stream) {
+static int decompress_impl(const void *values, const uint8_t *bitmask, int32_t dtype, int64_t rows, int64_t cols, void *out, void *workspace,
+                           const int *gate, void *stream) {
     if (!bitmask || !out || !workspace) return fail(CTB_EINVAL_NULL, "null buffer");
     ElemInfo e;
     if (!elem_info(dtype, &e)) return fail(CTB_EINVAL_DTYPE, "unsupported dtype for bitmask decompression");
@@ -410,16 +456,44 @@ extern "C" int ctb_bitmask_decompress(const void *values, const uint8_t *bitmask
     int64_t *offs = (int64_t *)workspace;
     int grid = grid_for(rows, 1, 8);
     int rc;
-    bm_popcount_kernel<<<grid, kThreads, 0, st>>>(bitmask, rows, cols, offs);
+    bm_popcount_kernel<<<grid, kThreads, 0, st>>>(bitmask, rows, cols, offs, gate);
     if ((rc = after_launch("bm_popcount_kernel"))) return rc;
-    row_scan_kernel<<<1, 1024, 0, st>>>(offs, rows, nullptr);
+    row_scan_kernel<<<1, 1024, 0, st>>>(offs, rows, nullptr, gate);
     if ((rc = after_launch("row_scan_kernel"))) return rc;
     const bool vec = cols % 8 == 0 && aligned16(out);
-    if (vec && e.esize == 2) bm_expand_kernel<2, true><<<grid, kThreads, 0, st>>>(values, bitmask, e.esize, rows, cols, offs, out);
-    else if (vec && e.esize == 1) bm_expand_kernel<1, true><<<grid, kThreads, 0, st>>>(values, bitmask, e.esize, rows, cols, offs, out);
-    else if (vec && e.esize == 4) bm_expand_kernel<4, true><<<grid, kThreads, 0, st>>>(values, bitmask, e.esize, rows, cols, offs, out);
-    else bm_expand_kernel<0, false><<<grid, kThreads, 0, st>>>(values, bitmask, e.esize, rows, cols, offs, out);
+    if (vec && e.esize == 2) bm_expand_kernel<2, true><<<grid, kThreads, 0, st>>>(values, bitmask, e.esize, rows, cols, offs, out, gate);
+    else if (vec && e.esize == 1) bm_expand_kernel<1, true><<<grid, kThreads, 0, st>>>(values, bitmask, e.esize, rows, cols, offs, out, gate);
+    else if (vec && e.esize == 4) bm_expand_kernel<4, true><<<grid, kThreads, 0, st>>>(values, bitmask, e.esize, rows, cols, offs, out, gate);
+    else bm_expand_kernel<0, false><<<grid, kThreads, 0, st>>>(values, bitmask, e.esize, rows, cols, offs, out, gate);
     return after_launch("bm_expand_kernel");
+}
+
+extern "C" int ctb_bitmask_decompress(const void *values, const uint8_t *bitmask, int32_t dtype, int64_t rows, int64_t cols, void *out,
+                                      void *workspace, void *stream) {
+    return decompress_impl(values, bitmask, dtype, rows, cols, out, workspace, nullptr, stream);
+}
+
+extern "C" int ctb_sparse24_decompress(const void *values, const uint8_t *bitmask, int32_t dtype, int64_t rows, int64_t cols, void *out,
+                                       void *workspace, void *stream) {
+    if (!values || !bitmask || !out || !workspace) return fail(CTB_EINVAL_NULL, "null buffer");
+    ElemInfo e;
+    if (!elem_info(dtype, &e)) return fail(CTB_EINVAL_DTYPE, "unsupported dtype for bitmask decompression");
+    if (rows <= 0 || cols <= 0) return rows < 0 || cols < 0 ? fail(CTB_EINVAL_SHAPE, "negative shape") : CTB_OK;
+    if (cols % 8 != 0 || !aligned16(out) || (reinterpret_cast<uintptr_t>(values) & 15u))
+        return decompress_impl(values, bitmask, dtype, rows, cols, out, workspace, nullptr, stream);
+    cudaStream_t st = as_stream(stream);
+    int *flag = reinterpret_cast<int *>(static_cast<char *>(workspace) + rows * 8);
+    cudaError_t ce = cudaMemsetAsync(flag, 0, sizeof(int), st);
+    if (ce != cudaSuccess) return fail(CTB_ECUDA, "cudaMemsetAsync: %s", cudaGetErrorString(ce));
+    const int64_t units = rows * cols / 8;
+    int grid = grid_for(units, kThreads, 8);
+    if (e.esize == 2) sparse24_expand_kernel<2><<<grid, kThreads, 0, st>>>(values, bitmask, units, out, flag);
+    else if (e.esize == 1) sparse24_expand_kernel<1><<<grid, kThreads, 0, st>>>(values, bitmask, units, out, flag);
+    else sparse24_expand_kernel<4><<<grid, kThreads, 0, st>>>(values, bitmask, units, out, flag);
+    int rc = after_launch("sparse24_expand_kernel");
+    if (rc) return rc;
+    // generic path, gated on the flag: returns immediately unless the bitmask was not two-per-run
+    return decompress_impl(values, bitmask, dtype, rows, cols, out, workspace, flag, stream);
 }
 
 // ------------------------------------------------------------------ decompress without caller scratch

@@ -12,7 +12,7 @@ from ._lib import CODE_DTYPE, CODE_FP4X2, CODE_PACK32, DT, QFLOAT, QINT, QDesc, 
 __all__ = [
     "quantize", "dequantize", "fake_quantize", "minmax", "calculate_qparams", "generate_gparam",
     "pack_int32", "unpack_int32", "pack_fp4", "unpack_fp4", "pack_bitmasks", "unpack_bitmasks",
-    "sparse24_mask", "sparse24_compress", "bitmask_compress", "bitmask_decompress", "hadamard",
+    "sparse24_mask", "sparse24_compress", "sparse24_decompress", "bitmask_compress", "bitmask_decompress", "hadamard",
     "absmax_quantize", "rotate_quantize_int4_batch", "unpack_dequantize_int4_batch", "tensor_table", "QINT", "QFLOAT",
 ]
 
@@ -287,6 +287,18 @@ def bitmask_decompress(values, bitmask, shape):
     ws = torch.empty(max(rows, 1), dtype=torch.int64, device=bitmask.device)
     check(lib().ctb_bitmask_decompress(ptr(values), ptr(bitmask), i32(DT[values.dtype]), i64(rows), i64(cols), ptr(out), ptr(ws),
                                        stream_of(bitmask)))
+    return out
+
+
+def sparse24_decompress(values, bitmask, shape):
+    """sparse_24_bitmask.py:206 sparse24_bitmask_decompress (scan-free when the mask is two-per-four)."""
+    require_cuda(values, bitmask)
+    values, bitmask = _c(values.flatten()), _c(bitmask)
+    rows, cols = int(shape[0]), int(shape[1])
+    out = torch.empty((rows, cols), dtype=values.dtype, device=bitmask.device)
+    ws = torch.empty(max(rows, 1) + 2, dtype=torch.int64, device=bitmask.device)
+    check(lib().ctb_sparse24_decompress(ptr(values), ptr(bitmask), i32(DT[values.dtype]), i64(rows), i64(cols), ptr(out), ptr(ws),
+                                        stream_of(bitmask)))
     return out
 
 

@@ -185,6 +185,12 @@ int ctb_masked_compress(const void *x, const uint8_t *bytemask, int32_t dtype, i
 int ctb_bitmask_decompress(const void *values, const uint8_t *bitmask, int32_t dtype, int64_t rows,
                            int64_t cols, void *out, void *workspace, void *stream);
 
+/* sparse_24_bitmask.py:206-224 sparse24_bitmask_decompress.  Same result as ctb_bitmask_decompress for any
+ * bitmask; when the bitmask keeps exactly two of every four columns (what the 2:4 compressor writes) a
+ * scan-free kernel does the work and the generic kernels return at once.  workspace: rows*8 + 16 bytes. */
+int ctb_sparse24_decompress(const void *values, const uint8_t *bitmask, int32_t dtype, int64_t rows,
+                            int64_t cols, void *out, void *workspace, void *stream);
+
 /* No counterpart in the reference.  Same result as ctb_bitmask_decompress, for callers that cannot
  * allocate device memory where they decompress (a server whose memory went to a fixed arena at
  * start-up, a load hook running while something else owns the allocator): the per-row offsets live

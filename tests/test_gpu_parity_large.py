@@ -185,6 +185,12 @@ def test_sparse_codecs_match_oracle(ops, orc):
         assert_bit_equal(dv.cpu(), v), assert_bit_equal(db.cpu(), b)
         assert_bit_equal(ops.sparse24_mask(t.cuda()).cpu(), mask, "keep mask on unpruned values")
         assert_bit_equal(ops.bitmask_decompress(dv, db, t.shape).cpu(), orc.bitmask_decompress(v, b, t.shape))
+    # the 2:4 decompress entry: scan-free on a regular mask, generic kernels take over on an irregular one
+    t = weights(64, 512, seed=12)
+    v, b = ops.sparse24_compress(t.cuda())
+    assert_bit_equal(ops.sparse24_decompress(v, b, t.shape).cpu(), ops.bitmask_decompress(v, b, t.shape).cpu(), "regular 2:4 mask")
+    vals, bm, _ = ops.bitmask_compress(w.cuda())  # unstructured: not two-per-four
+    assert_bit_equal(ops.sparse24_decompress(vals, bm, w.shape).cpu(), orc.bitmask_decompress(values, bitmask, w.shape), "irregular mask")
     # ops run twice give identical bits (no race in the compaction)
     gv2, gb2, gr2 = ops.bitmask_compress(w.cuda())
     assert_bit_equal(gv2.cpu(), gv.cpu()), assert_bit_equal(gr2.cpu(), gr.cpu())
