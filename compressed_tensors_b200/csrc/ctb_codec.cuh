@@ -306,6 +306,24 @@ __device__ __forceinline__ uint2 quant_fp8_codes_bf16(const uint32_t (&w)[4], fl
     return make_uint2(c[0] | (c[1] << 16), c[2] | (c[3] << 16));
 }
 
+// 8 bf16 inputs (4 packed words) -> 8 e2m1 codes (one 32-bit word, even element in the low nibble), fp32 effective
+// scale (NVFP4: e4m3 group scale / fp32 global scale).  x / s is the correctly rounded fp32 quotient (reciprocal +
+// Markstein correction; for x = -0.0 the correction step itself yields +0.0, which is also what the reference's
+// cast produces for a zero input), and the saturating round-to-nearest-even e2m1 convert equals the reference's
+// clamp to +-6 followed by FP4_E2M1_DATA.cast_to_fp4 (ties to the even code, a negative value that rounds to zero
+// keeps its sign bit).  Callers guarantee finite inputs and a scale in the normal range.
+__device__ __forceinline__ uint32_t quant_fp4_codes_f32(const uint32_t (&w)[4], float s, float r) {
+    uint32_t out = 0;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float x0 = __uint_as_float(w[k] << 16), x1 = __uint_as_float(w[k] & 0xFFFF0000u);
+        const float a0 = x0 * r, a1 = x1 * r;
+        const float q0 = fmaf(fmaf(-a0, s, x0), r, a0), q1 = fmaf(fmaf(-a1, s, x1), r, a1);
+        out |= (uint32_t)__nv_cvt_float2_to_fp4x2(make_float2(q0, q1), __NV_E2M1, cudaRoundNearest) << (8 * k);
+    }
+    return out;
+}
+
 // 8 values exactly representable in the scale's compute dtype (int8 / e4m3 / e2m1 codes), no zero point:
 // value * scale rounded once to bf16 -- what (x_q.to(scale.dtype) * scale).to(bf16) gives for a bf16 scale,
 // and, with an fp32 effective scale, the fp32 product rounded to bf16 (NVFP4 decompress).

@@ -171,17 +171,17 @@ namespace ctb {
 // symmetric scale of one group from its absolute maximum, helpers.py:99-122, in the dtype M of the
 // tensor; returns the effective fp32 scale used by the quantize step and stores the qparam.
 template <int M, int QK>
-__device__ __forceinline__ float group_scale(float amax, const float *gs, float half_range, void *out_scale, int64_t gi, bool writer) {
+__device__ __forceinline__ float group_scale(float amax, float g, float rg, float half_range, float r_half, void *out_scale, int64_t gi, bool writer) {
     if constexpr (QK == QK_FP4) {
-        const float g = __ldg(gs);
-        float sc = g * round_to<M>(div_by_rcp(amax, 6.0f, 0.16666667163372040f));  // RN(1/6); the quotient is correctly rounded
-        sc = clamp_nan(sc, -448.0f, 448.0f);
+        // g = global scale, rg = 1 / g (both fp32); quotients by constants are correctly rounded (Markstein)
+        float sc = g * round_to<M>(div_by_rcp(amax, 6.0f, 0.16666667163372040f));
+        sc = clamp_nan(sc, -448.0f, 448.0f);  // NaN (all-zero tensor: inf * 0) stays NaN, as in the reference
         uint8_t b = f32_to_e4m3(sc);
         if ((b & 0x7F) == 0) b = 0x20;  // zero scale -> 0.125
         if (writer) ((uint8_t *)out_scale)[gi] = b;
-        return __fdiv_rn(e4m3_to_f32(b), g);  // forward.py:468-469
+        return div_by_rcp(e4m3_to_f32(b), g, rg);  // forward.py:468-469 scale.to(f32) / global_scale
     } else {
-        float sc = fmaxf(round_to<M>(div_by_rcp(amax, half_range, __frcp_rn(half_range))), 1.1920928955078125e-07f);
+        float sc = fmaxf(round_to<M>(div_by_rcp(amax, half_range, r_half)), 1.1920928955078125e-07f);
         if (writer) store_f32(out_scale, M, gi, sc);
         return sc;
     }
@@ -194,6 +194,7 @@ __global__ void __launch_bounds__(kThreads) absmax_quant_group_kernel(const HArg
     constexpr int M = XF == F_BF16 ? CTB_BF16 : XF == F_F16 ? CTB_F16 : CTB_F32;
     constexpr int T = QK == QK_FP4 ? CTB_F32 : M;
     constexpr int U = ROT ? 1 : 4;  // chunks in flight per thread
+    const float gsv = (QK == QK_FP4) ? __ldg(a.gs) : 1.0f, rgs = __frcp_rn(gsv), r_half = __frcp_rn(a.half_range);
     const int64_t padded = (a.chunks + 31) & ~(int64_t)31;  // whole warps stay in the loop for the shuffles
     const int64_t stride = (int64_t)gridDim.x * kThreads * U;
     for (int64_t base = (int64_t)blockIdx.x * kThreads * U + threadIdx.x; base - threadIdx.x + (threadIdx.x & ~31) < padded; base += stride) {
@@ -216,10 +217,18 @@ __global__ void __launch_bounds__(kThreads) absmax_quant_group_kernel(const HArg
             for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
             for (int o = a.GL >> 1; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
             QP q;
-            q.s = group_scale<M, QK>(amax, a.gs, a.half_range, a.out_scale, c >> a.gl_shift, live && (c & (a.GL - 1)) == 0);
+            q.s = group_scale<M, QK>(amax, gsv, rgs, a.half_range, r_half, a.out_scale, c >> a.gl_shift, live && (c & (a.GL - 1)) == 0);
             q.r = __frcp_rn(q.s);
             q.zp = 0.0f;
             q.slow = !(fabsf(q.s) >= 1.0e-30f && fabsf(q.s) <= 1.0e30f);
+            if constexpr (XF == F_BF16 && QK == QK_FP4 && FOUT == F_FP4X2 && !ROT) {
+                // finite group (amax < inf) and a scale in the normal range: reciprocal + Markstein, saturating e2m1 convert
+                if (!q.slow && amax <= 3.0e38f) {
+                    const uint32_t w[4] = {raw[u].a.x, raw[u].a.y, raw[u].a.z, raw[u].a.w};
+                    if (live) st_stream4((char *)a.out + c * 4, quant_fp4_codes_f32(w, q.s, q.r));
+                    continue;
+                }
+            }
             if constexpr (XF == F_BF16 && ((QK == QK_INT && FOUT == F_PACK4) || (QK == QK_FP8 && FOUT == F_E4M3))) {
                 if (!q.slow) {
                     uint32_t w[4];
@@ -251,6 +260,7 @@ template <int CPL, int XF, int QK, int FOUT>
 __global__ void __launch_bounds__(kThreads) absmax_quant_warprow_kernel(const HArgs a, int64_t rows, int cpr) {
     constexpr int M = XF == F_BF16 ? CTB_BF16 : XF == F_F16 ? CTB_F16 : CTB_F32;
     const int lane = threadIdx.x & 31;
+    const float r_half = __frcp_rn(a.half_range);
     const int64_t warps = (int64_t)gridDim.x * (kThreads / 32);
     for (int64_t r = (int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5); r < rows; r += warps) {
         Raw8 raw[CPL];
@@ -271,7 +281,7 @@ __global__ void __launch_bounds__(kThreads) absmax_quant_warprow_kernel(const HA
         }
         for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
         QP q;
-        q.s = group_scale<M, QK>(amax, a.gs, a.half_range, a.out_scale, r, lane == 0);
+        q.s = group_scale<M, QK>(amax, 1.0f, 1.0f, a.half_range, r_half, a.out_scale, r, lane == 0);
         q.r = __frcp_rn(q.s);
         q.zp = 0.0f;
         q.slow = !(fabsf(q.s) >= 1.0e-30f && fabsf(q.s) <= 1.0e30f);
@@ -320,7 +330,7 @@ __global__ void __launch_bounds__(kThreads) absmax_quant_row_kernel(const HArgs 
 #pragma unroll
         for (int i = 0; i < kThreads / 32; ++i) amax = fmaxf(amax, red[i]);
         QP q;
-        q.s = group_scale<M, QK>(amax, a.gs, a.half_range, a.out_scale, r, threadIdx.x == 0);
+        q.s = group_scale<M, QK>(amax, 1.0f, 1.0f, a.half_range, __frcp_rn(a.half_range), a.out_scale, r, threadIdx.x == 0);
         q.r = __frcp_rn(q.s);
         q.zp = 0.0f;
         q.slow = !(fabsf(q.s) >= 1.0e-30f && fabsf(q.s) <= 1.0e30f);
