@@ -324,41 +324,29 @@ def main():
     e2e = None
     if not args.no_e2e:
         host_w = [torch.empty(w.shape, dtype=w.dtype, pin_memory=True).copy_(w) for w in weights]
-        plain = parallel.ShardCodec(weights, group_size=128, hadamard_n=128, signs=signs, precision=precision, use_graphs=False)
-        plain._compress()
-        host_p = [torch.empty(p.shape, dtype=p.dtype, pin_memory=True) for p in plain.packed]
-        host_s = [torch.empty(s.shape, dtype=s.dtype, pin_memory=True) for s in plain.scales]
-        host_r = [torch.empty(w.shape, dtype=w.dtype, pin_memory=True) for w in weights]
         torch.cuda.synchronize()
-
-        def e2e_step():
-            for i, hw in enumerate(host_w):
-                w = hw.to(dev, non_blocking=True)
-                p, s = ops.absmax_quantize(w, qtype=ops.QINT, bits=4, col_group=128, codec="pack32", hadamard_n=128, signs=signs, precision=precision)
-                host_p[i].copy_(p, non_blocking=True)
-                host_s[i].copy_(s, non_blocking=True)
-            for i, hw in enumerate(host_w):
-                p, s = host_p[i].to(dev, non_blocking=True), host_s[i].to(dev, non_blocking=True)
-                cols = hw.shape[1]
-                r = ops.dequantize(p, s, None, qtype=ops.QINT, bits=4, col_group=128, scale_row_stride=cols // 128,
-                                   out_dtype=torch.bfloat16, codec="pack32", cols=cols)
-                host_r[i].copy_(r, non_blocking=True)
-            torch.cuda.synchronize()
-
-        e2e_step()
+        trip = parallel.HostRoundTrip(host_w, group=len(shapes), device=dev, signs=signs, precision=precision)
+        trip.run()
         barrier()
         k = max(1, min(args.steps, 3))
         t0 = time.perf_counter()
         for _ in range(k):
-            e2e_step()
+            trip.run()
         te = torch.tensor([(time.perf_counter() - t0) / k], dtype=torch.float64, device=dev)
         if world > 1:
             dist.all_reduce(te, op=dist.ReduceOp.MAX)
-        packed_bytes = sum(p.numel() * 4 for p in host_p) + sum(s.numel() * 2 for s in host_s)
         e2e = {"value": 2 * 2 * total_elems / float(te) / 1e9, "unit": UNIT,
-               "h2d_bytes_per_step": 2 * my_elems + packed_bytes, "d2h_bytes_per_step": packed_bytes + 2 * my_elems,
-               "ms_per_step": float(te) * 1e3, "bytes_are": "per rank"}
-        del host_w, host_p, host_s, host_r, plain
+               "h2d_bytes_per_step": trip.h2d_bytes, "d2h_bytes_per_step": trip.d2h_bytes,
+               "ms_per_step": float(te) * 1e3, "bytes_are": "per rank",
+               "path": "HostRoundTrip: pinned host -> device -> fused kernels -> pinned host, 3 streams, one decoder layer per group"}
+        # the restored host weights must be what the device path produced
+        check = parallel.ShardCodec(weights[:len(shapes)], signs=signs, precision=precision)
+        check.compress(), check.decompress()
+        torch.cuda.synchronize()
+        for j in range(len(shapes)):
+            assert torch.equal(trip.host_r[j], check.restored[j].cpu()), "end-to-end result differs from the device path"
+        del check
+        del host_w, trip
 
     if rank == 0:
         peak, peak_kind = peaks()

@@ -13,7 +13,7 @@ from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 
-__all__ = ["LLAMA3_8B", "ModelShape", "linear_shapes", "partition_layers", "allreduce_amax", "ShardCodec"]
+__all__ = ["LLAMA3_8B", "ModelShape", "linear_shapes", "partition_layers", "allreduce_amax", "ShardCodec", "HostRoundTrip"]
 
 
 @dataclass(frozen=True)
@@ -160,3 +160,76 @@ class ShardCodec:
     @property
     def launches_per_pass(self) -> int:
         return -(-len(self.weights) // 256) if self.batched else len(self.weights)
+
+
+class HostRoundTrip:
+    """End-to-end compress + decompress of a shard whose tensors live in (pinned) HOST memory, the way the
+    reference's ModelCompressor sees a CPU state dict: weights go host -> device, packed words and scales come
+    back to the host, and the decompress half reads those host buffers again and returns dense weights to the
+    host.  Work is cut into groups of tensors (one decoder layer each) and spread over three streams -- copy-in,
+    kernels, copy-out -- so that both PCIe directions and the GPU stay busy at once; events carry the
+    dependencies (a group is decompressed only after its own packed bytes made the trip to the host and back)."""
+
+    def __init__(self, host_weights: Sequence[torch.Tensor], group: int, device, *, signs=None, precision=torch.float64):
+        self.device = torch.device(device)
+        self.host_w = list(host_weights)
+        self.groups = [list(range(i, min(i + group, len(self.host_w)))) for i in range(0, len(self.host_w), group)]
+        self.dev_w = [torch.empty(w.shape, dtype=w.dtype, device=self.device) for w in self.host_w]
+        self.codecs = [ShardCodec([self.dev_w[i] for i in g], signs=signs, precision=precision) for g in self.groups]
+        for c in self.codecs:
+            if not c.batched:
+                raise NotImplementedError("the host round trip is built for the batched bf16 / block-128 / group-128 path")
+            c._allocate()
+        pin = dict(pin_memory=True)
+        self.host_p = [torch.empty((w.shape[0], w.shape[1] // 8), dtype=torch.int32, **pin) for w in self.host_w]
+        self.host_s = [torch.empty((w.shape[0], w.shape[1] // 128), dtype=w.dtype, **pin) for w in self.host_w]
+        self.host_r = [torch.empty(w.shape, dtype=w.dtype, **pin) for w in self.host_w]
+        self.s_in, self.s_k, self.s_out = (torch.cuda.Stream(self.device) for _ in range(3))
+
+    @property
+    def h2d_bytes(self) -> int:
+        return sum(w.numel() * w.element_size() for w in self.host_w) + self.d2h_packed_bytes
+
+    @property
+    def d2h_packed_bytes(self) -> int:
+        return sum(p.numel() * 4 for p in self.host_p) + sum(s.numel() * s.element_size() for s in self.host_s)
+
+    @property
+    def d2h_bytes(self) -> int:
+        return self.d2h_packed_bytes + sum(w.numel() * w.element_size() for w in self.host_w)
+
+    def run(self) -> None:
+        """One round trip of the whole shard; returns after everything has landed in the host buffers."""
+        ev = torch.cuda.Event
+        for g, codec in zip(self.groups, self.codecs):
+            e_in, e_c, e_o, e_in2, e_d = ev(), ev(), ev(), ev(), ev()
+            with torch.cuda.stream(self.s_in):
+                for i in g:
+                    self.dev_w[i].copy_(self.host_w[i], non_blocking=True)
+                e_in.record()
+            with torch.cuda.stream(self.s_k):
+                self.s_k.wait_event(e_in)
+                codec._compress()
+                e_c.record()
+            with torch.cuda.stream(self.s_out):
+                self.s_out.wait_event(e_c)
+                for j, i in enumerate(g):
+                    self.host_p[i].copy_(codec.packed[j], non_blocking=True)
+                    self.host_s[i].copy_(codec.scales[j], non_blocking=True)
+                e_o.record()
+            with torch.cuda.stream(self.s_in):
+                self.s_in.wait_event(e_o)  # the packed bytes are on the host: bring them back for the decompress half
+                for j, i in enumerate(g):
+                    codec.packed[j].copy_(self.host_p[i], non_blocking=True)
+                    codec.scales[j].copy_(self.host_s[i], non_blocking=True)
+                e_in2.record()
+            with torch.cuda.stream(self.s_k):
+                self.s_k.wait_event(e_in2)
+                codec._decompress()
+                e_d.record()
+            with torch.cuda.stream(self.s_out):
+                self.s_out.wait_event(e_d)
+                for j, i in enumerate(g):
+                    self.host_r[i].copy_(codec.restored[j], non_blocking=True)
+        for s in (self.s_in, self.s_k, self.s_out):
+            s.synchronize()
