@@ -201,12 +201,19 @@ class HostRoundTrip:
     def run(self) -> None:
         """One round trip of the whole shard; returns after everything has landed in the host buffers."""
         ev = torch.cuda.Event
-        for g, codec in zip(self.groups, self.codecs):
-            e_in, e_c, e_o, e_in2, e_d = ev(), ev(), ev(), ev(), ev()
+        n = len(self.groups)
+
+        def copy_in(k):
+            e = ev()
             with torch.cuda.stream(self.s_in):
-                for i in g:
+                for i in self.groups[k]:
                     self.dev_w[i].copy_(self.host_w[i], non_blocking=True)
-                e_in.record()
+                e.record()
+            return e
+
+        e_in = copy_in(0)
+        for k, (g, codec) in enumerate(zip(self.groups, self.codecs)):
+            e_c, e_o, e_in2, e_d = ev(), ev(), ev(), ev()
             with torch.cuda.stream(self.s_k):
                 self.s_k.wait_event(e_in)
                 codec._compress()
@@ -217,6 +224,8 @@ class HostRoundTrip:
                     self.host_p[i].copy_(codec.packed[j], non_blocking=True)
                     self.host_s[i].copy_(codec.scales[j], non_blocking=True)
                 e_o.record()
+            if k + 1 < n:  # the next group's weights go in while this group's packed bytes make their trip out
+                e_in = copy_in(k + 1)
             with torch.cuda.stream(self.s_in):
                 self.s_in.wait_event(e_o)  # the packed bytes are on the host: bring them back for the decompress half
                 for j, i in enumerate(g):
