@@ -29,6 +29,9 @@ UNIT = "GB/s"
 WORKLOAD = "llama3-8b-linears hadamard128+w4a16-g128 compress+decompress"
 SEED = 0
 ALG_BYTES_PER_ELEM = 2 + 0.5 + 2 / 128  # bf16 in, 4 bits out, one bf16 scale per 128 (either direction)
+# dram__bytes_read.sum + dram__bytes_write.sum of rotquant128_tc_kernel per element, from the ncu capture of the two-layer
+# case (872.45 MB + 204.32 MB over 436,207,616 elements; traffic grows in proportion to the elements processed)
+NCU_TRAFFIC_BYTES_PER_ELEM = (872.452096e6 + 204.323584e6) / 436207616
 
 
 def peaks():
@@ -365,7 +368,8 @@ def main():
                        "cuda_graphs": codec.use_graphs, "one_grid_per_shard": codec.batched},
             "compress_gbs": 2 * total_elems / (tc / args.steps) / 1e9, "decompress_gbs": 2 * total_elems / (td / args.steps) / 1e9,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "kernel": "rotquant128_tc_kernel" if args.precision == "tc" else "rotquant128_kernel", "peak_kind": peak_kind,
+                         "traffic": (NCU_TRAFFIC_BYTES_PER_ELEM * rank_elems) if args.precision == "tc" else None,
+                         "traffic_source": "ncu capture of the 2-layer case scaled by elements per launch", "kernel": "rotquant128_tc_kernel" if args.precision == "tc" else "rotquant128_kernel", "peak_kind": peak_kind,
                          "decompress_frac": ALG_BYTES_PER_ELEM * rank_elems / (td / args.steps) / 1e9 / peak},
             "clocks": clocks, "gpu_launches": int(launches), "e2e": e2e,
         }
