@@ -246,7 +246,7 @@ def per_config_table(dev, peak):
         w = rnd(4096, 4096)
         w[torch.rand(4096, 4096, generator=g, device=dev) < 0.5] = 0
         return (w,)
-    run("c4b_bitmask_compress_bf16_50pct", unstructured, lambda w: ops.bitmask_compress(w), 2 * n, (2 + 1 + 0.125) * n, 3.2 * n)
+    run("c4b_bitmask_compress_bf16_50pct", unstructured, lambda w: ops._masked_compress(w, None, sync=False), 2 * n, (2 + 1 + 0.125) * n, 3.2 * n)
     run("c4b_bitmask_decompress_bf16_50pct", lambda: ops.bitmask_compress(unstructured()[0])[:2],
         lambda v, b: ops.bitmask_decompress(v, b, (4096, 4096)), 2 * n, (2 + 1 + 0.125) * n, 3.2 * n)
     return out

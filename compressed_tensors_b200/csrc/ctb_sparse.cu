@@ -373,6 +373,166 @@ __global__ void __launch_bounds__(kThreads) bm_expand_kernel(const void *values,
 
 }  // namespace ctb
 
+
+// ------------------------------------------------------------------ single-pass codec (cols % 8 == 0)
+//
+// The non-zero values of the whole tensor are one row-major stream, so compaction is a prefix sum over flat tiles
+// of 4096 elements.  Tiles are handed out by an atomic ticket (a tile only ever waits for tiles that were handed out
+// before it, which are running or done), each tile publishes its count and then its inclusive prefix in one 64-bit
+// status word, and a tile finds its starting offset by walking back over its predecessors' words ("decoupled
+// look-back").  Every element is read once and every output written once.  The walk is bounded: if a predecessor's
+// word does not appear within the budget the tile raises the error word and uses what it has.
+namespace ctb {
+
+constexpr int kOnePassEpt = 16;                         // elements per thread
+constexpr int kOnePassTile = kThreads * kOnePassEpt;    // 4096 elements per tile
+constexpr unsigned long long kFlagAgg = 1ull << 62, kFlagIncl = 2ull << 62, kValMask = (1ull << 62) - 1;
+constexpr long long kLookBackCycles = 2000000000LL;
+
+struct OnePassCtl {            // lives at the start of the workspace, zeroed by the entry point before every launch
+    unsigned int ticket;
+    int error;
+    unsigned long long pad;
+};
+
+__device__ __forceinline__ int block_excl_scan16(int v, int &total, int *wsum) {
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    int inc = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        int t = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+        if (lane >= o) inc += t;
+    }
+    if (lane == 31) wsum[w] = inc;
+    __syncthreads();
+    int base = 0;
+    total = 0;
+#pragma unroll
+    for (int i = 0; i < kThreads / 32; ++i) {
+        if (i < w) base += wsum[i];
+        total += wsum[i];
+    }
+    return base + inc - v;
+}
+
+// exclusive prefix of tile `tile` given its own total; publishes the tile's words.  One thread calls this.
+__device__ __forceinline__ unsigned long long look_back(volatile unsigned long long *state, unsigned int tile, unsigned long long total, int *error) {
+    if (tile == 0) {
+        state[0] = kFlagIncl | total;
+        return 0;
+    }
+    state[tile] = kFlagAgg | total;
+    unsigned long long run = 0;
+    const long long t0 = clock64();
+    for (long long j = (long long)tile - 1; j >= 0; --j) {
+        unsigned long long v = state[j];
+        while ((v >> 62) == 0) {
+            if (clock64() - t0 > kLookBackCycles) {
+                atomicExch(error, 1);
+                v = kFlagIncl;  // give up: treat the rest as empty so the kernel still terminates
+                break;
+            }
+            v = state[j];
+        }
+        run += v & kValMask;
+        if ((v >> 62) == 2) break;
+    }
+    state[tile] = kFlagIncl | (run + total);
+    return run;
+}
+
+template <int ES>
+__global__ void __launch_bounds__(kThreads) bm_compress_onepass_kernel(const void *x, uint32_t nzm, int64_t units, int64_t cols, int64_t rows, void *values,
+                                                                       uint8_t *bitmask, int64_t *row_offsets, int64_t *nnz, OnePassCtl *ctl,
+                                                                       volatile unsigned long long *state) {
+    __shared__ uint32_t stage[kOnePassTile];
+    __shared__ int wsum[kThreads / 32];
+    __shared__ unsigned int s_tile;
+    __shared__ unsigned long long s_prefix;
+    const unsigned int ntiles = (unsigned int)((units * 8 + kOnePassTile - 1) / kOnePassTile);
+    for (;;) {
+        if (threadIdx.x == 0) s_tile = atomicAdd(&ctl->ticket, 1u);
+        __syncthreads();
+        const unsigned int tile = s_tile;
+        if (tile >= ntiles) break;
+        const int64_t u0 = ((int64_t)tile * kThreads + threadIdx.x) * 2;  // first of this thread's two 8-element units
+        uint32_t b[16];
+        uint32_t mask = 0;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            uint32_t t8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            if (u0 + h < units) mask |= unit_mask<ES>(x, u0 + h, nzm, t8) << (8 * h);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) b[8 * h + j] = t8[j];
+        }
+        int total;
+        const int excl = block_excl_scan16(__popc(mask), total, wsum);
+        if (threadIdx.x == 0) s_prefix = look_back(state, tile, (unsigned long long)total, &ctl->error);
+        if (u0 < units) {
+            if (u0 + 1 < units) *reinterpret_cast<uint16_t *>(bitmask + u0) = (uint16_t)mask;
+            else bitmask[u0] = (uint8_t)mask;
+        }
+        int pos = excl;
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+            if ((mask >> j) & 1) stage[pos++] = b[j];
+        __syncthreads();
+        const unsigned long long prefix = s_prefix;
+        // rows that begin inside this thread's 16 elements (cols is a multiple of 8: only at offset 0 or 8)
+        if (u0 < units) {
+            const int64_t e0 = u0 * 8;
+            const int64_t r0 = (units <= 0x1FFFFFFF) ? (int64_t)((uint32_t)e0 / (uint32_t)cols) : e0 / cols;  // 32-bit divide when it fits
+            const int64_t rem = e0 - r0 * cols;
+            if (rem == 0) row_offsets[r0] = (int64_t)(prefix + excl);
+            if (rem + 8 == cols && r0 + 1 < rows && u0 + 1 < units) row_offsets[r0 + 1] = (int64_t)(prefix + excl + __popc(mask & 0xFFu));
+        }
+        for (int i = threadIdx.x; i < total; i += kThreads) store_bits(values, ES, (int64_t)prefix + i, stage[i]);
+        if (tile == ntiles - 1 && threadIdx.x == 0) *nnz = (int64_t)(prefix + total);
+        __syncthreads();
+    }
+}
+
+template <int ES>
+__global__ void __launch_bounds__(kThreads) bm_expand_onepass_kernel(const void *values, const uint8_t *bitmask, int64_t units, void *out, OnePassCtl *ctl,
+                                                                     volatile unsigned long long *state) {
+    __shared__ int wsum[kThreads / 32];
+    __shared__ unsigned int s_tile;
+    __shared__ unsigned long long s_prefix;
+    const unsigned int ntiles = (unsigned int)((units * 8 + kOnePassTile - 1) / kOnePassTile);
+    for (;;) {
+        if (threadIdx.x == 0) s_tile = atomicAdd(&ctl->ticket, 1u);
+        __syncthreads();
+        const unsigned int tile = s_tile;
+        if (tile >= ntiles) break;
+        const int64_t u0 = ((int64_t)tile * kThreads + threadIdx.x) * 2;
+        uint32_t mask = 0;
+        if (u0 + 1 < units) mask = *reinterpret_cast<const uint16_t *>(bitmask + u0);
+        else if (u0 < units) mask = bitmask[u0];
+        int total;
+        const int excl = block_excl_scan16(__popc(mask), total, wsum);
+        if (threadIdx.x == 0) s_prefix = look_back(state, tile, (unsigned long long)total, &ctl->error);
+        __syncthreads();
+        int64_t src = (int64_t)s_prefix + excl;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            if (u0 + h >= units) break;
+            uint32_t b[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) b[j] = ((mask >> (8 * h + j)) & 1) ? load_bits(values, ES, src++) : 0u;
+            char *o = (char *)out + (u0 + h) * 8 * ES;
+            if constexpr (ES == 2) st_stream(o, make_uint4(b[0] | (b[1] << 16), b[2] | (b[3] << 16), b[4] | (b[5] << 16), b[6] | (b[7] << 16)));
+            else if constexpr (ES == 1) st_stream8(o, make_uint2(b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24), b[4] | (b[5] << 8) | (b[6] << 16) | (b[7] << 24)));
+            else {
+                st_stream(o, make_uint4(b[0], b[1], b[2], b[3]));
+                st_stream(o + 16, make_uint4(b[4], b[5], b[6], b[7]));
+            }
+        }
+        __syncthreads();
+    }
+}
+
+}  // namespace ctb
+
 // ------------------------------------------------------------------ entry points
 
 using namespace ctb;
@@ -406,8 +566,13 @@ extern "C" int ctb_sparse24_compress(const void *x, int32_t dtype, int64_t rows,
     return after_launch("sparse24_compress_kernel");
 }
 
+static int64_t onepass_bytes(int64_t rows, int64_t cols) {
+    const int64_t tiles = (rows * cols + kOnePassTile - 1) / kOnePassTile;
+    return (int64_t)sizeof(OnePassCtl) + 8 * tiles;
+}
+
 static int compress_impl(const void *x, const uint8_t *pred, int32_t dtype, int64_t rows, int64_t cols, void *values, uint8_t *bitmask,
-                         int64_t *row_offsets, int64_t *nnz, void *stream) {
+                         int64_t *row_offsets, int64_t *nnz, void *workspace, void *stream) {
     if (!x || !values || !bitmask || !row_offsets || !nnz) return fail(CTB_EINVAL_NULL, "null buffer");
     ElemInfo e;
     if (!elem_info(dtype, &e)) return fail(CTB_EINVAL_DTYPE, "unsupported dtype for bitmask compression");
@@ -419,6 +584,19 @@ static int compress_impl(const void *x, const uint8_t *pred, int32_t dtype, int6
         return CTB_OK;
     }
     const bool vec = !pred && cols % 8 == 0 && aligned16(x);
+    if (vec && workspace != nullptr && rows * cols / kOnePassTile < 0x7FFFFFFF) {
+        // single pass: ticketed tiles + decoupled look-back
+        cudaError_t ce = cudaMemsetAsync(workspace, 0, (size_t)onepass_bytes(rows, cols), st);
+        if (ce != cudaSuccess) return fail(CTB_ECUDA, "cudaMemsetAsync: %s", cudaGetErrorString(ce));
+        OnePassCtl *ctl = static_cast<OnePassCtl *>(workspace);
+        volatile unsigned long long *state = reinterpret_cast<volatile unsigned long long *>(ctl + 1);
+        const int64_t units = rows * cols / 8;
+        int g1 = grid_for(units * 8, kOnePassTile, 6);
+        if (e.esize == 2) bm_compress_onepass_kernel<2><<<g1, kThreads, 0, st>>>(x, e.nz_mask, units, cols, rows, values, bitmask, row_offsets, nnz, ctl, state);
+        else if (e.esize == 1) bm_compress_onepass_kernel<1><<<g1, kThreads, 0, st>>>(x, e.nz_mask, units, cols, rows, values, bitmask, row_offsets, nnz, ctl, state);
+        else bm_compress_onepass_kernel<4><<<g1, kThreads, 0, st>>>(x, e.nz_mask, units, cols, rows, values, bitmask, row_offsets, nnz, ctl, state);
+        return after_launch("bm_compress_onepass_kernel");
+    }
     int grid = grid_for(rows, 1, 8);
     int rc;
 #define CTB_BM(KERNEL, ...)                                                                              \
@@ -434,25 +612,42 @@ static int compress_impl(const void *x, const uint8_t *pred, int32_t dtype, int6
     return after_launch("bm_scatter_kernel");
 }
 
+extern "C" int64_t ctb_bitmask_workspace_bytes(int64_t rows, int64_t cols) {
+    const int64_t a = onepass_bytes(rows, cols), b = rows * 8 + 16;
+    return a > b ? a : b;
+}
+
 extern "C" int ctb_bitmask_compress(const void *x, int32_t dtype, int64_t rows, int64_t cols, void *values, uint8_t *bitmask,
-                                    int64_t *row_offsets, int64_t *nnz, void *stream) {
-    return compress_impl(x, nullptr, dtype, rows, cols, values, bitmask, row_offsets, nnz, stream);
+                                    int64_t *row_offsets, int64_t *nnz, void *workspace, void *stream) {
+    return compress_impl(x, nullptr, dtype, rows, cols, values, bitmask, row_offsets, nnz, workspace, stream);
 }
 
 extern "C" int ctb_masked_compress(const void *x, const uint8_t *bytemask, int32_t dtype, int64_t rows, int64_t cols, void *values,
                                    uint8_t *bitmask, int64_t *row_offsets, int64_t *nnz, void *stream) {
     if (!bytemask) return fail(CTB_EINVAL_NULL, "null mask");
-    return compress_impl(x, bytemask, dtype, rows, cols, values, bitmask, row_offsets, nnz, stream);
+    return compress_impl(x, bytemask, dtype, rows, cols, values, bitmask, row_offsets, nnz, nullptr, stream);
 }
 
 static int decompress_impl(const void *values, const uint8_t *bitmask, int32_t dtype, int64_t rows, int64_t cols, void *out, void *workspace,
-                           const int *gate, void *stream) {
+                           const int *gate, void *stream, bool onepass_ok = false) {
     if (!bitmask || !out || !workspace) return fail(CTB_EINVAL_NULL, "null buffer");
     ElemInfo e;
     if (!elem_info(dtype, &e)) return fail(CTB_EINVAL_DTYPE, "unsupported dtype for bitmask decompression");
     if (rows <= 0 || cols <= 0) return rows < 0 || cols < 0 ? fail(CTB_EINVAL_SHAPE, "negative shape") : CTB_OK;
     if (!values) return fail(CTB_EINVAL_NULL, "null values");
     cudaStream_t st = as_stream(stream);
+    if (onepass_ok && gate == nullptr && cols % 8 == 0 && aligned16(out) && rows * cols / kOnePassTile < 0x7FFFFFFF) {
+        cudaError_t ce = cudaMemsetAsync(workspace, 0, (size_t)onepass_bytes(rows, cols), st);
+        if (ce != cudaSuccess) return fail(CTB_ECUDA, "cudaMemsetAsync: %s", cudaGetErrorString(ce));
+        OnePassCtl *ctl = static_cast<OnePassCtl *>(workspace);
+        volatile unsigned long long *state = reinterpret_cast<volatile unsigned long long *>(ctl + 1);
+        const int64_t units = rows * cols / 8;
+        int g1 = grid_for(units * 8, kOnePassTile, 8);
+        if (e.esize == 2) bm_expand_onepass_kernel<2><<<g1, kThreads, 0, st>>>(values, bitmask, units, out, ctl, state);
+        else if (e.esize == 1) bm_expand_onepass_kernel<1><<<g1, kThreads, 0, st>>>(values, bitmask, units, out, ctl, state);
+        else bm_expand_onepass_kernel<4><<<g1, kThreads, 0, st>>>(values, bitmask, units, out, ctl, state);
+        return after_launch("bm_expand_onepass_kernel");
+    }
     int64_t *offs = (int64_t *)workspace;
     int grid = grid_for(rows, 1, 8);
     int rc;
@@ -470,7 +665,7 @@ static int decompress_impl(const void *values, const uint8_t *bitmask, int32_t d
 
 extern "C" int ctb_bitmask_decompress(const void *values, const uint8_t *bitmask, int32_t dtype, int64_t rows, int64_t cols, void *out,
                                       void *workspace, void *stream) {
-    return decompress_impl(values, bitmask, dtype, rows, cols, out, workspace, nullptr, stream);
+    return decompress_impl(values, bitmask, dtype, rows, cols, out, workspace, nullptr, stream, true);
 }
 
 extern "C" int ctb_sparse24_decompress(const void *values, const uint8_t *bitmask, int32_t dtype, int64_t rows, int64_t cols, void *out,
@@ -534,5 +729,6 @@ extern "C" int ctb_bitmask_decompress_static(const void *values, const uint8_t *
     int rc = static_scratch(&scratch);
     if (rc) return rc;
     // every row's slot is rewritten by the popcount pass before the scan reads it: nothing has to start at zero
-    return ctb_bitmask_decompress(values, bitmask, dtype, rows, cols, out, scratch, stream);
+    const bool fits = rows > 0 && cols > 0 && onepass_bytes(rows, cols) <= kStaticMaxRows * 8;
+    return decompress_impl(values, bitmask, dtype, rows, cols, out, scratch, nullptr, stream, fits);
 }

@@ -239,19 +239,28 @@ def sparse24_mask(x):
     return out.view(torch.bool)
 
 
-def _masked_compress(x, mask):
+def _bitmask_workspace(rows, cols, device):
+    lib().ctb_bitmask_workspace_bytes.restype = ctypes.c_int64
+    n = int(lib().ctb_bitmask_workspace_bytes(i64(rows), i64(cols)))
+    return torch.empty(max(n, 16), dtype=torch.uint8, device=device)
+
+
+def _masked_compress(x, mask, sync=True):
     rows, cols = x.shape
     values = torch.empty(x.numel(), dtype=x.dtype, device=x.device)
     bitmask = torch.empty((rows, (cols + 7) // 8), dtype=torch.uint8, device=x.device)
     row_offsets = torch.empty(rows, dtype=torch.int64, device=x.device)
     nnz = torch.empty(1, dtype=torch.int64, device=x.device)
     if mask is None:
+        ws = _bitmask_workspace(rows, cols, x.device)
         check(lib().ctb_bitmask_compress(ptr(x), i32(DT[x.dtype]), i64(rows), i64(cols), ptr(values), ptr(bitmask),
-                                         ptr(row_offsets), ptr(nnz), stream_of(x)))
+                                         ptr(row_offsets), ptr(nnz), ptr(ws), stream_of(x)))
     else:
         m = _c(mask).view(torch.uint8)
         check(lib().ctb_masked_compress(ptr(x), ptr(m), i32(DT[x.dtype]), i64(rows), i64(cols), ptr(values), ptr(bitmask),
                                         ptr(row_offsets), ptr(nnz), stream_of(x)))
+    if not sync:  # full-capacity values buffer and the device-side count: no host round trip
+        return values, bitmask, row_offsets, nnz
     return values[: int(nnz.item())], bitmask, row_offsets
 
 
@@ -284,7 +293,7 @@ def bitmask_decompress(values, bitmask, shape):
     values, bitmask = _c(values.flatten()), _c(bitmask)
     rows, cols = int(shape[0]), int(shape[1])
     out = torch.empty((rows, cols), dtype=values.dtype, device=bitmask.device)
-    ws = torch.empty(max(rows, 1), dtype=torch.int64, device=bitmask.device)
+    ws = _bitmask_workspace(rows, cols, bitmask.device)
     check(lib().ctb_bitmask_decompress(ptr(values), ptr(bitmask), i32(DT[values.dtype]), i64(rows), i64(cols), ptr(out), ptr(ws),
                                        stream_of(bitmask)))
     return out
@@ -296,7 +305,7 @@ def sparse24_decompress(values, bitmask, shape):
     values, bitmask = _c(values.flatten()), _c(bitmask)
     rows, cols = int(shape[0]), int(shape[1])
     out = torch.empty((rows, cols), dtype=values.dtype, device=bitmask.device)
-    ws = torch.empty(max(rows, 1) + 2, dtype=torch.int64, device=bitmask.device)
+    ws = _bitmask_workspace(rows, cols, bitmask.device)
     check(lib().ctb_sparse24_decompress(ptr(values), ptr(bitmask), i32(DT[values.dtype]), i64(rows), i64(cols), ptr(out), ptr(ws),
                                         stream_of(bitmask)))
     return out

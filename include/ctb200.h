@@ -169,9 +169,13 @@ int ctb_sparse24_compress(const void *x, int32_t dtype, int64_t rows, int64_t co
  * out_values needs room for rows*cols elements; the first *out_nnz (device int64) are valid,
  * row-major.  out_row_offsets is int64 [rows] (exclusive prefix of per-row counts).
  * Elements equal to zero (+0.0 and -0.0) are dropped; NaN is kept. */
+/* `workspace`: ctb_bitmask_workspace_bytes(rows, cols) bytes of device scratch (contents ignored); with it the
+ * codec runs as a single pass (ticketed tiles + decoupled look-back, bounded waits); NULL selects the three-kernel
+ * count / scan / scatter path. */
+int64_t ctb_bitmask_workspace_bytes(int64_t rows, int64_t cols);
 int ctb_bitmask_compress(const void *x, int32_t dtype, int64_t rows, int64_t cols, void *out_values,
                          uint8_t *out_bitmask, int64_t *out_row_offsets, int64_t *out_nnz,
-                         void *stream);
+                         void *workspace, void *stream);
 /* The same compaction with the keep-mask given explicitly (uint8 0/1 [rows, cols]): the reference's
  * `tensor[bytemasks]` + pack_bitmasks (sparse_24_bitmask.py:192-203) for shapes the fused 2:4 kernel
  * does not take (cols % 8 != 0). */
@@ -180,14 +184,14 @@ int ctb_masked_compress(const void *x, const uint8_t *bytemask, int32_t dtype, i
                         int64_t *out_nnz, void *stream);
 /* sparse_bitmask.py:152-169 bitmask_decompress and sparse_24_bitmask.py:206-224
  * sparse24_bitmask_decompress: zeros, then values scattered row-major to the set bits.
- * `workspace` is device scratch of rows*8 bytes (per-row start offsets are rebuilt from the
- * bitmask; the reference does not consult row_offsets either). */
+ * `workspace` is device scratch of ctb_bitmask_workspace_bytes(rows, cols) bytes (start offsets are rebuilt
+ * from the bitmask; the reference does not consult row_offsets either). */
 int ctb_bitmask_decompress(const void *values, const uint8_t *bitmask, int32_t dtype, int64_t rows,
                            int64_t cols, void *out, void *workspace, void *stream);
 
 /* sparse_24_bitmask.py:206-224 sparse24_bitmask_decompress.  Same result as ctb_bitmask_decompress for any
  * bitmask; when the bitmask keeps exactly two of every four columns (what the 2:4 compressor writes) a
- * scan-free kernel does the work and the generic kernels return at once.  workspace: rows*8 + 16 bytes. */
+ * scan-free kernel does the work and the generic kernels return at once.  workspace: ctb_bitmask_workspace_bytes(). */
 int ctb_sparse24_decompress(const void *values, const uint8_t *bitmask, int32_t dtype, int64_t rows,
                             int64_t cols, void *out, void *workspace, void *stream);
 

@@ -31,7 +31,8 @@ def test_static_scratch_decompress_matches_twice():
             x = x.to(dtype).cuda()
             values, bitmask, _ = ops.bitmask_compress(x)
             want = torch.empty_like(x)
-            ws = torch.empty(rows, dtype=torch.int64, device="cuda")
+            lib.ctb_bitmask_workspace_bytes.restype = ctypes.c_int64
+            ws = torch.empty(int(lib.ctb_bitmask_workspace_bytes(L.i64(rows), L.i64(cols))), dtype=torch.uint8, device="cuda")
             got = torch.full_like(x, 7.0)
             assert _call(lib.ctb_bitmask_decompress, values, bitmask, rows, cols, want, L.ptr(ws)) == 0
             assert _call(lib.ctb_bitmask_decompress_static, values, bitmask, rows, cols, got) == 0
