@@ -415,29 +415,40 @@ __device__ __forceinline__ int block_excl_scan16(int v, int &total, int *wsum) {
     return base + inc - v;
 }
 
-// exclusive prefix of tile `tile` given its own total; publishes the tile's words.  One thread calls this.
+// exclusive prefix of tile `tile` given its own total; publishes the tile's words.  Called by all 32 lanes of one
+// warp: each round inspects the 32 preceding tiles at once and stops at the nearest published inclusive prefix.
 __device__ __forceinline__ unsigned long long look_back(volatile unsigned long long *state, unsigned int tile, unsigned long long total, int *error) {
+    const int lane = threadIdx.x & 31;
     if (tile == 0) {
-        state[0] = kFlagIncl | total;
+        if (lane == 0) state[0] = kFlagIncl | total;
         return 0;
     }
-    state[tile] = kFlagAgg | total;
+    if (lane == 0) state[tile] = kFlagAgg | total;
     unsigned long long run = 0;
+    long long top = (long long)tile - 1;
     const long long t0 = clock64();
-    for (long long j = (long long)tile - 1; j >= 0; --j) {
-        unsigned long long v = state[j];
-        while ((v >> 62) == 0) {
+    for (;;) {
+        const long long idx = top - lane;
+        unsigned long long v = idx >= 0 ? state[idx] : kFlagIncl;  // before the first tile: an inclusive prefix of zero
+        const unsigned int incl = __ballot_sync(0xFFFFFFFFu, (v >> 62) == 2);
+        const int first = incl ? __ffs(incl) - 1 : 32;
+        const unsigned int need = first == 32 ? 0xFFFFFFFFu : ((2u << first) - 1u);
+        const unsigned int invalid = __ballot_sync(0xFFFFFFFFu, (v >> 62) == 0) & need;
+        if (invalid) {  // a predecessor has not published yet: look again
             if (clock64() - t0 > kLookBackCycles) {
-                atomicExch(error, 1);
-                v = kFlagIncl;  // give up: treat the rest as empty so the kernel still terminates
-                break;
+                if (lane == 0) atomicExch(error, 1);
+                break;  // give up with what was summed so far so that the kernel still terminates
             }
-            v = state[j];
+            continue;
         }
-        run += v & kValMask;
-        if ((v >> 62) == 2) break;
+        unsigned long long c = ((need >> lane) & 1u) ? (v & kValMask) : 0ull;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xFFFFFFFFu, c, o);
+        run += c;
+        if (first < 32) break;
+        top -= 32;
     }
-    state[tile] = kFlagIncl | (run + total);
+    if (lane == 0) state[tile] = kFlagIncl | (run + total);
     return run;
 }
 
@@ -467,7 +478,10 @@ __global__ void __launch_bounds__(kThreads) bm_compress_onepass_kernel(const voi
         }
         int total;
         const int excl = block_excl_scan16(__popc(mask), total, wsum);
-        if (threadIdx.x == 0) s_prefix = look_back(state, tile, (unsigned long long)total, &ctl->error);
+        if (threadIdx.x < 32) {
+            const unsigned long long pfx = look_back(state, tile, (unsigned long long)total, &ctl->error);
+            if (threadIdx.x == 0) s_prefix = pfx;
+        }
         if (u0 < units) {
             if (u0 + 1 < units) *reinterpret_cast<uint16_t *>(bitmask + u0) = (uint16_t)mask;
             else bitmask[u0] = (uint8_t)mask;
@@ -510,7 +524,10 @@ __global__ void __launch_bounds__(kThreads) bm_expand_onepass_kernel(const void 
         else if (u0 < units) mask = bitmask[u0];
         int total;
         const int excl = block_excl_scan16(__popc(mask), total, wsum);
-        if (threadIdx.x == 0) s_prefix = look_back(state, tile, (unsigned long long)total, &ctl->error);
+        if (threadIdx.x < 32) {
+            const unsigned long long pfx = look_back(state, tile, (unsigned long long)total, &ctl->error);
+            if (threadIdx.x == 0) s_prefix = pfx;
+        }
         __syncthreads();
         int64_t src = (int64_t)s_prefix + excl;
 #pragma unroll
