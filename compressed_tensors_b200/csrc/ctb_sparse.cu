@@ -429,7 +429,8 @@ __device__ __forceinline__ unsigned long long look_back(volatile unsigned long l
     const long long t0 = clock64();
     for (;;) {
         const long long idx = top - lane;
-        unsigned long long v = idx >= 0 ? state[idx] : kFlagIncl;  // before the first tile: an inclusive prefix of zero
+        unsigned long long v = 2ull << 62;  // before the first tile: an inclusive prefix of zero
+        if (idx >= 0) v = state[idx];
         const unsigned int incl = __ballot_sync(0xFFFFFFFFu, (v >> 62) == 2);
         const int first = incl ? __ffs(incl) - 1 : 32;
         const unsigned int need = first == 32 ? 0xFFFFFFFFu : ((2u << first) - 1u);
