@@ -5,6 +5,7 @@
 // columns 8k..8k+7 with column 8k+j in bit j (numpy.packbits, bitorder="little"), row_offsets is the
 // int64 exclusive prefix of the per-row counts.
 #include "ctb_codec.cuh"
+#include "ctb_sparse24_simd.cuh"
 
 namespace ctb {
 
@@ -99,8 +100,53 @@ __global__ void __launch_bounds__(kThreads) sparse24_mask_kernel(const void *x, 
     }
 }
 
-// sparse24_bitmask_compress, cols % 8 == 0: one thread per 8 elements = 2 runs = 4 kept values and
-// one bitmask byte; four neighbouring lanes merge their bytes into one 32-bit store.
+// sparse24_bitmask_compress, cols % 8 == 0, 8- and 16-bit elements: one thread per 16 elements (two bitmask bytes,
+// eight kept values).  The keep rule runs on SIMD lanes of 32-bit words (ctb_sparse24_simd.cuh), about six integer
+// instructions per element, so the kernel stays bound by memory rather than by the selection logic.
+template <int ES>
+__global__ void __launch_bounds__(kThreads) sparse24_compress_simd_kernel(const void *x, int64_t units, void *values, uint8_t *bitmask) {
+    static_assert(ES == 1 || ES == 2, "SIMD lanes are 8 or 16 bits");
+    const int64_t items = (units + 1) >> 1;
+    for (int64_t it = (int64_t)blockIdx.x * kThreads + threadIdx.x; it < items; it += (int64_t)gridDim.x * kThreads) {
+        const int64_t u = it * 2;
+        const bool both = u + 1 < units;
+        if constexpr (ES == 1) {
+            uint4 w = make_uint4(0, 0, 0, 0);
+            if (both) w = ld_stream((const char *)x + u * 8);
+            else {
+                const uint2 t = ld_stream8((const char *)x + u * 8);
+                w.x = t.x;
+                w.y = t.y;
+            }
+            uint32_t v0, v1, m;
+            sparse24_pack_u8x16(w.x, w.y, w.z, w.w, v0, v1, m);
+            if (both) {
+                st_stream8((char *)values + u * 4, make_uint2(v0, v1));
+                *reinterpret_cast<uint16_t *>(bitmask + u) = (uint16_t)m;
+            } else {
+                st_stream4((char *)values + u * 4, v0);
+                bitmask[u] = (uint8_t)m;
+            }
+        } else {
+            const uint4 a = ld_stream((const char *)x + u * 16);
+            uint4 b = make_uint4(0, 0, 0, 0);
+            if (both) b = ld_stream((const char *)x + u * 16 + 16);
+            uint32_t v0, v1, v2, v3, m0, m1;
+            sparse24_pack_u16x8(a.x, a.y, a.z, a.w, v0, v1, m0);
+            sparse24_pack_u16x8(b.x, b.y, b.z, b.w, v2, v3, m1);
+            if (both) {
+                st_stream((char *)values + u * 8, make_uint4(v0, v1, v2, v3));
+                *reinterpret_cast<uint16_t *>(bitmask + u) = (uint16_t)(m0 | (m1 << 8));
+            } else {
+                st_stream8((char *)values + u * 8, make_uint2(v0, v1));
+                bitmask[u] = (uint8_t)m0;
+            }
+        }
+    }
+}
+
+// the same for 32-bit elements (and the model the SIMD kernels are tested against): one thread per 8 elements =
+// 2 runs = 4 kept values and one bitmask byte; four neighbouring lanes merge their bytes into one 32-bit store.
 template <int ES, bool IS_INT8>
 __global__ void __launch_bounds__(kThreads) sparse24_compress_kernel(const void *x, uint32_t nzm, int64_t units, void *values, uint8_t *bitmask) {
     const int64_t padded = (units + 31) & ~(int64_t)31;
@@ -137,10 +183,69 @@ __global__ void __launch_bounds__(kThreads) sparse24_compress_kernel(const void 
     }
 }
 
-// Fast expansion of a 2:4 compressed tensor (cols % 8 == 0): every run of four columns keeps exactly two, so
-// the values of byte u of the bitmask start at 4u and no prefix sum is needed.  A bitmask that breaks the
-// two-per-run rule raises *irregular; the generic kernels then redo the tensor (they are launched right
-// behind this one and return at once when the flag is clear).
+// Fast expansion of a 2:4 compressed tensor (cols % 8 == 0), 8- and 16-bit elements: every run of four columns
+// keeps exactly two, so the values of bitmask byte u start at 4u and no prefix sum is needed.  One thread per 16
+// elements; a run is rebuilt by ONE byte permute of its two values whose selector comes from a 16-entry table
+// indexed by the run's mask nibble.  A bitmask that breaks the two-per-run rule raises *irregular; the generic
+// kernels then redo the tensor (they are launched right behind this one and return at once when the flag is clear).
+template <int ES>
+__global__ void __launch_bounds__(kThreads) sparse24_expand_simd_kernel(const void *values, const uint8_t *bitmask, int64_t units, void *out, int *irregular) {
+    static_assert(ES == 1 || ES == 2, "byte-permute expansion is for 8- and 16-bit elements");
+    // selector of a run with mask nibble n: the lower set bit takes the first value, the upper one the second, the
+    // rest a zero byte (source byte 4).  ES == 1: four byte selectors; ES == 2: two words of two halfword selectors.
+    __shared__ uint32_t lut[16];
+    if (threadIdx.x < 16) {
+        const uint32_t n = threadIdx.x;
+        uint32_t sel = 0;
+        int seen = 0;
+        for (int i = 0; i < 4; ++i) {
+            uint32_t src = 4;  // zero
+            if ((n >> i) & 1) src = seen++ ? 1 : 0;
+            if (ES == 1) sel |= src << (4 * i);
+            else sel |= (src == 4 ? 0x44u : src == 0 ? 0x10u : 0x32u) << (8 * i);
+        }
+        lut[n] = sel;
+    }
+    __syncthreads();
+    bool bad = false;
+    const int64_t items = (units + 1) >> 1;
+    for (int64_t it = (int64_t)blockIdx.x * kThreads + threadIdx.x; it < items; it += (int64_t)gridDim.x * kThreads) {
+        const int64_t u = it * 2;
+        const bool both = u + 1 < units;
+        uint32_t m = both ? (uint32_t) * reinterpret_cast<const uint16_t *>(bitmask + u) : (uint32_t)bitmask[u];
+        {  // every nibble must have exactly two bits set (the absent second unit counts as regular)
+            uint32_t c = m - ((m >> 1) & 0x5555u);
+            c = (c & 0x3333u) + ((c >> 2) & 0x3333u);
+            bad |= c != (both ? 0x2222u : 0x0022u);
+        }
+        if constexpr (ES == 1) {
+            uint2 v = make_uint2(0, 0);
+            if (both) v = ld_stream8((const char *)values + u * 4);
+            else v.x = ld_stream4((const char *)values + u * 4);
+            const uint32_t o0 = prmt(v.x, 0, lut[m & 0xFu]);
+            const uint32_t o1 = prmt(v.x >> 16, 0, lut[(m >> 4) & 0xFu]);
+            const uint32_t o2 = prmt(v.y, 0, lut[(m >> 8) & 0xFu]);
+            const uint32_t o3 = prmt(v.y >> 16, 0, lut[(m >> 12) & 0xFu]);
+            if (both) st_stream((char *)out + u * 8, make_uint4(o0, o1, o2, o3));
+            else st_stream8((char *)out + u * 8, make_uint2(o0, o1));
+        } else {
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (both) v = ld_stream((const char *)values + u * 8);
+            else {
+                const uint2 t = ld_stream8((const char *)values + u * 8);
+                v.x = t.x;
+                v.y = t.y;
+            }
+            const uint32_t s0 = lut[m & 0xFu], s1 = lut[(m >> 4) & 0xFu], s2 = lut[(m >> 8) & 0xFu], s3 = lut[(m >> 12) & 0xFu];
+            st_stream((char *)out + u * 16, make_uint4(prmt(v.x, 0, s0 & 0xFFFFu), prmt(v.x, 0, s0 >> 16), prmt(v.y, 0, s1 & 0xFFFFu), prmt(v.y, 0, s1 >> 16)));
+            if (both)
+                st_stream((char *)out + u * 16 + 16, make_uint4(prmt(v.z, 0, s2 & 0xFFFFu), prmt(v.z, 0, s2 >> 16), prmt(v.w, 0, s3 & 0xFFFFu), prmt(v.w, 0, s3 >> 16)));
+        }
+    }
+    if (__any_sync(0xFFFFFFFFu, bad) && (threadIdx.x & 31) == 0) atomicExch(irregular, 1);
+}
+
+// the same for 32-bit elements: one thread per 8 elements
 template <int ES>
 __global__ void __launch_bounds__(kThreads) sparse24_expand_kernel(const void *values, const uint8_t *bitmask, int64_t units, void *out, int *irregular) {
     bool bad = false;
@@ -374,25 +479,21 @@ __global__ void __launch_bounds__(kThreads) bm_expand_kernel(const void *values,
 }  // namespace ctb
 
 
-// ------------------------------------------------------------------ single-pass codec (cols % 8 == 0)
+// ------------------------------------------------------------------ tile-parallel bitmask codec (cols % 8 == 0)
 //
-// The non-zero values of the whole tensor are one row-major stream, so compaction is a prefix sum over flat tiles
-// of 4096 elements.  Tiles are handed out by an atomic ticket (a tile only ever waits for tiles that were handed out
-// before it, which are running or done), each tile publishes its count and then its inclusive prefix in one 64-bit
-// status word, and a tile finds its starting offset by walking back over its predecessors' words ("decoupled
-// look-back").  Every element is read once and every output written once.  The walk is bounded: if a predecessor's
-// word does not appear within the budget the tile raises the error word and uses what it has.
+// The tensor is cut into tiles of 4096 consecutive elements.  A first kernel counts the kept elements of every
+// tile (writing the bitmask on the way, for compress) and the LAST block to finish turns the counts into exclusive
+// prefixes in place; a second kernel then compacts (or expands) every tile independently from its prefix.  Nothing
+// waits on anything inside a kernel, so the tiles run at full occupancy; the second read of the dense tensor
+// comes from L2 when the tensor fits there.
 namespace ctb {
 
-constexpr int kOnePassEpt = 16;                         // elements per thread
-constexpr int kOnePassTile = kThreads * kOnePassEpt;    // 4096 elements per tile
-constexpr unsigned long long kFlagAgg = 1ull << 62, kFlagIncl = 2ull << 62, kValMask = (1ull << 62) - 1;
-constexpr long long kLookBackCycles = 2000000000LL;
+constexpr int kTileEpt = 16;                      // elements per thread
+constexpr int kTileElems = kThreads * kTileEpt;   // 4096 elements per tile
 
-struct OnePassCtl {            // lives at the start of the workspace, zeroed by the entry point before every launch
-    unsigned int ticket;
-    int error;
-    unsigned long long pad;
+struct TileCtl {            // lives at the start of the workspace, zeroed by the entry point before every launch
+    unsigned int done;      // blocks of the counting kernel that have finished
+    unsigned int pad[3];
 };
 
 __device__ __forceinline__ int block_excl_scan16(int v, int &total, int *wsum) {
@@ -415,84 +516,197 @@ __device__ __forceinline__ int block_excl_scan16(int v, int &total, int *wsum) {
     return base + inc - v;
 }
 
-// exclusive prefix of tile `tile` given its own total; publishes the tile's words.  Called by all 32 lanes of one
-// warp: each round inspects the 32 preceding tiles at once and stops at the nearest published inclusive prefix.
-__device__ __forceinline__ unsigned long long look_back(volatile unsigned long long *state, unsigned int tile, unsigned long long total, int *error) {
-    const int lane = threadIdx.x & 31;
-    if (tile == 0) {
-        if (lane == 0) state[0] = kFlagIncl | total;
-        return 0;
-    }
-    if (lane == 0) state[tile] = kFlagAgg | total;
-    unsigned long long run = 0;
-    long long top = (long long)tile - 1;
-    const long long t0 = clock64();
-    for (;;) {
-        const long long idx = top - lane;
-        unsigned long long v = 2ull << 62;  // before the first tile: an inclusive prefix of zero
-        if (idx >= 0) v = state[idx];
-        const unsigned int incl = __ballot_sync(0xFFFFFFFFu, (v >> 62) == 2);
-        const int first = incl ? __ffs(incl) - 1 : 32;
-        const unsigned int need = first == 32 ? 0xFFFFFFFFu : ((2u << first) - 1u);
-        const unsigned int invalid = __ballot_sync(0xFFFFFFFFu, (v >> 62) == 0) & need;
-        if (invalid) {  // a predecessor has not published yet: look again
-            if (clock64() - t0 > kLookBackCycles) {
-                if (lane == 0) atomicExch(error, 1);
-                break;  // give up with what was summed so far so that the kernel still terminates
-            }
-            continue;
-        }
-        unsigned long long c = ((need >> lane) & 1u) ? (v & kValMask) : 0ull;
+// Called by every thread of every block once the block's counts are written: the last block to arrive replaces
+// pfx[0..ntiles) (per-tile counts) by their exclusive prefix sums and stores the total.
+__device__ __forceinline__ void last_block_scan(unsigned long long *pfx, int64_t ntiles, TileCtl *ctl, int64_t *total_out) {
+    __shared__ bool s_last;
+    __shared__ unsigned long long s_w[kThreads / 32];
+    __shared__ unsigned long long s_carry;
+    __threadfence();  // this block's counts are visible before its arrival is
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = atomicAdd(&ctl->done, 1u) == gridDim.x - 1;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    if (threadIdx.x == 0) s_carry = 0;
+    __syncthreads();
+    constexpr int kPer = 4;  // consecutive entries per thread and sweep
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    for (int64_t base = 0; base < ntiles; base += (int64_t)kThreads * kPer) {
+        const int64_t i0 = base + (int64_t)threadIdx.x * kPer;
+        unsigned long long v[kPer], sum = 0;
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xFFFFFFFFu, c, o);
-        run += c;
-        if (first < 32) break;
-        top -= 32;
+        for (int j = 0; j < kPer; ++j) {
+            v[j] = i0 + j < ntiles ? __ldcg(pfx + i0 + j) : 0ull;  // written by other blocks: read at L2
+            sum += v[j];
+        }
+        unsigned long long inc = sum;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const unsigned long long t = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+            if (lane >= o) inc += t;
+        }
+        if (lane == 31) s_w[w] = inc;
+        __syncthreads();
+        unsigned long long run = s_carry + inc - sum;
+        unsigned long long all = 0;
+#pragma unroll
+        for (int i = 0; i < kThreads / 32; ++i) {
+            if (i < w) run += s_w[i];
+            all += s_w[i];
+        }
+#pragma unroll
+        for (int j = 0; j < kPer; ++j) {
+            if (i0 + j < ntiles) pfx[i0 + j] = run;
+            run += v[j];
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) s_carry += all;
+        __syncthreads();
     }
-    if (lane == 0) state[tile] = kFlagIncl | (run + total);
-    return run;
+    if (threadIdx.x == 0 && total_out) *total_out = (int64_t)s_carry;
 }
 
+// raw 16-byte (ES = 2), 8-byte (ES = 1) or 32-byte (ES = 4) image of one 8-element unit; KEEP = the dense tensor is
+// read again by the next kernel, so leave it in L2 (default policy) instead of streaming it through
+template <int ES, bool KEEP>
+__device__ __forceinline__ Raw8 load_unit_raw(const void *x, int64_t unit) {
+    Raw8 r;
+    r.a = make_uint4(0, 0, 0, 0);
+    r.b = make_uint4(0, 0, 0, 0);
+    const char *p = (const char *)x + unit * (8 * ES);
+    if constexpr (ES == 2) r.a = KEEP ? *reinterpret_cast<const uint4 *>(p) : ld_stream(p);
+    else if constexpr (ES == 1) {
+        const uint2 t = KEEP ? *reinterpret_cast<const uint2 *>(p) : ld_stream8(p);
+        r.a.x = t.x;
+        r.a.y = t.y;
+    } else {
+        r.a = KEEP ? *reinterpret_cast<const uint4 *>(p) : ld_stream(p);
+        r.b = KEEP ? *reinterpret_cast<const uint4 *>(p + 16) : ld_stream(p + 16);
+    }
+    return r;
+}
 template <int ES>
-__global__ void __launch_bounds__(kThreads) bm_compress_onepass_kernel(const void *x, uint32_t nzm, int64_t units, int64_t cols, int64_t rows, void *values,
-                                                                       uint8_t *bitmask, int64_t *row_offsets, int64_t *nnz, OnePassCtl *ctl,
-                                                                       volatile unsigned long long *state) {
-    __shared__ uint32_t stage[kOnePassTile];
-    __shared__ int wsum[kThreads / 32];
-    __shared__ unsigned int s_tile;
-    __shared__ unsigned long long s_prefix;
-    const unsigned int ntiles = (unsigned int)((units * 8 + kOnePassTile - 1) / kOnePassTile);
-    for (;;) {
-        if (threadIdx.x == 0) s_tile = atomicAdd(&ctl->ticket, 1u);
-        __syncthreads();
-        const unsigned int tile = s_tile;
-        if (tile >= ntiles) break;
-        const int64_t u0 = ((int64_t)tile * kThreads + threadIdx.x) * 2;  // first of this thread's two 8-element units
-        uint32_t b[16];
-        uint32_t mask = 0;
+__device__ __forceinline__ void unit_bits(const Raw8 &r, uint32_t (&b)[8]) {
+    if constexpr (ES == 2) {
+        const uint32_t w[4] = {r.a.x, r.a.y, r.a.z, r.a.w};
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            uint32_t t8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-            if (u0 + h < units) mask |= unit_mask<ES>(x, u0 + h, nzm, t8) << (8 * h);
+        for (int i = 0; i < 4; ++i) { b[2 * i] = w[i] & 0xFFFFu; b[2 * i + 1] = w[i] >> 16; }
+    } else if constexpr (ES == 1) {
+        const uint32_t w[2] = {r.a.x, r.a.y};
 #pragma unroll
-            for (int j = 0; j < 8; ++j) b[8 * h + j] = t8[j];
+        for (int i = 0; i < 8; ++i) b[i] = (w[i >> 2] >> (8 * (i & 3))) & 0xFFu;
+    } else {
+        b[0] = r.a.x; b[1] = r.a.y; b[2] = r.a.z; b[3] = r.a.w;
+        b[4] = r.b.x; b[5] = r.b.y; b[6] = r.b.z; b[7] = r.b.w;
+    }
+}
+
+// 8-bit non-zero mask of one unit straight from its packed words (no per-element unpacking)
+template <int ES>
+__device__ __forceinline__ uint32_t unit_nz_mask(const Raw8 &r, uint32_t nzm) {
+    uint32_t m = 0;
+    if constexpr (ES == 2) {
+        const uint32_t w[4] = {r.a.x, r.a.y, r.a.z, r.a.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            m |= ((w[i] & nzm) != 0 ? 1u : 0u) << (2 * i);
+            m |= ((w[i] & (nzm << 16)) != 0 ? 1u : 0u) << (2 * i + 1);
         }
+    } else if constexpr (ES == 1) {
+        const uint32_t w[2] = {r.a.x, r.a.y};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) m |= ((w[i >> 2] & (nzm << (8 * (i & 3)))) != 0 ? 1u : 0u) << i;
+    } else {
+        const uint32_t w[8] = {r.a.x, r.a.y, r.a.z, r.a.w, r.b.x, r.b.y, r.b.z, r.b.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) m |= ((w[i] & nzm) != 0 ? 1u : 0u) << i;
+    }
+    return m;
+}
+
+__device__ __forceinline__ int block_count(int c, int *wsum) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xFFFFFFFFu, c, o);
+    if ((threadIdx.x & 31) == 0) wsum[threadIdx.x >> 5] = c;
+    __syncthreads();
+    int t = 0;
+#pragma unroll
+    for (int i = 0; i < kThreads / 32; ++i) t += wsum[i];
+    __syncthreads();  // wsum is reused by the next tile
+    return t;
+}
+
+// compress, kernel 1: bitmask bytes and per-tile counts, then the prefix scan by the last block
+template <int ES>
+__global__ void __launch_bounds__(kThreads) bm_tile_count_kernel(const void *x, uint32_t nzm, int64_t units, uint8_t *bitmask,
+                                                                 unsigned long long *pfx, TileCtl *ctl, int64_t *nnz) {
+    __shared__ int wsum[kThreads / 32];
+    const int64_t ntiles = (units * 8 + kTileElems - 1) / kTileElems;
+    for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+        const int64_t u0 = (tile * kThreads + threadIdx.x) * 2;
+        uint32_t mask = 0;
+        if (u0 + 1 < units) {
+            const Raw8 r0 = load_unit_raw<ES, true>(x, u0), r1 = load_unit_raw<ES, true>(x, u0 + 1);
+            mask = unit_nz_mask<ES>(r0, nzm) | (unit_nz_mask<ES>(r1, nzm) << 8);
+            *reinterpret_cast<uint16_t *>(bitmask + u0) = (uint16_t)mask;
+        } else if (u0 < units) {
+            mask = unit_nz_mask<ES>(load_unit_raw<ES, true>(x, u0), nzm);
+            bitmask[u0] = (uint8_t)mask;
+        }
+        const int total = block_count(__popc(mask), wsum);
+        if (threadIdx.x == 0) pfx[tile] = (unsigned long long)total;
+    }
+    last_block_scan(pfx, ntiles, ctl, nnz);
+}
+
+// decompress, kernel 1: per-tile counts from the bitmask, then the prefix scan by the last block
+__global__ void __launch_bounds__(kThreads) bm_tile_popcount_kernel(const uint8_t *bitmask, int64_t units, unsigned long long *pfx, TileCtl *ctl) {
+    __shared__ int wsum[kThreads / 32];
+    const int64_t ntiles = (units * 8 + kTileElems - 1) / kTileElems;
+    for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+        const int64_t u0 = (tile * kThreads + threadIdx.x) * 2;
+        uint32_t mask = 0;
+        if (u0 + 1 < units) mask = *reinterpret_cast<const uint16_t *>(bitmask + u0);
+        else if (u0 < units) mask = bitmask[u0];
+        const int total = block_count(__popc(mask), wsum);
+        if (threadIdx.x == 0) pfx[tile] = (unsigned long long)total;
+    }
+    last_block_scan(pfx, ntiles, ctl, nullptr);
+}
+
+// compress, kernel 2: compact every tile to values[pfx[tile] ...) through shared memory, and the row offsets
+template <int ES>
+__global__ void __launch_bounds__(kThreads) bm_tile_scatter_kernel(const void *x, const uint8_t *bitmask, int64_t units, int64_t cols, int64_t rows,
+                                                                   const unsigned long long *pfx, void *values, int64_t *row_offsets) {
+    __shared__ uint32_t stage[kTileElems];
+    __shared__ int wsum[kThreads / 32];
+    const int64_t ntiles = (units * 8 + kTileElems - 1) / kTileElems;
+    for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+        const int64_t u0 = (tile * kThreads + threadIdx.x) * 2;  // first of this thread's two 8-element units
+        uint32_t mask = 0;
+        Raw8 raw[2];
+        raw[0].a = raw[0].b = raw[1].a = raw[1].b = make_uint4(0, 0, 0, 0);
+        if (u0 + 1 < units) {
+            mask = *reinterpret_cast<const uint16_t *>(bitmask + u0);
+            raw[0] = load_unit_raw<ES, false>(x, u0);
+            raw[1] = load_unit_raw<ES, false>(x, u0 + 1);
+        } else if (u0 < units) {
+            mask = bitmask[u0];
+            raw[0] = load_unit_raw<ES, false>(x, u0);
+        }
+        const unsigned long long prefix = pfx[tile];
         int total;
         const int excl = block_excl_scan16(__popc(mask), total, wsum);
-        if (threadIdx.x < 32) {
-            const unsigned long long pfx = look_back(state, tile, (unsigned long long)total, &ctl->error);
-            if (threadIdx.x == 0) s_prefix = pfx;
-        }
-        if (u0 < units) {
-            if (u0 + 1 < units) *reinterpret_cast<uint16_t *>(bitmask + u0) = (uint16_t)mask;
-            else bitmask[u0] = (uint8_t)mask;
-        }
         int pos = excl;
 #pragma unroll
-        for (int j = 0; j < 16; ++j)
-            if ((mask >> j) & 1) stage[pos++] = b[j];
-        __syncthreads();
-        const unsigned long long prefix = s_prefix;
+        for (int h = 0; h < 2; ++h) {
+            uint32_t b[8];
+            unit_bits<ES>(raw[h], b);
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if ((mask >> (8 * h + j)) & 1) stage[pos++] = b[j];
+        }
         // rows that begin inside this thread's 16 elements (cols is a multiple of 8: only at offset 0 or 8)
         if (u0 < units) {
             const int64_t e0 = u0 * 8;
@@ -501,42 +715,61 @@ __global__ void __launch_bounds__(kThreads) bm_compress_onepass_kernel(const voi
             if (rem == 0) row_offsets[r0] = (int64_t)(prefix + excl);
             if (rem + 8 == cols && r0 + 1 < rows && u0 + 1 < units) row_offsets[r0 + 1] = (int64_t)(prefix + excl + __popc(mask & 0xFFu));
         }
-        for (int i = threadIdx.x; i < total; i += kThreads) store_bits(values, ES, (int64_t)prefix + i, stage[i]);
-        if (tile == ntiles - 1 && threadIdx.x == 0) *nnz = (int64_t)(prefix + total);
         __syncthreads();
+        if constexpr (ES == 2) {
+            // pairs of values per 32-bit store where the destination allows it
+            const int64_t dst0 = (int64_t)prefix;
+            const int odd = (int)(dst0 & 1);
+            if (threadIdx.x == 0 && odd && total > 0) store_bits(values, 2, dst0, stage[0]);
+            const int npairs = (total - odd) / 2;
+            for (int i = threadIdx.x; i < npairs; i += kThreads)
+                reinterpret_cast<uint32_t *>((char *)values + (dst0 + odd) * 2)[i] = stage[odd + 2 * i] | (stage[odd + 2 * i + 1] << 16);
+            if (threadIdx.x == 0 && total > odd && ((total - odd) & 1)) store_bits(values, 2, dst0 + total - 1, stage[total - 1]);
+        } else {
+            for (int i = threadIdx.x; i < total; i += kThreads) store_bits(values, ES, (int64_t)prefix + i, stage[i]);
+        }
+        __syncthreads();  // stage and wsum are reused by the next tile
     }
 }
 
+// decompress, kernel 2: every tile's kept values are one contiguous run of `values`; bring it in with coalesced
+// loads, then every thread rebuilds its 16 elements from shared memory
 template <int ES>
-__global__ void __launch_bounds__(kThreads) bm_expand_onepass_kernel(const void *values, const uint8_t *bitmask, int64_t units, void *out, OnePassCtl *ctl,
-                                                                     volatile unsigned long long *state) {
+__global__ void __launch_bounds__(kThreads) bm_tile_expand_kernel(const void *values, const uint8_t *bitmask, int64_t units, const unsigned long long *pfx,
+                                                                  void *out) {
+    __shared__ uint32_t stage[kTileElems];
     __shared__ int wsum[kThreads / 32];
-    __shared__ unsigned int s_tile;
-    __shared__ unsigned long long s_prefix;
-    const unsigned int ntiles = (unsigned int)((units * 8 + kOnePassTile - 1) / kOnePassTile);
-    for (;;) {
-        if (threadIdx.x == 0) s_tile = atomicAdd(&ctl->ticket, 1u);
-        __syncthreads();
-        const unsigned int tile = s_tile;
-        if (tile >= ntiles) break;
-        const int64_t u0 = ((int64_t)tile * kThreads + threadIdx.x) * 2;
+    const int64_t ntiles = (units * 8 + kTileElems - 1) / kTileElems;
+    for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+        const int64_t u0 = (tile * kThreads + threadIdx.x) * 2;
         uint32_t mask = 0;
         if (u0 + 1 < units) mask = *reinterpret_cast<const uint16_t *>(bitmask + u0);
         else if (u0 < units) mask = bitmask[u0];
+        const int64_t src0 = (int64_t)pfx[tile];
         int total;
         const int excl = block_excl_scan16(__popc(mask), total, wsum);
-        if (threadIdx.x < 32) {
-            const unsigned long long pfx = look_back(state, tile, (unsigned long long)total, &ctl->error);
-            if (threadIdx.x == 0) s_prefix = pfx;
+        if constexpr (ES == 2) {
+            const int odd = (int)(src0 & 1);
+            if (threadIdx.x == 0 && odd && total > 0) stage[0] = load_bits(values, 2, src0);
+            const int npairs = (total - odd) / 2;
+            const uint32_t *v32 = reinterpret_cast<const uint32_t *>((const char *)values + (src0 + odd) * 2);
+            for (int i = threadIdx.x; i < npairs; i += kThreads) {
+                const uint32_t w = ld_stream4(v32 + i);
+                stage[odd + 2 * i] = w & 0xFFFFu;
+                stage[odd + 2 * i + 1] = w >> 16;
+            }
+            if (threadIdx.x == 0 && total > odd && ((total - odd) & 1)) stage[total - 1] = load_bits(values, 2, src0 + total - 1);
+        } else {
+            for (int i = threadIdx.x; i < total; i += kThreads) stage[i] = load_bits(values, ES, src0 + i);
         }
         __syncthreads();
-        int64_t src = (int64_t)s_prefix + excl;
+        int pos = excl;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             if (u0 + h >= units) break;
             uint32_t b[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) b[j] = ((mask >> (8 * h + j)) & 1) ? load_bits(values, ES, src++) : 0u;
+            for (int j = 0; j < 8; ++j) b[j] = ((mask >> (8 * h + j)) & 1) ? stage[pos++] : 0u;
             char *o = (char *)out + (u0 + h) * 8 * ES;
             if constexpr (ES == 2) st_stream(o, make_uint4(b[0] | (b[1] << 16), b[2] | (b[3] << 16), b[4] | (b[5] << 16), b[6] | (b[7] << 16)));
             else if constexpr (ES == 1) st_stream8(o, make_uint2(b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24), b[4] | (b[5] << 8) | (b[6] << 16) | (b[7] << 24)));
@@ -545,7 +778,7 @@ __global__ void __launch_bounds__(kThreads) bm_expand_onepass_kernel(const void 
                 st_stream(o + 16, make_uint4(b[4], b[5], b[6], b[7]));
             }
         }
-        __syncthreads();
+        __syncthreads();  // stage and wsum are reused by the next tile
     }
 }
 
@@ -574,19 +807,23 @@ extern "C" int ctb_sparse24_compress(const void *x, int32_t dtype, int64_t rows,
     if ((rows * cols) % 4 != 0) return fail(CTB_EINVAL_SHAPE, "Tensor size must be a multiple of 4 for TWO_FOUR sparsity");
     if (cols % 8 != 0) return fail(CTB_EUNSUPPORTED, "fused 2:4 compression needs cols %% 8 == 0; use ctb_sparse24_mask + ctb_masked_compress");
     if (!aligned16(x) || !aligned16(values)) return fail(CTB_EINVAL_ALIGN, "buffers must be 16-byte aligned");
+    if (reinterpret_cast<uintptr_t>(bitmask) & 3u) return fail(CTB_EINVAL_ALIGN, "bitmask must be 4-byte aligned");
     int64_t units = rows * cols / 8;
     if (units == 0) return CTB_OK;
-    int grid = grid_for(units, kThreads, 8);
     cudaStream_t st = as_stream(stream);
-    if (e.esize == 2) sparse24_compress_kernel<2, false><<<grid, kThreads, 0, st>>>(x, e.nz_mask, units, values, bitmask);
-    else if (e.esize == 1) sparse24_compress_kernel<1, true><<<grid, kThreads, 0, st>>>(x, e.nz_mask, units, values, bitmask);
-    else sparse24_compress_kernel<4, false><<<grid, kThreads, 0, st>>>(x, e.nz_mask, units, values, bitmask);
-    return after_launch("sparse24_compress_kernel");
+    if (e.esize == 4) {
+        sparse24_compress_kernel<4, false><<<grid_for(units, kThreads, 8), kThreads, 0, st>>>(x, e.nz_mask, units, values, bitmask);
+        return after_launch("sparse24_compress_kernel");
+    }
+    const int grid = grid_for((units + 1) / 2, kThreads, 8);
+    if (e.esize == 2) sparse24_compress_simd_kernel<2><<<grid, kThreads, 0, st>>>(x, units, values, bitmask);
+    else sparse24_compress_simd_kernel<1><<<grid, kThreads, 0, st>>>(x, units, values, bitmask);
+    return after_launch("sparse24_compress_simd_kernel");
 }
 
-static int64_t onepass_bytes(int64_t rows, int64_t cols) {
-    const int64_t tiles = (rows * cols + kOnePassTile - 1) / kOnePassTile;
-    return (int64_t)sizeof(OnePassCtl) + 8 * tiles;
+static int64_t tile_bytes(int64_t rows, int64_t cols) {
+    const int64_t tiles = (rows * cols + kTileElems - 1) / kTileElems;
+    return (int64_t)sizeof(TileCtl) + 8 * tiles;  // arrival counter, then one count / prefix word per tile
 }
 
 static int compress_impl(const void *x, const uint8_t *pred, int32_t dtype, int64_t rows, int64_t cols, void *values, uint8_t *bitmask,
@@ -602,18 +839,23 @@ static int compress_impl(const void *x, const uint8_t *pred, int32_t dtype, int6
         return CTB_OK;
     }
     const bool vec = !pred && cols % 8 == 0 && aligned16(x);
-    if (vec && workspace != nullptr && rows * cols / kOnePassTile < 0x7FFFFFFF) {
-        // single pass: ticketed tiles + decoupled look-back
-        cudaError_t ce = cudaMemsetAsync(workspace, 0, (size_t)onepass_bytes(rows, cols), st);
+    if (vec && workspace != nullptr && (reinterpret_cast<uintptr_t>(values) & 3u) == 0 && (reinterpret_cast<uintptr_t>(bitmask) & 1u) == 0) {
+        // tile-parallel: count + scan, then scatter
+        TileCtl *ctl = static_cast<TileCtl *>(workspace);
+        unsigned long long *pfx = reinterpret_cast<unsigned long long *>(ctl + 1);
+        cudaError_t ce = cudaMemsetAsync(ctl, 0, sizeof(TileCtl), st);
         if (ce != cudaSuccess) return fail(CTB_ECUDA, "cudaMemsetAsync: %s", cudaGetErrorString(ce));
-        OnePassCtl *ctl = static_cast<OnePassCtl *>(workspace);
-        volatile unsigned long long *state = reinterpret_cast<volatile unsigned long long *>(ctl + 1);
         const int64_t units = rows * cols / 8;
-        int g1 = grid_for(units * 8, kOnePassTile, 6);
-        if (e.esize == 2) bm_compress_onepass_kernel<2><<<g1, kThreads, 0, st>>>(x, e.nz_mask, units, cols, rows, values, bitmask, row_offsets, nnz, ctl, state);
-        else if (e.esize == 1) bm_compress_onepass_kernel<1><<<g1, kThreads, 0, st>>>(x, e.nz_mask, units, cols, rows, values, bitmask, row_offsets, nnz, ctl, state);
-        else bm_compress_onepass_kernel<4><<<g1, kThreads, 0, st>>>(x, e.nz_mask, units, cols, rows, values, bitmask, row_offsets, nnz, ctl, state);
-        return after_launch("bm_compress_onepass_kernel");
+        const int g1 = grid_for(units * 8, kTileElems, 8);
+        int rc;
+        if (e.esize == 2) bm_tile_count_kernel<2><<<g1, kThreads, 0, st>>>(x, e.nz_mask, units, bitmask, pfx, ctl, nnz);
+        else if (e.esize == 1) bm_tile_count_kernel<1><<<g1, kThreads, 0, st>>>(x, e.nz_mask, units, bitmask, pfx, ctl, nnz);
+        else bm_tile_count_kernel<4><<<g1, kThreads, 0, st>>>(x, e.nz_mask, units, bitmask, pfx, ctl, nnz);
+        if ((rc = after_launch("bm_tile_count_kernel"))) return rc;
+        if (e.esize == 2) bm_tile_scatter_kernel<2><<<g1, kThreads, 0, st>>>(x, bitmask, units, cols, rows, pfx, values, row_offsets);
+        else if (e.esize == 1) bm_tile_scatter_kernel<1><<<g1, kThreads, 0, st>>>(x, bitmask, units, cols, rows, pfx, values, row_offsets);
+        else bm_tile_scatter_kernel<4><<<g1, kThreads, 0, st>>>(x, bitmask, units, cols, rows, pfx, values, row_offsets);
+        return after_launch("bm_tile_scatter_kernel");
     }
     int grid = grid_for(rows, 1, 8);
     int rc;
@@ -631,7 +873,7 @@ static int compress_impl(const void *x, const uint8_t *pred, int32_t dtype, int6
 }
 
 extern "C" int64_t ctb_bitmask_workspace_bytes(int64_t rows, int64_t cols) {
-    const int64_t a = onepass_bytes(rows, cols), b = rows * 8 + 16;
+    const int64_t a = tile_bytes(rows, cols), b = rows * 8 + 16;
     return a > b ? a : b;
 }
 
@@ -647,24 +889,28 @@ extern "C" int ctb_masked_compress(const void *x, const uint8_t *bytemask, int32
 }
 
 static int decompress_impl(const void *values, const uint8_t *bitmask, int32_t dtype, int64_t rows, int64_t cols, void *out, void *workspace,
-                           const int *gate, void *stream, bool onepass_ok = false) {
+                           const int *gate, void *stream, bool tiles_ok = false) {
     if (!bitmask || !out || !workspace) return fail(CTB_EINVAL_NULL, "null buffer");
     ElemInfo e;
     if (!elem_info(dtype, &e)) return fail(CTB_EINVAL_DTYPE, "unsupported dtype for bitmask decompression");
     if (rows <= 0 || cols <= 0) return rows < 0 || cols < 0 ? fail(CTB_EINVAL_SHAPE, "negative shape") : CTB_OK;
     if (!values) return fail(CTB_EINVAL_NULL, "null values");
     cudaStream_t st = as_stream(stream);
-    if (onepass_ok && gate == nullptr && cols % 8 == 0 && aligned16(out) && rows * cols / kOnePassTile < 0x7FFFFFFF) {
-        cudaError_t ce = cudaMemsetAsync(workspace, 0, (size_t)onepass_bytes(rows, cols), st);
+    if (tiles_ok && gate == nullptr && cols % 8 == 0 && aligned16(out) && (reinterpret_cast<uintptr_t>(values) & 3u) == 0 &&
+        (reinterpret_cast<uintptr_t>(bitmask) & 1u) == 0) {
+        TileCtl *ctl = static_cast<TileCtl *>(workspace);
+        unsigned long long *pfx = reinterpret_cast<unsigned long long *>(ctl + 1);
+        cudaError_t ce = cudaMemsetAsync(ctl, 0, sizeof(TileCtl), st);
         if (ce != cudaSuccess) return fail(CTB_ECUDA, "cudaMemsetAsync: %s", cudaGetErrorString(ce));
-        OnePassCtl *ctl = static_cast<OnePassCtl *>(workspace);
-        volatile unsigned long long *state = reinterpret_cast<volatile unsigned long long *>(ctl + 1);
         const int64_t units = rows * cols / 8;
-        int g1 = grid_for(units * 8, kOnePassTile, 8);
-        if (e.esize == 2) bm_expand_onepass_kernel<2><<<g1, kThreads, 0, st>>>(values, bitmask, units, out, ctl, state);
-        else if (e.esize == 1) bm_expand_onepass_kernel<1><<<g1, kThreads, 0, st>>>(values, bitmask, units, out, ctl, state);
-        else bm_expand_onepass_kernel<4><<<g1, kThreads, 0, st>>>(values, bitmask, units, out, ctl, state);
-        return after_launch("bm_expand_onepass_kernel");
+        const int g1 = grid_for(units * 8, kTileElems, 8);
+        bm_tile_popcount_kernel<<<g1, kThreads, 0, st>>>(bitmask, units, pfx, ctl);
+        int rc0 = after_launch("bm_tile_popcount_kernel");
+        if (rc0) return rc0;
+        if (e.esize == 2) bm_tile_expand_kernel<2><<<g1, kThreads, 0, st>>>(values, bitmask, units, pfx, out);
+        else if (e.esize == 1) bm_tile_expand_kernel<1><<<g1, kThreads, 0, st>>>(values, bitmask, units, pfx, out);
+        else bm_tile_expand_kernel<4><<<g1, kThreads, 0, st>>>(values, bitmask, units, pfx, out);
+        return after_launch("bm_tile_expand_kernel");
     }
     int64_t *offs = (int64_t *)workspace;
     int grid = grid_for(rows, 1, 8);
@@ -699,10 +945,12 @@ extern "C" int ctb_sparse24_decompress(const void *values, const uint8_t *bitmas
     cudaError_t ce = cudaMemsetAsync(flag, 0, sizeof(int), st);
     if (ce != cudaSuccess) return fail(CTB_ECUDA, "cudaMemsetAsync: %s", cudaGetErrorString(ce));
     const int64_t units = rows * cols / 8;
-    int grid = grid_for(units, kThreads, 8);
-    if (e.esize == 2) sparse24_expand_kernel<2><<<grid, kThreads, 0, st>>>(values, bitmask, units, out, flag);
-    else if (e.esize == 1) sparse24_expand_kernel<1><<<grid, kThreads, 0, st>>>(values, bitmask, units, out, flag);
-    else sparse24_expand_kernel<4><<<grid, kThreads, 0, st>>>(values, bitmask, units, out, flag);
+    const bool simd = e.esize != 4 && (reinterpret_cast<uintptr_t>(bitmask) & 1u) == 0;
+    if (simd && e.esize == 2) sparse24_expand_simd_kernel<2><<<grid_for((units + 1) / 2, kThreads, 8), kThreads, 0, st>>>(values, bitmask, units, out, flag);
+    else if (simd) sparse24_expand_simd_kernel<1><<<grid_for((units + 1) / 2, kThreads, 8), kThreads, 0, st>>>(values, bitmask, units, out, flag);
+    else if (e.esize == 2) sparse24_expand_kernel<2><<<grid_for(units, kThreads, 8), kThreads, 0, st>>>(values, bitmask, units, out, flag);
+    else if (e.esize == 1) sparse24_expand_kernel<1><<<grid_for(units, kThreads, 8), kThreads, 0, st>>>(values, bitmask, units, out, flag);
+    else sparse24_expand_kernel<4><<<grid_for(units, kThreads, 8), kThreads, 0, st>>>(values, bitmask, units, out, flag);
     int rc = after_launch("sparse24_expand_kernel");
     if (rc) return rc;
     // generic path, gated on the flag: returns immediately unless the bitmask was not two-per-run
@@ -747,6 +995,6 @@ extern "C" int ctb_bitmask_decompress_static(const void *values, const uint8_t *
     int rc = static_scratch(&scratch);
     if (rc) return rc;
     // every row's slot is rewritten by the popcount pass before the scan reads it: nothing has to start at zero
-    const bool fits = rows > 0 && cols > 0 && onepass_bytes(rows, cols) <= kStaticMaxRows * 8;
+    const bool fits = rows > 0 && cols > 0 && tile_bytes(rows, cols) <= kStaticMaxRows * 8;
     return decompress_impl(values, bitmask, dtype, rows, cols, out, scratch, nullptr, stream, fits);
 }
