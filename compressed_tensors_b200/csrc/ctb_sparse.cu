@@ -209,37 +209,56 @@ __global__ void __launch_bounds__(kThreads) sparse24_expand_simd_kernel(const vo
     __syncthreads();
     bool bad = false;
     const int64_t items = (units + 1) >> 1;
-    for (int64_t it = (int64_t)blockIdx.x * kThreads + threadIdx.x; it < items; it += (int64_t)gridDim.x * kThreads) {
-        const int64_t u = it * 2;
-        const bool both = u + 1 < units;
-        uint32_t m = both ? (uint32_t) * reinterpret_cast<const uint16_t *>(bitmask + u) : (uint32_t)bitmask[u];
-        {  // every nibble must have exactly two bits set (the absent second unit counts as regular)
-            uint32_t c = m - ((m >> 1) & 0x5555u);
-            c = (c & 0x3333u) + ((c >> 2) & 0x3333u);
-            bad |= c != (both ? 0x2222u : 0x0022u);
-        }
-        if constexpr (ES == 1) {
-            uint2 v = make_uint2(0, 0);
-            if (both) v = ld_stream8((const char *)values + u * 4);
-            else v.x = ld_stream4((const char *)values + u * 4);
-            const uint32_t o0 = prmt(v.x, 0, lut[m & 0xFu]);
-            const uint32_t o1 = prmt(v.x >> 16, 0, lut[(m >> 4) & 0xFu]);
-            const uint32_t o2 = prmt(v.y, 0, lut[(m >> 8) & 0xFu]);
-            const uint32_t o3 = prmt(v.y >> 16, 0, lut[(m >> 12) & 0xFu]);
-            if (both) st_stream((char *)out + u * 8, make_uint4(o0, o1, o2, o3));
-            else st_stream8((char *)out + u * 8, make_uint2(o0, o1));
-        } else {
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (both) v = ld_stream((const char *)values + u * 8);
-            else {
-                const uint2 t = ld_stream8((const char *)values + u * 8);
-                v.x = t.x;
-                v.y = t.y;
+    const int64_t stride = (int64_t)gridDim.x * kThreads;
+    constexpr int U = 4;  // items in flight per thread: the loads of all of them are issued before the first is used
+    for (int64_t it0 = (int64_t)blockIdx.x * kThreads + threadIdx.x; it0 < items; it0 += U * stride) {
+        uint32_t m[U];
+        uint4 v[U];
+#pragma unroll
+        for (int k = 0; k < U; ++k) {
+            const int64_t u = (it0 + k * stride) * 2;
+            m[k] = 0;
+            v[k] = make_uint4(0, 0, 0, 0);
+            if (u + 1 < units) {
+                m[k] = *reinterpret_cast<const uint16_t *>(bitmask + u);
+                if constexpr (ES == 1) {
+                    const uint2 t = ld_stream8((const char *)values + u * 4);
+                    v[k].x = t.x;
+                    v[k].y = t.y;
+                } else {
+                    v[k] = ld_stream((const char *)values + u * 8);
+                }
+            } else if (u < units) {
+                m[k] = bitmask[u];
+                if constexpr (ES == 1) v[k].x = ld_stream4((const char *)values + u * 4);
+                else {
+                    const uint2 t = ld_stream8((const char *)values + u * 8);
+                    v[k].x = t.x;
+                    v[k].y = t.y;
+                }
             }
-            const uint32_t s0 = lut[m & 0xFu], s1 = lut[(m >> 4) & 0xFu], s2 = lut[(m >> 8) & 0xFu], s3 = lut[(m >> 12) & 0xFu];
-            st_stream((char *)out + u * 16, make_uint4(prmt(v.x, 0, s0 & 0xFFFFu), prmt(v.x, 0, s0 >> 16), prmt(v.y, 0, s1 & 0xFFFFu), prmt(v.y, 0, s1 >> 16)));
-            if (both)
-                st_stream((char *)out + u * 16 + 16, make_uint4(prmt(v.z, 0, s2 & 0xFFFFu), prmt(v.z, 0, s2 >> 16), prmt(v.w, 0, s3 & 0xFFFFu), prmt(v.w, 0, s3 >> 16)));
+        }
+#pragma unroll
+        for (int k = 0; k < U; ++k) {
+            const int64_t u = (it0 + k * stride) * 2;
+            if (u >= units) break;
+            const bool both = u + 1 < units;
+            {  // every nibble must have exactly two bits set (the absent second unit counts as regular)
+                uint32_t c = m[k] - ((m[k] >> 1) & 0x5555u);
+                c = (c & 0x3333u) + ((c >> 2) & 0x3333u);
+                bad |= c != (both ? 0x2222u : 0x0022u);
+            }
+            const uint32_t s0 = lut[m[k] & 0xFu], s1 = lut[(m[k] >> 4) & 0xFu], s2 = lut[(m[k] >> 8) & 0xFu], s3 = lut[(m[k] >> 12) & 0xFu];
+            if constexpr (ES == 1) {
+                const uint32_t o0 = prmt(v[k].x, 0, s0), o1 = prmt(v[k].x >> 16, 0, s1);
+                const uint32_t o2 = prmt(v[k].y, 0, s2), o3 = prmt(v[k].y >> 16, 0, s3);
+                if (both) st_stream((char *)out + u * 8, make_uint4(o0, o1, o2, o3));
+                else st_stream8((char *)out + u * 8, make_uint2(o0, o1));
+            } else {
+                st_stream((char *)out + u * 16, make_uint4(prmt(v[k].x, 0, s0 & 0xFFFFu), prmt(v[k].x, 0, s0 >> 16), prmt(v[k].y, 0, s1 & 0xFFFFu), prmt(v[k].y, 0, s1 >> 16)));
+                if (both)
+                    st_stream((char *)out + u * 16 + 16, make_uint4(prmt(v[k].z, 0, s2 & 0xFFFFu), prmt(v[k].z, 0, s2 >> 16), prmt(v[k].w, 0, s3 & 0xFFFFu), prmt(v[k].w, 0, s3 >> 16)));
+            }
         }
     }
     if (__any_sync(0xFFFFFFFFu, bad) && (threadIdx.x & 31) == 0) atomicExch(irregular, 1);
@@ -479,92 +498,111 @@ __global__ void __launch_bounds__(kThreads) bm_expand_kernel(const void *values,
 }  // namespace ctb
 
 
-// ------------------------------------------------------------------ tile-parallel bitmask codec (cols % 8 == 0)
+// ------------------------------------------------------------------ warp-tile bitmask codec (cols % 8 == 0)
 //
-// The tensor is cut into tiles of 4096 consecutive elements.  A first kernel counts the kept elements of every
-// tile (writing the bitmask on the way, for compress) and the LAST block to finish turns the counts into exclusive
-// prefixes in place; a second kernel then compacts (or expands) every tile independently from its prefix.  Nothing
-// waits on anything inside a kernel, so the tiles run at full occupancy; the second read of the dense tensor
-// comes from L2 when the tensor fits there.
+// The flat tensor is cut into tiles of 512 consecutive elements, one per warp and step (16 elements, i.e. two
+// bitmask bytes, per lane), and every warp of the grid owns a CONTIGUOUS range of tiles.
+//   kernel 1 streams over the tensor (compress: writes the bitmask) or over the bitmask (decompress) and leaves
+//            the kept count of every warp's range and of every block;
+//   kernel 2, launched with the same grid, sums the counts of the blocks before it (a few hundred words), then
+//            every warp walks its range with a running offset: kept values go through a per-warp shared-memory
+//            window that mirrors the 4-byte alignment of `values`, so that the global side is whole 32-bit words.
+// There is no block barrier inside the loops and nothing waits on another block; the second read of the dense
+// tensor comes from L2 when the tensor fits there.
 namespace ctb {
 
-constexpr int kTileEpt = 16;                      // elements per thread
-constexpr int kTileElems = kThreads * kTileEpt;   // 4096 elements per tile
+constexpr int kWarps = kThreads / 32;
+constexpr int kWarpTile = 512;      // elements per warp and step
+constexpr int kTileMaxGrid = 4096;  // blocks per launch (bounds the scratch: nine words per block)
 
-struct TileCtl {            // lives at the start of the workspace, zeroed by the entry point before every launch
-    unsigned int done;      // blocks of the counting kernel that have finished
-    unsigned int pad[3];
+// word w of a warp's staging window lives at w + w / 4: lanes whose runs start 16 bytes apart (50 % density of
+// 16-bit elements) then fall on different banks
+__device__ __forceinline__ int pad_word(int w) { return w + (w >> 2); }
+__device__ __forceinline__ int pad_byte(int o) { return o + ((o >> 4) << 2); }
+template <int ES>
+struct StageWords {
+    static constexpr int value = (kWarpTile * ES / 4 + 2) * 5 / 4 + 2;
 };
 
-__device__ __forceinline__ int block_excl_scan16(int v, int &total, int *wsum) {
-    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-    int inc = v;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        int t = __shfl_up_sync(0xFFFFFFFFu, inc, o);
-        if (lane >= o) inc += t;
-    }
-    if (lane == 31) wsum[w] = inc;
-    __syncthreads();
-    int base = 0;
-    total = 0;
-#pragma unroll
-    for (int i = 0; i < kThreads / 32; ++i) {
-        if (i < w) base += wsum[i];
-        total += wsum[i];
-    }
-    return base + inc - v;
+template <int ES>
+__device__ __forceinline__ uint32_t stage_load(const uint32_t *st, int o) {
+    const char *p = reinterpret_cast<const char *>(st) + pad_byte(o);
+    if constexpr (ES == 1) return *reinterpret_cast<const uint8_t *>(p);
+    else if constexpr (ES == 2) return *reinterpret_cast<const uint16_t *>(p);
+    else return *reinterpret_cast<const uint32_t *>(p);
+}
+template <int ES>
+__device__ __forceinline__ void stage_store(uint32_t *st, int o, uint32_t v) {
+    char *p = reinterpret_cast<char *>(st) + pad_byte(o);
+    if constexpr (ES == 1) *reinterpret_cast<uint8_t *>(p) = (uint8_t)v;
+    else if constexpr (ES == 2) *reinterpret_cast<uint16_t *>(p) = (uint16_t)v;
+    else *reinterpret_cast<uint32_t *>(p) = v;
 }
 
-// Called by every thread of every block once the block's counts are written: the last block to arrive replaces
-// pfx[0..ntiles) (per-tile counts) by their exclusive prefix sums and stores the total.
-__device__ __forceinline__ void last_block_scan(unsigned long long *pfx, int64_t ntiles, TileCtl *ctl, int64_t *total_out) {
-    __shared__ bool s_last;
-    __shared__ unsigned long long s_w[kThreads / 32];
-    __shared__ unsigned long long s_carry;
-    __threadfence();  // this block's counts are visible before its arrival is
-    __syncthreads();
-    if (threadIdx.x == 0) s_last = atomicAdd(&ctl->done, 1u) == gridDim.x - 1;
-    __syncthreads();
-    if (!s_last) return;
-    __threadfence();
-    if (threadIdx.x == 0) s_carry = 0;
-    __syncthreads();
-    constexpr int kPer = 4;  // consecutive entries per thread and sweep
-    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-    for (int64_t base = 0; base < ntiles; base += (int64_t)kThreads * kPer) {
-        const int64_t i0 = base + (int64_t)threadIdx.x * kPer;
-        unsigned long long v[kPer], sum = 0;
+// tiles [first, last) of this warp when `ntiles` are dealt to all warps of the grid in contiguous ranges
+__device__ __forceinline__ void warp_range(int64_t ntiles, int64_t &first, int64_t &last) {
+    const int64_t nw = (int64_t)gridDim.x * kWarps;
+    const int64_t per = (ntiles + nw - 1) / nw;
+    const int64_t gw = (int64_t)blockIdx.x * kWarps + (threadIdx.x >> 5);
+    first = gw * per < ntiles ? gw * per : ntiles;
+    last = first + per < ntiles ? first + per : ntiles;
+}
+
+// kernel 1 epilogue: the kept count of this warp's range and of the block
+__device__ __forceinline__ void publish_counts(unsigned long long c, unsigned long long *block_tot, unsigned long long *warp_tot) {
+    __shared__ unsigned long long wt[kWarps];
 #pragma unroll
-        for (int j = 0; j < kPer; ++j) {
-            v[j] = i0 + j < ntiles ? __ldcg(pfx + i0 + j) : 0ull;  // written by other blocks: read at L2
-            sum += v[j];
-        }
-        unsigned long long inc = sum;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const unsigned long long t = __shfl_up_sync(0xFFFFFFFFu, inc, o);
-            if (lane >= o) inc += t;
-        }
-        if (lane == 31) s_w[w] = inc;
-        __syncthreads();
-        unsigned long long run = s_carry + inc - sum;
-        unsigned long long all = 0;
-#pragma unroll
-        for (int i = 0; i < kThreads / 32; ++i) {
-            if (i < w) run += s_w[i];
-            all += s_w[i];
-        }
-#pragma unroll
-        for (int j = 0; j < kPer; ++j) {
-            if (i0 + j < ntiles) pfx[i0 + j] = run;
-            run += v[j];
-        }
-        __syncthreads();
-        if (threadIdx.x == 0) s_carry += all;
-        __syncthreads();
+    for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xFFFFFFFFu, c, o);
+    if ((threadIdx.x & 31) == 0) {
+        wt[threadIdx.x >> 5] = c;
+        warp_tot[(int64_t)blockIdx.x * kWarps + (threadIdx.x >> 5)] = c;
     }
-    if (threadIdx.x == 0 && total_out) *total_out = (int64_t)s_carry;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned long long t = 0;
+#pragma unroll
+        for (int i = 0; i < kWarps; ++i) t += wt[i];
+        block_tot[blockIdx.x] = t;
+    }
+}
+
+// kernel 2 prologue: index of the first kept value of this warp's range (uniform over the warp); the last block
+// also stores the grand total
+__device__ __forceinline__ unsigned long long warp_first_value(const unsigned long long *block_tot, const unsigned long long *warp_tot, int64_t *nnz) {
+    __shared__ unsigned long long red[kWarps];
+    unsigned long long s = 0;
+    for (int i = threadIdx.x; i < (int)blockIdx.x; i += kThreads) s += block_tot[i];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+    __syncthreads();
+    unsigned long long base = 0;
+#pragma unroll
+    for (int i = 0; i < kWarps; ++i) base += red[i];
+    if (nnz != nullptr && blockIdx.x == gridDim.x - 1 && threadIdx.x == 0) *nnz = (int64_t)(base + block_tot[blockIdx.x]);
+    const int w = threadIdx.x >> 5;
+    for (int i = 0; i < w; ++i) base += warp_tot[(int64_t)blockIdx.x * kWarps + i];
+    return base;
+}
+
+// this lane's 16 mask bits of tile `tile` (units past the end read as zero)
+__device__ __forceinline__ uint32_t lane_mask(const uint8_t *bitmask, int64_t u0, int64_t units) {
+    if (u0 + 1 < units) return *reinterpret_cast<const uint16_t *>(bitmask + u0);
+    if (u0 < units) return bitmask[u0];
+    return 0u;
+}
+
+// exclusive prefix of c over the warp, and the warp total
+__device__ __forceinline__ int warp_excl_scan(int c, int &total) {
+    int inc = c;
+    const int lane = threadIdx.x & 31;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+        if (lane >= o) inc += t;
+    }
+    total = __shfl_sync(0xFFFFFFFFu, inc, 31);
+    return inc - c;
 }
 
 // raw 16-byte (ES = 2), 8-byte (ES = 1) or 32-byte (ES = 4) image of one 8-element unit; KEEP = the dense tensor is
@@ -625,26 +663,16 @@ __device__ __forceinline__ uint32_t unit_nz_mask(const Raw8 &r, uint32_t nzm) {
     return m;
 }
 
-__device__ __forceinline__ int block_count(int c, int *wsum) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xFFFFFFFFu, c, o);
-    if ((threadIdx.x & 31) == 0) wsum[threadIdx.x >> 5] = c;
-    __syncthreads();
-    int t = 0;
-#pragma unroll
-    for (int i = 0; i < kThreads / 32; ++i) t += wsum[i];
-    __syncthreads();  // wsum is reused by the next tile
-    return t;
-}
-
-// compress, kernel 1: bitmask bytes and per-tile counts, then the prefix scan by the last block
+// compress, kernel 1: bitmask bytes and the kept counts
 template <int ES>
-__global__ void __launch_bounds__(kThreads) bm_tile_count_kernel(const void *x, uint32_t nzm, int64_t units, uint8_t *bitmask,
-                                                                 unsigned long long *pfx, TileCtl *ctl, int64_t *nnz) {
-    __shared__ int wsum[kThreads / 32];
-    const int64_t ntiles = (units * 8 + kTileElems - 1) / kTileElems;
-    for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
-        const int64_t u0 = (tile * kThreads + threadIdx.x) * 2;
+__global__ void __launch_bounds__(kThreads) bm_warp_count_kernel(const void *x, uint32_t nzm, int64_t units, uint8_t *bitmask,
+                                                                 unsigned long long *block_tot, unsigned long long *warp_tot) {
+    int64_t first, last;
+    warp_range((units + 63) / 64, first, last);
+    const int lane = threadIdx.x & 31;
+    int cnt = 0;
+    for (int64_t tile = first; tile < last; ++tile) {
+        const int64_t u0 = tile * 64 + lane * 2;
         uint32_t mask = 0;
         if (u0 + 1 < units) {
             const Raw8 r0 = load_unit_raw<ES, true>(x, u0), r1 = load_unit_raw<ES, true>(x, u0 + 1);
@@ -654,131 +682,141 @@ __global__ void __launch_bounds__(kThreads) bm_tile_count_kernel(const void *x, 
             mask = unit_nz_mask<ES>(load_unit_raw<ES, true>(x, u0), nzm);
             bitmask[u0] = (uint8_t)mask;
         }
-        const int total = block_count(__popc(mask), wsum);
-        if (threadIdx.x == 0) pfx[tile] = (unsigned long long)total;
+        cnt += __popc(mask);
     }
-    last_block_scan(pfx, ntiles, ctl, nnz);
+    publish_counts((unsigned long long)cnt, block_tot, warp_tot);
 }
 
-// decompress, kernel 1: per-tile counts from the bitmask, then the prefix scan by the last block
-__global__ void __launch_bounds__(kThreads) bm_tile_popcount_kernel(const uint8_t *bitmask, int64_t units, unsigned long long *pfx, TileCtl *ctl) {
-    __shared__ int wsum[kThreads / 32];
-    const int64_t ntiles = (units * 8 + kTileElems - 1) / kTileElems;
-    for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
-        const int64_t u0 = (tile * kThreads + threadIdx.x) * 2;
-        uint32_t mask = 0;
-        if (u0 + 1 < units) mask = *reinterpret_cast<const uint16_t *>(bitmask + u0);
-        else if (u0 < units) mask = bitmask[u0];
-        const int total = block_count(__popc(mask), wsum);
-        if (threadIdx.x == 0) pfx[tile] = (unsigned long long)total;
+// decompress, kernel 1: the same counts from the bitmask (a tile is 64 bitmask bytes)
+__global__ void __launch_bounds__(kThreads) bm_warp_popcount_kernel(const uint8_t *bitmask, int64_t units, unsigned long long *block_tot,
+                                                                    unsigned long long *warp_tot, const int *gate) {
+    if (gate != nullptr && *gate == 0) return;  // the fast 2:4 expansion already produced the tensor
+    int64_t first, last;
+    warp_range((units + 63) / 64, first, last);
+    const int lane = threadIdx.x & 31;
+    const int64_t b0 = first * 64, b1 = last * 64 < units ? last * 64 : units;
+    unsigned long long c = 0;
+    int64_t i = b0 + lane * 16;
+    if ((reinterpret_cast<uintptr_t>(bitmask) & 15u) == 0) {
+        for (; i + 16 <= b1; i += 512) {
+            const uint4 v = *reinterpret_cast<const uint4 *>(bitmask + i);
+            c += __popc(v.x) + __popc(v.y) + __popc(v.z) + __popc(v.w);
+        }
     }
-    last_block_scan(pfx, ntiles, ctl, nullptr);
+    // ragged end (and unaligned bitmasks): a lane's first leftover chunk may be partial, later ones are whole
+    for (; i < b1; i += 512)
+        for (int64_t j = i; j < i + 16 && j < b1; ++j) c += __popc((uint32_t)bitmask[j]);
+    publish_counts(c, block_tot, warp_tot);
 }
 
-// compress, kernel 2: compact every tile to values[pfx[tile] ...) through shared memory, and the row offsets
+// compress, kernel 2 (same grid as kernel 1): compact every tile of the warp's range into `values`, and the row offsets
 template <int ES>
-__global__ void __launch_bounds__(kThreads) bm_tile_scatter_kernel(const void *x, const uint8_t *bitmask, int64_t units, int64_t cols, int64_t rows,
-                                                                   const unsigned long long *pfx, void *values, int64_t *row_offsets) {
-    __shared__ uint32_t stage[kTileElems];
-    __shared__ int wsum[kThreads / 32];
-    const int64_t ntiles = (units * 8 + kTileElems - 1) / kTileElems;
-    for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
-        const int64_t u0 = (tile * kThreads + threadIdx.x) * 2;  // first of this thread's two 8-element units
-        uint32_t mask = 0;
+__global__ void __launch_bounds__(kThreads) bm_warp_scatter_kernel(const void *x, const uint8_t *bitmask, int64_t units, int64_t cols, int64_t rows,
+                                                                   const unsigned long long *block_tot, const unsigned long long *warp_tot, void *values,
+                                                                   int64_t *row_offsets, int64_t *nnz) {
+    __shared__ uint32_t stage_all[kWarps][StageWords<ES>::value];
+    uint32_t *st = stage_all[threadIdx.x >> 5];
+    int64_t first, last;
+    warp_range((units + 63) / 64, first, last);
+    unsigned long long prefix = warp_first_value(block_tot, warp_tot, nnz);
+    const int lane = threadIdx.x & 31;
+    int64_t r_next = (first * kWarpTile + cols - 1) / cols;  // first row that starts inside this warp's range
+    int64_t e_next = r_next * cols;
+    for (int64_t tile = first; tile < last; ++tile) {
+        const int64_t u0 = tile * 64 + lane * 2;  // first of this lane's two 8-element units
+        const uint32_t mask = lane_mask(bitmask, u0, units);
         Raw8 raw[2];
         raw[0].a = raw[0].b = raw[1].a = raw[1].b = make_uint4(0, 0, 0, 0);
-        if (u0 + 1 < units) {
-            mask = *reinterpret_cast<const uint16_t *>(bitmask + u0);
-            raw[0] = load_unit_raw<ES, false>(x, u0);
-            raw[1] = load_unit_raw<ES, false>(x, u0 + 1);
-        } else if (u0 < units) {
-            mask = bitmask[u0];
-            raw[0] = load_unit_raw<ES, false>(x, u0);
-        }
-        const unsigned long long prefix = pfx[tile];
+        if (u0 < units) raw[0] = load_unit_raw<ES, false>(x, u0);
+        if (u0 + 1 < units) raw[1] = load_unit_raw<ES, false>(x, u0 + 1);
         int total;
-        const int excl = block_excl_scan16(__popc(mask), total, wsum);
-        int pos = excl;
+        const int excl = warp_excl_scan(__popc(mask), total);
+        char *dst = (char *)values + prefix * ES;
+        const int shift = (int)(reinterpret_cast<uintptr_t>(dst) & 3u);  // the window mirrors the destination's alignment
+        int o = shift + excl * ES;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             uint32_t b[8];
             unit_bits<ES>(raw[h], b);
 #pragma unroll
             for (int j = 0; j < 8; ++j)
-                if ((mask >> (8 * h + j)) & 1) stage[pos++] = b[j];
+                if ((mask >> (8 * h + j)) & 1) {
+                    stage_store<ES>(st, o, b[j]);
+                    o += ES;
+                }
         }
-        // rows that begin inside this thread's 16 elements (cols is a multiple of 8: only at offset 0 or 8)
-        if (u0 < units) {
-            const int64_t e0 = u0 * 8;
-            const int64_t r0 = (units <= 0x1FFFFFFF) ? (int64_t)((uint32_t)e0 / (uint32_t)cols) : e0 / cols;  // 32-bit divide when it fits
-            const int64_t rem = e0 - r0 * cols;
-            if (rem == 0) row_offsets[r0] = (int64_t)(prefix + excl);
-            if (rem + 8 == cols && r0 + 1 < rows && u0 + 1 < units) row_offsets[r0 + 1] = (int64_t)(prefix + excl + __popc(mask & 0xFFu));
+        // rows that begin inside this tile (cols is a multiple of 8, so at offset 0 or 8 of some lane's 16 elements)
+        while (e_next < (tile + 1) * kWarpTile && r_next < rows) {  // uniform over the warp
+            const int off = (int)(e_next - tile * kWarpTile);
+            if (lane == (off >> 4)) row_offsets[r_next] = (int64_t)(prefix + excl + ((off & 8) ? __popc(mask & 0xFFu) : 0));
+            ++r_next;
+            e_next += cols;
         }
-        __syncthreads();
-        if constexpr (ES == 2) {
-            // pairs of values per 32-bit store where the destination allows it
-            const int64_t dst0 = (int64_t)prefix;
-            const int odd = (int)(dst0 & 1);
-            if (threadIdx.x == 0 && odd && total > 0) store_bits(values, 2, dst0, stage[0]);
-            const int npairs = (total - odd) / 2;
-            for (int i = threadIdx.x; i < npairs; i += kThreads)
-                reinterpret_cast<uint32_t *>((char *)values + (dst0 + odd) * 2)[i] = stage[odd + 2 * i] | (stage[odd + 2 * i + 1] << 16);
-            if (threadIdx.x == 0 && total > odd && ((total - odd) & 1)) store_bits(values, 2, dst0 + total - 1, stage[total - 1]);
-        } else {
-            for (int i = threadIdx.x; i < total; i += kThreads) store_bits(values, ES, (int64_t)prefix + i, stage[i]);
+        __syncwarp();
+        const int nbytes = shift + total * ES;
+        const int first_full = shift ? 1 : 0, end_full = nbytes >> 2;  // words [first_full, end_full) are wholly this tile's
+        uint32_t *d0 = reinterpret_cast<uint32_t *>(dst - shift);
+#pragma unroll 4
+        for (int w = first_full + lane; w < end_full; w += 32) d0[w] = st[pad_word(w)];
+        if (lane < 8) {  // the ragged head and tail share their words with the neighbouring tiles: element by element
+            const int head_end = first_full * 4 < nbytes ? first_full * 4 : nbytes;
+            const int tail0 = end_full * 4 > head_end ? end_full * 4 : head_end;
+            const int p = lane < 4 ? shift + lane * ES : tail0 + (lane - 4) * ES;
+            const int lim = lane < 4 ? head_end : nbytes;
+            if (p < lim) store_bits(values, ES, (int64_t)prefix + (p - shift) / ES, stage_load<ES>(st, p));
         }
-        __syncthreads();  // stage and wsum are reused by the next tile
+        prefix += (unsigned long long)total;
+        __syncwarp();  // the window is reused by the next tile
     }
 }
 
-// decompress, kernel 2: every tile's kept values are one contiguous run of `values`; bring it in with coalesced
-// loads, then every thread rebuilds its 16 elements from shared memory
+// decompress, kernel 2 (same grid as kernel 1): every tile's kept values are one contiguous run of `values`; bring
+// it in as whole 32-bit words, then every lane rebuilds its 16 elements from the window
 template <int ES>
-__global__ void __launch_bounds__(kThreads) bm_tile_expand_kernel(const void *values, const uint8_t *bitmask, int64_t units, const unsigned long long *pfx,
-                                                                  void *out) {
-    __shared__ uint32_t stage[kTileElems];
-    __shared__ int wsum[kThreads / 32];
-    const int64_t ntiles = (units * 8 + kTileElems - 1) / kTileElems;
-    for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
-        const int64_t u0 = (tile * kThreads + threadIdx.x) * 2;
-        uint32_t mask = 0;
-        if (u0 + 1 < units) mask = *reinterpret_cast<const uint16_t *>(bitmask + u0);
-        else if (u0 < units) mask = bitmask[u0];
-        const int64_t src0 = (int64_t)pfx[tile];
+__global__ void __launch_bounds__(kThreads) bm_warp_expand_kernel(const void *values, const uint8_t *bitmask, int64_t units, const unsigned long long *block_tot,
+                                                                  const unsigned long long *warp_tot, void *out, const int *gate) {
+    if (gate != nullptr && *gate == 0) return;
+    __shared__ uint32_t stage_all[kWarps][StageWords<ES>::value];
+    uint32_t *st = stage_all[threadIdx.x >> 5];
+    int64_t first, last;
+    warp_range((units + 63) / 64, first, last);
+    unsigned long long src = warp_first_value(block_tot, warp_tot, nullptr);
+    const int lane = threadIdx.x & 31;
+    for (int64_t tile = first; tile < last; ++tile) {
+        const int64_t u0 = tile * 64 + lane * 2;
+        const uint32_t mask = lane_mask(bitmask, u0, units);
         int total;
-        const int excl = block_excl_scan16(__popc(mask), total, wsum);
-        if constexpr (ES == 2) {
-            const int odd = (int)(src0 & 1);
-            if (threadIdx.x == 0 && odd && total > 0) stage[0] = load_bits(values, 2, src0);
-            const int npairs = (total - odd) / 2;
-            const uint32_t *v32 = reinterpret_cast<const uint32_t *>((const char *)values + (src0 + odd) * 2);
-            for (int i = threadIdx.x; i < npairs; i += kThreads) {
-                const uint32_t w = ld_stream4(v32 + i);
-                stage[odd + 2 * i] = w & 0xFFFFu;
-                stage[odd + 2 * i + 1] = w >> 16;
-            }
-            if (threadIdx.x == 0 && total > odd && ((total - odd) & 1)) stage[total - 1] = load_bits(values, 2, src0 + total - 1);
-        } else {
-            for (int i = threadIdx.x; i < total; i += kThreads) stage[i] = load_bits(values, ES, src0 + i);
-        }
-        __syncthreads();
-        int pos = excl;
+        const int excl = warp_excl_scan(__popc(mask), total);
+        const char *a = (const char *)values + src * ES;
+        const int shift = (int)(reinterpret_cast<uintptr_t>(a) & 3u);
+        const int nwords = (shift + total * ES + 3) >> 2;  // whole words: the first and last may hold neighbours' bytes, never read
+        const uint32_t *a0 = reinterpret_cast<const uint32_t *>(a - shift);
+#pragma unroll 4
+        for (int w = lane; w < nwords; w += 32) st[pad_word(w)] = ld_stream4(a0 + w);
+        __syncwarp();
+        int o = shift + excl * ES;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             if (u0 + h >= units) break;
             uint32_t b[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) b[j] = ((mask >> (8 * h + j)) & 1) ? stage[pos++] : 0u;
-            char *o = (char *)out + (u0 + h) * 8 * ES;
-            if constexpr (ES == 2) st_stream(o, make_uint4(b[0] | (b[1] << 16), b[2] | (b[3] << 16), b[4] | (b[5] << 16), b[6] | (b[7] << 16)));
-            else if constexpr (ES == 1) st_stream8(o, make_uint2(b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24), b[4] | (b[5] << 8) | (b[6] << 16) | (b[7] << 24)));
+            for (int j = 0; j < 8; ++j) {
+                b[j] = 0u;
+                if ((mask >> (8 * h + j)) & 1) {
+                    b[j] = stage_load<ES>(st, o);
+                    o += ES;
+                }
+            }
+            char *q = (char *)out + (u0 + h) * 8 * ES;
+            if constexpr (ES == 2) st_stream(q, make_uint4(b[0] | (b[1] << 16), b[2] | (b[3] << 16), b[4] | (b[5] << 16), b[6] | (b[7] << 16)));
+            else if constexpr (ES == 1) st_stream8(q, make_uint2(b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24), b[4] | (b[5] << 8) | (b[6] << 16) | (b[7] << 24)));
             else {
-                st_stream(o, make_uint4(b[0], b[1], b[2], b[3]));
-                st_stream(o + 16, make_uint4(b[4], b[5], b[6], b[7]));
+                st_stream(q, make_uint4(b[0], b[1], b[2], b[3]));
+                st_stream(q + 16, make_uint4(b[4], b[5], b[6], b[7]));
             }
         }
-        __syncthreads();  // stage and wsum are reused by the next tile
+        src += (unsigned long long)total;
+        __syncwarp();  // the window is reused by the next tile
     }
 }
 
@@ -821,9 +859,17 @@ extern "C" int ctb_sparse24_compress(const void *x, int32_t dtype, int64_t rows,
     return after_launch("sparse24_compress_simd_kernel");
 }
 
-static int64_t tile_bytes(int64_t rows, int64_t cols) {
-    const int64_t tiles = (rows * cols + kTileElems - 1) / kTileElems;
-    return (int64_t)sizeof(TileCtl) + 8 * tiles;  // arrival counter, then one count / prefix word per tile
+static int64_t tile_bytes() {
+    return 8 * (int64_t)kTileMaxGrid * (1 + kWarps);  // one count per block, then one per warp
+}
+// the 2:4 decompress keeps its "bitmask is irregular" flag behind whichever scratch layout is used
+static int64_t flag_offset(int64_t rows) {
+    const int64_t a = tile_bytes(), b = rows * 8;
+    return a > b ? a : b;
+}
+static int tile_grid(int64_t units, int blocks_per_sm = 8) {
+    const int g = grid_for(units * 8, (int64_t)kWarpTile * kWarps, blocks_per_sm);
+    return g < kTileMaxGrid ? g : kTileMaxGrid;
 }
 
 static int compress_impl(const void *x, const uint8_t *pred, int32_t dtype, int64_t rows, int64_t cols, void *values, uint8_t *bitmask,
@@ -840,22 +886,19 @@ static int compress_impl(const void *x, const uint8_t *pred, int32_t dtype, int6
     }
     const bool vec = !pred && cols % 8 == 0 && aligned16(x);
     if (vec && workspace != nullptr && (reinterpret_cast<uintptr_t>(values) & 3u) == 0 && (reinterpret_cast<uintptr_t>(bitmask) & 1u) == 0) {
-        // tile-parallel: count + scan, then scatter
-        TileCtl *ctl = static_cast<TileCtl *>(workspace);
-        unsigned long long *pfx = reinterpret_cast<unsigned long long *>(ctl + 1);
-        cudaError_t ce = cudaMemsetAsync(ctl, 0, sizeof(TileCtl), st);
-        if (ce != cudaSuccess) return fail(CTB_ECUDA, "cudaMemsetAsync: %s", cudaGetErrorString(ce));
+        // warp tiles: count, then scatter (both kernels must see the same grid: it defines the tile ranges)
+        unsigned long long *block_tot = static_cast<unsigned long long *>(workspace), *warp_tot = block_tot + kTileMaxGrid;
         const int64_t units = rows * cols / 8;
-        const int g1 = grid_for(units * 8, kTileElems, 8);
+        const int g1 = tile_grid(units);
         int rc;
-        if (e.esize == 2) bm_tile_count_kernel<2><<<g1, kThreads, 0, st>>>(x, e.nz_mask, units, bitmask, pfx, ctl, nnz);
-        else if (e.esize == 1) bm_tile_count_kernel<1><<<g1, kThreads, 0, st>>>(x, e.nz_mask, units, bitmask, pfx, ctl, nnz);
-        else bm_tile_count_kernel<4><<<g1, kThreads, 0, st>>>(x, e.nz_mask, units, bitmask, pfx, ctl, nnz);
-        if ((rc = after_launch("bm_tile_count_kernel"))) return rc;
-        if (e.esize == 2) bm_tile_scatter_kernel<2><<<g1, kThreads, 0, st>>>(x, bitmask, units, cols, rows, pfx, values, row_offsets);
-        else if (e.esize == 1) bm_tile_scatter_kernel<1><<<g1, kThreads, 0, st>>>(x, bitmask, units, cols, rows, pfx, values, row_offsets);
-        else bm_tile_scatter_kernel<4><<<g1, kThreads, 0, st>>>(x, bitmask, units, cols, rows, pfx, values, row_offsets);
-        return after_launch("bm_tile_scatter_kernel");
+        if (e.esize == 2) bm_warp_count_kernel<2><<<g1, kThreads, 0, st>>>(x, e.nz_mask, units, bitmask, block_tot, warp_tot);
+        else if (e.esize == 1) bm_warp_count_kernel<1><<<g1, kThreads, 0, st>>>(x, e.nz_mask, units, bitmask, block_tot, warp_tot);
+        else bm_warp_count_kernel<4><<<g1, kThreads, 0, st>>>(x, e.nz_mask, units, bitmask, block_tot, warp_tot);
+        if ((rc = after_launch("bm_warp_count_kernel"))) return rc;
+        if (e.esize == 2) bm_warp_scatter_kernel<2><<<g1, kThreads, 0, st>>>(x, bitmask, units, cols, rows, block_tot, warp_tot, values, row_offsets, nnz);
+        else if (e.esize == 1) bm_warp_scatter_kernel<1><<<g1, kThreads, 0, st>>>(x, bitmask, units, cols, rows, block_tot, warp_tot, values, row_offsets, nnz);
+        else bm_warp_scatter_kernel<4><<<g1, kThreads, 0, st>>>(x, bitmask, units, cols, rows, block_tot, warp_tot, values, row_offsets, nnz);
+        return after_launch("bm_warp_scatter_kernel");
     }
     int grid = grid_for(rows, 1, 8);
     int rc;
@@ -873,8 +916,7 @@ static int compress_impl(const void *x, const uint8_t *pred, int32_t dtype, int6
 }
 
 extern "C" int64_t ctb_bitmask_workspace_bytes(int64_t rows, int64_t cols) {
-    const int64_t a = tile_bytes(rows, cols), b = rows * 8 + 16;
-    return a > b ? a : b;
+    return flag_offset(rows) + 16;
 }
 
 extern "C" int ctb_bitmask_compress(const void *x, int32_t dtype, int64_t rows, int64_t cols, void *values, uint8_t *bitmask,
@@ -896,21 +938,20 @@ static int decompress_impl(const void *values, const uint8_t *bitmask, int32_t d
     if (rows <= 0 || cols <= 0) return rows < 0 || cols < 0 ? fail(CTB_EINVAL_SHAPE, "negative shape") : CTB_OK;
     if (!values) return fail(CTB_EINVAL_NULL, "null values");
     cudaStream_t st = as_stream(stream);
-    if (tiles_ok && gate == nullptr && cols % 8 == 0 && aligned16(out) && (reinterpret_cast<uintptr_t>(values) & 3u) == 0 &&
+    if (tiles_ok && cols % 8 == 0 && aligned16(out) && (reinterpret_cast<uintptr_t>(values) & 3u) == 0 &&
         (reinterpret_cast<uintptr_t>(bitmask) & 1u) == 0) {
-        TileCtl *ctl = static_cast<TileCtl *>(workspace);
-        unsigned long long *pfx = reinterpret_cast<unsigned long long *>(ctl + 1);
-        cudaError_t ce = cudaMemsetAsync(ctl, 0, sizeof(TileCtl), st);
-        if (ce != cudaSuccess) return fail(CTB_ECUDA, "cudaMemsetAsync: %s", cudaGetErrorString(ce));
+        unsigned long long *block_tot = static_cast<unsigned long long *>(workspace), *warp_tot = block_tot + kTileMaxGrid;
         const int64_t units = rows * cols / 8;
-        const int g1 = grid_for(units * 8, kTileElems, 8);
-        bm_tile_popcount_kernel<<<g1, kThreads, 0, st>>>(bitmask, units, pfx, ctl);
-        int rc0 = after_launch("bm_tile_popcount_kernel");
+        // both kernels must see the same grid: it defines the tile ranges.  As the gated fallback of the 2:4
+        // expansion the launches almost always return at once: keep them small.
+        const int g1 = tile_grid(units, gate ? 1 : 8);
+        bm_warp_popcount_kernel<<<g1, kThreads, 0, st>>>(bitmask, units, block_tot, warp_tot, gate);
+        int rc0 = after_launch("bm_warp_popcount_kernel");
         if (rc0) return rc0;
-        if (e.esize == 2) bm_tile_expand_kernel<2><<<g1, kThreads, 0, st>>>(values, bitmask, units, pfx, out);
-        else if (e.esize == 1) bm_tile_expand_kernel<1><<<g1, kThreads, 0, st>>>(values, bitmask, units, pfx, out);
-        else bm_tile_expand_kernel<4><<<g1, kThreads, 0, st>>>(values, bitmask, units, pfx, out);
-        return after_launch("bm_tile_expand_kernel");
+        if (e.esize == 2) bm_warp_expand_kernel<2><<<g1, kThreads, 0, st>>>(values, bitmask, units, block_tot, warp_tot, out, gate);
+        else if (e.esize == 1) bm_warp_expand_kernel<1><<<g1, kThreads, 0, st>>>(values, bitmask, units, block_tot, warp_tot, out, gate);
+        else bm_warp_expand_kernel<4><<<g1, kThreads, 0, st>>>(values, bitmask, units, block_tot, warp_tot, out, gate);
+        return after_launch("bm_warp_expand_kernel");
     }
     int64_t *offs = (int64_t *)workspace;
     int grid = grid_for(rows, 1, 8);
@@ -941,7 +982,7 @@ extern "C" int ctb_sparse24_decompress(const void *values, const uint8_t *bitmas
     if (cols % 8 != 0 || !aligned16(out) || (reinterpret_cast<uintptr_t>(values) & 15u))
         return decompress_impl(values, bitmask, dtype, rows, cols, out, workspace, nullptr, stream);
     cudaStream_t st = as_stream(stream);
-    int *flag = reinterpret_cast<int *>(static_cast<char *>(workspace) + rows * 8);
+    int *flag = reinterpret_cast<int *>(static_cast<char *>(workspace) + flag_offset(rows));
     cudaError_t ce = cudaMemsetAsync(flag, 0, sizeof(int), st);
     if (ce != cudaSuccess) return fail(CTB_ECUDA, "cudaMemsetAsync: %s", cudaGetErrorString(ce));
     const int64_t units = rows * cols / 8;
@@ -954,7 +995,7 @@ extern "C" int ctb_sparse24_decompress(const void *values, const uint8_t *bitmas
     int rc = after_launch("sparse24_expand_kernel");
     if (rc) return rc;
     // generic path, gated on the flag: returns immediately unless the bitmask was not two-per-run
-    return decompress_impl(values, bitmask, dtype, rows, cols, out, workspace, flag, stream);
+    return decompress_impl(values, bitmask, dtype, rows, cols, out, workspace, flag, stream, true);
 }
 
 // ------------------------------------------------------------------ decompress without caller scratch
@@ -995,6 +1036,6 @@ extern "C" int ctb_bitmask_decompress_static(const void *values, const uint8_t *
     int rc = static_scratch(&scratch);
     if (rc) return rc;
     // every row's slot is rewritten by the popcount pass before the scan reads it: nothing has to start at zero
-    const bool fits = rows > 0 && cols > 0 && tile_bytes(rows, cols) <= kStaticMaxRows * 8;
+    const bool fits = rows > 0 && cols > 0 && tile_bytes() <= kStaticMaxRows * 8;
     return decompress_impl(values, bitmask, dtype, rows, cols, out, scratch, nullptr, stream, fits);
 }

@@ -68,30 +68,51 @@ CTB_HD Keep4 keep24_rule(uint32_t g10, uint32_t g20, uint32_t g30, uint32_t g21,
 // ---- four runs of int8-view elements (int8, uint8 and e4m3 tensors are ranked through torch's int8 abs, where
 // abs(-128) stays -128 and therefore ranks lowest)
 
-// lane-wise order-preserving key: u = abs_int8(v) + 128 as an unsigned byte
-CTB_HD uint32_t key_u8x4(uint32_t v) {
-    const uint32_t s = prmt(v, 0, 0xBA98);  // 0xFF in negative lanes
-    const uint32_t x = v ^ s;               // ~v in negative lanes
-    const uint32_t lo = (x & 0x7F7F7F7Fu) + (s & 0x01010101u);  // + 1 completes the negation; cannot leave the lane
-    return lo ^ (~x & 0x80808080u);
+// a - b, placed on the multiply-add pipe on the GPU: the selection logic saturates the integer ALU pipe, and the
+// dozen lane-wise subtractions and additions per 16 elements are the part of it that can run elsewhere
+CTB_HD uint32_t sub_fma_pipe(uint32_t a, uint32_t b) {
+#if defined(__CUDA_ARCH__)
+    uint32_t r;
+    asm("mad.lo.u32 %0, %1, %2, %3;" : "=r"(r) : "r"(b), "r"(0xFFFFFFFFu), "r"(a));
+    return r;
+#else
+    return a - b;
+#endif
+}
+CTB_HD uint32_t add_fma_pipe(uint32_t a, uint32_t b) {
+#if defined(__CUDA_ARCH__)
+    uint32_t r;
+    asm("mad.lo.u32 %0, %1, %2, %3;" : "=r"(r) : "r"(b), "r"(1u), "r"(a));
+    return r;
+#else
+    return a + b;
+#endif
 }
 
-// top bit of each 8-bit lane set where a >= b (unsigned); ah = a | 0x80.., bl = b & 0x7F..
-CTB_HD uint32_t ge_u8x4(uint32_t a, uint32_t b, uint32_t ah, uint32_t bl) {
-    const uint32_t t = ah - bl;  // per lane: 0x80 + (a & 0x7F) - (b & 0x7F), no borrow between lanes
-    return (a & ~b) | (~(a ^ b) & t);
+// lane-wise magnitude in torch's int8 arithmetic: m = abs_int8(v) as a byte, i.e. 0..127, and 0x80 for v = -128
+// (which therefore has to rank LOWEST: see ge_abs8x4)
+CTB_HD uint32_t abs_i8x4(uint32_t v) {
+    const uint32_t s = prmt(v, 0, 0xBA98);  // 0xFF in negative lanes
+    const uint32_t x = v ^ s;               // ~v in negative lanes; the lane's top bit is now clear
+    return add_fma_pipe(x, s & 0x01010101u);  // + 1 completes the negation; the sum stays inside the lane
+}
+
+// top bit of each 8-bit lane set where rank(a) >= rank(b), for magnitudes from abs_i8x4 (the rank of a magnitude
+// is the magnitude with its top bit flipped, so that 0x80 sorts below 0); ah = a | 0x80.., bl = b & 0x7F..
+CTB_HD uint32_t ge_abs8x4(uint32_t a, uint32_t b, uint32_t ah, uint32_t bl) {
+    const uint32_t t = sub_fma_pipe(ah, bl);  // per lane: 0x80 + (a & 0x7F) - (b & 0x7F), no borrow between lanes
+    // with A = ~a, B = ~b the rank top bits:  (A & ~B) | (~(A ^ B) & t)
+    return (~a & b) | (~(a ^ b) & t);
 }
 
 CTB_HD Keep4 keep24_u8x4(uint32_t x0, uint32_t x1, uint32_t x2, uint32_t x3) {
-    const uint32_t u0 = key_u8x4(x0), u1 = key_u8x4(x1), u2 = key_u8x4(x2), u3 = key_u8x4(x3);
+    const uint32_t u0 = abs_i8x4(x0), u1 = abs_i8x4(x1), u2 = abs_i8x4(x2), u3 = abs_i8x4(x3);
     const uint32_t H = 0x80808080u;
-    const uint32_t h0 = u0 | H, h1 = u1 | H, h2 = u2 | H, h3 = u3 | H;
+    const uint32_t h1 = u1 | H, h2 = u2 | H, h3 = u3 | H;
     const uint32_t l0 = u0 & ~H, l1 = u1 & ~H, l2 = u2 & ~H, l3 = u3 & ~H;
-    (void)h0;
-    (void)l3;
-    Keep4 k = keep24_rule(ge_u8x4(u1, u0, h1, l0), ge_u8x4(u2, u0, h2, l0), ge_u8x4(u3, u0, h3, l0), ge_u8x4(u2, u1, h2, l1),
-                          ge_u8x4(u3, u1, h3, l1), ge_u8x4(u3, u2, h3, l2), ge_u8x4(u1, u2, h1, l2), ge_u8x4(u1, u3, h1, l3),
-                          ge_u8x4(u2, u3, h2, l3));
+    Keep4 k = keep24_rule(ge_abs8x4(u1, u0, h1, l0), ge_abs8x4(u2, u0, h2, l0), ge_abs8x4(u3, u0, h3, l0), ge_abs8x4(u2, u1, h2, l1),
+                          ge_abs8x4(u3, u1, h3, l1), ge_abs8x4(u3, u2, h3, l2), ge_abs8x4(u1, u2, h1, l2), ge_abs8x4(u1, u3, h1, l3),
+                          ge_abs8x4(u2, u3, h2, l3));
     k.k0 = prmt(k.k0, 0, 0xBA98);
     k.k1 = prmt(k.k1, 0, 0xBA98);
     k.k2 = prmt(k.k2, 0, 0xBA98);
@@ -131,7 +152,8 @@ CTB_HD Keep4 keep24_u16x2(uint32_t x0, uint32_t x1, uint32_t x2, uint32_t x3) {
     const uint32_t u0 = x0 & M, u1 = x1 & M, u2 = x2 & M, u3 = x3 & M;
     const uint32_t h1 = u1 | H, h2 = u2 | H, h3 = u3 | H;
     // (a | H) - b keeps the lane's top bit iff a >= b (both below 0x8000); no borrow leaves a lane
-    Keep4 k = keep24_rule(h1 - u0, h2 - u0, h3 - u0, h2 - u1, h3 - u1, h3 - u2, h1 - u2, h1 - u3, h2 - u3);
+    Keep4 k = keep24_rule(sub_fma_pipe(h1, u0), sub_fma_pipe(h2, u0), sub_fma_pipe(h3, u0), sub_fma_pipe(h2, u1), sub_fma_pipe(h3, u1),
+                          sub_fma_pipe(h3, u2), sub_fma_pipe(h1, u2), sub_fma_pipe(h1, u3), sub_fma_pipe(h2, u3));
     k.k0 = prmt(k.k0, 0, 0xBB99);
     k.k1 = prmt(k.k1, 0, 0xBB99);
     k.k2 = prmt(k.k2, 0, 0xBB99);

@@ -196,6 +196,40 @@ def test_sparse_codecs_match_oracle(ops, orc):
     assert_bit_equal(gv2.cpu(), gv.cpu()), assert_bit_equal(gr2.cpu(), gr.cpu())
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32, torch.int8, torch.float8_e4m3fn])
+@pytest.mark.parametrize("shape", [(1, 8), (3, 8), (37, 24), (129, 1000), (5, 13), (700, 4096)])
+@pytest.mark.parametrize("density", [0.0, 0.03, 0.5, 1.0])
+def test_bitmask_codec_shapes_dtypes_densities(ops, orc, dtype, shape, density):
+    """ragged tile counts, every element size, empty / sparse / dense tensors, and a row length that is not a
+    multiple of 8 (the row-by-row kernels), all bit-exact against the oracle"""
+    g = torch.Generator().manual_seed(hash((shape, density)) % 1000)
+    if dtype == torch.int8:
+        w = torch.randint(1, 128, shape, generator=g).float()
+    else:
+        w = torch.randn(shape, generator=g) + 3.0  # no zeros before the mask is applied
+    w[torch.rand(shape, generator=g) >= density] = 0
+    w = w.to(dtype)
+    values, bitmask, row_offsets = orc.bitmask_compress(w)
+    gv, gb, gr = ops.bitmask_compress(w.cuda())
+    assert_bit_equal(gb.cpu(), bitmask, "bitmask"), assert_bit_equal(gr.cpu(), row_offsets, "row offsets")
+    assert_bit_equal(gv.cpu(), values, "values")
+    assert_bit_equal(ops.bitmask_decompress(gv, gb, w.shape).cpu(), orc.bitmask_decompress(values, bitmask, w.shape), "dense")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32, torch.int8, torch.float8_e4m3fn])
+@pytest.mark.parametrize("shape", [(1, 8), (3, 8), (37, 24), (129, 1000), (700, 4096)])
+def test_sparse24_codec_shapes_dtypes(ops, orc, dtype, shape):
+    """odd unit counts (the half-filled last thread) and every element size through the fused 2:4 kernels; small
+    integer magnitudes make ties the common case"""
+    g = torch.Generator().manual_seed(sum(shape))
+    t = torch.randint(-3, 4, shape, generator=g)
+    t = t.to(torch.int8) if dtype == torch.int8 else (t * 0.5).to(dtype)
+    v, b = orc.sparse24_compress(t)
+    dv, db = ops.sparse24_compress(t.cuda())
+    assert_bit_equal(db.cpu(), b, "bitmask"), assert_bit_equal(dv.cpu(), v, "values")
+    assert_bit_equal(ops.sparse24_decompress(dv, db, t.shape).cpu(), orc.bitmask_decompress(v, b, t.shape), "dense")
+
+
 @pytest.mark.parametrize("shape", [(14336, 4096), (4096, 14336), (1024, 4096)])
 def test_full_size_round_trip_properties(ops, shape):
     """At the benchmark's tensor sizes: compress -> decompress -> compress is a fixed point (same words, same
