@@ -187,6 +187,65 @@ __device__ __forceinline__ float group_scale(float amax, float g, float rg, floa
     }
 }
 
+// max |x| over 8 bf16 values held as four packed words (NaNs are skipped, as fmaxf skips them)
+__device__ __forceinline__ __nv_bfloat162 amax2_bf16(const uint4 &w) {
+    const __nv_bfloat162 a = __hmax2(__habs2(u32_as_bf162(w.x)), __habs2(u32_as_bf162(w.y)));
+    const __nv_bfloat162 b = __hmax2(__habs2(u32_as_bf162(w.z)), __habs2(u32_as_bf162(w.w)));
+    return __hmax2(a, b);
+}
+__device__ __forceinline__ float amax_of_pair(__nv_bfloat162 m) {
+    const uint32_t u = bf162_as_u32(m);
+    return fmaxf(__uint_as_float(u << 16), __uint_as_float(u & 0xFFFF0000u));
+}
+
+// W4A16 with groups of 128 on a bf16 weight, no rotation: calibrate + quantize + pack_to_int32 in one pass
+// (quantization/utils/helpers.py:110-122 for the scale, lifecycle/forward.py:420-448 for the codes,
+// compressors/quantized_compressors/pack_quantized.py:221 for the packing).  Two neighbouring lanes own a group:
+// lane half h holds the 16-byte chunks 2a + h (a = 0..7), so the pair reads 32 contiguous bytes per step, the
+// maximum stays in packed bf16 registers and the scale is computed once per 64 elements of a lane.
+__global__ void __launch_bounds__(kThreads) absmax_quant_g128_int4_kernel(const void *x, void *out, void *scale, int64_t ngroups) {
+    const int h = threadIdx.x & 1;
+    const int64_t pairs = (int64_t)gridDim.x * (kThreads / 2);
+    const int64_t padded = (ngroups + 15) & ~(int64_t)15;  // whole warps stay in the loop for the shuffles
+    for (int64_t g = (int64_t)blockIdx.x * (kThreads / 2) + (threadIdx.x >> 1); g < padded; g += pairs) {
+        const bool live = g < ngroups;
+        uint4 raw[8];
+#pragma unroll
+        for (int a = 0; a < 8; ++a) raw[a] = live ? ld_stream((const char *)x + (g * 16 + 2 * a + h) * 16) : make_uint4(0, 0, 0, 0);
+        __nv_bfloat162 m2 = amax2_bf16(raw[0]);
+#pragma unroll
+        for (int a = 1; a < 8; ++a) m2 = __hmax2(m2, amax2_bf16(raw[a]));
+        float amax = amax_of_pair(m2);
+        amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+        // scale = bf16(amax / 7.5) clamped at fp32 eps
+        const float s = fmaxf(round_to<CTB_BF16>(__fdiv_rn(amax, 7.5f)), 1.1920928955078125e-07f);
+        const float r = __frcp_rn(s);
+        if (live && h == 0) ((__nv_bfloat16 *)scale)[g] = __float2bfloat16_rn(s);
+        uint32_t word[8];
+#pragma unroll
+        for (int a = 0; a < 8; ++a) {
+            const uint32_t w[4] = {raw[a].x, raw[a].y, raw[a].z, raw[a].w};
+            word[a] = quant_int4_word_bf16(w, r, false, u32_as_bf162(0u));
+        }
+        // word[a] is output word 2a + h of the group's 16.  Swap so that half 0 owns words 0..7 and half 1 words
+        // 8..15, then two 16-byte stores per lane.
+        uint32_t mine[8];
+#pragma unroll
+        for (int a = 0; a < 4; ++a) {
+            const uint32_t send = h ? word[a] : word[a + 4];
+            const uint32_t got = __shfl_xor_sync(0xFFFFFFFFu, send, 1);
+            const uint32_t keep = h ? word[a + 4] : word[a];
+            mine[2 * a] = h ? got : keep;      // even word of the pair comes from half 0
+            mine[2 * a + 1] = h ? keep : got;  // odd word from half 1
+        }
+        if (live) {
+            char *o = (char *)out + g * 64 + h * 32;
+            st_stream(o, make_uint4(mine[0], mine[1], mine[2], mine[3]));
+            st_stream(o + 16, make_uint4(mine[4], mine[5], mine[6], mine[7]));
+        }
+    }
+}
+
 // groups of 8*GL consecutive elements (GL lanes, power of two <= 32), optional Hadamard in front.
 // A = float / double selects the rotation precision; ROT = false skips the rotation.
 template <typename A, bool ROT, int XF, int QK, int FOUT>
@@ -210,11 +269,16 @@ __global__ void __launch_bounds__(kThreads) absmax_quant_group_kernel(const HArg
             const int64_t c = base + (int64_t)u * kThreads;
             const bool live = c < a.chunks;
             float v[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-            if (live) decode8<XF>(raw[u], v);
-            if constexpr (ROT) rotate8<A, XF>(a, c, v);
             float amax = 0.0f;
+            constexpr bool kPackedMax = XF == F_BF16 && !ROT;  // the maximum straight from the packed words
+            if constexpr (kPackedMax) {
+                amax = amax_of_pair(amax2_bf16(raw[u].a));
+            } else {
+                if (live) decode8<XF>(raw[u], v);
+                if constexpr (ROT) rotate8<A, XF>(a, c, v);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+                for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+            }
             for (int o = a.GL >> 1; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
             QP q;
             q.s = group_scale<M, QK>(amax, gsv, rgs, a.half_range, r_half, a.out_scale, c >> a.gl_shift, live && (c & (a.GL - 1)) == 0);
@@ -248,6 +312,9 @@ __global__ void __launch_bounds__(kThreads) absmax_quant_group_kernel(const HArg
             }
             // the zero point calculate_qparams returns is all zeros; adding it matters only for the sign of an
             // fp8 zero (-0.0 + 0.0 = +0.0)
+            if constexpr (kPackedMax) {
+                if (live) decode8<XF>(raw[u], v);
+            }
             quant_prepare8<T>(v, q, QK == QK_FP8, 0.0f, a.qmin, a.qmax);
             if (live) encode_store8<QK, FOUT>(a.out, c, v);
         }
@@ -490,6 +557,11 @@ extern "C" int ctb_absmax_quantize(const ctb_qdesc *d, const void *x, const floa
         if (precision == CTB_F64) absmax_quant_group_kernel<double, true, F_BF16, QK_INT, F_PACK4><<<grid, kThreads, 0, st>>>(a);
         else absmax_quant_group_kernel<float, true, F_BF16, QK_INT, F_PACK4><<<grid, kThreads, 0, st>>>(a);
         return after_launch("absmax_quant_group_kernel");
+    }
+    if (fout == F_PACK4 && d->col_group == 128 && d->scale_row_stride == d->cols / 128) {
+        const int64_t ngroups = d->rows * d->cols / 128;
+        absmax_quant_g128_int4_kernel<<<grid_for(ngroups, kThreads / 2, 4), kThreads, 0, st>>>(x, out, out_scale, ngroups);
+        return after_launch("absmax_quant_g128_int4_kernel");
     }
     if (pow2(GL) && GL <= 32 && d->scale_row_stride == d->cols / d->col_group) {
         a.GL = (int)GL;
