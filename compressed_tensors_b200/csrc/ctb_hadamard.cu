@@ -321,6 +321,54 @@ __global__ void __launch_bounds__(kThreads) absmax_quant_group_kernel(const HArg
     }
 }
 
+// NVFP4 (groups of 16, e4m3 group scales under an fp32 global scale) on a bf16 tensor: one lane owns a group, so
+// the maximum needs no shuffle, the scale chain (e4m3 round trip, two corrected divisions, one reciprocal) runs
+// once per 16 elements, and a lane moves 32 contiguous bytes in and 8 + 1 out.  Two groups in flight per lane.
+__global__ void __launch_bounds__(kThreads) absmax_quant_g16_fp4_kernel(const HArgs a, int64_t ngroups) {
+    constexpr int U = 2;
+    const float gsv = __ldg(a.gs), rgs = __frcp_rn(gsv), r_half = __frcp_rn(a.half_range);
+    const int64_t stride = (int64_t)gridDim.x * kThreads * U;
+    for (int64_t base = (int64_t)blockIdx.x * kThreads * U + threadIdx.x; base < ngroups; base += stride) {
+        uint4 raw[U][2];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int64_t g = base + (int64_t)u * kThreads;
+            raw[u][0] = raw[u][1] = make_uint4(0, 0, 0, 0);
+            if (g < ngroups) {
+                raw[u][0] = ld_stream((const char *)a.x + g * 32);
+                raw[u][1] = ld_stream((const char *)a.x + g * 32 + 16);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int64_t g = base + (int64_t)u * kThreads;
+            if (g >= ngroups) break;
+            const float amax = amax_of_pair(__hmax2(amax2_bf16(raw[u][0]), amax2_bf16(raw[u][1])));
+            QP q;
+            q.s = group_scale<CTB_BF16, QK_FP4>(amax, gsv, rgs, a.half_range, r_half, a.out_scale, g, true);
+            q.r = __frcp_rn(q.s);
+            q.zp = 0.0f;
+            q.slow = !(fabsf(q.s) >= 1.0e-30f && fabsf(q.s) <= 1.0e30f);
+            if (!q.slow && amax <= 3.0e38f) {
+                // finite group and a scale in the normal range: reciprocal + Markstein, saturating e2m1 convert
+                const uint32_t w0[4] = {raw[u][0].x, raw[u][0].y, raw[u][0].z, raw[u][0].w};
+                const uint32_t w1[4] = {raw[u][1].x, raw[u][1].y, raw[u][1].z, raw[u][1].w};
+                st_stream8((char *)a.out + g * 8, make_uint2(quant_fp4_codes_f32(w0, q.s, q.r), quant_fp4_codes_f32(w1, q.s, q.r)));
+                continue;
+            }
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                Raw8 r8;
+                r8.a = raw[u][h];
+                float v[8];
+                decode8<F_BF16>(r8, v);
+                quant_prepare8<CTB_F32>(v, q, false, 0.0f, a.qmin, a.qmax);
+                encode_store8<QK_FP4, F_FP4X2>(a.out, g * 2 + h, v);
+            }
+        }
+    }
+}
+
 // one warp per row, the whole row in registers (CHANNEL / TOKEN with cols <= 8 * 32 * CPL): a single pass with
 // no shared memory and no block barrier.  CPL = 16-byte chunks per lane.
 template <int CPL, int XF, int QK, int FOUT>
@@ -562,6 +610,11 @@ extern "C" int ctb_absmax_quantize(const ctb_qdesc *d, const void *x, const floa
         const int64_t ngroups = d->rows * d->cols / 128;
         absmax_quant_g128_int4_kernel<<<grid_for(ngroups, kThreads / 2, 4), kThreads, 0, st>>>(x, out, out_scale, ngroups);
         return after_launch("absmax_quant_g128_int4_kernel");
+    }
+    if (fout == F_FP4X2 && d->col_group == 16 && d->scale_row_stride == d->cols / 16) {
+        const int64_t ngroups = d->rows * d->cols / 16;
+        absmax_quant_g16_fp4_kernel<<<grid_for(ngroups, kThreads * 2, 8), kThreads, 0, st>>>(a, ngroups);
+        return after_launch("absmax_quant_g16_fp4_kernel");
     }
     if (pow2(GL) && GL <= 32 && d->scale_row_stride == d->cols / d->col_group) {
         a.GL = (int)GL;
