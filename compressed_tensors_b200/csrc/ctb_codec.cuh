@@ -250,30 +250,40 @@ __device__ __forceinline__ void round8(float (&v)[8]) {
 __device__ __forceinline__ uint32_t bf162_as_u32(__nv_bfloat162 v) { return *reinterpret_cast<uint32_t *>(&v); }
 __device__ __forceinline__ __nv_bfloat162 u32_as_bf162(uint32_t v) { return *reinterpret_cast<__nv_bfloat162 *>(&v); }
 
-// int4 code byte (two nibbles) from a packed pair of bf16 values already divided by the scale
-__device__ __forceinline__ uint32_t int4_pair_code(__nv_bfloat162 q) {
+// A packed pair of bf16 values already divided by the scale -> clamp to [-8, 7], then add 200: the sum lies in
+// [192, 207], where a bf16 step is 1, so the addition rounds half to even and the low byte of each half is
+// 0x40 | (code + 8), i.e. its low nibble is the offset-binary int4 code.
+__device__ __forceinline__ uint32_t int4_pair_magic(__nv_bfloat162 q) {
     const __nv_bfloat162 lo = u32_as_bf162(0xC100C100u);     // -8, -8
     const __nv_bfloat162 hi = u32_as_bf162(0x40E040E0u);     //  7,  7
     const __nv_bfloat162 magic = u32_as_bf162(0x43484348u);  // 200, 200
-    q = __hmin2(__hmax2(q, lo), hi);
-    uint32_t m = bf162_as_u32(__hadd2(q, magic));
-    return (m & 0xFu) | ((m >> 12) & 0xF0u);  // bits 8.. are don't-care for the caller's byte permute
+    return bf162_as_u32(__hadd2(__hmin2(__hmax2(q, lo), hi), magic));
 }
 
+// byte permute by the PTX instruction (selector nibble i picks the source byte of result byte i)
+__device__ __forceinline__ uint32_t prmt_b32(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+    return r;
+}
 
 // 8 bf16 inputs (4 packed words) -> one pack_to_int32 word of int4 codes, compute dtype bf16:
 //   q = bf16_rn(x * rcp(s)) [+ zero point, rounded to bf16]; clamp to [-8, 7]; round half to even.
 // `zp2` is the zero point replicated in both halves (bf16x2), ignored unless has_zp.
+// The eight code bytes are gathered with byte permutes and their low nibbles merged two at a time.
 __device__ __forceinline__ uint32_t quant_int4_word_bf16(const uint32_t (&w)[4], float r, bool has_zp, __nv_bfloat162 zp2) {
-    uint32_t b[4];
+    uint32_t m[4];
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
         const float f0 = __uint_as_float(w[k] << 16), f1 = __uint_as_float(w[k] & 0xFFFF0000u);
         __nv_bfloat162 q = __floats2bfloat162_rn(f0 * r, f1 * r);
         if (has_zp) q = __hadd2(q, zp2);
-        b[k] = int4_pair_code(q);
+        m[k] = int4_pair_magic(q);
     }
-    return __byte_perm(__byte_perm(b[0], b[1], 0x0040), __byte_perm(b[2], b[3], 0x0040), 0x5410);
+    const uint32_t a = prmt_b32(m[0], m[1], 0x6420), b = prmt_b32(m[2], m[3], 0x6420);  // code bytes of elements 0-3, 4-7
+    const uint32_t ta = (a & 0x0F0F0F0Fu) | ((a >> 4) & 0xF0F0F0F0u);  // byte 0: elements 0, 1; byte 2: elements 2, 3
+    const uint32_t tb = (b & 0x0F0F0F0Fu) | ((b >> 4) & 0xF0F0F0F0u);
+    return prmt_b32(ta, tb, 0x6420);
 }
 
 // one pack_to_int32 word of int4 codes -> 8 bf16 outputs (4 packed words), compute dtype bf16:
