@@ -106,6 +106,49 @@ __global__ void __launch_bounds__(kThreads) qdq_vec8_kernel(const QArgs a) {
     }
 }
 
+// NVFP4 decompress (compressors/quantized_compressors/fp4_quantized.py:123-148 unpack, lifecycle/forward.py:468-469
+// and :500-509 for the arithmetic): e2m1 codes, e4m3 group scales under an fp32 global scale, bf16 out.  One lane
+// per 8 elements (4 code bytes in, 16 bytes out, both fully coalesced); the two lanes of a group read the same
+// scale byte.  There are only 256 possible scale bytes, so the effective scales float(e4m3) / global_scale are
+// divided once per block (IEEE division, exactly what the reference computes) into a shared table, and a chunk
+// costs one table read instead of a division.
+__global__ void __launch_bounds__(kThreads) dequant_fp4_g16_bf16_kernel(const void *codes, const uint8_t *scale, const float *gs, int64_t chunks, void *out) {
+    __shared__ float s_eff[256];
+    static_assert(kThreads == 256, "one table entry per thread");
+    s_eff[threadIdx.x] = __fdiv_rn(e4m3_to_f32((uint8_t)threadIdx.x), __ldg(gs));
+    __syncthreads();
+    constexpr int U = 8;
+    const int64_t stride = (int64_t)gridDim.x * kThreads * U;
+    for (int64_t base = (int64_t)blockIdx.x * kThreads * U + threadIdx.x; base < chunks; base += stride) {
+        uint32_t w[U], sb[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int64_t c = base + (int64_t)u * kThreads;
+            w[u] = 0;
+            sb[u] = 0;
+            if (c < chunks) {
+                w[u] = ld_stream4((const char *)codes + c * 4);
+                sb[u] = scale[c >> 1];
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int64_t c = base + (int64_t)u * kThreads;
+            if (c >= chunks) break;
+            const float s = s_eff[sb[u]];
+            uint32_t p[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                // low nibble = even element; nibble 0x8 decodes to -0.0, which the product keeps
+                const __half2_raw h = __nv_cvt_fp4x2_to_halfraw2((__nv_fp4x2_storage_t)((w[u] >> (8 * i)) & 0xFFu), __NV_E2M1);
+                const float2 f = __half22float2(__half2(h));
+                p[i] = bf162_as_u32(__floats2bfloat162_rn(f.x * s, f.y * s));  // fp32 product, then one rounding to bf16
+            }
+            st_stream((char *)out + c * 16, make_uint4(p[0], p[1], p[2], p[3]));
+        }
+    }
+}
+
 // ------------------------------------------------------------------ generic tier
 
 __device__ __forceinline__ float quant_scalar(const QArgs &a, float x, float s, bool has_zp, float zp) {
@@ -340,6 +383,11 @@ static int run(int mode, const ctb_qdesc *d, const void *in, const void *scale, 
             int sh = 0;
             while ((1LL << sh) < d->col_group) ++sh;
             a.gshift = sh;
+        }
+        if (mode == 1 && a.qk == QK_FP4 && a.fin == F_FP4X2 && a.fout == F_BF16 && d->scale_dtype == CTB_E4M3 && gs && !zp && flat &&
+            d->col_group == 16) {
+            dequant_fp4_g16_bf16_kernel<<<grid_for(a.chunks, (int64_t)kThreads * 8, 8), kThreads, 0, st>>>(in, (const uint8_t *)scale, gs, a.chunks, out);
+            return after_launch("dequant_fp4_g16_bf16_kernel");
         }
         bool handled = false;
         rc = dispatch_vec8(mode, a, st, &handled);

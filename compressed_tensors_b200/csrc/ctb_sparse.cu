@@ -106,11 +106,32 @@ __global__ void __launch_bounds__(kThreads) sparse24_mask_kernel(const void *x, 
 template <int ES>
 __global__ void __launch_bounds__(kThreads) sparse24_compress_simd_kernel(const void *x, int64_t units, void *values, uint8_t *bitmask) {
     static_assert(ES == 1 || ES == 2, "SIMD lanes are 8 or 16 bits");
-    const int64_t items = (units + 1) >> 1;
-    for (int64_t it = (int64_t)blockIdx.x * kThreads + threadIdx.x; it < items; it += (int64_t)gridDim.x * kThreads) {
-        const int64_t u = it * 2;
-        const bool both = u + 1 < units;
-        if constexpr (ES == 1) {
+    if constexpr (ES == 2) {
+        // 16 bytes per unit: lane l of a warp takes units 64 t + l and 64 t + 32 + l, so that every load and
+        // store instruction of the warp covers one contiguous span
+        const int64_t items = ((units + 63) >> 6) << 5;
+        for (int64_t it = (int64_t)blockIdx.x * kThreads + threadIdx.x; it < items; it += (int64_t)gridDim.x * kThreads) {
+            const int64_t ua = ((it >> 5) << 6) + (it & 31), ub = ua + 32;
+            uint4 a = make_uint4(0, 0, 0, 0), b = make_uint4(0, 0, 0, 0);
+            if (ua < units) a = ld_stream((const char *)x + ua * 16);
+            if (ub < units) b = ld_stream((const char *)x + ub * 16);
+            uint32_t v0, v1, v2, v3, m0, m1;
+            sparse24_pack_u16x8(a.x, a.y, a.z, a.w, v0, v1, m0);
+            sparse24_pack_u16x8(b.x, b.y, b.z, b.w, v2, v3, m1);
+            if (ua < units) {
+                st_stream8((char *)values + ua * 8, make_uint2(v0, v1));
+                bitmask[ua] = (uint8_t)m0;
+            }
+            if (ub < units) {
+                st_stream8((char *)values + ub * 8, make_uint2(v2, v3));
+                bitmask[ub] = (uint8_t)m1;
+            }
+        }
+    } else {
+        const int64_t items = (units + 1) >> 1;
+        for (int64_t it = (int64_t)blockIdx.x * kThreads + threadIdx.x; it < items; it += (int64_t)gridDim.x * kThreads) {
+            const int64_t u = it * 2;
+            const bool both = u + 1 < units;
             uint4 w = make_uint4(0, 0, 0, 0);
             if (both) w = ld_stream((const char *)x + u * 8);
             else {
@@ -126,20 +147,6 @@ __global__ void __launch_bounds__(kThreads) sparse24_compress_simd_kernel(const 
             } else {
                 st_stream4((char *)values + u * 4, v0);
                 bitmask[u] = (uint8_t)m;
-            }
-        } else {
-            const uint4 a = ld_stream((const char *)x + u * 16);
-            uint4 b = make_uint4(0, 0, 0, 0);
-            if (both) b = ld_stream((const char *)x + u * 16 + 16);
-            uint32_t v0, v1, v2, v3, m0, m1;
-            sparse24_pack_u16x8(a.x, a.y, a.z, a.w, v0, v1, m0);
-            sparse24_pack_u16x8(b.x, b.y, b.z, b.w, v2, v3, m1);
-            if (both) {
-                st_stream((char *)values + u * 8, make_uint4(v0, v1, v2, v3));
-                *reinterpret_cast<uint16_t *>(bitmask + u) = (uint16_t)(m0 | (m1 << 8));
-            } else {
-                st_stream8((char *)values + u * 8, make_uint2(v0, v1));
-                bitmask[u] = (uint8_t)m0;
             }
         }
     }
@@ -208,56 +215,81 @@ __global__ void __launch_bounds__(kThreads) sparse24_expand_simd_kernel(const vo
     }
     __syncthreads();
     bool bad = false;
-    const int64_t items = (units + 1) >> 1;
     const int64_t stride = (int64_t)gridDim.x * kThreads;
-    constexpr int U = 4;  // items in flight per thread: the loads of all of them are issued before the first is used
-    for (int64_t it0 = (int64_t)blockIdx.x * kThreads + threadIdx.x; it0 < items; it0 += U * stride) {
-        uint32_t m[U];
-        uint4 v[U];
+    if constexpr (ES == 2) {
+        // lane l of a warp takes units 64 t + l and 64 t + 32 + l: every load and store instruction of the warp
+        // covers one contiguous span (16 bytes out per unit)
+        const int64_t items = ((units + 63) >> 6) << 5;
+        constexpr int U = 2;
+        for (int64_t it0 = (int64_t)blockIdx.x * kThreads + threadIdx.x; it0 < items; it0 += U * stride) {
+            uint32_t m[U][2];
+            uint2 v[U][2];
 #pragma unroll
-        for (int k = 0; k < U; ++k) {
-            const int64_t u = (it0 + k * stride) * 2;
-            m[k] = 0;
-            v[k] = make_uint4(0, 0, 0, 0);
-            if (u + 1 < units) {
-                m[k] = *reinterpret_cast<const uint16_t *>(bitmask + u);
-                if constexpr (ES == 1) {
-                    const uint2 t = ld_stream8((const char *)values + u * 4);
-                    v[k].x = t.x;
-                    v[k].y = t.y;
-                } else {
-                    v[k] = ld_stream((const char *)values + u * 8);
+            for (int k = 0; k < U; ++k) {
+                const int64_t it = it0 + k * stride;
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int64_t u = ((it >> 5) << 6) + (it & 31) + 32 * h;
+                    m[k][h] = 0x33u;  // an absent unit counts as regular
+                    v[k][h] = make_uint2(0, 0);
+                    if (it < items && u < units) {
+                        m[k][h] = bitmask[u];
+                        v[k][h] = ld_stream8((const char *)values + u * 8);
+                    }
                 }
-            } else if (u < units) {
-                m[k] = bitmask[u];
-                if constexpr (ES == 1) v[k].x = ld_stream4((const char *)values + u * 4);
-                else {
-                    const uint2 t = ld_stream8((const char *)values + u * 8);
-                    v[k].x = t.x;
-                    v[k].y = t.y;
+            }
+#pragma unroll
+            for (int k = 0; k < U; ++k) {
+                const int64_t it = it0 + k * stride;
+                if (it >= items) break;
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int64_t u = ((it >> 5) << 6) + (it & 31) + 32 * h;
+                    const uint32_t mm = m[k][h];
+                    uint32_t c = mm - ((mm >> 1) & 0x55u);
+                    c = (c & 0x33u) + ((c >> 2) & 0x33u);
+                    bad |= c != 0x22u;  // each nibble must have exactly two bits set
+                    const uint32_t s0 = lut[mm & 0xFu], s1 = lut[mm >> 4];
+                    if (u < units)
+                        st_stream((char *)out + u * 16, make_uint4(prmt(v[k][h].x, 0, s0 & 0xFFFFu), prmt(v[k][h].x, 0, s0 >> 16),
+                                                                   prmt(v[k][h].y, 0, s1 & 0xFFFFu), prmt(v[k][h].y, 0, s1 >> 16)));
                 }
             }
         }
+    } else {
+        const int64_t items = (units + 1) >> 1;
+        constexpr int U = 4;  // items in flight per thread: the loads of all of them are issued before the first is used
+        for (int64_t it0 = (int64_t)blockIdx.x * kThreads + threadIdx.x; it0 < items; it0 += U * stride) {
+            uint32_t m[U];
+            uint2 v[U];
 #pragma unroll
-        for (int k = 0; k < U; ++k) {
-            const int64_t u = (it0 + k * stride) * 2;
-            if (u >= units) break;
-            const bool both = u + 1 < units;
-            {  // every nibble must have exactly two bits set (the absent second unit counts as regular)
-                uint32_t c = m[k] - ((m[k] >> 1) & 0x5555u);
-                c = (c & 0x3333u) + ((c >> 2) & 0x3333u);
-                bad |= c != (both ? 0x2222u : 0x0022u);
+            for (int k = 0; k < U; ++k) {
+                const int64_t u = (it0 + k * stride) * 2;
+                m[k] = 0;
+                v[k] = make_uint2(0, 0);
+                if (u + 1 < units) {
+                    m[k] = *reinterpret_cast<const uint16_t *>(bitmask + u);
+                    v[k] = ld_stream8((const char *)values + u * 4);
+                } else if (u < units) {
+                    m[k] = bitmask[u];
+                    v[k].x = ld_stream4((const char *)values + u * 4);
+                }
             }
-            const uint32_t s0 = lut[m[k] & 0xFu], s1 = lut[(m[k] >> 4) & 0xFu], s2 = lut[(m[k] >> 8) & 0xFu], s3 = lut[(m[k] >> 12) & 0xFu];
-            if constexpr (ES == 1) {
+#pragma unroll
+            for (int k = 0; k < U; ++k) {
+                const int64_t u = (it0 + k * stride) * 2;
+                if (u >= units) break;
+                const bool both = u + 1 < units;
+                {  // every nibble must have exactly two bits set (the absent second unit counts as regular)
+                    uint32_t c = m[k] - ((m[k] >> 1) & 0x5555u);
+                    c = (c & 0x3333u) + ((c >> 2) & 0x3333u);
+                    bad |= c != (both ? 0x2222u : 0x0022u);
+                }
+                const uint32_t s0 = lut[m[k] & 0xFu], s1 = lut[(m[k] >> 4) & 0xFu], s2 = lut[(m[k] >> 8) & 0xFu], s3 = lut[(m[k] >> 12) & 0xFu];
                 const uint32_t o0 = prmt(v[k].x, 0, s0), o1 = prmt(v[k].x >> 16, 0, s1);
                 const uint32_t o2 = prmt(v[k].y, 0, s2), o3 = prmt(v[k].y >> 16, 0, s3);
                 if (both) st_stream((char *)out + u * 8, make_uint4(o0, o1, o2, o3));
                 else st_stream8((char *)out + u * 8, make_uint2(o0, o1));
-            } else {
-                st_stream((char *)out + u * 16, make_uint4(prmt(v[k].x, 0, s0 & 0xFFFFu), prmt(v[k].x, 0, s0 >> 16), prmt(v[k].y, 0, s1 & 0xFFFFu), prmt(v[k].y, 0, s1 >> 16)));
-                if (both)
-                    st_stream((char *)out + u * 16 + 16, make_uint4(prmt(v[k].z, 0, s2 & 0xFFFFu), prmt(v[k].z, 0, s2 >> 16), prmt(v[k].w, 0, s3 & 0xFFFFu), prmt(v[k].w, 0, s3 >> 16)));
             }
         }
     }
@@ -585,24 +617,25 @@ __device__ __forceinline__ unsigned long long warp_first_value(const unsigned lo
     return base;
 }
 
-// this lane's 16 mask bits of tile `tile` (units past the end read as zero)
-__device__ __forceinline__ uint32_t lane_mask(const uint8_t *bitmask, int64_t u0, int64_t units) {
-    if (u0 + 1 < units) return *reinterpret_cast<const uint16_t *>(bitmask + u0);
-    if (u0 < units) return bitmask[u0];
-    return 0u;
-}
+// Within a tile of 64 units (8 elements each) lane l owns unit l of the first half and unit 32 + l of the second,
+// so that each load or store instruction of the warp covers one contiguous span.  In tile order the lane's two
+// pieces are (half 0, lane l) and (half 1, lane l).
 
-// exclusive prefix of c over the warp, and the warp total
-__device__ __forceinline__ int warp_excl_scan(int c, int &total) {
-    int inc = c;
+// exclusive prefixes of this lane's two pieces within the tile, and the tile total: one scan on the packed pair
+// of counts (each at most 8 per lane, 256 per half)
+__device__ __forceinline__ void warp_excl_scan2(int c0, int c1, int &excl0, int &excl1, int &total) {
     const int lane = threadIdx.x & 31;
+    uint32_t inc = (uint32_t)c0 | ((uint32_t)c1 << 16);
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
-        const int t = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+        const uint32_t t = __shfl_up_sync(0xFFFFFFFFu, inc, o);
         if (lane >= o) inc += t;
     }
-    total = __shfl_sync(0xFFFFFFFFu, inc, 31);
-    return inc - c;
+    const uint32_t all = __shfl_sync(0xFFFFFFFFu, inc, 31);
+    const int tot0 = (int)(all & 0xFFFFu);
+    excl0 = (int)(inc & 0xFFFFu) - c0;
+    excl1 = tot0 + (int)(inc >> 16) - c1;
+    total = tot0 + (int)(all >> 16);
 }
 
 // raw 16-byte (ES = 2), 8-byte (ES = 1) or 32-byte (ES = 4) image of one 8-element unit; KEEP = the dense tensor is
@@ -672,17 +705,15 @@ __global__ void __launch_bounds__(kThreads) bm_warp_count_kernel(const void *x, 
     const int lane = threadIdx.x & 31;
     int cnt = 0;
     for (int64_t tile = first; tile < last; ++tile) {
-        const int64_t u0 = tile * 64 + lane * 2;
-        uint32_t mask = 0;
-        if (u0 + 1 < units) {
-            const Raw8 r0 = load_unit_raw<ES, true>(x, u0), r1 = load_unit_raw<ES, true>(x, u0 + 1);
-            mask = unit_nz_mask<ES>(r0, nzm) | (unit_nz_mask<ES>(r1, nzm) << 8);
-            *reinterpret_cast<uint16_t *>(bitmask + u0) = (uint16_t)mask;
-        } else if (u0 < units) {
-            mask = unit_nz_mask<ES>(load_unit_raw<ES, true>(x, u0), nzm);
-            bitmask[u0] = (uint8_t)mask;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int64_t u = tile * 64 + 32 * h + lane;
+            if (u < units) {
+                const uint32_t m = unit_nz_mask<ES>(load_unit_raw<ES, true>(x, u), nzm);
+                bitmask[u] = (uint8_t)m;
+                cnt += __popc(m);
+            }
         }
-        cnt += __popc(mask);
     }
     publish_counts((unsigned long long)cnt, block_tot, warp_tot);
 }
@@ -718,37 +749,49 @@ __global__ void __launch_bounds__(kThreads) bm_warp_scatter_kernel(const void *x
     uint32_t *st = stage_all[threadIdx.x >> 5];
     int64_t first, last;
     warp_range((units + 63) / 64, first, last);
-    unsigned long long prefix = warp_first_value(block_tot, warp_tot, nnz);
     const int lane = threadIdx.x & 31;
+    uint32_t mask_n[2] = {0, 0};
+    Raw8 raw_n[2];
+    auto fetch = [&](int64_t t) {  // a tile's loads do not depend on the running offset: they are issued one tile ahead
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int64_t u = t * 64 + 32 * h + lane;
+            mask_n[h] = 0;
+            raw_n[h].a = raw_n[h].b = make_uint4(0, 0, 0, 0);
+            if (u < units) {
+                mask_n[h] = bitmask[u];
+                raw_n[h] = load_unit_raw<ES, false>(x, u);
+            }
+        }
+    };
+    if (first < last) fetch(first);  // in flight during the prologue
+    unsigned long long prefix = warp_first_value(block_tot, warp_tot, nnz);
     int64_t r_next = (first * kWarpTile + cols - 1) / cols;  // first row that starts inside this warp's range
     int64_t e_next = r_next * cols;
     for (int64_t tile = first; tile < last; ++tile) {
-        const int64_t u0 = tile * 64 + lane * 2;  // first of this lane's two 8-element units
-        const uint32_t mask = lane_mask(bitmask, u0, units);
-        Raw8 raw[2];
-        raw[0].a = raw[0].b = raw[1].a = raw[1].b = make_uint4(0, 0, 0, 0);
-        if (u0 < units) raw[0] = load_unit_raw<ES, false>(x, u0);
-        if (u0 + 1 < units) raw[1] = load_unit_raw<ES, false>(x, u0 + 1);
-        int total;
-        const int excl = warp_excl_scan(__popc(mask), total);
+        const uint32_t mask[2] = {mask_n[0], mask_n[1]};
+        const Raw8 raw[2] = {raw_n[0], raw_n[1]};
+        if (tile + 1 < last) fetch(tile + 1);
+        int excl[2], total;
+        warp_excl_scan2(__popc(mask[0]), __popc(mask[1]), excl[0], excl[1], total);
         char *dst = (char *)values + prefix * ES;
         const int shift = (int)(reinterpret_cast<uintptr_t>(dst) & 3u);  // the window mirrors the destination's alignment
-        int o = shift + excl * ES;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             uint32_t b[8];
             unit_bits<ES>(raw[h], b);
+            int o = shift + excl[h] * ES;
 #pragma unroll
             for (int j = 0; j < 8; ++j)
-                if ((mask >> (8 * h + j)) & 1) {
+                if ((mask[h] >> j) & 1) {
                     stage_store<ES>(st, o, b[j]);
                     o += ES;
                 }
         }
-        // rows that begin inside this tile (cols is a multiple of 8, so at offset 0 or 8 of some lane's 16 elements)
+        // rows that begin inside this tile (cols is a multiple of 8: at the first element of one of its 64 units)
         while (e_next < (tile + 1) * kWarpTile && r_next < rows) {  // uniform over the warp
-            const int off = (int)(e_next - tile * kWarpTile);
-            if (lane == (off >> 4)) row_offsets[r_next] = (int64_t)(prefix + excl + ((off & 8) ? __popc(mask & 0xFFu) : 0));
+            const int unit = (int)(e_next - tile * kWarpTile) >> 3;
+            if (lane == (unit & 31)) row_offsets[r_next] = (int64_t)(prefix + ((unit >> 5) ? excl[1] : excl[0]));
             ++r_next;
             e_next += cols;
         }
@@ -771,7 +814,7 @@ __global__ void __launch_bounds__(kThreads) bm_warp_scatter_kernel(const void *x
 }
 
 // decompress, kernel 2 (same grid as kernel 1): every tile's kept values are one contiguous run of `values`; bring
-// it in as whole 32-bit words, then every lane rebuilds its 16 elements from the window
+// it in as whole 32-bit words, then every lane rebuilds its two units from the window
 template <int ES>
 __global__ void __launch_bounds__(kThreads) bm_warp_expand_kernel(const void *values, const uint8_t *bitmask, int64_t units, const unsigned long long *block_tot,
                                                                   const unsigned long long *warp_tot, void *out, const int *gate) {
@@ -780,13 +823,22 @@ __global__ void __launch_bounds__(kThreads) bm_warp_expand_kernel(const void *va
     uint32_t *st = stage_all[threadIdx.x >> 5];
     int64_t first, last;
     warp_range((units + 63) / 64, first, last);
-    unsigned long long src = warp_first_value(block_tot, warp_tot, nullptr);
     const int lane = threadIdx.x & 31;
+    uint32_t mask_n[2] = {0, 0};
+    auto fetch = [&](int64_t t) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int64_t u = t * 64 + 32 * h + lane;
+            mask_n[h] = u < units ? (uint32_t)bitmask[u] : 0u;
+        }
+    };
+    if (first < last) fetch(first);  // in flight during the prologue
+    unsigned long long src = warp_first_value(block_tot, warp_tot, nullptr);
     for (int64_t tile = first; tile < last; ++tile) {
-        const int64_t u0 = tile * 64 + lane * 2;
-        const uint32_t mask = lane_mask(bitmask, u0, units);
-        int total;
-        const int excl = warp_excl_scan(__popc(mask), total);
+        const uint32_t mask[2] = {mask_n[0], mask_n[1]};
+        if (tile + 1 < last) fetch(tile + 1);  // one tile ahead
+        int excl[2], total;
+        warp_excl_scan2(__popc(mask[0]), __popc(mask[1]), excl[0], excl[1], total);
         const char *a = (const char *)values + src * ES;
         const int shift = (int)(reinterpret_cast<uintptr_t>(a) & 3u);
         const int nwords = (shift + total * ES + 3) >> 2;  // whole words: the first and last may hold neighbours' bytes, never read
@@ -794,20 +846,21 @@ __global__ void __launch_bounds__(kThreads) bm_warp_expand_kernel(const void *va
 #pragma unroll 4
         for (int w = lane; w < nwords; w += 32) st[pad_word(w)] = ld_stream4(a0 + w);
         __syncwarp();
-        int o = shift + excl * ES;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-            if (u0 + h >= units) break;
+            const int64_t u = tile * 64 + 32 * h + lane;
+            if (u >= units) continue;
+            int o = shift + excl[h] * ES;
             uint32_t b[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 b[j] = 0u;
-                if ((mask >> (8 * h + j)) & 1) {
+                if ((mask[h] >> j) & 1) {
                     b[j] = stage_load<ES>(st, o);
                     o += ES;
                 }
             }
-            char *q = (char *)out + (u0 + h) * 8 * ES;
+            char *q = (char *)out + u * 8 * ES;
             if constexpr (ES == 2) st_stream(q, make_uint4(b[0] | (b[1] << 16), b[2] | (b[3] << 16), b[4] | (b[5] << 16), b[6] | (b[7] << 16)));
             else if constexpr (ES == 1) st_stream8(q, make_uint2(b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24), b[4] | (b[5] << 8) | (b[6] << 16) | (b[7] << 24)));
             else {
