@@ -547,13 +547,14 @@ constexpr int kWarps = kThreads / 32;
 constexpr int kWarpTile = 512;      // elements per warp and step
 constexpr int kTileMaxGrid = 4096;  // blocks per launch (bounds the scratch: nine words per block)
 
-// word w of a warp's staging window lives at w + w / 4: lanes whose runs start 16 bytes apart (50 % density of
-// 16-bit elements) then fall on different banks
-__device__ __forceinline__ int pad_word(int w) { return w + (w >> 2); }
-__device__ __forceinline__ int pad_byte(int o) { return o + ((o >> 4) << 2); }
+// A warp's staging window is addressed plainly: with lane l owning units l and 32 + l, the lanes' runs start
+// about 8 bytes apart at 50 % density of 16-bit elements, i.e. two lanes per bank, and the index arithmetic that
+// padding would add to every element costs more than that conflict.
+__device__ __forceinline__ int pad_word(int w) { return w; }
+__device__ __forceinline__ int pad_byte(int o) { return o; }
 template <int ES>
 struct StageWords {
-    static constexpr int value = (kWarpTile * ES / 4 + 2) * 5 / 4 + 2;
+    static constexpr int value = kWarpTile * ES / 4 + 2;
 };
 
 template <int ES>
