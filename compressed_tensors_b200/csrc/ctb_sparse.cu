@@ -4,12 +4,22 @@
 // Layout facts shared with the reference: values are row-major, bitmask byte k of a row holds
 // columns 8k..8k+7 with column 8k+j in bit j (numpy.packbits, bitorder="little"), row_offsets is the
 // int64 exclusive prefix of the per-row counts.
+#include <atomic>
+
 #include "ctb_codec.cuh"
 #include "ctb_sparse24_simd.cuh"
 
 namespace ctb {
 
 constexpr int kThreads = 256;
+
+// A kernel launched as the fallback of another one runs only if *flag holds `value`.  The value is a per-call
+// ticket rather than 1, so the flag word never has to be cleared between calls: a stale word matches a new ticket
+// with probability 2^-32, and a false match only costs the time of the (correct) generic kernels.
+struct Gate {
+    const int *flag;
+    int value;
+};
 
 
 // element classes by storage size; `nz_mask` selects the bits that make an element non-zero
@@ -196,7 +206,7 @@ __global__ void __launch_bounds__(kThreads) sparse24_compress_kernel(const void 
 // indexed by the run's mask nibble.  A bitmask that breaks the two-per-run rule raises *irregular; the generic
 // kernels then redo the tensor (they are launched right behind this one and return at once when the flag is clear).
 template <int ES>
-__global__ void __launch_bounds__(kThreads) sparse24_expand_simd_kernel(const void *values, const uint8_t *bitmask, int64_t units, void *out, int *irregular) {
+__global__ void __launch_bounds__(kThreads) sparse24_expand_simd_kernel(const void *values, const uint8_t *bitmask, int64_t units, void *out, int *irregular, int irregular_value) {
     static_assert(ES == 1 || ES == 2, "byte-permute expansion is for 8- and 16-bit elements");
     // selector of a run with mask nibble n: the lower set bit takes the first value, the upper one the second, the
     // rest a zero byte (source byte 4).  ES == 1: four byte selectors; ES == 2: two words of two halfword selectors.
@@ -293,12 +303,12 @@ __global__ void __launch_bounds__(kThreads) sparse24_expand_simd_kernel(const vo
             }
         }
     }
-    if (__any_sync(0xFFFFFFFFu, bad) && (threadIdx.x & 31) == 0) atomicExch(irregular, 1);
+    if (__any_sync(0xFFFFFFFFu, bad) && (threadIdx.x & 31) == 0) atomicExch(irregular, irregular_value);
 }
 
 // the same for 32-bit elements: one thread per 8 elements
 template <int ES>
-__global__ void __launch_bounds__(kThreads) sparse24_expand_kernel(const void *values, const uint8_t *bitmask, int64_t units, void *out, int *irregular) {
+__global__ void __launch_bounds__(kThreads) sparse24_expand_kernel(const void *values, const uint8_t *bitmask, int64_t units, void *out, int *irregular, int irregular_value) {
     bool bad = false;
     for (int64_t u = (int64_t)blockIdx.x * kThreads + threadIdx.x; u < units; u += (int64_t)gridDim.x * kThreads) {
         const uint32_t m = bitmask[u];
@@ -332,7 +342,7 @@ __global__ void __launch_bounds__(kThreads) sparse24_expand_kernel(const void *v
             st_stream((char *)out + u * 32 + 16, make_uint4(b[4], b[5], b[6], b[7]));
         }
     }
-    if (__any_sync(0xFFFFFFFFu, bad) && (threadIdx.x & 31) == 0) atomicExch(irregular, 1);
+    if (__any_sync(0xFFFFFFFFu, bad) && (threadIdx.x & 31) == 0) atomicExch(irregular, irregular_value);
 }
 
 }  // namespace ctb
@@ -420,8 +430,8 @@ __global__ void __launch_bounds__(kThreads) bm_count_kernel(const void *x, const
 }
 
 // per-row counts straight from a bitmask (decompress)
-__global__ void __launch_bounds__(kThreads) bm_popcount_kernel(const uint8_t *bitmask, int64_t rows, int64_t cols, int64_t *row_counts, const int *gate) {
-    if (gate != nullptr && *gate == 0) return;  // the fast 2:4 expansion already produced the tensor
+__global__ void __launch_bounds__(kThreads) bm_popcount_kernel(const uint8_t *bitmask, int64_t rows, int64_t cols, int64_t *row_counts, Gate gate) {
+    if (gate.flag != nullptr && *gate.flag != gate.value) return;  // the fast 2:4 expansion already produced the tensor
     const int64_t upr = (cols + 7) / 8;
     const int tail = (int)(cols & 7);
     for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
@@ -437,8 +447,8 @@ __global__ void __launch_bounds__(kThreads) bm_popcount_kernel(const uint8_t *bi
 }
 
 // pass 2: in-place exclusive scan of the row counts (single block), total to *nnz
-__global__ void __launch_bounds__(1024) row_scan_kernel(int64_t *counts, int64_t rows, int64_t *nnz, const int *gate = nullptr) {
-    if (gate != nullptr && *gate == 0) return;
+__global__ void __launch_bounds__(1024) row_scan_kernel(int64_t *counts, int64_t rows, int64_t *nnz, Gate gate = Gate{nullptr, 0}) {
+    if (gate.flag != nullptr && *gate.flag != gate.value) return;
     __shared__ int64_t wsum[32];
     __shared__ int64_t carry_s;
     if (threadIdx.x == 0) carry_s = 0;
@@ -491,8 +501,8 @@ __global__ void __launch_bounds__(kThreads) bm_scatter_kernel(const void *x, con
 // 8 output elements per round and writes them with one vector store when the row layout allows.
 template <int ES, bool VEC>
 __global__ void __launch_bounds__(kThreads) bm_expand_kernel(const void *values, const uint8_t *bitmask, int es, int64_t rows, int64_t cols, const int64_t *row_offsets, void *out,
-                                                               const int *gate) {
-    if (gate != nullptr && *gate == 0) return;
+                                                               Gate gate) {
+    if (gate.flag != nullptr && *gate.flag != gate.value) return;
     const int64_t upr = (cols + 7) / 8;
     const int tail = (int)(cols & 7);
     for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
@@ -721,8 +731,8 @@ __global__ void __launch_bounds__(kThreads) bm_warp_count_kernel(const void *x, 
 
 // decompress, kernel 1: the same counts from the bitmask (a tile is 64 bitmask bytes)
 __global__ void __launch_bounds__(kThreads) bm_warp_popcount_kernel(const uint8_t *bitmask, int64_t units, unsigned long long *block_tot,
-                                                                    unsigned long long *warp_tot, const int *gate) {
-    if (gate != nullptr && *gate == 0) return;  // the fast 2:4 expansion already produced the tensor
+                                                                    unsigned long long *warp_tot, Gate gate) {
+    if (gate.flag != nullptr && *gate.flag != gate.value) return;  // the fast 2:4 expansion already produced the tensor
     int64_t first, last;
     warp_range((units + 63) / 64, first, last);
     const int lane = threadIdx.x & 31;
@@ -818,8 +828,8 @@ __global__ void __launch_bounds__(kThreads) bm_warp_scatter_kernel(const void *x
 // it in as whole 32-bit words, then every lane rebuilds its two units from the window
 template <int ES>
 __global__ void __launch_bounds__(kThreads) bm_warp_expand_kernel(const void *values, const uint8_t *bitmask, int64_t units, const unsigned long long *block_tot,
-                                                                  const unsigned long long *warp_tot, void *out, const int *gate) {
-    if (gate != nullptr && *gate == 0) return;
+                                                                  const unsigned long long *warp_tot, void *out, Gate gate) {
+    if (gate.flag != nullptr && *gate.flag != gate.value) return;
     __shared__ uint32_t stage_all[kWarps][StageWords<ES>::value];
     uint32_t *st = stage_all[threadIdx.x >> 5];
     int64_t first, last;
@@ -985,7 +995,7 @@ extern "C" int ctb_masked_compress(const void *x, const uint8_t *bytemask, int32
 }
 
 static int decompress_impl(const void *values, const uint8_t *bitmask, int32_t dtype, int64_t rows, int64_t cols, void *out, void *workspace,
-                           const int *gate, void *stream, bool tiles_ok = false) {
+                           Gate gate, void *stream, bool tiles_ok = false) {
     if (!bitmask || !out || !workspace) return fail(CTB_EINVAL_NULL, "null buffer");
     ElemInfo e;
     if (!elem_info(dtype, &e)) return fail(CTB_EINVAL_DTYPE, "unsupported dtype for bitmask decompression");
@@ -998,7 +1008,7 @@ static int decompress_impl(const void *values, const uint8_t *bitmask, int32_t d
         const int64_t units = rows * cols / 8;
         // both kernels must see the same grid: it defines the tile ranges.  As the gated fallback of the 2:4
         // expansion the launches almost always return at once: keep them small.
-        const int g1 = tile_grid(units, gate ? 1 : 8);
+        const int g1 = tile_grid(units, gate.flag ? 1 : 8);
         bm_warp_popcount_kernel<<<g1, kThreads, 0, st>>>(bitmask, units, block_tot, warp_tot, gate);
         int rc0 = after_launch("bm_warp_popcount_kernel");
         if (rc0) return rc0;
@@ -1024,7 +1034,7 @@ static int decompress_impl(const void *values, const uint8_t *bitmask, int32_t d
 
 extern "C" int ctb_bitmask_decompress(const void *values, const uint8_t *bitmask, int32_t dtype, int64_t rows, int64_t cols, void *out,
                                       void *workspace, void *stream) {
-    return decompress_impl(values, bitmask, dtype, rows, cols, out, workspace, nullptr, stream, true);
+    return decompress_impl(values, bitmask, dtype, rows, cols, out, workspace, Gate{nullptr, 0}, stream, true);
 }
 
 extern "C" int ctb_sparse24_decompress(const void *values, const uint8_t *bitmask, int32_t dtype, int64_t rows, int64_t cols, void *out,
@@ -1034,22 +1044,22 @@ extern "C" int ctb_sparse24_decompress(const void *values, const uint8_t *bitmas
     if (!elem_info(dtype, &e)) return fail(CTB_EINVAL_DTYPE, "unsupported dtype for bitmask decompression");
     if (rows <= 0 || cols <= 0) return rows < 0 || cols < 0 ? fail(CTB_EINVAL_SHAPE, "negative shape") : CTB_OK;
     if (cols % 8 != 0 || !aligned16(out) || (reinterpret_cast<uintptr_t>(values) & 15u))
-        return decompress_impl(values, bitmask, dtype, rows, cols, out, workspace, nullptr, stream);
+        return decompress_impl(values, bitmask, dtype, rows, cols, out, workspace, Gate{nullptr, 0}, stream);
     cudaStream_t st = as_stream(stream);
     int *flag = reinterpret_cast<int *>(static_cast<char *>(workspace) + flag_offset(rows));
-    cudaError_t ce = cudaMemsetAsync(flag, 0, sizeof(int), st);
-    if (ce != cudaSuccess) return fail(CTB_ECUDA, "cudaMemsetAsync: %s", cudaGetErrorString(ce));
+    static std::atomic<int> s_ticket{1};
+    const int ticket = s_ticket.fetch_add(1, std::memory_order_relaxed);  // see Gate: no clearing of the flag word
     const int64_t units = rows * cols / 8;
     const bool simd = e.esize != 4 && (reinterpret_cast<uintptr_t>(bitmask) & 1u) == 0;
-    if (simd && e.esize == 2) sparse24_expand_simd_kernel<2><<<grid_for((units + 1) / 2, kThreads, 8), kThreads, 0, st>>>(values, bitmask, units, out, flag);
-    else if (simd) sparse24_expand_simd_kernel<1><<<grid_for((units + 1) / 2, kThreads, 8), kThreads, 0, st>>>(values, bitmask, units, out, flag);
-    else if (e.esize == 2) sparse24_expand_kernel<2><<<grid_for(units, kThreads, 8), kThreads, 0, st>>>(values, bitmask, units, out, flag);
-    else if (e.esize == 1) sparse24_expand_kernel<1><<<grid_for(units, kThreads, 8), kThreads, 0, st>>>(values, bitmask, units, out, flag);
-    else sparse24_expand_kernel<4><<<grid_for(units, kThreads, 8), kThreads, 0, st>>>(values, bitmask, units, out, flag);
+    if (simd && e.esize == 2) sparse24_expand_simd_kernel<2><<<grid_for((units + 1) / 2, kThreads, 8), kThreads, 0, st>>>(values, bitmask, units, out, flag, ticket);
+    else if (simd) sparse24_expand_simd_kernel<1><<<grid_for((units + 1) / 2, kThreads, 8), kThreads, 0, st>>>(values, bitmask, units, out, flag, ticket);
+    else if (e.esize == 2) sparse24_expand_kernel<2><<<grid_for(units, kThreads, 8), kThreads, 0, st>>>(values, bitmask, units, out, flag, ticket);
+    else if (e.esize == 1) sparse24_expand_kernel<1><<<grid_for(units, kThreads, 8), kThreads, 0, st>>>(values, bitmask, units, out, flag, ticket);
+    else sparse24_expand_kernel<4><<<grid_for(units, kThreads, 8), kThreads, 0, st>>>(values, bitmask, units, out, flag, ticket);
     int rc = after_launch("sparse24_expand_kernel");
     if (rc) return rc;
     // generic path, gated on the flag: returns immediately unless the bitmask was not two-per-run
-    return decompress_impl(values, bitmask, dtype, rows, cols, out, workspace, flag, stream, true);
+    return decompress_impl(values, bitmask, dtype, rows, cols, out, workspace, Gate{flag, ticket}, stream, true);
 }
 
 // ------------------------------------------------------------------ decompress without caller scratch
@@ -1091,5 +1101,5 @@ extern "C" int ctb_bitmask_decompress_static(const void *values, const uint8_t *
     if (rc) return rc;
     // every row's slot is rewritten by the popcount pass before the scan reads it: nothing has to start at zero
     const bool fits = rows > 0 && cols > 0 && tile_bytes() <= kStaticMaxRows * 8;
-    return decompress_impl(values, bitmask, dtype, rows, cols, out, scratch, nullptr, stream, fits);
+    return decompress_impl(values, bitmask, dtype, rows, cols, out, scratch, Gate{nullptr, 0}, stream, fits);
 }
