@@ -110,6 +110,24 @@ __global__ void __launch_bounds__(kThreads) sparse24_mask_kernel(const void *x, 
     }
 }
 
+// get_24_bytemasks for 8- and 16-bit elements on SIMD lanes: 16 bytes in per thread, one 0/1 byte per element out
+template <int ES>
+__global__ void __launch_bounds__(kThreads) sparse24_mask_simd_kernel(const void *x, int64_t chunks, uint8_t *out) {
+    static_assert(ES == 1 || ES == 2, "SIMD lanes are 8 or 16 bits");
+    for (int64_t c = (int64_t)blockIdx.x * kThreads + threadIdx.x; c < chunks; c += (int64_t)gridDim.x * kThreads) {
+        const uint4 w = ld_stream((const char *)x + c * 16);
+        if constexpr (ES == 1) {
+            uint4 o;
+            sparse24_bytemask_u8x16(w.x, w.y, w.z, w.w, o.x, o.y, o.z, o.w);
+            st_stream(out + c * 16, o);
+        } else {
+            uint2 o;
+            sparse24_bytemask_u16x8(w.x, w.y, w.z, w.w, o.x, o.y);
+            st_stream8(out + c * 8, o);
+        }
+    }
+}
+
 // sparse24_bitmask_compress, cols % 8 == 0, 8- and 16-bit elements: one thread per 16 elements (two bitmask bytes,
 // eight kept values).  The keep rule runs on SIMD lanes of 32-bit words (ctb_sparse24_simd.cuh), about six integer
 // instructions per element, so the kernel stays bound by memory rather than by the selection logic.
@@ -896,9 +914,26 @@ extern "C" int ctb_sparse24_mask(const void *x, int32_t dtype, int64_t numel, ui
     if (!elem_info(dtype, &e)) return fail(CTB_EINVAL_DTYPE, "unsupported dtype for 2:4 masks");
     if (numel % 4 != 0) return fail(CTB_EINVAL_SHAPE, "Tensor size must be a multiple of 4 for TWO_FOUR sparsity");
     if (numel == 0) return CTB_OK;
-    int grid = grid_for(numel / 4, kThreads, 8);
-    if (e.is_int8) sparse24_mask_kernel<true><<<grid, kThreads, 0, as_stream(stream)>>>(x, e.esize, e.nz_mask, numel / 4, out);
-    else sparse24_mask_kernel<false><<<grid, kThreads, 0, as_stream(stream)>>>(x, e.esize, e.nz_mask, numel / 4, out);
+    cudaStream_t st = as_stream(stream);
+    int64_t done = 0;  // elements covered by the SIMD kernel; the scalar kernel takes what is left (less than one chunk)
+    if (e.esize != 4 && aligned16(x) && (reinterpret_cast<uintptr_t>(out) & 15u) == 0) {
+        const int per = 16 / e.esize;  // elements per 16-byte chunk
+        const int64_t chunks = numel / per;
+        if (chunks > 0) {
+            const int grid = grid_for(chunks, kThreads, 8);
+            if (e.esize == 1) sparse24_mask_simd_kernel<1><<<grid, kThreads, 0, st>>>(x, chunks, out);
+            else sparse24_mask_simd_kernel<2><<<grid, kThreads, 0, st>>>(x, chunks, out);
+            int rc = after_launch("sparse24_mask_simd_kernel");
+            if (rc) return rc;
+        }
+        done = chunks * per;
+    }
+    if (done == numel) return CTB_OK;
+    const void *xr = (const char *)x + done * e.esize;
+    const int64_t groups = (numel - done) / 4;
+    int grid = grid_for(groups, kThreads, 8);
+    if (e.is_int8) sparse24_mask_kernel<true><<<grid, kThreads, 0, st>>>(xr, e.esize, e.nz_mask, groups, out + done);
+    else sparse24_mask_kernel<false><<<grid, kThreads, 0, st>>>(xr, e.esize, e.nz_mask, groups, out + done);
     return after_launch("sparse24_mask_kernel");
 }
 

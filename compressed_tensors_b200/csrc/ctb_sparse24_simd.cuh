@@ -145,6 +145,14 @@ CTB_HD void sparse24_pack_u8x16(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t 
     mask16 = prmt(by, 0, 0x4420);
 }
 
+// get_24_bytemasks for the same sixteen elements: one 0/1 byte per element, run g in word g
+CTB_HD void sparse24_bytemask_u8x16(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3, uint32_t &o0, uint32_t &o1, uint32_t &o2, uint32_t &o3) {
+    uint32_t x0, x1, x2, x3;
+    transpose_u8x4(w0, w1, w2, w3, x0, x1, x2, x3);
+    const Keep4 k = keep24_u8x4(x0, x1, x2, x3);
+    transpose_u8x4(k.k0 & 0x01010101u, k.k1 & 0x01010101u, k.k2 & 0x01010101u, k.k3 & 0x01010101u, o0, o1, o2, o3);
+}
+
 // ---- two runs of 16-bit float elements (bf16 / fp16): keys are the 15 magnitude bits
 
 CTB_HD Keep4 keep24_u16x2(uint32_t x0, uint32_t x1, uint32_t x2, uint32_t x3) {
@@ -172,6 +180,16 @@ CTB_HD void sparse24_pack_u16x8(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t 
     val1 = prmt(lo, hi, 0x7632);  // lo_b hi_b
     const uint32_t nib = (k.k0 & 0x00010001u) | (k.k1 & 0x00020002u) | (k.k2 & 0x00040004u) | (k.k3 & 0x00080008u);
     mask8 = (nib | (nib >> 12)) & 0xFFu;
+}
+
+// get_24_bytemasks for the same eight elements: one 0/1 byte per element, run a in o0 and run b in o1
+CTB_HD void sparse24_bytemask_u16x8(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3, uint32_t &o0, uint32_t &o1) {
+    const uint32_t x0 = prmt(w0, w2, 0x5410), x1 = prmt(w0, w2, 0x7632);
+    const uint32_t x2 = prmt(w1, w3, 0x5410), x3 = prmt(w1, w3, 0x7632);
+    const Keep4 k = keep24_u16x2(x0, x1, x2, x3);
+    const uint32_t t0 = prmt(k.k0, k.k1, 0x6420), t1 = prmt(k.k2, k.k3, 0x6420);  // low bytes of both lanes of each mask
+    o0 = prmt(t0, t1, 0x6420) & 0x01010101u;
+    o1 = prmt(t0, t1, 0x7531) & 0x01010101u;
 }
 
 }  // namespace ctb

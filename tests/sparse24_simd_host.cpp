@@ -32,4 +32,24 @@ void simd24_pack_u16(const uint16_t *x, int64_t n8, uint16_t *values, uint8_t *m
         mask[i] = (uint8_t)m;
     }
 }
+
+// x: n16 * 16 int8-view elements -> mask: one 0/1 byte per element
+void simd24_bytemask_u8(const uint8_t *x, int64_t n16, uint8_t *mask) {
+    for (int64_t i = 0; i < n16; ++i) {
+        uint32_t w[4], o[4];
+        std::memcpy(w, x + 16 * i, 16);
+        ctb::sparse24_bytemask_u8x16(w[0], w[1], w[2], w[3], o[0], o[1], o[2], o[3]);
+        std::memcpy(mask + 16 * i, o, 16);
+    }
+}
+
+// x: n8 * 8 16-bit elements -> mask: one 0/1 byte per element
+void simd24_bytemask_u16(const uint16_t *x, int64_t n8, uint8_t *mask) {
+    for (int64_t i = 0; i < n8; ++i) {
+        uint32_t w[4], o[2];
+        std::memcpy(w, x + 8 * i, 16);
+        ctb::sparse24_bytemask_u16x8(w[0], w[1], w[2], w[3], o[0], o[1]);
+        std::memcpy(mask + 8 * i, o, 8);
+    }
+}
 }

@@ -230,6 +230,17 @@ def test_sparse24_codec_shapes_dtypes(ops, orc, dtype, shape):
     assert_bit_equal(ops.sparse24_decompress(dv, db, t.shape).cpu(), orc.bitmask_decompress(v, b, t.shape), "dense")
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32, torch.int8, torch.float8_e4m3fn])
+@pytest.mark.parametrize("shape", [(1, 4), (3, 4), (5, 12), (37, 24), (129, 1000), (700, 4096)])
+def test_sparse24_mask_shapes_dtypes(ops, orc, dtype, shape):
+    """get_24_bytemasks: sizes that are not a whole number of 16-byte chunks (scalar tail behind the SIMD kernel),
+    every element size, small integer magnitudes so that ties are the common case"""
+    g = torch.Generator().manual_seed(sum(shape) + 1)
+    t = torch.randint(-3, 4, shape, generator=g)
+    t = t.to(torch.int8) if dtype == torch.int8 else (t * 0.5).to(dtype)
+    assert_bit_equal(ops.sparse24_mask(t.cuda()).cpu(), orc.sparse24_mask(t), "keep mask")
+
+
 @pytest.mark.parametrize("shape", [(14336, 4096), (4096, 14336), (1024, 4096)])
 def test_full_size_round_trip_properties(ops, shape):
     """At the benchmark's tensor sizes: compress -> decompress -> compress is a fixed point (same words, same

@@ -41,6 +41,15 @@ def _check(simd, x):
     ov, ob = ref.sparse24_compress(x)
     assert torch.equal(b, ob)
     assert torch.equal(v.view(torch.uint8), ov.view(torch.uint8))
+    # the bytemask form of the same rule (get_24_bytemasks)
+    xc = x.contiguous()
+    bm = torch.empty(xc.shape, dtype=torch.uint8)
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    if xc.element_size() == 1:
+        simd.simd24_bytemask_u8(p(xc), ctypes.c_int64(xc.numel() // 16), p(bm))
+    else:
+        simd.simd24_bytemask_u16(p(xc), ctypes.c_int64(xc.numel() // 8), p(bm))
+    assert torch.equal(bm.bool(), ref.sparse24_mask(x))
 
 
 def _orderings(levels):
