@@ -153,6 +153,35 @@ __global__ void gparam_kernel(const void *mn_p, const void *mx_p, int M, float *
     out[0] = round_to_rt(M, __fdiv_rn(2688.0f, fmaxf(fabsf(mn), fabsf(mx))));
 }
 
+// quantization/utils/mxfp4_utils.py.  MODE 0: round_to_power_2 (bf16 bits in, bf16 bits out); MODE 1:
+// generate_mxfp4_scales (bf16 in, uint8 exponent out).  Both work on the bit pattern: add a quarter of the mantissa
+// range and keep sign + exponent (a sum past 16 bits wraps, as the reference's cast back to uint16 does); the
+// exponent byte is e + 125 for a positive normal power of two 2^e and 0 for everything whose log2 is not finite
+// (zero, negatives, inf), which is what the reference's float -> int32 conversion and clamp leave.
+template <int MODE>
+__global__ void __launch_bounds__(256) mxfp4_scale_kernel(const uint16_t *x, int64_t n, void *out) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const uint32_t p = ((uint32_t)x[i] + 32u) & 0xFF80u;
+        if constexpr (MODE == 0) {
+            ((uint16_t *)out)[i] = (uint16_t)p;
+        } else {
+            const int be = (int)((p >> 7) & 0xFFu);
+            int v = 0;
+            if ((p >> 15) == 0 && be != 0 && be != 0xFF) v = max(be - 2, 0);  // (be - 127) + 125
+            ((uint8_t *)out)[i] = (uint8_t)v;
+        }
+    }
+}
+
+// convert_mxfp4_exp_scale: 2 ** (scale - 127) in fp32 (2^-127 is an fp32 subnormal, exponent byte 255 overflows to
+// inf, which is also what shifting it into the exponent field gives), then the cast to the dense dtype
+__global__ void __launch_bounds__(256) mxfp4_convert_kernel(const uint8_t *scale, int64_t n, int odt, void *out) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const uint32_t b = scale[i];
+        store_f32(out, odt, i, __uint_as_float(b ? b << 23 : 0x00400000u));
+    }
+}
+
 static int flat_blocks() { return sm_count() * 4; }
 
 }  // namespace ctb
@@ -226,4 +255,29 @@ extern "C" int ctb_generate_gparam(const void *mn, const void *mx, int32_t dtype
     if (!is_float_dtype(dtype)) return fail(CTB_EINVAL_DTYPE, "min/max must be bf16, f16 or f32");
     gparam_kernel<<<1, 1, 0, as_stream(stream)>>>(mn, mx, dtype, out);
     return after_launch("gparam_kernel");
+}
+
+extern "C" int ctb_mxfp4_round_pow2(const void *x, int64_t n, void *out, void *stream) {
+    if (!x || !out) return fail(CTB_EINVAL_NULL, "null buffer");
+    if (n < 0) return fail(CTB_EINVAL_SHAPE, "negative size");
+    if (n == 0) return CTB_OK;
+    mxfp4_scale_kernel<0><<<grid_for(n, 256, 8), 256, 0, as_stream(stream)>>>((const uint16_t *)x, n, out);
+    return after_launch("mxfp4_scale_kernel");
+}
+
+extern "C" int ctb_mxfp4_generate_scales(const void *x, int64_t n, uint8_t *out, void *stream) {
+    if (!x || !out) return fail(CTB_EINVAL_NULL, "null buffer");
+    if (n < 0) return fail(CTB_EINVAL_SHAPE, "negative size");
+    if (n == 0) return CTB_OK;
+    mxfp4_scale_kernel<1><<<grid_for(n, 256, 8), 256, 0, as_stream(stream)>>>((const uint16_t *)x, n, out);
+    return after_launch("mxfp4_scale_kernel");
+}
+
+extern "C" int ctb_mxfp4_convert_scales(const uint8_t *scale, int64_t n, int32_t out_dtype, void *out, void *stream) {
+    if (!scale || !out) return fail(CTB_EINVAL_NULL, "null buffer");
+    if (!is_float_dtype(out_dtype)) return fail(CTB_EINVAL_DTYPE, "dense scales are bf16, f16 or f32");
+    if (n < 0) return fail(CTB_EINVAL_SHAPE, "negative size");
+    if (n == 0) return CTB_OK;
+    mxfp4_convert_kernel<<<grid_for(n, 256, 8), 256, 0, as_stream(stream)>>>(scale, n, out_dtype, out);
+    return after_launch("mxfp4_convert_kernel");
 }

@@ -600,6 +600,18 @@ __device__ __forceinline__ void stage_store(uint32_t *st, int o, uint32_t v) {
     else *reinterpret_cast<uint32_t *>(p) = v;
 }
 
+// The per-element placement, written as predicated instructions: `if (bit) { store; advance; }` in C++ becomes a
+// branch with its divergence bookkeeping per element, which is most of what these kernels would execute.
+// `saddr` is a shared-window byte address (32-bit shared state space) and advances by ES when the bit is set.
+template <int ES>
+__device__ __forceinline__ void stage_put_if(uint32_t &saddr, uint32_t v, uint32_t bit) {
+    if constexpr (ES == 1)
+        asm volatile("{ .reg .pred p; setp.ne.u32 p, %2, 0; @p st.shared.u8 [%0], %1; @p add.u32 %0, %0, 1; }" : "+r"(saddr) : "r"(v), "r"(bit) : "memory");
+    else if constexpr (ES == 2)
+        asm volatile("{ .reg .pred p; setp.ne.u32 p, %2, 0; @p st.shared.u16 [%0], %1; @p add.u32 %0, %0, 2; }" : "+r"(saddr) : "h"((unsigned short)v), "r"(bit) : "memory");
+    else
+        asm volatile("{ .reg .pred p; setp.ne.u32 p, %2, 0; @p st.shared.u32 [%0], %1; @p add.u32 %0, %0, 4; }" : "+r"(saddr) : "r"(v), "r"(bit) : "memory");
+}
 // tiles [first, last) of this warp when `ntiles` are dealt to all warps of the grid in contiguous ranges
 __device__ __forceinline__ void warp_range(int64_t ntiles, int64_t &first, int64_t &last) {
     const int64_t nw = (int64_t)gridDim.x * kWarps;
@@ -776,6 +788,7 @@ __global__ void __launch_bounds__(kThreads) bm_warp_scatter_kernel(const void *x
                                                                    int64_t *row_offsets, int64_t *nnz) {
     __shared__ uint32_t stage_all[kWarps][StageWords<ES>::value];
     uint32_t *st = stage_all[threadIdx.x >> 5];
+    const uint32_t st_addr = (uint32_t)__cvta_generic_to_shared(st);
     int64_t first, last;
     warp_range((units + 63) / 64, first, last);
     const int lane = threadIdx.x & 31;
@@ -809,13 +822,9 @@ __global__ void __launch_bounds__(kThreads) bm_warp_scatter_kernel(const void *x
         for (int h = 0; h < 2; ++h) {
             uint32_t b[8];
             unit_bits<ES>(raw[h], b);
-            int o = shift + excl[h] * ES;
+            uint32_t sa = st_addr + (uint32_t)(shift + excl[h] * ES);
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
-                if ((mask[h] >> j) & 1) {
-                    stage_store<ES>(st, o, b[j]);
-                    o += ES;
-                }
+            for (int j = 0; j < 8; ++j) stage_put_if<ES>(sa, b[j], mask[h] & (1u << j));
         }
         // rows that begin inside this tile (cols is a multiple of 8: at the first element of one of its 64 units)
         while (e_next < (tile + 1) * kWarpTile && r_next < rows) {  // uniform over the warp
@@ -845,13 +854,14 @@ __global__ void __launch_bounds__(kThreads) bm_warp_scatter_kernel(const void *x
 // decompress, kernel 2 (same grid as kernel 1): every tile's kept values are one contiguous run of `values`; bring
 // it in as whole 32-bit words, then every lane rebuilds its two units from the window
 template <int ES>
-__global__ void __launch_bounds__(kThreads) bm_warp_expand_kernel(const void *values, const uint8_t *bitmask, int64_t units, const unsigned long long *block_tot,
+__global__ void __launch_bounds__(kThreads, ES == 4 ? 4 : 8) bm_warp_expand_kernel(const void *values, const uint8_t *bitmask, int64_t units, const unsigned long long *block_tot,
                                                                   const unsigned long long *warp_tot, void *out, Gate gate) {
     if (gate.flag != nullptr && *gate.flag != gate.value) return;
     __shared__ uint32_t stage_all[kWarps][StageWords<ES>::value];
     uint32_t *st = stage_all[threadIdx.x >> 5];
+    const int64_t ntiles = (units + 63) / 64;
     int64_t first, last;
-    warp_range((units + 63) / 64, first, last);
+    warp_range(ntiles, first, last);
     const int lane = threadIdx.x & 31;
     uint32_t mask_n[2] = {0, 0};
     auto fetch = [&](int64_t t) {
@@ -870,10 +880,19 @@ __global__ void __launch_bounds__(kThreads) bm_warp_expand_kernel(const void *va
         warp_excl_scan2(__popc(mask[0]), __popc(mask[1]), excl[0], excl[1], total);
         const char *a = (const char *)values + src * ES;
         const int shift = (int)(reinterpret_cast<uintptr_t>(a) & 3u);
-        const int nwords = (shift + total * ES + 3) >> 2;  // whole words: the first and last may hold neighbours' bytes, never read
+        // Whole 32-bit words: the first may begin with the previous tile's bytes and the last may end with the next
+        // tile's, which are never used.  Only behind the very last tile is there no next tile: its ragged last word
+        // could run past the end of `values` and is fetched element by element.
+        const int nbytes = shift + total * ES;
+        const bool at_end = tile == ntiles - 1;
+        const int nwords = at_end ? nbytes >> 2 : (nbytes + 3) >> 2;
         const uint32_t *a0 = reinterpret_cast<const uint32_t *>(a - shift);
 #pragma unroll 4
         for (int w = lane; w < nwords; w += 32) st[pad_word(w)] = ld_stream4(a0 + w);
+        if (at_end && lane < 4) {
+            const int p = (nwords * 4 > shift ? nwords * 4 : shift) + lane * ES;
+            if (p < nbytes) stage_store<ES>(st, p, load_bits(values, ES, (int64_t)src + (p - shift) / ES));
+        }
         __syncwarp();
 #pragma unroll
         for (int h = 0; h < 2; ++h) {

@@ -11,6 +11,7 @@ from ._lib import CODE_DTYPE, CODE_FP4X2, CODE_PACK32, DT, QFLOAT, QINT, QDesc, 
 
 __all__ = [
     "quantize", "dequantize", "fake_quantize", "minmax", "calculate_qparams", "generate_gparam",
+    "mxfp4_round_pow2", "mxfp4_generate_scales", "mxfp4_convert_scales",
     "pack_int32", "unpack_int32", "pack_fp4", "unpack_fp4", "pack_bitmasks", "unpack_bitmasks",
     "sparse24_mask", "sparse24_compress", "sparse24_decompress", "bitmask_compress", "bitmask_decompress", "hadamard",
     "absmax_quantize", "rotate_quantize_int4_batch", "unpack_dequantize_int4_batch", "tensor_table", "QINT", "QFLOAT",
@@ -146,6 +147,39 @@ def generate_gparam(mn, mx):
     mn, mx = _c(mn.reshape(1)), _c(mx.reshape(1))
     out = torch.empty(1, dtype=torch.float32, device=mn.device)
     check(lib().ctb_generate_gparam(ptr(mn), ptr(mx), i32(DT[mn.dtype]), ptr(out), stream_of(mn)))
+    return out
+
+
+def mxfp4_round_pow2(x):
+    """quantization/utils/mxfp4_utils.py:43 round_to_power_2 (bf16 in, bf16 out)."""
+    require_cuda(x)
+    if x.dtype is not torch.bfloat16:
+        raise AssertionError("round_to_power_2 takes bfloat16")
+    x = _c(x)
+    out = torch.empty_like(x)
+    check(lib().ctb_mxfp4_round_pow2(ptr(x), i64(x.numel()), ptr(out), stream_of(x)))
+    return out
+
+
+def mxfp4_generate_scales(x):
+    """quantization/utils/mxfp4_utils.py:75 generate_mxfp4_scales (bf16 in, uint8 exponents out)."""
+    require_cuda(x)
+    if x.dtype is not torch.bfloat16:
+        raise AssertionError("generate_mxfp4_scales takes bfloat16")
+    x = _c(x)
+    out = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+    check(lib().ctb_mxfp4_generate_scales(ptr(x), i64(x.numel()), ptr(out), stream_of(x)))
+    return out
+
+
+def mxfp4_convert_scales(scale, dtype=torch.bfloat16):
+    """quantization/utils/mxfp4_utils.py:25 convert_mxfp4_exp_scale (uint8 exponents in, dense powers of two out)."""
+    require_cuda(scale)
+    if scale.dtype is not torch.uint8:
+        raise AssertionError("mxfp4 scales are uint8 exponents")
+    scale = _c(scale)
+    out = torch.empty(scale.shape, dtype=dtype, device=scale.device)
+    check(lib().ctb_mxfp4_convert_scales(ptr(scale), i64(scale.numel()), i32(DT[dtype]), ptr(out), stream_of(scale)))
     return out
 
 

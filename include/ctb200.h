@@ -134,6 +134,12 @@ int ctb_calculate_qparams(const void *min_vals, const void *max_vals, int32_t dt
 int ctb_generate_gparam(const void *min_val, const void *max_val, int32_t dtype, float *out,
                         void *stream);
 
+/* quantization/utils/mxfp4_utils.py:43-72 round_to_power_2 (bf16 in, bf16 out), :75-97 generate_mxfp4_scales
+ * (bf16 in, uint8 exponent out) and :25-40 convert_mxfp4_exp_scale (uint8 exponent in, bf16 / f16 / f32 out). */
+int ctb_mxfp4_round_pow2(const void *x_bf16, int64_t n, void *out_bf16, void *stream);
+int ctb_mxfp4_generate_scales(const void *x_bf16, int64_t n, uint8_t *out_exponent, void *stream);
+int ctb_mxfp4_convert_scales(const uint8_t *exponent, int64_t n, int32_t out_dtype, void *out, void *stream);
+
 /* ---- stand-alone packing ---------------------------------------------------------------
  * pack_quantized.py:186-246 pack_to_int32.  value is int8 [rows, cols] addressed with element
  * strides (row_stride, col_stride) so that packed_dim=0 is the same call on the transposed view;

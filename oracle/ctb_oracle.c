@@ -507,6 +507,43 @@ int orc_sparse24_gather(const void *x, int dt, const uint8_t *bytemask, int64_t 
 /* ----------------------------------------------------------------- Hadamard */
 
 /* transform/utils/hadamard.py:33-62 deterministic_hadamard_matrix (Sylvester): H[i][j] = (-1)^popcount(i&j) */
+/* ---- MXFP4 scale helpers (quantization/utils/mxfp4_utils.py) ------------------------------------ */
+
+/* mxfp4_utils.py:43-72 round_to_power_2: on the bf16 bit pattern, add a quarter of the mantissa range
+ * (1 << 5) and keep sign + exponent; sums that overflow 16 bits wrap (the cast back to uint16). */
+int orc_mxfp4_round_pow2(const uint16_t *x, int64_t n, uint16_t *out) {
+    for (int64_t i = 0; i < n; ++i) out[i] = (uint16_t)(((uint32_t)x[i] + 32u) & 0xFF80u);
+    return 0;
+}
+
+/* mxfp4_utils.py:75-97 generate_mxfp4_scales: 127 + floor(log2(p)) - 2 clamped to uint8, p the rounded power of
+ * two.  For p = 2^e that is e + 125.  log2 of zero, of a negative number and of inf gives -inf / NaN / inf, whose
+ * conversion to int32 is INT_MIN on the reference's hosts, so all of them clamp to 0. */
+int orc_mxfp4_generate_scales(const uint16_t *x, int64_t n, uint8_t *out) {
+    for (int64_t i = 0; i < n; ++i) {
+        const uint32_t p = ((uint32_t)x[i] + 32u) & 0xFF80u;
+        const int sign = (p >> 15) & 1, be = (p >> 7) & 0xFF;  /* the mantissa of p is zero */
+        int v = 0;
+        if (!sign && be != 0 && be != 0xFF) {
+            v = (be - 127) + 125;
+            if (v < 0) v = 0;
+            if (v > 255) v = 255;
+        }
+        out[i] = (uint8_t)v;
+    }
+    return 0;
+}
+
+/* mxfp4_utils.py:25-40 convert_mxfp4_exp_scale: 2.0 ** (scale - 127) in fp32 (2^-127 is an fp32 subnormal,
+ * 2^128 overflows to inf), then the cast to the dense dtype. */
+int orc_mxfp4_convert_scales(const uint8_t *scale, int64_t n, int odt, void *out) {
+    for (int64_t i = 0; i < n; ++i) {
+        const float v = scale[i] ? bits_f32((uint32_t)scale[i] << 23) : bits_f32(0x00400000u);
+        store_from_f32(out, odt, i, v);
+    }
+    return 0;
+}
+
 static inline double sylvester(int64_t i, int64_t j) { return (__builtin_popcountll(i & j) & 1) ? -1.0 : 1.0; }
 
 /* transform/factory/hadamard.py:104-121 HadamardTransform.forward with the offline precision float64

@@ -236,6 +236,27 @@ def sparse24_compress(x):
     return values, bitmask
 
 
+def mxfp4_round_pow2(x):
+    x = _c(x)
+    out = torch.empty_like(x)
+    lib().orc_mxfp4_round_pow2(_p(x), ctypes.c_int64(x.numel()), _p(out))
+    return out
+
+
+def mxfp4_generate_scales(x):
+    x = _c(x)
+    out = torch.empty(x.shape, dtype=torch.uint8)
+    lib().orc_mxfp4_generate_scales(_p(x), ctypes.c_int64(x.numel()), _p(out))
+    return out
+
+
+def mxfp4_convert_scales(scale, dtype=torch.bfloat16):
+    scale = _c(scale)
+    out = torch.empty(scale.shape, dtype=dtype)
+    lib().orc_mxfp4_convert_scales(_p(scale), ctypes.c_int64(scale.numel()), DT[dtype], _p(out))
+    return out
+
+
 def hadamard(x, n, signs=None, inverse=False, side=0):
     x = _c(x)
     rows, cols = x.shape

@@ -3,7 +3,7 @@
 Usage (only where the reference checkout is available; the fixtures are committed so the
 test-suite never needs it):
 
-    python tests/golden/make_golden.py /path/to/compressed-tensors
+    python tests/golden/make_golden.py /path/to/compressed-tensors [fixture-name]
 
 The reference is imported from ``<checkout>/src`` with a stub for its build-generated
 ``version`` module, in eager mode (``TORCHDYNAMO_DISABLE=1``).  Every fixture is a dict of
@@ -319,12 +319,33 @@ def gen_hadamard():
     torch.save(out, os.path.join(OUT, "hadamard.pt"))
 
 
+def gen_mxfp4():
+    """quantization/utils/mxfp4_utils.py on EVERY bf16 bit pattern and every uint8 exponent."""
+    from compressed_tensors.quantization.utils.mxfp4_utils import (
+        convert_mxfp4_exp_scale,
+        generate_mxfp4_scales,
+        round_to_power_2,
+    )
+
+    bits = torch.arange(65536, dtype=torch.int32).to(torch.uint16)
+    x = bits.view(torch.bfloat16)
+    exps = torch.arange(256, dtype=torch.int32).to(torch.uint8)
+    out = {
+        "all_bf16": {"round_pow2_bits": round_to_power_2(x).view(torch.uint16).to(torch.int32).to(torch.uint16),
+                     "scales": generate_mxfp4_scales(x)},
+        "all_exponents": {"bf16": convert_mxfp4_exp_scale(exps, torch.bfloat16),
+                          "f16": convert_mxfp4_exp_scale(exps, torch.float16),
+                          "f32": convert_mxfp4_exp_scale(exps, torch.float32)},
+    }
+    torch.save(out, os.path.join(OUT, "mxfp4.pt"))
+
+
 if __name__ == "__main__":
-    gen_int()
-    gen_fp8()
-    gen_nvfp4()
-    gen_sparse()
-    gen_hadamard()
+    only = sys.argv[2] if len(sys.argv) > 2 else None  # e.g. "mxfp4": regenerate one fixture
+    for name, fn in (("int_quant", gen_int), ("fp8_quant", gen_fp8), ("nvfp4", gen_nvfp4), ("sparse", gen_sparse),
+                     ("hadamard", gen_hadamard), ("mxfp4", gen_mxfp4)):
+        if only is None or only == name:
+            fn()
     for f in sorted(os.listdir(OUT)):
         if f.endswith(".pt"):
             print(f, os.path.getsize(os.path.join(OUT, f)))

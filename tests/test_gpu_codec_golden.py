@@ -222,3 +222,17 @@ def test_hadamard(golden, ops):
         # fp32 accumulation: rel-err <= 1e-3 against the float64 result (norm-wise)
         err = (fast.double().cpu() - d["out"].double()).norm() / d["out"].double().norm()
         assert err <= 1e-3, (name, float(err))
+
+
+def test_mxfp4_scale_helpers_every_input(golden, ops):
+    """mxfp4_utils.py on all 65536 bf16 bit patterns and all 256 exponent bytes, through the host mirror"""
+    from compressed_tensors_b200.quantization.utils import convert_mxfp4_exp_scale, generate_mxfp4_scales, round_to_power_2
+
+    d = golden("mxfp4")
+    x = torch.arange(65536, dtype=torch.int32).to(torch.uint16).view(torch.bfloat16).cuda()
+    assert torch.equal(round_to_power_2(x).view(torch.uint16).cpu(), d["all_bf16"]["round_pow2_bits"])
+    assert torch.equal(generate_mxfp4_scales(x).cpu(), d["all_bf16"]["scales"])
+    e = torch.arange(256, dtype=torch.int32).to(torch.uint8).cuda()
+    for key, dt in (("bf16", torch.bfloat16), ("f16", torch.float16), ("f32", torch.float32)):
+        assert_bit_equal(convert_mxfp4_exp_scale(e, dt).cpu(), d["all_exponents"][key], key)
+

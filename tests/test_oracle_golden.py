@@ -226,3 +226,15 @@ def test_hadamard(golden):
             assert_bit_equal(out, d["out"], name)
         else:
             torch.testing.assert_close(out, d["out"], rtol=1e-6, atol=1e-7, msg=name)
+
+
+def test_mxfp4_scale_helpers_every_input(golden):
+    """mxfp4_utils.py on all 65536 bf16 bit patterns and all 256 exponent bytes"""
+    d = golden("mxfp4")
+    x = torch.arange(65536, dtype=torch.int32).to(torch.uint16).view(torch.bfloat16)
+    assert torch.equal(orc.mxfp4_round_pow2(x).view(torch.uint16), d["all_bf16"]["round_pow2_bits"])
+    assert torch.equal(orc.mxfp4_generate_scales(x), d["all_bf16"]["scales"])
+    e = torch.arange(256, dtype=torch.int32).to(torch.uint8)
+    for key, dt in (("bf16", torch.bfloat16), ("f16", torch.float16), ("f32", torch.float32)):
+        assert_bit_equal(orc.mxfp4_convert_scales(e, dt), d["all_exponents"][key], key)
+
