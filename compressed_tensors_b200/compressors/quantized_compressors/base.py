@@ -62,9 +62,45 @@ class BaseQuantizationCompressor(BaseCompressor):
         return args.symmetric or packed
 
     def decompress(self, path_to_model_or_tensors, names_to_scheme: Dict[str, Any], device: str = "cpu"):
-        if not isinstance(path_to_model_or_tensors, dict):
-            raise NotImplementedError("reading safetensors from disk is outside this package; pass a state dict")
-        yield from self.decompress_from_state_dict(path_to_model_or_tensors, names_to_scheme)
+        """A state dict, a safetensors file or a checkpoint folder -> (module path, {name: tensor}) with the dense
+        `weight` added.  From disk (quantized_compressors/base.py:190-237 of the reference), each layer's packed
+        tensors are opened straight onto the GPU and unpacked + dequantized there; `device` is where the results
+        are left ("cpu" reproduces the reference's default, a CUDA device keeps them where they were computed)."""
+        if isinstance(path_to_model_or_tensors, dict):
+            yield from self.decompress_from_state_dict(path_to_model_or_tensors, names_to_scheme)
+        else:
+            yield from self._decompress_from_path(str(path_to_model_or_tensors), names_to_scheme, device)
+
+    def _decompress_from_path(self, path: str, names_to_scheme: Dict[str, Any], device: str):
+        from safetensors import safe_open
+
+        from ...utils.safetensors_load import get_nested_weight_mappings
+
+        gpu = torch.device(device) if torch.device(device).type == "cuda" else torch.device("cuda", torch.cuda.current_device())
+        handles: Dict[str, Any] = {}
+        try:
+            for module_path, locations in get_nested_weight_mappings(path, self.compression_param_names).items():
+                weight_data: Dict[str, Tensor] = {}
+                for param_name, file in locations.items():
+                    if file not in handles:
+                        handles[file] = safe_open(file, framework="pt", device=str(gpu))
+                    weight_data[param_name] = handles[file].get_tensor(module_path + "." + param_name if module_path else param_name)
+                if "weight_scale" in weight_data and module_path in names_to_scheme:
+                    weight_data["weight"] = self.decompress_weight(compressed_data=weight_data,
+                                                                   quantization_args=names_to_scheme[module_path].weights)
+                    yield module_path, {k: v.to(device) for k, v in weight_data.items()}
+        finally:
+            handles.clear()
+
+    def decompress_module(self, module: torch.nn.Module) -> Optional[Tensor]:
+        """Dense weight of one compressed leaf module (compressors/base.py:165-190 of the reference), or None when
+        the module carries no weight scheme."""
+        scheme = getattr(module, "quantization_scheme", None)
+        if scheme is None or getattr(scheme, "weights", None) is None:
+            return None
+        device = next(module.parameters()).device
+        data = {name: on_gpu(p.data) for name, p in module.named_parameters(recurse=False)}
+        return self.decompress_weight(compressed_data=data, quantization_args=scheme.weights).to(device)
 
     def decompress_from_state_dict(self, state_dict: Dict[str, Tensor], names_to_scheme: Dict[str, Any]
                                    ) -> Generator[Tuple[str, Dict[str, Tensor]], None, None]:

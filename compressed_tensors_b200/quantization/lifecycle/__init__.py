@@ -1,1 +1,2 @@
 from .forward import *  # noqa: F401,F403
+from .initialize import *  # noqa: F401,F403

@@ -153,3 +153,75 @@ def test_amax_exchange_two_ranks_gloo():
     assert all(p.exitcode == 0 for p in procs)
     assert (gmn, gmx) == (-2.0, 2.5) and dt == "torch.bfloat16"
     assert layers == [list(range(16)), list(range(16, 32))]
+
+
+def test_safetensors_weight_mappings(tmp_path):
+    """single file, folder with one file, sharded folder with an index: utils/safetensors_load.py:128-291"""
+    import json
+
+    from safetensors.torch import save_file
+
+    from compressed_tensors_b200.utils import (get_nested_mappings_from_state_dict, get_nested_weight_mappings,
+                                               get_safetensors_header, get_weight_mappings)
+
+    a = {"m.0.weight_packed": torch.zeros(2, 2, dtype=torch.int32), "m.0.weight_scale": torch.ones(2, 1), "m.0.bias": torch.zeros(2)}
+    b = {"m.1.weight_packed": torch.zeros(1, 2, dtype=torch.int32), "m.1.weight_shape": torch.tensor([1, 16])}
+    one = tmp_path / "one.safetensors"
+    save_file(a, str(one), metadata={"format": "pt"})
+    assert set(get_safetensors_header(str(one))) == set(a) | {"__metadata__"}
+    assert get_weight_mappings(str(one)) == {k: str(one) for k in a}
+    folder = tmp_path / "single"
+    folder.mkdir()
+    save_file(a, str(folder / "model.safetensors"))
+    assert get_weight_mappings(str(folder)) == {k: str(folder / "model.safetensors") for k in a}
+    shard = tmp_path / "sharded"
+    shard.mkdir()
+    save_file(a, str(shard / "model-00001-of-00002.safetensors"))
+    save_file(b, str(shard / "model-00002-of-00002.safetensors"))
+    index = {"weight_map": {**{k: "model-00001-of-00002.safetensors" for k in a}, **{k: "model-00002-of-00002.safetensors" for k in b}}}
+    (shard / "model.safetensors.index.json").write_text(json.dumps(index))
+    nested, rest = get_nested_weight_mappings(str(shard), ("weight_packed", "weight_scale", "weight_shape"), return_unmatched_params=True)
+    assert set(nested) == {"m.0", "m.1"} and set(nested["m.0"]) == {"weight_packed", "weight_scale"}
+    assert nested["m.1"]["weight_shape"].endswith("model-00002-of-00002.safetensors") and set(rest) == {"m.0.bias"}
+    assert set(get_nested_mappings_from_state_dict({**a, **b}, ("weight_packed",))) == {"m.0", "m.1"}
+    with pytest.raises(ValueError):
+        get_weight_mappings(str(tmp_path / "nothing-here"))
+
+
+def test_initialize_qparams_shapes_and_compressed_linear_parameters():
+    """lifecycle/initialize.py:153-277 shapes and dtypes; linear/compressed_linear.py:49-96 parameter set"""
+    import warnings
+
+    from compressed_tensors_b200.linear import CompressedLinear
+    from compressed_tensors_b200.quantization import (QuantizationArgs, QuantizationScheme, QuantizationStatus,
+                                                      initialize_module_for_quantization)
+
+    def params(args, **kw):
+        lin = torch.nn.Linear(256, 64, bias=False, dtype=torch.bfloat16)
+        initialize_module_for_quantization(lin, QuantizationScheme(targets=["Linear"], weights=args), **kw)
+        return {n: (tuple(p.shape), p.dtype) for n, p in lin.named_parameters() if n != "weight"}
+
+    assert params(QuantizationArgs(num_bits=8, strategy="tensor")) == {
+        "weight_scale": ((1,), torch.bfloat16), "weight_zero_point": ((1,), torch.int8)}
+    assert params(QuantizationArgs(num_bits=8, strategy="channel"), force_zero_point=False) == {"weight_scale": ((64, 1), torch.bfloat16)}
+    assert params(QuantizationArgs(num_bits=4, strategy="group", group_size=128, symmetric=False), force_zero_point=False) == {
+        "weight_scale": ((64, 2), torch.bfloat16), "weight_zero_point": ((64, 2), torch.int8)}
+    got = params(QuantizationArgs(num_bits=4, strategy="group", group_size=64, actorder="group"), force_zero_point=False)
+    assert got["weight_g_idx"] == ((256,), torch.int32) and got["weight_scale"] == ((64, 4), torch.bfloat16)
+    assert params(QuantizationArgs(num_bits=8, type="float", strategy="block", block_structure=[16, 64]), force_zero_point=False) == {
+        "weight_scale": ((4, 4), torch.bfloat16)}
+    got = params(QuantizationArgs(num_bits=4, type="float", strategy="tensor_group", group_size=16), force_zero_point=False)
+    assert got == {"weight_global_scale": ((1,), torch.float32), "weight_scale": ((64, 16), torch.float8_e4m3fn)}
+
+    lin = torch.nn.Linear(256, 64, bias=True, dtype=torch.bfloat16)
+    scheme = QuantizationScheme(targets=["Linear"], weights=QuantizationArgs(num_bits=4, strategy="group", group_size=128))
+    mod = CompressedLinear.from_linear(lin, scheme, "pack-quantized")
+    assert isinstance(mod, CompressedLinear) and mod.quantization_status == QuantizationStatus.COMPRESSED
+    assert {n: (tuple(p.shape), p.dtype) for n, p in mod.named_parameters()} == {
+        "bias": ((64,), torch.bfloat16), "weight_scale": ((64, 2), torch.bfloat16),
+        "weight_packed": ((64, 32), torch.int32), "weight_shape": ((2,), torch.int32)}
+    with warnings.catch_warnings(record=True) as w:
+        warnings.simplefilter("always")
+        CompressedLinear(8, 8)
+    assert any("from_linear" in str(x.message) for x in w)
+

@@ -248,3 +248,52 @@ def test_model_compressor_round_trip():
         assert got.dtype == want.dtype and torch.equal(got, want), name  # numeric equality, as the reference's reload test
     y = model(torch.randn(2, 256, dtype=torch.bfloat16, device="cuda"))
     assert y.shape == (2, 32)
+
+
+@pytest.mark.parametrize("fmt,group", [("pack-quantized", "W4A16"), ("nvfp4-pack-quantized", "NVFP4A16"), ("float-quantized", "FP8")])
+def test_disk_decompress_and_compressed_linear(tmp_path, fmt, group):
+    """checkpoint on disk -> packed tensors opened on the GPU -> unpack + dequantize (quantized base.py:190-237), and
+    CompressedLinear decompressing at its first forward (linear/compressed_linear.py:98-109): both give the bits of
+    the in-memory decompress"""
+    from safetensors.torch import save_file
+
+    from compressed_tensors_b200.compressors import BaseCompressor, ModelCompressor
+    from compressed_tensors_b200.linear import CompressedLinear
+    from compressed_tensors_b200.quantization import (QuantizationConfig, QuantizationStatus, apply_quantization_config,
+                                                      calibrate_weight_qparams)
+
+    torch.manual_seed(1)
+    model = torch.nn.Sequential(torch.nn.Linear(256, 128, bias=False), torch.nn.Linear(128, 64, bias=True)).to(torch.bfloat16).cuda()
+    cfg = QuantizationConfig(config_groups={group: ["Linear"]}, format=fmt)
+    apply_quantization_config(model, cfg)
+    schemes = {}
+    for name, m in model.named_modules():
+        if isinstance(m, torch.nn.Linear):
+            calibrate_weight_qparams(m)
+            schemes[name] = m.quantization_scheme
+    sd = ModelCompressor(quantization_config=cfg).compress(model)
+    comp = BaseCompressor.load_from_registry(fmt)
+    in_memory = {path: data["weight"] for path, data in comp.decompress(sd, names_to_scheme=schemes)}
+    assert set(in_memory) == {"0", "1"}
+
+    single = tmp_path / "model.safetensors"
+    save_file({k: v.contiguous() for k, v in sd.items()}, str(single))
+    for where in (str(single), str(tmp_path)):
+        for device in ("cpu", "cuda:0"):
+            from_disk = dict(comp.decompress(where, names_to_scheme=schemes, device=device))
+            assert set(from_disk) == {"0", "1"}
+            for path, data in from_disk.items():
+                assert data["weight"].device.type == device.split(":")[0]
+                assert_bit_equal(data["weight"].cpu(), in_memory[path].cpu(), f"{where} {path}")
+
+    lin = torch.nn.Linear(256, 128, bias=False, dtype=torch.bfloat16).cuda()
+    mod = CompressedLinear.from_linear(lin, schemes["0"], fmt)
+    missing, unexpected = mod.load_state_dict({k.removeprefix("0."): v for k, v in sd.items() if k.startswith("0.")}, strict=False)
+    assert not unexpected and not hasattr(mod, "weight")
+    x = torch.randn(4, 256, dtype=torch.bfloat16, device="cuda")
+    y = mod(x)
+    assert mod.quantization_status == QuantizationStatus.FROZEN
+    assert_bit_equal(mod.weight.data.cpu(), in_memory["0"].cpu(), "weight decompressed at the first forward")
+    assert_bit_equal(y.cpu(), torch.nn.functional.linear(x, in_memory["0"].cuda()).cpu(), "forward")
+    assert_bit_equal(mod(x).cpu(), y.cpu(), "second forward reuses the dense weight")
+
