@@ -1,5 +1,6 @@
 """TransformFactory / TransformBase (transform/factory/base.py of the reference): the fuse-into-weight
-locations.  Online (activation-side) locations are outside this package."""
+locations and the activation-side `input` / `output` hooks.  The attention locations (`q_attn`, `k_cache`) hook
+into a transformers model and are outside this package."""
 from abc import ABC, abstractmethod
 from typing import Optional
 
@@ -44,10 +45,20 @@ class TransformFactory(RegistryMixin, ABC):
             for _, module in match_named_modules(model, args.targets, args.ignore):
                 self._apply_to_module(module, args)
 
-    @torch.no_grad()
     def _apply_to_module(self, module: Module, args: TransformArgs) -> None:
-        """base.py:111-192, weight_input / weight_output: rotate the weight once and keep no submodule."""
-        if TransformLocation(args.location).is_online():
-            raise NotImplementedError("online (activation-side) transforms are outside this package")
+        """base.py:111-192.  weight_input / weight_output: rotate the weight once and keep no submodule.
+        input / output: keep the transform as a submodule and run it on the activations through a forward
+        (pre-)hook."""
+        location = TransformLocation(args.location)
         transform = self.create_transform(module, args)
-        module.weight.data = transform(module.weight.data)
+        if location in (TransformLocation.WEIGHT_INPUT, TransformLocation.WEIGHT_OUTPUT):
+            with torch.no_grad():
+                module.weight.data = transform(module.weight.data)
+            return
+        if location not in (TransformLocation.INPUT, TransformLocation.OUTPUT):
+            raise NotImplementedError(f"{location.value} transforms hook into a transformers attention module: outside this package")
+        module.add_module(f"{self.name}_{location.value}", transform)
+        if location == TransformLocation.INPUT:
+            module.register_forward_pre_hook(lambda _, inputs: transform(inputs[0]), prepend=True)
+        else:
+            module.register_forward_hook(lambda _, _inputs, output: transform(output))

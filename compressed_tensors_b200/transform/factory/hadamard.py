@@ -47,11 +47,21 @@ class HadamardTransform(TransformBase):
         self._scale = math.sqrt(weight.size(0))
 
     def forward(self, value: torch.Tensor) -> torch.Tensor:
-        """hadamard.py:104-121: (apply_transform_weight(W_h, value.to(W_h.dtype)) / sqrt(n)).to(value.dtype)."""
+        """hadamard.py:104-121: (apply_transform_weight(W_h, value.to(W_h.dtype)) / sqrt(n)).to(value.dtype).
+        Weights rotate along their input (side 0) or output (side 1) dimension; activations (`input` / `output`)
+        rotate along their last dimension, in blocks of the transform size."""
         if self.module_type != torch.nn.Linear:
             raise NotImplementedError(f"Applying transforms to {self.module_type} {self.args.location} is not supported")
         location = TransformLocation(self.args.location)
-        side = 0 if location == TransformLocation.WEIGHT_INPUT else 1
+        if location in (TransformLocation.Q_ATTN, TransformLocation.K_CACHE):
+            raise NotImplementedError(f"{location.value} transforms are outside this package")
         acc = torch.float64 if self.weight.dtype == torch.float64 else torch.float32
-        return ops.hadamard(value, self.weight.size(0), signs=self._signs.to(value.device), inverse=bool(self.args.inverse),
-                            side=side, precision=acc)
+        signs = self._signs.to(value.device)
+        if location == TransformLocation.WEIGHT_OUTPUT:
+            return ops.hadamard(value, self.weight.size(0), signs=signs, inverse=bool(self.args.inverse), side=1, precision=acc)
+        # matrix.py:113-119: activations are multiplied by the matrix itself (value @ M), a weight's input side by
+        # its transpose (value @ M.T), so the two differ in which of M / M.T the `inverse` flag selects
+        transposed = bool(self.args.inverse) != location.is_online()
+        flat = value.reshape(-1, value.shape[-1])
+        out = ops.hadamard(flat, self.weight.size(0), signs=signs, inverse=transposed, side=0, precision=acc)
+        return out.reshape(value.shape)

@@ -544,6 +544,91 @@ int orc_mxfp4_convert_scales(const uint8_t *scale, int64_t n, int odt, void *out
     return 0;
 }
 
+/* ---- Marlin-24 (compressors/sparse_quantized_compressors/marlin_24.py) --------------------------- */
+
+/* utils/semi_structured_conversions.py:79-209 sparse_semi_structured_from_dense_cutlass for a 16-bit dense
+ * dtype (int16 meta, four quadruples per meta element), on int8 codes standing for the fp16 tensor of the
+ * same integers: per run of four, two values are kept by the non-zero pattern (:160-176), their indices
+ * form a 4-bit code, four codes make a meta element, and the meta matrix is scattered into CUTLASS's
+ * reordered, column-interleaved layout (:43-73). */
+int orc_cutlass24_compress(const int8_t *dense, int64_t m, int64_t k, int8_t *sparse, int16_t *meta_reordered) {
+    if (m % 32 || k % 16) return 1;
+    const int64_t ncols = k / 16;
+    for (int64_t r = 0; r < m; ++r)
+        for (int64_t c = 0; c < ncols; ++c) {
+            uint32_t elem = 0;
+            for (int j = 0; j < 4; ++j) {
+                const int8_t *d = dense + r * k + (c * 4 + j) * 4;
+                const int m0 = d[0] != 0, m1 = d[1] != 0, m3 = d[3] != 0;
+                const int e0 = m0 && m1, e1 = !m0 && m1, e2 = !m0 && !m1;
+                const int i0 = e1 | (e2 << 1), i1 = (e0 | e2 | m3) | ((e1 | !m1) << 1);
+                sparse[r * (k / 2) + (c * 4 + j) * 2] = d[i0];
+                sparse[r * (k / 2) + (c * 4 + j) * 2 + 1] = d[i1];
+                elem |= (uint32_t)(i0 | (i1 << 2)) << (4 * j);
+            }
+            int64_t dr = r / 64 * 64 + (r % 2) * 2 + (r % 8) / 4 + ((r % 32) % 4) / 2 * 32 + ((r % 64) / 8) * 4, dc = c;
+            const int tr = (dr % 2 == 0) && (dc % 2 == 1), bl = (dr % 2 == 1) && (dc % 2 == 0);
+            dr += tr - bl;
+            dc -= tr - bl;
+            meta_reordered[(dc / 2) * m * 2 + dr * 2 + dc % 2] = (int16_t)elem;
+        }
+    return 0;
+}
+
+/* utils/permutations_24.py:32-65 */
+static void marlin24_perm(int bits, int *perm /* 1024 */) {
+    int list[1024], n = 0;
+    for (int i = 0; i < 32; ++i) {
+        int perm1[8], p = 0;
+        const int col = i / 4, col_o = col / 2;
+        for (int block = 0; block < 2; ++block) {
+            const int rows4[4] = {2 * (i % 4), 2 * (i % 4) + 1, 2 * (i % 4 + 4), 2 * (i % 4 + 4) + 1};
+            for (int t = 0; t < 4; ++t) perm1[p++] = 16 * rows4[t] + col_o * 256 + 8 * (col % 2) + 4 * block;
+        }
+        for (int j = 0; j < 4; ++j)
+            for (int t = 0; t < 8; ++t) list[n++] = perm1[t] + j;
+    }
+    static const int il4[8] = {0, 2, 4, 6, 1, 3, 5, 7}, il8[4] = {0, 2, 1, 3};
+    const int L = bits == 4 ? 8 : 4;
+    for (int b = 0; b < 1024 / L; ++b)
+        for (int t = 0; t < L; ++t) perm[b * L + t] = list[b * L + (bits == 4 ? il4[t] : il8[t])];
+}
+
+/* marlin_24.py:208-249 marlin_permute_weights + pack_weight_24 on the transposed, offset codes:
+ * sparse is [n, k2] (k2 = in_features / 2); out is [k2 / 16, n * 16 / (32 / bits)] int32. */
+int orc_marlin24_pack_weight(const int8_t *sparse, int64_t n, int64_t k2, int bits, int32_t *out) {
+    if ((bits != 4 && bits != 8) || k2 % 16 || n % 64) return 1;
+    int perm[1024];
+    marlin24_perm(bits, perm);
+    const int pf = 32 / bits, half = (1 << bits) / 2;
+    const int64_t row_elems = n * 16;
+    for (int64_t kt = 0; kt < k2 / 16; ++kt)
+        for (int64_t j = 0; j < row_elems / pf; ++j) {
+            uint32_t word = 0;
+            for (int i = 0; i < pf; ++i) {
+                const int64_t idx = j * pf + i, src = idx / 1024 * 1024 + perm[idx % 1024];
+                const int64_t nt = src / 256, ki = (src % 256) / 16, ni = src % 16;
+                const uint32_t v = (uint32_t)((int)sparse[(nt * 16 + ni) * k2 + kt * 16 + ki] + half);
+                word |= v << (bits * i);
+            }
+            out[kt * (row_elems / pf) + j] = (int32_t)word;
+        }
+    return 0;
+}
+
+/* marlin_24.py:252-273 pack_scales_24: scale is [n, g] (16-bit), out is [g, n]; `grouped` selects the
+ * group permutation (group size below in_features / 2), otherwise the per-channel one (the identity). */
+int orc_marlin24_pack_scales(const uint16_t *scale, int64_t n, int64_t g, int grouped, uint16_t *out) {
+    if (n % 64) return 1;
+    static const int inner[8] = {0, 4, 1, 5, 2, 6, 3, 7};
+    for (int64_t f = 0; f < g * n; ++f) {  /* flat index of the transposed [g, n] tensor */
+        const int64_t blk = f / 64, w = f % 64;
+        const int64_t src = blk * 64 + (grouped ? (w / 8) * 8 + inner[w % 8] : w);
+        out[f] = scale[(src % n) * g + src / n];
+    }
+    return 0;
+}
+
 static inline double sylvester(int64_t i, int64_t j) { return (__builtin_popcountll(i & j) & 1) ? -1.0 : 1.0; }
 
 /* transform/factory/hadamard.py:104-121 HadamardTransform.forward with the offline precision float64

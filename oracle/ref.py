@@ -236,6 +236,35 @@ def sparse24_compress(x):
     return values, bitmask
 
 
+def cutlass24_compress(q):
+    q = _c(q.to(torch.int8))
+    m, k = q.shape
+    sparse = torch.empty((m, k // 2), dtype=torch.int8)
+    meta = torch.empty((m, k // 16), dtype=torch.int16)
+    rc = lib().orc_cutlass24_compress(_p(q), ctypes.c_int64(m), ctypes.c_int64(k), _p(sparse), _p(meta))
+    if rc:
+        raise RuntimeError("rows must be divisible by 32 and columns by 16")
+    return sparse, meta
+
+
+def marlin24_pack_weight(sparse, bits):
+    sparse = _c(sparse.to(torch.int8))
+    n, k2 = sparse.shape
+    out = torch.empty((k2 // 16, n * 16 // (32 // bits)), dtype=torch.int32)
+    rc = lib().orc_marlin24_pack_weight(_p(sparse), ctypes.c_int64(n), ctypes.c_int64(k2), bits, _p(out))
+    assert rc == 0
+    return out
+
+
+def marlin24_pack_scales(scale, grouped):
+    scale = _c(scale.to(torch.float16))
+    n, g = scale.shape
+    out = torch.empty((g, n), dtype=torch.float16)
+    rc = lib().orc_marlin24_pack_scales(_p(scale), ctypes.c_int64(n), ctypes.c_int64(g), int(grouped), _p(out))
+    assert rc == 0
+    return out
+
+
 def mxfp4_round_pow2(x):
     x = _c(x)
     out = torch.empty_like(x)

@@ -319,6 +319,62 @@ def gen_hadamard():
     torch.save(out, os.path.join(OUT, "hadamard.pt"))
 
 
+def gen_hadamard_online():
+    """Activation-side (input / output) Hadamard transforms at the scheme's runtime precision (fp32)."""
+    out = {}
+    gen = torch.Generator().manual_seed(5)
+    for tag, fac_cls, seed in (("hadamard", HadamardFactory, None), ("random", RandomHadamardFactory, 7)):
+        for location in ("input", "output"):
+            for inverse in (False, True):
+                for dtype in (torch.bfloat16, torch.float32):
+                    i, o = (256, 16) if location == "input" else (16, 256)
+                    lin = torch.nn.Linear(i, o, bias=False, dtype=dtype)
+                    scheme = TransformScheme(type=tag if tag == "hadamard" else "random-hadamard", head_dim=128,
+                                             apply=[TransformArgs(targets=["Linear"], location=location, inverse=inverse)])
+                    fac = fac_cls("t", scheme, seed=seed)
+                    tr = fac.create_transform(lin, scheme.apply[0])
+                    x = torch.randn(2, 3, 256, generator=gen).to(dtype)
+                    with torch.no_grad():
+                        y = tr(x)
+                    name = f"{tag}_{location}_{'inv' if inverse else 'fwd'}_{str(dtype).split('.')[-1]}"
+                    out[name] = {"x": x, "out": y.detach(), "matrix": tr.weight.detach().to(torch.int8)}
+    torch.save(out, os.path.join(OUT, "hadamard_online.pt"))
+
+
+def gen_marlin24():
+    """Marlin24Compressor on 2:4-pruned weights: the quantized codes, the CUTLASS 2:4 compaction with its reordered
+    meta, and the final packed tensors, for group-128 and channel scales at 4 and 8 bits."""
+    from compressed_tensors.compressors.sparse_quantized_compressors.marlin_24 import Marlin24Compressor, compress_weight_24
+    from compressed_tensors.quantization import QuantizationScheme
+    from compressed_tensors.quantization.utils import calculate_qparams
+
+    out = {}
+    gen = torch.Generator().manual_seed(24)
+    for bits in (4, 8):
+        for strategy, rows, cols in (("group", 64, 256), ("channel", 128, 128), ("group", 64, 128), ("group", 64, 512)):
+            w = weights(gen, rows, cols, torch.float32, std=0.05)
+            w[:, 5] = 0.0  # incidental zeros: runs with three zeros
+            w[3, :] = 0.0  # and runs that are all zero
+            a = w.abs().reshape(-1, 4)
+            keep = torch.zeros_like(a, dtype=torch.bool).scatter_(1, a.topk(2, dim=1).indices, True)
+            w = (w.reshape(-1, 4) * keep).reshape(rows, cols)
+            args = QuantizationArgs(num_bits=bits, symmetric=True, strategy=strategy, group_size=128 if strategy == "group" else None)
+            if strategy == "group":
+                mn, mx = group_minmax(w, 128)
+            else:
+                mn, mx = w.amin(dim=1, keepdim=True), w.amax(dim=1, keepdim=True)
+            scale, zp = calculate_qparams(mn, mx, args)
+            q = quantize(x=w.to(torch.float16), scale=scale.to(torch.float16), zero_point=None, args=args)
+            sparse, meta = compress_weight_24(q)
+            scheme = QuantizationScheme(targets=["Linear"], weights=args)
+            packed = Marlin24Compressor().compress({"l.weight": w.clone(), "l.weight_scale": scale.clone()}, {"l": scheme})
+            out[f"w{bits}_{strategy}_{rows}x{cols}"] = {
+                "weight": w.to(torch.float16), "scale": scale, "bits": torch.tensor(bits), "group": torch.tensor(128 if strategy == "group" else 0),
+                "q": q.to(torch.int8), "sparse": sparse.to(torch.int8), "meta_reordered": meta,
+                "weight_packed": packed["l.weight_packed"], "scale_packed": packed["l.scale_packed"], "meta": packed["l.meta"]}
+    torch.save(out, os.path.join(OUT, "marlin24.pt"))
+
+
 def gen_mxfp4():
     """quantization/utils/mxfp4_utils.py on EVERY bf16 bit pattern and every uint8 exponent."""
     from compressed_tensors.quantization.utils.mxfp4_utils import (
@@ -343,7 +399,7 @@ def gen_mxfp4():
 if __name__ == "__main__":
     only = sys.argv[2] if len(sys.argv) > 2 else None  # e.g. "mxfp4": regenerate one fixture
     for name, fn in (("int_quant", gen_int), ("fp8_quant", gen_fp8), ("nvfp4", gen_nvfp4), ("sparse", gen_sparse),
-                     ("hadamard", gen_hadamard), ("mxfp4", gen_mxfp4)):
+                     ("hadamard", gen_hadamard), ("hadamard_online", gen_hadamard_online), ("mxfp4", gen_mxfp4), ("marlin24", gen_marlin24)):
         if only is None or only == name:
             fn()
     for f in sorted(os.listdir(OUT)):

@@ -299,3 +299,41 @@ def test_disk_decompress_and_compressed_linear(tmp_path, fmt, group):
     assert_bit_equal(y.cpu(), torch.nn.functional.linear(x, in_memory["0"].cuda()).cpu(), "forward")
     assert_bit_equal(mod(x).cpu(), y.cpu(), "second forward reuses the dense weight")
 
+
+def test_online_hadamard_hooks(golden):
+    """input / output transforms on activations (transform/factory/base.py:132-167): the reference computes them
+    as an fp32 matmul, the butterfly sums in another order, so the match is to one bf16 step / 1e-5 relative"""
+    from compressed_tensors_b200.transform import TransformArgs, TransformFactory, TransformScheme
+    from tests.helpers import bf16_ulp_distance
+
+    g = golden("hadamard_online")
+    for name, d in g.items():
+        tag, location, direction, dtype = name.split("_")
+        inverse = direction == "inv"
+        i, o = (256, 16) if location == "input" else (16, 256)
+        lin = torch.nn.Linear(i, o, bias=False, dtype=d["x"].dtype).cuda()
+        scheme = TransformScheme(type="hadamard" if tag == "hadamard" else "random-hadamard", head_dim=128,
+                                 apply=[TransformArgs(targets=["Linear"], location=location, inverse=inverse)])
+        fac = TransformFactory.from_scheme(scheme, name="t", seed=None if tag == "hadamard" else 7)
+        tr = fac.create_transform(lin, scheme.apply[0])
+        assert torch.equal(tr.weight.data.to(torch.int8).cpu(), d["matrix"]), name
+        y = tr(d["x"].cuda()).cpu()
+        assert y.dtype == d["out"].dtype and y.shape == d["out"].shape
+        if y.dtype == torch.bfloat16:
+            assert bf16_ulp_distance(y, d["out"]) <= 1, name
+        else:
+            torch.testing.assert_close(y, d["out"], rtol=1e-5, atol=1e-6)
+    # the hooks: a pre-hook rotates the input, a forward hook rotates the output
+    torch.manual_seed(3)
+    lin = torch.nn.Linear(256, 256, bias=False, dtype=torch.bfloat16).cuda()
+    plain = torch.nn.Linear(256, 256, bias=False, dtype=torch.bfloat16).cuda()
+    plain.weight.data.copy_(lin.weight.data)
+    scheme = TransformScheme(type="hadamard", head_dim=128, apply=[TransformArgs(targets=["Linear"], location="input"),
+                                                                   TransformArgs(targets=["Linear"], location="output", inverse=True)])
+    fac = TransformFactory.from_scheme(scheme, name="R")
+    fac.apply_to_model(torch.nn.Sequential(lin))
+    assert {n for n, _ in lin.named_children()} == {"R_input", "R_output"}
+    x = torch.randn(5, 256, dtype=torch.bfloat16, device="cuda")
+    tin, tout = lin.R_input, lin.R_output
+    assert_bit_equal(lin(x).cpu(), tout(plain(tin(x))).cpu(), "hooked forward")
+
