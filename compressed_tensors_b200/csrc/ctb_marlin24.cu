@@ -1,0 +1,153 @@
+// Marlin-24 packing (compressors/sparse_quantized_compressors/marlin_24.py): a quantized, 2:4-sparse weight
+// becomes (1) the CUTLASS 2:4 compaction with its reordered metadata
+// (utils/semi_structured_conversions.py:79-209), (2) the compacted codes transposed, shifted to unsigned,
+// shuffled into Marlin's 16 x 64 tensor-core tiles and packed 8 (4) to an int32 (marlin_24.py:208-249,
+// utils/permutations_24.py:32-65), (3) the scales transposed and permuted (marlin_24.py:252-273).
+//
+// Everything here is index arithmetic on small integers: one pass over the codes per step, every output element
+// computed from its own index (gather), no scratch, no atomics.
+#include "ctb_common.cuh"
+
+namespace ctb {
+
+constexpr int kMThreads = 256;
+
+// ---- step 1: one thread per metadata element = 16 consecutive elements of a row = 4 runs of four
+//
+// A run keeps two values chosen by its non-zero pattern (semi_structured_conversions.py:160-176): with m_i the
+// non-zero flags, index0 = (~m0 & m1) | ((~m0 & ~m1) << 1) and index1 = ((m0 & m1) | (~m0 & ~m1) | m3) |
+// (((~m0 & m1) | ~m1) << 1); the run's 4-bit code is index0 | index1 << 2.  Four codes make an int16 metadata
+// element, which is stored at its place in CUTLASS's reordered, column-interleaved layout (:43-73).
+// ES = 1: int8 codes (standing for the 16-bit tensor holding the same integers), ES = 2: fp16 / bf16 values.
+template <int ES>
+__global__ void __launch_bounds__(kMThreads) cutlass24_compress_kernel(const void *dense, int64_t m, int64_t k, void *sparse, int16_t *meta_reordered) {
+    const int64_t ncols = k / 16, total = m * ncols;
+    for (int64_t t = (int64_t)blockIdx.x * kMThreads + threadIdx.x; t < total; t += (int64_t)gridDim.x * kMThreads) {
+        const int64_t r = t / ncols, c = t - r * ncols;
+        uint32_t v[16];  // raw bits of the 16 elements
+        if constexpr (ES == 1) {
+            const uint4 w = *reinterpret_cast<const uint4 *>((const char *)dense + (r * k + c * 16));
+            const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = (ww[i >> 2] >> (8 * (i & 3))) & 0xFFu;
+        } else {
+            const uint4 *p = reinterpret_cast<const uint4 *>((const char *)dense + (r * k + c * 16) * 2);
+            const uint4 a = p[0], b = p[1];
+            const uint32_t ww[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = (ww[i >> 1] >> (16 * (i & 1))) & 0xFFFFu;
+        }
+        const uint32_t nz = ES == 1 ? 0xFFu : 0x7FFFu;  // -0.0 is zero for the float types (`dense != 0`)
+        uint32_t elem = 0, kept[8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const bool m0 = (v[4 * j] & nz) != 0, m1 = (v[4 * j + 1] & nz) != 0, m3 = (v[4 * j + 3] & nz) != 0;
+            const bool e0 = m0 && m1, e1 = !m0 && m1, e2 = !m0 && !m1;
+            const int i0 = (int)e1 | ((int)e2 << 1), i1 = (int)(e0 || e2 || m3) | ((int)(e1 || !m1) << 1);
+            // register arrays cannot be indexed dynamically: select
+            kept[2 * j] = i0 == 0 ? v[4 * j] : i0 == 1 ? v[4 * j + 1] : v[4 * j + 2];  // index0 is never 3
+            kept[2 * j + 1] = i1 == 1 ? v[4 * j + 1] : i1 == 2 ? v[4 * j + 2] : v[4 * j + 3];  // index1 is never 0
+            elem |= (uint32_t)(i0 | (i1 << 2)) << (4 * j);
+        }
+        if constexpr (ES == 1) {
+            uint2 o;
+            o.x = kept[0] | (kept[1] << 8) | (kept[2] << 16) | (kept[3] << 24);
+            o.y = kept[4] | (kept[5] << 8) | (kept[6] << 16) | (kept[7] << 24);
+            *reinterpret_cast<uint2 *>((char *)sparse + (r * (k / 2) + c * 8)) = o;
+        } else {
+            uint4 o;
+            o.x = kept[0] | (kept[1] << 16);
+            o.y = kept[2] | (kept[3] << 16);
+            o.z = kept[4] | (kept[5] << 16);
+            o.w = kept[6] | (kept[7] << 16);
+            *reinterpret_cast<uint4 *>((char *)sparse + (r * (k / 2) + c * 8) * 2) = o;
+        }
+        int64_t dr = r / 64 * 64 + (r % 2) * 2 + (r % 8) / 4 + ((r % 32) % 4) / 2 * 32 + ((r % 64) / 8) * 4, dc = c;
+        const int swap = ((dr % 2 == 0) && (dc % 2 == 1)) - ((dr % 2 == 1) && (dc % 2 == 0));
+        dr += swap;
+        dc -= swap;
+        meta_reordered[(dc / 2) * m * 2 + dr * 2 + dc % 2] = (int16_t)elem;
+    }
+}
+
+// utils/permutations_24.py:32-65: source position inside a 1024-element chunk for destination position d
+__device__ __forceinline__ int marlin24_perm(int d, int bits) {
+    const int L = bits == 4 ? 8 : 4;
+    const int t = d % L, b = d / L;
+    const int il = bits == 4 ? ((t & 3) * 2 + (t >> 2)) : (t == 1 ? 2 : t == 2 ? 1 : t);  // {0,2,4,6,1,3,5,7} / {0,2,1,3}
+    const int e = b * L + il;  // index into the un-interleaved list: 32 blocks of 4 x 8
+    const int i = e / 32, j = (e % 32) / 8, q = e % 8;
+    const int col = i / 4, col_o = col / 2, block = q / 4, rr = q % 4;
+    const int row = rr == 0 ? 2 * (i % 4) : rr == 1 ? 2 * (i % 4) + 1 : rr == 2 ? 2 * (i % 4 + 4) : 2 * (i % 4 + 4) + 1;
+    return 16 * row + col_o * 256 + 8 * (col % 2) + 4 * block + j;
+}
+
+// ---- step 2: one thread per packed word.  sparse is [n, k2] int8 codes; out is [k2 / 16, n * 16 / pf] int32.
+__global__ void __launch_bounds__(kMThreads) marlin24_pack_weight_kernel(const int8_t *sparse, int64_t n, int64_t k2, int bits, int32_t *out) {
+    __shared__ uint16_t perm[1024];
+    for (int d = threadIdx.x; d < 1024; d += kMThreads) perm[d] = (uint16_t)marlin24_perm(d, bits);
+    __syncthreads();
+    const int pf = 32 / bits, half = (1 << bits) / 2;
+    const int64_t words_per_row = n * 16 / pf, total = (k2 / 16) * words_per_row;
+    for (int64_t t = (int64_t)blockIdx.x * kMThreads + threadIdx.x; t < total; t += (int64_t)gridDim.x * kMThreads) {
+        const int64_t kt = t / words_per_row, j = t - kt * words_per_row;
+        uint32_t word = 0;
+        for (int i = 0; i < pf; ++i) {
+            const int64_t idx = j * pf + i, src = (idx & ~(int64_t)1023) + perm[idx & 1023];
+            const int64_t nt = src >> 8, ki = (src & 255) >> 4, ni = src & 15;
+            const uint32_t v = (uint32_t)((int)sparse[(nt * 16 + ni) * k2 + kt * 16 + ki] + half);
+            word |= v << (bits * i);
+        }
+        out[t] = (int32_t)word;
+    }
+}
+
+// ---- step 3: scale is [n, g] (16-bit elements), out is [g, n]
+__global__ void __launch_bounds__(kMThreads) marlin24_pack_scales_kernel(const uint16_t *scale, int64_t n, int64_t g, int grouped, uint16_t *out) {
+    const int64_t total = n * g;
+    for (int64_t f = (int64_t)blockIdx.x * kMThreads + threadIdx.x; f < total; f += (int64_t)gridDim.x * kMThreads) {
+        const int64_t blk = f >> 6;
+        const int w = (int)(f & 63), q = w & 7;
+        const int inner = (q & 1) * 4 + (q >> 1);  // {0,4,1,5,2,6,3,7}
+        const int64_t src = blk * 64 + (grouped ? (w & ~7) + inner : w);
+        out[f] = scale[(src % n) * g + src / n];
+    }
+}
+
+}  // namespace ctb
+
+using namespace ctb;
+
+extern "C" int ctb_cutlass24_compress(const void *dense, int32_t dtype, int64_t rows, int64_t cols, void *out_sparse, int16_t *out_meta,
+                                      void *stream) {
+    if (!dense || !out_sparse || !out_meta) return fail(CTB_EINVAL_NULL, "null buffer");
+    if (dtype != CTB_I8 && dtype != CTB_F16 && dtype != CTB_BF16) return fail(CTB_EINVAL_DTYPE, "dense must be int8 codes, f16 or bf16");
+    if (rows < 0 || cols < 0) return fail(CTB_EINVAL_SHAPE, "negative shape");
+    if (rows % 64 != 0) return fail(CTB_EINVAL_SHAPE, "Number of rows of dense matrix %lld must be divisible by 64", (long long)rows);
+    if (cols % 16 != 0) return fail(CTB_EINVAL_SHAPE, "Number of columns of dense matrix %lld must be divisible by 16", (long long)cols);
+    if (!aligned16(dense) || !aligned16(out_sparse)) return fail(CTB_EINVAL_ALIGN, "buffers must be 16-byte aligned");
+    if (rows == 0 || cols == 0) return CTB_OK;
+    const int grid = grid_for(rows * (cols / 16), kMThreads, 8);
+    if (dtype == CTB_I8) cutlass24_compress_kernel<1><<<grid, kMThreads, 0, as_stream(stream)>>>(dense, rows, cols, out_sparse, out_meta);
+    else cutlass24_compress_kernel<2><<<grid, kMThreads, 0, as_stream(stream)>>>(dense, rows, cols, out_sparse, out_meta);
+    return after_launch("cutlass24_compress_kernel");
+}
+
+extern "C" int ctb_marlin24_pack_weight(const int8_t *sparse, int64_t n, int64_t k2, int32_t num_bits, int32_t *out, void *stream) {
+    if (!sparse || !out) return fail(CTB_EINVAL_NULL, "null buffer");
+    if (num_bits != 4 && num_bits != 8) return fail(CTB_EINVAL_SHAPE, "num_bits must be 4 or 8, got %d", num_bits);
+    if (n < 0 || k2 < 0 || k2 % 16 != 0 || n % 64 != 0) return fail(CTB_EINVAL_SHAPE, "size_k must be a multiple of 16 and size_n of 64");
+    if (n == 0 || k2 == 0) return CTB_OK;
+    const int64_t words = (k2 / 16) * (n * 16 / (32 / num_bits));
+    marlin24_pack_weight_kernel<<<grid_for(words, kMThreads, 8), kMThreads, 0, as_stream(stream)>>>(sparse, n, k2, num_bits, out);
+    return after_launch("marlin24_pack_weight_kernel");
+}
+
+extern "C" int ctb_marlin24_pack_scales(const void *scale, int64_t n, int64_t groups, int32_t grouped, void *out, void *stream) {
+    if (!scale || !out) return fail(CTB_EINVAL_NULL, "null buffer");
+    if (n < 0 || groups < 0 || n % 64 != 0) return fail(CTB_EINVAL_SHAPE, "size_n must be a multiple of 64");
+    if (n == 0 || groups == 0) return CTB_OK;
+    marlin24_pack_scales_kernel<<<grid_for(n * groups, kMThreads, 8), kMThreads, 0, as_stream(stream)>>>((const uint16_t *)scale, n, groups,
+                                                                                                          grouped, (uint16_t *)out);
+    return after_launch("marlin24_pack_scales_kernel");
+}

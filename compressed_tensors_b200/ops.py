@@ -12,6 +12,7 @@ from ._lib import CODE_DTYPE, CODE_FP4X2, CODE_PACK32, DT, QFLOAT, QINT, QDesc, 
 __all__ = [
     "quantize", "dequantize", "fake_quantize", "minmax", "calculate_qparams", "generate_gparam",
     "mxfp4_round_pow2", "mxfp4_generate_scales", "mxfp4_convert_scales",
+    "cutlass24_compress", "marlin24_pack_weight", "marlin24_pack_scales",
     "pack_int32", "unpack_int32", "pack_fp4", "unpack_fp4", "pack_bitmasks", "unpack_bitmasks",
     "sparse24_mask", "sparse24_compress", "sparse24_decompress", "bitmask_compress", "bitmask_decompress", "hadamard",
     "absmax_quantize", "rotate_quantize_int4_batch", "unpack_dequantize_int4_batch", "tensor_table", "QINT", "QFLOAT",
@@ -344,6 +345,43 @@ def sparse24_decompress(values, bitmask, shape):
     ws = _bitmask_workspace(rows, cols, bitmask.device)
     check(lib().ctb_sparse24_decompress(ptr(values), ptr(bitmask), i32(DT[values.dtype]), i64(rows), i64(cols), ptr(out), ptr(ws),
                                         stream_of(bitmask)))
+    return out
+
+
+def cutlass24_compress(dense):
+    """utils/semi_structured_conversions.py:79 sparse_semi_structured_from_dense_cutlass for f16 / bf16 values or
+    int8 codes -> (sparse [rows, cols/2], meta int16 [rows, cols/16] in CUTLASS's reordered layout)."""
+    require_cuda(dense)
+    if dense.dim() != 2:
+        raise RuntimeError(f"Expected 2-dimensional dense tensor, got {dense.dim()}-dimensional tensor")
+    dense = _c(dense)
+    rows, cols = dense.shape
+    sparse = torch.empty((rows, cols // 2), dtype=dense.dtype, device=dense.device)
+    meta = torch.empty((rows, cols // 16), dtype=torch.int16, device=dense.device)
+    check(lib().ctb_cutlass24_compress(ptr(dense), i32(DT[dense.dtype]), i64(rows), i64(cols), ptr(sparse), ptr(meta), stream_of(dense)))
+    return sparse, meta
+
+
+def marlin24_pack_weight(sparse, num_bits):
+    """marlin_24.py:186-249: int8 codes [size_n, size_k] of the 2:4-compacted weight -> Marlin-24 packed int32
+    [size_k/16, size_n*16/(32/num_bits)] (transpose, shift to unsigned, tile permutation, packing)."""
+    require_cuda(sparse)
+    sparse = _c(sparse.to(torch.int8))
+    n, k2 = sparse.shape
+    out = torch.empty((k2 // 16, n * 16 // (32 // num_bits)), dtype=torch.int32, device=sparse.device)
+    check(lib().ctb_marlin24_pack_weight(ptr(sparse), i64(n), i64(k2), i32(num_bits), ptr(out), stream_of(sparse)))
+    return out
+
+
+def marlin24_pack_scales(scale, grouped):
+    """marlin_24.py:252-273 (with the transpose of :188): fp16 scales [size_n, groups] -> [groups, size_n]."""
+    require_cuda(scale)
+    scale = _c(scale)
+    if scale.element_size() != 2:
+        raise ValueError("Marlin-24 scales are float16")
+    n, g = scale.shape
+    out = torch.empty((g, n), dtype=scale.dtype, device=scale.device)
+    check(lib().ctb_marlin24_pack_scales(ptr(scale), i64(n), i64(g), i32(1 if grouped else 0), ptr(out), stream_of(scale)))
     return out
 
 

@@ -229,6 +229,21 @@ int ctb_hadamard(const void *x, int32_t dtype, int64_t rows, int64_t cols, int32
                  const int8_t *signs, int32_t inverse, int32_t side, int32_t precision,
                  int32_t normalize, void *out, void *stream);
 
+/* ---- Marlin-24 packing (compressors/sparse_quantized_compressors/marlin_24.py:124-273) --------------------
+ * utils/semi_structured_conversions.py:79-209 sparse_semi_structured_from_dense_cutlass for a 16-bit dense dtype:
+ * dense [rows, cols] (f16 / bf16 values, or int8 codes standing for the 16-bit tensor of the same integers) ->
+ * out_sparse [rows, cols/2] (same element type) and out_meta int16 [rows, cols/16] in CUTLASS's reordered layout. */
+int ctb_cutlass24_compress(const void *dense, int32_t dtype, int64_t rows, int64_t cols, void *out_sparse,
+                           int16_t *out_meta, void *stream);
+/* marlin_24.py:208-249 marlin_permute_weights + pack_weight_24 (including the transpose and the shift to unsigned
+ * of :186-193): sparse int8 codes [size_n, size_k] -> int32 [size_k/16, size_n*16/(32/num_bits)]. */
+int ctb_marlin24_pack_weight(const int8_t *sparse, int64_t size_n, int64_t size_k, int32_t num_bits, int32_t *out,
+                             void *stream);
+/* marlin_24.py:252-273 pack_scales_24 (including the transpose of :188): 16-bit scales [size_n, groups] ->
+ * [groups, size_n]; `grouped` != 0 selects the group permutation (group size below size_k). */
+int ctb_marlin24_pack_scales(const void *scale, int64_t size_n, int64_t groups, int32_t grouped, void *out,
+                             void *stream);
+
 /* ---- fused calibrate + quantize + pack (single pass over the dense tensor) -------------------
  * Symmetric min-max calibration (helpers.py:67-146 with the group's own amin/amax) followed by
  * ctb_quantize with the scales it produced.  out_scale is written in desc->scale_dtype, which

@@ -337,3 +337,39 @@ def test_online_hadamard_hooks(golden):
     tin, tout = lin.R_input, lin.R_output
     assert_bit_equal(lin(x).cpu(), tout(plain(tin(x))).cpu(), "hooked forward")
 
+
+def test_marlin24_compressor(golden):
+    """Marlin24Compressor.compress and its steps against the reference's tensors (marlin_24.py:124-273)"""
+    from compressed_tensors_b200 import ops
+    from compressed_tensors_b200.compressors import BaseCompressor, Marlin24Compressor, compress_weight_24, pack_scales_24, pack_weight_24
+    from compressed_tensors_b200.quantization import QuantizationArgs, QuantizationScheme
+
+    comp = BaseCompressor.load_from_registry("marlin-24")
+    assert isinstance(comp, Marlin24Compressor) and comp.compression_param_names == ("weight_packed", "scale_packed", "meta")
+    for name, d in golden("marlin24").items():
+        bits, group = int(d["bits"]), int(d["group"])
+        args = QuantizationArgs(num_bits=bits, symmetric=True, strategy="group" if group else "channel", group_size=group or None)
+        # the steps on the reference's intermediate tensors
+        sparse, meta = ops.cutlass24_compress(d["q"].cuda())
+        assert_bit_equal(sparse.cpu(), d["sparse"], name), assert_bit_equal(meta.cpu(), d["meta_reordered"], name)
+        s16, m16 = compress_weight_24(d["q"].to(torch.float16))  # the 16-bit element path takes the same decisions
+        assert_bit_equal(s16.cpu(), d["sparse"].to(torch.float16), name), assert_bit_equal(m16.cpu(), d["meta_reordered"], name)
+        unsigned = (d["sparse"].t().to(torch.int32) + (1 << bits) // 2).contiguous()
+        assert_bit_equal(pack_weight_24(unsigned, args).cpu(), d["weight_packed"], name)
+        scale_t = d["scale"].to(torch.float16).t().contiguous()
+        assert_bit_equal(pack_scales_24(scale_t, args, unsigned.shape).cpu(), d["scale_packed"], name)
+        # the whole compressor
+        out = comp.compress({"l.weight": d["weight"].cuda(), "l.weight_scale": d["scale"].cuda(), "l.bias": torch.zeros(3)},
+                            {"l": QuantizationScheme(targets=["Linear"], weights=args)})
+        assert set(out) == {"l.weight_packed", "l.scale_packed", "l.meta", "l.bias"} and all(not v.is_cuda for v in out.values())
+        for key in ("weight_packed", "scale_packed", "meta"):
+            assert_bit_equal(out[f"l.{key}"], d[key], f"{name} {key}")
+    dense = torch.ones(64, 64, dtype=torch.float16, device="cuda")
+    with pytest.raises(ValueError, match="2:4 sparsity structure"):
+        comp.compress({"l.weight": dense, "l.weight_scale": torch.ones(64, 1, device="cuda")},
+                      {"l": QuantizationScheme(targets=["Linear"], weights=QuantizationArgs(num_bits=4, strategy="channel"))})
+    with pytest.raises(ValueError, match="group size 128"):
+        comp.validate_quant_compatability({"l": QuantizationScheme(targets=["Linear"], weights=QuantizationArgs(num_bits=4, strategy="group", group_size=64))})
+    with pytest.raises(NotImplementedError):
+        comp.decompress("x")
+

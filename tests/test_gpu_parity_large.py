@@ -241,6 +241,23 @@ def test_sparse24_mask_shapes_dtypes(ops, orc, dtype, shape):
     assert_bit_equal(ops.sparse24_mask(t.cuda()).cpu(), orc.sparse24_mask(t), "keep mask")
 
 
+@pytest.mark.parametrize("bits", [4, 8])
+def test_marlin24_steps_match_oracle(ops, orc, bits):
+    """the Marlin-24 kernels against the oracle on a weight-sized tensor with every non-zero pattern of a run"""
+    g = torch.Generator().manual_seed(24 + bits)
+    n, k = 512, 2048
+    half = (1 << bits) // 2
+    q = torch.randint(-half, half, (n, k), generator=g, dtype=torch.int8)
+    q[torch.rand(n, k, generator=g) < 0.55] = 0  # runs with 0..4 non-zeros: every branch of the index selection
+    sparse, meta = orc.cutlass24_compress(q)
+    gs, gm = ops.cutlass24_compress(q.cuda())
+    assert_bit_equal(gs.cpu(), sparse, "2:4 values"), assert_bit_equal(gm.cpu(), meta, "reordered meta")
+    assert_bit_equal(ops.marlin24_pack_weight(gs, bits).cpu(), orc.marlin24_pack_weight(sparse, bits), "packed weight")
+    scale = torch.rand(n, k // 128, generator=g).to(torch.float16)
+    for grouped in (False, True):
+        assert_bit_equal(ops.marlin24_pack_scales(scale.cuda(), grouped).cpu(), orc.marlin24_pack_scales(scale, grouped), "scales")
+
+
 @pytest.mark.parametrize("shape", [(14336, 4096), (4096, 14336), (1024, 4096)])
 def test_full_size_round_trip_properties(ops, shape):
     """At the benchmark's tensor sizes: compress -> decompress -> compress is a fixed point (same words, same

@@ -238,3 +238,15 @@ def test_mxfp4_scale_helpers_every_input(golden):
     for key, dt in (("bf16", torch.bfloat16), ("f16", torch.float16), ("f32", torch.float32)):
         assert_bit_equal(orc.mxfp4_convert_scales(e, dt), d["all_exponents"][key], key)
 
+
+def test_marlin24_steps(golden):
+    """CUTLASS 2:4 compaction + reordered meta, tile permutation + packing, scale permutation (marlin_24.py:124-273)"""
+    for name, d in golden("marlin24").items():
+        bits, group = int(d["bits"]), int(d["group"])
+        sparse, meta = orc.cutlass24_compress(d["q"])
+        assert torch.equal(sparse, d["sparse"]) and torch.equal(meta, d["meta_reordered"]), name
+        assert torch.equal(orc.marlin24_pack_weight(sparse, bits), d["weight_packed"]), name
+        grouped = group > 0 and group < sparse.shape[1]
+        assert_bit_equal(orc.marlin24_pack_scales(d["scale"], grouped), d["scale_packed"], name)
+        assert torch.equal(meta.reshape(meta.shape[1] // 2, meta.shape[0] * 2), d["meta"]), name
+
