@@ -17,7 +17,9 @@ import types
 os.environ.setdefault("TORCHDYNAMO_DISABLE", "1")
 os.environ.setdefault("HF_HUB_OFFLINE", "1")
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    sys.exit(__doc__)
+REF = sys.argv[1]
 _v = types.ModuleType("compressed_tensors.version")
 _v.__version__ = _v.version = "0.0.0"
 _v.__all__ = ["__version__", "version"]
