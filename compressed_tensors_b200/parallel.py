@@ -199,21 +199,26 @@ class HostRoundTrip:
         return self.d2h_packed_bytes + sum(w.numel() * w.element_size() for w in self.host_w)
 
     def run(self) -> None:
-        """One round trip of the whole shard; returns after everything has landed in the host buffers."""
+        """One round trip of the whole shard; returns after everything has landed in the host buffers.
+
+        Two stages per group, issued one group apart so that neither copy direction ever waits on the other:
+          A(k): weights host -> device, compress, packed bytes device -> host;
+          B(k): packed bytes host -> device, decompress, dense weights device -> host.
+        Issue order A(0), A(1), B(0), A(2), B(1), ...: the copy-in stream then carries W0 W1 P0 W2 P1 ... and the
+        copy-out stream P0 P1 R0 P2 R1 ..., i.e. the small packed transfer of the NEXT group is already through
+        when the large dense transfer of this group starts, and the packed bytes a B stage needs back are on the
+        host long before its turn."""
         ev = torch.cuda.Event
         n = len(self.groups)
+        packed_on_host = [None] * n
 
-        def copy_in(k):
-            e = ev()
+        def stage_a(k):
+            g, codec = self.groups[k], self.codecs[k]
+            e_in, e_c, e_o = ev(), ev(), ev()
             with torch.cuda.stream(self.s_in):
-                for i in self.groups[k]:
+                for i in g:
                     self.dev_w[i].copy_(self.host_w[i], non_blocking=True)
-                e.record()
-            return e
-
-        e_in = copy_in(0)
-        for k, (g, codec) in enumerate(zip(self.groups, self.codecs)):
-            e_c, e_o, e_in2, e_d = ev(), ev(), ev(), ev()
+                e_in.record()
             with torch.cuda.stream(self.s_k):
                 self.s_k.wait_event(e_in)
                 codec._compress()
@@ -224,10 +229,13 @@ class HostRoundTrip:
                     self.host_p[i].copy_(codec.packed[j], non_blocking=True)
                     self.host_s[i].copy_(codec.scales[j], non_blocking=True)
                 e_o.record()
-            if k + 1 < n:  # the next group's weights go in while this group's packed bytes make their trip out
-                e_in = copy_in(k + 1)
+            packed_on_host[k] = e_o
+
+        def stage_b(k):
+            g, codec = self.groups[k], self.codecs[k]
+            e_in2, e_d = ev(), ev()
             with torch.cuda.stream(self.s_in):
-                self.s_in.wait_event(e_o)  # the packed bytes are on the host: bring them back for the decompress half
+                self.s_in.wait_event(packed_on_host[k])  # the packed bytes made it to the host: bring them back
                 for j, i in enumerate(g):
                     codec.packed[j].copy_(self.host_p[i], non_blocking=True)
                     codec.scales[j].copy_(self.host_s[i], non_blocking=True)
@@ -240,5 +248,11 @@ class HostRoundTrip:
                 self.s_out.wait_event(e_d)
                 for j, i in enumerate(g):
                     self.host_r[i].copy_(codec.restored[j], non_blocking=True)
+
+        for k in range(n + 1):
+            if k < n:
+                stage_a(k)
+            if k >= 1:
+                stage_b(k - 1)
         for s in (self.s_in, self.s_k, self.s_out):
             s.synchronize()
