@@ -341,7 +341,7 @@ def main():
         e2e = {"value": 2 * 2 * total_elems / float(te) / 1e9, "unit": UNIT,
                "h2d_bytes_per_step": trip.h2d_bytes, "d2h_bytes_per_step": trip.d2h_bytes,
                "ms_per_step": float(te) * 1e3, "bytes_are": "per rank",
-               "path": "HostRoundTrip: pinned host -> device -> fused kernels -> pinned host, 3 streams, one decoder layer per group"}
+               "path": "HostRoundTrip: pinned host -> device -> fused kernels -> pinned host, 3 streams, one decoder layer per step, stages issued one step apart"}
         # the restored host weights must be what the device path produced
         check = parallel.ShardCodec(weights[:len(shapes)], signs=signs, precision=precision)
         check.compress(), check.decompress()

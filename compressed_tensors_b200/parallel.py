@@ -170,10 +170,16 @@ class HostRoundTrip:
     kernels, copy-out -- so that both PCIe directions and the GPU stay busy at once; events carry the
     dependencies (a group is decompressed only after its own packed bytes made the trip to the host and back)."""
 
-    def __init__(self, host_weights: Sequence[torch.Tensor], group: int, device, *, signs=None, precision=torch.float64):
+    def __init__(self, host_weights: Sequence[torch.Tensor], group: int, device, *, signs=None, precision=torch.float64, ramp: int = 0):
+        """`group` tensors per pipeline step; the first and last `ramp` tensors go one per step, which shortens the
+        stretch at either end of the trip during which only one copy direction has work."""
         self.device = torch.device(device)
         self.host_w = list(host_weights)
-        self.groups = [list(range(i, min(i + group, len(self.host_w)))) for i in range(0, len(self.host_w), group)]
+        n = len(self.host_w)
+        ramp = max(0, min(ramp, n // 2))
+        self.groups = [[i] for i in range(ramp)]
+        self.groups += [list(range(i, min(i + group, n - ramp))) for i in range(ramp, n - ramp, group)]
+        self.groups += [[i] for i in range(n - ramp, n)]
         self.dev_w = [torch.empty(w.shape, dtype=w.dtype, device=self.device) for w in self.host_w]
         self.codecs = [ShardCodec([self.dev_w[i] for i in g], signs=signs, precision=precision) for g in self.groups]
         for c in self.codecs:
