@@ -502,7 +502,7 @@ extern "C" int ctb_unpack_dequantize_int4_batch(const ctb_tensor_ref *tensors, i
         B.count = n;
         B.ustart[n] = g;
         if (g == 0) continue;
-        int grid = grid_for(g, 1, 8);
+        int grid = grid_for(g, 1, 64);  // more blocks than fit at once: the resident ones then sweep the output as one moving window
         dequant_int4_batch_kernel<<<grid, kThreads, 0, as_stream(stream)>>>(B);
         int rc = after_launch("dequant_int4_batch_kernel");
         if (rc) return rc;
