@@ -608,7 +608,7 @@ extern "C" int ctb_absmax_quantize(const ctb_qdesc *d, const void *x, const floa
     }
     if (fout == F_PACK4 && d->col_group == 128 && d->scale_row_stride == d->cols / 128) {
         const int64_t ngroups = d->rows * d->cols / 128;
-        absmax_quant_g128_int4_kernel<<<grid_for(ngroups, kThreads / 2, 4), kThreads, 0, st>>>(x, out, out_scale, ngroups);
+        absmax_quant_g128_int4_kernel<<<grid_for(ngroups, kThreads / 2, 16), kThreads, 0, st>>>(x, out, out_scale, ngroups);
         return after_launch("absmax_quant_g128_int4_kernel");
     }
     if (fout == F_FP4X2 && d->col_group == 16 && d->scale_row_stride == d->cols / 16) {

@@ -386,7 +386,7 @@ static int run(int mode, const ctb_qdesc *d, const void *in, const void *scale, 
         }
         if (mode == 1 && a.qk == QK_FP4 && a.fin == F_FP4X2 && a.fout == F_BF16 && d->scale_dtype == CTB_E4M3 && gs && !zp && flat &&
             d->col_group == 16) {
-            dequant_fp4_g16_bf16_kernel<<<grid_for(a.chunks, (int64_t)kThreads * 8, 8), kThreads, 0, st>>>(in, (const uint8_t *)scale, gs, a.chunks, out);
+            dequant_fp4_g16_bf16_kernel<<<grid_for(a.chunks, (int64_t)kThreads * 8, 32), kThreads, 0, st>>>(in, (const uint8_t *)scale, gs, a.chunks, out);
             return after_launch("dequant_fp4_g16_bf16_kernel");
         }
         bool handled = false;
@@ -502,7 +502,9 @@ extern "C" int ctb_unpack_dequantize_int4_batch(const ctb_tensor_ref *tensors, i
         B.count = n;
         B.ustart[n] = g;
         if (g == 0) continue;
-        int grid = grid_for(g, 1, 64);  // more blocks than fit at once: the resident ones then sweep the output as one moving window
+        // many more blocks than fit at once (a handful of units each): the resident ones then sweep the output as one
+        // moving window, which measured 6 % faster on this write-heavy kernel than one persistent block per slot
+        int grid = grid_for(g, 1, 256);
         dequant_int4_batch_kernel<<<grid, kThreads, 0, as_stream(stream)>>>(B);
         int rc = after_launch("dequant_int4_batch_kernel");
         if (rc) return rc;
