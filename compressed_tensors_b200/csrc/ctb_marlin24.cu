@@ -22,8 +22,9 @@ constexpr int kMThreads = 256;
 template <int ES>
 __global__ void __launch_bounds__(kMThreads) cutlass24_compress_kernel(const void *dense, int64_t m, int64_t k, void *sparse, int16_t *meta_reordered) {
     const int64_t ncols = k / 16, total = m * ncols;
+    const bool small = total < 0x7FFFFFFF;  // 32-bit division when the index fits
     for (int64_t t = (int64_t)blockIdx.x * kMThreads + threadIdx.x; t < total; t += (int64_t)gridDim.x * kMThreads) {
-        const int64_t r = t / ncols, c = t - r * ncols;
+        const int64_t r = small ? (int64_t)((uint32_t)t / (uint32_t)ncols) : t / ncols, c = t - r * ncols;
         uint32_t v[16];  // raw bits of the 16 elements
         if constexpr (ES == 1) {
             const uint4 w = *reinterpret_cast<const uint4 *>((const char *)dense + (r * k + c * 16));
@@ -62,11 +63,13 @@ __global__ void __launch_bounds__(kMThreads) cutlass24_compress_kernel(const voi
             o.w = kept[6] | (kept[7] << 16);
             *reinterpret_cast<uint4 *>((char *)sparse + (r * (k / 2) + c * 8) * 2) = o;
         }
-        int64_t dr = r / 64 * 64 + (r % 2) * 2 + (r % 8) / 4 + ((r % 32) % 4) / 2 * 32 + ((r % 64) / 8) * 4, dc = c;
-        const int swap = ((dr % 2 == 0) && (dc % 2 == 1)) - ((dr % 2 == 1) && (dc % 2 == 0));
-        dr += swap;
+        const int rl = (int)(r & 63);  // position inside the 64-row group; the group's base row is unchanged
+        int dl = (rl & 1) * 2 + ((rl & 7) >> 2) + (((rl & 3) >> 1) << 5) + ((rl >> 3) << 2);
+        int64_t dc = c;
+        const int swap = (int)(((dl & 1) == 0) && ((dc & 1) == 1)) - (int)(((dl & 1) == 1) && ((dc & 1) == 0));
+        dl += swap;
         dc -= swap;
-        meta_reordered[(dc / 2) * m * 2 + dr * 2 + dc % 2] = (int16_t)elem;
+        meta_reordered[(dc >> 1) * m * 2 + ((r & ~(int64_t)63) + dl) * 2 + (dc & 1)] = (int16_t)elem;
     }
 }
 
@@ -82,23 +85,31 @@ __device__ __forceinline__ int marlin24_perm(int d, int bits) {
     return 16 * row + col_o * 256 + 8 * (col % 2) + 4 * block + j;
 }
 
-// ---- step 2: one thread per packed word.  sparse is [n, k2] int8 codes; out is [k2 / 16, n * 16 / pf] int32.
-__global__ void __launch_bounds__(kMThreads) marlin24_pack_weight_kernel(const int8_t *sparse, int64_t n, int64_t k2, int bits, int32_t *out) {
+// ---- step 2: one block per 1024-element chunk = a 16 (k) x 64 (n) tile of the compacted codes.  sparse is
+// [n, k2] int8 codes; out is [k2 / 16, n * 16 / pf] int32.  The tile comes in as 64 rows of 16 contiguous bytes,
+// goes through shared memory, and leaves as 1024 / pf consecutive words.
+constexpr int kPackThreads = 128;
+__global__ void __launch_bounds__(kPackThreads) marlin24_pack_weight_kernel(const int8_t *sparse, int64_t n, int64_t k2, int bits, int32_t *out) {
     __shared__ uint16_t perm[1024];
-    for (int d = threadIdx.x; d < 1024; d += kMThreads) perm[d] = (uint16_t)marlin24_perm(d, bits);
-    __syncthreads();
-    const int pf = 32 / bits, half = (1 << bits) / 2;
-    const int64_t words_per_row = n * 16 / pf, total = (k2 / 16) * words_per_row;
-    for (int64_t t = (int64_t)blockIdx.x * kMThreads + threadIdx.x; t < total; t += (int64_t)gridDim.x * kMThreads) {
-        const int64_t kt = t / words_per_row, j = t - kt * words_per_row;
-        uint32_t word = 0;
-        for (int i = 0; i < pf; ++i) {
-            const int64_t idx = j * pf + i, src = (idx & ~(int64_t)1023) + perm[idx & 1023];
-            const int64_t nt = src >> 8, ki = (src & 255) >> 4, ni = src & 15;
-            const uint32_t v = (uint32_t)((int)sparse[(nt * 16 + ni) * k2 + kt * 16 + ki] + half);
-            word |= v << (bits * i);
+    __shared__ __align__(16) uint8_t tile[64 * 16];  // tile[ni_global(64)][ki(16)]
+    for (int d = threadIdx.x; d < 1024; d += kPackThreads) perm[d] = (uint16_t)marlin24_perm(d, bits);
+    const int pf = 32 / bits, half = (1 << bits) / 2, words = 1024 / pf;
+    const int64_t chunks_per_row = n / 64, total = (k2 / 16) * chunks_per_row;
+    for (int64_t blk = blockIdx.x; blk < total; blk += gridDim.x) {
+        const int64_t kt = blk / chunks_per_row, ch = blk - kt * chunks_per_row;
+        __syncthreads();  // the previous tile has been consumed (and perm is complete)
+        if (threadIdx.x < 64)
+            *reinterpret_cast<uint4 *>(tile + threadIdx.x * 16) = *reinterpret_cast<const uint4 *>(sparse + (ch * 64 + threadIdx.x) * k2 + kt * 16);
+        __syncthreads();
+        for (int w = threadIdx.x; w < words; w += kPackThreads) {
+            uint32_t word = 0;
+            for (int i = 0; i < pf; ++i) {
+                // position inside the chunk: (n tile of 16, k, n inside the tile), marlin_24.py:213-217
+                const int src = perm[w * pf + i], nt = src >> 8, ki = (src & 255) >> 4, ni = src & 15;
+                word |= (uint32_t)((int)(int8_t)tile[(nt * 16 + ni) * 16 + ki] + half) << (bits * i);
+            }
+            out[kt * (chunks_per_row * words) + ch * words + w] = (int32_t)word;
         }
-        out[t] = (int32_t)word;
     }
 }
 
@@ -138,8 +149,8 @@ extern "C" int ctb_marlin24_pack_weight(const int8_t *sparse, int64_t n, int64_t
     if (num_bits != 4 && num_bits != 8) return fail(CTB_EINVAL_SHAPE, "num_bits must be 4 or 8, got %d", num_bits);
     if (n < 0 || k2 < 0 || k2 % 16 != 0 || n % 64 != 0) return fail(CTB_EINVAL_SHAPE, "size_k must be a multiple of 16 and size_n of 64");
     if (n == 0 || k2 == 0) return CTB_OK;
-    const int64_t words = (k2 / 16) * (n * 16 / (32 / num_bits));
-    marlin24_pack_weight_kernel<<<grid_for(words, kMThreads, 8), kMThreads, 0, as_stream(stream)>>>(sparse, n, k2, num_bits, out);
+    if (reinterpret_cast<uintptr_t>(sparse) & 15u) return fail(CTB_EINVAL_ALIGN, "codes must be 16-byte aligned");
+    marlin24_pack_weight_kernel<<<grid_for((k2 / 16) * (n / 64), 1, 16), kPackThreads, 0, as_stream(stream)>>>(sparse, n, k2, num_bits, out);
     return after_launch("marlin24_pack_weight_kernel");
 }
 
