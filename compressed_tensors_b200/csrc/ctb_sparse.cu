@@ -792,28 +792,40 @@ __global__ void __launch_bounds__(kThreads) bm_warp_scatter_kernel(const void *x
     int64_t first, last;
     warp_range((units + 63) / 64, first, last);
     const int lane = threadIdx.x & 31;
-    uint32_t mask_n[2] = {0, 0};
-    Raw8 raw_n[2];
-    auto fetch = [&](int64_t t) {  // a tile's loads do not depend on the running offset: they are issued one tile ahead
+    uint32_t mask[2] = {0, 0};
+    Raw8 raw[2];
+    // a tile's loads do not depend on the running offset: they are issued as soon as the registers of the tile
+    // before are free, i.e. before that tile's copy-out
+    const char *xw = (const char *)x + (first * 64 + lane) * (8 * ES);  // this lane's unit of the range's first tile
+    const uint8_t *mw = bitmask + first * 64 + lane;
+    auto fetch = [&](int64_t t) {
+        const uint32_t off = (uint32_t)(t - first) * 64u;  // units from the range's first tile (ranges are short)
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-            const int64_t u = t * 64 + 32 * h + lane;
-            mask_n[h] = 0;
-            raw_n[h].a = raw_n[h].b = make_uint4(0, 0, 0, 0);
-            if (u < units) {
-                mask_n[h] = bitmask[u];
-                raw_n[h] = load_unit_raw<ES, false>(x, u);
+            mask[h] = 0;
+            raw[h].a = raw[h].b = make_uint4(0, 0, 0, 0);
+            if (t * 64 + 32 * h + lane < units) {
+                mask[h] = mw[off + 32 * h];
+                const char *p = xw + (size_t)(off + 32 * h) * (8 * ES);
+                if constexpr (ES == 2) raw[h].a = ld_stream(p);
+                else if constexpr (ES == 1) {
+                    const uint2 v = ld_stream8(p);
+                    raw[h].a.x = v.x;
+                    raw[h].a.y = v.y;
+                } else {
+                    raw[h].a = ld_stream(p);
+                    raw[h].b = ld_stream(p + 16);
+                }
             }
         }
     };
     if (first < last) fetch(first);  // in flight during the prologue
     unsigned long long prefix = warp_first_value(block_tot, warp_tot, nnz);
-    int64_t r_next = (first * kWarpTile + cols - 1) / cols;  // first row that starts inside this warp's range
+    // first row that starts inside this warp's range (32-bit division when the element index fits)
+    const int64_t e_first = first * kWarpTile + cols - 1;
+    int64_t r_next = (units < 0x10000000 && cols < 0x7FFFFFFF) ? (int64_t)((uint32_t)e_first / (uint32_t)cols) : e_first / cols;
     int64_t e_next = r_next * cols;
     for (int64_t tile = first; tile < last; ++tile) {
-        const uint32_t mask[2] = {mask_n[0], mask_n[1]};
-        const Raw8 raw[2] = {raw_n[0], raw_n[1]};
-        if (tile + 1 < last) fetch(tile + 1);
         int excl[2], total;
         warp_excl_scan2(__popc(mask[0]), __popc(mask[1]), excl[0], excl[1], total);
         char *dst = (char *)values + prefix * ES;
@@ -826,6 +838,7 @@ __global__ void __launch_bounds__(kThreads) bm_warp_scatter_kernel(const void *x
 #pragma unroll
             for (int j = 0; j < 8; ++j) stage_put_if<ES>(sa, b[j], mask[h] & (1u << j));
         }
+        if (tile + 1 < last) fetch(tile + 1);
         // rows that begin inside this tile (cols is a multiple of 8: at the first element of one of its 64 units)
         while (e_next < (tile + 1) * kWarpTile && r_next < rows) {  // uniform over the warp
             const int unit = (int)(e_next - tile * kWarpTile) >> 3;
@@ -836,9 +849,10 @@ __global__ void __launch_bounds__(kThreads) bm_warp_scatter_kernel(const void *x
         __syncwarp();
         const int nbytes = shift + total * ES;
         const int first_full = shift ? 1 : 0, end_full = nbytes >> 2;  // words [first_full, end_full) are wholly this tile's
-        uint32_t *d0 = reinterpret_cast<uint32_t *>(dst - shift);
-#pragma unroll 4
-        for (int w = first_full + lane; w < end_full; w += 32) d0[w] = st[pad_word(w)];
+        uint32_t *dw = reinterpret_cast<uint32_t *>(dst - shift) + first_full + lane;
+        const uint32_t *sw = st + first_full + lane;
+        for (int left = end_full - first_full; left > 0; left -= 32, dw += 32, sw += 32)  // uniform trip count
+            if (lane < left) *dw = *sw;
         if (lane < 8) {  // the ragged head and tail share their words with the neighbouring tiles: element by element
             const int head_end = first_full * 4 < nbytes ? first_full * 4 : nbytes;
             const int tail0 = end_full * 4 > head_end ? end_full * 4 : head_end;
