@@ -176,8 +176,9 @@ int ctb_sparse24_compress(const void *x, int32_t dtype, int64_t rows, int64_t co
  * row-major.  out_row_offsets is int64 [rows] (exclusive prefix of per-row counts).
  * Elements equal to zero (+0.0 and -0.0) are dropped; NaN is kept. */
 /* `workspace`: ctb_bitmask_workspace_bytes(rows, cols) bytes of device scratch (contents ignored); with it the
- * codec runs as two kernels over flat 4096-element tiles (count + scan of the per-block totals by the last block,
- * then scatter); NULL selects the row-by-row count / scan / scatter path. */
+ * codec runs as two kernels over flat 512-element tiles, one per warp and step (kept counts of every warp's
+ * contiguous range of tiles, then the compaction with a running offset); NULL selects the row-by-row
+ * count / scan / scatter path. */
 int64_t ctb_bitmask_workspace_bytes(int64_t rows, int64_t cols);
 int ctb_bitmask_compress(const void *x, int32_t dtype, int64_t rows, int64_t cols, void *out_values,
                          uint8_t *out_bitmask, int64_t *out_row_offsets, int64_t *out_nnz,
