@@ -12,64 +12,74 @@ namespace ctb {
 
 constexpr int kMThreads = 256;
 
-// ---- step 1: one thread per metadata element = 16 consecutive elements of a row = 4 runs of four
+// ---- step 1: one thread per metadata element = 16 consecutive elements of a row = 4 runs of four; one block per
+// tile of 64 rows x 8 metadata columns.
 //
 // A run keeps two values chosen by its non-zero pattern (semi_structured_conversions.py:160-176): with m_i the
 // non-zero flags, index0 = (~m0 & m1) | ((~m0 & ~m1) << 1) and index1 = ((m0 & m1) | (~m0 & ~m1) | m3) |
 // (((~m0 & m1) | ~m1) << 1); the run's 4-bit code is index0 | index1 << 2.  Four codes make an int16 metadata
-// element, which is stored at its place in CUTLASS's reordered, column-interleaved layout (:43-73).
+// element, which goes to its place in CUTLASS's reordered, column-interleaved layout (:43-73).  That reordering
+// permutes rows inside groups of 64 and swaps elements inside 2 x 2 blocks, so a 64-row tile of a column pair is one
+// contiguous run of 128 elements of the output: the tile's elements are placed in shared memory and written out
+// as whole runs.
 // ES = 1: int8 codes (standing for the 16-bit tensor holding the same integers), ES = 2: fp16 / bf16 values.
 template <int ES>
 __global__ void __launch_bounds__(kMThreads) cutlass24_compress_kernel(const void *dense, int64_t m, int64_t k, void *sparse, int16_t *meta_reordered) {
-    const int64_t ncols = k / 16, total = m * ncols;
-    const bool small = total < 0x7FFFFFFF;  // 32-bit division when the index fits
-    for (int64_t t = (int64_t)blockIdx.x * kMThreads + threadIdx.x; t < total; t += (int64_t)gridDim.x * kMThreads) {
-        const int64_t r = small ? (int64_t)((uint32_t)t / (uint32_t)ncols) : t / ncols, c = t - r * ncols;
-        uint32_t v[16];  // raw bits of the 16 elements
-        if constexpr (ES == 1) {
-            const uint4 w = *reinterpret_cast<const uint4 *>((const char *)dense + (r * k + c * 16));
-            const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+    __shared__ __align__(4) int16_t smeta[4][128];  // [column pair of the tile][reordered row * 2 + column parity]
+    const int64_t ncols = k / 16, tiles_c = (ncols + 7) / 8, tiles = (m / 64) * tiles_c;
+    for (int64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+        const int64_t tr = tile / tiles_c, r0 = tr * 64, c0 = (tile - tr * tiles_c) * 8;
+        for (int e = threadIdx.x; e < 512; e += kMThreads) {
+            const int row = e >> 3;
+            const int64_t r = r0 + row, c = c0 + (e & 7);
+            if (c >= ncols) continue;
+            uint32_t v[16];  // raw bits of the 16 elements
+            if constexpr (ES == 1) {
+                const uint4 w = ld_stream((const char *)dense + (r * k + c * 16));
+                const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
-            for (int i = 0; i < 16; ++i) v[i] = (ww[i >> 2] >> (8 * (i & 3))) & 0xFFu;
-        } else {
-            const uint4 *p = reinterpret_cast<const uint4 *>((const char *)dense + (r * k + c * 16) * 2);
-            const uint4 a = p[0], b = p[1];
-            const uint32_t ww[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+                for (int i = 0; i < 16; ++i) v[i] = (ww[i >> 2] >> (8 * (i & 3))) & 0xFFu;
+            } else {
+                const char *p = (const char *)dense + (r * k + c * 16) * 2;
+                const uint4 a = ld_stream(p), b = ld_stream(p + 16);
+                const uint32_t ww[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
 #pragma unroll
-            for (int i = 0; i < 16; ++i) v[i] = (ww[i >> 1] >> (16 * (i & 1))) & 0xFFFFu;
-        }
-        const uint32_t nz = ES == 1 ? 0xFFu : 0x7FFFu;  // -0.0 is zero for the float types (`dense != 0`)
-        uint32_t elem = 0, kept[8];
+                for (int i = 0; i < 16; ++i) v[i] = (ww[i >> 1] >> (16 * (i & 1))) & 0xFFFFu;
+            }
+            const uint32_t nz = ES == 1 ? 0xFFu : 0x7FFFu;  // -0.0 is zero for the float types (`dense != 0`)
+            uint32_t elem = 0, kept[8];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const bool m0 = (v[4 * j] & nz) != 0, m1 = (v[4 * j + 1] & nz) != 0, m3 = (v[4 * j + 3] & nz) != 0;
-            const bool e0 = m0 && m1, e1 = !m0 && m1, e2 = !m0 && !m1;
-            const int i0 = (int)e1 | ((int)e2 << 1), i1 = (int)(e0 || e2 || m3) | ((int)(e1 || !m1) << 1);
-            // register arrays cannot be indexed dynamically: select
-            kept[2 * j] = i0 == 0 ? v[4 * j] : i0 == 1 ? v[4 * j + 1] : v[4 * j + 2];  // index0 is never 3
-            kept[2 * j + 1] = i1 == 1 ? v[4 * j + 1] : i1 == 2 ? v[4 * j + 2] : v[4 * j + 3];  // index1 is never 0
-            elem |= (uint32_t)(i0 | (i1 << 2)) << (4 * j);
+            for (int j = 0; j < 4; ++j) {
+                const bool m0 = (v[4 * j] & nz) != 0, m1 = (v[4 * j + 1] & nz) != 0, m3 = (v[4 * j + 3] & nz) != 0;
+                const bool e0 = m0 && m1, e1 = !m0 && m1, e2 = !m0 && !m1;
+                const int i0 = (int)e1 | ((int)e2 << 1), i1 = (int)(e0 || e2 || m3) | ((int)(e1 || !m1) << 1);
+                // register arrays cannot be indexed dynamically: select
+                kept[2 * j] = i0 == 0 ? v[4 * j] : i0 == 1 ? v[4 * j + 1] : v[4 * j + 2];  // index0 is never 3
+                kept[2 * j + 1] = i1 == 1 ? v[4 * j + 1] : i1 == 2 ? v[4 * j + 2] : v[4 * j + 3];  // index1 is never 0
+                elem |= (uint32_t)(i0 | (i1 << 2)) << (4 * j);
+            }
+            if constexpr (ES == 1) {
+                st_stream8((char *)sparse + (r * (k / 2) + c * 8),
+                           make_uint2(kept[0] | (kept[1] << 8) | (kept[2] << 16) | (kept[3] << 24), kept[4] | (kept[5] << 8) | (kept[6] << 16) | (kept[7] << 24)));
+            } else {
+                st_stream((char *)sparse + (r * (k / 2) + c * 8) * 2,
+                          make_uint4(kept[0] | (kept[1] << 16), kept[2] | (kept[3] << 16), kept[4] | (kept[5] << 16), kept[6] | (kept[7] << 16)));
+            }
+            // reordered row inside the 64-row group (a permutation of the row's bits), then the 2 x 2 swap
+            int dl = (row & 1) * 2 + ((row & 7) >> 2) + (((row & 3) >> 1) << 5) + ((row >> 3) << 2);
+            int dcl = e & 7;
+            const int swap = (int)(((dl & 1) == 0) && ((dcl & 1) == 1)) - (int)(((dl & 1) == 1) && ((dcl & 1) == 0));
+            dl += swap;
+            dcl -= swap;
+            smeta[dcl >> 1][dl * 2 + (dcl & 1)] = (int16_t)elem;
         }
-        if constexpr (ES == 1) {
-            uint2 o;
-            o.x = kept[0] | (kept[1] << 8) | (kept[2] << 16) | (kept[3] << 24);
-            o.y = kept[4] | (kept[5] << 8) | (kept[6] << 16) | (kept[7] << 24);
-            *reinterpret_cast<uint2 *>((char *)sparse + (r * (k / 2) + c * 8)) = o;
-        } else {
-            uint4 o;
-            o.x = kept[0] | (kept[1] << 16);
-            o.y = kept[2] | (kept[3] << 16);
-            o.z = kept[4] | (kept[5] << 16);
-            o.w = kept[6] | (kept[7] << 16);
-            *reinterpret_cast<uint4 *>((char *)sparse + (r * (k / 2) + c * 8) * 2) = o;
+        __syncthreads();
+        {  // 4 column pairs x 128 elements, two elements (one 32-bit word) per thread
+            const int pair = threadIdx.x >> 6, within = (threadIdx.x & 63) * 2;
+            if (c0 + pair * 2 < ncols)
+                *reinterpret_cast<uint32_t *>(meta_reordered + (c0 / 2 + pair) * m * 2 + r0 * 2 + within) = *reinterpret_cast<const uint32_t *>(&smeta[pair][within]);
         }
-        const int rl = (int)(r & 63);  // position inside the 64-row group; the group's base row is unchanged
-        int dl = (rl & 1) * 2 + ((rl & 7) >> 2) + (((rl & 3) >> 1) << 5) + ((rl >> 3) << 2);
-        int64_t dc = c;
-        const int swap = (int)(((dl & 1) == 0) && ((dc & 1) == 1)) - (int)(((dl & 1) == 1) && ((dc & 1) == 0));
-        dl += swap;
-        dc -= swap;
-        meta_reordered[(dc >> 1) * m * 2 + ((r & ~(int64_t)63) + dl) * 2 + (dc & 1)] = (int16_t)elem;
+        __syncthreads();  // smeta is reused by the next tile
     }
 }
 
@@ -135,10 +145,11 @@ extern "C" int ctb_cutlass24_compress(const void *dense, int32_t dtype, int64_t 
     if (dtype != CTB_I8 && dtype != CTB_F16 && dtype != CTB_BF16) return fail(CTB_EINVAL_DTYPE, "dense must be int8 codes, f16 or bf16");
     if (rows < 0 || cols < 0) return fail(CTB_EINVAL_SHAPE, "negative shape");
     if (rows % 64 != 0) return fail(CTB_EINVAL_SHAPE, "Number of rows of dense matrix %lld must be divisible by 64", (long long)rows);
-    if (cols % 16 != 0) return fail(CTB_EINVAL_SHAPE, "Number of columns of dense matrix %lld must be divisible by 16", (long long)cols);
-    if (!aligned16(dense) || !aligned16(out_sparse)) return fail(CTB_EINVAL_ALIGN, "buffers must be 16-byte aligned");
+    // 16 in the reference's check, but with an odd number of metadata columns its 2 x 2 swap leaves the matrix
+    if (cols % 32 != 0) return fail(CTB_EINVAL_SHAPE, "Number of columns of dense matrix %lld must be divisible by 32", (long long)cols);
+    if (!aligned16(dense) || !aligned16(out_sparse) || (reinterpret_cast<uintptr_t>(out_meta) & 3u)) return fail(CTB_EINVAL_ALIGN, "buffers must be 16-byte aligned (the metadata 4-byte)");
     if (rows == 0 || cols == 0) return CTB_OK;
-    const int grid = grid_for(rows * (cols / 16), kMThreads, 8);
+    const int grid = grid_for((rows / 64) * ((cols / 16 + 7) / 8), 1, 8);
     if (dtype == CTB_I8) cutlass24_compress_kernel<1><<<grid, kMThreads, 0, as_stream(stream)>>>(dense, rows, cols, out_sparse, out_meta);
     else cutlass24_compress_kernel<2><<<grid, kMThreads, 0, as_stream(stream)>>>(dense, rows, cols, out_sparse, out_meta);
     return after_launch("cutlass24_compress_kernel");

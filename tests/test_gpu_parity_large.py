@@ -288,6 +288,66 @@ def test_full_size_round_trip_properties(ops, shape):
     assert int(words.to(torch.int64).sum()) == int(words2.to(torch.int64).sum())
 
 
+@pytest.mark.parametrize("shape", [(14336, 4096), (4096, 11008)])
+def test_full_size_sparse_codec_properties(ops, shape):
+    """At the benchmark's tensor sizes, through properties that need no CPU pass over the tensor: bitmask and 2:4
+    round trips restore the input bit for bit, counts agree with the bitmask, row offsets are the running counts,
+    the 2:4 mask keeps exactly two per run and never a smaller magnitude over a larger one."""
+    g = torch.Generator(device="cuda").manual_seed(13)
+    w = (torch.randn(shape, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    w[torch.rand(shape, generator=g, device="cuda") < 0.5] = 0
+    values, bitmask, row_offsets = ops.bitmask_compress(w)
+    nz = w != 0
+    assert values.numel() == int(nz.sum())
+    assert torch.equal(ops.unpack_bitmasks(bitmask, list(shape)), nz)
+    counts = nz.sum(dim=1)
+    assert torch.equal(row_offsets, torch.cumsum(counts, 0) - counts)
+    assert torch.equal(values, w[nz]), "kept values in row-major order"
+    assert_bit_equal(ops.bitmask_decompress(values, bitmask, shape).cpu(), torch.where(nz, w, torch.zeros((), dtype=w.dtype, device="cuda")).cpu())
+    # 2:4
+    d = (torch.randn(shape, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    keep = ops.sparse24_mask(d)
+    assert bool((keep.view(-1, 4).sum(dim=1) == 2).all())
+    mag = d.abs().float().view(-1, 4)
+    kept_min = torch.where(keep.view(-1, 4), mag, torch.full_like(mag, float("inf"))).amin(dim=1)
+    drop_max = torch.where(keep.view(-1, 4), torch.full_like(mag, -1.0), mag).amax(dim=1)
+    assert bool((kept_min >= drop_max).all()), "no dropped element is larger than a kept one"
+    pruned = torch.where(keep, d, torch.zeros((), dtype=d.dtype, device="cuda"))
+    v24, b24 = ops.sparse24_compress(pruned)
+    assert torch.equal(ops.unpack_bitmasks(b24, list(shape)), ops.sparse24_mask(pruned)), "bitmask == mask of the pruned tensor"
+    assert torch.equal(v24.flatten(), pruned[ops.unpack_bitmasks(b24, list(shape))])
+    assert torch.equal(ops.sparse24_decompress(v24, b24, shape), pruned)
+
+
+def test_full_size_fp8_and_nvfp4_properties(ops):
+    """FP8 per-token activations (8192 x 4096) and NVFP4 weights (14336 x 4096): fused calibrate+quantize equals the
+    separate calls, dequantize(quantize) is a fixed point of quantize, and the error stays inside half a step."""
+    g = torch.Generator(device="cuda").manual_seed(17)
+    x = torch.randn(8192, 4096, generator=g, device="cuda").to(torch.bfloat16)
+    kw8 = dict(qtype=ops.QFLOAT, bits=8, col_group=4096)
+    q, s = ops.absmax_quantize(x, codec="dtype", out_dtype=torch.float8_e4m3fn, **kw8)
+    mn, mx = ops.minmax(x, 1, 4096)
+    amax = torch.maximum(mn.abs(), mx.abs()).float()
+    assert torch.equal(s.float().flatten(), torch.clamp((amax / 448.0).to(torch.bfloat16).float(), min=torch.finfo(torch.float32).eps).flatten())
+    assert_bit_equal(ops.quantize(x, s, None, out_dtype=torch.float8_e4m3fn, scale_row_stride=1, **kw8).cpu(), q.cpu(), "fused == separate")
+    deq = ops.dequantize(q, s, None, scale_row_stride=1, out_dtype=torch.bfloat16, **kw8)
+    assert bool(((deq.float() - x.float()).abs() <= 0.0725 * x.float().abs() + 2.0 ** -9 * s.float()).all()), "e4m3 relative step"
+    w = (torch.randn(14336, 4096, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    mn, mx = ops.minmax(w, 14336, 4096)
+    gs = ops.generate_gparam(mn, mx)
+    kw4 = dict(qtype=ops.QFLOAT, bits=4, col_group=16)
+    p, sc = ops.absmax_quantize(w, codec="fp4x2", global_scale=gs, **kw4)
+    assert_bit_equal(ops.quantize(w, sc, None, codec="fp4x2", global_scale=gs, scale_row_stride=256, **kw4).cpu(), p.cpu(), "fused == separate")
+    deq = ops.dequantize(p, sc, None, scale_row_stride=256, out_dtype=torch.bfloat16, codec="fp4x2", global_scale=gs, **kw4)
+    again = ops.quantize(deq, sc, None, codec="fp4x2", global_scale=gs, scale_row_stride=256, **kw4)
+    # the codes agree except that a negative value that rounded to zero keeps its sign bit (0x8) the first time only
+    deq2 = ops.dequantize(again, sc, None, scale_row_stride=256, out_dtype=torch.bfloat16, codec="fp4x2", global_scale=gs, **kw4)
+    assert torch.equal(deq2, deq), "re-quantizing the dequantized tensor with the same scales restores the same values"
+    assert bool((((again ^ p) & 0x77) == 0).all()), "magnitude bits of every code are a fixed point"
+    eff = (sc.float() / gs).repeat_interleave(16, dim=1)
+    assert bool(((deq.float() - w.float()).abs() <= 1.01 * eff).all()), "inside one e2m1 step of the largest magnitudes"
+
+
 def test_whole_shard_batch_equals_per_tensor(ops):
     """One grid over a list of tensors (ragged sizes, a tensor smaller than one warp of blocks) gives exactly
     the per-tensor results, in both rotation precisions, and decompress restores the same values."""
