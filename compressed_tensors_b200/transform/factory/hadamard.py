@@ -20,6 +20,7 @@ class HadamardFactory(TransformFactory):
     def __init__(self, name: str, scheme: TransformScheme, seed: Optional[int] = None):
         super().__init__(name, scheme, seed)
         self._weights = {}
+        self._perms = {}
 
     def create_transform(self, module: Module, args: TransformArgs) -> "HadamardTransform":
         size = get_transform_size(module, args.location, self.scheme.head_dim)
@@ -28,9 +29,12 @@ class HadamardFactory(TransformFactory):
         key = (size, precision)
         if key not in self._weights:  # one matrix per size, shared by every module (hadamard.py:64)
             self._weights[key] = self._create_weight(size, torch.device("cpu"), torch.device("cpu"), precision)
-        if self.scheme.randomize:
-            raise NotImplementedError("randomize=True (row/column permutation of the Hadamard matrix) is not built")
-        return HadamardTransform(self._weights[key], None, self.scheme, args, type(module))
+        perm = None
+        if self.scheme.randomize:  # hadamard.py:62: one permutation per weight, drawn after the weight
+            if key not in self._perms:
+                self._perms[key] = Parameter(torch.randperm(size, generator=self.generator), requires_grad=False)
+            perm = self._perms[key]
+        return HadamardTransform(self._weights[key], perm, self.scheme, args, type(module))
 
     def _create_weight(self, size: int, device, construct_device, precision: torch.dtype) -> Parameter:
         return Parameter(deterministic_hadamard_matrix(size, precision, construct_device), requires_grad=False)
@@ -57,11 +61,26 @@ class HadamardTransform(TransformBase):
             raise NotImplementedError(f"{location.value} transforms are outside this package")
         acc = torch.float64 if self.weight.dtype == torch.float64 else torch.float32
         signs = self._signs.to(value.device)
+        n = self.weight.size(0)
+        # randomize (hadamard.py:104-108) applies M[perm][:, perm] = P M P^T: permute the transformed axis into the
+        # matrix's index space, run the butterfly, permute back.  The permutation acts inside every block of n.
+        perm = inv = None
+        if self.perm is not None:
+            perm = self.perm.data.to(value.device)
+            inv = torch.empty_like(perm)
+            inv[perm] = torch.arange(n, device=perm.device)
         if location == TransformLocation.WEIGHT_OUTPUT:
-            return ops.hadamard(value, self.weight.size(0), signs=signs, inverse=bool(self.args.inverse), side=1, precision=acc)
+            if perm is not None:
+                value = value.reshape(-1, n, value.shape[-1])[:, inv, :].reshape(value.shape)
+            out = ops.hadamard(value, n, signs=signs, inverse=bool(self.args.inverse), side=1, precision=acc)
+            return out if perm is None else out.reshape(-1, n, out.shape[-1])[:, perm, :].reshape(out.shape)
         # matrix.py:113-119: activations are multiplied by the matrix itself (value @ M), a weight's input side by
         # its transpose (value @ M.T), so the two differ in which of M / M.T the `inverse` flag selects
         transposed = bool(self.args.inverse) != location.is_online()
         flat = value.reshape(-1, value.shape[-1])
-        out = ops.hadamard(flat, self.weight.size(0), signs=signs, inverse=transposed, side=0, precision=acc)
+        if perm is not None:
+            flat = flat.reshape(flat.shape[0], -1, n)[:, :, inv].reshape(flat.shape)
+        out = ops.hadamard(flat.contiguous(), n, signs=signs, inverse=transposed, side=0, precision=acc)
+        if perm is not None:
+            out = out.reshape(out.shape[0], -1, n)[:, :, perm].reshape(out.shape)
         return out.reshape(value.shape)

@@ -377,6 +377,27 @@ def gen_marlin24():
     torch.save(out, os.path.join(OUT, "marlin24.pt"))
 
 
+def gen_hadamard_randomize():
+    """randomize=True: the Hadamard matrix with its rows and columns permuted (factory/hadamard.py:62, :104-108)."""
+    out = {}
+    gen = torch.Generator().manual_seed(6)
+    for tag, fac_cls in (("hadamard", HadamardFactory), ("random", RandomHadamardFactory)):
+        for location in ("weight_input", "weight_output", "input"):
+            for inverse in (False, True):
+                i, o = (16, 256) if location == "weight_output" else (256, 16)
+                lin = torch.nn.Linear(i, o, bias=False, dtype=torch.bfloat16)
+                scheme = TransformScheme(type=tag if tag == "hadamard" else "random-hadamard", head_dim=128, randomize=True,
+                                         apply=[TransformArgs(targets=["Linear"], location=location, inverse=inverse)])
+                fac = fac_cls("t", scheme, seed=11)
+                tr = fac.create_transform(lin, scheme.apply[0])
+                x = weights(gen, o, i, torch.bfloat16) if location != "input" else torch.randn(3, 256, generator=gen).to(torch.bfloat16)
+                with torch.no_grad():
+                    y = tr(x)
+                out[f"{tag}_{location}_{'inv' if inverse else 'fwd'}"] = {
+                    "x": x, "out": y.detach(), "matrix": tr.weight.detach().to(torch.int8), "perm": tr.perm.detach().clone()}
+    torch.save(out, os.path.join(OUT, "hadamard_randomize.pt"))
+
+
 def gen_mxfp4():
     """quantization/utils/mxfp4_utils.py on EVERY bf16 bit pattern and every uint8 exponent."""
     from compressed_tensors.quantization.utils.mxfp4_utils import (
@@ -401,7 +422,7 @@ def gen_mxfp4():
 if __name__ == "__main__":
     only = sys.argv[2] if len(sys.argv) > 2 else None  # e.g. "mxfp4": regenerate one fixture
     for name, fn in (("int_quant", gen_int), ("fp8_quant", gen_fp8), ("nvfp4", gen_nvfp4), ("sparse", gen_sparse),
-                     ("hadamard", gen_hadamard), ("hadamard_online", gen_hadamard_online), ("mxfp4", gen_mxfp4), ("marlin24", gen_marlin24)):
+                     ("hadamard", gen_hadamard), ("hadamard_online", gen_hadamard_online), ("hadamard_randomize", gen_hadamard_randomize), ("mxfp4", gen_mxfp4), ("marlin24", gen_marlin24)):
         if only is None or only == name:
             fn()
     for f in sorted(os.listdir(OUT)):

@@ -373,3 +373,26 @@ def test_marlin24_compressor(golden):
     with pytest.raises(NotImplementedError):
         comp.decompress("x")
 
+
+def test_randomized_hadamard(golden):
+    """randomize=True (factory/hadamard.py:62, :104-108): same permutation as the reference for the same seed, and
+    the permuted transform applied around the butterfly kernel gives the reference's bits (float64 offline) or its
+    values to one bf16 step (fp32 online)"""
+    from compressed_tensors_b200.transform import TransformArgs, TransformFactory, TransformScheme
+    from tests.helpers import bf16_ulp_distance
+
+    for name, d in golden("hadamard_randomize").items():
+        tag, rest = name.split("_", 1)
+        location, direction = rest.rsplit("_", 1)
+        i, o = (16, 256) if location == "weight_output" else (256, 16)
+        lin = torch.nn.Linear(i, o, bias=False, dtype=torch.bfloat16).cuda()
+        scheme = TransformScheme(type="hadamard" if tag == "hadamard" else "random-hadamard", head_dim=128, randomize=True,
+                                 apply=[TransformArgs(targets=["Linear"], location=location, inverse=direction == "inv")])
+        tr = TransformFactory.from_scheme(scheme, name="t", seed=11).create_transform(lin, scheme.apply[0])
+        assert torch.equal(tr.weight.data.to(torch.int8).cpu(), d["matrix"]) and torch.equal(tr.perm.data.cpu(), d["perm"]), name
+        y = tr(d["x"].cuda()).cpu()
+        if location == "input":
+            assert bf16_ulp_distance(y, d["out"]) <= 1, name
+        else:
+            assert_bit_equal(y, d["out"], name)
+
