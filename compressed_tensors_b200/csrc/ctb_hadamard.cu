@@ -507,7 +507,7 @@ static bool pow2(int64_t v) { return v > 0 && (v & (v - 1)) == 0; }
 
 extern "C" int ctb_hadamard(const void *x, int32_t dtype, int64_t rows, int64_t cols, int32_t n, const int8_t *signs, int32_t inverse,
                             int32_t side, int32_t precision, int32_t normalize, void *out, void *stream) {
-    if (!x || !out) return fail(CTB_EINVAL_NULL, "null buffer");
+    if (rows != 0 && cols != 0 && (!x || !out)) return fail(CTB_EINVAL_NULL, "null buffer");  // an empty tensor has no storage
     if (!is_float_dtype(dtype)) return fail(CTB_EINVAL_DTYPE, "weights must be bf16, f16 or f32");
     if (!pow2(n)) return fail(CTB_EUNSUPPORTED, "only Sylvester sizes (powers of two) are built");
     if (precision != CTB_F64 && precision != CTB_F32 && precision != CTB_ROT_TENSOR) return fail(CTB_EINVAL_DTYPE, "precision must be F64, F32 or CTB_ROT_TENSOR");
@@ -558,7 +558,8 @@ extern "C" int ctb_hadamard(const void *x, int32_t dtype, int64_t rows, int64_t 
 
 extern "C" int ctb_absmax_quantize(const ctb_qdesc *d, const void *x, const float *gs, void *out_scale, void *out, int32_t n,
                                    const int8_t *signs, int32_t precision, void *stream) {
-    if (!d || !x || !out_scale || !out) return fail(CTB_EINVAL_NULL, "null descriptor or buffer");
+    if (!d) return fail(CTB_EINVAL_NULL, "null descriptor");
+    if (d->rows != 0 && (!x || !out_scale || !out)) return fail(CTB_EINVAL_NULL, "null buffer");  // an empty tensor has no storage
     if (d->x_dtype != CTB_BF16) return fail(CTB_EUNSUPPORTED, "fused calibration is built for bf16 tensors");
     if (d->rows < 0 || d->cols <= 0 || d->col_group <= 0 || d->cols % d->col_group) return fail(CTB_EINVAL_SHAPE, "tensor column shape must be divisble by the given group_size");
     if (d->row_group != 1) return fail(CTB_EUNSUPPORTED, "fused calibration does not take 2-D blocks");

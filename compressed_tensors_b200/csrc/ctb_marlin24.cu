@@ -141,7 +141,7 @@ using namespace ctb;
 
 extern "C" int ctb_cutlass24_compress(const void *dense, int32_t dtype, int64_t rows, int64_t cols, void *out_sparse, int16_t *out_meta,
                                       void *stream) {
-    if (!dense || !out_sparse || !out_meta) return fail(CTB_EINVAL_NULL, "null buffer");
+    if (rows != 0 && cols != 0 && (!dense || !out_sparse || !out_meta)) return fail(CTB_EINVAL_NULL, "null buffer");  // an empty tensor has no storage
     if (dtype != CTB_I8 && dtype != CTB_F16 && dtype != CTB_BF16) return fail(CTB_EINVAL_DTYPE, "dense must be int8 codes, f16 or bf16");
     if (rows < 0 || cols < 0) return fail(CTB_EINVAL_SHAPE, "negative shape");
     if (rows % 64 != 0) return fail(CTB_EINVAL_SHAPE, "Number of rows of dense matrix %lld must be divisible by 64", (long long)rows);
@@ -156,7 +156,7 @@ extern "C" int ctb_cutlass24_compress(const void *dense, int32_t dtype, int64_t 
 }
 
 extern "C" int ctb_marlin24_pack_weight(const int8_t *sparse, int64_t n, int64_t k2, int32_t num_bits, int32_t *out, void *stream) {
-    if (!sparse || !out) return fail(CTB_EINVAL_NULL, "null buffer");
+    if (n != 0 && k2 != 0 && (!sparse || !out)) return fail(CTB_EINVAL_NULL, "null buffer");
     if (num_bits != 4 && num_bits != 8) return fail(CTB_EINVAL_SHAPE, "num_bits must be 4 or 8, got %d", num_bits);
     if (n < 0 || k2 < 0 || k2 % 16 != 0 || n % 64 != 0) return fail(CTB_EINVAL_SHAPE, "size_k must be a multiple of 16 and size_n of 64");
     if (n == 0 || k2 == 0) return CTB_OK;
@@ -166,7 +166,7 @@ extern "C" int ctb_marlin24_pack_weight(const int8_t *sparse, int64_t n, int64_t
 }
 
 extern "C" int ctb_marlin24_pack_scales(const void *scale, int64_t n, int64_t groups, int32_t grouped, void *out, void *stream) {
-    if (!scale || !out) return fail(CTB_EINVAL_NULL, "null buffer");
+    if (n != 0 && groups != 0 && (!scale || !out)) return fail(CTB_EINVAL_NULL, "null buffer");
     if (n < 0 || groups < 0 || n % 64 != 0) return fail(CTB_EINVAL_SHAPE, "size_n must be a multiple of 64");
     if (n == 0 || groups == 0) return CTB_OK;
     marlin24_pack_scales_kernel<<<grid_for(n * groups, kMThreads, 8), kMThreads, 0, as_stream(stream)>>>((const uint16_t *)scale, n, groups,

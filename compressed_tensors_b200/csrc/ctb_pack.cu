@@ -88,7 +88,7 @@ __global__ void __launch_bounds__(kThreads) unpack_bitmasks_kernel(const uint8_t
 using namespace ctb;
 
 extern "C" int ctb_pack_int32(const int8_t *value, int64_t rows, int64_t cols, int64_t rs, int64_t cs, int32_t bits, int32_t *out, void *stream) {
-    if (!value || !out) return fail(CTB_EINVAL_NULL, "null buffer");
+    if (rows != 0 && cols != 0 && (!value || !out)) return fail(CTB_EINVAL_NULL, "null buffer");  // an empty tensor has no storage
     if (bits > 8) return fail(CTB_EINVAL_SHAPE, "Packing is only supported for less than 8 bits");
     if (bits < 1) return fail(CTB_EINVAL_SHAPE, "num_bits must be at least 1, got %d", bits);
     if (rows < 0 || cols < 0) return fail(CTB_EINVAL_SHAPE, "negative shape");
@@ -99,7 +99,7 @@ extern "C" int ctb_pack_int32(const int8_t *value, int64_t rows, int64_t cols, i
 }
 
 extern "C" int ctb_unpack_int32(const int32_t *words, int64_t rows, int64_t cols, int64_t rs, int64_t cs, int32_t bits, int8_t *out, void *stream) {
-    if (!words || !out) return fail(CTB_EINVAL_NULL, "null buffer");
+    if (rows != 0 && cols != 0 && (!words || !out)) return fail(CTB_EINVAL_NULL, "null buffer");
     if (bits > 8) return fail(CTB_EINVAL_SHAPE, "Unpacking is only supported for less than 8 bits");
     if (bits < 1) return fail(CTB_EINVAL_SHAPE, "num_bits must be at least 1, got %d", bits);
     if (rows < 0 || cols < 0) return fail(CTB_EINVAL_SHAPE, "negative shape");
@@ -109,7 +109,7 @@ extern "C" int ctb_unpack_int32(const int32_t *words, int64_t rows, int64_t cols
 }
 
 extern "C" int ctb_pack_fp4(const void *x, int32_t dtype, int64_t m, int64_t n, uint8_t *out, void *stream) {
-    if (!x || !out) return fail(CTB_EINVAL_NULL, "null buffer");
+    if (m != 0 && n != 0 && (!x || !out)) return fail(CTB_EINVAL_NULL, "null buffer");
     if (n % 2 != 0) return fail(CTB_EINVAL_SHAPE, "tensor must have an even number of columns for nvfp4 compression");
     if (!is_float_dtype(dtype)) return fail(CTB_EINVAL_DTYPE, "fp4 values must be held in bf16, f16 or f32");
     if (m * n == 0) return CTB_OK;
@@ -118,7 +118,7 @@ extern "C" int ctb_pack_fp4(const void *x, int32_t dtype, int64_t m, int64_t n, 
 }
 
 extern "C" int ctb_unpack_fp4(const uint8_t *packed, int64_t m, int64_t n, void *out, int32_t odt, void *stream) {
-    if (!packed || !out) return fail(CTB_EINVAL_NULL, "null buffer");
+    if (m != 0 && n != 0 && (!packed || !out)) return fail(CTB_EINVAL_NULL, "null buffer");
     if (n % 2 != 0) return fail(CTB_EINVAL_SHAPE, "odd column count");
     if (!is_float_dtype(odt)) return fail(CTB_EINVAL_DTYPE, "output must be bf16, f16 or f32");
     if (m * n == 0) return CTB_OK;
@@ -127,14 +127,14 @@ extern "C" int ctb_unpack_fp4(const uint8_t *packed, int64_t m, int64_t n, void 
 }
 
 extern "C" int ctb_pack_bitmasks(const uint8_t *bytemask, int64_t rows, int64_t cols, uint8_t *out, void *stream) {
-    if (!bytemask || !out) return fail(CTB_EINVAL_NULL, "null buffer");
+    if (rows != 0 && cols != 0 && (!bytemask || !out)) return fail(CTB_EINVAL_NULL, "null buffer");
     if (rows * cols == 0) return CTB_OK;
     pack_bitmasks_kernel<<<grid_for(rows * cdiv(cols, 8), kThreads, 8), kThreads, 0, as_stream(stream)>>>(bytemask, rows, cols, out);
     return after_launch("pack_bitmasks_kernel");
 }
 
 extern "C" int ctb_unpack_bitmasks(const uint8_t *packed, int64_t rows, int64_t cols, uint8_t *out, void *stream) {
-    if (!packed || !out) return fail(CTB_EINVAL_NULL, "null buffer");
+    if (rows != 0 && cols != 0 && (!packed || !out)) return fail(CTB_EINVAL_NULL, "null buffer");
     if (rows * cols == 0) return CTB_OK;
     unpack_bitmasks_kernel<<<grid_for(rows * cols, kThreads, 8), kThreads, 0, as_stream(stream)>>>(packed, rows, cols, out);
     return after_launch("unpack_bitmasks_kernel");

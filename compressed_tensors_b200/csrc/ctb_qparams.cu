@@ -239,7 +239,7 @@ extern "C" int ctb_minmax(const void *x, int32_t dt, int64_t rows, int64_t cols,
 
 extern "C" int ctb_calculate_qparams(const void *mins, const void *maxs, int32_t dtype, int64_t n, int32_t qtype, int32_t bits,
                                      int32_t symmetric, const float *gs, void *out_scale, void *out_zp, int32_t zdt, void *stream) {
-    if (!mins || !maxs || !out_scale || !out_zp) return fail(CTB_EINVAL_NULL, "null buffer");
+    if (n != 0 && (!mins || !maxs || !out_scale || !out_zp)) return fail(CTB_EINVAL_NULL, "null buffer");  // an empty tensor has no storage
     if (!is_float_dtype(dtype)) return fail(CTB_EINVAL_DTYPE, "min/max must be bf16, f16 or f32");
     if (qtype == CTB_QFLOAT && bits == 4 && !symmetric) return fail(CTB_EUNSUPPORTED, "Asymmetric Quantization is not supported for FP4");
     if (qtype == CTB_QFLOAT && bits != 4 && bits != 8) return fail(CTB_EUNSUPPORTED, "Range calculation only supported for 4 and 8 bits");
@@ -258,7 +258,7 @@ extern "C" int ctb_generate_gparam(const void *mn, const void *mx, int32_t dtype
 }
 
 extern "C" int ctb_mxfp4_round_pow2(const void *x, int64_t n, void *out, void *stream) {
-    if (!x || !out) return fail(CTB_EINVAL_NULL, "null buffer");
+    if (n != 0 && (!x || !out)) return fail(CTB_EINVAL_NULL, "null buffer");
     if (n < 0) return fail(CTB_EINVAL_SHAPE, "negative size");
     if (n == 0) return CTB_OK;
     mxfp4_scale_kernel<0><<<grid_for(n, 256, 8), 256, 0, as_stream(stream)>>>((const uint16_t *)x, n, out);
@@ -266,7 +266,7 @@ extern "C" int ctb_mxfp4_round_pow2(const void *x, int64_t n, void *out, void *s
 }
 
 extern "C" int ctb_mxfp4_generate_scales(const void *x, int64_t n, uint8_t *out, void *stream) {
-    if (!x || !out) return fail(CTB_EINVAL_NULL, "null buffer");
+    if (n != 0 && (!x || !out)) return fail(CTB_EINVAL_NULL, "null buffer");
     if (n < 0) return fail(CTB_EINVAL_SHAPE, "negative size");
     if (n == 0) return CTB_OK;
     mxfp4_scale_kernel<1><<<grid_for(n, 256, 8), 256, 0, as_stream(stream)>>>((const uint16_t *)x, n, out);
@@ -274,7 +274,7 @@ extern "C" int ctb_mxfp4_generate_scales(const void *x, int64_t n, uint8_t *out,
 }
 
 extern "C" int ctb_mxfp4_convert_scales(const uint8_t *scale, int64_t n, int32_t out_dtype, void *out, void *stream) {
-    if (!scale || !out) return fail(CTB_EINVAL_NULL, "null buffer");
+    if (n != 0 && (!scale || !out)) return fail(CTB_EINVAL_NULL, "null buffer");
     if (!is_float_dtype(out_dtype)) return fail(CTB_EINVAL_DTYPE, "dense scales are bf16, f16 or f32");
     if (n < 0) return fail(CTB_EINVAL_SHAPE, "negative size");
     if (n == 0) return CTB_OK;

@@ -278,7 +278,8 @@ static int code_fmt(const ctb_qdesc *d) {
 }
 
 static int validate(const ctb_qdesc *d, const void *in, const void *scale, const void *out, int mode) {
-    if (!d || !in || !scale || !out) return fail(CTB_EINVAL_NULL, "null descriptor or buffer");
+    if (!d) return fail(CTB_EINVAL_NULL, "null descriptor");
+    if (d->rows != 0 && d->cols != 0 && (!in || !scale || !out)) return fail(CTB_EINVAL_NULL, "null buffer");  // an empty tensor has no storage
     if (d->rows < 0 || d->cols < 0) return fail(CTB_EINVAL_SHAPE, "negative shape");
     if (d->col_group <= 0 || d->row_group <= 0) return fail(CTB_EINVAL_SHAPE, "group sizes must be positive");
     // forward.py:277-282 / :215-224: columns (rows) must divide into whole groups (blocks)

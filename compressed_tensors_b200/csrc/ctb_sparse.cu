@@ -942,7 +942,7 @@ __global__ void __launch_bounds__(kThreads, ES == 4 ? 4 : 8) bm_warp_expand_kern
 using namespace ctb;
 
 extern "C" int ctb_sparse24_mask(const void *x, int32_t dtype, int64_t numel, uint8_t *out, void *stream) {
-    if (!x || !out) return fail(CTB_EINVAL_NULL, "null buffer");
+    if (numel != 0 && (!x || !out)) return fail(CTB_EINVAL_NULL, "null buffer");  // an empty tensor has no storage
     ElemInfo e;
     if (!elem_info(dtype, &e)) return fail(CTB_EINVAL_DTYPE, "unsupported dtype for 2:4 masks");
     if (numel % 4 != 0) return fail(CTB_EINVAL_SHAPE, "Tensor size must be a multiple of 4 for TWO_FOUR sparsity");
@@ -971,7 +971,7 @@ extern "C" int ctb_sparse24_mask(const void *x, int32_t dtype, int64_t numel, ui
 }
 
 extern "C" int ctb_sparse24_compress(const void *x, int32_t dtype, int64_t rows, int64_t cols, void *values, uint8_t *bitmask, void *stream) {
-    if (!x || !values || !bitmask) return fail(CTB_EINVAL_NULL, "null buffer");
+    if (rows != 0 && cols != 0 && (!x || !values || !bitmask)) return fail(CTB_EINVAL_NULL, "null buffer");
     ElemInfo e;
     if (!elem_info(dtype, &e)) return fail(CTB_EINVAL_DTYPE, "unsupported dtype for 2:4 compression");
     if ((rows * cols) % 4 != 0) return fail(CTB_EINVAL_SHAPE, "Tensor size must be a multiple of 4 for TWO_FOUR sparsity");
@@ -1006,7 +1006,7 @@ static int tile_grid(int64_t units, int blocks_per_sm = 8) {
 
 static int compress_impl(const void *x, const uint8_t *pred, int32_t dtype, int64_t rows, int64_t cols, void *values, uint8_t *bitmask,
                          int64_t *row_offsets, int64_t *nnz, void *workspace, void *stream) {
-    if (!x || !values || !bitmask || !row_offsets || !nnz) return fail(CTB_EINVAL_NULL, "null buffer");
+    if (!nnz || (rows != 0 && cols != 0 && (!x || !values || !bitmask || !row_offsets))) return fail(CTB_EINVAL_NULL, "null buffer");
     ElemInfo e;
     if (!elem_info(dtype, &e)) return fail(CTB_EINVAL_DTYPE, "unsupported dtype for bitmask compression");
     if (rows < 0 || cols < 0) return fail(CTB_EINVAL_SHAPE, "negative shape");
@@ -1058,13 +1058,13 @@ extern "C" int ctb_bitmask_compress(const void *x, int32_t dtype, int64_t rows, 
 
 extern "C" int ctb_masked_compress(const void *x, const uint8_t *bytemask, int32_t dtype, int64_t rows, int64_t cols, void *values,
                                    uint8_t *bitmask, int64_t *row_offsets, int64_t *nnz, void *stream) {
-    if (!bytemask) return fail(CTB_EINVAL_NULL, "null mask");
+    if (rows != 0 && cols != 0 && !bytemask) return fail(CTB_EINVAL_NULL, "null mask");
     return compress_impl(x, bytemask, dtype, rows, cols, values, bitmask, row_offsets, nnz, nullptr, stream);
 }
 
 static int decompress_impl(const void *values, const uint8_t *bitmask, int32_t dtype, int64_t rows, int64_t cols, void *out, void *workspace,
                            Gate gate, void *stream, bool tiles_ok = false) {
-    if (!bitmask || !out || !workspace) return fail(CTB_EINVAL_NULL, "null buffer");
+    if (rows != 0 && cols != 0 && (!bitmask || !out || !workspace)) return fail(CTB_EINVAL_NULL, "null buffer");
     ElemInfo e;
     if (!elem_info(dtype, &e)) return fail(CTB_EINVAL_DTYPE, "unsupported dtype for bitmask decompression");
     if (rows <= 0 || cols <= 0) return rows < 0 || cols < 0 ? fail(CTB_EINVAL_SHAPE, "negative shape") : CTB_OK;
@@ -1107,7 +1107,7 @@ extern "C" int ctb_bitmask_decompress(const void *values, const uint8_t *bitmask
 
 extern "C" int ctb_sparse24_decompress(const void *values, const uint8_t *bitmask, int32_t dtype, int64_t rows, int64_t cols, void *out,
                                        void *workspace, void *stream) {
-    if (!values || !bitmask || !out || !workspace) return fail(CTB_EINVAL_NULL, "null buffer");
+    if (rows != 0 && cols != 0 && (!values || !bitmask || !out || !workspace)) return fail(CTB_EINVAL_NULL, "null buffer");
     ElemInfo e;
     if (!elem_info(dtype, &e)) return fail(CTB_EINVAL_DTYPE, "unsupported dtype for bitmask decompression");
     if (rows <= 0 || cols <= 0) return rows < 0 || cols < 0 ? fail(CTB_EINVAL_SHAPE, "negative shape") : CTB_OK;

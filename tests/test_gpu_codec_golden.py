@@ -236,3 +236,34 @@ def test_mxfp4_scale_helpers_every_input(golden, ops):
     for key, dt in (("bf16", torch.bfloat16), ("f16", torch.float16), ("f32", torch.float32)):
         assert_bit_equal(convert_mxfp4_exp_scale(e, dt).cpu(), d["all_exponents"][key], key)
 
+
+def test_empty_and_degenerate_tensors(ops):
+    """a tensor with no elements has no storage (null pointer): every codec returns an empty result of the right
+    shape instead of raising, as the reference's tensor expressions do; all-zero and all-dense tensors round-trip"""
+    dev = "cuda"
+    e16 = torch.empty((0, 16), dtype=torch.bfloat16, device=dev)
+    v, b, r = ops.bitmask_compress(e16)
+    assert (tuple(v.shape), tuple(b.shape), tuple(r.shape)) == ((0,), (0, 2), (0,))
+    assert tuple(ops.bitmask_decompress(v, b, (0, 16)).shape) == (0, 16)
+    assert tuple(ops.sparse24_mask(e16).shape) == (0, 16)
+    v, b = ops.sparse24_compress(e16)
+    assert (tuple(v.shape), tuple(b.shape)) == ((0, 8), (0, 2))
+    assert tuple(ops.sparse24_decompress(v, b, (0, 16)).shape) == (0, 16)
+    sp, meta = ops.cutlass24_compress(torch.empty((0, 64), dtype=torch.int8, device=dev))
+    assert (tuple(sp.shape), tuple(meta.shape)) == ((0, 32), (0, 4))
+    assert ops.mxfp4_generate_scales(torch.empty((0,), dtype=torch.bfloat16, device=dev)).numel() == 0
+    q, s = ops.absmax_quantize(torch.empty((0, 128), dtype=torch.bfloat16, device=dev), qtype=ops.QINT, bits=4, col_group=128, codec="pack32")
+    assert (tuple(q.shape), tuple(s.shape)) == ((0, 16), (0, 1))
+    kw = dict(qtype=ops.QINT, bits=4, col_group=128, scale_row_stride=1)
+    assert tuple(ops.quantize(torch.empty((0, 128), dtype=torch.bfloat16, device=dev), s, None, codec="pack32", **kw).shape) == (0, 16)
+    assert tuple(ops.dequantize(q, s, None, out_dtype=torch.bfloat16, codec="pack32", cols=128, **kw).shape) == (0, 128)
+    assert tuple(ops.hadamard(torch.empty((0, 128), dtype=torch.bfloat16, device=dev), 128).shape) == (0, 128)
+    z = torch.zeros((512, 4096), dtype=torch.bfloat16, device=dev)
+    v, b, r = ops.bitmask_compress(z)
+    assert v.numel() == 0 and int(b.sum()) == 0 and int(r.sum()) == 0
+    assert torch.equal(ops.bitmask_decompress(v, b, (512, 4096)), z)
+    o = torch.ones((512, 4096), dtype=torch.bfloat16, device=dev)
+    v, b, r = ops.bitmask_compress(o)
+    assert v.numel() == o.numel() and bool((b == 255).all()) and int(r[-1]) == 511 * 4096
+    assert torch.equal(ops.bitmask_decompress(v, b, (512, 4096)), o)
+
