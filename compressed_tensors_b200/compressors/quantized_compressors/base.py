@@ -88,9 +88,21 @@ class BaseQuantizationCompressor(BaseCompressor):
                 if "weight_scale" in weight_data and module_path in names_to_scheme:
                     weight_data["weight"] = self.decompress_weight(compressed_data=weight_data,
                                                                    quantization_args=names_to_scheme[module_path].weights)
-                    yield module_path, {k: v.to(device) for k, v in weight_data.items()}
+                    yield module_path, {k: self._deliver(v, device) for k, v in weight_data.items()}
         finally:
             handles.clear()
+
+    @staticmethod
+    def _deliver(tensor: Tensor, device) -> Tensor:
+        """Leave a result on `device`.  To the host it goes through page-locked memory (a pageable destination makes
+        the driver stage the copy in small pieces, which is slower than the decompression itself); torch's host
+        allocator recycles the page-locked blocks once the caller drops the tensors."""
+        if torch.device(device).type != "cpu" or not tensor.is_cuda:
+            return tensor.to(device)
+        out = torch.empty(tensor.shape, dtype=tensor.dtype, pin_memory=True)
+        out.copy_(tensor, non_blocking=True)
+        torch.cuda.current_stream(tensor.device).synchronize()
+        return out
 
     def decompress_module(self, module: torch.nn.Module) -> Optional[Tensor]:
         """Dense weight of one compressed leaf module (compressors/base.py:165-190 of the reference), or None when
