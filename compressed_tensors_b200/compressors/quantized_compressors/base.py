@@ -42,7 +42,7 @@ class BaseQuantizationCompressor(BaseCompressor):
                     global_scale=on_gpu(model_state.get(prefix + "weight_global_scale")), g_idx=on_gpu(model_state.get(prefix + "weight_g_idx")),
                     quantization_args=names_to_scheme[module_path].weights, device=compression_device)
                 for k, v in compressed.items():
-                    out[prefix + k] = v.to(compression_device)
+                    out[prefix + k] = self._deliver(v, compression_device)
             else:
                 if name.endswith("zero_point") and self._skip_zp(name, names_to_scheme):
                     continue
