@@ -54,11 +54,12 @@ class HadamardTransform(TransformBase):
         """hadamard.py:104-121: (apply_transform_weight(W_h, value.to(W_h.dtype)) / sqrt(n)).to(value.dtype).
         Weights rotate along their input (side 0) or output (side 1) dimension; activations (`input` / `output`)
         rotate along their last dimension, in blocks of the transform size."""
-        if self.module_type != torch.nn.Linear:
-            raise NotImplementedError(f"Applying transforms to {self.module_type} {self.args.location} is not supported")
         location = TransformLocation(self.args.location)
         if location in (TransformLocation.Q_ATTN, TransformLocation.K_CACHE):
             raise NotImplementedError(f"{location.value} transforms are outside this package")
+        embedding = self.module_type == torch.nn.Embedding
+        if not (self.module_type == torch.nn.Linear or (embedding and not location.is_online())):
+            raise NotImplementedError(f"Applying transforms to {self.module_type} {self.args.location} is not supported")
         acc = torch.float64 if self.weight.dtype == torch.float64 else torch.float32
         signs = self._signs.to(value.device)
         n = self.weight.size(0)
@@ -69,14 +70,17 @@ class HadamardTransform(TransformBase):
             perm = self.perm.data.to(value.device)
             inv = torch.empty_like(perm)
             inv[perm] = torch.arange(n, device=perm.device)
-        if location == TransformLocation.WEIGHT_OUTPUT:
+        # matrix.py:113-126: which product each location stands for.  Linear (y = x W.T): weight_input is value @ M.T,
+        # weight_output is M.T @ value, activations are value @ M.  Embedding (y = x W): weight_input is M @ value and
+        # weight_output is value @ M.  The kernel's side 1 computes M.T @ value and its side 0 value @ M.T; `inverse`
+        # (M replaced by M.T) flips either.
+        rows_side = location == (TransformLocation.WEIGHT_INPUT if embedding else TransformLocation.WEIGHT_OUTPUT)
+        if rows_side:
             if perm is not None:
                 value = value.reshape(-1, n, value.shape[-1])[:, inv, :].reshape(value.shape)
-            out = ops.hadamard(value, n, signs=signs, inverse=bool(self.args.inverse), side=1, precision=acc)
+            out = ops.hadamard(value, n, signs=signs, inverse=bool(self.args.inverse) != embedding, side=1, precision=acc)
             return out if perm is None else out.reshape(-1, n, out.shape[-1])[:, perm, :].reshape(out.shape)
-        # matrix.py:113-119: activations are multiplied by the matrix itself (value @ M), a weight's input side by
-        # its transpose (value @ M.T), so the two differ in which of M / M.T the `inverse` flag selects
-        transposed = bool(self.args.inverse) != location.is_online()
+        transposed = bool(self.args.inverse) != (location.is_online() or embedding)
         flat = value.reshape(-1, value.shape[-1])
         if perm is not None:
             flat = flat.reshape(flat.shape[0], -1, n)[:, :, inv].reshape(flat.shape)

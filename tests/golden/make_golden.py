@@ -398,6 +398,26 @@ def gen_hadamard_randomize():
     torch.save(out, os.path.join(OUT, "hadamard_randomize.pt"))
 
 
+def gen_hadamard_embedding():
+    """Transforms fused into an Embedding weight (matrix.py:121-126: the weight is applied as y = x W, so the sides
+    swap relative to Linear)."""
+    out = {}
+    gen = torch.Generator().manual_seed(8)
+    for tag, fac_cls, seed in (("random", RandomHadamardFactory, 7),):
+        for location in ("weight_input", "weight_output"):
+            for inverse in (False, True):
+                emb = torch.nn.Embedding(128, 128, dtype=torch.bfloat16)
+                emb.weight.data = weights(gen, 128, 128, torch.bfloat16)
+                scheme = TransformScheme(type=tag if tag == "hadamard" else "random-hadamard", head_dim=128,
+                                         apply=[TransformArgs(targets=["Embedding"], location=location, inverse=inverse)])
+                tr = fac_cls("t", scheme, seed=seed).create_transform(emb, scheme.apply[0])
+                w0 = emb.weight.data.clone()
+                with torch.no_grad():
+                    w1 = tr(emb.weight)
+                out[f"{tag}_{location}_{'inv' if inverse else 'fwd'}"] = {"w": w0, "out": w1.detach()}
+    torch.save(out, os.path.join(OUT, "hadamard_embedding.pt"))
+
+
 def gen_mxfp4():
     """quantization/utils/mxfp4_utils.py on EVERY bf16 bit pattern and every uint8 exponent."""
     from compressed_tensors.quantization.utils.mxfp4_utils import (
@@ -422,7 +442,7 @@ def gen_mxfp4():
 if __name__ == "__main__":
     only = sys.argv[2] if len(sys.argv) > 2 else None  # e.g. "mxfp4": regenerate one fixture
     for name, fn in (("int_quant", gen_int), ("fp8_quant", gen_fp8), ("nvfp4", gen_nvfp4), ("sparse", gen_sparse),
-                     ("hadamard", gen_hadamard), ("hadamard_online", gen_hadamard_online), ("hadamard_randomize", gen_hadamard_randomize), ("mxfp4", gen_mxfp4), ("marlin24", gen_marlin24)):
+                     ("hadamard", gen_hadamard), ("hadamard_online", gen_hadamard_online), ("hadamard_randomize", gen_hadamard_randomize), ("hadamard_embedding", gen_hadamard_embedding), ("mxfp4", gen_mxfp4), ("marlin24", gen_marlin24)):
         if only is None or only == name:
             fn()
     for f in sorted(os.listdir(OUT)):

@@ -396,3 +396,17 @@ def test_randomized_hadamard(golden):
         else:
             assert_bit_equal(y, d["out"], name)
 
+
+def test_embedding_transforms(golden):
+    """transforms fused into an Embedding weight (transform/utils/matrix.py:121-126), float64 offline: bit-exact"""
+    from compressed_tensors_b200.transform import TransformArgs, TransformFactory, TransformScheme
+
+    for name, d in golden("hadamard_embedding").items():
+        tag, rest = name.split("_", 1)
+        location, direction = rest.rsplit("_", 1)
+        emb = torch.nn.Embedding(128, 128, dtype=torch.bfloat16).cuda()
+        scheme = TransformScheme(type="random-hadamard", head_dim=128,
+                                 apply=[TransformArgs(targets=["Embedding"], location=location, inverse=direction == "inv")])
+        tr = TransformFactory.from_scheme(scheme, name="t", seed=7).create_transform(emb, scheme.apply[0])
+        assert_bit_equal(tr(d["w"].cuda()).cpu(), d["out"], name)
+
