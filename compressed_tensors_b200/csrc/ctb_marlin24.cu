@@ -83,6 +83,56 @@ __global__ void __launch_bounds__(kMThreads) cutlass24_compress_kernel(const voi
     }
 }
 
+// The inverse (semi_structured_conversions.py:216-308): one thread per metadata element reads it from its
+// reordered place, and writes its 16 dense elements: the two kept values of every run at the positions their 2-bit
+// indices name (the second write wins when both name the same position, as in the reference's scatter), zeros
+// elsewhere.
+template <int ES>
+__global__ void __launch_bounds__(kMThreads) cutlass24_decompress_kernel(const void *sparse, const int16_t *meta_reordered, int64_t m, int64_t k2, void *dense) {
+    const int64_t ncols = k2 / 8, total = m * ncols;
+    const bool small = total < 0x7FFFFFFF;
+    for (int64_t t = (int64_t)blockIdx.x * kMThreads + threadIdx.x; t < total; t += (int64_t)gridDim.x * kMThreads) {
+        const int64_t r = small ? (int64_t)((uint32_t)t / (uint32_t)ncols) : t / ncols, c = t - r * ncols;
+        const int rl = (int)(r & 63);
+        int dl = (rl & 1) * 2 + ((rl & 7) >> 2) + (((rl & 3) >> 1) << 5) + ((rl >> 3) << 2);
+        int64_t dc = c;
+        const int swap = (int)(((dl & 1) == 0) && ((dc & 1) == 1)) - (int)(((dl & 1) == 1) && ((dc & 1) == 0));
+        dl += swap;
+        dc -= swap;
+        const uint32_t elem = (uint16_t)meta_reordered[(dc >> 1) * m * 2 + ((r & ~(int64_t)63) + dl) * 2 + (dc & 1)];
+        uint32_t kept[8];
+        if constexpr (ES == 1) {
+            const uint2 w = *reinterpret_cast<const uint2 *>((const char *)sparse + (r * k2 + c * 8));
+#pragma unroll
+            for (int i = 0; i < 8; ++i) kept[i] = ((i < 4 ? w.x : w.y) >> (8 * (i & 3))) & 0xFFu;
+        } else {
+            const uint4 w = *reinterpret_cast<const uint4 *>((const char *)sparse + (r * k2 + c * 8) * 2);
+            const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) kept[i] = (ww[i >> 1] >> (16 * (i & 1))) & 0xFFFFu;
+        }
+        uint32_t v[16];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int i0 = (elem >> (4 * j)) & 3, i1 = (elem >> (4 * j + 2)) & 3;
+#pragma unroll
+            for (int p = 0; p < 4; ++p) v[4 * j + p] = p == i1 ? kept[2 * j + 1] : p == i0 ? kept[2 * j] : 0u;
+        }
+        if constexpr (ES == 1) {
+            uint4 o;
+            o.x = v[0] | (v[1] << 8) | (v[2] << 16) | (v[3] << 24);
+            o.y = v[4] | (v[5] << 8) | (v[6] << 16) | (v[7] << 24);
+            o.z = v[8] | (v[9] << 8) | (v[10] << 16) | (v[11] << 24);
+            o.w = v[12] | (v[13] << 8) | (v[14] << 16) | (v[15] << 24);
+            *reinterpret_cast<uint4 *>((char *)dense + (r * k2 * 2 + c * 16)) = o;
+        } else {
+            uint4 *o = reinterpret_cast<uint4 *>((char *)dense + (r * k2 * 2 + c * 16) * 2);
+            o[0] = make_uint4(v[0] | (v[1] << 16), v[2] | (v[3] << 16), v[4] | (v[5] << 16), v[6] | (v[7] << 16));
+            o[1] = make_uint4(v[8] | (v[9] << 16), v[10] | (v[11] << 16), v[12] | (v[13] << 16), v[14] | (v[15] << 16));
+        }
+    }
+}
+
 // utils/permutations_24.py:32-65: source position inside a 1024-element chunk for destination position d
 __device__ __forceinline__ int marlin24_perm(int d, int bits) {
     const int L = bits == 4 ? 8 : 4;
@@ -173,3 +223,18 @@ extern "C" int ctb_marlin24_pack_scales(const void *scale, int64_t n, int64_t gr
                                                                                                           grouped, (uint16_t *)out);
     return after_launch("marlin24_pack_scales_kernel");
 }
+
+extern "C" int ctb_cutlass24_decompress(const void *sparse, const int16_t *meta, int32_t dtype, int64_t rows, int64_t cols_sparse, void *out_dense,
+                                        void *stream) {
+    if (rows != 0 && cols_sparse != 0 && (!sparse || !meta || !out_dense)) return fail(CTB_EINVAL_NULL, "null buffer");
+    if (dtype != CTB_I8 && dtype != CTB_F16 && dtype != CTB_BF16) return fail(CTB_EINVAL_DTYPE, "values must be int8 codes, f16 or bf16");
+    if (rows < 0 || cols_sparse < 0) return fail(CTB_EINVAL_SHAPE, "negative shape");
+    if (rows % 64 != 0 || cols_sparse % 16 != 0) return fail(CTB_EINVAL_SHAPE, "rows must be divisible by 64 and the compacted columns by 16");
+    if (rows == 0 || cols_sparse == 0) return CTB_OK;
+    if (!aligned16(sparse) || !aligned16(out_dense)) return fail(CTB_EINVAL_ALIGN, "buffers must be 16-byte aligned");
+    const int grid = grid_for(rows * (cols_sparse / 8), kMThreads, 8);
+    if (dtype == CTB_I8) cutlass24_decompress_kernel<1><<<grid, kMThreads, 0, as_stream(stream)>>>(sparse, meta, rows, cols_sparse, out_dense);
+    else cutlass24_decompress_kernel<2><<<grid, kMThreads, 0, as_stream(stream)>>>(sparse, meta, rows, cols_sparse, out_dense);
+    return after_launch("cutlass24_decompress_kernel");
+}
+

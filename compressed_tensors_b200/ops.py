@@ -12,7 +12,7 @@ from ._lib import CODE_DTYPE, CODE_FP4X2, CODE_PACK32, DT, QFLOAT, QINT, QDesc, 
 __all__ = [
     "quantize", "dequantize", "fake_quantize", "minmax", "calculate_qparams", "generate_gparam",
     "mxfp4_round_pow2", "mxfp4_generate_scales", "mxfp4_convert_scales",
-    "cutlass24_compress", "marlin24_pack_weight", "marlin24_pack_scales",
+    "cutlass24_compress", "cutlass24_decompress", "marlin24_pack_weight", "marlin24_pack_scales",
     "pack_int32", "unpack_int32", "pack_fp4", "unpack_fp4", "pack_bitmasks", "unpack_bitmasks",
     "sparse24_mask", "sparse24_compress", "sparse24_decompress", "bitmask_compress", "bitmask_decompress", "hadamard",
     "absmax_quantize", "rotate_quantize_int4_batch", "unpack_dequantize_int4_batch", "tensor_table", "QINT", "QFLOAT",
@@ -360,6 +360,22 @@ def cutlass24_compress(dense):
     meta = torch.empty((rows, cols // 16), dtype=torch.int16, device=dense.device)
     check(lib().ctb_cutlass24_compress(ptr(dense), i32(DT[dense.dtype]), i64(rows), i64(cols), ptr(sparse), ptr(meta), stream_of(dense)))
     return sparse, meta
+
+
+def cutlass24_decompress(sparse, meta):
+    """utils/semi_structured_conversions.py:216 sparse_semi_structured_to_dense_cutlass (int16 reordered meta)."""
+    require_cuda(sparse, meta)
+    if sparse.dim() != 2 or meta.dim() != 2:
+        raise RuntimeError("Expected 2-dimensional sparse and meta tensors")
+    if meta.dtype is not torch.int16:
+        raise RuntimeError(f"Invalid datatype {meta.dtype} of meta matrix")
+    sparse, meta = _c(sparse), _c(meta)
+    rows, k2 = sparse.shape
+    if meta.shape[0] != rows or meta.shape[1] * 8 != k2:
+        raise RuntimeError(f"meta matrix of shape {tuple(meta.shape)} does not match sparse matrix of shape {tuple(sparse.shape)}")
+    dense = torch.empty((rows, 2 * k2), dtype=sparse.dtype, device=sparse.device)
+    check(lib().ctb_cutlass24_decompress(ptr(sparse), ptr(meta), i32(DT[sparse.dtype]), i64(rows), i64(k2), ptr(dense), stream_of(sparse)))
+    return dense
 
 
 def marlin24_pack_weight(sparse, num_bits):

@@ -236,6 +236,10 @@ int ctb_hadamard(const void *x, int32_t dtype, int64_t rows, int64_t cols, int32
  * out_sparse [rows, cols/2] (same element type) and out_meta int16 [rows, cols/16] in CUTLASS's reordered layout. */
 int ctb_cutlass24_compress(const void *dense, int32_t dtype, int64_t rows, int64_t cols, void *out_sparse,
                            int16_t *out_meta, void *stream);
+/* utils/semi_structured_conversions.py:216-308 sparse_semi_structured_to_dense_cutlass (int16 meta): the inverse,
+ * sparse [rows, cols_sparse] + reordered meta [rows, cols_sparse/8] -> dense [rows, 2 * cols_sparse]. */
+int ctb_cutlass24_decompress(const void *sparse, const int16_t *meta, int32_t dtype, int64_t rows, int64_t cols_sparse,
+                             void *out_dense, void *stream);
 /* marlin_24.py:208-249 marlin_permute_weights + pack_weight_24 (including the transpose and the shift to unsigned
  * of :186-193): sparse int8 codes [size_n, size_k] -> int32 [size_k/16, size_n*16/(32/num_bits)]. */
 int ctb_marlin24_pack_weight(const int8_t *sparse, int64_t size_n, int64_t size_k, int32_t num_bits, int32_t *out,

@@ -575,6 +575,29 @@ int orc_cutlass24_compress(const int8_t *dense, int64_t m, int64_t k, int8_t *sp
     return 0;
 }
 
+/* utils/semi_structured_conversions.py:216-308 sparse_semi_structured_to_dense_cutlass (int16 meta): undo the
+ * reordering, then scatter every kept value to the position its 2-bit index names; everything else is zero. */
+int orc_cutlass24_decompress(const int8_t *sparse, const int16_t *meta_reordered, int64_t m, int64_t k2, int8_t *dense) {
+    const int64_t ncols = k2 / 8, k = k2 * 2;
+    if (m % 32 || k2 % 8) return 1;
+    memset(dense, 0, (size_t)(m * k));
+    for (int64_t r = 0; r < m; ++r)
+        for (int64_t c = 0; c < ncols; ++c) {
+            int64_t dr = r / 64 * 64 + (r % 2) * 2 + (r % 8) / 4 + ((r % 32) % 4) / 2 * 32 + ((r % 64) / 8) * 4, dc = c;
+            const int tr = (dr % 2 == 0) && (dc % 2 == 1), bl = (dr % 2 == 1) && (dc % 2 == 0);
+            dr += tr - bl;
+            dc -= tr - bl;
+            const uint32_t elem = (uint16_t)meta_reordered[(dc / 2) * m * 2 + dr * 2 + dc % 2];
+            for (int j = 0; j < 4; ++j) {
+                const int i0 = (elem >> (4 * j)) & 3, i1 = (elem >> (4 * j + 2)) & 3;
+                int8_t *d = dense + r * k + (c * 4 + j) * 4;
+                d[i0] = sparse[r * k2 + (c * 4 + j) * 2];      /* scatter order: a later write wins */
+                d[i1] = sparse[r * k2 + (c * 4 + j) * 2 + 1];
+            }
+        }
+    return 0;
+}
+
 /* utils/permutations_24.py:32-65 */
 static void marlin24_perm(int bits, int *perm /* 1024 */) {
     int list[1024], n = 0;

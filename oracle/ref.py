@@ -247,6 +247,15 @@ def cutlass24_compress(q):
     return sparse, meta
 
 
+def cutlass24_decompress(sparse, meta):
+    sparse, meta = _c(sparse.to(torch.int8)), _c(meta)
+    m, k2 = sparse.shape
+    dense = torch.empty((m, 2 * k2), dtype=torch.int8)
+    rc = lib().orc_cutlass24_decompress(_p(sparse), _p(meta), ctypes.c_int64(m), ctypes.c_int64(k2), _p(dense))
+    assert rc == 0
+    return dense
+
+
 def marlin24_pack_weight(sparse, bits):
     sparse = _c(sparse.to(torch.int8))
     n, k2 = sparse.shape

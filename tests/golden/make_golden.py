@@ -368,12 +368,19 @@ def gen_marlin24():
             scale, zp = calculate_qparams(mn, mx, args)
             q = quantize(x=w.to(torch.float16), scale=scale.to(torch.float16), zero_point=None, args=args)
             sparse, meta = compress_weight_24(q)
+            from compressed_tensors.utils.semi_structured_conversions import sparse_semi_structured_to_dense_cutlass
+            dense_back = sparse_semi_structured_to_dense_cutlass(sparse, meta)
             scheme = QuantizationScheme(targets=["Linear"], weights=args)
             packed = Marlin24Compressor().compress({"l.weight": w.clone(), "l.weight_scale": scale.clone()}, {"l": scheme})
             out[f"w{bits}_{strategy}_{rows}x{cols}"] = {
                 "weight": w.to(torch.float16), "scale": scale, "bits": torch.tensor(bits), "group": torch.tensor(128 if strategy == "group" else 0),
-                "q": q.to(torch.int8), "sparse": sparse.to(torch.int8), "meta_reordered": meta,
+                "q": q.to(torch.int8), "sparse": sparse.to(torch.int8), "meta_reordered": meta, "dense_back": dense_back.to(torch.int8),
                 "weight_packed": packed["l.weight_packed"], "scale_packed": packed["l.scale_packed"], "meta": packed["l.meta"]}
+    from compressed_tensors.utils.permutations_24 import get_permutations_24
+    for bits in (4, 8):
+        perm, scale_perm, scale_perm_single = get_permutations_24(bits)
+        out[f"permutations_{bits}"] = {"perm": perm.to(torch.int16), "scale_perm": torch.tensor(scale_perm, dtype=torch.int16),
+                                       "scale_perm_single": torch.tensor(scale_perm_single, dtype=torch.int16)}
     torch.save(out, os.path.join(OUT, "marlin24.pt"))
 
 

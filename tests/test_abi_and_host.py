@@ -225,3 +225,16 @@ def test_initialize_qparams_shapes_and_compressed_linear_parameters():
         CompressedLinear(8, 8)
     assert any("from_linear" in str(x.message) for x in w)
 
+
+def test_marlin24_permutation_tables(golden):
+    """utils/permutations_24.py:32-65"""
+    from compressed_tensors_b200.utils import get_permutations_24
+
+    for bits in (4, 8):
+        d = golden("marlin24")[f"permutations_{bits}"]
+        perm, scale_perm, scale_perm_single = get_permutations_24(bits)
+        assert torch.equal(perm.to(torch.int16), d["perm"])
+        assert scale_perm == d["scale_perm"].tolist() and scale_perm_single == d["scale_perm_single"].tolist()
+    with pytest.raises(ValueError):
+        get_permutations_24(3)
+

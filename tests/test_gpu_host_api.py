@@ -346,8 +346,16 @@ def test_marlin24_compressor(golden):
 
     comp = BaseCompressor.load_from_registry("marlin-24")
     assert isinstance(comp, Marlin24Compressor) and comp.compression_param_names == ("weight_packed", "scale_packed", "meta")
+    from compressed_tensors_b200.utils import sparse_semi_structured_from_dense_cutlass, sparse_semi_structured_to_dense_cutlass
+
     for name, d in golden("marlin24").items():
+        if name.startswith("permutations_"):
+            continue
         bits, group = int(d["bits"]), int(d["group"])
+        # the inverse conversion (semi_structured_conversions.py:216) on codes and on the 16-bit tensor
+        assert_bit_equal(ops.cutlass24_decompress(d["sparse"].cuda(), d["meta_reordered"].cuda()).cpu(), d["dense_back"], name)
+        s_h, m_h = sparse_semi_structured_from_dense_cutlass(d["q"].to(torch.float16))
+        assert_bit_equal(sparse_semi_structured_to_dense_cutlass(s_h, m_h).cpu(), d["dense_back"].to(torch.float16), name)
         args = QuantizationArgs(num_bits=bits, symmetric=True, strategy="group" if group else "channel", group_size=group or None)
         # the steps on the reference's intermediate tensors
         sparse, meta = ops.cutlass24_compress(d["q"].cuda())

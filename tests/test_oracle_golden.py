@@ -242,7 +242,10 @@ def test_mxfp4_scale_helpers_every_input(golden):
 def test_marlin24_steps(golden):
     """CUTLASS 2:4 compaction + reordered meta, tile permutation + packing, scale permutation (marlin_24.py:124-273)"""
     for name, d in golden("marlin24").items():
+        if name.startswith("permutations_"):
+            continue
         bits, group = int(d["bits"]), int(d["group"])
+        assert torch.equal(orc.cutlass24_decompress(d["sparse"], d["meta_reordered"]), d["dense_back"]), name
         sparse, meta = orc.cutlass24_compress(d["q"])
         assert torch.equal(sparse, d["sparse"]) and torch.equal(meta, d["meta_reordered"]), name
         assert torch.equal(orc.marlin24_pack_weight(sparse, bits), d["weight_packed"]), name
