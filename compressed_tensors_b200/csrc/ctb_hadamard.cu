@@ -162,6 +162,116 @@ __global__ void __launch_bounds__(kThreads) hadamard_rows_kernel(const void *x, 
     }
 }
 
+// weight_output rotation for 16-bit tensors and n = 32 .. 256: the butterflies run over ROWS, so a column is an
+// independent length-n transform.  A block takes a tile of n rows x 32*CPT columns; a warp owns a strip of 4*CPT
+// columns of it.  Row index bits 0-1 and 5+ of a lane's values live in registers, bits 2-4 across lanes
+// (lane = 4 * bits[2..4] + column part), so three of the log2(n) stages are shuffles and the rest register
+// arithmetic; every load instruction of a warp touches 8 rows x 32 (16) contiguous bytes and the block as a whole
+// 256 (128) contiguous bytes of each row.  CPT = 4 columns per lane in float, 2 in double (register budget).
+// Arithmetic and its order of roundings are those of hadamard_rows_kernel: signs before the transform (forward) or
+// after it (inverse), quotient by sqrt(n) correctly rounded in A, cast chain A -> float -> tensor dtype, +0.0.
+template <typename A, int XF, int LOG_HI>
+__global__ void __launch_bounds__(kThreads) hadamard_rows_fast_kernel(const void *x, int64_t rows, int64_t cols, const int8_t *signs, int inverse,
+                                                                       int normalize, void *out) {
+    constexpr int CPT = sizeof(A) == 8 ? 2 : 4, HI = 1 << LOG_HI, N = 32 * HI, TILE_COLS = 32 * CPT;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, r_mid = lane >> 2, cpart = lane & 3;
+    const int64_t col_tiles = (cols + TILE_COLS - 1) / TILE_COLS, tiles = (rows / N) * col_tiles;
+    // x / sqrt(N): exact reciprocal multiply when sqrt(N) is a power of two, otherwise reciprocal + one Markstein
+    // correction, which gives the correctly rounded quotient (the operands are far from the overflow / underflow ends)
+    const A sc = normalize ? (A)sqrt((double)N) : (A)1, rsc = (A)1 / sc;
+    for (int64_t t = blockIdx.x; t < tiles; t += gridDim.x) {
+        const int64_t tr = t / col_tiles, r0 = tr * N, c = (t - tr * col_tiles) * TILE_COLS + (warp * 4 + cpart) * CPT;
+        const bool live = c < cols;
+        A v[HI][4][CPT];
+#pragma unroll
+        for (int hi = 0; hi < HI; ++hi)
+#pragma unroll
+            for (int lo = 0; lo < 4; ++lo) {
+                const int rr = lo + 4 * r_mid + 32 * hi;
+                uint32_t w[2] = {0, 0};
+                if (live) {
+                    const char *p = (const char *)x + ((r0 + rr) * cols + c) * 2;
+                    if constexpr (CPT == 4) {
+                        const uint2 q = ld_stream8(p);
+                        w[0] = q.x;
+                        w[1] = q.y;
+                    } else {
+                        w[0] = ld_stream4(p);
+                    }
+                }
+                const A sg = (!inverse && signs) ? (A)signs[rr] : (A)1;
+#pragma unroll
+                for (int k = 0; k < CPT; ++k) {
+                    const uint32_t bits = (w[k >> 1] >> (16 * (k & 1))) & 0xFFFFu;
+                    const float f = XF == F_BF16 ? __uint_as_float(bits << 16) : __half2float(__ushort_as_half((unsigned short)bits));
+                    v[hi][lo][k] = (A)f * sg;
+                }
+            }
+        // register stages: row bits 0, 1 (lo) and 5.. (hi)
+#pragma unroll
+        for (int h = 1; h < 4; h <<= 1)
+#pragma unroll
+            for (int hi = 0; hi < HI; ++hi)
+#pragma unroll
+                for (int lo = 0; lo < 4; ++lo)
+                    if ((lo & h) == 0)
+#pragma unroll
+                        for (int k = 0; k < CPT; ++k) {
+                            const A a = v[hi][lo][k], b = v[hi][lo | h][k];
+                            v[hi][lo][k] = a + b;
+                            v[hi][lo | h][k] = a - b;
+                        }
+#pragma unroll
+        for (int h = 1; h < HI; h <<= 1)
+#pragma unroll
+            for (int hi = 0; hi < HI; ++hi)
+                if ((hi & h) == 0)
+#pragma unroll
+                    for (int lo = 0; lo < 4; ++lo)
+#pragma unroll
+                        for (int k = 0; k < CPT; ++k) {
+                            const A a = v[hi][lo][k], b = v[hi | h][lo][k];
+                            v[hi][lo][k] = a + b;
+                            v[hi | h][lo][k] = a - b;
+                        }
+        // shuffle stages: row bits 2, 3, 4 = lane bits 2, 3, 4
+#pragma unroll
+        for (int m = 4; m < 32; m <<= 1) {
+            const bool upper = (lane & m) != 0;
+#pragma unroll
+            for (int hi = 0; hi < HI; ++hi)
+#pragma unroll
+                for (int lo = 0; lo < 4; ++lo)
+#pragma unroll
+                    for (int k = 0; k < CPT; ++k) {
+                        const A mine = v[hi][lo][k], other = rq_shfl_xor<A>(mine, m);
+                        v[hi][lo][k] = upper ? other - mine : mine + other;
+                    }
+        }
+        if (!live) continue;
+#pragma unroll
+        for (int hi = 0; hi < HI; ++hi)
+#pragma unroll
+            for (int lo = 0; lo < 4; ++lo) {
+                const int rr = lo + 4 * r_mid + 32 * hi;
+                const float sg = (inverse && signs) ? (float)signs[rr] : 1.0f;
+                uint32_t bits[CPT];
+#pragma unroll
+                for (int k = 0; k < CPT; ++k) {
+                    const A tv = v[hi][lo][k];
+                    A q = tv * rsc;
+                    if constexpr (sizeof(A) == 8) q = fma(fma(-q, sc, tv), rsc, q);
+                    else q = fmaf(fmaf(-q, sc, tv), rsc, q);
+                    float f = (float)q * sg + 0.0f;  // exact zeros are +0.0 in the reference's matmul
+                    bits[k] = XF == F_BF16 ? (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(f)) : (uint32_t)__half_as_ushort(__float2half_rn(f));
+                }
+                char *p = (char *)out + ((r0 + rr) * cols + c) * 2;
+                if constexpr (CPT == 4) st_stream8(p, make_uint2(bits[0] | (bits[1] << 16), bits[2] | (bits[3] << 16)));
+                else st_stream4(p, bits[0] | (bits[1] << 16));
+            }
+    }
+}
+
 }  // namespace ctb
 
 // ------------------------------------------------------------------ fused calibrate + quantize + pack
@@ -542,6 +652,24 @@ extern "C" int ctb_hadamard(const void *x, int32_t dtype, int64_t rows, int64_t 
     if (side != 1) return fail(CTB_EINVAL_SHAPE, "side must be 0 (weight_input) or 1 (weight_output)");
     if (rows % n) return fail(CTB_EINVAL_SHAPE, "rows %lld are not a multiple of the Hadamard size %d", (long long)rows, n);
     if (n > 512) return fail(CTB_EUNSUPPORTED, "weight_output rotation is built for n <= 512");
+    if ((dtype == CTB_BF16 || dtype == CTB_F16) && (n == 32 || n == 64 || n == 128 || n == 256) && cols % 4 == 0 &&
+        (reinterpret_cast<uintptr_t>(x) & 7u) == 0 && (reinterpret_cast<uintptr_t>(out) & 7u) == 0) {
+        const bool f64 = precision == CTB_F64;
+        const int tile_cols = f64 ? 64 : 128;
+        const int fgrid = grid_for((rows / n) * cdiv(cols, tile_cols), 1, n <= 64 ? 4 : 2);
+#define CTB_HR(A_, XF_, LH_) hadamard_rows_fast_kernel<A_, XF_, LH_><<<fgrid, kThreads, 0, st>>>(x, rows, cols, signs, inverse, normalize, out)
+#define CTB_HR_N(A_, XF_)                                   \
+    if (n == 32) CTB_HR(A_, XF_, 0);                        \
+    else if (n == 64) CTB_HR(A_, XF_, 1);                   \
+    else if (n == 128) CTB_HR(A_, XF_, 2);                  \
+    else CTB_HR(A_, XF_, 3);
+        if (f64) {
+            if (dtype == CTB_BF16) { CTB_HR_N(double, F_BF16) } else { CTB_HR_N(double, F_F16) }
+        } else {
+            if (dtype == CTB_BF16) { CTB_HR_N(float, F_BF16) } else { CTB_HR_N(float, F_F16) }
+        }
+        return after_launch("hadamard_rows_fast_kernel");
+    }
     int64_t tiles = (rows / n) * cdiv(cols, 32);
     int grid = grid_for(tiles, 1, 2);
     if (precision == CTB_F64) {

@@ -348,6 +348,26 @@ def test_full_size_fp8_and_nvfp4_properties(ops):
     assert bool(((deq.float() - w.float()).abs() <= 1.01 * eff).all()), "inside one e2m1 step of the largest magnitudes"
 
 
+@pytest.mark.parametrize("n", [32, 64, 128, 256, 512])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_weight_output_rotation_sizes(ops, orc, n, dtype):
+    """rows-direction Hadamard (weight_output): every built size, both 16-bit dtypes, forward and inverse, with random
+    signs, on shapes whose column count is not a whole tile; float64 mode bit-exact against the oracle, float32 mode
+    within one step of the tensor dtype"""
+    g = torch.Generator().manual_seed(n)
+    signs = (torch.randint(0, 2, (n,), generator=g) * 2 - 1).to(torch.int8)
+    for rows, cols in ((n, 36), (2 * n, 200), (n, 4096)):
+        w = (torch.randn(rows, cols, generator=g) * 0.05).to(dtype)
+        for inverse in (False, True):
+            want = orc.hadamard(w, n, signs=signs, inverse=inverse, side=1)
+            got = ops.hadamard(w.cuda(), n, signs=signs.cuda(), inverse=inverse, side=1, precision=torch.float64).cpu()
+            assert_bit_equal(got, want, f"n={n} {rows}x{cols} inverse={inverse}")
+            fast = ops.hadamard(w.cuda(), n, signs=signs.cuda(), inverse=inverse, side=1, precision=torch.float32).cpu()
+            err = (fast.float() - want.float()).abs()
+            step = want.float().abs() * (2.0 ** -7 if dtype == torch.bfloat16 else 2.0 ** -10) + 1e-6
+            assert bool((err <= step).all()), f"n={n} float32 mode"
+
+
 def test_whole_shard_batch_equals_per_tensor(ops):
     """One grid over a list of tensors (ragged sizes, a tensor smaller than one warp of blocks) gives exactly
     the per-tensor results, in both rotation precisions, and decompress restores the same values."""
