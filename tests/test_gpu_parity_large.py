@@ -368,6 +368,31 @@ def test_weight_output_rotation_sizes(ops, orc, n, dtype):
             assert bool((err <= step).all()), f"n={n} float32 mode"
 
 
+def test_vector_pack_kernels_match_oracle(ops, orc):
+    """pack_to_int32 / unpack_from_int32 / pack_bitmasks / unpack_bitmasks on shapes that take the 16-bytes-per-thread
+    kernels, against the oracle, including codes outside the field range (whose reference result spills into the
+    neighbouring fields) and mask bytes other than 0 / 1"""
+    g = torch.Generator().manual_seed(3)
+    for bits in (4, 8):
+        half = 1 << (bits - 1)
+        q = torch.randint(-half, half, (96, 1024), generator=g, dtype=torch.int8)
+        if bits == 4:
+            q[5, 17], q[5, 18], q[40, 0], q[95, 1023] = 100, -100, 127, -128  # out of range for 4 bits
+        want = orc.pack_int32(q, bits)
+        got = ops.pack_int32(q.cuda(), bits)
+        assert_bit_equal(got.cpu(), want, f"pack {bits}")
+        inside = q.clamp(-half, half - 1)
+        words = orc.pack_int32(inside, bits)
+        assert_bit_equal(ops.unpack_int32(words.cuda(), bits, (96, 1024)).cpu(), inside, f"unpack {bits}")
+        assert_bit_equal(ops.unpack_int32(words.cuda(), bits, (96, 1024)).cpu(), orc.unpack_int32(words, bits, (96, 1024)), f"unpack vs oracle {bits}")
+    m = torch.randint(0, 3, (64, 2048), generator=g, dtype=torch.uint8) * 127  # 0, 127, 254: any non-zero byte is "set"
+    m[3] = 0
+    m[7] = 255
+    want = orc.pack_bitmasks(m.bool())
+    assert_bit_equal(ops.pack_bitmasks(m.bool().cuda()).cpu(), want, "pack_bitmasks")
+    assert_bit_equal(ops.unpack_bitmasks(want.cuda(), [64, 2048]).cpu(), m.bool(), "unpack_bitmasks")
+
+
 def test_whole_shard_batch_equals_per_tensor(ops):
     """One grid over a list of tensors (ragged sizes, a tensor smaller than one warp of blocks) gives exactly
     the per-tensor results, in both rotation precisions, and decompress restores the same values."""
