@@ -134,12 +134,69 @@ __device__ __forceinline__ uint32_t nearest_e2m1(float x, int dt) {
         float d = round_to_rt(dt, fabsf(round_to_rt(dt, a - grid[k])));
         if (d < bd) { bd = d; best = k; }
     }
-    return (uint32_t)best | ((__float_as_uint(x) >> 31) << 3);
+    return (uint32_t)best;
+}
+
+// torch.signbit of element i, from the stored bits (widening a negative f16 NaN to fp32 would drop its sign)
+__device__ __forceinline__ uint32_t stored_sign(const void *x, int dt, int64_t i) {
+    return dt == CTB_F32 ? reinterpret_cast<const uint32_t *>(x)[i] >> 31 : (uint32_t)(reinterpret_cast<const uint16_t *>(x)[i] >> 15);
 }
 
 __global__ void __launch_bounds__(kThreads) pack_fp4_kernel(const void *x, int dt, int64_t nbytes, uint8_t *out) {
     for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < nbytes; i += (int64_t)gridDim.x * kThreads)
-        out[i] = (uint8_t)(nearest_e2m1(load_f32(x, dt, 2 * i), dt) | (nearest_e2m1(load_f32(x, dt, 2 * i + 1), dt) << 4));
+        out[i] = (uint8_t)(nearest_e2m1(load_f32(x, dt, 2 * i), dt) | (stored_sign(x, dt, 2 * i) << 3) |
+                           (nearest_e2m1(load_f32(x, dt, 2 * i + 1), dt) << 4) | (stored_sign(x, dt, 2 * i + 1) << 7));
+}
+
+// 8 values -> 4 bytes per thread.  A magnitude that already sits on the e2m1 grid (the normal input: values the
+// quantizer produced) maps to its code from the float bits alone: 1, 1.5, 2, 3, 4, 6 are (bits >> 22) - 252 = 2..7
+// with an empty low mantissa; anything else takes the full nearest-magnitude search.
+template <int F>
+__global__ void __launch_bounds__(kThreads) pack_fp4_vec_kernel(const void *x, int dt, int64_t chunks, uint32_t *out) {
+    for (int64_t c = (int64_t)blockIdx.x * kThreads + threadIdx.x; c < chunks; c += (int64_t)gridDim.x * kThreads) {
+        const Raw8 raw = load_raw<F>(x, c);
+        float v[8];
+        decode8<F>(raw, v);
+        uint32_t word, k[8];
+        if constexpr (F == F_F32) {  // sign bits from the stored pattern -> bit 3 of every nibble
+            const uint32_t w[8] = {raw.a.x, raw.a.y, raw.a.z, raw.a.w, raw.b.x, raw.b.y, raw.b.z, raw.b.w};
+            word = 0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) word |= (w[i] >> 31) << (4 * i + 3);
+        } else {
+            const uint32_t w[4] = {raw.a.x, raw.a.y, raw.a.z, raw.a.w};
+            word = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) word |= (((w[i] >> 15) & 1u) << (8 * i + 3)) | ((w[i] >> 31) << (8 * i + 7));
+        }
+        bool all_on = true;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t ab = __float_as_uint(v[i]) & 0x7FFFFFFFu;
+            k[i] = (ab >> 22) - 252u;
+            bool on = (ab & 0x3FFFFFu) == 0 && k[i] - 2u <= 5u;
+            if (ab == 0) { k[i] = 0; on = true; }
+            if (ab == 0x3F000000u) { k[i] = 1; on = true; }
+            all_on = all_on && on;
+        }
+        if (!all_on) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) k[i] = nearest_e2m1(v[i], dt);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) word |= k[i] << (4 * i);
+        st_stream4(out + c, word);
+    }
+}
+
+// 4 bytes -> 8 values per thread
+template <int F>
+__global__ void __launch_bounds__(kThreads) unpack_fp4_vec_kernel(const uint8_t *a, int64_t chunks, void *out) {
+    for (int64_t c = (int64_t)blockIdx.x * kThreads + threadIdx.x; c < chunks; c += (int64_t)gridDim.x * kThreads) {
+        float v[8];
+        decode8<F_FP4X2>(load_raw<F_FP4X2>(a, c), v);
+        store8_float<F>(out, c, v);
+    }
 }
 
 // fp4_quantized.py:187-221
@@ -215,6 +272,15 @@ extern "C" int ctb_pack_fp4(const void *x, int32_t dtype, int64_t m, int64_t n, 
     if (n % 2 != 0) return fail(CTB_EINVAL_SHAPE, "tensor must have an even number of columns for nvfp4 compression");
     if (!is_float_dtype(dtype)) return fail(CTB_EINVAL_DTYPE, "fp4 values must be held in bf16, f16 or f32");
     if (m * n == 0) return CTB_OK;
+    if (m * n % 8 == 0 && aligned16(x) && (reinterpret_cast<uintptr_t>(out) & 3u) == 0) {
+        const int64_t chunks = m * n / 8;
+        const int grid = grid_for(chunks, kThreads, 16);
+        uint32_t *o = reinterpret_cast<uint32_t *>(out);
+        if (dtype == CTB_BF16) pack_fp4_vec_kernel<F_BF16><<<grid, kThreads, 0, as_stream(stream)>>>(x, dtype, chunks, o);
+        else if (dtype == CTB_F16) pack_fp4_vec_kernel<F_F16><<<grid, kThreads, 0, as_stream(stream)>>>(x, dtype, chunks, o);
+        else pack_fp4_vec_kernel<F_F32><<<grid, kThreads, 0, as_stream(stream)>>>(x, dtype, chunks, o);
+        return after_launch("pack_fp4_vec_kernel");
+    }
     pack_fp4_kernel<<<grid_for(m * n / 2, kThreads, 8), kThreads, 0, as_stream(stream)>>>(x, dtype, m * n / 2, out);
     return after_launch("pack_fp4_kernel");
 }
@@ -224,6 +290,14 @@ extern "C" int ctb_unpack_fp4(const uint8_t *packed, int64_t m, int64_t n, void 
     if (n % 2 != 0) return fail(CTB_EINVAL_SHAPE, "odd column count");
     if (!is_float_dtype(odt)) return fail(CTB_EINVAL_DTYPE, "output must be bf16, f16 or f32");
     if (m * n == 0) return CTB_OK;
+    if (m * n % 8 == 0 && aligned16(out) && (reinterpret_cast<uintptr_t>(packed) & 3u) == 0) {
+        const int64_t chunks = m * n / 8;
+        const int grid = grid_for(chunks, kThreads, 16);
+        if (odt == CTB_BF16) unpack_fp4_vec_kernel<F_BF16><<<grid, kThreads, 0, as_stream(stream)>>>(packed, chunks, out);
+        else if (odt == CTB_F16) unpack_fp4_vec_kernel<F_F16><<<grid, kThreads, 0, as_stream(stream)>>>(packed, chunks, out);
+        else unpack_fp4_vec_kernel<F_F32><<<grid, kThreads, 0, as_stream(stream)>>>(packed, chunks, out);
+        return after_launch("unpack_fp4_vec_kernel");
+    }
     unpack_fp4_kernel<<<grid_for(m * n / 2, kThreads, 8), kThreads, 0, as_stream(stream)>>>(packed, m * n / 2, out, odt);
     return after_launch("unpack_fp4_kernel");
 }

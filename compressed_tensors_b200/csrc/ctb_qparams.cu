@@ -73,6 +73,24 @@ __global__ void __launch_bounds__(kThreads) minmax_tile_kernel(const void *x, in
     }
 }
 
+// (b'') one block per [row_group x col_group] tile whose rows are whole 16-byte chunks (BLOCK strategy): 128-bit loads
+template <int F>
+__global__ void __launch_bounds__(kThreads) minmax_tile_vec_kernel(const void *x, int dt, int64_t rows, int64_t cols, int rg, int cg,
+                                                                    void *out_min, void *out_max) {
+    const int64_t tiles_c = cols / cg, tiles = (rows / rg) * tiles_c, cpr = cols / 8;
+    const int cpt = cg / 8, per_tile = rg * cpt;  // chunks per tile row / per tile
+    for (int64_t t = blockIdx.x; t < tiles; t += gridDim.x) {
+        const int64_t tr = t / tiles_c, base = tr * rg * cpr + (t - tr * tiles_c) * cpt;  // first chunk of the tile
+        float mn = FLT_MAX, mx = -FLT_MAX;
+        for (int i = threadIdx.x; i < per_tile; i += kThreads) {
+            const int r = i / cpt;
+            chunk_minmax<F>(x, base + (int64_t)r * cpr + (i - r * cpt), mn, mx);
+        }
+        block_minmax(mn, mx);
+        if (threadIdx.x == 0) { store_f32(out_min, dt, t, mn); store_f32(out_max, dt, t, mx); }
+    }
+}
+
 // (b') one block per row, 128-bit loads (CHANNEL / TOKEN: the tile is a whole row)
 template <int F>
 __global__ void __launch_bounds__(kThreads) minmax_row_kernel(const void *x, int dt, int64_t rows, int64_t cpr, void *out_min, void *out_max) {
@@ -233,6 +251,12 @@ extern "C" int ctb_minmax(const void *x, int32_t dt, int64_t rows, int64_t cols,
         }
     }
     int grid = grid_for((rows / rg) * (cols / cg), 1, 8);
+    if (cols % 8 == 0 && cg % 8 == 0 && aligned16(x) && rg * (cg / 8) < 0x7FFFFFFF) {
+        if (dt == CTB_BF16) minmax_tile_vec_kernel<F_BF16><<<grid, kThreads, 0, st>>>(x, dt, rows, cols, (int)rg, (int)cg, out_min, out_max);
+        else if (dt == CTB_F16) minmax_tile_vec_kernel<F_F16><<<grid, kThreads, 0, st>>>(x, dt, rows, cols, (int)rg, (int)cg, out_min, out_max);
+        else minmax_tile_vec_kernel<F_F32><<<grid, kThreads, 0, st>>>(x, dt, rows, cols, (int)rg, (int)cg, out_min, out_max);
+        return after_launch("minmax_tile_vec_kernel");
+    }
     minmax_tile_kernel<<<grid, kThreads, 0, st>>>(x, dt, rows, cols, rg, cg, out_min, out_max);
     return after_launch("minmax_tile_kernel");
 }

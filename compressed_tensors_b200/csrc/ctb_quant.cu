@@ -9,6 +9,7 @@
 //   generic : one output unit (element, packed word or fp4 byte) per thread, everything decided
 //             at run time; covers ragged shapes, any num_bits, g_idx column maps.
 #include "ctb_codec.cuh"
+#include "ctb_fastdiv.h"
 
 namespace ctb {
 
@@ -101,6 +102,194 @@ __global__ void __launch_bounds__(kThreads) qdq_vec8_kernel(const QArgs a) {
                 round8<QK>(v);
                 dequant8<TS>(v, q, has_zp);
                 store8_float<FOUT>(a.out, c, v);
+            }
+        }
+    }
+}
+
+// ---- lean tier: bf16 tensor, bf16 scale (compute dtype bf16), 32-bit chunk indices ---------------------------
+//
+// The vec8 kernel above spends as many instructions per chunk on bookkeeping (64-bit indices, a run-time switch
+// per qparam load, an IEEE reciprocal) as on arithmetic, and its quantize half works one float at a time.  This
+// tier keeps every step in packed bf16x2 registers:
+//   q    = bf16_rn(x * rcp(s))          rcp.approx is within 1 ulp, far inside the 2^-17 margin that keeps the
+//                                       rounded product equal to the rounded IEEE quotient of two bf16 numbers
+//   q   += zero_point (bf16 add), clamp to [q_min, q_max]
+//   INT : u = q + copysign(128, q) is exact-or-rounded-half-to-even to an integer because |u| lies in [128, 256],
+//         where a bf16 step is 1; the low byte of each half of u is |code| and its sign bit the code's sign.
+//         u - copysign(128, q) is the rounded value itself (fake quantize), with q's sign put back on a zero.
+//   FP8 : saturating e4m3 convert of q.
+// A chunk whose scale lies outside [2^-99, 2^99), an FP8 chunk that produced a NaN code, or an FP8 zero point
+// other than zero, is recomputed by the float path of the vec8 tier (lean_exact_chunk).
+struct LeanArgs {
+    const uint4 *in;
+    const uint16_t *scale;
+    const void *zp;
+    void *out;
+    uint32_t chunks, cpr, srs;
+    int shift;  // >= 0: qparam index = chunk >> shift; < 0: [row_group x col_group] blocks through the dividers
+    FastDiv by_cpr, by_row_group, by_col_chunks;
+    float qmin, qmax;
+    int zdt;
+};
+
+// One chunk by the float arithmetic of the vec8 tier, an element at a time (few registers: this is the rare path
+// and its register count would otherwise bound the occupancy of the whole kernel).
+template <int MODE, int QK, int FOUT>
+__device__ __noinline__ void lean_exact_chunk(const LeanArgs &a, uint32_t c, uint32_t qi) {
+    const bool has_zp = a.zp != nullptr;
+    const QP q = load_qp(a.scale, CTB_BF16, a.zp, a.zdt, nullptr, qi);
+    const uint16_t *x = reinterpret_cast<const uint16_t *>(a.in + c);
+    uint64_t acc = 0;
+#pragma unroll 1
+    for (int i = 0; i < 8; ++i) {
+        float t = scaled_div<CTB_BF16>(bf16_bits_to_f32(x[i]), q);       // forward.py:471-481
+        if (has_zp) t = round_to<CTB_BF16>(t + q.zp);
+        t = clamp_nan(t, a.qmin, a.qmax);
+        float val;
+        if constexpr (QK == QK_INT) {
+            val = rintf(t);
+            const uint32_t code = (uint32_t)(int)val;
+            if constexpr (FOUT == F_PACK4) acc |= (uint64_t)((code + 8u) & 0xFu) << (4 * i);
+            else if constexpr (FOUT == F_PACK8) acc |= (uint64_t)((code & 0xFFu) ^ 0x80u) << (8 * i);
+            else acc |= (uint64_t)(code & 0xFFu) << (8 * i);
+        } else {
+            uint32_t code = (uint32_t)__nv_cvt_float_to_fp8(t, __NV_SATFINITE, __NV_E4M3);
+            if (t != t) code = 0x7Fu | ((__float_as_uint(t) >> 24) & 0x80u);  // Tensor.to(float8_e4m3fn) keeps a NaN's sign
+            acc |= (uint64_t)code << (8 * i);
+            val = (t != t) ? t : e4m3_to_f32((uint8_t)code);
+        }
+        if constexpr (MODE == 2) {  // forward.py:504-512, every step rounded to bf16
+            float d = round_to<CTB_BF16>(val);
+            if (has_zp) d = round_to<CTB_BF16>(d - round_to<CTB_BF16>(q.zp));
+            store_f32(a.out, CTB_BF16, (int64_t)c * 8 + i, d * q.s);
+        }
+    }
+    if constexpr (MODE == 0) {
+        if constexpr (FOUT == F_PACK4) st_stream4((char *)a.out + (size_t)c * 4, (uint32_t)acc);
+        else st_stream8((char *)a.out + (size_t)c * 8, make_uint2((uint32_t)acc, (uint32_t)(acc >> 32)));
+    }
+}
+
+__device__ __forceinline__ float rcp_approx(float s) {
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(s));
+    return r;
+}
+
+// both halves of one packed word times r, each rounded once to bf16
+__device__ __forceinline__ __nv_bfloat162 scale_pair(uint32_t w, float r) {
+    return __floats2bfloat162_rn(__uint_as_float(w << 16) * r, __uint_as_float(w & 0xFFFF0000u) * r);
+}
+
+// like scale_pair, then "+ 0" (an all-zero zero point turns -0.0 into +0.0)
+__device__ __forceinline__ __nv_bfloat162 scale_pair_plus_zero(uint32_t w, float r) {
+    return __floats2bfloat162_rn(fmaf(__uint_as_float(w << 16), r, 0.0f), fmaf(__uint_as_float(w & 0xFFFF0000u), r, 0.0f));
+}
+
+// int8 codes of four sign-magnitude halves (two words of u = q + copysign(128, q)): |code| bytes, a 0x00 / 0xFF
+// sign byte each, then a per-byte negate whose "+ 1" cannot carry into the neighbouring byte
+__device__ __forceinline__ uint32_t int8_codes_of(uint32_t u0, uint32_t u1) {
+    const uint32_t mag = prmt_b32(u0, u1, 0x6420), neg = prmt_b32(u0, u1, 0xFDB9);
+    const uint32_t x = mag ^ neg;
+    return ((x & 0x7F7F7F7Fu) + (neg & 0x01010101u)) ^ (x & 0x80808080u);
+}
+
+constexpr int kLeanUnroll = 2;
+
+template <int MODE, int QK, int FOUT>
+__global__ void __launch_bounds__(kThreads) quant_bf16_lean_kernel(const __grid_constant__ LeanArgs a) {
+    const bool has_zp = a.zp != nullptr;
+    const __nv_bfloat162 lo2 = __float2bfloat162_rn(a.qmin), hi2 = __float2bfloat162_rn(a.qmax);
+    const uint32_t stride = gridDim.x * (uint32_t)(kThreads * kLeanUnroll);
+    for (uint32_t base = blockIdx.x * (uint32_t)(kThreads * kLeanUnroll) + threadIdx.x; base < a.chunks; base += stride) {
+        uint4 raw[kLeanUnroll];
+#pragma unroll
+        for (int u = 0; u < kLeanUnroll; ++u) {
+            const uint32_t c = base + u * kThreads;
+            if (c < a.chunks) raw[u] = ld_stream(a.in + c);
+        }
+#pragma unroll
+        for (int u = 0; u < kLeanUnroll; ++u) {
+            const uint32_t c = base + u * kThreads;
+            if (c >= a.chunks) break;
+            uint32_t qi;
+            if (a.shift >= 0) {
+                qi = c >> a.shift;
+            } else {
+                const uint32_t row = fastdiv(c, a.by_cpr);
+                qi = fastdiv(row, a.by_row_group) * a.srs + fastdiv(c - row * a.cpr, a.by_col_chunks);
+            }
+            const uint32_t sbits = __ldg(a.scale + qi);
+            const uint32_t w[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+            bool exact = ((sbits >> 7) & 0xFFu) - 28u > 197u;  // biased exponent outside [28, 225]
+            float zf = 0.0f;
+            if (has_zp) {
+                zf = load_f32(a.zp, a.zdt, qi);
+                if constexpr (QK == QK_FP8) exact = exact || zf != 0.0f;
+            }
+            if (exact) {
+                lean_exact_chunk<MODE, QK, FOUT>(a, c, qi);
+                continue;
+            }
+            const float r = rcp_approx(__uint_as_float(sbits << 16));
+            const __nv_bfloat162 z2 = __float2bfloat162_rn(zf);
+            if constexpr (QK == QK_INT && FOUT == F_PACK4) {
+                st_stream4((char *)a.out + (size_t)c * 4, quant_int4_word_bf16(w, r, has_zp, z2));
+            } else if constexpr (QK == QK_INT) {
+                const __nv_bfloat162 s2 = u32_as_bf162(sbits * 0x00010001u);
+                uint32_t o[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    __nv_bfloat162 q = scale_pair(w[k], r);
+                    if (has_zp) q = __hadd2(q, z2);
+                    // codes: a NaN input takes q_min (its integer cast is unspecified in the reference); fake: NaN stays NaN
+                    if constexpr (MODE == 0) q = __hmin2(__hmax2(q, lo2), hi2);
+                    else q = __hmin2_nan(__hmax2_nan(q, lo2), hi2);
+                    const uint32_t sign = bf162_as_u32(q) & 0x80008000u;
+                    const __nv_bfloat162 m = u32_as_bf162(sign | 0x43004300u);
+                    const __nv_bfloat162 uu = __hadd2(q, m);
+                    if constexpr (MODE == 0) {
+                        o[k] = bf162_as_u32(uu);
+                    } else {
+                        __nv_bfloat162 t = u32_as_bf162(bf162_as_u32(__hsub2(uu, m)) | sign);
+                        if (has_zp) t = __hsub2(t, z2);
+                        o[k] = bf162_as_u32(__hmul2(t, s2));
+                    }
+                }
+                if constexpr (MODE == 0) {
+                    uint32_t c0 = int8_codes_of(o[0], o[1]), c1 = int8_codes_of(o[2], o[3]);
+                    if constexpr (FOUT == F_PACK8) { c0 ^= 0x80808080u; c1 ^= 0x80808080u; }
+                    st_stream8((char *)a.out + (size_t)c * 8, make_uint2(c0, c1));
+                } else {
+                    st_stream((char *)a.out + (size_t)c * 16, make_uint4(o[0], o[1], o[2], o[3]));
+                }
+            } else {  // FP8
+                uint32_t code[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const uint32_t q = bf162_as_u32(has_zp ? scale_pair_plus_zero(w[k], r) : scale_pair(w[k], r));
+                    code[k] = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(__uint_as_float(q << 16), __uint_as_float(q & 0xFFFF0000u)),
+                                                                 __NV_SATFINITE, __NV_E4M3);
+                }
+                const uint32_t c0 = code[0] | (code[1] << 16), c1 = code[2] | (code[3] << 16);
+                if constexpr (MODE == 0) {
+                    // a NaN code (0x7F under the sign bit) must carry its input's sign: rare, take the float path
+                    if (((((c0 & 0x7F7F7F7Fu) + 0x01010101u) | ((c1 & 0x7F7F7F7Fu) + 0x01010101u)) & 0x80808080u) != 0) {
+                        lean_exact_chunk<MODE, QK, FOUT>(a, c, qi);
+                        continue;
+                    }
+                    st_stream8((char *)a.out + (size_t)c * 8, make_uint2(c0, c1));
+                } else {
+                    const float s = __uint_as_float(sbits << 16);
+                    uint32_t o[4];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const float2 f = __half22float2(__half2(__nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)code[k], __NV_E4M3)));
+                        o[k] = bf162_as_u32(__floats2bfloat162_rn(f.x * s, f.y * s));
+                    }
+                    st_stream((char *)a.out + (size_t)c * 16, make_uint4(o[0], o[1], o[2], o[3]));
+                }
             }
         }
     }
@@ -349,6 +538,37 @@ static int dispatch_vec8(int mode, const QArgs &a, cudaStream_t st, bool *handle
     return CTB_OK;
 }
 
+template <int MODE, int QK, int FOUT>
+static int launch_lean(const LeanArgs &l, cudaStream_t st) {
+    // 40 to 47 registers: five or six resident blocks per SM; 12 per SM measured fastest for every instantiation
+    quant_bf16_lean_kernel<MODE, QK, FOUT><<<grid_for(l.chunks, (int64_t)kThreads * kLeanUnroll, 12), kThreads, 0, st>>>(l);
+    return after_launch("quant_bf16_lean_kernel");
+}
+
+// bf16 tensor with a bf16 scale: quantize to packed int4 / int8 / e4m3 codes, or fake-quantize back to bf16
+static int dispatch_lean(int mode, const QArgs &a, cudaStream_t st, bool *handled) {
+    *handled = false;
+    if (a.xdt != CTB_BF16 || a.sdt != CTB_BF16 || a.gs || a.chunks >= (1LL << 31) || a.srs >= (1LL << 31)) return CTB_OK;
+    if (!(mode == 0 || (mode == 2 && a.fout == F_BF16)) || a.qk == QK_FP4) return CTB_OK;
+    LeanArgs l{};
+    l.in = (const uint4 *)a.in; l.scale = (const uint16_t *)a.scale; l.zp = a.zp; l.out = a.out;
+    l.chunks = (uint32_t)a.chunks; l.cpr = (uint32_t)a.cpr; l.srs = (uint32_t)a.srs;
+    l.shift = a.gshift >= 3 ? a.gshift - 3 : -1;
+    l.by_cpr = make_fastdiv((uint32_t)a.cpr);
+    l.by_row_group = make_fastdiv((uint32_t)a.row_group);
+    l.by_col_chunks = make_fastdiv((uint32_t)(a.col_group / 8));
+    l.qmin = a.qmin; l.qmax = a.qmax; l.zdt = a.zdt;
+    *handled = true;
+    if (mode == 0 && a.qk == QK_INT && a.fout == F_PACK4) return launch_lean<0, QK_INT, F_PACK4>(l, st);
+    if (mode == 0 && a.qk == QK_INT && a.fout == F_PACK8) return launch_lean<0, QK_INT, F_PACK8>(l, st);
+    if (mode == 0 && a.qk == QK_INT && a.fout == F_I8) return launch_lean<0, QK_INT, F_I8>(l, st);
+    if (mode == 0 && a.qk == QK_FP8 && a.fout == F_E4M3) return launch_lean<0, QK_FP8, F_E4M3>(l, st);
+    if (mode == 2 && a.qk == QK_INT) return launch_lean<2, QK_INT, F_BF16>(l, st);
+    if (mode == 2 && a.qk == QK_FP8) return launch_lean<2, QK_FP8, F_BF16>(l, st);
+    *handled = false;
+    return CTB_OK;
+}
+
 static int run(int mode, const ctb_qdesc *d, const void *in, const void *scale, const void *zp,
                const int32_t *g_idx, const float *gs, void *out, void *stream) {
     int rc = validate(d, in, scale, out, mode);
@@ -391,6 +611,8 @@ static int run(int mode, const ctb_qdesc *d, const void *in, const void *scale, 
             return after_launch("dequant_fp4_g16_bf16_kernel");
         }
         bool handled = false;
+        rc = dispatch_lean(mode, a, st, &handled);
+        if (handled) return rc;
         rc = dispatch_vec8(mode, a, st, &handled);
         if (handled) return rc;
     }

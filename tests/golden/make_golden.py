@@ -446,10 +446,29 @@ def gen_mxfp4():
     torch.save(out, os.path.join(OUT, "mxfp4.pt"))
 
 
+def gen_fp4_pack_all():
+    """pack_fp4_to_uint8 on EVERY bf16 and f16 bit pattern (off-grid magnitudes, ties, infinities, NaNs) and on a
+    float32 sweep; unpack_fp4_from_uint8 on every byte, in the three dense dtypes."""
+    bits = torch.arange(65536, dtype=torch.int32).to(torch.uint16).reshape(256, 256)
+    gen = torch.Generator().manual_seed(11)
+    f32 = torch.cat([torch.linspace(-7, 7, 4001), torch.randn(4191, generator=gen) * 3]).reshape(64, 128)
+    every_byte = torch.arange(256, dtype=torch.int32).to(torch.uint8).reshape(16, 16)
+    out = {
+        "bf16_packed": pack_fp4_to_uint8(bits.view(torch.bfloat16)),
+        "f16_packed": pack_fp4_to_uint8(bits.view(torch.float16)),
+        "f32": f32, "f32_packed": pack_fp4_to_uint8(f32),
+        "unpacked_bf16": unpack_fp4_from_uint8(every_byte, 16, 32, dtype=torch.bfloat16),
+        "unpacked_f16": unpack_fp4_from_uint8(every_byte, 16, 32, dtype=torch.float16),
+        "unpacked_f32": unpack_fp4_from_uint8(every_byte, 16, 32, dtype=torch.float32),
+    }
+    torch.save(out, os.path.join(OUT, "fp4_pack_all.pt"))
+
+
 if __name__ == "__main__":
     only = sys.argv[2] if len(sys.argv) > 2 else None  # e.g. "mxfp4": regenerate one fixture
     for name, fn in (("int_quant", gen_int), ("fp8_quant", gen_fp8), ("nvfp4", gen_nvfp4), ("sparse", gen_sparse),
-                     ("hadamard", gen_hadamard), ("hadamard_online", gen_hadamard_online), ("hadamard_randomize", gen_hadamard_randomize), ("hadamard_embedding", gen_hadamard_embedding), ("mxfp4", gen_mxfp4), ("marlin24", gen_marlin24)):
+                     ("hadamard", gen_hadamard), ("hadamard_online", gen_hadamard_online), ("hadamard_randomize", gen_hadamard_randomize), ("hadamard_embedding", gen_hadamard_embedding), ("mxfp4", gen_mxfp4), ("marlin24", gen_marlin24),
+                     ("fp4_pack_all", gen_fp4_pack_all)):
         if only is None or only == name:
             fn()
     for f in sorted(os.listdir(OUT)):

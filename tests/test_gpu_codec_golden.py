@@ -237,6 +237,37 @@ def test_mxfp4_scale_helpers_every_input(golden, ops):
         assert_bit_equal(convert_mxfp4_exp_scale(e, dt).cpu(), d["all_exponents"][key], key)
 
 
+def test_fp4_pack_every_16bit_input(golden, ops):
+    """pack_fp4_to_uint8 on all 65536 bf16 and f16 bit patterns and a float32 sweep; unpack on every byte; both the
+    8-values-per-thread kernels and (odd element counts, unaligned views) the scalar ones"""
+    d = golden("fp4_pack_all")
+    bits = torch.arange(65536, dtype=torch.int32).to(torch.uint16).reshape(256, 256)
+    for key, dt in (("bf16", torch.bfloat16), ("f16", torch.float16)):
+        x = bits.view(dt).cuda()
+        assert torch.equal(ops.pack_fp4(x).cpu(), d[key + "_packed"]), key
+        assert torch.equal(ops.pack_fp4(x[:, :254].contiguous()).cpu(), d[key + "_packed"][:, :127]), key + " scalar kernel"
+    assert torch.equal(ops.pack_fp4(d["f32"].cuda()).cpu(), d["f32_packed"])
+    assert torch.equal(ops.pack_fp4(d["f32"][:, :126].contiguous().cuda()).cpu(), d["f32_packed"][:, :63])
+    every_byte = torch.arange(256, dtype=torch.int32).to(torch.uint8).reshape(16, 16).cuda()
+    for key, dt in (("bf16", torch.bfloat16), ("f16", torch.float16), ("f32", torch.float32)):
+        assert_bit_equal(ops.unpack_fp4(every_byte, 16, 32, dtype=dt).cpu(), d["unpacked_" + key], key)
+        assert_bit_equal(ops.unpack_fp4(every_byte[:1, :3].contiguous(), 1, 6, dtype=dt).cpu(), d["unpacked_" + key].reshape(-1)[:6].reshape(1, 6), key)
+
+
+def test_minmax_tiles_match_oracle(ops):
+    """BLOCK-strategy min / max: tiles whose rows are whole 16-byte chunks (vector kernel) and tiles that are not"""
+    from oracle import ref as orc
+
+    g = torch.Generator().manual_seed(21)
+    for dt in (torch.bfloat16, torch.float16, torch.float32):
+        x = torch.randn(256, 384, generator=g).to(dt)
+        for rg, cg in ((128, 128), (64, 32), (16, 8), (256, 96), (2, 384), (32, 4), (8, 12)):
+            mn, mx = ops.minmax(x.cuda(), rg, cg)
+            wmn, wmx = orc.minmax(x, rg, cg)
+            assert_bit_equal(mn.cpu(), wmn, f"min {dt} {rg}x{cg}")
+            assert_bit_equal(mx.cpu(), wmx, f"max {dt} {rg}x{cg}")
+
+
 def test_empty_and_degenerate_tensors(ops):
     """a tensor with no elements has no storage (null pointer): every codec returns an empty result of the right
     shape instead of raising, as the reference's tensor expressions do; all-zero and all-dense tensors round-trip"""

@@ -420,3 +420,75 @@ def test_whole_shard_batch_equals_per_tensor(ops):
     torch.cuda.synchronize()
     for i in range(len(ws)):
         assert_bit_equal(graphed.packed[i].cpu(), exact.packed[i].cpu(), "graph replay")
+
+
+def _same_bits_or_both_nan(a, b, what):
+    assert a.dtype == b.dtype and tuple(a.shape) == tuple(b.shape), what
+    if a.dtype == torch.float8_e4m3fn:
+        ba, bb = a.view(torch.uint8), b.view(torch.uint8)
+        ok = ba == bb  # e4m3 NaN codes carry the input's sign: compared as bits
+    else:
+        from tests.helpers import bits_of
+        ok = (bits_of(a) == bits_of(b)) | (a.float().isnan() & b.float().isnan())
+    bad = (~ok).flatten().nonzero().flatten()
+    assert bad.numel() == 0, f"{what}: {bad.numel()} differ; first at {int(bad[0])}: {a.flatten()[int(bad[0])].item()!r} vs {b.flatten()[int(bad[0])].item()!r}"
+
+
+def test_bf16_quantize_and_fake_quantize_kernels_match_oracle(ops, orc):
+    """quantize (packed int4 / int8 / e4m3 codes) and fake_quantize of a bf16 tensor with bf16 scales, the path that
+    stays in packed bf16x2 arithmetic, against the oracle: rounding ties, both clamp ends, -0.0 results, infinities,
+    NaNs where the reference defines the result, zero points, scales outside the fast range (tiny, huge, zero,
+    infinite, NaN), GROUP / CHANNEL / BLOCK layouts with power-of-two and other group sizes"""
+    g = torch.Generator().manual_seed(77)
+    rows, cols = 192, 768
+    base = torch.randn(rows, cols, generator=g) * 0.02
+    layouts = [(1, 128, "group128"), (1, 96, "group96"), (1, cols, "channel"), (64, 96, "block64x96"), (rows, cols, "tensor")]
+    for rg, cg, name in layouts:
+        srs = cols // cg
+        for qtype, bits in ((orc.QINT, 4), (orc.QINT, 8), (orc.QINT, 6), (orc.QFLOAT, 8)):
+            is_int = qtype == orc.QINT
+            x = base.clone()
+            mn, mx = orc.minmax(x.to(torch.bfloat16), rg, cg)
+            scale, _ = orc.calculate_qparams(mn, mx, qtype=qtype, bits=bits, symmetric=True)
+            sf = scale.float().reshape(rows // rg, srs)
+            # plant, per row-group 0 / qparam 0..: ties, clamp ends, signed zeros, infinities
+            half = (1 << (bits - 1)) if is_int else 448
+            s00 = float(sf[0, 0])
+            ks = torch.arange(-half - 2, half + 2, dtype=torch.float32)
+            plant = torch.cat([(ks + 0.5) * s00, ks * s00, torch.tensor([-0.0, 0.0, -1e-9, 1e-9, float("inf"), float("-inf")])])
+            n_plant = min(plant.numel(), cg)
+            x[0, :n_plant] = plant[:n_plant]
+            special = [1e-38, 2.0 ** 100]        # outside the fast range: recomputed by the float path
+            if not is_int:
+                special += [0.0, float("inf"), float("nan")]
+            flat = scale.reshape(-1).clone()
+            for i, v in enumerate(special):
+                if flat.numel() > 2 + i:
+                    flat[2 + i] = v
+            scale = flat.reshape(scale.shape)
+            xb = x.to(torch.bfloat16)
+            if not is_int:
+                xb[1, 5], xb[1, 6] = float("nan"), -float("nan")
+            zps = [None, torch.zeros(scale.shape, dtype=torch.int8 if is_int else torch.float8_e4m3fn)]
+            if is_int:
+                zps.append(torch.randint(-half // 2, half // 2, scale.shape, generator=g, dtype=torch.int8))
+            else:
+                nz = torch.zeros(scale.shape, dtype=torch.float32)
+                nz.reshape(-1)[0] = 2.0  # an fp8 zero point other than zero: float path
+                zps.append(nz.to(torch.float8_e4m3fn))
+            for zi, zp in enumerate(zps):
+                kw = dict(qtype=qtype, bits=bits, col_group=cg, row_group=rg, scale_row_stride=srs)
+                dz = None if zp is None else zp.cuda()
+                what = f"{name} bits={bits} {'int' if is_int else 'fp8'} zp#{zi}"
+                code_dt = torch.int8 if is_int else torch.float8_e4m3fn
+                want = orc.quantize(xb, scale, zp, out_dtype=code_dt, **kw)
+                got = ops.quantize(xb.cuda(), scale.cuda(), dz, out_dtype=code_dt, **kw)
+                _same_bits_or_both_nan(got.cpu(), want, "quantize " + what)
+                if is_int and bits in (4, 8) and rg == 1:
+                    words = ops.quantize(xb.cuda(), scale.cuda(), dz, codec="pack32", **kw)
+                    assert_bit_equal(words.cpu(), orc.pack_int32(want, bits), "pack32 " + what)
+                xf = xb.clone()
+                xf[2, 3] = float("nan")  # fake quantize: a NaN stays a NaN
+                wantf = orc.fake_quantize(xf, scale, zp, out_dtype=torch.bfloat16, **kw)
+                gotf = ops.fake_quantize(xf.cuda(), scale.cuda(), dz, out_dtype=torch.bfloat16, **kw)
+                _same_bits_or_both_nan(gotf.cpu(), wantf, "fake_quantize " + what)

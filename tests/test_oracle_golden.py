@@ -239,6 +239,18 @@ def test_mxfp4_scale_helpers_every_input(golden):
         assert_bit_equal(orc.mxfp4_convert_scales(e, dt), d["all_exponents"][key], key)
 
 
+def test_fp4_pack_every_16bit_input(golden):
+    """pack_fp4_to_uint8 on all 65536 bf16 and f16 bit patterns and a float32 sweep; unpack on every byte"""
+    d = golden("fp4_pack_all")
+    bits = torch.arange(65536, dtype=torch.int32).to(torch.uint16).reshape(256, 256)
+    assert torch.equal(orc.pack_fp4(bits.view(torch.bfloat16)), d["bf16_packed"])
+    assert torch.equal(orc.pack_fp4(bits.view(torch.float16)), d["f16_packed"])
+    assert torch.equal(orc.pack_fp4(d["f32"]), d["f32_packed"])
+    every_byte = torch.arange(256, dtype=torch.int32).to(torch.uint8).reshape(16, 16)
+    for key, dt in (("bf16", torch.bfloat16), ("f16", torch.float16), ("f32", torch.float32)):
+        assert_bit_equal(orc.unpack_fp4(every_byte, 16, 32, dtype=dt), d["unpacked_" + key], key)
+
+
 def test_marlin24_steps(golden):
     """CUTLASS 2:4 compaction + reordered meta, tile permutation + packing, scale permutation (marlin_24.py:124-273)"""
     for name, d in golden("marlin24").items():

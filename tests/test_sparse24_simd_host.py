@@ -88,3 +88,18 @@ def test_random(simd):
     _check(simd, torch.randint(-4, 5, (512, 1024), generator=g, dtype=torch.int8))  # many ties
     _check(simd, torch.randint(0, 65536, (256, 1024), generator=g, dtype=torch.int32).to(torch.uint16).view(torch.bfloat16))
     _check(simd, (torch.randint(-3, 4, (256, 1024), generator=g) * 0.25).to(torch.bfloat16))
+
+
+def test_fastdiv_matches_integer_division(tmp_path):
+    """csrc/ctb_fastdiv.h (the index arithmetic of the BLOCK-strategy kernels): every divisor up to 4096, powers of
+    two and their neighbours, large divisors, on random 31-bit numerators and on the edges of every quotient step"""
+    so = tmp_path / "libfastdiv.so"
+    subprocess.run(["/usr/bin/g++", "-O2", "-shared", "-fPIC", "-std=c++17", "-I", str(ROOT / "compressed_tensors_b200" / "csrc"),
+                    str(ROOT / "tests" / "fastdiv_host.cpp"), "-o", str(so)], check=True)
+    lib = ctypes.CDLL(str(so))
+    lib.fastdiv_mismatches.restype = ctypes.c_int64
+    g = torch.Generator().manual_seed(5)
+    ns = torch.randint(0, 2 ** 31, (4096,), generator=g, dtype=torch.int64).to(torch.int32).contiguous()
+    divisors = list(range(1, 4097)) + [2 ** k + o for k in range(12, 31) for o in (-1, 0, 1)] + [2 ** 31 - 1, 1000003, 14336 // 8, 28672]
+    for d in divisors:
+        assert lib.fastdiv_mismatches(ctypes.c_uint32(d), ctypes.c_void_p(ns.data_ptr()), ctypes.c_int64(ns.numel())) == 0, d
