@@ -387,6 +387,21 @@ __device__ __forceinline__ void quant_prepare8(float (&v)[8], const QP &q, bool 
     }
 }
 
+// the same steps for one element with its own qparam (activation-ordered groups: every column names its group)
+template <int T>
+__device__ __forceinline__ float quant_prepare1(float x, const QP &q, bool has_zp, float qmin, float qmax) {
+    float t = scaled_div<T>(x, q);
+    if (has_zp) t = round_to<T>(t + q.zp);
+    return clamp_nan(t, qmin, qmax);
+}
+
+template <int TS>
+__device__ __forceinline__ float dequant1(float v, const QP &q, bool has_zp) {
+    float t = round_to<TS>(v);
+    if (has_zp) t = round_to<TS>(t - round_to<TS>(q.zp));
+    return round_to<TS>(t * q.s);
+}
+
 // forward.py:504-512: x_q.to(scale.dtype), subtract zero point, multiply by scale; all in Ts.
 template <int TS>
 __device__ __forceinline__ void dequant8(float (&v)[8], const QP &q, bool has_zp) {

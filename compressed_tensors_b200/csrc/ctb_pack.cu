@@ -148,43 +148,41 @@ __global__ void __launch_bounds__(kThreads) pack_fp4_kernel(const void *x, int d
                            (nearest_e2m1(load_f32(x, dt, 2 * i + 1), dt) << 4) | (stored_sign(x, dt, 2 * i + 1) << 7));
 }
 
-// 8 values -> 4 bytes per thread.  A magnitude that already sits on the e2m1 grid (the normal input: values the
-// quantizer produced) maps to its code from the float bits alone: 1, 1.5, 2, 3, 4, 6 are (bits >> 22) - 252 = 2..7
-// with an empty low mantissa; anything else takes the full nearest-magnitude search.
+// 8 values -> 4 bytes per thread.  The hardware e2m1 convert gives the code of a value that already sits on the
+// grid (the normal input: values the quantizer produced), sign bit included; whether all eight did is checked by
+// decoding the codes again and comparing in f16.  A float that only rounds to a grid value in f16 is so close to it
+// that it is its nearest grid value under any rounding of the distances, so it may pass; everything else (off-grid
+// magnitudes, infinities, NaNs) takes the reference's nearest-magnitude search.
 template <int F>
 __global__ void __launch_bounds__(kThreads) pack_fp4_vec_kernel(const void *x, int dt, int64_t chunks, uint32_t *out) {
     for (int64_t c = (int64_t)blockIdx.x * kThreads + threadIdx.x; c < chunks; c += (int64_t)gridDim.x * kThreads) {
         const Raw8 raw = load_raw<F>(x, c);
         float v[8];
         decode8<F>(raw, v);
-        uint32_t word, k[8];
-        if constexpr (F == F_F32) {  // sign bits from the stored pattern -> bit 3 of every nibble
-            const uint32_t w[8] = {raw.a.x, raw.a.y, raw.a.z, raw.a.w, raw.b.x, raw.b.y, raw.b.z, raw.b.w};
-            word = 0;
+        uint32_t word = 0, diff = 0;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) word |= (w[i] >> 31) << (4 * i + 3);
-        } else {
-            const uint32_t w[4] = {raw.a.x, raw.a.y, raw.a.z, raw.a.w};
-            word = 0;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) word |= (((w[i] >> 15) & 1u) << (8 * i + 3)) | ((w[i] >> 31) << (8 * i + 7));
+        for (int k = 0; k < 4; ++k) {
+            const uint32_t code = (uint32_t)__nv_cvt_float2_to_fp4x2(make_float2(v[2 * k], v[2 * k + 1]), __NV_E2M1, cudaRoundNearest);
+            const __half2 back = __half2(__nv_cvt_fp4x2_to_halfraw2((__nv_fp4x2_storage_t)code, __NV_E2M1));
+            const __half2 xh = __floats2half2_rn(v[2 * k], v[2 * k + 1]);
+            diff |= *reinterpret_cast<const uint32_t *>(&back) ^ *reinterpret_cast<const uint32_t *>(&xh);
+            word |= code << (8 * k);
         }
-        bool all_on = true;
+        if (diff != 0) {
+            if constexpr (F == F_F32) {  // sign bits from the stored pattern -> bit 3 of every nibble
+                const uint32_t w[8] = {raw.a.x, raw.a.y, raw.a.z, raw.a.w, raw.b.x, raw.b.y, raw.b.z, raw.b.w};
+                word = 0;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const uint32_t ab = __float_as_uint(v[i]) & 0x7FFFFFFFu;
-            k[i] = (ab >> 22) - 252u;
-            bool on = (ab & 0x3FFFFFu) == 0 && k[i] - 2u <= 5u;
-            if (ab == 0) { k[i] = 0; on = true; }
-            if (ab == 0x3F000000u) { k[i] = 1; on = true; }
-            all_on = all_on && on;
+                for (int i = 0; i < 8; ++i) word |= (w[i] >> 31) << (4 * i + 3);
+            } else {
+                const uint32_t w[4] = {raw.a.x, raw.a.y, raw.a.z, raw.a.w};
+                word = 0;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) word |= (((w[i] >> 15) & 1u) << (8 * i + 3)) | ((w[i] >> 31) << (8 * i + 7));
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) word |= nearest_e2m1(v[i], dt) << (4 * i);
         }
-        if (!all_on) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) k[i] = nearest_e2m1(v[i], dt);
-        }
-#pragma unroll
-        for (int i = 0; i < 8; ++i) word |= k[i] << (4 * i);
         st_stream4(out + c, word);
     }
 }

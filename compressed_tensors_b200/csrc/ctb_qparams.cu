@@ -38,6 +38,84 @@ __device__ __forceinline__ void chunk_minmax(const void *x, int64_t chunk, float
     for (int i = 0; i < 8; ++i) { mn = fminf(mn, v[i]); mx = fmaxf(mx, v[i]); }
 }
 
+// ---- 16-bit element types: min / max stay packed two to a register (like fminf / fmaxf, a NaN operand is ignored)
+template <int F>
+__device__ __forceinline__ uint32_t min2(uint32_t a, uint32_t b) {
+    if constexpr (F == F_BF16) return bf162_as_u32(__hmin2(u32_as_bf162(a), u32_as_bf162(b)));
+    else { const __half2 r = __hmin2(*reinterpret_cast<__half2 *>(&a), *reinterpret_cast<__half2 *>(&b)); return *reinterpret_cast<const uint32_t *>(&r); }
+}
+template <int F>
+__device__ __forceinline__ uint32_t max2(uint32_t a, uint32_t b) {
+    if constexpr (F == F_BF16) return bf162_as_u32(__hmax2(u32_as_bf162(a), u32_as_bf162(b)));
+    else { const __half2 r = __hmax2(*reinterpret_cast<__half2 *>(&a), *reinterpret_cast<__half2 *>(&b)); return *reinterpret_cast<const uint32_t *>(&r); }
+}
+template <int F> struct Packed16 {  // +inf / -inf in both halves
+    static constexpr uint32_t kPosInf = F == F_BF16 ? 0x7F807F80u : 0x7C007C00u;
+    static constexpr uint32_t kNegInf = kPosInf | 0x80008000u;
+};
+
+// running packed min / max over one 8-element chunk
+template <int F, typename Index>
+__device__ __forceinline__ void chunk_minmax16(const void *x, Index chunk, uint32_t &mn2, uint32_t &mx2) {
+    const uint4 q = ld_stream(reinterpret_cast<const uint4 *>(x) + chunk);
+    mn2 = min2<F>(min2<F>(mn2, q.x), min2<F>(min2<F>(q.y, q.z), q.w));
+    mx2 = max2<F>(max2<F>(mx2, q.x), max2<F>(max2<F>(q.y, q.z), q.w));
+}
+
+// one register holding (min, -max) of both halves: a single packed min then reduces both at once
+template <int F>
+__device__ __forceinline__ uint32_t fold_minmax16(uint32_t mn2, uint32_t mx2) {
+    const uint32_t nmx = mx2 ^ 0x80008000u;
+    return min2<F>(prmt_b32(mn2, nmx, 0x5410), prmt_b32(mn2, nmx, 0x7632));
+}
+
+template <int F>
+__device__ __forceinline__ void unpack_minmax16(uint32_t mn2, uint32_t mx2, float &mn, float &mx) {
+    const uint32_t k = fold_minmax16<F>(mn2, mx2);
+    if constexpr (F == F_BF16) { mn = bf16_bits_to_f32(k & 0xFFFFu); mx = -bf16_bits_to_f32(k >> 16); }
+    else { const float2 f = half2_bits_to_float2(k); mn = f.x; mx = -f.y; }
+}
+
+// (a16) the group kernel for bf16 / f16: one chunk per lane, L lanes reduce one packed (min, -max) register.
+//       32-bit chunk indices (the host checks the range).
+template <int F, int L>
+__global__ void __launch_bounds__(kThreads) minmax_group16_kernel(const uint4 *x, uint32_t chunks, uint16_t *out_min, uint16_t *out_max) {
+    constexpr int kShift = L == 1 ? 0 : L == 2 ? 1 : L == 4 ? 2 : L == 8 ? 3 : L == 16 ? 4 : 5;
+    const uint32_t stride = gridDim.x * kThreads;
+    const uint32_t padded = (chunks + 31u) & ~31u;  // whole warps stay in the loop for the shuffles
+    for (uint32_t c = blockIdx.x * kThreads + threadIdx.x; c < padded; c += 2 * stride) {
+        const uint32_t c1 = c + stride;
+        uint32_t mn0 = Packed16<F>::kPosInf, mx0 = Packed16<F>::kNegInf, mn1 = mn0, mx1 = mx0;
+        if (c < chunks) chunk_minmax16<F>(x, c, mn0, mx0);
+        if (c1 < chunks) chunk_minmax16<F>(x, c1, mn1, mx1);
+        uint32_t k0 = fold_minmax16<F>(mn0, mx0), k1 = fold_minmax16<F>(mn1, mx1);
+#pragma unroll
+        for (int o = L >> 1; o > 0; o >>= 1) {
+            k0 = min2<F>(k0, __shfl_xor_sync(0xFFFFFFFFu, k0, o));
+            k1 = min2<F>(k1, __shfl_xor_sync(0xFFFFFFFFu, k1, o));
+        }
+        if ((c & (L - 1)) == 0) {
+            if (c < chunks) { out_min[c >> kShift] = (uint16_t)k0; out_max[c >> kShift] = (uint16_t)((k0 >> 16) ^ 0x8000u); }
+            if (c1 < chunks) { out_min[c1 >> kShift] = (uint16_t)k1; out_max[c1 >> kShift] = (uint16_t)((k1 >> 16) ^ 0x8000u); }
+        }
+    }
+}
+
+template <int F>
+static void launch_group16(int L, int grid, cudaStream_t st, const void *x, int64_t chunks, void *out_min, void *out_max) {
+    const uint4 *p = (const uint4 *)x;
+    uint16_t *mn = (uint16_t *)out_min, *mx = (uint16_t *)out_max;
+    const uint32_t n = (uint32_t)chunks;
+    switch (L) {
+    case 1: minmax_group16_kernel<F, 1><<<grid, kThreads, 0, st>>>(p, n, mn, mx); break;
+    case 2: minmax_group16_kernel<F, 2><<<grid, kThreads, 0, st>>>(p, n, mn, mx); break;
+    case 4: minmax_group16_kernel<F, 4><<<grid, kThreads, 0, st>>>(p, n, mn, mx); break;
+    case 8: minmax_group16_kernel<F, 8><<<grid, kThreads, 0, st>>>(p, n, mn, mx); break;
+    case 16: minmax_group16_kernel<F, 16><<<grid, kThreads, 0, st>>>(p, n, mn, mx); break;
+    default: minmax_group16_kernel<F, 32><<<grid, kThreads, 0, st>>>(p, n, mn, mx); break;
+    }
+}
+
 // (a) groups of 8*L consecutive elements inside a row, L a power of two <= 32: one chunk per lane,
 //     L lanes cooperate through shuffles.  Flat indexing: group g covers chunks [g*L, (g+1)*L).
 template <int F>
@@ -82,9 +160,25 @@ __global__ void __launch_bounds__(kThreads) minmax_tile_vec_kernel(const void *x
     for (int64_t t = blockIdx.x; t < tiles; t += gridDim.x) {
         const int64_t tr = t / tiles_c, base = tr * rg * cpr + (t - tr * tiles_c) * cpt;  // first chunk of the tile
         float mn = FLT_MAX, mx = -FLT_MAX;
-        for (int i = threadIdx.x; i < per_tile; i += kThreads) {
-            const int r = i / cpt;
-            chunk_minmax<F>(x, base + (int64_t)r * cpr + (i - r * cpt), mn, mx);
+        if constexpr (F == F_F32) {
+            for (int i = threadIdx.x; i < per_tile; i += kThreads) {
+                const int r = i / cpt;
+                chunk_minmax<F>(x, base + (int64_t)r * cpr + (i - r * cpt), mn, mx);
+            }
+        } else {
+            uint32_t mn2 = Packed16<F>::kPosInf, mx2 = Packed16<F>::kNegInf;
+            // thread i walks chunks i, i + kThreads, ... of the tile: (row, column) advance by a fixed step with one carry
+            const int dr = kThreads / cpt, dj = kThreads - dr * cpt;
+            int r = (int)threadIdx.x / cpt, j = (int)threadIdx.x - r * cpt;
+            const uint4 *p = reinterpret_cast<const uint4 *>(x) + base;
+#pragma unroll 4
+            for (int i = threadIdx.x; i < per_tile; i += kThreads) {
+                chunk_minmax16<F>(p, (int64_t)r * cpr + j, mn2, mx2);
+                j += dj;
+                r += dr;
+                if (j >= cpt) { j -= cpt; ++r; }
+            }
+            unpack_minmax16<F>(mn2, mx2, mn, mx);
         }
         block_minmax(mn, mx);
         if (threadIdx.x == 0) { store_f32(out_min, dt, t, mn); store_f32(out_max, dt, t, mx); }
@@ -96,7 +190,14 @@ template <int F>
 __global__ void __launch_bounds__(kThreads) minmax_row_kernel(const void *x, int dt, int64_t rows, int64_t cpr, void *out_min, void *out_max) {
     for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
         float mn = FLT_MAX, mx = -FLT_MAX;
-        for (int64_t c = threadIdx.x; c < cpr; c += kThreads) chunk_minmax<F>(x, r * cpr + c, mn, mx);
+        if constexpr (F == F_F32) {
+            for (int64_t c = threadIdx.x; c < cpr; c += kThreads) chunk_minmax<F>(x, r * cpr + c, mn, mx);
+        } else {
+            uint32_t mn2 = Packed16<F>::kPosInf, mx2 = Packed16<F>::kNegInf;
+#pragma unroll 4
+            for (int64_t c = threadIdx.x; c < cpr; c += kThreads) chunk_minmax16<F>(x, r * cpr + c, mn2, mx2);
+            unpack_minmax16<F>(mn2, mx2, mn, mx);
+        }
         block_minmax(mn, mx);
         if (threadIdx.x == 0) { store_f32(out_min, dt, r, mn); store_f32(out_max, dt, r, mx); }
     }
@@ -107,8 +208,16 @@ template <int F>
 __global__ void __launch_bounds__(kThreads) minmax_flat_kernel(const void *x, int dt, int64_t n, float *partial) {
     float mn = FLT_MAX, mx = -FLT_MAX;
     const int64_t chunks = n / 8;
-    for (int64_t c = (int64_t)blockIdx.x * kThreads + threadIdx.x; c < chunks; c += (int64_t)gridDim.x * kThreads)
-        chunk_minmax<F>(x, c, mn, mx);
+    if constexpr (F == F_F32) {
+        for (int64_t c = (int64_t)blockIdx.x * kThreads + threadIdx.x; c < chunks; c += (int64_t)gridDim.x * kThreads)
+            chunk_minmax<F>(x, c, mn, mx);
+    } else {
+        uint32_t mn2 = Packed16<F>::kPosInf, mx2 = Packed16<F>::kNegInf;
+#pragma unroll 4
+        for (int64_t c = (int64_t)blockIdx.x * kThreads + threadIdx.x; c < chunks; c += (int64_t)gridDim.x * kThreads)
+            chunk_minmax16<F>(x, c, mn2, mx2);
+        unpack_minmax16<F>(mn2, mx2, mn, mx);
+    }
     if (blockIdx.x == 0)
         for (int64_t i = chunks * 8 + threadIdx.x; i < n; i += kThreads) {  // ragged tail
             float v = load_f32(x, dt, i);
@@ -200,7 +309,7 @@ __global__ void __launch_bounds__(256) mxfp4_convert_kernel(const uint8_t *scale
     }
 }
 
-static int flat_blocks() { return sm_count() * 4; }
+static int flat_blocks() { return sm_count() * 8; }
 
 }  // namespace ctb
 
@@ -237,13 +346,15 @@ extern "C" int ctb_minmax(const void *x, int32_t dt, int64_t rows, int64_t cols,
         if (L <= 32 && (L & (L - 1)) == 0) {
             int64_t chunks = rows * cols / 8;
             int grid = grid_for(chunks, kThreads, 8);
-            if (F == F_BF16) minmax_group_kernel<F_BF16><<<grid, kThreads, 0, st>>>(x, chunks, (int)L, dt, out_min, out_max);
+            if (F == F_BF16 && chunks < (1LL << 31)) launch_group16<F_BF16>((int)L, grid, st, x, chunks, out_min, out_max);
+            else if (F == F_F16 && chunks < (1LL << 31)) launch_group16<F_F16>((int)L, grid, st, x, chunks, out_min, out_max);
+            else if (F == F_BF16) minmax_group_kernel<F_BF16><<<grid, kThreads, 0, st>>>(x, chunks, (int)L, dt, out_min, out_max);
             else if (F == F_F16) minmax_group_kernel<F_F16><<<grid, kThreads, 0, st>>>(x, chunks, (int)L, dt, out_min, out_max);
             else minmax_group_kernel<F_F32><<<grid, kThreads, 0, st>>>(x, chunks, (int)L, dt, out_min, out_max);
             return after_launch("minmax_group_kernel");
         }
         if (cg == cols) {
-            int grid = grid_for(rows, 1, 8);
+            int grid = grid_for(rows, 1, 64);
             if (F == F_BF16) minmax_row_kernel<F_BF16><<<grid, kThreads, 0, st>>>(x, dt, rows, cols / 8, out_min, out_max);
             else if (F == F_F16) minmax_row_kernel<F_F16><<<grid, kThreads, 0, st>>>(x, dt, rows, cols / 8, out_min, out_max);
             else minmax_row_kernel<F_F32><<<grid, kThreads, 0, st>>>(x, dt, rows, cols / 8, out_min, out_max);

@@ -31,6 +31,7 @@ struct QArgs {
     int qk;          // QKind
     int bits;
     int fin, fout;   // Fmt of both sides (generic tier)
+    FastDiv by_cpr;  // chunk -> row (g_idx tier)
 };
 
 constexpr int kThreads = 256;
@@ -103,6 +104,40 @@ __global__ void __launch_bounds__(kThreads) qdq_vec8_kernel(const QArgs a) {
                 dequant8<TS>(v, q, has_zp);
                 store8_float<FOUT>(a.out, c, v);
             }
+        }
+    }
+}
+
+// The vec8 tier with a column -> group map (g_idx, forward.py:300-352: activation-ordered groups).  The reference
+// permutes the columns so that groups become contiguous, quantizes group by group and permutes back; element for
+// element that is "column c uses qparam g_idx[c] of its row".  Loads and stores stay 8 elements wide; the eight
+// group numbers of a chunk are two 16-byte loads and the qparams eight small gathers that hit in L1 / L2.
+template <int MODE, int T, int TS, int QK, int FIN, int FOUT>
+__global__ void __launch_bounds__(kThreads) qdq_vec8_gidx_kernel(const QArgs a) {
+    const bool has_zp = a.zp != nullptr;
+    const FastDiv by_cpr = a.by_cpr;
+    for (uint32_t c = blockIdx.x * kThreads + threadIdx.x; c < (uint32_t)a.chunks; c += gridDim.x * kThreads) {
+        const Raw8 raw = load_raw<FIN>(a.in, c);
+        const uint32_t row = fastdiv(c, by_cpr), col0 = (c - row * (uint32_t)a.cpr) * 8;
+        const int4 g0 = __ldg(reinterpret_cast<const int4 *>(a.g_idx + col0)), g1 = __ldg(reinterpret_cast<const int4 *>(a.g_idx + col0 + 4));
+        const int g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+        const int64_t base = (int64_t)row * a.srs;
+        float v[8];
+        decode8<FIN>(raw, v);
+        QP q[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) q[i] = load_qp(a.scale, a.sdt, a.zp, a.zdt, a.gs, base + g[i]);
+        if constexpr (MODE != 1) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = quant_prepare1<T>(v[i], q[i], has_zp, a.qmin, a.qmax);
+        }
+        if constexpr (MODE == 0) {
+            encode_store8<QK, FOUT>(a.out, c, v);
+        } else {
+            if constexpr (MODE == 2) round8<QK>(v);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = dequant1<TS>(v[i], q[i], has_zp);
+            store8_float<FOUT>(a.out, c, v);
         }
     }
 }
@@ -569,6 +604,26 @@ static int dispatch_lean(int mode, const QArgs &a, cudaStream_t st, bool *handle
     return CTB_OK;
 }
 
+#define CTB_TRY_GIDX(MODE, T_, TS_, QK_, FIN_, FOUT_)                                                   \
+    if (mode == MODE && (MODE == 1 || a.T == T_) && (MODE == 0 || a.TS == TS_) && a.qk == QK_ &&        \
+        a.fin == FIN_ && a.fout == FOUT_) {                                                              \
+        qdq_vec8_gidx_kernel<MODE, T_, TS_, QK_, FIN_, FOUT_><<<grid_for(a.chunks, kThreads, 8), kThreads, 0, st>>>(a); \
+        return after_launch("qdq_vec8_gidx_kernel");                                                     \
+    }
+
+// group-strategy int codes of a 16-bit tensor with a column -> group map; anything else runs on the generic tier
+static int dispatch_gidx(int mode, const QArgs &a, cudaStream_t st, bool *handled) {
+    *handled = true;
+    constexpr int B = CTB_BF16, H = CTB_F16, S = CTB_F32;
+    CTB_TRY_GIDX(0, B, S, QK_INT, F_BF16, F_PACK4) CTB_TRY_GIDX(0, B, S, QK_INT, F_BF16, F_I8)
+    CTB_TRY_GIDX(0, H, S, QK_INT, F_F16, F_PACK4) CTB_TRY_GIDX(0, H, S, QK_INT, F_F16, F_I8)
+    CTB_TRY_GIDX(1, S, B, QK_INT, F_PACK4, F_BF16) CTB_TRY_GIDX(1, S, B, QK_INT, F_I8, F_BF16)
+    CTB_TRY_GIDX(1, S, H, QK_INT, F_PACK4, F_F16) CTB_TRY_GIDX(1, S, H, QK_INT, F_I8, F_F16)
+    CTB_TRY_GIDX(2, B, B, QK_INT, F_BF16, F_BF16) CTB_TRY_GIDX(2, H, H, QK_INT, F_F16, F_F16)
+    *handled = false;
+    return CTB_OK;
+}
+
 static int run(int mode, const ctb_qdesc *d, const void *in, const void *scale, const void *zp,
                const int32_t *g_idx, const float *gs, void *out, void *stream) {
     int rc = validate(d, in, scale, out, mode);
@@ -614,6 +669,15 @@ static int run(int mode, const ctb_qdesc *d, const void *in, const void *scale, 
         rc = dispatch_lean(mode, a, st, &handled);
         if (handled) return rc;
         rc = dispatch_vec8(mode, a, st, &handled);
+        if (handled) return rc;
+    }
+    if (g_idx && !pack_other && d->row_group == 1 && d->cols % 8 == 0 && aligned16(in) && aligned16(out) && aligned16(g_idx) &&
+        d->rows * d->cols / 8 < (1LL << 31)) {
+        a.chunks = d->rows * d->cols / 8;
+        a.cpr = d->cols / 8;
+        a.by_cpr = make_fastdiv((uint32_t)a.cpr);
+        bool handled = false;
+        rc = dispatch_gidx(mode, a, st, &handled);
         if (handled) return rc;
     }
     int per = (mode == 0 && d->codec == CTB_CODE_PACK32) ? 32 / d->num_bits : ((mode == 0 && d->codec == CTB_CODE_FP4X2) ? 2 : 1);

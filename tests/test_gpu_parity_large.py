@@ -492,3 +492,32 @@ def test_bf16_quantize_and_fake_quantize_kernels_match_oracle(ops, orc):
                 wantf = orc.fake_quantize(xf, scale, zp, out_dtype=torch.bfloat16, **kw)
                 gotf = ops.fake_quantize(xf.cuda(), scale.cuda(), dz, out_dtype=torch.bfloat16, **kw)
                 _same_bits_or_both_nan(gotf.cpu(), wantf, "fake_quantize " + what)
+
+
+def test_activation_ordered_groups_match_oracle(ops, orc):
+    """g_idx (a group number per column, forward.py:300-352) through the 8-wide kernels: int8 codes, packed words,
+    dequantize from both, fake quantize; symmetric and asymmetric; bf16 and f16"""
+    g = torch.Generator().manual_seed(31)
+    rows, cols, group = 96, 512, 64
+    perm = torch.randperm(cols, generator=g)
+    g_idx = torch.empty(cols, dtype=torch.int32)
+    g_idx[perm] = (torch.arange(cols) // group).to(torch.int32)
+    for dt in (torch.bfloat16, torch.float16):
+        x = (torch.randn(rows, cols, generator=g) * 0.05 + 0.01).to(dt)
+        xs = x.index_select(-1, torch.argsort(g_idx))
+        mn, mx = orc.minmax(xs, 1, group)
+        for sym in (True, False):
+            scale, zp = orc.calculate_qparams(mn, mx, qtype=orc.QINT, bits=4, symmetric=sym)
+            kw = dict(qtype=orc.QINT, bits=4, col_group=group, row_group=1, scale_row_stride=cols // group)
+            want = orc.quantize(x, scale, zp, out_dtype=torch.int8, g_idx=g_idx, **kw)
+            dz, dg = zp.cuda(), g_idx.cuda()
+            got = ops.quantize(x.cuda(), scale.cuda(), dz, out_dtype=torch.int8, g_idx=dg, **kw)
+            assert_bit_equal(got.cpu(), want, f"codes {dt} sym={sym}")
+            words = ops.quantize(x.cuda(), scale.cuda(), dz, codec="pack32", g_idx=dg, **kw)
+            assert_bit_equal(words.cpu(), orc.pack_int32(want, 4), f"words {dt} sym={sym}")
+            wantd = orc.dequantize(want, scale, zp, out_dtype=dt, g_idx=g_idx, **kw)
+            assert_bit_equal(ops.dequantize(got, scale.cuda(), dz, out_dtype=dt, g_idx=dg, **kw).cpu(), wantd, f"dequant {dt} sym={sym}")
+            assert_bit_equal(ops.dequantize(words, scale.cuda(), dz, out_dtype=dt, codec="pack32", cols=cols, g_idx=dg, **kw).cpu(), wantd,
+                             f"dequant from words {dt} sym={sym}")
+            wantf = orc.fake_quantize(x, scale, zp, out_dtype=dt, g_idx=g_idx, **kw)
+            assert_bit_equal(ops.fake_quantize(x.cuda(), scale.cuda(), dz, out_dtype=dt, g_idx=dg, **kw).cpu(), wantf, f"fake {dt} sym={sym}")
