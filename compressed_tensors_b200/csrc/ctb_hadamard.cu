@@ -118,40 +118,150 @@ __global__ void __launch_bounds__(kThreads) hadamard_cols_kernel(const HArgs a) 
     }
 }
 
-// weight_output rotation: a [n rows x 32 cols] tile per block, butterflies over rows in shared memory
+// weight_input rotation for n = 512 .. 8192 (a whole hidden dimension): one Hadamard block of n = 256 * M elements
+// per thread block.  Index bits 0-2 run in registers and bits 3-7 across the lanes of a warp exactly as in the small
+// kernel (a 256-point transform per warp and chunk); the remaining log2(M) bits go through shared memory, where
+// thread r gathers the M elements j * 256 + r, runs an M-point butterfly in registers and puts them back.
 template <typename A>
-__global__ void __launch_bounds__(kThreads) hadamard_rows_kernel(const void *x, int dt, int64_t rows, int64_t cols, int n, const int8_t *signs,
-                                                                  int inverse, int normalize, void *out) {
+__device__ __forceinline__ void smem_put8(A *dst, const A (&t)[8]) {
+    if constexpr (sizeof(A) == 8) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) reinterpret_cast<double2 *>(dst)[i] = make_double2(t[2 * i], t[2 * i + 1]);
+    } else {
+        reinterpret_cast<float4 *>(dst)[0] = make_float4(t[0], t[1], t[2], t[3]);
+        reinterpret_cast<float4 *>(dst)[1] = make_float4(t[4], t[5], t[6], t[7]);
+    }
+}
+
+template <typename A>
+__device__ __forceinline__ void smem_get8(const A *src, A (&t)[8]) {
+    if constexpr (sizeof(A) == 8) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { const double2 d = reinterpret_cast<const double2 *>(src)[i]; t[2 * i] = d.x; t[2 * i + 1] = d.y; }
+    } else {
+        const float4 a = reinterpret_cast<const float4 *>(src)[0], b = reinterpret_cast<const float4 *>(src)[1];
+        t[0] = a.x; t[1] = a.y; t[2] = a.z; t[3] = a.w; t[4] = b.x; t[5] = b.y; t[6] = b.z; t[7] = b.w;
+    }
+}
+
+template <typename A, int XF, int LOG_M>
+__global__ void __launch_bounds__(kThreads) hadamard_cols_big_kernel(const void *x, int64_t blocks, const int8_t *signs, int inverse,
+                                                                      int normalize, void *out) {
+    constexpr int M = 1 << LOG_M, N = 256 * M, CH = N / 8;  // CH: 8-element chunks per Hadamard block, a multiple of 32
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    A *tile = reinterpret_cast<A *>(smem_raw);  // [n][33]
-    const int64_t col_tiles = (cols + 31) / 32, tiles = (rows / n) * col_tiles;
+    A *buf = reinterpret_cast<A *>(smem_raw);  // [N]
+    const int lane = threadIdx.x & 31;
+    for (int64_t b = blockIdx.x; b < blocks; b += gridDim.x) {
+        const int64_t c0 = b * CH;
+        for (int ci = threadIdx.x; ci < CH; ci += kThreads) {  // whole warps: the lane stages shuffle
+            float v[8];
+            decode8<XF>(load_raw<XF>(x, c0 + ci), v);
+            A t[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) t[i] = (A)((inverse && signs) ? v[i] * (float)signs[ci * 8 + i] : v[i]);
+            fwht8<A>(t);
+            fwht_lanes<A>(t, 32, lane);
+            smem_put8<A>(buf + ci * 8, t);
+        }
+        __syncthreads();
+        {
+            A t[M];
+#pragma unroll
+            for (int j = 0; j < M; ++j) t[j] = buf[j * 256 + threadIdx.x];
+#pragma unroll
+            for (int h = 1; h < M; h <<= 1)
+#pragma unroll
+                for (int j = 0; j < M; ++j)
+                    if ((j & h) == 0) {
+                        const A u = t[j], w = t[j | h];
+                        t[j] = u + w;
+                        t[j | h] = u - w;
+                    }
+#pragma unroll
+            for (int j = 0; j < M; ++j) buf[j * 256 + threadIdx.x] = t[j];
+        }
+        __syncthreads();
+        for (int ci = threadIdx.x; ci < CH; ci += kThreads) {
+            A t[8];
+            smem_get8<A>(buf + ci * 8, t);
+            float v[8];
+            if constexpr (sizeof(A) == 8) {
+                const double sc = normalize ? sqrt((double)N) : 1.0;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = (float)(t[i] / sc);  // float64 quotient, then the cast chain of .to(dtype)
+            } else {
+                const float sc = normalize ? 1.0f / sqrtf((float)N) : 1.0f;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = t[i] * sc;
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                if (!inverse && signs) v[i] *= (float)signs[ci * 8 + i];
+                v[i] += 0.0f;  // an exact zero comes out of the reference's matmul as +0.0, whatever the signs
+                v[i] = round_to<XF == F_BF16 ? CTB_BF16 : XF == F_F16 ? CTB_F16 : CTB_F32>(v[i]);
+            }
+            store8_float<XF>(out, c0 + ci, v);
+        }
+        __syncthreads();  // the next block's first phase overwrites the buffer
+    }
+}
+
+template <typename A, int XF>
+static int launch_cols_big(int n, int64_t blocks, const void *x, const int8_t *signs, int inverse, int normalize, void *out, cudaStream_t st) {
+    const size_t smem = (size_t)n * sizeof(A);
+    const int grid = grid_for(blocks, 1, 4);
+#define CTB_HCB(LM_)                                                                                                       \
+    {                                                                                                                      \
+        cudaFuncSetAttribute(hadamard_cols_big_kernel<A, XF, LM_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        hadamard_cols_big_kernel<A, XF, LM_><<<grid, kThreads, smem, st>>>(x, blocks, signs, inverse, normalize, out);     \
+    }
+    switch (n) {
+    case 512: CTB_HCB(1) break;
+    case 1024: CTB_HCB(2) break;
+    case 2048: CTB_HCB(3) break;
+    case 4096: CTB_HCB(4) break;
+    default: CTB_HCB(5) break;
+    }
+#undef CTB_HCB
+    return after_launch("hadamard_cols_big_kernel");
+}
+
+// weight_output rotation: a [n rows x W cols] tile per block (W a power of two <= 32, as many as fit in shared memory),
+// butterflies over rows in shared memory
+template <typename A>
+__global__ void __launch_bounds__(kThreads) hadamard_rows_kernel(const void *x, int dt, int64_t rows, int64_t cols, int n, int wshift,
+                                                                  const int8_t *signs, int inverse, int normalize, void *out) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    A *tile = reinterpret_cast<A *>(smem_raw);  // [n][W + 1]
+    const int W = 1 << wshift, pitch = W + 1;
+    const int64_t col_tiles = (cols + W - 1) >> wshift, tiles = (rows / n) * col_tiles;
     const A scale = normalize ? (A)sqrt((double)n) : (A)1;
     for (int64_t t = blockIdx.x; t < tiles; t += gridDim.x) {
-        const int64_t r0 = (t / col_tiles) * n, c0 = (t % col_tiles) * 32;
-        for (int i = threadIdx.x; i < n * 32; i += kThreads) {
-            int r = i >> 5, c = i & 31;
+        const int64_t tr = t / col_tiles, r0 = tr * n, c0 = (t - tr * col_tiles) << wshift;
+        for (int i = threadIdx.x; i < n * W; i += kThreads) {
+            int r = i >> wshift, c = i & (W - 1);
             A v = 0;
             if (c0 + c < cols) {
                 v = (A)load_f32(x, dt, (r0 + r) * cols + c0 + c);
                 if (!inverse && signs) v *= (A)signs[r];
             }
-            tile[r * 33 + c] = v;
+            tile[r * pitch + c] = v;
         }
         __syncthreads();
         for (int h = 1; h < n; h <<= 1) {
-            for (int i = threadIdx.x; i < (n / 2) * 32; i += kThreads) {
-                int p = i >> 5, c = i & 31;
+            for (int i = threadIdx.x; i < (n / 2) * W; i += kThreads) {
+                int p = i >> wshift, c = i & (W - 1);
                 int r = ((p & ~(h - 1)) << 1) | (p & (h - 1));  // row with bit h clear
-                A u = tile[r * 33 + c], w = tile[(r | h) * 33 + c];
-                tile[r * 33 + c] = u + w;
-                tile[(r | h) * 33 + c] = u - w;
+                A u = tile[r * pitch + c], w = tile[(r | h) * pitch + c];
+                tile[r * pitch + c] = u + w;
+                tile[(r | h) * pitch + c] = u - w;
             }
             __syncthreads();
         }
-        for (int i = threadIdx.x; i < n * 32; i += kThreads) {
-            int r = i >> 5, c = i & 31;
+        for (int i = threadIdx.x; i < n * W; i += kThreads) {
+            int r = i >> wshift, c = i & (W - 1);
             if (c0 + c < cols) {
-                A v = tile[r * 33 + c] / scale;
+                A v = tile[r * pitch + c] / scale;
                 float f = (float)v;
                 if (inverse && signs) f *= (float)signs[r];
                 f += 0.0f;  // exact zeros are +0.0 in the reference's matmul
@@ -647,11 +757,19 @@ extern "C" int ctb_hadamard(const void *x, int32_t dtype, int64_t rows, int64_t 
             if (precision == CTB_F64) { CTB_HC(double) } else { CTB_HC(float) }
             return after_launch("hadamard_cols_kernel");
         }
-        return fail(CTB_EUNSUPPORTED, "weight_input rotation needs 8 <= n <= 256 and 16-byte aligned buffers");
+        if (n >= 512 && n <= 8192 && aligned16(x) && aligned16(out)) {
+            const int64_t blocks = rows * cols / n;
+#define CTB_HCB_DT(A_)                                                                                                   \
+    if (dtype == CTB_BF16) return launch_cols_big<A_, F_BF16>(n, blocks, x, signs, inverse, normalize, out, st);         \
+    else if (dtype == CTB_F16) return launch_cols_big<A_, F_F16>(n, blocks, x, signs, inverse, normalize, out, st);      \
+    else return launch_cols_big<A_, F_F32>(n, blocks, x, signs, inverse, normalize, out, st);
+            if (precision == CTB_F64) { CTB_HCB_DT(double) } else { CTB_HCB_DT(float) }
+        }
+        return fail(CTB_EUNSUPPORTED, "weight_input rotation needs 8 <= n <= 8192 and 16-byte aligned buffers");
     }
     if (side != 1) return fail(CTB_EINVAL_SHAPE, "side must be 0 (weight_input) or 1 (weight_output)");
     if (rows % n) return fail(CTB_EINVAL_SHAPE, "rows %lld are not a multiple of the Hadamard size %d", (long long)rows, n);
-    if (n > 512) return fail(CTB_EUNSUPPORTED, "weight_output rotation is built for n <= 512");
+    if (n > 8192) return fail(CTB_EUNSUPPORTED, "weight_output rotation is built for n <= 8192");
     if ((dtype == CTB_BF16 || dtype == CTB_F16) && (n == 32 || n == 64 || n == 128 || n == 256) && cols % 4 == 0 &&
         (reinterpret_cast<uintptr_t>(x) & 7u) == 0 && (reinterpret_cast<uintptr_t>(out) & 7u) == 0) {
         const bool f64 = precision == CTB_F64;
@@ -670,16 +788,19 @@ extern "C" int ctb_hadamard(const void *x, int32_t dtype, int64_t rows, int64_t 
         }
         return after_launch("hadamard_rows_fast_kernel");
     }
-    int64_t tiles = (rows / n) * cdiv(cols, 32);
+    // widest power-of-two tile (<= 32 columns) whose [n][W + 1] buffer fits in 200 KiB of shared memory
+    const size_t esize = precision == CTB_F64 ? sizeof(double) : sizeof(float);
+    int wshift = 5;
+    while (wshift > 0 && (size_t)n * ((1u << wshift) + 1) * esize > 200u * 1024u) --wshift;
+    const size_t smem = (size_t)n * ((1u << wshift) + 1) * esize;
+    int64_t tiles = (rows / n) * cdiv(cols, 1 << wshift);
     int grid = grid_for(tiles, 1, 2);
     if (precision == CTB_F64) {
-        size_t smem = (size_t)n * 33 * sizeof(double);
         cudaFuncSetAttribute(hadamard_rows_kernel<double>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        hadamard_rows_kernel<double><<<grid, kThreads, smem, st>>>(x, dtype, rows, cols, n, signs, inverse, normalize, out);
+        hadamard_rows_kernel<double><<<grid, kThreads, smem, st>>>(x, dtype, rows, cols, n, wshift, signs, inverse, normalize, out);
     } else {
-        size_t smem = (size_t)n * 33 * sizeof(float);
         cudaFuncSetAttribute(hadamard_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        hadamard_rows_kernel<float><<<grid, kThreads, smem, st>>>(x, dtype, rows, cols, n, signs, inverse, normalize, out);
+        hadamard_rows_kernel<float><<<grid, kThreads, smem, st>>>(x, dtype, rows, cols, n, wshift, signs, inverse, normalize, out);
     }
     return after_launch("hadamard_rows_kernel");
 }

@@ -1,16 +1,23 @@
-"""Hadamard matrix construction (transform/utils/hadamard.py of the reference).  These are tiny host-side
-objects (at most a few hundred rows); the rotation of the weights themselves runs in the CUDA kernels,
-which only need the +-1 diagonal."""
+"""Hadamard matrix construction (transform/utils/hadamard.py of the reference).  These are host-side objects
+kept for inspection and serialisation; the rotation of the weights themselves runs in the CUDA kernels, which
+only need the +-1 diagonal."""
 import math
 from typing import Optional
 
 import torch
 
-__all__ = ["random_hadamard_matrix", "deterministic_hadamard_matrix", "is_pow2", "random_hadamard_signs", "SYLVESTER_RANDOM_SIZES"]
+__all__ = ["random_hadamard_matrix", "deterministic_hadamard_matrix", "is_pow2", "random_hadamard_signs", "SYLVESTER_RANDOM_SIZES",
+           "is_sylvester_random_size"]
 
-# sizes for which the reference's stored base matrix is the Sylvester matrix, so that
+# sizes up to 256 for which the reference's stored base matrix is the Sylvester matrix, so that
 # random_hadamard_matrix(n) == diag(Q) @ H_n; other sizes need the reference's data file
 SYLVESTER_RANDOM_SIZES = (1, 2, 4, 8, 16, 64, 128, 256)
+
+
+def is_sylvester_random_size(size: int) -> bool:
+    """True where random_hadamard_matrix(size) is diag(Q) @ Sylvester: the stored Sylvester sizes, and every larger
+    power of two, which the reference builds as butterfly(size / 256) (x) stored H_256 (hadamard.py:102-163)."""
+    return size in SYLVESTER_RANDOM_SIZES or (size >= 512 and size & (size - 1) == 0)
 
 
 def is_pow2(n: int) -> bool:
@@ -42,8 +49,8 @@ def random_hadamard_signs(size: int, gen: Optional[torch.Generator] = None, dtyp
 def random_hadamard_matrix(size: int, dtype: torch.dtype = torch.bfloat16, device: torch.device = torch.device("cpu"),
                            gen: Optional[torch.Generator] = None) -> torch.Tensor:
     """diag(Q) @ H_size with Q a seeded +-1 vector (hadamard.py:65-89)."""
-    if size not in SYLVESTER_RANDOM_SIZES:
-        raise NotImplementedError(f"random Hadamard matrices are built for sizes {SYLVESTER_RANDOM_SIZES}; size {size} needs "
+    if not is_sylvester_random_size(size):
+        raise NotImplementedError(f"random Hadamard matrices are built for sizes {SYLVESTER_RANDOM_SIZES} and powers of two from 512; size {size} needs "
                                   "the reference's table of stored base matrices")
     q = random_hadamard_signs(size, gen, dtype).to(device)
     return q[:, None] * deterministic_hadamard_matrix(size, dtype, device)

@@ -446,6 +446,28 @@ def gen_mxfp4():
     torch.save(out, os.path.join(OUT, "mxfp4.pt"))
 
 
+def gen_hadamard_full():
+    """Transforms as wide as the whole dimension (no head_dim): n = 1024 and 2048, both factories, both weight sides.
+    Only the first column of each matrix is stored (the random signs; all ones for the deterministic matrix)."""
+    out = {}
+    gen = torch.Generator().manual_seed(14)
+    for n in (1024, 2048):
+        for tag, fac_cls, seed in (("hadamard", HadamardFactory, None), ("random", RandomHadamardFactory, 7)):
+            for location, inverse in (("weight_input", False), ("weight_input", True), ("weight_output", False), ("weight_output", True)):
+                o, i = (8, n) if location == "weight_input" else (n, 8)
+                lin = torch.nn.Linear(i, o, bias=False, dtype=torch.bfloat16)
+                lin.weight.data = weights(gen, o, i, torch.bfloat16)
+                scheme = TransformScheme(type=tag if tag == "hadamard" else "random-hadamard",
+                                         apply=[TransformArgs(targets=["Linear"], location=location, inverse=inverse)])
+                fac = fac_cls("t", scheme, seed=seed)
+                tr = fac.create_transform(lin, scheme.apply[0])
+                w0 = lin.weight.data.clone()
+                with torch.no_grad():
+                    w1 = tr(lin.weight)
+                out[f"{tag}_{location}_{'inv' if inverse else 'fwd'}_{n}"] = {"w": w0, "out": w1.detach(), "signs": tr.weight.detach()[:, 0].to(torch.int8)}
+    torch.save(out, os.path.join(OUT, "hadamard_full.pt"))
+
+
 def gen_fp4_pack_all():
     """pack_fp4_to_uint8 on EVERY bf16 and f16 bit pattern (off-grid magnitudes, ties, infinities, NaNs) and on a
     float32 sweep; unpack_fp4_from_uint8 on every byte, in the three dense dtypes."""
@@ -468,7 +490,7 @@ if __name__ == "__main__":
     only = sys.argv[2] if len(sys.argv) > 2 else None  # e.g. "mxfp4": regenerate one fixture
     for name, fn in (("int_quant", gen_int), ("fp8_quant", gen_fp8), ("nvfp4", gen_nvfp4), ("sparse", gen_sparse),
                      ("hadamard", gen_hadamard), ("hadamard_online", gen_hadamard_online), ("hadamard_randomize", gen_hadamard_randomize), ("hadamard_embedding", gen_hadamard_embedding), ("mxfp4", gen_mxfp4), ("marlin24", gen_marlin24),
-                     ("fp4_pack_all", gen_fp4_pack_all)):
+                     ("fp4_pack_all", gen_fp4_pack_all), ("hadamard_full", gen_hadamard_full)):
         if only is None or only == name:
             fn()
     for f in sorted(os.listdir(OUT)):

@@ -300,6 +300,32 @@ def test_disk_decompress_and_compressed_linear(tmp_path, fmt, group):
     assert_bit_equal(mod(x).cpu(), y.cpu(), "second forward reuses the dense weight")
 
 
+def test_hadamard_whole_dimension(golden):
+    """HadamardFactory / RandomHadamardFactory without head_dim: the transform spans the whole input (weight_input) or
+    output (weight_output) dimension, n = 1024 and 2048; float64 offline path, bit-exact against the reference; the
+    fp32 mode of the same kernels within one bf16 step of the value"""
+    from compressed_tensors_b200 import ops
+    from compressed_tensors_b200.transform import TransformArgs, TransformFactory, TransformScheme
+
+    for name, d in golden("hadamard_full").items():
+        tag, rest = name.split("_", 1)
+        location, direction, n = rest.rsplit("_", 2)
+        n, inverse = int(n), direction == "inv"
+        o, i = d["w"].shape
+        lin = torch.nn.Linear(i, o, bias=False, dtype=torch.bfloat16, device="cuda")
+        lin.weight.data = d["w"].cuda()
+        scheme = TransformScheme(type="hadamard" if tag == "hadamard" else "random-hadamard",
+                                 apply=[TransformArgs(targets=["Linear"], location=location, inverse=inverse)])
+        fac = TransformFactory.from_scheme(scheme, name="t", seed=None if tag == "hadamard" else 7)
+        tr = fac.create_transform(lin, scheme.apply[0])
+        assert tr.weight.shape == (n, n) and torch.equal(tr.weight.data[:, 0].to(torch.int8).cpu(), d["signs"]), name
+        assert_bit_equal(tr(lin.weight.data).cpu(), d["out"], name)
+        fast = ops.hadamard(d["w"].cuda(), n, signs=d["signs"].cuda(), inverse=inverse, side=0 if location == "weight_input" else 1,
+                            precision=torch.float32)
+        want = d["out"].float()
+        assert bool(((fast.cpu().float() - want).abs() <= want.abs() * 2.0 ** -7 + 1e-6).all()), name + " float32 mode"
+
+
 def test_online_hadamard_hooks(golden):
     """input / output transforms on activations (transform/factory/base.py:132-167): the reference computes them
     as an fp32 matmul, the butterfly sums in another order, so the match is to one bf16 step / 1e-5 relative"""

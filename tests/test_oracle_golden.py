@@ -228,6 +228,15 @@ def test_hadamard(golden):
             torch.testing.assert_close(out, d["out"], rtol=1e-6, atol=1e-7, msg=name)
 
 
+def test_hadamard_whole_dimension(golden):
+    """transforms as wide as the dimension (n = 1024, 2048; no head_dim), float64 offline path: bit-exact"""
+    for name, d in golden("hadamard_full").items():
+        n = int(name.rsplit("_", 1)[1])
+        side = 0 if "weight_input" in name else 1
+        out = orc.hadamard(d["w"], n, signs=d["signs"], inverse="_inv_" in name, side=side)
+        assert_bit_equal(out, d["out"], name)
+
+
 def test_mxfp4_scale_helpers_every_input(golden):
     """mxfp4_utils.py on all 65536 bf16 bit patterns and all 256 exponent bytes"""
     d = golden("mxfp4")
