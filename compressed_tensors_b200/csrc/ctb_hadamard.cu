@@ -272,6 +272,129 @@ __global__ void __launch_bounds__(kThreads) hadamard_rows_kernel(const void *x, 
     }
 }
 
+// weight_output rotation for 16-bit tensors and n = 512 .. 8192 (a whole output dimension).  A block takes a tile of
+// n rows x W columns (W * 2 bytes of every row), stores it TRANSPOSED in shared memory, so that each column becomes a
+// contiguous length-n vector, and then runs the three phases of the wide weight_input kernel on the W vectors:
+// 256-point transforms in registers and across lanes, M-point transforms through strided gathers, and the scaled,
+// signed, rounded write back.  W is as wide as 128 KiB of shared memory allows.
+constexpr int kBigThreads = 512;
+
+template <typename A, int LOG_M>
+struct RowsBig {
+    static constexpr int N = 256 << LOG_M;
+    static constexpr int W = (131072 / (int)sizeof(A)) / N >= 8 ? 8 : (131072 / (int)sizeof(A)) / N;  // 8, 4 or 2
+};
+
+template <typename A, int XF, int LOG_M>
+__global__ void __launch_bounds__(kBigThreads) hadamard_rows_big_kernel(const void *x, int64_t rows, int64_t cols, const int8_t *signs,
+                                                                         int inverse, int normalize, void *out) {
+    constexpr int M = 1 << LOG_M, N = RowsBig<A, LOG_M>::N, W = RowsBig<A, LOG_M>::W, CH = N / 8;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    A *col = reinterpret_cast<A *>(smem_raw);  // [W][N]
+    const int lane = threadIdx.x & 31;
+    const int64_t col_tiles = cols / W, tiles = (rows / N) * col_tiles;
+    const uint16_t *xin = reinterpret_cast<const uint16_t *>(x);
+    uint16_t *xout = reinterpret_cast<uint16_t *>(out);
+    for (int64_t t = blockIdx.x; t < tiles; t += gridDim.x) {
+        const int64_t tr = t / col_tiles, r0 = tr * N, c0 = (t - tr * col_tiles) * W;
+        // rows of the tile -> columns in shared memory
+#pragma unroll 4
+        for (int r = threadIdx.x; r < N; r += kBigThreads) {
+            const uint16_t *src = xin + (r0 + r) * cols + c0;
+            uint32_t w[W / 2];
+            if constexpr (W == 8) { const uint4 q = ld_stream(src); w[0] = q.x; w[1] = q.y; w[2] = q.z; w[3] = q.w; }
+            else if constexpr (W == 4) { const uint2 q = ld_stream8(src); w[0] = q.x; w[1] = q.y; }
+            else { w[0] = ld_stream4(src); }
+            const float sg = (!inverse && signs) ? (float)signs[r] : 1.0f;
+#pragma unroll
+            for (int k = 0; k < W / 2; ++k) {
+                float lo, hi;
+                if constexpr (XF == F_BF16) { lo = __uint_as_float(w[k] << 16); hi = __uint_as_float(w[k] & 0xFFFF0000u); }
+                else { const float2 f = half2_bits_to_float2(w[k]); lo = f.x; hi = f.y; }
+                col[(2 * k) * N + r] = (A)(lo * sg);
+                col[(2 * k + 1) * N + r] = (A)(hi * sg);
+            }
+        }
+        __syncthreads();
+        for (int q = threadIdx.x; q < W * CH; q += kBigThreads) {  // whole warps; a chunk never straddles two columns
+            A v[8];
+            smem_get8<A>(col + q * 8, v);
+            fwht8<A>(v);
+            fwht_lanes<A>(v, 32, lane);
+            smem_put8<A>(col + q * 8, v);
+        }
+        __syncthreads();
+        for (int q = threadIdx.x; q < W * 256; q += kBigThreads) {
+            A *base = col + (q >> 8) * N + (q & 255);
+            A v[M];
+#pragma unroll
+            for (int j = 0; j < M; ++j) v[j] = base[j * 256];
+#pragma unroll
+            for (int h = 1; h < M; h <<= 1)
+#pragma unroll
+                for (int j = 0; j < M; ++j)
+                    if ((j & h) == 0) {
+                        const A u = v[j], w2 = v[j | h];
+                        v[j] = u + w2;
+                        v[j | h] = u - w2;
+                    }
+#pragma unroll
+            for (int j = 0; j < M; ++j) base[j * 256] = v[j];
+        }
+        __syncthreads();
+#pragma unroll 4
+        for (int r = threadIdx.x; r < N; r += kBigThreads) {
+            const float sg = (inverse && signs) ? (float)signs[r] : 1.0f;
+            uint32_t w[W / 2];
+#pragma unroll
+            for (int k = 0; k < W / 2; ++k) {
+                float f[2];
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const A v = col[(2 * k + e) * N + r];
+                    if constexpr (sizeof(A) == 8) f[e] = (float)(v / (normalize ? sqrt((double)N) : 1.0));
+                    else f[e] = v / (normalize ? sqrtf((float)N) : 1.0f);
+                    f[e] = f[e] * sg + 0.0f;  // exact zeros are +0.0 in the reference's matmul
+                }
+                if constexpr (XF == F_BF16) { const __nv_bfloat162 h = __floats2bfloat162_rn(f[0], f[1]); w[k] = *reinterpret_cast<const uint32_t *>(&h); }
+                else { const __half2 h = __floats2half2_rn(f[0], f[1]); w[k] = *reinterpret_cast<const uint32_t *>(&h); }
+            }
+            uint16_t *dst = xout + (r0 + r) * cols + c0;
+            if constexpr (W == 8) st_stream(dst, make_uint4(w[0], w[1], w[2], w[3]));
+            else if constexpr (W == 4) st_stream8(dst, make_uint2(w[0], w[1]));
+            else st_stream4(dst, w[0]);
+        }
+        __syncthreads();
+    }
+}
+
+template <typename A, int XF>
+static int launch_rows_big(int n, const void *x, int64_t rows, int64_t cols, const int8_t *signs, int inverse, int normalize, void *out,
+                           cudaStream_t st) {
+#define CTB_HRB(LM_)                                                                                                        \
+    {                                                                                                                       \
+        const int smem = RowsBig<A, LM_>::N * RowsBig<A, LM_>::W * (int)sizeof(A);                                          \
+        const int grid = grid_for((rows / n) * (cols / RowsBig<A, LM_>::W), 1, 1);                                          \
+        cudaFuncSetAttribute(hadamard_rows_big_kernel<A, XF, LM_>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);      \
+        hadamard_rows_big_kernel<A, XF, LM_><<<grid, kBigThreads, smem, st>>>(x, rows, cols, signs, inverse, normalize, out); \
+    }
+    switch (n) {
+    case 512: CTB_HRB(1) break;
+    case 1024: CTB_HRB(2) break;
+    case 2048: CTB_HRB(3) break;
+    case 4096: CTB_HRB(4) break;
+    default: CTB_HRB(5) break;
+    }
+#undef CTB_HRB
+    return after_launch("hadamard_rows_big_kernel");
+}
+
+// tile width of the wide weight_output kernel for a Hadamard size and accumulator
+static int rows_big_width(int n, bool f64) {
+    const int fit = (131072 / (f64 ? 8 : 4)) / n;
+    return fit >= 8 ? 8 : fit;
+}
+
 // weight_output rotation for 16-bit tensors and n = 32 .. 256: the butterflies run over ROWS, so a column is an
 // independent length-n transform.  A block takes a tile of n rows x 32*CPT columns; a warp owns a strip of 4*CPT
 // columns of it.  Row index bits 0-1 and 5+ of a lane's values live in registers, bits 2-4 across lanes
@@ -787,6 +910,17 @@ extern "C" int ctb_hadamard(const void *x, int32_t dtype, int64_t rows, int64_t 
             if (dtype == CTB_BF16) { CTB_HR_N(float, F_BF16) } else { CTB_HR_N(float, F_F16) }
         }
         return after_launch("hadamard_rows_fast_kernel");
+    }
+    if ((dtype == CTB_BF16 || dtype == CTB_F16) && n >= 512) {
+        const int w = rows_big_width(n, precision == CTB_F64);
+        if (cols % w == 0 && (reinterpret_cast<uintptr_t>(x) % (2 * w)) == 0 && (reinterpret_cast<uintptr_t>(out) % (2 * w)) == 0) {
+            if (precision == CTB_F64) {
+                if (dtype == CTB_BF16) return launch_rows_big<double, F_BF16>(n, x, rows, cols, signs, inverse, normalize, out, st);
+                return launch_rows_big<double, F_F16>(n, x, rows, cols, signs, inverse, normalize, out, st);
+            }
+            if (dtype == CTB_BF16) return launch_rows_big<float, F_BF16>(n, x, rows, cols, signs, inverse, normalize, out, st);
+            return launch_rows_big<float, F_F16>(n, x, rows, cols, signs, inverse, normalize, out, st);
+        }
     }
     // widest power-of-two tile (<= 32 columns) whose [n][W + 1] buffer fits in 200 KiB of shared memory
     const size_t esize = precision == CTB_F64 ? sizeof(double) : sizeof(float);

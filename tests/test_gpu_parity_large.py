@@ -521,3 +521,25 @@ def test_activation_ordered_groups_match_oracle(ops, orc):
                              f"dequant from words {dt} sym={sym}")
             wantf = orc.fake_quantize(x, scale, zp, out_dtype=dt, g_idx=g_idx, **kw)
             assert_bit_equal(ops.fake_quantize(x.cuda(), scale.cuda(), dz, out_dtype=dt, g_idx=dg, **kw).cpu(), wantf, f"fake {dt} sym={sym}")
+
+
+@pytest.mark.parametrize("n", [512, 1024, 4096, 8192])
+def test_whole_dimension_rotation_sizes(ops, orc, n):
+    """Hadamard transforms as wide as a hidden dimension, both weight sides, forward and inverse, random signs,
+    bf16 and f16; float64 mode bit-exact against the oracle, float32 mode within one step of the tensor dtype.
+    The weight_output shapes cover the wide-tile kernel (8, 4 or 2 columns per tile) and a column count it cannot
+    tile (generic kernel)."""
+    g = torch.Generator().manual_seed(n)
+    signs = (torch.randint(0, 2, (n,), generator=g) * 2 - 1).to(torch.int8)
+    for dtype in (torch.bfloat16, torch.float16):
+        shapes = [(0, 3, n), (1, n, 8)] if n >= 4096 else [(0, 5, 2 * n), (1, 2 * n, 24), (1, n, 7)]
+        for side, rows, cols in shapes:
+            w = (torch.randn(rows, cols, generator=g) * 0.05).to(dtype)
+            for inverse in (False, True):
+                want = orc.hadamard(w, n, signs=signs, inverse=inverse, side=side)
+                got = ops.hadamard(w.cuda(), n, signs=signs.cuda(), inverse=inverse, side=side, precision=torch.float64).cpu()
+                assert_bit_equal(got, want, f"n={n} side={side} {rows}x{cols} inverse={inverse} {dtype}")
+                fast = ops.hadamard(w.cuda(), n, signs=signs.cuda(), inverse=inverse, side=side, precision=torch.float32).cpu()
+                err = (fast.float() - want.float()).abs()
+                step = want.float().abs() * (2.0 ** -7 if dtype == torch.bfloat16 else 2.0 ** -10) + 1e-6
+                assert bool((err <= step).all()), f"n={n} side={side} float32 mode"
