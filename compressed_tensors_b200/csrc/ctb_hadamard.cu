@@ -10,6 +10,8 @@
 // each divided by sqrt(n) and rounded to the dtype of W.  The reference computes in float64; sums of
 // at most 256 bf16/fp16 values are exact in float64 whatever the order, so the float64 butterfly
 // below reproduces its matmul bit for bit.  The float32 mode trades that for speed.
+#include <algorithm>
+
 #include "ctb_codec.cuh"
 #include "ctb_rotquant.cuh"
 
@@ -278,11 +280,13 @@ __global__ void __launch_bounds__(kThreads) hadamard_rows_kernel(const void *x, 
 // 256-point transforms in registers and across lanes, M-point transforms through strided gathers, and the scaled,
 // signed, rounded write back.  W is as wide as 128 KiB of shared memory allows.
 constexpr int kBigThreads = 512;
+constexpr int kRowsBigBytes = 131072;  // most shared memory a tile may take
 
 template <typename A, int LOG_M>
 struct RowsBig {
     static constexpr int N = 256 << LOG_M;
-    static constexpr int W = (131072 / (int)sizeof(A)) / N >= 8 ? 8 : (131072 / (int)sizeof(A)) / N;  // 8, 4 or 2
+    static constexpr int kFit = (kRowsBigBytes / (int)sizeof(A)) / N;
+    static constexpr int W = kFit >= 8 ? 8 : kFit >= 2 ? kFit : 2;  // 8, 4 or 2
 };
 
 template <typename A, int XF, int LOG_M>
@@ -374,7 +378,7 @@ static int launch_rows_big(int n, const void *x, int64_t rows, int64_t cols, con
 #define CTB_HRB(LM_)                                                                                                        \
     {                                                                                                                       \
         const int smem = RowsBig<A, LM_>::N * RowsBig<A, LM_>::W * (int)sizeof(A);                                          \
-        const int grid = grid_for((rows / n) * (cols / RowsBig<A, LM_>::W), 1, 1);                                          \
+        const int grid = grid_for((rows / n) * (cols / RowsBig<A, LM_>::W), 1, std::min(4, std::max(1, 200 * 1024 / smem)));                                          \
         cudaFuncSetAttribute(hadamard_rows_big_kernel<A, XF, LM_>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);      \
         hadamard_rows_big_kernel<A, XF, LM_><<<grid, kBigThreads, smem, st>>>(x, rows, cols, signs, inverse, normalize, out); \
     }
@@ -391,8 +395,8 @@ static int launch_rows_big(int n, const void *x, int64_t rows, int64_t cols, con
 
 // tile width of the wide weight_output kernel for a Hadamard size and accumulator
 static int rows_big_width(int n, bool f64) {
-    const int fit = (131072 / (f64 ? 8 : 4)) / n;
-    return fit >= 8 ? 8 : fit;
+    const int fit = (kRowsBigBytes / (f64 ? 8 : 4)) / n;
+    return fit >= 8 ? 8 : fit >= 2 ? fit : 2;
 }
 
 // weight_output rotation for 16-bit tensors and n = 32 .. 256: the butterflies run over ROWS, so a column is an
