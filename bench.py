@@ -153,18 +153,11 @@ def run_reference(args):
     }))
 
 
-def per_config_table(dev, peak):
-    """Device-timed throughput of the other BASELINE.json configs (C1-C4) on their named shapes.  Each op runs
-    over a rotating set of distinct input/output buffers whose total exceeds 2x the L2 size, so every launch
-    streams from HBM.  GB/s is bf16 (dense-side) input bytes / time; frac = algorithmic bytes / time / peak."""
-    from compressed_tensors_b200 import ops
-
-    out = {}
-    g = torch.Generator(device=dev).manual_seed(SEED + 1)
+def op_timer(out, peak):
+    """Returns run(name, make_args, fn, dense_bytes, alg_bytes, per_set_bytes): times fn over a rotating set of
+    distinct argument sets whose total exceeds 2x the L2 size (every launch streams from HBM), replayed from a CUDA
+    graph, with CUDA events on the current stream, and records us / dense GB/s / fraction of `peak` under out[name]."""
     l2 = 2 * 126 * 1024 * 1024
-
-    def rnd(r, c, std=0.02):
-        return (torch.randn(r, c, generator=g, device=dev) * std).to(torch.bfloat16)
 
     def run(name, make_args, fn, dense_bytes, alg_bytes, per_set_bytes):
         nsets = int(max(2, min(16, -(-l2 // int(per_set_bytes)))))
@@ -197,6 +190,23 @@ def per_config_table(dev, peak):
         en.synchronize()
         sec = st.elapsed_time(en) / 1e3 / (reps * nsets)
         out[name] = {"us": round(sec * 1e6, 2), "dense_gbs": round(dense_bytes / sec / 1e9, 1), "frac": round(alg_bytes / sec / 1e9 / peak, 3), "timed": mode}
+
+    return run
+
+
+def per_config_table(dev, peak):
+    """Device-timed throughput of the other BASELINE.json configs (C1-C4) on their named shapes.  Each op runs
+    over a rotating set of distinct input/output buffers whose total exceeds 2x the L2 size, so every launch
+    streams from HBM.  GB/s is bf16 (dense-side) input bytes / time; frac = algorithmic bytes / time / peak."""
+    from compressed_tensors_b200 import ops
+
+    out = {}
+    g = torch.Generator(device=dev).manual_seed(SEED + 1)
+
+    def rnd(r, c, std=0.02):
+        return (torch.randn(r, c, generator=g, device=dev) * std).to(torch.bfloat16)
+
+    run = op_timer(out, peak)
 
     kw4 = dict(qtype=ops.QINT, bits=4, col_group=128)
     n = 4096 * 4096
@@ -252,6 +262,68 @@ def per_config_table(dev, peak):
     return out
 
 
+def standalone_ops_table(dev, peak, size=8192):
+    """Device-timed throughput of the reference's operators as separate calls with given qparams (the building blocks the
+    compressors and the calibration lifecycle call one by one) on a size x size bf16 tensor: quantize to packed words /
+    int8 / e4m3 codes, fake_quantize, min/max per strategy, the stand-alone packers, whole-dimension Hadamard."""
+    from compressed_tensors_b200 import ops
+
+    out = {}
+    run = op_timer(out, peak)
+    g = torch.Generator(device=dev).manual_seed(SEED + 2)
+    R = C = size
+    n = R * C
+
+    def rnd():
+        return (torch.randn(R, C, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+
+    w0 = rnd()
+    kw4 = dict(qtype=ops.QINT, bits=4, col_group=128, scale_row_stride=C // 128)
+    mn, mx = ops.minmax(w0, 1, 128)
+    s4, _ = ops.calculate_qparams(mn, mx, qtype=ops.QINT, bits=4, symmetric=True)
+    s4a, z4a = ops.calculate_qparams(mn, mx, qtype=ops.QINT, bits=4, symmetric=False)
+    kw8 = dict(qtype=ops.QINT, bits=8, col_group=C, scale_row_stride=1)
+    mn, mx = ops.minmax(w0, 1, C)
+    s8, _ = ops.calculate_qparams(mn, mx, qtype=ops.QINT, bits=8, symmetric=True)
+    kwf = dict(qtype=ops.QFLOAT, bits=8, col_group=C, scale_row_stride=1)
+    sf, _ = ops.calculate_qparams(mn, mx, qtype=ops.QFLOAT, bits=8, symmetric=True)
+    kwb = dict(qtype=ops.QFLOAT, bits=8, col_group=128, row_group=128, scale_row_stride=C // 128)
+    mn, mx = ops.minmax(w0, 128, 128)
+    sb, _ = ops.calculate_qparams(mn, mx, qtype=ops.QFLOAT, bits=8, symmetric=True)
+    one = lambda: (rnd(),)
+    run("quantize_int4_g128_pack32", one, lambda w: ops.quantize(w, s4, None, codec="pack32", **kw4), 2 * n, 2.515625 * n, 2.6 * n)
+    run("quantize_int4_g128_asym_pack32", one, lambda w: ops.quantize(w, s4a, z4a, codec="pack32", **kw4), 2 * n, 2.53 * n, 2.6 * n)
+    run("quantize_int8_channel_codes", one, lambda w: ops.quantize(w, s8, None, out_dtype=torch.int8, **kw8), 2 * n, 3 * n, 3 * n)
+    run("fake_quantize_int4_g128", one, lambda w: ops.fake_quantize(w, s4, None, out_dtype=torch.bfloat16, **kw4), 2 * n, 4 * n, 4 * n)
+    run("fake_quantize_int8_channel", one, lambda w: ops.fake_quantize(w, s8, None, out_dtype=torch.bfloat16, **kw8), 2 * n, 4 * n, 4 * n)
+    run("quantize_fp8_channel", one, lambda w: ops.quantize(w, sf, None, out_dtype=torch.float8_e4m3fn, **kwf), 2 * n, 3 * n, 3 * n)
+    run("quantize_fp8_block128x128", one, lambda w: ops.quantize(w, sb, None, out_dtype=torch.float8_e4m3fn, **kwb), 2 * n, 3 * n, 3 * n)
+    run("fake_quantize_fp8_block128x128", one, lambda w: ops.fake_quantize(w, sb, None, out_dtype=torch.bfloat16, **kwb), 2 * n, 4 * n, 4 * n)
+    gi = (torch.arange(C, device=dev, dtype=torch.int32) // 128)[torch.randperm(C, generator=g, device=dev)].contiguous()
+    run("quantize_int4_g128_actorder_codes", one, lambda w: ops.quantize(w, s4, None, out_dtype=torch.int8, g_idx=gi, **kw4), 2 * n, 3 * n, 3 * n)
+    run("minmax_group128", one, lambda w: ops.minmax(w, 1, 128), 2 * n, 2 * n, 2 * n)
+    run("minmax_channel", one, lambda w: ops.minmax(w, 1, C), 2 * n, 2 * n, 2 * n)
+    run("minmax_block128x128", one, lambda w: ops.minmax(w, 128, 128), 2 * n, 2 * n, 2 * n)
+    run("minmax_tensor", one, lambda w: ops.minmax(w, R, C), 2 * n, 2 * n, 2 * n)
+    codes = lambda: (ops.quantize(rnd(), s4, None, out_dtype=torch.int8, **kw4),)
+    run("pack_to_int32_4bit", codes, lambda q: ops.pack_int32(q, 4), 2 * n, 1.5 * n, 1.5 * n)
+    run("unpack_from_int32_4bit", lambda: (ops.pack_int32(codes()[0], 4),), lambda p: ops.unpack_int32(p, 4, (R, C)), 2 * n, 1.5 * n, 1.5 * n)
+    masks = lambda: (rnd() > 0,)
+    run("pack_bitmasks", masks, lambda m: ops.pack_bitmasks(m), 2 * n, 1.125 * n, 1.125 * n)
+    run("unpack_bitmasks", lambda: (ops.pack_bitmasks(masks()[0]),), lambda p: ops.unpack_bitmasks(p, [R, C]), 2 * n, 1.125 * n, 1.125 * n)
+    fp4 = lambda: (ops.unpack_fp4(torch.randint(0, 256, (R, C // 2), device=dev, dtype=torch.uint8, generator=g), R, C),)
+    run("pack_fp4_to_uint8", fp4, lambda q: ops.pack_fp4(q), 2 * n, 2.5 * n, 2.5 * n)
+    run("unpack_fp4_from_uint8", lambda: (ops.pack_fp4(fp4()[0]),), lambda p: ops.unpack_fp4(p, R, C), 2 * n, 2.5 * n, 2.5 * n)
+    run("get_24_bytemasks", one, lambda w: ops.sparse24_mask(w), 2 * n, 3 * n, 3 * n)
+    for hn in (128, 4096):
+        sg = (torch.randint(0, 2, (hn,), device=dev, generator=g) * 2 - 1).to(torch.int8)
+        for side, tag in ((0, "weight_input"), (1, "weight_output")):
+            for prec, ptag in ((torch.float32, "f32"), (torch.float64, "f64")):
+                run(f"hadamard_{tag}_n{hn}_{ptag}", one, lambda w, side=side, prec=prec, hn=hn, sg=sg: ops.hadamard(w, hn, signs=sg, side=side, precision=prec),
+                    2 * n, 4 * n, 4 * n)
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -267,6 +339,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-per-config", action="store_true", help="skip the C1-C4 per-scheme table")
     ap.add_argument("--no-other-modes", action="store_true", help="skip timing the other rotation arithmetics")
+    ap.add_argument("--standalone-ops", action="store_true",
+                    help="time the operators as separate calls on an 8192 x 8192 tensor, print that table alone and exit (1 GPU)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
@@ -282,6 +356,13 @@ def main():
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+    if args.standalone_ops:
+        if rank == 0:
+            print(json.dumps({"standalone_ops": standalone_ops_table(dev, peaks()[0]), "tensor": "8192x8192 bf16",
+                              "peak_gbs": peaks()[0], "timing": "CUDA events over CUDA-graph replays, rotating inputs larger than L2"}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     model = parallel.LLAMA3_8B
     shapes = parallel.linear_shapes(model)

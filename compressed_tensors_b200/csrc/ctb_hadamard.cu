@@ -49,14 +49,35 @@ __device__ __forceinline__ void fwht8(A (&v)[8]) {
 template <typename A>
 __device__ __forceinline__ void fwht_lanes(A (&v)[8], int L, int lane_in_block) {
     for (int o = 1; o < L; o <<= 1) {
-        const bool upper = (lane_in_block & o) != 0;
+        const A sgn = (lane_in_block & o) != 0 ? (A)-1 : (A)1;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             A other = shfl_xor<A>(v[i], o);
-            v[i] = upper ? (other - v[i]) : (v[i] + other);
+            v[i] = fma(sgn, v[i], other);  // other - v in the upper half, v + other in the lower: one exact fma
         }
     }
 }
+
+// Sign-bit masks (bit 31 where the +-1 entry is negative) of 8 consecutive entries of the diagonal: multiplying a
+// float by +-1 is flipping its sign bit.  One 8-byte load where the address allows it.
+__device__ __forceinline__ void sign_masks8(const int8_t *signs, int base, uint32_t (&m)[8]) {
+    if (signs == nullptr) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) m[i] = 0u;
+    } else if ((reinterpret_cast<uintptr_t>(signs) & 7u) == 0) {
+        const uint2 w = __ldg(reinterpret_cast<const uint2 *>(signs + base));
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            m[i] = (w.x << (24 - 8 * i)) & 0x80000000u;
+            m[4 + i] = (w.y << (24 - 8 * i)) & 0x80000000u;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) m[i] = signs[base + i] < 0 ? 0x80000000u : 0u;
+    }
+}
+
+__device__ __forceinline__ float flip(float v, uint32_t mask) { return __uint_as_float(__float_as_uint(v) ^ mask); }
 
 struct HArgs {
     const void *x;
@@ -79,12 +100,11 @@ struct HArgs {
 template <typename A, int XF>
 __device__ __forceinline__ void rotate8(const HArgs &a, int64_t c, float (&v)[8]) {
     const int lane_in_block = (int)(c & (a.L - 1));
-    float sg[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) sg[i] = a.signs ? (float)a.signs[lane_in_block * 8 + i] : 1.0f;
+    uint32_t sg[8];
+    sign_masks8(a.signs, lane_in_block * 8, sg);
     A t[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) t[i] = (A)(a.inverse ? v[i] * sg[i] : v[i]);
+    for (int i = 0; i < 8; ++i) t[i] = (A)(a.inverse ? flip(v[i], sg[i]) : v[i]);
     fwht8<A>(t);
     fwht_lanes<A>(t, a.L, lane_in_block);
     if constexpr (sizeof(A) == 8) {
@@ -98,7 +118,7 @@ __device__ __forceinline__ void rotate8(const HArgs &a, int64_t c, float (&v)[8]
     }
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-        if (!a.inverse) v[i] *= sg[i];
+        if (!a.inverse) v[i] = flip(v[i], sg[i]);
         v[i] += 0.0f;  // an exact zero comes out of the reference's matmul as +0.0, whatever the signs
         v[i] = round_to<XF == F_BF16 ? CTB_BF16 : XF == F_F16 ? CTB_F16 : CTB_F32>(v[i]);
     }
@@ -159,8 +179,14 @@ __global__ void __launch_bounds__(kThreads) hadamard_cols_big_kernel(const void 
             float v[8];
             decode8<XF>(load_raw<XF>(x, c0 + ci), v);
             A t[8];
+            if (inverse) {
+                uint32_t sg[8];
+                sign_masks8(signs, ci * 8, sg);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) t[i] = (A)((inverse && signs) ? v[i] * (float)signs[ci * 8 + i] : v[i]);
+                for (int i = 0; i < 8; ++i) v[i] = flip(v[i], sg[i]);
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) t[i] = (A)v[i];
             fwht8<A>(t);
             fwht_lanes<A>(t, 32, lane);
             smem_put8<A>(buf + ci * 8, t);
@@ -196,9 +222,11 @@ __global__ void __launch_bounds__(kThreads) hadamard_cols_big_kernel(const void 
 #pragma unroll
                 for (int i = 0; i < 8; ++i) v[i] = t[i] * sc;
             }
+            uint32_t sg[8];
+            sign_masks8(inverse ? nullptr : signs, ci * 8, sg);
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-                if (!inverse && signs) v[i] *= (float)signs[ci * 8 + i];
+                v[i] = flip(v[i], sg[i]);
                 v[i] += 0.0f;  // an exact zero comes out of the reference's matmul as +0.0, whatever the signs
                 v[i] = round_to<XF == F_BF16 ? CTB_BF16 : XF == F_F16 ? CTB_F16 : CTB_F32>(v[i]);
             }
@@ -474,7 +502,7 @@ __global__ void __launch_bounds__(kThreads) hadamard_rows_fast_kernel(const void
         // shuffle stages: row bits 2, 3, 4 = lane bits 2, 3, 4
 #pragma unroll
         for (int m = 4; m < 32; m <<= 1) {
-            const bool upper = (lane & m) != 0;
+            const A sgn = (lane & m) != 0 ? (A)-1 : (A)1;
 #pragma unroll
             for (int hi = 0; hi < HI; ++hi)
 #pragma unroll
@@ -482,7 +510,7 @@ __global__ void __launch_bounds__(kThreads) hadamard_rows_fast_kernel(const void
 #pragma unroll
                     for (int k = 0; k < CPT; ++k) {
                         const A mine = v[hi][lo][k], other = rq_shfl_xor<A>(mine, m);
-                        v[hi][lo][k] = upper ? other - mine : mine + other;
+                        v[hi][lo][k] = fma(sgn, mine, other);  // other - mine in the upper half, mine + other in the lower
                     }
         }
         if (!live) continue;
