@@ -114,12 +114,13 @@ __device__ __forceinline__ void store_f32(void *p, int dt, int64_t i, float v) {
 
 // Correctly rounded fp32 quotient x / s from r = __frcp_rn(s): one multiply, one exact residual,
 // one corrective fma (Markstein).  Falls back to the first product where the residual is not
-// finite (x or s infinite, s == 0), which is what IEEE division returns there.
+// finite (x or s infinite, s == 0), which is what IEEE division returns there, and for x == +-0, whose
+// residual (+0) + x would turn a negative zero quotient into +0.
 __device__ __forceinline__ float div_by_rcp(float x, float s, float r) {
     float q0 = x * r;
     float e = fmaf(-q0, s, x);
     float q1 = fmaf(e, r, q0);
-    return (fabsf(q1) <= 3.0e38f) ? q1 : q0;
+    return (fabsf(q1) <= 3.0e38f && x != 0.0f) ? q1 : q0;
 }
 
 // torch.clamp: NaN passes through

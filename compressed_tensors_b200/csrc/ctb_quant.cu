@@ -31,7 +31,9 @@ struct QArgs {
     int qk;          // QKind
     int bits;
     int fin, fout;   // Fmt of both sides (generic tier)
-    FastDiv by_cpr;  // chunk -> row (g_idx tier)
+    FastDiv by_cpr;  // chunk -> row (g_idx tier, BLOCK layouts)
+    FastDiv by_row_group, by_col_chunks;  // row -> block row, chunk of a row -> block column
+    int idx32;       // chunk indices fit 31 bits: BLOCK layouts index qparams through the dividers
 };
 
 constexpr int kThreads = 256;
@@ -39,6 +41,10 @@ constexpr int kUnroll = 4;
 
 __device__ __forceinline__ int64_t qp_index_chunk(const QArgs &a, int64_t chunk) {
     if (a.gshift >= 0) return (chunk << 3) >> a.gshift;
+    if (a.idx32) {
+        const uint32_t c = (uint32_t)chunk, row = fastdiv(c, a.by_cpr);
+        return (int64_t)fastdiv(row, a.by_row_group) * a.srs + fastdiv(c - row * (uint32_t)a.cpr, a.by_col_chunks);
+    }
     int64_t row = chunk / a.cpr;
     int64_t col = (chunk - row * a.cpr) << 3;
     return (row / a.row_group) * a.srs + col / a.col_group;
@@ -158,7 +164,7 @@ __global__ void __launch_bounds__(kThreads) qdq_vec8_gidx_kernel(const QArgs a) 
 // other than zero, is recomputed by the float path of the vec8 tier (lean_exact_chunk).
 struct LeanArgs {
     const uint4 *in;
-    const uint16_t *scale;
+    const void *scale;  // bf16 or fp32 (template parameter ST of the kernel)
     const void *zp;
     void *out;
     uint32_t chunks, cpr, srs;
@@ -170,16 +176,16 @@ struct LeanArgs {
 
 // One chunk by the float arithmetic of the vec8 tier, an element at a time (few registers: this is the rare path
 // and its register count would otherwise bound the occupancy of the whole kernel).
-template <int MODE, int QK, int FOUT>
+template <int MODE, int QK, int FOUT, int ST>
 __device__ __noinline__ void lean_exact_chunk(const LeanArgs &a, uint32_t c, uint32_t qi) {
     const bool has_zp = a.zp != nullptr;
-    const QP q = load_qp(a.scale, CTB_BF16, a.zp, a.zdt, nullptr, qi);
+    const QP q = load_qp(a.scale, ST, a.zp, a.zdt, nullptr, qi);
     const uint16_t *x = reinterpret_cast<const uint16_t *>(a.in + c);
     uint64_t acc = 0;
 #pragma unroll 1
     for (int i = 0; i < 8; ++i) {
-        float t = scaled_div<CTB_BF16>(bf16_bits_to_f32(x[i]), q);       // forward.py:471-481
-        if (has_zp) t = round_to<CTB_BF16>(t + q.zp);
+        float t = scaled_div<ST>(bf16_bits_to_f32(x[i]), q);       // forward.py:471-481
+        if (has_zp) t = round_to<ST>(t + q.zp);
         t = clamp_nan(t, a.qmin, a.qmax);
         float val;
         if constexpr (QK == QK_INT) {
@@ -194,10 +200,10 @@ __device__ __noinline__ void lean_exact_chunk(const LeanArgs &a, uint32_t c, uin
             acc |= (uint64_t)code << (8 * i);
             val = (t != t) ? t : e4m3_to_f32((uint8_t)code);
         }
-        if constexpr (MODE == 2) {  // forward.py:504-512, every step rounded to bf16
-            float d = round_to<CTB_BF16>(val);
-            if (has_zp) d = round_to<CTB_BF16>(d - round_to<CTB_BF16>(q.zp));
-            store_f32(a.out, CTB_BF16, (int64_t)c * 8 + i, d * q.s);
+        if constexpr (MODE == 2) {  // forward.py:504-512, every step rounded to the scale dtype, the result to bf16
+            float d = round_to<ST>(val);
+            if (has_zp) d = round_to<ST>(d - round_to<ST>(q.zp));
+            store_f32(a.out, CTB_BF16, (int64_t)c * 8 + i, round_to<ST>(d * q.s));
         }
     }
     if constexpr (MODE == 0) {
@@ -233,8 +239,8 @@ __device__ __forceinline__ uint32_t int8_codes_of(uint32_t u0, uint32_t u1) {
 constexpr int kLeanUnroll = 2;
 
 // 32 registers (a few bytes of spill in the rare path): eight resident blocks per SM measured faster than six at 40
-template <int MODE, int QK, int FOUT>
-__global__ void __launch_bounds__(kThreads, 8) quant_bf16_lean_kernel(const __grid_constant__ LeanArgs a) {
+template <int MODE, int QK, int FOUT, int ST>
+__global__ void __launch_bounds__(kThreads, ST == CTB_BF16 ? 8 : 6) quant_bf16_lean_kernel(const __grid_constant__ LeanArgs a) {
     const bool has_zp = a.zp != nullptr;
     const __nv_bfloat162 lo2 = __float2bfloat162_rn(a.qmin), hi2 = __float2bfloat162_rn(a.qmax);
     const uint32_t stride = gridDim.x * (uint32_t)(kThreads * kLeanUnroll);
@@ -256,16 +262,82 @@ __global__ void __launch_bounds__(kThreads, 8) quant_bf16_lean_kernel(const __gr
                 const uint32_t row = fastdiv(c, a.by_cpr);
                 qi = fastdiv(row, a.by_row_group) * a.srs + fastdiv(c - row * a.cpr, a.by_col_chunks);
             }
-            const uint32_t sbits = __ldg(a.scale + qi);
+            uint32_t sbits;  // the scale's bits (bf16: low half)
+            if constexpr (ST == CTB_BF16) sbits = __ldg(reinterpret_cast<const uint16_t *>(a.scale) + qi);
+            else sbits = __ldg(reinterpret_cast<const uint32_t *>(a.scale) + qi);
             const uint32_t w[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
-            bool exact = ((sbits >> 7) & 0xFFu) - 28u > 197u;  // biased exponent outside [28, 225]
+            bool exact = ((sbits >> (ST == CTB_BF16 ? 7 : 23)) & 0xFFu) - 28u > 197u;  // biased exponent outside [28, 225]
             float zf = 0.0f;
             if (has_zp) {
                 zf = load_f32(a.zp, a.zdt, qi);
                 if constexpr (QK == QK_FP8) exact = exact || zf != 0.0f;
             }
             if (exact) {
-                lean_exact_chunk<MODE, QK, FOUT>(a, c, qi);
+                lean_exact_chunk<MODE, QK, FOUT, ST>(a, c, qi);
+                continue;
+            }
+            if constexpr (ST == CTB_F32) {
+                // fp32 scale: compute dtype fp32.  x / s is the correctly rounded quotient (reciprocal + Markstein step),
+                // the zero point an fp32 add, rounding to the grid by the convert instructions.
+                const float sc = __uint_as_float(sbits), r = __frcp_rn(sc);
+                float q[8];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    q[2 * k] = div_by_rcp(__uint_as_float(w[k] << 16), sc, r);
+                    q[2 * k + 1] = div_by_rcp(__uint_as_float(w[k] & 0xFFFF0000u), sc, r);
+                }
+                if (has_zp) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) q[i] += zf;
+                }
+                if constexpr (QK == QK_INT) {
+                    if constexpr (MODE == 0) {
+                        int code[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) code[i] = __float2int_rn(fminf(fmaxf(q[i], a.qmin), a.qmax));
+                        const uint32_t b0 = prmt_b32(prmt_b32(code[0], code[1], 0x0040), prmt_b32(code[2], code[3], 0x0040), 0x5410);
+                        const uint32_t b1 = prmt_b32(prmt_b32(code[4], code[5], 0x0040), prmt_b32(code[6], code[7], 0x0040), 0x5410);
+                        if constexpr (FOUT == F_PACK4) {  // (code + 8) & 15 == (code & 15) ^ 8; then two nibbles per byte
+                            const uint32_t n0 = (b0 & 0x0F0F0F0Fu) ^ 0x08080808u, n1 = (b1 & 0x0F0F0F0Fu) ^ 0x08080808u;
+                            const uint32_t t0 = n0 | ((n0 >> 4) & 0xF0F0F0F0u), t1 = n1 | ((n1 >> 4) & 0xF0F0F0F0u);
+                            st_stream4((char *)a.out + (size_t)c * 4, prmt_b32(t0, t1, 0x6420));
+                        } else if constexpr (FOUT == F_PACK8) {
+                            st_stream8((char *)a.out + (size_t)c * 8, make_uint2(b0 ^ 0x80808080u, b1 ^ 0x80808080u));
+                        } else {
+                            st_stream8((char *)a.out + (size_t)c * 8, make_uint2(b0, b1));
+                        }
+                    } else {
+                        uint32_t o[4];
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            float d0 = rintf(clamp_nan(q[2 * k], a.qmin, a.qmax)), d1 = rintf(clamp_nan(q[2 * k + 1], a.qmin, a.qmax));
+                            if (has_zp) { d0 -= zf; d1 -= zf; }
+                            o[k] = bf162_as_u32(__floats2bfloat162_rn(d0 * sc, d1 * sc));
+                        }
+                        st_stream((char *)a.out + (size_t)c * 16, make_uint4(o[0], o[1], o[2], o[3]));
+                    }
+                } else {
+                    uint32_t code[4];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        code[k] = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(q[2 * k], q[2 * k + 1]), __NV_SATFINITE, __NV_E4M3);
+                    const uint32_t c0 = code[0] | (code[1] << 16), c1 = code[2] | (code[3] << 16);
+                    if constexpr (MODE == 0) {
+                        if (((((c0 & 0x7F7F7F7Fu) + 0x01010101u) | ((c1 & 0x7F7F7F7Fu) + 0x01010101u)) & 0x80808080u) != 0) {
+                            lean_exact_chunk<MODE, QK, FOUT, ST>(a, c, qi);  // a NaN code must carry its input's sign
+                            continue;
+                        }
+                        st_stream8((char *)a.out + (size_t)c * 8, make_uint2(c0, c1));
+                    } else {
+                        uint32_t o[4];
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const float2 f = __half22float2(__half2(__nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)code[k], __NV_E4M3)));
+                            o[k] = bf162_as_u32(__floats2bfloat162_rn(f.x * sc, f.y * sc));
+                        }
+                        st_stream((char *)a.out + (size_t)c * 16, make_uint4(o[0], o[1], o[2], o[3]));
+                    }
+                }
                 continue;
             }
             const float r = rcp_approx(__uint_as_float(sbits << 16));
@@ -312,7 +384,7 @@ __global__ void __launch_bounds__(kThreads, 8) quant_bf16_lean_kernel(const __gr
                 if constexpr (MODE == 0) {
                     // a NaN code (0x7F under the sign bit) must carry its input's sign: rare, take the float path
                     if (((((c0 & 0x7F7F7F7Fu) + 0x01010101u) | ((c1 & 0x7F7F7F7Fu) + 0x01010101u)) & 0x80808080u) != 0) {
-                        lean_exact_chunk<MODE, QK, FOUT>(a, c, qi);
+                        lean_exact_chunk<MODE, QK, FOUT, ST>(a, c, qi);
                         continue;
                     }
                     st_stream8((char *)a.out + (size_t)c * 8, make_uint2(c0, c1));
@@ -535,7 +607,9 @@ static int validate(const ctb_qdesc *d, const void *in, const void *scale, const
 
 template <int MODE, int T, int TS, int QK, int FIN, int FOUT>
 static int launch_vec8(const QArgs &a, cudaStream_t st) {
-    int grid = grid_for(a.chunks, (int64_t)kThreads * kUnroll, 8);
+    // dequantize writes 2-8x what it reads: many more blocks than are resident (they sweep the output as one moving
+    // window) measured faster than a persistent grid, as for the batched dequantize kernel
+    int grid = grid_for(a.chunks, (int64_t)kThreads * kUnroll, MODE == 1 ? 256 : 8);
     qdq_vec8_kernel<MODE, T, TS, QK, FIN, FOUT><<<grid, kThreads, 0, st>>>(a);
     return after_launch("qdq_vec8_kernel");
 }
@@ -575,18 +649,20 @@ static int dispatch_vec8(int mode, const QArgs &a, cudaStream_t st, bool *handle
 }
 
 template <int MODE, int QK, int FOUT>
-static int launch_lean(const LeanArgs &l, cudaStream_t st) {
-    quant_bf16_lean_kernel<MODE, QK, FOUT><<<grid_for(l.chunks, (int64_t)kThreads * kLeanUnroll, 16), kThreads, 0, st>>>(l);
+static int launch_lean(const LeanArgs &l, int sdt, cudaStream_t st) {
+    const int grid = grid_for(l.chunks, (int64_t)kThreads * kLeanUnroll, sdt == CTB_BF16 ? 16 : 12);
+    if (sdt == CTB_BF16) quant_bf16_lean_kernel<MODE, QK, FOUT, CTB_BF16><<<grid, kThreads, 0, st>>>(l);
+    else quant_bf16_lean_kernel<MODE, QK, FOUT, CTB_F32><<<grid, kThreads, 0, st>>>(l);
     return after_launch("quant_bf16_lean_kernel");
 }
 
-// bf16 tensor with a bf16 scale: quantize to packed int4 / int8 / e4m3 codes, or fake-quantize back to bf16
+// bf16 tensor with a bf16 or fp32 scale: quantize to packed int4 / int8 / e4m3 codes, or fake-quantize back to bf16
 static int dispatch_lean(int mode, const QArgs &a, cudaStream_t st, bool *handled) {
     *handled = false;
-    if (a.xdt != CTB_BF16 || a.sdt != CTB_BF16 || a.gs || a.chunks >= (1LL << 31) || a.srs >= (1LL << 31)) return CTB_OK;
+    if (a.xdt != CTB_BF16 || !(a.sdt == CTB_BF16 || a.sdt == CTB_F32) || a.gs || a.chunks >= (1LL << 31) || a.srs >= (1LL << 31)) return CTB_OK;
     if (!(mode == 0 || (mode == 2 && a.fout == F_BF16)) || a.qk == QK_FP4) return CTB_OK;
     LeanArgs l{};
-    l.in = (const uint4 *)a.in; l.scale = (const uint16_t *)a.scale; l.zp = a.zp; l.out = a.out;
+    l.in = (const uint4 *)a.in; l.scale = a.scale; l.zp = a.zp; l.out = a.out;
     l.chunks = (uint32_t)a.chunks; l.cpr = (uint32_t)a.cpr; l.srs = (uint32_t)a.srs;
     l.shift = a.gshift >= 3 ? a.gshift - 3 : -1;
     l.by_cpr = make_fastdiv((uint32_t)a.cpr);
@@ -594,12 +670,12 @@ static int dispatch_lean(int mode, const QArgs &a, cudaStream_t st, bool *handle
     l.by_col_chunks = make_fastdiv((uint32_t)(a.col_group / 8));
     l.qmin = a.qmin; l.qmax = a.qmax; l.zdt = a.zdt;
     *handled = true;
-    if (mode == 0 && a.qk == QK_INT && a.fout == F_PACK4) return launch_lean<0, QK_INT, F_PACK4>(l, st);
-    if (mode == 0 && a.qk == QK_INT && a.fout == F_PACK8) return launch_lean<0, QK_INT, F_PACK8>(l, st);
-    if (mode == 0 && a.qk == QK_INT && a.fout == F_I8) return launch_lean<0, QK_INT, F_I8>(l, st);
-    if (mode == 0 && a.qk == QK_FP8 && a.fout == F_E4M3) return launch_lean<0, QK_FP8, F_E4M3>(l, st);
-    if (mode == 2 && a.qk == QK_INT) return launch_lean<2, QK_INT, F_BF16>(l, st);
-    if (mode == 2 && a.qk == QK_FP8) return launch_lean<2, QK_FP8, F_BF16>(l, st);
+    if (mode == 0 && a.qk == QK_INT && a.fout == F_PACK4) return launch_lean<0, QK_INT, F_PACK4>(l, a.sdt, st);
+    if (mode == 0 && a.qk == QK_INT && a.fout == F_PACK8) return launch_lean<0, QK_INT, F_PACK8>(l, a.sdt, st);
+    if (mode == 0 && a.qk == QK_INT && a.fout == F_I8) return launch_lean<0, QK_INT, F_I8>(l, a.sdt, st);
+    if (mode == 0 && a.qk == QK_FP8 && a.fout == F_E4M3) return launch_lean<0, QK_FP8, F_E4M3>(l, a.sdt, st);
+    if (mode == 2 && a.qk == QK_INT) return launch_lean<2, QK_INT, F_BF16>(l, a.sdt, st);
+    if (mode == 2 && a.qk == QK_FP8) return launch_lean<2, QK_FP8, F_BF16>(l, a.sdt, st);
     *handled = false;
     return CTB_OK;
 }
@@ -654,6 +730,12 @@ static int run(int mode, const ctb_qdesc *d, const void *in, const void *scale, 
         a.chunks = d->rows * d->cols / 8;
         a.cpr = d->cols / 8;
         a.gshift = -1;
+        a.idx32 = a.chunks < (1LL << 31);
+        if (a.idx32) {
+            a.by_cpr = make_fastdiv((uint32_t)a.cpr);
+            a.by_row_group = make_fastdiv((uint32_t)d->row_group);
+            a.by_col_chunks = make_fastdiv((uint32_t)(d->col_group / 8));
+        }
         bool flat = d->row_group == 1 && (d->scale_row_stride == d->cols / d->col_group);
         if (flat && (d->col_group & (d->col_group - 1)) == 0) {
             int sh = 0;

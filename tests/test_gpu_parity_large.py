@@ -1,5 +1,7 @@
 """Parity of the CUDA path against the CPU oracle on seeded inputs at sizes the oracle finishes in
 seconds, plus size-independent properties at the benchmark's full tensor sizes."""
+import itertools
+
 import pytest
 import torch
 
@@ -435,8 +437,8 @@ def _same_bits_or_both_nan(a, b, what):
 
 
 def test_bf16_quantize_and_fake_quantize_kernels_match_oracle(ops, orc):
-    """quantize (packed int4 / int8 / e4m3 codes) and fake_quantize of a bf16 tensor with bf16 scales, the path that
-    stays in packed bf16x2 arithmetic, against the oracle: rounding ties, both clamp ends, -0.0 results, infinities,
+    """quantize (packed int4 / int8 / e4m3 codes) and fake_quantize of a bf16 tensor with bf16 scales (the path that
+    stays in packed bf16x2 arithmetic) and with fp32 scales (fp32 quotients), against the oracle: rounding ties, both clamp ends, -0.0 results, infinities,
     NaNs where the reference defines the result, zero points, scales outside the fast range (tiny, huge, zero,
     infinite, NaN), GROUP / CHANNEL / BLOCK layouts with power-of-two and other group sizes"""
     g = torch.Generator().manual_seed(77)
@@ -476,10 +478,13 @@ def test_bf16_quantize_and_fake_quantize_kernels_match_oracle(ops, orc):
                 nz = torch.zeros(scale.shape, dtype=torch.float32)
                 nz.reshape(-1)[0] = 2.0  # an fp8 zero point other than zero: float path
                 zps.append(nz.to(torch.float8_e4m3fn))
-            for zi, zp in enumerate(zps):
+            # the same scales in fp32 (compute dtype fp32), exact and perturbed so that the quotients are not bf16-friendly
+            jitter = 1.0 + 1e-3 * torch.rand(scale.shape, generator=g)
+            variants = [(scale, "bf16 scale"), (scale.float(), "fp32 scale"), (scale.float() * jitter, "fp32 scale, perturbed")]
+            for (scale, stag), (zi, zp) in itertools.product(variants, enumerate(zps)):
                 kw = dict(qtype=qtype, bits=bits, col_group=cg, row_group=rg, scale_row_stride=srs)
                 dz = None if zp is None else zp.cuda()
-                what = f"{name} bits={bits} {'int' if is_int else 'fp8'} zp#{zi}"
+                what = f"{name} bits={bits} {'int' if is_int else 'fp8'} zp#{zi} {stag}"
                 code_dt = torch.int8 if is_int else torch.float8_e4m3fn
                 want = orc.quantize(xb, scale, zp, out_dtype=code_dt, **kw)
                 got = ops.quantize(xb.cuda(), scale.cuda(), dz, out_dtype=code_dt, **kw)
