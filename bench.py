@@ -299,6 +299,20 @@ def standalone_ops_table(dev, peak, size=8192):
     run("quantize_fp8_channel", one, lambda w: ops.quantize(w, sf, None, out_dtype=torch.float8_e4m3fn, **kwf), 2 * n, 3 * n, 3 * n)
     run("quantize_fp8_block128x128", one, lambda w: ops.quantize(w, sb, None, out_dtype=torch.float8_e4m3fn, **kwb), 2 * n, 3 * n, 3 * n)
     run("fake_quantize_fp8_block128x128", one, lambda w: ops.fake_quantize(w, sb, None, out_dtype=torch.bfloat16, **kwb), 2 * n, 4 * n, 4 * n)
+    s8f, sff = s8.float(), sf.float()
+    run("quantize_int8_channel_fp32_scale", one, lambda w: ops.quantize(w, s8f, None, out_dtype=torch.int8, **kw8), 2 * n, 3 * n, 3 * n)
+    run("quantize_fp8_channel_fp32_scale", one, lambda w: ops.quantize(w, sff, None, out_dtype=torch.float8_e4m3fn, **kwf), 2 * n, 3 * n, 3 * n)
+    run("fake_quantize_fp8_channel_fp32_scale", one, lambda w: ops.fake_quantize(w, sff, None, out_dtype=torch.bfloat16, **kwf), 2 * n, 4 * n, 4 * n)
+    run("dequantize_int4_g128_pack32", lambda: (ops.quantize(rnd(), s4, None, codec="pack32", **kw4),),
+        lambda p: ops.dequantize(p, s4, None, out_dtype=torch.bfloat16, codec="pack32", cols=C, **kw4), 2 * n, 2.515625 * n, 2.6 * n)
+    run("dequantize_int4_g128_asym_pack32", lambda: (ops.quantize(rnd(), s4a, z4a, codec="pack32", **kw4),),
+        lambda p: ops.dequantize(p, s4a, z4a, out_dtype=torch.bfloat16, codec="pack32", cols=C, **kw4), 2 * n, 2.53 * n, 2.6 * n)
+    run("dequantize_int8_channel", lambda: (ops.quantize(rnd(), s8, None, out_dtype=torch.int8, **kw8),),
+        lambda q: ops.dequantize(q, s8, None, out_dtype=torch.bfloat16, **kw8), 2 * n, 3 * n, 3 * n)
+    run("dequantize_fp8_channel", lambda: (ops.quantize(rnd(), sf, None, out_dtype=torch.float8_e4m3fn, **kwf),),
+        lambda q: ops.dequantize(q, sf, None, out_dtype=torch.bfloat16, **kwf), 2 * n, 3 * n, 3 * n)
+    run("dequantize_fp8_block128x128", lambda: (ops.quantize(rnd(), sb, None, out_dtype=torch.float8_e4m3fn, **kwb),),
+        lambda q: ops.dequantize(q, sb, None, out_dtype=torch.bfloat16, **kwb), 2 * n, 3 * n, 3 * n)
     gi = (torch.arange(C, device=dev, dtype=torch.int32) // 128)[torch.randperm(C, generator=g, device=dev)].contiguous()
     run("quantize_int4_g128_actorder_codes", one, lambda w: ops.quantize(w, s4, None, out_dtype=torch.int8, g_idx=gi, **kw4), 2 * n, 3 * n, 3 * n)
     run("minmax_group128", one, lambda w: ops.minmax(w, 1, 128), 2 * n, 2 * n, 2 * n)
