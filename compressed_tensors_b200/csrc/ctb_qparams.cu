@@ -203,6 +203,24 @@ __global__ void __launch_bounds__(kThreads) minmax_row_kernel(const void *x, int
     }
 }
 
+// (b16) CHANNEL / TOKEN for bf16 / f16 rows of up to 4096 chunks: a warp per row, no block barrier; the lanes read
+//       32 consecutive chunks per step (512 contiguous bytes), four steps in flight
+template <int F>
+__global__ void __launch_bounds__(kThreads) minmax_warprow16_kernel(const uint4 *x, int64_t rows, int cpr, uint16_t *out_min, uint16_t *out_max) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warps = (int64_t)gridDim.x * (kThreads / 32);
+    for (int64_t r = (int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5); r < rows; r += warps) {
+        const uint4 *row = x + r * cpr;
+        uint32_t mn2 = Packed16<F>::kPosInf, mx2 = Packed16<F>::kNegInf;
+#pragma unroll 4
+        for (int c = lane; c < cpr; c += 32) chunk_minmax16<F>(row, c, mn2, mx2);
+        uint32_t k = fold_minmax16<F>(mn2, mx2);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) k = min2<F>(k, __shfl_xor_sync(0xFFFFFFFFu, k, o));
+        if (lane == 0) { out_min[r] = (uint16_t)k; out_max[r] = (uint16_t)((k >> 16) ^ 0x8000u); }
+    }
+}
+
 // (c) one tile = the whole tensor: per-block partials into the workspace, then a one-block finish
 template <int F>
 __global__ void __launch_bounds__(kThreads) minmax_flat_kernel(const void *x, int dt, int64_t n, float *partial) {
@@ -213,7 +231,7 @@ __global__ void __launch_bounds__(kThreads) minmax_flat_kernel(const void *x, in
             chunk_minmax<F>(x, c, mn, mx);
     } else {
         uint32_t mn2 = Packed16<F>::kPosInf, mx2 = Packed16<F>::kNegInf;
-#pragma unroll 4
+#pragma unroll 8
         for (int64_t c = (int64_t)blockIdx.x * kThreads + threadIdx.x; c < chunks; c += (int64_t)gridDim.x * kThreads)
             chunk_minmax16<F>(x, c, mn2, mx2);
         unpack_minmax16<F>(mn2, mx2, mn, mx);
@@ -352,6 +370,12 @@ extern "C" int ctb_minmax(const void *x, int32_t dt, int64_t rows, int64_t cols,
             else if (F == F_F16) minmax_group_kernel<F_F16><<<grid, kThreads, 0, st>>>(x, chunks, (int)L, dt, out_min, out_max);
             else minmax_group_kernel<F_F32><<<grid, kThreads, 0, st>>>(x, chunks, (int)L, dt, out_min, out_max);
             return after_launch("minmax_group_kernel");
+        }
+        if (cg == cols && F != F_F32 && cols / 8 <= 4096) {
+            const int grid = grid_for(rows, kThreads / 32, 8);
+            if (F == F_BF16) minmax_warprow16_kernel<F_BF16><<<grid, kThreads, 0, st>>>((const uint4 *)x, rows, (int)(cols / 8), (uint16_t *)out_min, (uint16_t *)out_max);
+            else minmax_warprow16_kernel<F_F16><<<grid, kThreads, 0, st>>>((const uint4 *)x, rows, (int)(cols / 8), (uint16_t *)out_min, (uint16_t *)out_max);
+            return after_launch("minmax_warprow16_kernel");
         }
         if (cg == cols) {
             int grid = grid_for(rows, 1, 64);
