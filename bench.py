@@ -315,6 +315,8 @@ def standalone_ops_table(dev, peak, size=8192):
         lambda q: ops.dequantize(q, sb, None, out_dtype=torch.bfloat16, **kwb), 2 * n, 3 * n, 3 * n)
     gi = (torch.arange(C, device=dev, dtype=torch.int32) // 128)[torch.randperm(C, generator=g, device=dev)].contiguous()
     run("quantize_int4_g128_actorder_codes", one, lambda w: ops.quantize(w, s4, None, out_dtype=torch.int8, g_idx=gi, **kw4), 2 * n, 3 * n, 3 * n)
+    run("dequantize_int4_g128_actorder_pack32", lambda: (ops.quantize(rnd(), s4, None, codec="pack32", g_idx=gi, **kw4),),
+        lambda p: ops.dequantize(p, s4, None, out_dtype=torch.bfloat16, codec="pack32", cols=C, g_idx=gi, **kw4), 2 * n, 2.515625 * n, 2.6 * n)
     run("minmax_group128", one, lambda w: ops.minmax(w, 1, 128), 2 * n, 2 * n, 2 * n)
     run("minmax_channel", one, lambda w: ops.minmax(w, 1, C), 2 * n, 2 * n, 2 * n)
     run("minmax_block128x128", one, lambda w: ops.minmax(w, 128, 128), 2 * n, 2 * n, 2 * n)

@@ -119,32 +119,37 @@ __global__ void __launch_bounds__(kThreads) qdq_vec8_kernel(const QArgs a) {
 // element that is "column c uses qparam g_idx[c] of its row".  Loads and stores stay 8 elements wide; the eight
 // group numbers of a chunk are two 16-byte loads and the qparams eight small gathers that hit in L1 / L2.
 template <int MODE, int T, int TS, int QK, int FIN, int FOUT>
-__global__ void __launch_bounds__(kThreads) qdq_vec8_gidx_kernel(const QArgs a) {
+__device__ __forceinline__ void gidx_chunk_float(const QArgs &a, uint32_t c, uint32_t row, uint32_t col0) {
     const bool has_zp = a.zp != nullptr;
+    const Raw8 raw = load_raw<FIN>(a.in, c);
+    const int4 g0 = __ldg(reinterpret_cast<const int4 *>(a.g_idx + col0)), g1 = __ldg(reinterpret_cast<const int4 *>(a.g_idx + col0 + 4));
+    const int g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+    const int64_t base = (int64_t)row * a.srs;
+    float v[8];
+    decode8<FIN>(raw, v);
+    QP q[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) q[i] = load_qp(a.scale, a.sdt, a.zp, a.zdt, a.gs, base + g[i]);
+    if constexpr (MODE != 1) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = quant_prepare1<T>(v[i], q[i], has_zp, a.qmin, a.qmax);
+    }
+    if constexpr (MODE == 0) {
+        encode_store8<QK, FOUT>(a.out, c, v);
+    } else {
+        if constexpr (MODE == 2) round8<QK>(v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = dequant1<TS>(v[i], q[i], has_zp);
+        store8_float<FOUT>(a.out, c, v);
+    }
+}
+
+template <int MODE, int T, int TS, int QK, int FIN, int FOUT>
+__global__ void __launch_bounds__(kThreads) qdq_vec8_gidx_kernel(const QArgs a) {
     const FastDiv by_cpr = a.by_cpr;
     for (uint32_t c = blockIdx.x * kThreads + threadIdx.x; c < (uint32_t)a.chunks; c += gridDim.x * kThreads) {
-        const Raw8 raw = load_raw<FIN>(a.in, c);
-        const uint32_t row = fastdiv(c, by_cpr), col0 = (c - row * (uint32_t)a.cpr) * 8;
-        const int4 g0 = __ldg(reinterpret_cast<const int4 *>(a.g_idx + col0)), g1 = __ldg(reinterpret_cast<const int4 *>(a.g_idx + col0 + 4));
-        const int g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
-        const int64_t base = (int64_t)row * a.srs;
-        float v[8];
-        decode8<FIN>(raw, v);
-        QP q[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) q[i] = load_qp(a.scale, a.sdt, a.zp, a.zdt, a.gs, base + g[i]);
-        if constexpr (MODE != 1) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) v[i] = quant_prepare1<T>(v[i], q[i], has_zp, a.qmin, a.qmax);
-        }
-        if constexpr (MODE == 0) {
-            encode_store8<QK, FOUT>(a.out, c, v);
-        } else {
-            if constexpr (MODE == 2) round8<QK>(v);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) v[i] = dequant1<TS>(v[i], q[i], has_zp);
-            store8_float<FOUT>(a.out, c, v);
-        }
+        const uint32_t row = fastdiv(c, by_cpr);
+        gidx_chunk_float<MODE, T, TS, QK, FIN, FOUT>(a, c, row, (c - row * (uint32_t)a.cpr) * 8);
     }
 }
 
@@ -397,6 +402,126 @@ __global__ void __launch_bounds__(kThreads, ST == CTB_BF16 ? 8 : 6) quant_bf16_l
                         o[k] = bf162_as_u32(__floats2bfloat162_rn(f.x * s, f.y * s));
                     }
                     st_stream((char *)a.out + (size_t)c * 16, make_uint4(o[0], o[1], o[2], o[3]));
+                }
+            }
+        }
+    }
+}
+
+// ---- activation-ordered groups on the packed tier -----------------------------------------------------------
+// bf16 tensor, bf16 scales, int codes.  A block takes a row: the row's qparams (one per group, a few hundred) are
+// staged in shared memory once -- reciprocal, scale and zero point ready to use -- and every element then costs one
+// shared-memory lookup by its group number instead of a global gather, a reciprocal and a range check.  The
+// arithmetic is that of the packed tier, with a different scale in each half of a bf16x2 register.  A row with a
+// scale outside [2^-99, 2^99) is redone by the float path (gidx_chunk_float).
+struct GidxSmem {
+    float r;      // 1 / scale (rcp.approx: within 1 ulp, see the packed tier)
+    uint32_t sz;  // scale bits | zero point (bf16 bits) << 16
+};
+
+constexpr int kGidxThreads = 128;  // short rows per block: more blocks in different phases hide the per-row barriers
+
+template <int MODE, int FC>  // FC: format of the codes (F_PACK4 / F_I8); unused for fake quantize
+__global__ void __launch_bounds__(kGidxThreads) gidx_row_kernel(const QArgs a) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    GidxSmem *qp = reinterpret_cast<GidxSmem *>(smem_raw);  // [srs]
+    const bool has_zp = a.zp != nullptr;
+    const uint32_t srs = (uint32_t)a.srs, cpr = (uint32_t)a.cpr;
+    const __nv_bfloat162 lo2 = __float2bfloat162_rn(a.qmin), hi2 = __float2bfloat162_rn(a.qmax);
+    const uint16_t *scale = reinterpret_cast<const uint16_t *>(a.scale);
+    for (uint32_t row = blockIdx.x; row < (uint32_t)a.rows; row += gridDim.x) {
+        __syncthreads();  // the previous row is done with the table
+        int bad = 0;
+        for (uint32_t j = threadIdx.x; j < srs; j += kGidxThreads) {
+            const uint32_t sb = __ldg(scale + (size_t)row * srs + j);
+            bad |= ((sb >> 7) & 0xFFu) - 28u > 197u;
+            const float zf = has_zp ? load_f32(a.zp, a.zdt, (int64_t)row * srs + j) : 0.0f;
+            const __nv_bfloat16 zb = __float2bfloat16_rn(zf);
+            qp[j].r = rcp_approx(__uint_as_float(sb << 16));
+            qp[j].sz = sb | ((uint32_t)(*reinterpret_cast<const uint16_t *>(&zb)) << 16);
+        }
+        const bool exact = __syncthreads_or(bad) != 0;
+        for (uint32_t cc = threadIdx.x; cc < cpr; cc += kGidxThreads) {
+            const uint32_t c = row * cpr + cc, col0 = cc * 8;
+            if (exact) {
+                if constexpr (MODE == 0) gidx_chunk_float<0, CTB_BF16, CTB_F32, QK_INT, F_BF16, FC>(a, c, row, col0);
+                else if constexpr (MODE == 1) gidx_chunk_float<1, CTB_F32, CTB_BF16, QK_INT, FC, F_BF16>(a, c, row, col0);
+                else gidx_chunk_float<2, CTB_BF16, CTB_BF16, QK_INT, F_BF16, F_BF16>(a, c, row, col0);
+                continue;
+            }
+            const int4 g0 = __ldg(reinterpret_cast<const int4 *>(a.g_idx + col0)), g1 = __ldg(reinterpret_cast<const int4 *>(a.g_idx + col0 + 4));
+            const int gi[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+            float r[8];
+            uint32_t s2[4], z2[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {  // an out-of-range group number reads the last entry instead of faulting
+                const GidxSmem e0 = qp[min((uint32_t)gi[2 * k], srs - 1)], e1 = qp[min((uint32_t)gi[2 * k + 1], srs - 1)];
+                r[2 * k] = e0.r;
+                r[2 * k + 1] = e1.r;
+                s2[k] = prmt_b32(e0.sz, e1.sz, 0x5410);
+                z2[k] = prmt_b32(e0.sz, e1.sz, 0x7632);
+            }
+            if constexpr (MODE == 1) {
+                uint32_t p[4];  // the codes as bf16 pairs, exactly
+                if constexpr (FC == F_PACK4) {
+                    const uint32_t word = ld_stream4(reinterpret_cast<const uint32_t *>(a.in) + c);
+                    uint32_t t[4];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) t[k] = ((word >> (4 * k)) & 0x000F000Fu) | 0x43004300u;  // 128 + nibble; low half k, high half k + 4
+                    p[0] = prmt_b32(t[0], t[1], 0x5410); p[1] = prmt_b32(t[2], t[3], 0x5410);
+                    p[2] = prmt_b32(t[0], t[1], 0x7632); p[3] = prmt_b32(t[2], t[3], 0x7632);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)  // (128 + nibble) - 136 = code, exact
+                        p[k] = bf162_as_u32(__hsub2(u32_as_bf162(p[k]), u32_as_bf162(0x43084308u)));
+                } else {
+                    const uint2 w = ld_stream8(reinterpret_cast<const uint2 *>(a.in) + c);
+                    const uint32_t ww[2] = {w.x, w.y};
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const uint32_t h = ww[k >> 1] >> (16 * (k & 1));
+                        p[k] = bf162_as_u32(__floats2bfloat162_rn((float)(int)(int8_t)(h & 0xFFu), (float)(int)(int8_t)((h >> 8) & 0xFFu)));
+                    }
+                }
+                uint32_t o[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    __nv_bfloat162 t = u32_as_bf162(p[k]);
+                    if (has_zp) t = __hsub2(t, u32_as_bf162(z2[k]));
+                    o[k] = bf162_as_u32(__hmul2(t, u32_as_bf162(s2[k])));
+                }
+                st_stream((char *)a.out + (size_t)c * 16, make_uint4(o[0], o[1], o[2], o[3]));
+            } else {
+                const uint4 raw = ld_stream(reinterpret_cast<const uint4 *>(a.in) + c);
+                const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+                uint32_t o[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    __nv_bfloat162 q = __floats2bfloat162_rn(__uint_as_float(w[k] << 16) * r[2 * k], __uint_as_float(w[k] & 0xFFFF0000u) * r[2 * k + 1]);
+                    if (has_zp) q = __hadd2(q, u32_as_bf162(z2[k]));
+                    if constexpr (MODE == 0) q = __hmin2(__hmax2(q, lo2), hi2);
+                    else q = __hmin2_nan(__hmax2_nan(q, lo2), hi2);
+                    const uint32_t sign = bf162_as_u32(q) & 0x80008000u;
+                    const __nv_bfloat162 m = u32_as_bf162(sign | 0x43004300u);
+                    const __nv_bfloat162 uu = __hadd2(q, m);  // |uu| in [128, 256]: the add rounds half to even to an integer
+                    if constexpr (MODE == 0) {
+                        o[k] = bf162_as_u32(uu);
+                    } else {
+                        __nv_bfloat162 t = u32_as_bf162(bf162_as_u32(__hsub2(uu, m)) | sign);
+                        if (has_zp) t = __hsub2(t, u32_as_bf162(z2[k]));
+                        o[k] = bf162_as_u32(__hmul2(t, u32_as_bf162(s2[k])));
+                    }
+                }
+                if constexpr (MODE == 2) {
+                    st_stream((char *)a.out + (size_t)c * 16, make_uint4(o[0], o[1], o[2], o[3]));
+                } else {
+                    const uint32_t c0 = int8_codes_of(o[0], o[1]), c1 = int8_codes_of(o[2], o[3]);
+                    if constexpr (FC == F_I8) {
+                        st_stream8((char *)a.out + (size_t)c * 8, make_uint2(c0, c1));
+                    } else {  // (code + 8) & 15 == (code & 15) ^ 8, two nibbles per byte
+                        const uint32_t n0 = (c0 & 0x0F0F0F0Fu) ^ 0x08080808u, n1 = (c1 & 0x0F0F0F0Fu) ^ 0x08080808u;
+                        const uint32_t t0 = n0 | ((n0 >> 4) & 0xF0F0F0F0u), t1 = n1 | ((n1 >> 4) & 0xF0F0F0F0u);
+                        st_stream4((char *)a.out + (size_t)c * 4, prmt_b32(t0, t1, 0x6420));
+                    }
                 }
             }
         }
@@ -690,6 +815,21 @@ static int dispatch_lean(int mode, const QArgs &a, cudaStream_t st, bool *handle
 // group-strategy int codes of a 16-bit tensor with a column -> group map; anything else runs on the generic tier
 static int dispatch_gidx(int mode, const QArgs &a, cudaStream_t st, bool *handled) {
     *handled = true;
+    if (a.xdt == CTB_BF16 && a.sdt == CTB_BF16 && !a.gs && a.qk == QK_INT && a.srs <= 4096 && a.rows < (1LL << 31)) {
+        const size_t smem = (size_t)a.srs * sizeof(GidxSmem);
+        const int grid = grid_for(a.rows, 1, 16);
+#define CTB_GIDX_ROW(MODE_, FC_)                                                 \
+    {                                                                            \
+        gidx_row_kernel<MODE_, FC_><<<grid, kGidxThreads, smem, st>>>(a);        \
+        return after_launch("gidx_row_kernel");                                  \
+    }
+        if (mode == 0 && a.T == CTB_BF16 && a.fout == F_PACK4) CTB_GIDX_ROW(0, F_PACK4)
+        if (mode == 0 && a.T == CTB_BF16 && a.fout == F_I8) CTB_GIDX_ROW(0, F_I8)
+        if (mode == 1 && a.TS == CTB_BF16 && a.fin == F_PACK4 && a.fout == F_BF16) CTB_GIDX_ROW(1, F_PACK4)
+        if (mode == 1 && a.TS == CTB_BF16 && a.fin == F_I8 && a.fout == F_BF16) CTB_GIDX_ROW(1, F_I8)
+        if (mode == 2 && a.T == CTB_BF16 && a.TS == CTB_BF16 && a.fout == F_BF16) CTB_GIDX_ROW(2, F_BF16)
+#undef CTB_GIDX_ROW
+    }
     constexpr int B = CTB_BF16, H = CTB_F16, S = CTB_F32;
     CTB_TRY_GIDX(0, B, S, QK_INT, F_BF16, F_PACK4) CTB_TRY_GIDX(0, B, S, QK_INT, F_BF16, F_I8)
     CTB_TRY_GIDX(0, H, S, QK_INT, F_F16, F_PACK4) CTB_TRY_GIDX(0, H, S, QK_INT, F_F16, F_I8)

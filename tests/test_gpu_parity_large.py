@@ -513,6 +513,8 @@ def test_activation_ordered_groups_match_oracle(ops, orc):
         mn, mx = orc.minmax(xs, 1, group)
         for sym in (True, False):
             scale, zp = orc.calculate_qparams(mn, mx, qtype=orc.QINT, bits=4, symmetric=sym)
+            if dt == torch.bfloat16:
+                scale[3, 1], scale[5, 0] = 1e-38, 2.0 ** 100  # rows with a scale outside the fast range take the float path
             kw = dict(qtype=orc.QINT, bits=4, col_group=group, row_group=1, scale_row_stride=cols // group)
             want = orc.quantize(x, scale, zp, out_dtype=torch.int8, g_idx=g_idx, **kw)
             dz, dg = zp.cuda(), g_idx.cuda()
