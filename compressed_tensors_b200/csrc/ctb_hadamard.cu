@@ -31,6 +31,15 @@ __device__ __forceinline__ A shfl_xor(A v, int o) {
     }
 }
 
+// t / c for a run-time constant c = sqrt(n) with rc = 1 / c (both correctly rounded): exact when c is a power of
+// two, otherwise the reciprocal product plus one Markstein correction, which is the correctly rounded quotient for
+// operands this far from the overflow / underflow ends.  (A zero keeps no sign: every caller adds +0.0 afterwards.)
+template <typename A>
+__device__ __forceinline__ A div_const(A t, A c, A rc) {
+    const A q0 = t * rc;
+    return fma(fma(-q0, c, t), rc, q0);
+}
+
 // in-register butterfly over the 8 elements a lane holds (index bits 0..2 of the block position)
 template <typename A>
 __device__ __forceinline__ void fwht8(A (&v)[8]) {
@@ -108,9 +117,9 @@ __device__ __forceinline__ void rotate8(const HArgs &a, int64_t c, float (&v)[8]
     fwht8<A>(t);
     fwht_lanes<A>(t, a.L, lane_in_block);
     if constexpr (sizeof(A) == 8) {
-        const double s = a.normalize ? sqrt((double)a.n) : 1.0;
+        const double s = a.normalize ? sqrt((double)a.n) : 1.0, rs = 1.0 / s;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] = (float)(t[i] / s);  // float64 quotient, then the cast chain of .to(dtype)
+        for (int i = 0; i < 8; ++i) v[i] = (float)div_const<double>(t[i], s, rs);  // float64 quotient, then the cast chain of .to(dtype)
     } else {
         const float s = a.normalize ? 1.0f / sqrtf((float)a.n) : 1.0f;
 #pragma unroll
@@ -214,9 +223,9 @@ __global__ void __launch_bounds__(kThreads) hadamard_cols_big_kernel(const void 
             smem_get8<A>(buf + ci * 8, t);
             float v[8];
             if constexpr (sizeof(A) == 8) {
-                const double sc = normalize ? sqrt((double)N) : 1.0;
+                const double sc = normalize ? sqrt((double)N) : 1.0, rsc = 1.0 / sc;
 #pragma unroll
-                for (int i = 0; i < 8; ++i) v[i] = (float)(t[i] / sc);  // float64 quotient, then the cast chain of .to(dtype)
+                for (int i = 0; i < 8; ++i) v[i] = (float)div_const<double>(t[i], sc, rsc);  // float64 quotient, then the cast chain of .to(dtype)
             } else {
                 const float sc = normalize ? 1.0f / sqrtf((float)N) : 1.0f;
 #pragma unroll
@@ -265,7 +274,7 @@ __global__ void __launch_bounds__(kThreads) hadamard_rows_kernel(const void *x, 
     A *tile = reinterpret_cast<A *>(smem_raw);  // [n][W + 1]
     const int W = 1 << wshift, pitch = W + 1;
     const int64_t col_tiles = (cols + W - 1) >> wshift, tiles = (rows / n) * col_tiles;
-    const A scale = normalize ? (A)sqrt((double)n) : (A)1;
+    const A scale = normalize ? (A)sqrt((double)n) : (A)1, rscale = (A)1 / scale;
     for (int64_t t = blockIdx.x; t < tiles; t += gridDim.x) {
         const int64_t tr = t / col_tiles, r0 = tr * n, c0 = (t - tr * col_tiles) << wshift;
         for (int i = threadIdx.x; i < n * W; i += kThreads) {
@@ -291,7 +300,7 @@ __global__ void __launch_bounds__(kThreads) hadamard_rows_kernel(const void *x, 
         for (int i = threadIdx.x; i < n * W; i += kThreads) {
             int r = i >> wshift, c = i & (W - 1);
             if (c0 + c < cols) {
-                A v = tile[r * pitch + c] / scale;
+                A v = div_const<A>(tile[r * pitch + c], scale, rscale);
                 float f = (float)v;
                 if (inverse && signs) f *= (float)signs[r];
                 f += 0.0f;  // exact zeros are +0.0 in the reference's matmul
@@ -323,6 +332,7 @@ __global__ void __launch_bounds__(kBigThreads) hadamard_rows_big_kernel(const vo
     constexpr int M = 1 << LOG_M, N = RowsBig<A, LOG_M>::N, W = RowsBig<A, LOG_M>::W, CH = N / 8;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     A *col = reinterpret_cast<A *>(smem_raw);  // [W][N]
+    const A sc = normalize ? (A)sqrt((double)N) : (A)1, rsc = (A)1 / sc;
     const int lane = threadIdx.x & 31;
     const int64_t col_tiles = cols / W, tiles = (rows / N) * col_tiles;
     const uint16_t *xin = reinterpret_cast<const uint16_t *>(x);
@@ -384,8 +394,7 @@ __global__ void __launch_bounds__(kBigThreads) hadamard_rows_big_kernel(const vo
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                     const A v = col[(2 * k + e) * N + r];
-                    if constexpr (sizeof(A) == 8) f[e] = (float)(v / (normalize ? sqrt((double)N) : 1.0));
-                    else f[e] = v / (normalize ? sqrtf((float)N) : 1.0f);
+                    f[e] = (float)div_const<A>(v, sc, rsc);
                     f[e] = f[e] * sg + 0.0f;  // exact zeros are +0.0 in the reference's matmul
                 }
                 if constexpr (XF == F_BF16) { const __nv_bfloat162 h = __floats2bfloat162_rn(f[0], f[1]); w[k] = *reinterpret_cast<const uint32_t *>(&h); }

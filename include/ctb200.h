@@ -225,7 +225,9 @@ int ctb_bitmask_decompress_static(const void *values, const uint8_t *bitmask, in
  * Wh = diag(signs) @ H_n (Sylvester; signs int8 +-1 [n] or NULL = all +1; transform/utils/
  * hadamard.py:33-89), transposed when `inverse`; result / sqrt(n) cast to the dtype of W.
  * precision: CTB_F64 accumulates like the reference's offline path; CTB_F32 is the fast mode.
- * normalize = 0 leaves out the division by sqrt(n) (apply_transform_weight on its own, matrix.py:65). */
+ * normalize = 0 leaves out the division by sqrt(n) (apply_transform_weight on its own, matrix.py:65).
+ * n is a power of two: 8 .. 8192 for side 0 (16-byte aligned buffers), up to 8192 for side 1; a head_dim-sized
+ * block (128) or a whole hidden dimension (4096, 8192).  Other sizes return CTB_EUNSUPPORTED. */
 int ctb_hadamard(const void *x, int32_t dtype, int64_t rows, int64_t cols, int32_t n,
                  const int8_t *signs, int32_t inverse, int32_t side, int32_t precision,
                  int32_t normalize, void *out, void *stream);
