@@ -10,7 +10,7 @@ from ... import ops
 from ..quant_args import QuantizationArgs, QuantizationStrategy
 from ..utils.helpers import qtype_code
 
-__all__ = ["quantize", "dequantize", "fake_quantize", "infer_dequant_args"]
+__all__ = ["quantize", "dequantize", "fake_quantize", "infer_dequant_args", "forward_quantize", "wrap_module_forward_quantized"]
 
 _FLOATS = (torch.bfloat16, torch.float16, torch.float32)
 
@@ -116,3 +116,63 @@ def fake_quantize(x: torch.Tensor, scale: torch.Tensor, zero_point: Optional[tor
     kw, grouped, sdt = _common(x, scale, args, g_idx, global_scale)
     out_dtype = x.dtype if grouped else sdt
     return ops.fake_quantize(x, scale, zero_point, out_dtype=out_dtype, **kw)
+
+
+@torch.no_grad()
+def forward_quantize(module: torch.nn.Module, value: torch.Tensor, base_name: str, args: QuantizationArgs) -> torch.Tensor:
+    """forward.py:415-452: fake-quantize `value` ("input", "weight" or "output" of `module`) with the module's static
+    qparams, or with qparams computed from the value itself when `args.dynamic` (per token / tensor / group; NVFP4
+    activations keep their static `<base_name>_global_scale` and only the local scales are dynamic)."""
+    from ..quant_args import DynamicType
+    from ..quant_config import QuantizationStatus
+    from ..utils.helpers import compute_dynamic_scales_and_zp
+
+    if base_name == "weight" and getattr(module, "quantization_status", None) == QuantizationStatus.COMPRESSED:
+        return value  # the stored weight already is the quantized one
+    if value.numel() == 0:
+        return value
+    g_idx = getattr(module, "weight_g_idx", None)
+    global_scale = getattr(module, f"{base_name}_global_scale", None)
+    if args.dynamic in (True, DynamicType.LOCAL):
+        scale, zero_point = compute_dynamic_scales_and_zp(value=value, args=args, module=module, global_scale=global_scale)
+    else:
+        scale = getattr(module, f"{base_name}_scale")
+        zero_point = getattr(module, f"{base_name}_zero_point", None)
+    return fake_quantize(x=value, scale=scale, zero_point=zero_point, args=args, g_idx=g_idx, global_scale=global_scale)
+
+
+def wrap_module_forward_quantized(module: torch.nn.Module, scheme) -> None:
+    """forward.py:355-412: replace `module.forward` by a forward that fake-quantizes the input activations, runs the
+    layer on a fake-quantized copy of the weight (restored afterwards) and fake-quantizes the output, each only where
+    the scheme asks for it; `module.quantization_enabled = False` bypasses all of it.  The module must carry the
+    parameters that initialize_module_for_quantization registers."""
+    import functools
+
+    from ..quant_config import QuantizationStatus
+
+    plain = module.forward  # bound method (or partial) of the un-wrapped layer
+
+    @functools.wraps(getattr(plain, "__func__", plain))
+    def quantized_forward(self, *args, **kwargs):
+        if not getattr(self, "quantization_enabled", True):
+            return plain(*args, **kwargs)
+        x = args[0]
+        status = getattr(self, "quantization_status", None)
+        fake_weight = scheme.weights is not None and status != QuantizationStatus.COMPRESSED
+        if scheme.input_activations is not None:
+            x = forward_quantize(self, x, "input", scheme.input_activations)
+        if fake_weight:
+            kept = self.weight.data
+            self.weight.data = forward_quantize(self, self.weight.data, "weight", scheme.weights)
+        try:
+            out = plain(x, *args[1:], **kwargs)
+        finally:
+            if fake_weight:
+                self.weight.data = kept
+        if scheme.output_activations is not None:
+            calibrating_static = status == QuantizationStatus.CALIBRATION and not scheme.output_activations.dynamic
+            if not calibrating_static:  # static output qparams are still being observed: leave the output alone
+                out = forward_quantize(self, out, "output", scheme.output_activations)
+        return out
+
+    module.forward = quantized_forward.__get__(module, module.__class__)

@@ -1,9 +1,10 @@
 """Registration of quantization parameters on a module, with the reference's names and shapes
 (quantization/lifecycle/initialize.py:60-143 initialize_module_for_quantization, :153-277 initialize_qparams).
 
-Only the parameter bookkeeping is mirrored: a compressed checkpoint can be loaded into, and decompressed from, a
-module that carries `weight_scale`, `weight_zero_point`, `weight_global_scale`, `weight_g_idx` of the right shape
-and dtype.  Observers, calibration and the wrapped quantized forward are not part of this package.
+The parameter bookkeeping and the wrapped quantized forward are mirrored: a compressed checkpoint can be loaded into,
+and decompressed from, a module that carries `weight_scale`, `weight_zero_point`, `weight_global_scale`,
+`weight_g_idx` of the right shape and dtype, and its forward fake-quantizes activations and weights through the CUDA
+kernels (lifecycle/forward.py).  Observers and calibration are not part of this package.
 """
 from typing import Optional, Tuple, Union
 
@@ -51,6 +52,14 @@ def initialize_module_for_quantization(module: Module, scheme: Optional[Quantiza
         initialize_qparams(module, "weight", scheme.weights, weight.shape, weight.dtype, force_zero_point)
     if scheme.output_activations is not None:
         initialize_qparams(module, "output", scheme.output_activations, weight.shape[:-1], weight.dtype, force_zero_point)
+    # initialize.py:138-141: the forward acts on the call-time status; a re-initialised module wraps its plain forward again
+    from .forward import wrap_module_forward_quantized
+
+    plain = getattr(module, "_ctb_plain_forward", None)
+    if plain is None:
+        module._ctb_plain_forward = plain = module.forward
+    module.forward = plain
+    wrap_module_forward_quantized(module, scheme)
     module.quantization_scheme = scheme
     module.quantization_status = QuantizationStatus.INITIALIZED
 

@@ -6,7 +6,7 @@ import torch
 from .. import ops
 from .._lib import on_gpu
 
-__all__ = ["sparse_semi_structured_from_dense_cutlass", "sparse_semi_structured_to_dense_cutlass"]
+__all__ = ["sparse_semi_structured_from_dense_cutlass", "sparse_semi_structured_to_dense_cutlass", "mask_creator"]
 
 
 def sparse_semi_structured_from_dense_cutlass(dense: torch.Tensor):
@@ -22,3 +22,12 @@ def sparse_semi_structured_to_dense_cutlass(sparse: torch.Tensor, meta_reordered
     """(sparse [m, k/2], meta_reordered int16 [m, k/16]) -> dense [m, k]."""
     return ops.cutlass24_decompress(on_gpu(sparse), on_gpu(meta_reordered))
 
+
+
+def mask_creator(tensor: torch.Tensor) -> torch.Tensor:
+    """semi_structured_conversions.py:313-342: a 2:4 keep mask (1.0 = keep, 0.0 = prune) over runs of four elements of
+    the flattened tensor, by magnitude.  Runs with equal magnitudes follow the tie order of get_24_bytemasks (the
+    reference's argsort leaves that order unspecified)."""
+    if tensor.numel() % 4 != 0:
+        raise ValueError(f"Tensor of size {tensor.shape} can't be evenly divided into 4 groups")
+    return ops.sparse24_mask(tensor.detach()).to(torch.float32)

@@ -468,6 +468,62 @@ def gen_hadamard_full():
     torch.save(out, os.path.join(OUT, "hadamard_full.pt"))
 
 
+def gen_forward_quantize():
+    """forward_quantize and the wrapped quantized forward (lifecycle/forward.py:355-452) on a Linear(256, 128):
+    static group weights, dynamic per-token int8 / fp8 activations, static per-tensor int8 input and output."""
+    from compressed_tensors.quantization import QuantizationScheme, QuantizationStatus
+    from compressed_tensors.quantization.lifecycle.forward import forward_quantize
+    from compressed_tensors.quantization.lifecycle.initialize import initialize_module_for_quantization
+
+    out = {}
+    gen = torch.Generator().manual_seed(21)
+    w = weights(gen, 128, 256, torch.bfloat16)
+    x = torch.randn(2, 24, 256, generator=gen).to(torch.bfloat16)
+    x[..., 7] *= 20
+    cases = {
+        "w4a16_g128": dict(weights=QuantizationArgs(num_bits=4, symmetric=True, strategy="group", group_size=128)),
+        "w8a8_int_dynamic_token": dict(weights=QuantizationArgs(num_bits=8, symmetric=True, strategy="channel"),
+                                       input_activations=QuantizationArgs(num_bits=8, symmetric=True, strategy="token", dynamic=True)),
+        "w8a8_fp8_dynamic_token": dict(weights=QuantizationArgs(num_bits=8, type="float", symmetric=True, strategy="channel"),
+                                       input_activations=QuantizationArgs(num_bits=8, type="float", symmetric=True, strategy="token", dynamic=True)),
+        "w8a8_int_static_tensor_in_out": dict(weights=QuantizationArgs(num_bits=8, symmetric=False, strategy="channel"),
+                                              input_activations=QuantizationArgs(num_bits=8, symmetric=True, strategy="tensor"),
+                                              output_activations=QuantizationArgs(num_bits=8, symmetric=True, strategy="tensor")),
+    }
+    for name, sides in cases.items():
+        scheme = QuantizationScheme(targets=["Linear"], **sides)
+        lin = torch.nn.Linear(256, 128, bias=False, dtype=torch.bfloat16)
+        lin.weight.data = w.clone()
+        initialize_module_for_quantization(lin, scheme)
+        wa = scheme.weights
+        g = wa.group_size if wa.strategy == "group" else 256
+        mn, mx = group_minmax(w, g)
+        s, z = calculate_qparams(mn, mx, wa)
+        lin.weight_scale.data = s.reshape(lin.weight_scale.shape).to(lin.weight_scale.dtype)
+        if hasattr(lin, "weight_zero_point"):
+            lin.weight_zero_point.data = z.reshape(lin.weight_zero_point.shape).to(lin.weight_zero_point.dtype)
+        d = {"w": w, "x": x, "weight_scale": lin.weight_scale.data.clone()}
+        if hasattr(lin, "weight_zero_point"):
+            d["weight_zero_point"] = lin.weight_zero_point.data.clone()
+        for side in ("input", "output"):
+            a = getattr(scheme, f"{side}_activations")
+            if a is not None and not a.dynamic:
+                amax = x.abs().max() if side == "input" else torch.tensor(40.0, dtype=torch.bfloat16)
+                sc, zp = calculate_qparams(-amax.reshape(1), amax.reshape(1), a)
+                getattr(lin, f"{side}_scale").data = sc.reshape(getattr(lin, f"{side}_scale").shape).to(torch.bfloat16)
+                d[f"{side}_scale"] = getattr(lin, f"{side}_scale").data.clone()
+        lin.quantization_status = QuantizationStatus.FROZEN
+        with torch.no_grad():
+            d["fq_weight"] = forward_quantize(lin, lin.weight.data, "weight", scheme.weights)
+            if scheme.input_activations is not None:
+                d["fq_input"] = forward_quantize(lin, x, "input", scheme.input_activations)
+            d["y"] = lin(x)
+            lin.quantization_enabled = False
+            d["y_disabled"] = lin(x)
+        out[name] = d
+    torch.save(out, os.path.join(OUT, "forward_quantize.pt"))
+
+
 def gen_fp4_pack_all():
     """pack_fp4_to_uint8 on EVERY bf16 and f16 bit pattern (off-grid magnitudes, ties, infinities, NaNs) and on a
     float32 sweep; unpack_fp4_from_uint8 on every byte, in the three dense dtypes."""
@@ -490,7 +546,7 @@ if __name__ == "__main__":
     only = sys.argv[2] if len(sys.argv) > 2 else None  # e.g. "mxfp4": regenerate one fixture
     for name, fn in (("int_quant", gen_int), ("fp8_quant", gen_fp8), ("nvfp4", gen_nvfp4), ("sparse", gen_sparse),
                      ("hadamard", gen_hadamard), ("hadamard_online", gen_hadamard_online), ("hadamard_randomize", gen_hadamard_randomize), ("hadamard_embedding", gen_hadamard_embedding), ("mxfp4", gen_mxfp4), ("marlin24", gen_marlin24),
-                     ("fp4_pack_all", gen_fp4_pack_all), ("hadamard_full", gen_hadamard_full)):
+                     ("fp4_pack_all", gen_fp4_pack_all), ("hadamard_full", gen_hadamard_full), ("forward_quantize", gen_forward_quantize)):
         if only is None or only == name:
             fn()
     for f in sorted(os.listdir(OUT)):

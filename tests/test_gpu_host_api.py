@@ -296,8 +296,14 @@ def test_disk_decompress_and_compressed_linear(tmp_path, fmt, group):
     y = mod(x)
     assert mod.quantization_status == QuantizationStatus.FROZEN
     assert_bit_equal(mod.weight.data.cpu(), in_memory["0"].cpu(), "weight decompressed at the first forward")
-    assert_bit_equal(y.cpu(), torch.nn.functional.linear(x, in_memory["0"].cuda()).cpu(), "forward")
-    assert_bit_equal(mod(x).cpu(), y.cpu(), "second forward reuses the dense weight")
+    # the forward installed by initialize_module_for_quantization fake-quantizes the input where the scheme has input
+    # activations (forward.py:355-412), as the reference's CompressedLinear does
+    from compressed_tensors_b200.quantization import forward_quantize
+    acts = schemes["0"].input_activations
+    xin = x if acts is None else forward_quantize(mod, x, "input", acts)
+    assert_bit_equal(y.cpu(), torch.nn.functional.linear(xin, in_memory["0"].cuda()).cpu(), "forward")
+    assert_bit_equal(mod(x).cpu(), y.cpu(), "second forward reuses the dense weight (fake-quantizing it again changes nothing)")
+    assert_bit_equal(mod.weight.data.cpu(), in_memory["0"].cpu(), "the dense weight is left as decompressed")
 
 
 def test_hadamard_whole_dimension(golden):
@@ -444,3 +450,72 @@ def test_embedding_transforms(golden):
         tr = TransformFactory.from_scheme(scheme, name="t", seed=7).create_transform(emb, scheme.apply[0])
         assert_bit_equal(tr(d["w"].cuda()).cpu(), d["out"], name)
 
+
+
+def test_forward_quantize_and_wrapped_forward(golden):
+    """forward_quantize (static group weights, dynamic per-token int8 / fp8 activations, static per-tensor input and
+    output) and the quantized forward that initialize_module_for_quantization installs, against the reference's
+    outputs: fake-quantized weights and inputs bit-exact; the layer output to the step that one bf16 unit of the
+    matmul can move it by (the matmul itself is torch's, on another device than the reference's)"""
+    from compressed_tensors_b200.quantization import (QuantizationArgs, QuantizationScheme, QuantizationStatus, disable_quantization,
+                                                      enable_quantization, forward_quantize, initialize_module_for_quantization)
+
+    cases = {
+        "w4a16_g128": dict(weights=QuantizationArgs(num_bits=4, symmetric=True, strategy="group", group_size=128)),
+        "w8a8_int_dynamic_token": dict(weights=QuantizationArgs(num_bits=8, symmetric=True, strategy="channel"),
+                                       input_activations=QuantizationArgs(num_bits=8, symmetric=True, strategy="token", dynamic=True)),
+        "w8a8_fp8_dynamic_token": dict(weights=QuantizationArgs(num_bits=8, type="float", symmetric=True, strategy="channel"),
+                                       input_activations=QuantizationArgs(num_bits=8, type="float", symmetric=True, strategy="token", dynamic=True)),
+        "w8a8_int_static_tensor_in_out": dict(weights=QuantizationArgs(num_bits=8, symmetric=False, strategy="channel"),
+                                              input_activations=QuantizationArgs(num_bits=8, symmetric=True, strategy="tensor"),
+                                              output_activations=QuantizationArgs(num_bits=8, symmetric=True, strategy="tensor")),
+    }
+    g = golden("forward_quantize")
+    for name, sides in cases.items():
+        d = g[name]
+        scheme = QuantizationScheme(targets=["Linear"], **sides)
+        lin = torch.nn.Linear(256, 128, bias=False, dtype=torch.bfloat16, device="cuda")
+        lin.weight.data = d["w"].cuda()
+        initialize_module_for_quantization(lin, scheme)
+        for key in ("weight_scale", "weight_zero_point", "input_scale", "output_scale"):
+            if key in d:
+                assert getattr(lin, key).shape == d[key].shape and getattr(lin, key).dtype == d[key].dtype, f"{name} {key}"
+                getattr(lin, key).data = d[key].cuda()
+        lin.quantization_status = QuantizationStatus.FROZEN
+        x = d["x"].cuda()
+        assert_bit_equal(forward_quantize(lin, lin.weight.data, "weight", scheme.weights).cpu(), d["fq_weight"], name + " weight")
+        if "fq_input" in d:
+            assert_bit_equal(forward_quantize(lin, x, "input", scheme.input_activations).cpu(), d["fq_input"], name + " input")
+        before = lin.weight.data.clone()
+        y = lin(x).cpu().float()
+        assert torch.equal(lin.weight.data, before), name + ": the weight is restored after the forward"
+        want = d["y"].float()
+        step = float(d["output_scale"].float().max()) if "output_scale" in d else 0.0
+        assert bool(((y - want).abs() <= want.abs() * 2.0 ** -6 + 1e-3 + step).all()), name + " output"
+        disable_quantization(lin)
+        plain = torch.nn.functional.linear(x, lin.weight.data)
+        assert torch.equal(lin(x), plain), name + ": disabled quantization is the plain layer"
+        torch.testing.assert_close(lin(x).cpu().float(), d["y_disabled"].float(), rtol=2.0 ** -6, atol=1e-3)
+        enable_quantization(lin)
+        lin.quantization_status = QuantizationStatus.COMPRESSED  # the stored weight is taken as already quantized
+        stored = lin.weight.data
+        assert forward_quantize(lin, stored, "weight", scheme.weights) is stored
+
+
+def test_mask_creator_and_structure_check():
+    """mask_creator (semi_structured_conversions.py:313) keeps the two largest magnitudes of every run of four;
+    tensor_follows_mask_structure (utils/helpers.py:93) accepts the pruned tensor and rejects the dense one"""
+    from compressed_tensors_b200.utils import mask_creator, tensor_follows_mask_structure
+
+    g = torch.Generator().manual_seed(8)
+    w = torch.randn(64, 256, generator=g).to(torch.bfloat16)  # distinct magnitudes almost surely: no tie order involved
+    mask = mask_creator(w.cuda())
+    assert mask.dtype == torch.float32 and mask.shape == w.shape
+    runs = w.float().abs().reshape(-1, 4)
+    want = torch.ones_like(runs).scatter_(1, torch.argsort(runs, dim=1)[:, :2], 0.0).reshape(w.shape)
+    ties = (runs.sort(dim=1).values.diff(dim=1) == 0).any(dim=1).reshape(-1, 1).expand(-1, 4).reshape(w.shape)
+    assert torch.equal(mask.cpu()[~ties], want[~ties])
+    assert bool((mask.reshape(-1, 4).sum(dim=1) == 2).all())
+    assert tensor_follows_mask_structure((w.cuda() * mask.to(torch.bfloat16)))
+    with pytest.raises(ValueError):
+        tensor_follows_mask_structure(w.cuda() + 1.0)
