@@ -317,6 +317,12 @@ def standalone_ops_table(dev, peak, size=8192):
     run("quantize_int4_g128_actorder_codes", one, lambda w: ops.quantize(w, s4, None, out_dtype=torch.int8, g_idx=gi, **kw4), 2 * n, 3 * n, 3 * n)
     run("dequantize_int4_g128_actorder_pack32", lambda: (ops.quantize(rnd(), s4, None, codec="pack32", g_idx=gi, **kw4),),
         lambda p: ops.dequantize(p, s4, None, out_dtype=torch.bfloat16, codec="pack32", cols=C, g_idx=gi, **kw4), 2 * n, 2.515625 * n, 2.6 * n)
+    nt = 8192 * 4096
+    tok = lambda: (torch.randn(1, 8192, 4096, generator=g, device=dev).to(torch.bfloat16),)
+    from compressed_tensors_b200.quantization import QuantizationArgs, forward_quantize
+    for label, a in (("int8", QuantizationArgs(num_bits=8, symmetric=True, strategy="token", dynamic=True)),
+                     ("fp8", QuantizationArgs(num_bits=8, type="float", symmetric=True, strategy="token", dynamic=True))):
+        run(f"forward_quantize_dynamic_token_{label}_8192x4096", tok, lambda x, a=a: forward_quantize(None, x, "input", a), 2 * nt, 4 * nt, 4 * nt)
     run("minmax_group128", one, lambda w: ops.minmax(w, 1, 128), 2 * n, 2 * n, 2 * n)
     run("minmax_channel", one, lambda w: ops.minmax(w, 1, C), 2 * n, 2 * n, 2 * n)
     run("minmax_block128x128", one, lambda w: ops.minmax(w, 128, 128), 2 * n, 2 * n, 2 * n)

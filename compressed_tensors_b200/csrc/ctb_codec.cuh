@@ -345,6 +345,56 @@ __device__ __forceinline__ uint4 dequant8_to_bf16(const float (&v)[8], float s) 
     return make_uint4(p[0], p[1], p[2], p[3]);
 }
 
+// ---- packed bf16x2 quantize helpers shared by the given-qparam tier and the fused calibrate kernels ---------------
+
+__device__ __forceinline__ float rcp_approx(float s) {
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(s));
+    return r;
+}
+
+// both halves of one packed word times r, each rounded once to bf16
+__device__ __forceinline__ __nv_bfloat162 scale_pair(uint32_t w, float r) {
+    return __floats2bfloat162_rn(__uint_as_float(w << 16) * r, __uint_as_float(w & 0xFFFF0000u) * r);
+}
+
+// like scale_pair, then "+ 0" (an all-zero zero point turns -0.0 into +0.0)
+__device__ __forceinline__ __nv_bfloat162 scale_pair_plus_zero(uint32_t w, float r) {
+    return __floats2bfloat162_rn(fmaf(__uint_as_float(w << 16), r, 0.0f), fmaf(__uint_as_float(w & 0xFFFF0000u), r, 0.0f));
+}
+
+// int8 codes of four sign-magnitude halves (two words of u = q + copysign(128, q)): |code| bytes, a 0x00 / 0xFF
+// sign byte each, then a per-byte negate whose "+ 1" cannot carry into the neighbouring byte
+__device__ __forceinline__ uint32_t int8_codes_of(uint32_t u0, uint32_t u1) {
+    const uint32_t mag = prmt_b32(u0, u1, 0x6420), neg = prmt_b32(u0, u1, 0xFDB9);
+    const uint32_t x = mag ^ neg;
+    return ((x & 0x7F7F7F7Fu) + (neg & 0x01010101u)) ^ (x & 0x80808080u);
+}
+
+// fake quantize of one packed word to an integer grid, compute dtype bf16 (forward.py:471-512): q = bf16(x * r)
+// [+ zero point], clamp (a NaN stays a NaN), u = q + copysign(128, q) rounds half to even because |u| is in
+// [128, 256] where a bf16 step is 1, back by the same constant with q's sign put on a zero, [- zero point], * scale.
+__device__ __forceinline__ uint32_t fake_int_pair_bf16(uint32_t w, float r, bool has_zp, __nv_bfloat162 z2, __nv_bfloat162 lo2,
+                                                       __nv_bfloat162 hi2, __nv_bfloat162 s2) {
+    __nv_bfloat162 q = scale_pair(w, r);
+    if (has_zp) q = __hadd2(q, z2);
+    q = __hmin2_nan(__hmax2_nan(q, lo2), hi2);
+    const uint32_t sign = bf162_as_u32(q) & 0x80008000u;
+    const __nv_bfloat162 m = u32_as_bf162(sign | 0x43004300u);
+    __nv_bfloat162 t = u32_as_bf162(bf162_as_u32(__hsub2(__hadd2(q, m), m)) | sign);
+    if (has_zp) t = __hsub2(t, z2);
+    return bf162_as_u32(__hmul2(t, s2));
+}
+
+// fake quantize of one packed word to e4m3, compute dtype bf16, symmetric (no zero point, or the all-zero one)
+__device__ __forceinline__ uint32_t fake_fp8_pair_bf16(uint32_t w, float r, bool plus_zero, float s) {
+    const uint32_t q = bf162_as_u32(plus_zero ? scale_pair_plus_zero(w, r) : scale_pair(w, r));
+    const uint32_t code = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(__uint_as_float(q << 16), __uint_as_float(q & 0xFFFF0000u)),
+                                                             __NV_SATFINITE, __NV_E4M3);
+    const float2 f = __half22float2(__half2(__nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)code, __NV_E4M3)));
+    return bf162_as_u32(__floats2bfloat162_rn(f.x * s, f.y * s));
+}
+
 // qparam for a chunk, as fp32
 struct QP {
     float s;   // effective scale (scale or scale / global_scale)

@@ -795,10 +795,36 @@ __global__ void __launch_bounds__(kThreads) absmax_quant_warprow_kernel(const HA
                         continue;
                     }
                 }
+                if constexpr (FOUT == F_BF16 && XF == F_BF16) {
+                    if (!q.slow) {  // packed bf16x2 arithmetic; the scale is a bf16 value, so its top half is all of it
+                        const uint32_t w[4] = {raw[k].a.x, raw[k].a.y, raw[k].a.z, raw[k].a.w};
+                        uint32_t o[4];
+                        if constexpr (QK == QK_INT) {
+                            const __nv_bfloat162 lo2 = __float2bfloat162_rn(a.qmin), hi2 = __float2bfloat162_rn(a.qmax);
+                            const __nv_bfloat162 s2 = u32_as_bf162((__float_as_uint(q.s) >> 16) * 0x00010001u), z2 = u32_as_bf162(0u);
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) o[j] = fake_int_pair_bf16(w[j], q.r, true, z2, lo2, hi2, s2);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) o[j] = fake_fp8_pair_bf16(w[j], q.r, true, q.s);
+                        }
+                        st_stream((char *)a.out + (r * cpr + c) * 16, make_uint4(o[0], o[1], o[2], o[3]));
+                        continue;
+                    }
+                }
                 float v[8];
                 decode8<XF>(raw[k], v);
-                quant_prepare8<M>(v, q, QK == QK_FP8, 0.0f, a.qmin, a.qmax);
-                encode_store8<QK, FOUT>(a.out, r * cpr + c, v);
+                if constexpr (FOUT == F_BF16) {
+                    // dynamic fake quantize (forward.py:157-189 with the all-zero zero point calculate_qparams returns for a
+                    // symmetric scheme): x / s + 0, clamp, round to the grid, (q - 0) * s, every step in the tensor dtype
+                    quant_prepare8<M>(v, q, true, 0.0f, a.qmin, a.qmax);
+                    round8<QK>(v);
+                    dequant8<M>(v, q, true);
+                    store8_float<F_BF16>(a.out, r * cpr + c, v);
+                } else {
+                    quant_prepare8<M>(v, q, QK == QK_FP8, 0.0f, a.qmin, a.qmax);
+                    encode_store8<QK, FOUT>(a.out, r * cpr + c, v);
+                }
             }
         }
     }
@@ -997,7 +1023,10 @@ extern "C" int ctb_absmax_quantize(const ctb_qdesc *d, const void *x, const floa
     else if (d->codec == CTB_CODE_DTYPE && qk == QK_INT && d->q_dtype == CTB_I8) fout = F_I8;
     else if (d->codec == CTB_CODE_DTYPE && qk == QK_FP8 && d->q_dtype == CTB_E4M3) fout = F_E4M3;
     else if (d->codec == CTB_CODE_FP4X2 && qk == QK_FP4) fout = F_FP4X2;
-    else return fail(CTB_EUNSUPPORTED, "fused calibration writes PACK32 (4/8 bit), int8, e4m3 or FP4X2");
+    else if (d->codec == CTB_CODE_DTYPE && qk != QK_FP4 && d->q_dtype == CTB_BF16) fout = F_BF16;  // fake quantize: dequantized values
+    else return fail(CTB_EUNSUPPORTED, "fused calibration writes PACK32 (4/8 bit), int8, e4m3, FP4X2 or (fake quantize) bf16");
+    if (fout == F_BF16 && !(n <= 0 && d->col_group == d->cols && d->scale_row_stride == 1 && d->cols / 8 <= 32 * 32))
+        return fail(CTB_EUNSUPPORTED, "fused dynamic fake quantize is built for whole rows of up to 8192 elements");
     if (d->rows == 0) return CTB_OK;
     HArgs a{};
     a.x = x; a.signs = signs; a.out = out; a.out_scale = out_scale; a.gs = gs;
@@ -1041,7 +1070,7 @@ extern "C" int ctb_absmax_quantize(const ctb_qdesc *d, const void *x, const floa
         absmax_quant_g16_fp4_kernel<<<grid_for(ngroups, kThreads * 2, 8), kThreads, 0, st>>>(a, ngroups);
         return after_launch("absmax_quant_g16_fp4_kernel");
     }
-    if (pow2(GL) && GL <= 32 && d->scale_row_stride == d->cols / d->col_group) {
+    if (fout != F_BF16 && pow2(GL) && GL <= 32 && d->scale_row_stride == d->cols / d->col_group) {
         a.GL = (int)GL;
         a.gl_shift = 0;
         while ((1 << a.gl_shift) < a.GL) ++a.gl_shift;
@@ -1051,16 +1080,19 @@ extern "C" int ctb_absmax_quantize(const ctb_qdesc *d, const void *x, const floa
         else if (fout == F_PACK8) CTB_AQ(QK_INT, F_PACK8);
         else if (fout == F_I8) CTB_AQ(QK_INT, F_I8);
         else if (fout == F_E4M3) CTB_AQ(QK_FP8, F_E4M3);
-        else CTB_AQ(QK_FP4, F_FP4X2);
+        else if (fout == F_FP4X2) CTB_AQ(QK_FP4, F_FP4X2);
+        else return fail(CTB_EUNSUPPORTED, "no fused group kernel for this output format");
         return after_launch("absmax_quant_group_kernel");
     }
     if (d->col_group == d->cols && d->scale_row_stride == 1 && qk != QK_FP4) {
         const int64_t cpr = d->cols / 8;
-        if (cpr <= 32 * 32 && (fout == F_E4M3 || fout == F_I8)) {
+        if (cpr <= 32 * 32 && (fout == F_E4M3 || fout == F_I8 || fout == F_BF16)) {
             int wgrid = grid_for(d->rows, kThreads / 32, cpr <= 512 ? 4 : 2);
 #define CTB_WR(CPL_)                                                                                                              \
     if (fout == F_E4M3) absmax_quant_warprow_kernel<CPL_, F_BF16, QK_FP8, F_E4M3><<<wgrid, kThreads, 0, st>>>(a, d->rows, (int)cpr); \
-    else absmax_quant_warprow_kernel<CPL_, F_BF16, QK_INT, F_I8><<<wgrid, kThreads, 0, st>>>(a, d->rows, (int)cpr);
+    else if (fout == F_I8) absmax_quant_warprow_kernel<CPL_, F_BF16, QK_INT, F_I8><<<wgrid, kThreads, 0, st>>>(a, d->rows, (int)cpr); \
+    else if (qk == QK_FP8) absmax_quant_warprow_kernel<CPL_, F_BF16, QK_FP8, F_BF16><<<wgrid, kThreads, 0, st>>>(a, d->rows, (int)cpr); \
+    else absmax_quant_warprow_kernel<CPL_, F_BF16, QK_INT, F_BF16><<<wgrid, kThreads, 0, st>>>(a, d->rows, (int)cpr);
             if (cpr <= 128) { CTB_WR(4) } else if (cpr <= 256) { CTB_WR(8) } else if (cpr <= 512) { CTB_WR(16) } else { CTB_WR(32) }
             return after_launch("absmax_quant_warprow_kernel");
         }
@@ -1068,7 +1100,8 @@ extern "C" int ctb_absmax_quantize(const ctb_qdesc *d, const void *x, const floa
         if (fout == F_E4M3) absmax_quant_row_kernel<F_BF16, QK_FP8, F_E4M3><<<grid, kThreads, 0, st>>>(a, d->rows, cpr);
         else if (fout == F_I8) absmax_quant_row_kernel<F_BF16, QK_INT, F_I8><<<grid, kThreads, 0, st>>>(a, d->rows, cpr);
         else if (fout == F_PACK8) absmax_quant_row_kernel<F_BF16, QK_INT, F_PACK8><<<grid, kThreads, 0, st>>>(a, d->rows, cpr);
-        else absmax_quant_row_kernel<F_BF16, QK_INT, F_PACK4><<<grid, kThreads, 0, st>>>(a, d->rows, cpr);
+        else if (fout == F_PACK4) absmax_quant_row_kernel<F_BF16, QK_INT, F_PACK4><<<grid, kThreads, 0, st>>>(a, d->rows, cpr);
+        else return fail(CTB_EUNSUPPORTED, "no fused row kernel for this output format");
         return after_launch("absmax_quant_row_kernel");
     }
     return fail(CTB_EUNSUPPORTED, "fused calibration takes groups of 8..256 (power of two) or whole rows");

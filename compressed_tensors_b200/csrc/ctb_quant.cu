@@ -217,30 +217,6 @@ __device__ __noinline__ void lean_exact_chunk(const LeanArgs &a, uint32_t c, uin
     }
 }
 
-__device__ __forceinline__ float rcp_approx(float s) {
-    float r;
-    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(s));
-    return r;
-}
-
-// both halves of one packed word times r, each rounded once to bf16
-__device__ __forceinline__ __nv_bfloat162 scale_pair(uint32_t w, float r) {
-    return __floats2bfloat162_rn(__uint_as_float(w << 16) * r, __uint_as_float(w & 0xFFFF0000u) * r);
-}
-
-// like scale_pair, then "+ 0" (an all-zero zero point turns -0.0 into +0.0)
-__device__ __forceinline__ __nv_bfloat162 scale_pair_plus_zero(uint32_t w, float r) {
-    return __floats2bfloat162_rn(fmaf(__uint_as_float(w << 16), r, 0.0f), fmaf(__uint_as_float(w & 0xFFFF0000u), r, 0.0f));
-}
-
-// int8 codes of four sign-magnitude halves (two words of u = q + copysign(128, q)): |code| bytes, a 0x00 / 0xFF
-// sign byte each, then a per-byte negate whose "+ 1" cannot carry into the neighbouring byte
-__device__ __forceinline__ uint32_t int8_codes_of(uint32_t u0, uint32_t u1) {
-    const uint32_t mag = prmt_b32(u0, u1, 0x6420), neg = prmt_b32(u0, u1, 0xFDB9);
-    const uint32_t x = mag ^ neg;
-    return ((x & 0x7F7F7F7Fu) + (neg & 0x01010101u)) ^ (x & 0x80808080u);
-}
-
 constexpr int kLeanUnroll = 2;
 
 // 32 registers (a few bytes of spill in the rare path): eight resident blocks per SM measured faster than six at 40
@@ -354,20 +330,15 @@ __global__ void __launch_bounds__(kThreads, ST == CTB_BF16 ? 8 : 6) quant_bf16_l
                 uint32_t o[4];
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
-                    __nv_bfloat162 q = scale_pair(w[k], r);
-                    if (has_zp) q = __hadd2(q, z2);
-                    // codes: a NaN input takes q_min (its integer cast is unspecified in the reference); fake: NaN stays NaN
-                    if constexpr (MODE == 0) q = __hmin2(__hmax2(q, lo2), hi2);
-                    else q = __hmin2_nan(__hmax2_nan(q, lo2), hi2);
-                    const uint32_t sign = bf162_as_u32(q) & 0x80008000u;
-                    const __nv_bfloat162 m = u32_as_bf162(sign | 0x43004300u);
-                    const __nv_bfloat162 uu = __hadd2(q, m);
                     if constexpr (MODE == 0) {
-                        o[k] = bf162_as_u32(uu);
+                        // codes: a NaN input takes q_min (its integer cast is unspecified in the reference)
+                        __nv_bfloat162 q = scale_pair(w[k], r);
+                        if (has_zp) q = __hadd2(q, z2);
+                        q = __hmin2(__hmax2(q, lo2), hi2);
+                        const uint32_t sign = bf162_as_u32(q) & 0x80008000u;
+                        o[k] = bf162_as_u32(__hadd2(q, u32_as_bf162(sign | 0x43004300u)));  // sign-magnitude: 128 + |code|
                     } else {
-                        __nv_bfloat162 t = u32_as_bf162(bf162_as_u32(__hsub2(uu, m)) | sign);
-                        if (has_zp) t = __hsub2(t, z2);
-                        o[k] = bf162_as_u32(__hmul2(t, s2));
+                        o[k] = fake_int_pair_bf16(w[k], r, has_zp, z2, lo2, hi2, s2);
                     }
                 }
                 if constexpr (MODE == 0) {

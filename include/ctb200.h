@@ -256,7 +256,10 @@ int ctb_marlin24_pack_scales(const void *scale, int64_t size_n, int64_t groups, 
  * ctb_quantize with the scales it produced.  out_scale is written in desc->scale_dtype, which
  * must equal desc->x_dtype; zero points are all zero and not written.
  * With n > 0 the weight_input Hadamard rotation of ctb_hadamard (side 0) is applied in front,
- * rounding to x_dtype in between exactly as the two separate calls would. */
+ * rounding to x_dtype in between exactly as the two separate calls would.
+ * codec CTB_CODE_DTYPE with q_dtype CTB_BF16 selects dynamic fake quantization (forward.py:415-452 forward_quantize
+ * with args.dynamic, per token / channel): the output is ctb_fake_quantize with the row's own symmetric qparams;
+ * built for whole rows (col_group == cols) of up to 8192 int8 / fp8-quantized elements. */
 int ctb_absmax_quantize(const ctb_qdesc *desc, const void *x, const float *global_scale,
                         void *out_scale, void *out, int32_t hadamard_n, const int8_t *signs,
                         int32_t precision, void *stream);

@@ -550,3 +550,27 @@ def test_whole_dimension_rotation_sizes(ops, orc, n):
                 err = (fast.float() - want.float()).abs()
                 step = want.float().abs() * (2.0 ** -7 if dtype == torch.bfloat16 else 2.0 ** -10) + 1e-6
                 assert bool((err <= step).all()), f"n={n} side={side} float32 mode"
+
+
+def test_fused_dynamic_token_fake_quantize_equals_separate_kernels(ops, orc):
+    """dynamic per-token fake quantization in one pass (min/max + qparams + fake_quantize of the row held in registers)
+    against the three separate kernels and the oracle: int8 and fp8, outlier channels, an all-zero token, signed zeros"""
+    g = torch.Generator().manual_seed(12)
+    for cols in (256, 4096, 8192):
+        x = torch.randn(96, cols, generator=g)
+        x[:, torch.randperm(cols, generator=g)[: cols // 100 + 1]] *= 20
+        x[5] = 0
+        x[6, :8] = torch.tensor([-0.0, 0.0, -1e-30, 1e-30, 3.0, -3.0, 1e-3, -1e-3])
+        x = x.to(torch.bfloat16)
+        for qtype, zdt in ((orc.QINT, torch.int8), (orc.QFLOAT, torch.float8_e4m3fn)):
+            mn, mx = orc.minmax(x, 1, cols)
+            scale, zp = orc.calculate_qparams(mn, mx, qtype=qtype, bits=8, symmetric=True)
+            kw = dict(qtype=qtype, bits=8, col_group=cols, row_group=1, scale_row_stride=1)
+            want = orc.fake_quantize(x, scale, zp, out_dtype=torch.bfloat16, **kw)
+            fused, fscale = ops.absmax_quantize(x.cuda(), qtype=qtype, bits=8, col_group=cols, codec="dtype", out_dtype=torch.bfloat16)
+            assert_bit_equal(fscale.cpu().reshape(scale.shape), scale, f"scale {cols}")
+            assert_bit_equal(fused.cpu(), want, f"fused fake quantize {cols} qtype={qtype}")
+            dmn, dmx = ops.minmax(x.cuda(), 1, cols)
+            dscale, dzp = ops.calculate_qparams(dmn, dmx, qtype=qtype, bits=8, symmetric=True)
+            sep = ops.fake_quantize(x.cuda(), dscale, dzp, out_dtype=torch.bfloat16, **kw)
+            assert_bit_equal(sep.cpu(), want, f"separate kernels {cols} qtype={qtype}")
