@@ -323,6 +323,8 @@ def standalone_ops_table(dev, peak, size=8192):
     for label, a in (("int8", QuantizationArgs(num_bits=8, symmetric=True, strategy="token", dynamic=True)),
                      ("fp8", QuantizationArgs(num_bits=8, type="float", symmetric=True, strategy="token", dynamic=True))):
         run(f"forward_quantize_dynamic_token_{label}_8192x4096", tok, lambda x, a=a: forward_quantize(None, x, "input", a), 2 * nt, 4 * nt, 4 * nt)
+    ga = QuantizationArgs(num_bits=8, type="float", symmetric=True, strategy="group", group_size=128, dynamic=True)
+    run("forward_quantize_dynamic_group128_fp8_8192x4096", tok, lambda x: forward_quantize(None, x, "input", ga), 2 * nt, 4 * nt, 4 * nt)
     run("minmax_group128", one, lambda w: ops.minmax(w, 1, 128), 2 * n, 2 * n, 2 * n)
     run("minmax_channel", one, lambda w: ops.minmax(w, 1, C), 2 * n, 2 * n, 2 * n)
     run("minmax_block128x128", one, lambda w: ops.minmax(w, 128, 128), 2 * n, 2 * n, 2 * n)

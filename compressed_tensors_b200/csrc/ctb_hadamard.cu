@@ -694,13 +694,37 @@ __global__ void __launch_bounds__(kThreads) absmax_quant_group_kernel(const HArg
                     continue;
                 }
             }
+            if constexpr (XF == F_BF16 && FOUT == F_BF16 && !ROT) {  // dynamic fake quantize, packed bf16x2 arithmetic
+                if (!q.slow) {
+                    const uint32_t w[4] = {raw[u].a.x, raw[u].a.y, raw[u].a.z, raw[u].a.w};
+                    uint32_t o[4];
+                    if constexpr (QK == QK_INT) {
+                        const __nv_bfloat162 lo2 = __float2bfloat162_rn(a.qmin), hi2 = __float2bfloat162_rn(a.qmax);
+                        const __nv_bfloat162 s2 = u32_as_bf162((__float_as_uint(q.s) >> 16) * 0x00010001u), z2 = u32_as_bf162(0u);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) o[j] = fake_int_pair_bf16(w[j], q.r, true, z2, lo2, hi2, s2);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) o[j] = fake_fp8_pair_bf16(w[j], q.r, true, q.s);
+                    }
+                    if (live) st_stream((char *)a.out + c * 16, make_uint4(o[0], o[1], o[2], o[3]));
+                    continue;
+                }
+            }
             // the zero point calculate_qparams returns is all zeros; adding it matters only for the sign of an
-            // fp8 zero (-0.0 + 0.0 = +0.0)
+            // fp8 zero (-0.0 + 0.0 = +0.0) and of a fake-quantized zero
             if constexpr (kPackedMax) {
                 if (live) decode8<XF>(raw[u], v);
             }
-            quant_prepare8<T>(v, q, QK == QK_FP8, 0.0f, a.qmin, a.qmax);
-            if (live) encode_store8<QK, FOUT>(a.out, c, v);
+            if constexpr (FOUT == F_BF16) {
+                quant_prepare8<T>(v, q, true, 0.0f, a.qmin, a.qmax);
+                round8<QK>(v);
+                dequant8<M>(v, q, true);
+                if (live) store8_float<F_BF16>(a.out, c, v);
+            } else {
+                quant_prepare8<T>(v, q, QK == QK_FP8, 0.0f, a.qmin, a.qmax);
+                if (live) encode_store8<QK, FOUT>(a.out, c, v);
+            }
         }
     }
 }
@@ -1025,8 +1049,11 @@ extern "C" int ctb_absmax_quantize(const ctb_qdesc *d, const void *x, const floa
     else if (d->codec == CTB_CODE_FP4X2 && qk == QK_FP4) fout = F_FP4X2;
     else if (d->codec == CTB_CODE_DTYPE && qk != QK_FP4 && d->q_dtype == CTB_BF16) fout = F_BF16;  // fake quantize: dequantized values
     else return fail(CTB_EUNSUPPORTED, "fused calibration writes PACK32 (4/8 bit), int8, e4m3, FP4X2 or (fake quantize) bf16");
-    if (fout == F_BF16 && !(n <= 0 && d->col_group == d->cols && d->scale_row_stride == 1 && d->cols / 8 <= 32 * 32))
-        return fail(CTB_EUNSUPPORTED, "fused dynamic fake quantize is built for whole rows of up to 8192 elements");
+    const bool whole_row = d->col_group == d->cols && d->scale_row_stride == 1;
+    const int64_t lanes = d->col_group / 8;
+    if (fout == F_BF16 && !(n <= 0 && ((whole_row && d->cols / 8 <= 32 * 32) ||
+                                       (lanes <= 32 && (lanes & (lanes - 1)) == 0 && d->scale_row_stride == d->cols / d->col_group))))
+        return fail(CTB_EUNSUPPORTED, "fused dynamic fake quantize is built for whole rows of up to 8192 elements and power-of-two groups of 8..256");
     if (d->rows == 0) return CTB_OK;
     HArgs a{};
     a.x = x; a.signs = signs; a.out = out; a.out_scale = out_scale; a.gs = gs;
@@ -1070,7 +1097,7 @@ extern "C" int ctb_absmax_quantize(const ctb_qdesc *d, const void *x, const floa
         absmax_quant_g16_fp4_kernel<<<grid_for(ngroups, kThreads * 2, 8), kThreads, 0, st>>>(a, ngroups);
         return after_launch("absmax_quant_g16_fp4_kernel");
     }
-    if (fout != F_BF16 && pow2(GL) && GL <= 32 && d->scale_row_stride == d->cols / d->col_group) {
+    if (!(fout == F_BF16 && whole_row) && pow2(GL) && GL <= 32 && d->scale_row_stride == d->cols / d->col_group) {
         a.GL = (int)GL;
         a.gl_shift = 0;
         while ((1 << a.gl_shift) < a.GL) ++a.gl_shift;
@@ -1081,6 +1108,8 @@ extern "C" int ctb_absmax_quantize(const ctb_qdesc *d, const void *x, const floa
         else if (fout == F_I8) CTB_AQ(QK_INT, F_I8);
         else if (fout == F_E4M3) CTB_AQ(QK_FP8, F_E4M3);
         else if (fout == F_FP4X2) CTB_AQ(QK_FP4, F_FP4X2);
+        else if (fout == F_BF16 && qk == QK_INT) CTB_AQ(QK_INT, F_BF16);
+        else if (fout == F_BF16 && qk == QK_FP8) CTB_AQ(QK_FP8, F_BF16);
         else return fail(CTB_EUNSUPPORTED, "no fused group kernel for this output format");
         return after_launch("absmax_quant_group_kernel");
     }

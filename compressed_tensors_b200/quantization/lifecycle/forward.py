@@ -133,11 +133,11 @@ def forward_quantize(module: torch.nn.Module, value: torch.Tensor, base_name: st
         return value
     g_idx = getattr(module, "weight_g_idx", None)
     global_scale = getattr(module, f"{base_name}_global_scale", None)
-    if _fused_dynamic_token(value, args, g_idx, global_scale):
-        # calibrate + fake-quantize a token in one pass: the same bits as the three separate kernels below
+    group = _fused_dynamic_group(value, args, g_idx, global_scale)
+    if group:
+        # calibrate + fake-quantize a token / group in one pass: the same bits as the three separate kernels below
         flat = value.reshape(-1, value.shape[-1])
-        fake, _ = ops.absmax_quantize(flat, qtype=qtype_code(args), bits=args.num_bits, col_group=flat.shape[-1], codec="dtype",
-                                      out_dtype=torch.bfloat16)
+        fake, _ = ops.absmax_quantize(flat, qtype=qtype_code(args), bits=args.num_bits, col_group=group, codec="dtype", out_dtype=torch.bfloat16)
         return fake.reshape(value.shape)
     if args.dynamic in (True, DynamicType.LOCAL):
         scale, zero_point = compute_dynamic_scales_and_zp(value=value, args=args, module=module, global_scale=global_scale)
@@ -147,12 +147,23 @@ def forward_quantize(module: torch.nn.Module, value: torch.Tensor, base_name: st
     return fake_quantize(x=value, scale=scale, zero_point=zero_point, args=args, g_idx=g_idx, global_scale=global_scale)
 
 
-def _fused_dynamic_token(value: torch.Tensor, args: QuantizationArgs, g_idx, global_scale) -> bool:
-    """Dynamic symmetric per-token int8 / fp8 quantization of a bf16 [..., tokens, hidden] tensor with hidden <= 8192:
-    the case the single-pass kernel is built for."""
-    return (args.dynamic is True and args.symmetric and args.strategy == QuantizationStrategy.TOKEN and args.num_bits == 8
-            and value.dtype == torch.bfloat16 and value.ndim == 3 and value.is_cuda and value.is_contiguous()
-            and value.shape[-1] % 8 == 0 and value.shape[-1] <= 8192 and g_idx is None and global_scale is None)
+def _fused_dynamic_group(value: torch.Tensor, args: QuantizationArgs, g_idx, global_scale) -> int:
+    """Group size for the single-pass calibrate + fake-quantize kernel, or 0 when the case is not one it is built for:
+    dynamic symmetric int (<= 8 bit) / fp8 quantization of a contiguous bf16 tensor, per token ([batch, tokens, hidden]
+    with hidden <= 8192) or per power-of-two group of 8..256 elements."""
+    cols = value.shape[-1]
+    if not (args.dynamic is True and args.symmetric and value.dtype == torch.bfloat16 and value.is_cuda and value.is_contiguous()
+            and cols % 8 == 0 and g_idx is None and global_scale is None):
+        return 0
+    if not (args.num_bits == 8 or (args.type == "int" and args.num_bits < 8)):
+        return 0
+    if args.strategy == QuantizationStrategy.TOKEN and value.ndim == 3 and cols <= 8192:
+        return cols
+    if args.strategy == QuantizationStrategy.GROUP and value.ndim >= 2:
+        g = args.group_size
+        if g and 8 <= g <= 256 and g & (g - 1) == 0 and cols % g == 0:
+            return g
+    return 0
 
 
 def wrap_module_forward_quantized(module: torch.nn.Module, scheme) -> None:

@@ -574,3 +574,26 @@ def test_fused_dynamic_token_fake_quantize_equals_separate_kernels(ops, orc):
             dscale, dzp = ops.calculate_qparams(dmn, dmx, qtype=qtype, bits=8, symmetric=True)
             sep = ops.fake_quantize(x.cuda(), dscale, dzp, out_dtype=torch.bfloat16, **kw)
             assert_bit_equal(sep.cpu(), want, f"separate kernels {cols} qtype={qtype}")
+
+
+def test_fused_dynamic_group_fake_quantize_matches_oracle(ops, orc):
+    """dynamic per-group fake quantization in one pass (group-128 FP8 activations of the FP8_BLOCK preset, int8 and
+    int4 groups) against the oracle's min/max -> qparams -> fake_quantize, and through forward_quantize"""
+    from compressed_tensors_b200.quantization import QuantizationArgs, forward_quantize
+
+    g = torch.Generator().manual_seed(13)
+    x = torch.randn(64, 1024, generator=g)
+    x[:, 17] *= 30
+    x[3, :128] = 0
+    x[4, :4] = torch.tensor([-0.0, 0.0, -1e-30, 1e-30])
+    x = x.to(torch.bfloat16)
+    for qtype, bits, group, tname in ((orc.QFLOAT, 8, 128, "float"), (orc.QINT, 8, 128, "int"), (orc.QINT, 4, 32, "int"), (orc.QINT, 8, 256, "int")):
+        mn, mx = orc.minmax(x, 1, group)
+        scale, zp = orc.calculate_qparams(mn, mx, qtype=qtype, bits=bits, symmetric=True)
+        kw = dict(qtype=qtype, bits=bits, col_group=group, row_group=1, scale_row_stride=1024 // group)
+        want = orc.fake_quantize(x, scale, zp, out_dtype=torch.bfloat16, **kw)
+        fused, fscale = ops.absmax_quantize(x.cuda(), qtype=qtype, bits=bits, col_group=group, codec="dtype", out_dtype=torch.bfloat16)
+        assert_bit_equal(fscale.cpu(), scale, f"scale g{group} {tname}{bits}")
+        assert_bit_equal(fused.cpu(), want, f"fused g{group} {tname}{bits}")
+        args = QuantizationArgs(num_bits=bits, type=tname, symmetric=True, strategy="group", group_size=group, dynamic=True)
+        assert_bit_equal(forward_quantize(None, x.cuda().reshape(2, 32, 1024), "input", args).cpu().reshape(64, 1024), want, f"forward_quantize g{group}")
