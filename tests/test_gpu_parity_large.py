@@ -597,3 +597,38 @@ def test_fused_dynamic_group_fake_quantize_matches_oracle(ops, orc):
         assert_bit_equal(fused.cpu(), want, f"fused g{group} {tname}{bits}")
         args = QuantizationArgs(num_bits=bits, type=tname, symmetric=True, strategy="group", group_size=group, dynamic=True)
         assert_bit_equal(forward_quantize(None, x.cuda().reshape(2, 32, 1024), "input", args).cpu().reshape(64, 1024), want, f"forward_quantize g{group}")
+
+
+def test_tiny_and_odd_shapes_through_the_fast_kernels(ops, orc):
+    """one row, one chunk, groups of 8 / 24 / 40 elements, blocks of 1 x 8 and 3 x 24, fewer chunks than a warp: the
+    packed quantize / fake_quantize / dequantize kernels, the packed min / max kernels and the fused dynamic fake
+    quantization against the oracle"""
+    g = torch.Generator().manual_seed(99)
+    shapes = [(1, 8, 1, 8), (1, 16, 1, 8), (3, 24, 1, 24), (3, 24, 3, 24), (5, 120, 1, 40), (5, 120, 5, 24), (2, 256, 1, 256), (7, 64, 7, 64),
+              (33, 8, 1, 8), (1, 8200, 1, 8200)]
+    for rows, cols, rg, cg in shapes:
+        x = (torch.randn(rows, cols, generator=g) * 0.1).to(torch.bfloat16)
+        mn, mx = orc.minmax(x, rg, cg)
+        dmn, dmx = ops.minmax(x.cuda(), rg, cg)
+        assert_bit_equal(dmn.cpu(), mn, f"min {rows}x{cols} tile {rg}x{cg}")
+        assert_bit_equal(dmx.cpu(), mx, f"max {rows}x{cols} tile {rg}x{cg}")
+        srs = cols // cg
+        for qtype, bits, sym, code_dt in ((orc.QINT, 4, True, torch.int8), (orc.QINT, 8, False, torch.int8), (orc.QFLOAT, 8, True, torch.float8_e4m3fn)):
+            scale, zp = orc.calculate_qparams(mn, mx, qtype=qtype, bits=bits, symmetric=sym)
+            for sc in (scale, scale.float()):
+                kw = dict(qtype=qtype, bits=bits, col_group=cg, row_group=rg, scale_row_stride=srs)
+                what = f"{rows}x{cols} tile {rg}x{cg} bits={bits} {sc.dtype}"
+                want = orc.quantize(x, sc, zp, out_dtype=code_dt, **kw)
+                got = ops.quantize(x.cuda(), sc.cuda(), zp.cuda(), out_dtype=code_dt, **kw)
+                assert_bit_equal(got.cpu(), want, "quantize " + what)
+                assert_bit_equal(ops.fake_quantize(x.cuda(), sc.cuda(), zp.cuda(), out_dtype=torch.bfloat16, **kw).cpu(),
+                                 orc.fake_quantize(x, sc, zp, out_dtype=torch.bfloat16, **kw), "fake " + what)
+                assert_bit_equal(ops.dequantize(got, sc.cuda(), zp.cuda(), out_dtype=torch.bfloat16, **kw).cpu(),
+                                 orc.dequantize(want, sc, zp, out_dtype=torch.bfloat16, **kw), "dequantize " + what)
+        if rg == 1 and (cg == cols or cg & (cg - 1) == 0) and cols <= 8192:
+            for qtype in (orc.QINT, orc.QFLOAT):
+                scale, zp = orc.calculate_qparams(mn, mx, qtype=qtype, bits=8, symmetric=True)
+                kw = dict(qtype=qtype, bits=8, col_group=cg, row_group=1, scale_row_stride=srs)
+                fused, fs = ops.absmax_quantize(x.cuda(), qtype=qtype, bits=8, col_group=cg, codec="dtype", out_dtype=torch.bfloat16)
+                assert_bit_equal(fs.cpu().reshape(scale.shape), scale, f"fused scale {rows}x{cols} g{cg}")
+                assert_bit_equal(fused.cpu(), orc.fake_quantize(x, scale, zp, out_dtype=torch.bfloat16, **kw), f"fused fake {rows}x{cols} g{cg}")
