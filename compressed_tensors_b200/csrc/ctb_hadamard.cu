@@ -135,7 +135,7 @@ __device__ __forceinline__ void rotate8(const HArgs &a, int64_t c, float (&v)[8]
 
 // weight_input rotation: one 8-element chunk per lane
 template <typename A, int XF>
-__global__ void __launch_bounds__(kThreads) hadamard_cols_kernel(const HArgs a) {
+__global__ void __launch_bounds__(kThreads, sizeof(A) == 8 ? 5 : 8) hadamard_cols_kernel(const HArgs a) {
     const int64_t padded = (a.chunks + 31) & ~(int64_t)31;
     for (int64_t c = (int64_t)blockIdx.x * kThreads + threadIdx.x; c < padded; c += (int64_t)gridDim.x * kThreads) {
         float v[8] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -743,8 +743,9 @@ __global__ void __launch_bounds__(kThreads) absmax_quant_g16_fp4_kernel(const HA
             const int64_t g = base + (int64_t)u * kThreads;
             raw[u][0] = raw[u][1] = make_uint4(0, 0, 0, 0);
             if (g < ngroups) {
-                raw[u][0] = ld_stream((const char *)a.x + g * 32);
-                raw[u][1] = ld_stream((const char *)a.x + g * 32 + 16);
+                // a lane's two halves share a 32-byte sector: let L1 keep it between the two instructions
+                raw[u][0] = __ldg(reinterpret_cast<const uint4 *>((const char *)a.x + g * 32));
+                raw[u][1] = __ldg(reinterpret_cast<const uint4 *>((const char *)a.x + g * 32 + 16));
             }
         }
 #pragma unroll
@@ -963,7 +964,8 @@ extern "C" int ctb_hadamard(const void *x, int32_t dtype, int64_t rows, int64_t 
         if (n >= 8 && n <= 256 && aligned16(x) && aligned16(out)) {
             HArgs a{};
             a.x = x; a.signs = signs; a.out = out; a.chunks = rows * cols / 8; a.n = n; a.L = n / 8; a.inverse = inverse; a.normalize = normalize; a.xdt = dtype;
-            int grid = grid_for(a.chunks, kThreads, 8);
+            // whole waves of resident blocks: 8 per SM at 32 registers (fp32), 5 at 48 (fp64)
+            int grid = grid_for(a.chunks, kThreads, precision == CTB_F64 ? 10 : 8);
 #define CTB_HC(A_)                                                                                   \
     if (dtype == CTB_BF16) hadamard_cols_kernel<A_, F_BF16><<<grid, kThreads, 0, st>>>(a);            \
     else if (dtype == CTB_F16) hadamard_cols_kernel<A_, F_F16><<<grid, kThreads, 0, st>>>(a);         \
@@ -1094,7 +1096,7 @@ extern "C" int ctb_absmax_quantize(const ctb_qdesc *d, const void *x, const floa
     }
     if (fout == F_FP4X2 && d->col_group == 16 && d->scale_row_stride == d->cols / 16) {
         const int64_t ngroups = d->rows * d->cols / 16;
-        absmax_quant_g16_fp4_kernel<<<grid_for(ngroups, kThreads * 2, 8), kThreads, 0, st>>>(a, ngroups);
+        absmax_quant_g16_fp4_kernel<<<grid_for(ngroups, kThreads * 2, 10), kThreads, 0, st>>>(a, ngroups);  // 47 registers: 5 resident blocks per SM, two waves
         return after_launch("absmax_quant_g16_fp4_kernel");
     }
     if (!(fout == F_BF16 && whole_row) && pow2(GL) && GL <= 32 && d->scale_row_stride == d->cols / d->col_group) {

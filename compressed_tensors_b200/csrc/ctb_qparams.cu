@@ -223,7 +223,7 @@ __global__ void __launch_bounds__(kThreads) minmax_warprow16_kernel(const uint4 
 
 // (c) one tile = the whole tensor: per-block partials into the workspace, then a one-block finish
 template <int F>
-__global__ void __launch_bounds__(kThreads) minmax_flat_kernel(const void *x, int dt, int64_t n, float *partial) {
+__global__ void __launch_bounds__(kThreads, 8) minmax_flat_kernel(const void *x, int dt, int64_t n, float *partial) {
     float mn = FLT_MAX, mx = -FLT_MAX;
     const int64_t chunks = n / 8;
     if constexpr (F == F_F32) {
