@@ -6,7 +6,8 @@ bf16, N(0, 0.02), synthetic), random-Hadamard rotation (block 128) fused with W4
 quantize + pack_to_int32, then unpack + dequantize.  Layers are dealt to the ranks in contiguous
 blocks (strong scaling: the model is fixed, ranks split it); no collective is on the data path.
 
-One "step" = compress every weight of the shard, then decompress every weight of the shard.
+One "step" = ModelCompressor.compress_model (rotate + calibrate + quantize + pack, fused) then
+ModelCompressor.decompress_model (unpack + dequantize) of the rank's share of a Llama-3-8B-shaped module tree.
 value = bf16 bytes through both directions (2 x weight bytes, all ranks) / max-over-ranks device time.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
@@ -105,6 +106,41 @@ def time_region(fn, steps, stream):
     return start.elapsed_time(end) / 1e3  # seconds
 
 
+def build_model(layers, shapes, weights):
+    """A module tree with Llama's names: model.layers.<i>.self_attn.q_proj ... mlp.down_proj, one Linear per weight
+    (no bias), the given tensors as parameters.  No forward pass is needed: the codec walks parameters."""
+    nn = torch.nn
+    root = nn.Module()
+    root.add_module("model", nn.Module())
+    root.model.add_module("layers", nn.ModuleList())
+    it = iter(weights)
+    for _ in layers:
+        layer = nn.Module()
+        for name, o, i in shapes:
+            parent = layer
+            *path, leaf = name.split(".")
+            for p in path:
+                if not hasattr(parent, p):
+                    parent.add_module(p, nn.Module())
+                parent = getattr(parent, p)
+            lin = nn.Linear(i, o, bias=False, dtype=torch.bfloat16, device="meta")
+            lin.weight = nn.Parameter(next(it), requires_grad=False)
+            parent.add_module(leaf, lin)
+        root.model.layers.append(layer)
+    return root
+
+
+def configs(pkg):
+    """(transform config, quantization config) of the workload, built from `pkg` (this package or the reference)."""
+    q, t = pkg.quantization, pkg.transform
+    tcfg = t.TransformConfig(config_groups={"u": t.TransformScheme(type="random-hadamard", head_dim=128, apply=[
+        t.TransformArgs(targets=["Linear"], ignore=["lm_head"], location="weight_input")])})
+    qcfg = q.QuantizationConfig(config_groups={"group_0": q.QuantizationScheme(
+        targets=["Linear"], weights=q.QuantizationArgs(num_bits=4, symmetric=True, strategy="group", group_size=128))},
+        ignore=["lm_head"], format="pack-quantized")
+    return tcfg, qcfg
+
+
 def cpu_pass(ws, signs):
     """One pass of the path on the host through the oracle port (rotate, calibrate, quantize, pack, unpack, dequantize)."""
     from oracle import ref as orc
@@ -120,35 +156,95 @@ def cpu_pass(ws, signs):
     return out
 
 
+SAMPLE = (("self_attn.q_proj", 4096, 4096), ("self_attn.k_proj", 1024, 4096), ("mlp.gate_proj", 14336, 4096))
+SAMPLE_TEXT = "q_proj 4096x4096 + k_proj 1024x4096 + gate_proj 14336x4096 of one decoder layer per step"
+
+
 def cpu_sample():
     """Bounded sample of the workload for the CPU arm: q_proj, k_proj and gate_proj of one layer."""
     g = torch.Generator().manual_seed(SEED)
-    return [(torch.randn(o, i, generator=g) * 0.02).to(torch.bfloat16) for o, i in ((4096, 4096), (1024, 4096), (14336, 4096))]
+    return [(torch.randn(o, i, generator=g) * 0.02).to(torch.bfloat16) for _, o, i in SAMPLE]
+
+
+class CpuArm:
+    """The CPU side of the comparison on the bounded sample.  kind "reference": the reference package itself
+    (oracle/_ref, installed from the checkout by __graft_entry__.build()) through its own public calls --
+    apply_transform_config, min-max scales by calculate_qparams, ModelCompressor.compress_model and
+    decompress_model -- in eager mode on all host threads.  kind "port": the C + OpenMP restatement, used only
+    where the reference package is not present."""
+
+    def __init__(self):
+        from oracle import reference
+        self.cores = os.cpu_count() or 1
+        self.ws = cpu_sample()
+        self.elems = sum(w.numel() for w in self.ws)
+        self.kind = "reference" if reference.available() else "port"
+        if self.kind == "reference":
+            torch.set_num_threads(self.cores)
+            self.ct = reference.load()
+            import compressed_tensors.compressors, compressed_tensors.quantization, compressed_tensors.transform  # noqa: F401
+        else:
+            from oracle import ref as orc
+            orc.build()
+            orc.set_threads(self.cores)
+            self.signs = make_signs()
+
+    def one_pass(self):
+        if self.kind == "port":
+            return cpu_pass(self.ws, self.signs)
+        import copy
+
+        ct = self.ct
+        from compressed_tensors.quantization.utils.helpers import calculate_qparams
+        tcfg, qcfg = configs(ct)
+        model = build_model([0], SAMPLE, [w.clone() for w in self.ws])
+        with torch.no_grad():
+            ct.transform.apply_transform_config(model, tcfg)
+            ct.quantization.apply_quantization_config(model, qcfg)
+            for m in model.modules():
+                a = getattr(getattr(m, "quantization_scheme", None), "weights", None)
+                if a is None:
+                    continue
+                grouped = m.weight.data.unflatten(-1, (-1, a.group_size))
+                scale, _ = calculate_qparams(grouped.amin(-1), grouped.amax(-1), a)
+                m.weight_scale.data = scale.reshape(m.weight_scale.shape).to(m.weight_scale.dtype)
+            mc = ct.compressors.ModelCompressor(quantization_config=copy.deepcopy(qcfg))
+            mc.compress_model(model)
+            mc.decompress_model(model)
+        return self.elems
+
+    def time(self, steps, warmup):
+        for _ in range(warmup):
+            self.one_pass()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            self.one_pass()
+        dt = (time.perf_counter() - t0) / steps
+        return dt, 2 * 2 * self.elems / dt / 1e9
+
+
+def workload_config(layers, world, precision):
+    return {"workload": WORKLOAD, "layers": layers, "partition": f"layers/{world}",
+            "hadamard_accumulate": {"f64": "float64 butterfly (bit-identical to the reference)", "f32": "float32 butterfly",
+                                    "tc": "tcgen05 bf16 x bf16 -> fp32 in TMEM"}[precision],
+            "l2": "inputs larger than L2 (no flush needed)"}
 
 
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    from oracle import ref as orc
-    orc.build()
-    cores = os.cpu_count() or 1
-    orc.set_threads(cores)
-    ws, signs = cpu_sample(), make_signs()
-    elems = sum(w.numel() for w in ws)
-    for _ in range(args.warmup):
-        cpu_pass(ws, signs)
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        cpu_pass(ws, signs)
-    dt = (time.perf_counter() - t0) / args.steps
-    val = 2 * 2 * elems / dt / 1e9
-    sample = "q_proj 4096x4096 + k_proj 1024x4096 + gate_proj 14336x4096 of one layer per step"
+    arm = CpuArm()
+    dt, val = arm.time(args.steps, args.warmup)
+    cfg = workload_config(args.layers, args.gpus, args.precision)
+    cfg["sample"] = SAMPLE_TEXT
+    cfg["path"] = ("reference package: apply_transform_config -> calculate_qparams -> ModelCompressor.compress_model -> decompress_model"
+                   if arm.kind == "reference" else "C + OpenMP restatement of the same calls")
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic", "config": {"workload": WORKLOAD, "sample": sample},
-        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "dtype": "bf16", "data": "synthetic", "config": cfg,
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": arm.cores, "kind": arm.kind, "sample": SAMPLE_TEXT},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
@@ -262,6 +358,122 @@ def per_config_table(dev, peak):
     return out
 
 
+def copy_ceiling(dev, bytes_w, bytes_p, world):
+    """What the PCIe copies of one end-to-end step cost on their own: the step's byte mix (weights in, packed out,
+    packed in, weights out) as bare copies between page-locked host memory and the device, both directions at
+    once on two streams, every rank doing the same at the same time.  Returned in the metric's unit (bf16 weight
+    bytes through both directions per second, all ranks), so that e2e.value can be read against it."""
+    import torch.distributed as dist
+
+    chunk = 256 << 20
+    host_a = torch.empty(chunk, dtype=torch.uint8, pin_memory=True)
+    host_b = torch.empty(chunk, dtype=torch.uint8, pin_memory=True)
+    dev_a = torch.empty(chunk, dtype=torch.uint8, device=dev)
+    dev_b = torch.empty(chunk, dtype=torch.uint8, device=dev)
+    s1, s2 = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+
+    def run():
+        for stream, dst, src, total in ((s1, dev_a, host_a, bytes_w + bytes_p), (s2, host_b, dev_b, bytes_p + bytes_w)):
+            with torch.cuda.stream(stream):
+                left = total
+                while left > 0:
+                    n = min(left, chunk)
+                    dst[:n].copy_(src[:n], non_blocking=True)
+                    left -= n
+        s1.synchronize()
+        s2.synchronize()
+
+    run()
+    if world > 1:
+        dist.barrier()
+    t0 = time.perf_counter()
+    run()
+    dt = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+    return 2 * bytes_w * world / float(dt) / 1e9
+
+
+def per_config_cpu(ct):
+    """Seconds the reference's own functions take on this host for the stages behind each per_config row (all host
+    threads, eager mode, seeded inputs of the named shapes; best of two, a single run for stages over half a second)."""
+    from compressed_tensors.compressors.quantized_compressors.fp4_quantized import pack_fp4_to_uint8, unpack_fp4_from_uint8
+    from compressed_tensors.compressors.quantized_compressors.pack_quantized import pack_to_int32, unpack_from_int32
+    from compressed_tensors.compressors.sparse_compressors.sparse_24_bitmask import (get_24_bytemasks, sparse24_bitmask_compress,
+                                                                                       sparse24_bitmask_decompress)
+    from compressed_tensors.compressors.sparse_compressors.sparse_bitmask import bitmask_compress, bitmask_decompress
+    from compressed_tensors.quantization import QuantizationArgs
+    from compressed_tensors.quantization.lifecycle.forward import dequantize, quantize
+    from compressed_tensors.quantization.utils.helpers import calculate_qparams, compute_dynamic_scales_and_zp, generate_gparam
+
+    g = torch.Generator().manual_seed(SEED + 1)
+    out = {}
+
+    def timed(name, fn):
+        t0 = time.perf_counter()
+        res = fn()
+        dt = time.perf_counter() - t0
+        if dt < 0.5:
+            t0 = time.perf_counter()
+            res = fn()
+            dt = min(dt, time.perf_counter() - t0)
+        out[name] = dt
+        return res
+
+    def rnd(r, c, std=0.02):
+        return (torch.randn(r, c, generator=g) * std).to(torch.bfloat16)
+
+    with torch.no_grad():
+        w = rnd(4096, 4096)
+        a4 = QuantizationArgs(num_bits=4, symmetric=True, strategy="group", group_size=128)
+
+        def c1():
+            grouped = w.unflatten(-1, (-1, 128))
+            s, z = calculate_qparams(grouped.amin(-1), grouped.amax(-1), a4)
+            return pack_to_int32(quantize(w, s, z, a4, dtype=torch.int8), 4), s
+        words, s4 = timed("c1_w4a16_calibrate_quantize_pack", c1)
+        timed("c1_w4a16_unpack_dequantize", lambda: dequantize(unpack_from_int32(words, 4, w.shape), s4))
+        a8 = QuantizationArgs(num_bits=8, type="float", symmetric=True, strategy="channel")
+
+        def c2w():
+            s, z = calculate_qparams(w.amin(-1, keepdim=True), w.amax(-1, keepdim=True), a8)
+            return quantize(w, s, z, a8, dtype=torch.float8_e4m3fn)
+        timed("c2_fp8_weight_channel_calibrate_quantize", c2w)
+        x = torch.randn(1, 8192, 4096, generator=g)
+        x[..., torch.randperm(4096, generator=g)[:41]] *= 20
+        x = x.to(torch.bfloat16)
+        at = QuantizationArgs(num_bits=8, type="float", symmetric=True, strategy="token", dynamic=True)
+
+        def c2a():
+            s, z = compute_dynamic_scales_and_zp(x, at, torch.nn.Identity())
+            return quantize(x, s, z, at, dtype=torch.float8_e4m3fn), s
+        xq, sx = timed("c2_fp8_activation_token_calibrate_quantize", c2a)
+        timed("c2_fp8_activation_dequantize", lambda: dequantize(xq, sx, None, at))
+        wn = rnd(14336, 4096)
+        af = QuantizationArgs(num_bits=4, type="float", symmetric=True, strategy="tensor_group", group_size=16)
+
+        def c3():
+            mn, mx = torch.aminmax(wn)
+            gs = generate_gparam(mn, mx)
+            grouped = wn.unflatten(-1, (-1, 16))
+            s, z = calculate_qparams(grouped.amin(-1), grouped.amax(-1), af, global_scale=gs)
+            return pack_fp4_to_uint8(quantize(wn, s, z, af, global_scale=gs)), s, gs
+        packed, sn, gs = timed("c3_nvfp4_amax_scales_quantize_pack", c3)
+        timed("c3_nvfp4_unpack_dequantize",
+              lambda: dequantize(unpack_fp4_from_uint8(packed, 14336, 4096), sn, global_scale=gs, dtype=torch.bfloat16))
+        ws = rnd(4096, 11008)
+        ws = torch.where(get_24_bytemasks(ws), ws, torch.zeros((), dtype=ws.dtype))
+        s, z = calculate_qparams(ws.amin(-1, keepdim=True), ws.amax(-1, keepdim=True), a8)
+        q = quantize(ws, s, z, a8, dtype=torch.float8_e4m3fn)
+        vals, bm = timed("c4a_sparse24_compress_e4m3", lambda: sparse24_bitmask_compress(q))
+        timed("c4a_sparse24_decompress_e4m3", lambda: sparse24_bitmask_decompress(vals, bm, q.shape))
+        wu = rnd(4096, 4096)
+        wu[torch.rand(4096, 4096, generator=g) < 0.5] = 0
+        v, b, _ = timed("c4b_bitmask_compress_bf16_50pct", lambda: bitmask_compress(wu))
+        timed("c4b_bitmask_decompress_bf16_50pct", lambda: bitmask_decompress(v, b, wu.shape))
+    return out
+
+
 def standalone_ops_table(dev, peak, size=8192):
     """Device-timed throughput of the reference's operators as separate calls with given qparams (the building blocks the
     compressors and the calibration lifecycle call one by one) on a size x size bf16 tensor: quantize to packed words /
@@ -357,8 +569,7 @@ def main():
     ap.add_argument("--precision", default="tc", choices=["f64", "f32", "tc"],
                     help="Hadamard rotation: float64 butterfly (bit-identical to the reference), float32 butterfly, or tcgen05 tensor cores with fp32 accumulators")
     ap.add_argument("--layers", type=int, default=32, help="decoder layers of the model (32 = Llama-3-8B)")
-    ap.add_argument("--no-graphs", action="store_true")
-    ap.add_argument("--no-batch", action="store_true", help="one launch per tensor instead of one grid per shard")
+    ap.add_argument("--no-copy-ceiling", action="store_true", help="skip timing bare pinned copies with the round trip's byte mix")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-per-config", action="store_true", help="skip the C1-C4 per-scheme table")
@@ -388,20 +599,40 @@ def main():
             dist.destroy_process_group()
         return
 
-    model = parallel.LLAMA3_8B
-    shapes = parallel.linear_shapes(model)
+    import compressed_tensors_b200 as ctb
+    import compressed_tensors_b200.compressors, compressed_tensors_b200.quantization, compressed_tensors_b200.transform  # noqa: F401
+    from compressed_tensors_b200.compressors import ModelCompressor
+
+    shape = parallel.LLAMA3_8B
+    shapes = parallel.linear_shapes(shape)
     my_layers = parallel.partition_layers(args.layers, world, rank)
     weights = make_weights(my_layers, dev, shapes)
-    signs = make_signs().to(dev)
-    precision = {"f64": torch.float64, "f32": torch.float32, "tc": ops.ROT_TENSOR}[args.precision]
-    codec = parallel.ShardCodec(weights, group_size=128, hadamard_n=128, signs=signs, precision=precision, use_graphs=not args.no_graphs, batch=not args.no_batch)
-    stream = torch.cuda.current_stream()
-    my_elems = codec.numel
     total_elems = sum(o * i for _, o, i in shapes) * args.layers
+    rank_elems = sum(w.numel() for w in weights)
+    tcfg, qcfg = configs(ctb)
+    rotation = {"f64": "exact", "f32": "float32", "tc": "tensor"}[args.precision]
+
+    def new_compressor():
+        return ModelCompressor(quantization_config=qcfg.model_copy(deep=True), transform_config=tcfg, rotation_precision=rotation)
+
+    # ---- device-resident: the module tree lives on the GPU, both calls leave their results there
+    model = build_model(my_layers, shapes, [w.clone() for w in weights])
+    ctb.quantization.apply_quantization_config(model, qcfg)
+    mc = new_compressor()
+    mc.engine.record_kernel_times = True
+    stream = torch.cuda.current_stream()
+
+    def compress():
+        if getattr(model, "transform_config", None) is not None:
+            del model.transform_config  # the dequantized weights of the last step are this step's fresh, un-rotated model
+        mc.compress_model(model)
+
+    def decompress():
+        mc.decompress_model(model)
 
     def step():
-        codec.compress()
-        codec.decompress()
+        compress()
+        decompress()
 
     def barrier():
         if world > 1:
@@ -411,104 +642,133 @@ def main():
     for _ in range(args.warmup):
         step()
     barrier()
-    launches0 = _lib.launch_count()
+    mc.engine.kernel_times.clear()
+    launches0 = mc.engine.launches
     sampler = ClockSampler(local) if rank == 0 else None
     t = time_region(step, args.steps, stream)
     barrier()
     clocks = sampler.stop() if sampler else None
-    launches = _lib.launch_count() - launches0
-    if codec.use_graphs:
-        launches = 2 * codec.launches_per_pass * args.steps  # replayed from CUDA graphs
-    # phase timings for the roofline (same region, compress and decompress timed apart)
-    tc = time_region(codec.compress, args.steps, stream)
-    td = time_region(codec.decompress, args.steps, stream)
-    barrier()
+    launches = mc.engine.launches - launches0
+    # duration of the two kernels themselves inside that timed region (CUDA events recorded around each launch)
+    tc = sum(a.elapsed_time(b) for kind, a, b in mc.engine.kernel_times if kind == "compress") / 1e3
+    td = sum(a.elapsed_time(b) for kind, a, b in mc.engine.kernel_times if kind == "decompress") / 1e3
+    mc.engine.record_kernel_times = False
+    mc.engine.kernel_times.clear()
     times = torch.tensor([t, tc, td], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     t, tc, td = (float(v) for v in times.cpu())
 
-    # ---- end to end: host buffers in, host buffers out, copies inside the timed region
+    # ---- end to end: the module tree lives in page-locked HOST memory; copies in both directions are inside the timed region
     e2e = None
     if not args.no_e2e:
         host_w = [torch.empty(w.shape, dtype=w.dtype, pin_memory=True).copy_(w) for w in weights]
         torch.cuda.synchronize()
-        trip = parallel.HostRoundTrip(host_w, group=len(shapes), device=dev, signs=signs, precision=precision)
-        trip.run()
+        hmodel = build_model(my_layers, shapes, host_w)
+        ctb.quantization.apply_quantization_config(hmodel, qcfg)
+        hmc = new_compressor()
+        del host_w
+
+        def trip():
+            if getattr(hmodel, "transform_config", None) is not None:
+                del hmodel.transform_config
+            with hmc.pipelined():
+                hmc.compress_model(hmodel)
+                hmc.decompress_model(hmodel)
+
+        first = {n: p.data.clone() for n, p in list(hmodel.named_parameters())[:len(shapes)]}
+        trip()
+        # the restored host weights of the first layer must be what the device path produces from the same weights
+        check = build_model(my_layers[:1], shapes, [v.to(dev) for v in first.values()])
+        ctb.quantization.apply_quantization_config(check, qcfg)
+        cmc = new_compressor()
+        cmc.compress_model(check)
+        cmc.decompress_model(check)
+        torch.cuda.synchronize()
+        got = {n: p.data for n, p in hmodel.named_parameters() if n.endswith(".weight") and n.startswith("model.layers.0.")}
+        want = {n: p.data.cpu() for n, p in check.named_parameters() if n.endswith(".weight")}
+        for n, v in want.items():
+            assert torch.equal(got[n], v), f"end-to-end result differs from the device path: {n}"
+        del check, cmc, first, got, want
         barrier()
+        bytes_w = 2 * rank_elems
+        bytes_p = rank_elems // 2 + 2 * (rank_elems // 128)
         k = max(1, min(args.steps, 3))
         t0 = time.perf_counter()
         for _ in range(k):
-            trip.run()
+            trip()
         te = torch.tensor([(time.perf_counter() - t0) / k], dtype=torch.float64, device=dev)
+        # the same trip without letting the two calls overlap (each call waits for its own results)
+        t0 = time.perf_counter()
+        if getattr(hmodel, "transform_config", None) is not None:
+            del hmodel.transform_config
+        hmc.compress_model(hmodel)
+        hmc.decompress_model(hmodel)
+        ts = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device=dev)
+        ceiling = None if args.no_copy_ceiling else copy_ceiling(dev, bytes_w, bytes_p, world)
         if world > 1:
             dist.all_reduce(te, op=dist.ReduceOp.MAX)
+            dist.all_reduce(ts, op=dist.ReduceOp.MAX)
         e2e = {"value": 2 * 2 * total_elems / float(te) / 1e9, "unit": UNIT,
-               "h2d_bytes_per_step": trip.h2d_bytes, "d2h_bytes_per_step": trip.d2h_bytes,
+               "h2d_bytes_per_step": bytes_w + bytes_p, "d2h_bytes_per_step": bytes_p + bytes_w,
                "ms_per_step": float(te) * 1e3, "bytes_are": "per rank",
-               "path": "HostRoundTrip: pinned host -> device -> fused kernels -> pinned host, 3 streams, one decoder layer per step, stages issued one step apart"}
-        # the restored host weights must be what the device path produced
-        check = parallel.ShardCodec(weights[:len(shapes)], signs=signs, precision=precision)
-        check.compress(), check.decompress()
-        torch.cuda.synchronize()
-        for j in range(len(shapes)):
-            assert torch.equal(trip.host_r[j], check.restored[j].cpu()), "end-to-end result differs from the device path"
-        del check
-        del host_w, trip
+               "sequential_value": 2 * 2 * total_elems / float(ts) / 1e9,
+               "copy_ceiling_gbs": ceiling,
+               "path": "ModelCompressor.compress_model + ModelCompressor.decompress_model on a module tree in page-locked host memory, "
+                       "inside ModelCompressor.pipelined(): host -> device -> fused kernels -> host, one decoder layer per pipeline step; "
+                       "sequential_value = the same two calls without pipelined()"}
+        del hmodel, hmc
 
     if rank == 0:
         peak, peak_kind = peaks()
         ms = t / args.steps * 1e3
-        # dominant kernel: the fused rotate+calibrate+quantize+pack launches of the compress phase.
-        # per-rank algorithmic bytes of one compress pass / per-rank device time of that pass
-        rank_elems = total_elems / world
+        # dominant kernel: the fused rotate+calibrate+quantize+pack launch of compress_model.
+        # per-rank algorithmic bytes of one compress pass / average device time of that launch
         achieved = ALG_BYTES_PER_ELEM * rank_elems / (tc / args.steps) / 1e9
+        cfg = workload_config(args.layers, world, args.precision)
+        cfg.update({"tensors_per_rank": len(weights), "api": "ModelCompressor.compress_model / decompress_model on a CUDA-resident module tree",
+                    "one_grid_per_shard": launches == 2 * args.steps})
         out = {
             "metric": METRIC, "value": 2 * 2 * total_elems / (t / args.steps) / 1e9, "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "layers": args.layers, "tensors_per_rank": len(weights), "partition": f"layers/{world}",
-                       "hadamard_accumulate": {"f64": "float64 butterfly (bit-identical to the reference)", "f32": "float32 butterfly",
-                                               "tc": "tcgen05 bf16 x bf16 -> fp32 in TMEM"}[args.precision], "l2": "inputs larger than L2 (no flush needed)",
-                       "cuda_graphs": codec.use_graphs, "one_grid_per_shard": codec.batched},
-            "compress_gbs": 2 * total_elems / (tc / args.steps) / 1e9, "decompress_gbs": 2 * total_elems / (td / args.steps) / 1e9,
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": cfg,
+            "kernel_compress_gbs": 2 * rank_elems * world / (tc / args.steps) / 1e9, "kernel_decompress_gbs": 2 * rank_elems * world / (td / args.steps) / 1e9,
+            "kernel_ms_per_step": (tc + td) / args.steps * 1e3,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": (NCU_TRAFFIC_BYTES_PER_ELEM * rank_elems) if args.precision == "tc" else None,
                          "traffic_source": "ncu capture of the 2-layer case scaled by elements per launch", "kernel": "rotquant128_tc_kernel" if args.precision == "tc" else "rotquant128_kernel", "peak_kind": peak_kind,
+                         "timed": "CUDA events around the launch, on its stream, inside the timed region",
                          "decompress_frac": ALG_BYTES_PER_ELEM * rank_elems / (td / args.steps) / 1e9 / peak},
             "clocks": clocks, "gpu_launches": int(launches), "e2e": e2e,
         }
         if world == 1 and not args.no_other_modes:
-            # the same compress pass with the other two rotation arithmetics, for the record
+            # the same compress pass with the other two rotation arithmetics, for the record (kernel time only)
             modes = {}
             for tag, prec in (("f64", torch.float64), ("f32", torch.float32), ("tc", ops.ROT_TENSOR)):
                 if tag == args.precision:
                     continue
-                alt = parallel.ShardCodec(weights, group_size=128, hadamard_n=128, signs=signs, precision=prec, use_graphs=False)
+                alt = parallel.ShardCodec(weights, group_size=128, hadamard_n=128, signs=make_signs().to(dev), precision=prec, use_graphs=False)
                 alt.compress()
                 torch.cuda.synchronize()
                 ta = time_region(alt.compress, 3, stream) / 3
                 modes[tag] = {"compress_gbs": round(2 * total_elems / ta / 1e9, 1), "frac": round(ALG_BYTES_PER_ELEM * total_elems / ta / 1e9 / peak, 3)}
                 del alt
             out["other_rotation_modes"] = modes
+        arm = None
+        if world == 1 and not args.no_cpu_baseline:
+            arm = CpuArm()
         if world == 1 and not args.no_per_config:
-            del codec, weights
+            del model, mc, weights
             torch.cuda.empty_cache()
             out["per_config"] = per_config_table(dev, peak)
-        if world == 1 and not args.no_cpu_baseline:
-            from oracle import ref as orc
-            orc.build()
-            cores = os.cpu_count() or 1
-            orc.set_threads(cores)
-            ws, sg = cpu_sample(), make_signs()
-            cpu_pass(ws, sg)
-            t0 = time.perf_counter()
-            reps = 2
-            for _ in range(reps):
-                cpu_pass(ws, sg)
-            dt = (time.perf_counter() - t0) / reps
-            out["cpu_baseline"] = {"value": 2 * 2 * sum(w.numel() for w in ws) / dt / 1e9, "unit": UNIT, "cores": cores, "kind": "port",
-                                   "sample": "q_proj + k_proj + gate_proj of one layer, 2 passes"}
+            if arm is not None and arm.kind == "reference":
+                for name, sec in per_config_cpu(arm.ct).items():
+                    if name in out["per_config"]:
+                        out["per_config"][name]["cpu_reference_ms"] = round(sec * 1e3, 1)
+                        out["per_config"][name]["cpu_reference_dense_gbs"] = round(out["per_config"][name]["dense_gbs"] * out["per_config"][name]["us"] / (sec * 1e6), 3)
+        if arm is not None:
+            dt, val = arm.time(2, 1)
+            out["cpu_baseline"] = {"value": val, "unit": UNIT, "cores": arm.cores, "kind": arm.kind, "sample": SAMPLE_TEXT + ", 2 passes"}
         print(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()

@@ -1,0 +1,518 @@
+"""The machinery under ModelCompressor: whole-model compress / decompress as a few large grids and a
+copy pipeline instead of the reference's tensor-by-tensor walk
+(compressors/model_compressors/model_compressor.py:453-617 driving quantized_compressors/base.py:69-134
+and sparse_compressors/base.py:66-107 once per module).
+
+A *job* is one module's parameters.  Jobs whose weights already live on a GPU are processed where they are,
+all at once.  Jobs whose weights live in host memory are cut into *steps* of a few hundred megabytes and
+streamed: copy-in, kernels and copy-out of consecutive steps run on three streams, so both PCIe directions
+and the GPU work at the same time, nothing synchronises per tensor, and results land in page-locked host
+memory.  Inside a step, every weight of a scheme that has a whole-shard entry point (W4A16 group 128 with
+or without the block-128 Hadamard rotation in front, and its unpack + dequantize) goes through ONE launch;
+everything else calls the per-tensor compressor on the device tensors of the step.
+
+The results are those of the per-tensor walk: the batched kernels are the per-tensor kernels run over a
+table, and the per-tensor compressors are the registered ones.
+"""
+import contextlib
+import ctypes
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+from torch import Tensor
+
+from ... import _lib as L
+from ... import ops
+from ...config import CompressionFormat
+from ...quantization.quant_args import QuantizationArgs, QuantizationStrategy, QuantizationType
+from ...quantization.utils.helpers import calculate_qparams, generate_gparam, is_fp4
+
+__all__ = ["Job", "CodecEngine", "minmax_qparams", "is_w4a16_g128", "STEP_BYTES"]
+
+STEP_BYTES = 384 << 20   # host-resident work is streamed in steps of about this many input bytes
+MAX_INFLIGHT = 6         # steps whose device buffers may be alive at once
+_ALIGN = 256
+
+# parameters a quantization compressor reads next to the weight
+_QPARAMS = ("weight_scale", "weight_zero_point", "weight_g_idx", "weight_global_scale")
+
+
+def is_w4a16_g128(args: Optional[QuantizationArgs]) -> bool:
+    """True for the scheme the whole-shard int4 entry points are built for: symmetric int4, group 128, static."""
+    return (args is not None and args.type == QuantizationType.INT and args.num_bits == 4 and args.symmetric
+            and args.strategy == QuantizationStrategy.GROUP.value and args.group_size == 128 and not args.dynamic
+            and args.actorder is None)
+
+
+@torch.no_grad()
+def minmax_qparams(weight: Tensor, args: QuantizationArgs) -> Dict[str, Tensor]:
+    """Min-max calibration of one weight on its device: `weight_scale`, `weight_zero_point` and, for NVFP4,
+    `weight_global_scale`, shaped as quantization/lifecycle/initialize.py:155-280 shapes them
+    (quantization/utils/helpers.py:67-146 calculate_qparams over the strategy's reduction)."""
+    rows, cols = weight.shape
+    out: Dict[str, Tensor] = {}
+    gs = None
+    strategy = QuantizationStrategy(args.strategy)
+    if strategy == QuantizationStrategy.TENSOR_GROUP:
+        mn, mx = ops.minmax(weight, rows, cols)
+        gs = generate_gparam(mn.reshape(()), mx.reshape(()))
+        out["weight_global_scale"] = gs
+    if strategy in (QuantizationStrategy.GROUP, QuantizationStrategy.TENSOR_GROUP):
+        mn, mx = ops.minmax(weight, 1, args.group_size)
+    elif strategy == QuantizationStrategy.CHANNEL:
+        mn, mx = ops.minmax(weight, 1, cols)
+    elif strategy == QuantizationStrategy.TENSOR:
+        mn, mx = ops.minmax(weight, rows, cols)
+        mn, mx = mn.reshape(()), mx.reshape(())
+    elif strategy == QuantizationStrategy.BLOCK:
+        bh, bw = args.block_structure
+        mn, mx = ops.minmax(weight, bh, bw)
+    else:
+        raise NotImplementedError(f"weight calibration for strategy {args.strategy}")
+    scale, zp = calculate_qparams(mn, mx, args, global_scale=gs if is_fp4(args) else None)
+    out["weight_scale"], out["weight_zero_point"] = scale, zp
+    return out
+
+
+@dataclass
+class Job:
+    """One module's parameters on their way through a compressor."""
+
+    prefix: str
+    state: Dict[str, Tensor]                    # local parameter name -> tensor, where the caller keeps it
+    scheme: object = None                       # QuantizationScheme or None
+    compressor: object = None                   # the quantization compressor of the module's format, or None
+    sparse: bool = False                        # the module is a target of the sparsity compressor
+    transforms: Sequence = ()                   # weight-side transforms still to be fused (compress only)
+    kind: str = "generic"
+    shape: Optional[Tuple[int, int]] = None     # dense weight shape where it is known without reading a tensor
+    # results; parameters that pass through unchanged are not repeated in any of them
+    out: Dict[str, Tensor] = field(default_factory=dict)         # what compress_weight / decompress_weight returned
+    qparams: Dict[str, Tensor] = field(default_factory=dict)     # scales the pass calibrated itself (fused rotation)
+    sparse_out: Dict[str, Tensor] = field(default_factory=dict)  # the sparsity compressor's parameters (replace `weight`)
+    quantized: bool = False                                      # compress_weight ran: `out` stands for `weight`
+
+    def results(self):
+        """(dict, name, tensor) over everything the pass produced."""
+        for d in (self.out, self.qparams, self.sparse_out):
+            for name, value in list(d.items()):
+                yield d, name, value
+
+
+def _nbytes(t: Tensor) -> int:
+    return t.numel() * t.element_size()
+
+
+def _up(n: int) -> int:
+    return (n + _ALIGN - 1) // _ALIGN * _ALIGN
+
+
+class _Arena:
+    """A buffer handing out 256-byte aligned views: one allocation per step and side instead of one per tensor, and
+    one contiguous span for the tensor map of the tensor-core kernel."""
+
+    def __init__(self, nbytes: int, device=None, pinned: bool = False):
+        if pinned:
+            self.buf = torch.empty(max(nbytes, 1), dtype=torch.uint8, pin_memory=True)
+        else:
+            self.buf = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=device)
+        self.off = 0
+        self._typed: Dict[torch.dtype, Tensor] = {}
+
+    def take(self, shape, dtype: torch.dtype) -> Tensor:
+        """A contiguous view of `shape` and `dtype` at the next aligned offset."""
+        item = _ITEMSIZE[dtype]
+        typed = self._typed.get(dtype)
+        if typed is None:
+            typed = self._typed[dtype] = self.buf.view(dtype) if self.buf.numel() % item == 0 else self.buf[: self.buf.numel() // item * item].view(dtype)
+        shape = tuple(int(s) for s in shape)
+        n, strides = 1, []
+        for d in reversed(shape):
+            strides.append(n)
+            n *= d
+        view = typed.as_strided(shape, tuple(reversed(strides)), self.off // item)
+        self.off += _up(n * item)
+        return view
+
+
+_ITEMSIZE = {torch.bfloat16: 2, torch.float16: 2, torch.float32: 4, torch.float64: 8, torch.int8: 1, torch.uint8: 1,
+             torch.bool: 1, torch.int16: 2, torch.int32: 4, torch.int64: 8, torch.float8_e4m3fn: 1}
+
+
+def _table(ins: List[Tensor], outs: List[Tensor], scales: List[Tensor], shapes: List[Tuple[int, int]]):
+    """ctb_tensor_ref[n] as a numpy array (five int64 per entry: in, out, scale, rows, cols)."""
+    n = len(ins)
+    t = np.empty((n, 5), dtype=np.int64)
+    t[:, 0] = [x.data_ptr() for x in ins]
+    t[:, 1] = [x.data_ptr() for x in outs]
+    t[:, 2] = [x.data_ptr() for x in scales]
+    t[:, 3:5] = shapes
+    return t
+
+
+def _table_ptr(t: np.ndarray):
+    return ctypes.cast(t.ctypes.data, ctypes.POINTER(L.TensorRef))
+
+
+class CodecEngine:
+    """Runs lists of jobs.  One engine per ModelCompressor; streams are created per device on first use."""
+
+    def __init__(self, rotation_precision=torch.float64):
+        self.rotation_precision = rotation_precision
+        self._streams: Dict[Tuple[int, str], Tuple[torch.cuda.Stream, ...]] = {}
+        self._status: Dict[int, Tensor] = {}
+        self._status_reads: List[Tuple[torch.cuda.Event, Tensor, int]] = []  # (copy done, host copy of the word, device)
+        # host storage -> event after which its bytes are valid (results still on their way while `deferred`)
+        self._host_ready: Dict[int, torch.cuda.Event] = {}
+        self._tail: List[torch.cuda.Event] = []
+        self.deferred = False
+        self.launches = 0
+        # measurement hook: with record_kernel_times set, every whole-shard launch is bracketed by two CUDA events
+        # on its stream and (kind, start, end) is appended to kernel_times
+        self.record_kernel_times = False
+        self.kernel_times: List[Tuple[str, torch.cuda.Event, torch.cuda.Event]] = []
+
+    # ------------------------------------------------------------------ plumbing
+    def _get_streams(self, dev: torch.device, role: str):
+        key = (dev.index, role)
+        if key not in self._streams:
+            self._streams[key] = tuple(torch.cuda.Stream(dev) for _ in range(3))
+        return self._streams[key]
+
+    def _status_word(self, dev: torch.device) -> Tensor:
+        if dev.index not in self._status:
+            self._status[dev.index] = torch.zeros(1, dtype=torch.int32, device=dev)
+        return self._status[dev.index]
+
+    @contextlib.contextmanager
+    def _timed(self, kind: str, dev: torch.device):
+        if not self.record_kernel_times:
+            yield
+            return
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(torch.cuda.current_stream(dev))
+        yield
+        b.record(torch.cuda.current_stream(dev))
+        self.kernel_times.append((kind, a, b))
+
+    def _watch_status(self, dev: torch.device) -> None:
+        """After a launch that may report a time-out: bring the status word to the host behind it, without a sync."""
+        host = torch.empty(1, dtype=torch.int32, pin_memory=True)
+        host.copy_(self._status_word(dev), non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(dev))
+        self._status_reads.append((ev, host, dev.index))
+
+    def _check_status(self, wait: bool) -> None:
+        """Raise for a time-out that a finished launch reported (all launches when `wait`)."""
+        left = []
+        for ev, host, idx in self._status_reads:
+            if wait:
+                ev.synchronize()
+            elif not ev.query():
+                left.append((ev, host, idx))
+                continue
+            if int(host[0]) != 0:
+                self._status[idx].zero_()
+                self._status_reads = []
+                raise TimeoutError(f"a bounded wait inside the tensor-core rotation kernel gave up on cuda:{idx}; "
+                                   "the outputs of that compress pass are incomplete")
+        self._status_reads = left
+
+    def finish(self) -> None:
+        """Wait for everything this engine has put in flight, and turn a device-side time-out into an exception."""
+        for ev in self._tail:
+            ev.synchronize()
+        self._tail.clear()
+        self._host_ready.clear()
+        self._check_status(wait=True)
+
+    # ------------------------------------------------------------------ compress
+    def classify_compress(self, job: Job) -> None:
+        job.kind = "generic"
+        w = job.state.get("weight")
+        if w is None or job.compressor is None or job.scheme is None or job.scheme.weights is None or w.ndim != 2:
+            return
+        args = job.scheme.weights
+        fmt = getattr(job.compressor, "_format_name", None)
+        rows, cols = w.shape
+        if fmt != CompressionFormat.pack_quantized.value or not is_w4a16_g128(args) or w.dtype != torch.bfloat16 or cols % 128:
+            return
+        if job.sparse and "weight" in job.compressor.compression_param_names:
+            return
+        if job.transforms:
+            if len(job.transforms) == 1 and _fusable_rotation(job.transforms[0]):
+                if self.rotation_precision != ops.ROT_TENSOR or (rows * cols) % (128 * 128) == 0:
+                    job.kind = "rotq4"
+            return
+        s = job.state.get("weight_scale")
+        if (s is not None and s.dtype == torch.bfloat16 and tuple(s.shape) == (rows, cols // 128)
+                and job.state.get("weight_g_idx") is None):
+            job.kind = "q4"
+
+    def _compress_on_device(self, jobs: List[Job], dev: torch.device) -> None:
+        """All jobs hold device tensors of `dev`; the current stream is the one to launch on.  Fills job.out
+        with device tensors."""
+        rot = [j for j in jobs if j.kind == "rotq4"]
+        given = [j for j in jobs if j.kind == "q4"]
+        for group, fused in ((rot, True), (given, False)):
+            if not group:
+                continue
+            shapes = [tuple(j.state["weight"].shape) for j in group]
+            words = _Arena(sum(_up(r * c // 2) for r, c in shapes), dev)
+            packed = [words.take((r, c // 8), torch.int32) for r, c in shapes]
+            if fused:
+                sarena = _Arena(sum(_up(r * c // 64) for r, c in shapes), dev)
+                scales = [sarena.take((r, c // 128), torch.bfloat16) for r, c in shapes]
+            else:
+                scales = [j.state["weight_scale"].contiguous() for j in group]
+            ins = [j.state["weight"].contiguous() for j in group]
+            table = _table(ins, packed, scales, shapes)
+            stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+            if fused:
+                # groups of jobs that share one sign vector (one transform weight per size: normally a single group)
+                by_signs: Dict[int, List[int]] = {}
+                for i, j in enumerate(group):
+                    by_signs.setdefault(id(j.transforms[0].weight), []).append(i)
+                for idxs in by_signs.values():
+                    signs = group[idxs[0]].transforms[0]._signs.to(dev)
+                    sub = np.ascontiguousarray(table[idxs])
+                    with self._timed("compress", dev):
+                        L.check(L.lib().ctb_rotate_quantize_int4_batch(_table_ptr(sub), L.i32(len(idxs)), L.ptr(signs),
+                                                                       L.i32(ops._precision_code(self.rotation_precision)),
+                                                                       L.ptr(self._status_word(dev)), stream))
+                    self.launches += 1
+                if self.rotation_precision == ops.ROT_TENSOR:
+                    self._watch_status(dev)
+            else:
+                with self._timed("compress", dev):
+                    L.check(L.lib().ctb_quantize_pack_int4_batch(_table_ptr(table), L.i32(len(group)), stream))
+                self.launches += 1
+            shape_rows = torch.tensor(shapes).unbind(0)  # int64 [2] each, as torch.tensor(weight.shape)
+            for j, p, s, shp, srow in zip(group, packed, scales, shapes, shape_rows):
+                j.out = {"weight_shape": srow, "weight_packed": p}
+                if fused:
+                    j.qparams = {"weight_scale": s}
+                j.shape, j.quantized = shp, True
+        for j in jobs:
+            if j.kind == "generic":
+                self._compress_generic(j)
+
+    def _compress_generic(self, j: Job) -> None:
+        """The per-tensor walk on device tensors: fuse pending transforms, calibrate where a rotation invalidated
+        the scales, then the registered compressor (quantized_compressors/base.py:91-134)."""
+        st = dict(j.state)
+        w = st.get("weight")
+        if w is not None and j.transforms:
+            for tr in j.transforms:
+                w = tr(w)
+            st["weight"] = w
+            if j.scheme is not None and j.scheme.weights is not None:
+                st.update(minmax_qparams(w, j.scheme.weights))
+        if w is not None and j.transforms:
+            j.qparams = {k: st[k] for k in _QPARAMS if k in st and st[k] is not j.state.get(k)}
+        if w is not None and j.compressor is not None and j.scheme is not None and j.scheme.weights is not None \
+                and st.get("weight_scale") is not None:
+            j.out = dict(j.compressor.compress_weight(weight=w, scale=st["weight_scale"], zero_point=st.get("weight_zero_point"),
+                                                      global_scale=st.get("weight_global_scale"), g_idx=st.get("weight_g_idx"),
+                                                      quantization_args=j.scheme.weights, device=None))
+            j.shape, j.quantized = tuple(w.shape), True
+        elif w is not None and j.transforms:
+            j.out = {"weight": w}
+
+    # ------------------------------------------------------------------ decompress
+    def classify_decompress(self, job: Job) -> None:
+        job.kind = "generic"
+        if job.compressor is None or job.scheme is None or job.sparse:
+            return
+        fmt = getattr(job.compressor, "_format_name", None)
+        p, s = job.state.get("weight_packed"), job.state.get("weight_scale")
+        if (fmt != CompressionFormat.pack_quantized.value or not is_w4a16_g128(job.scheme.weights) or p is None or s is None
+                or p.dtype != torch.int32 or s.dtype != torch.bfloat16 or p.ndim != 2 or s.ndim != 2):
+            return
+        if job.state.get("weight_g_idx") is not None or job.state.get("weight_zero_point") is not None:
+            return
+        rows, cols = p.shape[0], s.shape[1] * 128
+        if p.shape[1] * 8 != cols or s.shape[0] != rows:
+            return
+        job.kind, job.shape = "dq4", (rows, cols)
+
+    def _decompress_on_device(self, jobs: List[Job], dev: torch.device, sparsity_compressor=None) -> None:
+        group = [j for j in jobs if j.kind == "dq4"]
+        if group:
+            shapes = [j.shape for j in group]
+            dense = _Arena(sum(_up(r * c * 2) for r, c in shapes), dev)
+            outs = [dense.take((r, c), torch.bfloat16) for r, c in shapes]
+            table = _table([j.state["weight_packed"].contiguous() for j in group], outs,
+                           [j.state["weight_scale"].contiguous() for j in group], shapes)
+            stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+            with self._timed("decompress", dev):
+                L.check(L.lib().ctb_unpack_dequantize_int4_batch(_table_ptr(table), L.i32(len(group)), stream))
+            self.launches += 1
+            for j, o in zip(group, outs):
+                j.out = {"weight": o}
+        for j in jobs:
+            if j.kind != "generic":
+                continue
+            st = dict(j.state)
+            if j.sparse and sparsity_compressor is not None:
+                names = sparsity_compressor.compression_param_names
+                data = {k: v for k, v in st.items() if k in names}
+                if data:
+                    st = {k: v for k, v in st.items() if k not in names}
+                    st["weight"] = sparsity_compressor.decompress_weight(data)
+            out = {}
+            if j.compressor is not None and j.scheme is not None and "weight_scale" in st and j.scheme.weights is not None:
+                out["weight"] = j.compressor.decompress_weight(compressed_data=st, quantization_args=j.scheme.weights)
+            elif "weight" in st and st["weight"] is not j.state.get("weight"):
+                out["weight"] = st["weight"]
+            j.out = out
+
+    # ------------------------------------------------------------------ drivers
+    def run(self, jobs: List[Job], direction: str, deliver: Optional[str] = None, sparsity_compressor=None,
+            sparse_compress: Optional[Callable[[Job], None]] = None) -> None:
+        """Process `jobs` ("compress" or "decompress").  Results (job.out) are left on the device of the job's
+        weight, or in page-locked host memory for host-resident jobs and when `deliver` is "cpu"."""
+        work = self._compress_on_device if direction == "compress" else (
+            lambda js, d: self._decompress_on_device(js, d, sparsity_compressor))
+        self._check_status(wait=False)  # a time-out reported by an earlier, purely device-side call surfaces here
+        host_side = False
+        by_dev: Dict[Optional[int], List[Job]] = {}
+        for j in jobs:
+            t = _anchor(j)
+            by_dev.setdefault(t.device.index if (t is not None and t.is_cuda) else None, []).append(j)
+        for idx, js in by_dev.items():
+            if idx is None:
+                self._run_host(js, work, direction, sparse_compress)
+                host_side = True
+            else:
+                dev = torch.device("cuda", idx)
+                with torch.cuda.device(dev):
+                    work(js, dev)
+                    if sparse_compress is not None:
+                        for j in js:
+                            sparse_compress(j)
+                    if deliver == "cpu":
+                        self._deliver_host(js, dev)
+                        host_side = True
+        # Device-resident work is ordered on the caller's stream like any torch op and needs no host wait; results
+        # that land in host memory are waited for here unless the caller deferred that (`deferred`).
+        if host_side and not self.deferred:
+            self.finish()
+
+    def _deliver_host(self, jobs: List[Job], dev: torch.device) -> None:
+        cur = torch.cuda.current_stream(dev)
+        total = sum(_up(_nbytes(v)) for j in jobs for _, _, v in j.results() if v.is_cuda)
+        host = _Arena(total, pinned=True)
+        for j in jobs:
+            for d, k, v in j.results():
+                if v.is_cuda:
+                    h = host.take(v.shape, v.dtype)
+                    h.copy_(v.contiguous(), non_blocking=True)
+                    d[k] = h
+        ev = torch.cuda.Event()
+        ev.record(cur)
+        self._tail.append(ev)
+
+    def _run_host(self, jobs: List[Job], work, direction: str, sparse_compress) -> None:
+        """Host-resident jobs: steps of about STEP_BYTES streamed over three streams of the current device."""
+        if not torch.cuda.is_available():
+            raise RuntimeError("compressed_tensors_b200 needs a CUDA device (no CPU fallback)")
+        dev = torch.device("cuda", torch.cuda.current_device())
+        s_in, s_k, s_out = self._get_streams(dev, direction)
+        steps: List[List[Job]] = [[]]
+        acc = 0
+        for j in jobs:
+            nb = sum(_nbytes(v) for v in self._inputs_of(j, direction).values())
+            if steps[-1] and acc + nb > STEP_BYTES:
+                steps.append([])
+                acc = 0
+            steps[-1].append(j)
+            acc += nb
+        done: List[torch.cuda.Event] = []
+        for k, step in enumerate(steps):
+            if k >= MAX_INFLIGHT:
+                done[k - MAX_INFLIGHT].synchronize()  # bounds the device memory in flight
+            ev_in, ev_k, ev_out = torch.cuda.Event(), torch.cuda.Event(), torch.cuda.Event()
+            originals = []
+            with torch.cuda.stream(s_in):
+                feeds = [self._inputs_of(j, direction) for j in step]
+                arena = _Arena(sum(_up(_nbytes(v)) for f in feeds for v in f.values()), dev)
+                for j, f in zip(step, feeds):
+                    originals.append(j.state)
+                    st = dict(j.state)
+                    for name, h in f.items():
+                        ready = self._host_ready.get(h.untyped_storage().data_ptr())
+                        if ready is not None:
+                            s_in.wait_event(ready)  # bytes a deferred earlier pass is still delivering
+                        d = arena.take(h.shape, h.dtype)
+                        d.copy_(h, non_blocking=True)
+                        st[name] = d
+                    j.state = st
+                ev_in.record(s_in)
+            arena.buf.record_stream(s_k)
+            with torch.cuda.stream(s_k):
+                s_k.wait_event(ev_in)
+                work(step, dev)
+                if sparse_compress is not None:
+                    for j in step:
+                        sparse_compress(j)
+                ev_k.record(s_k)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_k)
+                outs = [(d, name, v) for j in step for d, name, v in j.results() if v.is_cuda]  # small host tensors (shapes) stay
+                host = _Arena(sum(_up(_nbytes(v)) for _, _, v in outs), pinned=True)
+                for d, name, v in outs:
+                    v = v.contiguous()
+                    v.record_stream(s_out)
+                    h = host.take(v.shape, v.dtype)
+                    h.copy_(v, non_blocking=True)
+                    d[name] = h
+                ev_out.record(s_out)
+                if outs:
+                    self._host_ready[host.buf.untyped_storage().data_ptr()] = ev_out
+            for j, orig in zip(step, originals):
+                j.state = orig
+            done.append(ev_out)
+            self._tail.append(ev_out)
+
+    @staticmethod
+    def _inputs_of(j: Job, direction: str) -> Dict[str, Tensor]:
+        """The host tensors a job needs on the device."""
+        if direction == "compress":
+            names = ("weight",) + _QPARAMS
+        else:
+            names = ("weight_packed", "weight_scale", "weight_zero_point", "weight_g_idx", "weight_global_scale", "weight_shape",
+                     "weight", "compressed", "bitmask", "row_offsets", "shape", "meta", "scale_packed")
+        out = {}
+        for n in names:
+            t = j.state.get(n)
+            if t is not None and not t.is_cuda and t.device.type == "cpu":
+                if direction == "decompress" and n in ("weight_shape", "shape"):
+                    continue  # read on the host
+                out[n] = t
+        return out
+
+
+def _anchor(j: Job) -> Optional[Tensor]:
+    for n in ("weight", "weight_packed", "compressed", "bitmask"):
+        t = j.state.get(n)
+        if t is not None:
+            return t
+    for t in j.state.values():
+        return t
+    return None
+
+
+def _fusable_rotation(tr) -> bool:
+    """A block-128, forward, unpermuted weight_input Hadamard rotation of a Linear weight: what the fused
+    rotate + calibrate + quantize + pack kernels implement."""
+    from ...transform.transform_args import TransformLocation
+
+    try:
+        return (TransformLocation(tr.args.location) == TransformLocation.WEIGHT_INPUT and not tr.args.inverse
+                and tr.perm is None and tr.module_type == torch.nn.Linear and tr.weight.size(0) == 128)
+    except AttributeError:
+        return False

@@ -1,19 +1,37 @@
-"""Whole-model compress / decompress (compressors/model_compressors/model_compressor.py:87-920 of the
-reference, the in-memory paths).  Same order of operations -- quantization compressor first, sparsity
-compressor second on compress, the reverse on decompress -- and the same state-dict key contract; the
-per-tensor work runs on the GPU that holds the module's weight.  Disk I/O (safetensors, config.json)
-stays with the caller."""
-from typing import Dict, List, Optional, Union
+"""Whole-model compress / decompress with the reference's interface
+(compressors/model_compressors/model_compressor.py:87-920): `compress`, `compress_model`, `decompress_model`,
+`decompress(model_path, model)`.  Same order of operations -- quantization compressor first, sparsity
+compressor second on compress, the reverse on decompress -- and the same state-dict key contract.
+
+Where the reference walks the modules one tensor at a time on the CPU, these methods hand the whole list to
+`CodecEngine`: weights that share a scheme with a whole-shard kernel go through one launch, host-resident
+models are streamed through the GPU in a three-stream copy pipeline, and nothing synchronises per tensor.
+
+Two additions, both off unless asked for:
+  * a `transform_config` that has NOT been applied to the model yet (no `model.transform_config`) is fused
+    into the compress pass: weights are rotated, calibrated (min-max, as a rotation invalidates earlier
+    scales), quantized and packed in one kernel; the result equals apply_transform_config + min-max
+    calibration + compress done one after the other;
+  * `with compressor.pipelined():` lets consecutive calls overlap on the GPU (host results become valid
+    when the block exits).
+"""
+import contextlib
+from typing import Dict, List, Optional, Set, Tuple
 
 import torch
-from torch.nn import Module
+from torch.nn import Module, Parameter
 
+from ... import ops
 from ...config import CompressionFormat, SparsityCompressionConfig
-from ...quantization.quant_config import QuantizationConfig, QuantizationStatus, match_named_modules
+from ...quantization.quant_config import QuantizationConfig, QuantizationStatus, apply_quantization_config, match_named_modules
 from ...quantization.quant_scheme import QuantizationScheme
+from ...utils.helpers import merge_names
 from ..base import BaseCompressor
+from .engine import CodecEngine, Job
 
 __all__ = ["ModelCompressor", "map_module_to_scheme"]
+
+_PRECISIONS = {"exact": torch.float64, "float64": torch.float64, "float32": torch.float32, "tensor": ops.ROT_TENSOR}
 
 
 def map_module_to_scheme(model: Module) -> Dict[str, QuantizationScheme]:
@@ -29,10 +47,15 @@ def map_module_to_scheme(model: Module) -> Dict[str, QuantizationScheme]:
 class ModelCompressor:
     def __init__(self, sparsity_config: Optional[SparsityCompressionConfig] = None,
                  quantization_config: Optional[QuantizationConfig] = None, transform_config=None,
-                 compression_formats: Optional[List[str]] = None):
+                 compression_formats: Optional[List[str]] = None, rotation_precision: str = "exact",
+                 transform_seed: Optional[int] = None):
+        """`rotation_precision` selects the arithmetic of a fused Hadamard rotation: "exact" (float64, the
+        reference's offline precision, bit-identical results), "float32", or "tensor" (tcgen05 tensor cores with
+        fp32 accumulators, inside the 1e-3 relative tolerance)."""
         self.sparsity_config = sparsity_config
         self.quantization_config = quantization_config
         self.transform_config = transform_config
+        self.transform_seed = transform_seed
         self.compression_formats = compression_formats
         self.sparsity_compressor = None
         self.quantization_compressor: Optional[Dict[str, BaseCompressor]] = None
@@ -42,9 +65,13 @@ class ModelCompressor:
             if not self.compression_formats:
                 fmt = quantization_config.format
                 self.compression_formats = list(fmt) if isinstance(fmt, (list, tuple)) else [fmt]
-            self.quantization_compressor = {
-                f: BaseCompressor.load_from_registry(f, config=quantization_config) for f in self.compression_formats
-            }
+            self.quantization_compressor = {}
+            for f in self.compression_formats:
+                comp = BaseCompressor.load_from_registry(f, config=quantization_config)
+                comp._format_name = f
+                self.quantization_compressor[f] = comp
+        self.engine = CodecEngine(_PRECISIONS[rotation_precision])
+        self._transforms: Dict[tuple, object] = {}  # transform objects of `transform_config`, made once
 
     # ------------------------------------------------------------------ helpers
     def _format_for(self, scheme: QuantizationScheme) -> str:
@@ -59,83 +86,332 @@ class ModelCompressor:
             return []
         return [n for n, _ in match_named_modules(model, self.sparsity_config.targets or [], self.sparsity_config.ignore or [])]
 
-    # ------------------------------------------------------------------ state-dict path
-    def compress(self, model: Module, state_dict: Optional[Dict[str, torch.Tensor]] = None, show_progress: bool = False
-                 ) -> Dict[str, torch.Tensor]:
-        """model_compressor.py:621-674: returns the compressed state dict (tensors on the CPU, as the
-        reference leaves them); the model itself is not modified."""
-        if state_dict is None:
-            state_dict = model.state_dict()
-        if self.quantization_compressor is not None:
-            module_to_scheme = map_module_to_scheme(model)
-            by_format: Dict[str, Dict[str, torch.Tensor]] = {}
-            rest: Dict[str, torch.Tensor] = {}
-            for key, value in state_dict.items():
-                module_name = key.rsplit(".", 1)[0] if "." in key else ""
-                if module_name in module_to_scheme:
-                    by_format.setdefault(self._format_for(module_to_scheme[module_name]), {})[key] = value
-                else:
-                    rest[key] = value
-            merged: Dict[str, torch.Tensor] = {}
-            for fmt, part in by_format.items():
-                merged.update(self.quantization_compressor[fmt].compress(part, names_to_scheme=module_to_scheme,
-                                                                         show_progress=show_progress, compression_device="cpu"))
-            merged.update({k: v.to("cpu") for k, v in rest.items()})
-            # keep the original key order where a key survived
-            state_dict = {**{k: merged[k] for k in state_dict if k in merged}, **{k: v for k, v in merged.items() if k not in state_dict}}
-        if self.sparsity_compressor is not None:
-            targets = set(self._sparse_targets(model))
-            state_dict = self.sparsity_compressor.compress(state_dict, compression_targets=targets, show_progress=show_progress)
-        return state_dict
+    @contextlib.contextmanager
+    def pipelined(self):
+        """Inside the block, compress / decompress calls only enqueue their work: a later call may start on the
+        results of an earlier one while that one is still running (copies in both directions and kernels of
+        different calls overlap).  Host tensors produced inside the block hold valid bytes once it exits."""
+        self.engine.deferred = True
+        try:
+            yield self
+        finally:
+            self.engine.deferred = False
+            self.engine.finish()
+
+    def _pending_transforms(self, model: Module, named=None) -> Dict[int, list]:
+        """{id(module): [transform, ...]} for the weight-side transforms of `transform_config` when the config has
+        not been applied to the model yet (transform/apply.py:26 marks an applied model with `transform_config`)."""
+        if self.transform_config is None or getattr(model, "transform_config", None) is not None:
+            return {}
+        from ...transform.factory.base import TransformFactory
+        from ...transform.transform_args import TransformLocation
+
+        from ...transform.utils.matrix import get_transform_size
+
+        out: Dict[int, list] = {}
+        for name, scheme in self.transform_config.config_groups.items():
+            factory = None
+            shared = self._transforms  # modules of one size and type share the transform object, across calls too
+            for k, args in enumerate(scheme.apply):
+                if TransformLocation(args.location).is_online():
+                    continue
+                for _, module in match_named_modules(named if named is not None else model, args.targets, args.ignore):
+                    key = (name, k, type(module), get_transform_size(module, args.location, scheme.head_dim))
+                    if key not in shared:
+                        if factory is None:  # one factory per scheme: its generator gives every size its own draw, in order
+                            factory = TransformFactory.from_scheme(scheme, name=name, seed=self.transform_seed)
+                        shared[key] = factory.create_transform(module, args)
+                    out.setdefault(id(module), []).append(shared[key])
+        return out
+
+    def _state_after_compress(self, job: Job, state: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+        """The module's local state after both compressors.  Quantization (quantized_compressors/base.py:91-134): the
+        weight replaced by what compress_weight returned, zero points of symmetric or packed schemes dropped, every
+        other parameter kept.  Sparsity (sparse_compressors/base.py:66-107): `weight` replaced by the compressor's
+        parameters."""
+        base = {**state, **job.qparams}
+        compressed = job.quantized
+        out: Dict[str, torch.Tensor] = {}
+        for name, value in base.items():
+            if name == "weight" and compressed:
+                out.update(job.out)
+            elif name == "weight" and "weight" in job.out:  # rotated, no scheme to compress with
+                out["weight"] = job.out["weight"]
+            elif (compressed and name.endswith("zero_point") and name not in job.out
+                  and job.compressor._skip_zp(merge_names(job.prefix, name), {job.prefix: job.scheme})):
+                continue
+            elif name not in out:
+                out[name] = value
+        if job.sparse_out:
+            out.pop("weight", None)
+            out.update(job.sparse_out)
+        return out
+
+    def _sparse_compress_job(self, job: Job) -> None:
+        """Sparsity second (model_compressor.py:512-519): compress the module's `weight`, dense or already quantized to
+        one element per weight, on the device it is on."""
+        if not job.sparse or self.sparsity_compressor is None:
+            return
+        if job.quantized and "weight" not in job.out:
+            return  # the quantization compressor replaced `weight` by packed words: nothing left for this compressor
+        w = job.out.get("weight", job.state.get("weight"))
+        if w is None:
+            return
+        fmt = self.sparsity_config.format
+        if fmt == CompressionFormat.sparse_24_bitmask.value and w.is_cuda:
+            values, bitmask = ops.sparse24_compress(w)
+            new = {"shape": torch.tensor(list(w.shape)).reshape(-1, 1), "compressed": values, "bitmask": bitmask}
+        elif fmt == CompressionFormat.sparse_bitmask.value and w.is_cuda:
+            values, bitmask, row_offsets = ops.bitmask_compress(w if w.ndim == 2 else w.reshape(-1, w.shape[-1]))
+            new = {"shape": torch.tensor(list(w.shape)), "compressed": values, "bitmask": bitmask, "row_offsets": row_offsets}
+        else:
+            data = self.sparsity_compressor.compress_weight(job.prefix, w)
+            new = {k.removeprefix(job.prefix + "."): v for k, v in data.items()}
+        job.out.pop("weight", None)
+        job.sparse_out = new
+
+    def _survey(self, model: Module, with_transforms: bool):
+        """One walk over the model: (named modules, {name: scheme}, sparsity targets, pending transforms)."""
+        named = list(model.named_modules())
+        schemes: Dict[str, QuantizationScheme] = {}
+        for name, module in named:
+            scheme = module.__dict__.get("quantization_scheme")
+            if scheme is not None and (scheme.weights is not None or scheme.input_activations is not None):
+                schemes[name] = scheme
+        sparse: Set[str] = set()
+        if self.sparsity_config is not None:
+            sparse = {n for n, _ in match_named_modules(named, self.sparsity_config.targets or [], self.sparsity_config.ignore or [])}
+        transforms = self._pending_transforms(model, named) if with_transforms else {}
+        return named, schemes, sparse, transforms
+
+    def _jobs(self, named, schemes, sparse: Set[str], transforms=None) -> Tuple[List[Job], List[Module]]:
+        jobs, owners = [], []
+        transforms = transforms or {}
+        formats: Dict[int, object] = {}
+        for prefix, module in named:
+            scheme = schemes.get(prefix)
+            if scheme is None and prefix not in sparse:
+                continue
+            comp = None
+            if scheme is not None and self.quantization_compressor is not None:
+                comp = formats.get(id(scheme))
+                if comp is None:
+                    comp = formats[id(scheme)] = self.quantization_compressor[self._format_for(scheme)]
+            jobs.append(Job(prefix, {k: v.data for k, v in module._parameters.items() if v is not None}, scheme, comp,
+                            prefix in sparse, transforms.get(id(module), ())))
+            owners.append(module)
+        return jobs, owners
+
+    @staticmethod
+    def _install(module: Module, state: Dict[str, torch.Tensor], device: torch.device, status) -> None:
+        """Replace the module's parameters by `state` (model_compressor.py:521-531) and set its status."""
+        params = module._parameters
+        params.clear()
+        make = torch.Tensor._make_subclass
+        for name, value in state.items():
+            if value.device != device and device.type != "meta":
+                value = value.to(device)
+            params[name] = make(Parameter, value, False)
+        module.__dict__["quantization_status"] = status
 
     # ------------------------------------------------------------------ in-place paths
     @torch.no_grad()
     def compress_model(self, model: Module) -> None:
-        """model_compressor.py:453-539: replace each targeted module's parameters by their compressed form."""
-        module_to_scheme = map_module_to_scheme(model)
-        sparse_targets = self._sparse_targets(model)
-        names = list(dict.fromkeys([*sparse_targets, *module_to_scheme.keys()]))
-        modules = dict(model.named_modules())
-        for prefix in names:
-            module = modules[prefix]
-            device = next(module.parameters(recurse=False)).device
-            state = {f"{prefix}.{n}": p.data for n, p in module.named_parameters(recurse=False)}
-            if prefix in module_to_scheme and self.quantization_compressor is not None:
-                comp = self.quantization_compressor[self._format_for(module_to_scheme[prefix])]
-                state = comp.compress(state, names_to_scheme=module_to_scheme, show_progress=False, compression_device=device)
-            if prefix in sparse_targets:
-                state = self.sparsity_compressor.compress(state, compression_targets=set(sparse_targets), show_progress=False)
-            for n, _ in list(module.named_parameters(recurse=False)):
-                delattr(module, n)
-            for n, v in state.items():
-                module.register_parameter(n.removeprefix(f"{prefix}."), torch.nn.Parameter(v.to(device), requires_grad=False))
-            module.quantization_status = QuantizationStatus.COMPRESSED
+        """model_compressor.py:453-539: replace each targeted module's parameters by their compressed form, on the
+        device the module is on."""
+        named, schemes, sparse, transforms = self._survey(model, with_transforms=True)
+        jobs, owners = self._jobs(named, schemes, sparse, transforms)
+        for j in jobs:
+            self.engine.classify_compress(j)
+        self.engine.run(jobs, "compress", sparse_compress=self._sparse_compress_job if self.sparsity_compressor else None)
+        _place_small(jobs, owners)
+        for j, module in zip(jobs, owners):
+            self._install(module, self._state_after_compress(j, j.state), _module_device(module), QuantizationStatus.COMPRESSED)
+        if transforms:
+            model.transform_config = self.transform_config
         if self.quantization_config is not None and self.quantization_config.format != CompressionFormat.dense.value:
             self.quantization_config.quantization_status = QuantizationStatus.COMPRESSED
 
     @torch.no_grad()
     def decompress_model(self, model: Module) -> None:
-        """model_compressor.py:541-617: sparsity decompression first, then quantization decompression."""
-        module_to_scheme = map_module_to_scheme(model)
-        sparse_targets = self._sparse_targets(model)
-        names = list(dict.fromkeys([*sparse_targets, *module_to_scheme.keys()]))
+        """model_compressor.py:541-617: sparsity decompression first, then quantization decompression; every other
+        parameter of the module stays."""
+        named, schemes, sparse, _ = self._survey(model, with_transforms=False)
+        jobs, owners = self._jobs(named, schemes, sparse)
+        for j in jobs:
+            self.engine.classify_decompress(j)
+        self.engine.run(jobs, "decompress", sparsity_compressor=self.sparsity_compressor)
+        sparse_names = self.sparsity_compressor.compression_param_names if self.sparsity_compressor is not None else ()
+        for j, module in zip(jobs, owners):
+            state = j.state
+            if j.sparse and any(k in state for k in sparse_names):
+                state = {k: v for k, v in state.items() if k not in sparse_names}  # sparse_compressors/base.py:154-176
+            state.update(j.out)
+            self._install(module, state, _module_device(module), QuantizationStatus.FROZEN)
+
+    # ------------------------------------------------------------------ state-dict path
+    @torch.no_grad()
+    def compress(self, model: Module, state_dict: Optional[Dict[str, torch.Tensor]] = None, show_progress: bool = False
+                 ) -> Dict[str, torch.Tensor]:
+        """model_compressor.py:621-674: returns the compressed state dict with its tensors in host memory, as the
+        reference leaves them; the model itself is not modified."""
+        if state_dict is None:
+            state_dict = model.state_dict()
+        named, module_to_scheme, sparse_targets, transforms = self._survey(model, with_transforms=True)
+        if self.quantization_compressor is None:
+            module_to_scheme = {}
+        modules = dict(named)
+        grouped: Dict[str, Dict[str, torch.Tensor]] = {}
+        for key, value in state_dict.items():
+            prefix, _, local = key.rpartition(".")
+            grouped.setdefault(prefix, {})[local] = value
+        comp = next(iter(self.quantization_compressor.values())) if self.quantization_compressor else None  # :643-644
+        jobs: List[Job] = []
+        for prefix, state in grouped.items():
+            scheme = module_to_scheme.get(prefix)
+            if "weight" not in state or (scheme is None and prefix not in sparse_targets):
+                continue
+            jobs.append(Job(prefix=prefix, state=state, scheme=scheme, compressor=comp if scheme is not None else None,
+                            sparse=prefix in sparse_targets,
+                            transforms=transforms.get(id(modules.get(prefix)), ()) if prefix in modules else ()))
+            self.engine.classify_compress(jobs[-1])
+        self.engine.run(jobs, "compress", deliver="cpu",
+                        sparse_compress=self._sparse_compress_job if self.sparsity_compressor else None)
+        done = {j.prefix: j for j in jobs}
+        out: Dict[str, torch.Tensor] = {}
+        for prefix, state in grouped.items():
+            j = done.get(prefix)
+            if j is None:
+                if comp is not None and prefix in module_to_scheme:  # no weight here, zero points may still be dropped
+                    state = {k: v for k, v in state.items()
+                             if not (k.endswith("zero_point") and comp._skip_zp(merge_names(prefix, k), module_to_scheme))}
+                new = state
+            else:
+                new = self._state_after_compress(j, state)
+            for k, v in new.items():
+                out[merge_names(prefix, k)] = v
+        if self.quantization_config is not None and self.quantization_compressor is not None \
+                and self.quantization_config.format != CompressionFormat.dense.value:
+            self.quantization_config.quantization_status = QuantizationStatus.COMPRESSED
+        self.engine.finish()
+        return {k: (v if not v.is_cuda else _to_host(v)) for k, v in out.items()}
+
+    # ------------------------------------------------------------------ disk path
+    @torch.no_grad()
+    def decompress(self, model_path: str, model: Module) -> None:
+        """model_compressor.py:678-767: overwrite the weights of `model` with the weights decompressed from the
+        safetensors checkpoint at `model_path` (a file or a folder).  Packed tensors are opened straight onto the
+        GPU, decompressed there, and left on the device of the module that receives them."""
+        from ...utils.safetensors_load import get_nested_weight_mappings, get_weight_mappings
+        from safetensors import safe_open
+
+        quant = next(iter(self.quantization_compressor.values())) if self.quantization_compressor else None
+        gpu = torch.device("cuda", torch.cuda.current_device())
         modules = dict(model.named_modules())
-        for prefix in names:
-            module = modules[prefix]
-            device = next(module.parameters(recurse=False)).device
-            state = {f"{prefix}.{n}": p.data for n, p in module.named_parameters(recurse=False)}
-            if prefix in sparse_targets and self.sparsity_compressor is not None:
-                state = dict(self.sparsity_compressor.decompress_from_state_dict(state)) | {
-                    k: v for k, v in state.items() if k.rsplit(".", 1)[-1] not in self.sparsity_compressor.compression_param_names}
-            if prefix in module_to_scheme and self.quantization_compressor is not None:
-                comp = self.quantization_compressor[self._format_for(module_to_scheme[prefix])]
-                state = comp.decompress_module_from_state_dict(prefix, state, scheme=module_to_scheme[prefix])
-            for n, _ in list(module.named_parameters(recurse=False)):
-                delattr(module, n)
-            drop = ("weight_packed", "weight_shape", "compressed", "bitmask", "shape", "row_offsets")
-            for n, v in state.items():
-                short = n.removeprefix(f"{prefix}.")
-                if short in drop:
-                    continue
-                module.register_parameter(short, torch.nn.Parameter(v.to(device), requires_grad=False))
-            module.quantization_status = QuantizationStatus.FROZEN
+        handles: Dict[str, object] = {}
+
+        def read(name: str, file: str) -> torch.Tensor:
+            if file not in handles:
+                handles[file] = safe_open(file, framework="pt", device=str(gpu))
+            return handles[file].get_tensor(name)
+
+        try:
+            sparse_done = False
+            if self.sparsity_compressor is not None and self.sparsity_config.format != CompressionFormat.dense.value:
+                skip = quant.compression_param_names if quant is not None else ()
+                nested, rest = get_nested_weight_mappings(model_path, self.sparsity_compressor.compression_param_names,
+                                                          return_unmatched_params=True)
+                for prefix, files in nested.items():
+                    data = {p: read(merge_names(prefix, p), f) for p, f in files.items()}
+                    _set_param(modules[prefix], "weight", self.sparsity_compressor.decompress_weight(data))
+                for name, file in rest.items():
+                    if any(s in name for s in skip):
+                        continue
+                    prefix, _, local = name.rpartition(".")
+                    if prefix in modules and local in modules[prefix]._parameters:
+                        _set_param(modules[prefix], local, read(name, file))
+                model.sparsity_config = self.sparsity_compressor.config
+                sparse_done = True
+            if quant is not None:
+                apply_quantization_config(model, self.quantization_config)
+                schemes = {n: m.quantization_scheme for n, m in model.named_modules()
+                           if getattr(m, "quantization_scheme", None) is not None}
+                mapping = get_weight_mappings(model_path)
+                # activation scales / zero points and, after a sparse pass or for a dense checkpoint, weight qparams
+                for name, file in mapping.items():
+                    prefix, _, local = name.rpartition(".")
+                    if prefix not in schemes or not local.endswith(("_scale", "_zero_point", "_g_idx")):
+                        continue
+                    if local.startswith("weight") and not sparse_done:
+                        continue
+                    _set_param(modules[prefix], local, read(name, file))
+                jobs: List[Job] = []
+                if sparse_done:
+                    for prefix, scheme in schemes.items():
+                        st = {k: v.data for k, v in modules[prefix]._parameters.items() if v is not None}
+                        if "weight_scale" in st:
+                            jobs.append(Job(prefix=prefix, state={k: (v if v.is_cuda else v.to(gpu)) for k, v in st.items()},
+                                            scheme=scheme, compressor=quant))
+                else:
+                    for prefix, files in get_nested_weight_mappings(model_path, quant.compression_param_names).items():
+                        if prefix in schemes and "weight_scale" in files:
+                            jobs.append(Job(prefix=prefix, state={p: read(merge_names(prefix, p), f) for p, f in files.items()},
+                                            scheme=schemes[prefix], compressor=quant))
+                for j in jobs:
+                    self.engine.classify_decompress(j)
+                self.engine.run(jobs, "decompress")
+                for j in jobs:
+                    module = modules[j.prefix]
+                    for k, v in {**{k: v for k, v in j.state.items() if k.startswith("weight_") and k in module._parameters
+                                    or k in ("weight_scale", "weight_zero_point", "weight_g_idx", "weight_global_scale")},
+                                 **j.out}.items():
+                        if k in ("weight_packed", "weight_shape"):
+                            continue
+                        _set_param(module, k, v)
+                for m in model.modules():
+                    m.quantization_status = QuantizationStatus.FROZEN
+                model.quantization_config = self.quantization_config
+        finally:
+            handles.clear()
+        self.engine.finish()
+
+
+def _module_device(module: Module) -> torch.device:
+    for p in module._parameters.values():
+        if p is not None:
+            return p.device
+    return torch.device("cpu")
+
+
+def _place_small(jobs: List[Job], owners: List[Module]) -> None:
+    """`weight_shape` and `shape` are made on the host; for modules on a GPU they go over in ONE copy per device
+    (the module's parameters then are views of that tensor) instead of one tiny synchronous copy each."""
+    per_dev: Dict[torch.device, list] = {}
+    for j, module in zip(jobs, owners):
+        dev = _module_device(module)
+        if dev.type != "cuda":
+            continue
+        for d, name, v in j.results():
+            if name in ("weight_shape", "shape") and not v.is_cuda:
+                per_dev.setdefault(dev, []).append((d, name, v))
+    for dev, items in per_dev.items():
+        flat = torch.cat([v.reshape(-1) for _, _, v in items]).to(dev)
+        off = 0
+        for d, name, v in items:
+            d[name] = flat[off:off + v.numel()].view(v.shape)
+            off += v.numel()
+
+
+def _set_param(module: Module, name: str, value: torch.Tensor) -> None:
+    """Overwrite (or add) one parameter, keeping the device of the one it replaces."""
+    old = module._parameters.get(name)
+    if old is not None and old.device.type != "meta" and old.device != value.device:
+        value = value.to(old.device)
+    module._parameters[name] = Parameter(value, requires_grad=False)
+
+
+def _to_host(t: torch.Tensor) -> torch.Tensor:
+    out = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
+    out.copy_(t, non_blocking=True)
+    torch.cuda.current_stream(t.device).synchronize()
+    return out

@@ -907,7 +907,8 @@ __global__ void __launch_bounds__(kThreads) absmax_quant_row_kernel(const HArgs 
 
 namespace ctb {
 
-int rotquant_tc_launch(const ctb_tensor_ref *tensors, int32_t count, const int8_t *signs, bool quant, int32_t *status, cudaStream_t st);
+int rotquant_tc_launch(const ctb_tensor_ref *tensors, int32_t count, const int8_t *signs, bool quant, int32_t *status, cudaStream_t st,
+                       long long spin_cycles = 0, int skip_tile = -1);
 
 // launch the batched block-128 kernel over `B` (already filled except for nothing: starts, counts, pointers)
 static int launch_rotquant(const RQBatch &B, const int8_t *signs, int precision, bool quant, cudaStream_t st) {
@@ -1139,6 +1140,13 @@ extern "C" int ctb_absmax_quantize(const ctb_qdesc *d, const void *x, const floa
 }
 
 
+
+extern "C" int ctb_rotate_quantize_int4_batch_bounded(const ctb_tensor_ref *tensors, int32_t count, const int8_t *signs,
+                                                      int32_t *device_status, int64_t spin_cycles, int32_t skip_tile, void *stream) {
+    if (!tensors && count > 0) return fail(CTB_EINVAL_NULL, "null tensor table");
+    if (spin_cycles <= 0) return fail(CTB_EINVAL_SHAPE, "the wait budget must be positive");
+    return rotquant_tc_launch(tensors, count, signs, true, device_status, as_stream(stream), spin_cycles, skip_tile);
+}
 
 extern "C" int ctb_rotate_quantize_int4_batch(const ctb_tensor_ref *tensors, int32_t count, const int8_t *signs, int32_t precision,
                                               int32_t *device_status, void *stream) {

@@ -960,6 +960,100 @@ __global__ void __launch_bounds__(kThreads) dequant_int4_batch_kernel(const __gr
 
 }  // namespace ctb
 
+namespace ctb {
+
+// The mirror of the kernel above for the compress direction when the scales are GIVEN (a calibrated model:
+// compressors/quantized_compressors/base.py:91-122 calling pack_quantized.py:88-145 once per weight): symmetric int4,
+// group 128, bf16 weights and bf16 scales, every tensor of the table in one grid.  Same table type; `in` is the dense
+// weight, `scale` is read, `out` receives the pack_to_int32 words.  The arithmetic is the packed-bf16x2 tier of
+// quant_bf16_lean_kernel (and its float routine for a scale outside [2^-99, 2^99)), so the words equal ctb_quantize's.
+__global__ void __launch_bounds__(kThreads) quant_int4_batch_kernel(const __grid_constant__ DQBatch B) {
+    const int64_t total = B.ustart[B.count];
+    int t = 0;
+    uint4 raw[kUnroll];
+    uint32_t sbits[kUnroll];
+    bool ok[kUnroll];
+    int64_t cbase = 0;
+    auto fetch = [&](int64_t unit) {
+        while (t + 1 < B.count && unit >= B.ustart[t + 1]) ++t;
+        cbase = (unit - B.ustart[t]) * kDQUnit;
+        const uint32_t left = (uint32_t)min((int64_t)kDQUnit, B.nchunks[t] - cbase);
+        const char *ip = (const char *)B.in[t] + cbase * 16;
+        const unsigned short *sp = (const unsigned short *)B.scale[t] + (cbase >> 4);
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const uint32_t c = u * kThreads + threadIdx.x;
+            ok[u] = c < left;
+            if (ok[u]) {
+                raw[u] = ld_stream(ip + (size_t)c * 16);
+                sbits[u] = __ldg(sp + (c >> 4));
+            }
+        }
+    };
+    int64_t unit = blockIdx.x;
+    if (unit < total) fetch(unit);
+    while (unit < total) {
+        uint4 w[kUnroll];
+        uint32_t s[kUnroll];
+        bool k[kUnroll];
+        const int ct = t;
+        const int64_t cb = cbase;
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) { w[u] = raw[u]; s[u] = sbits[u]; k[u] = ok[u]; }
+        const int64_t next = unit + gridDim.x;
+        if (next < total) fetch(next);
+        char *o = (char *)B.out[ct] + cb * 4;
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            if (!k[u]) continue;
+            const uint32_t c = u * kThreads + threadIdx.x;
+            if (((s[u] >> 7) & 0xFFu) - 28u > 197u) {  // scale outside the range the reciprocal form is proved for
+                LeanArgs l{};
+                l.in = (const uint4 *)B.in[ct] + cb; l.scale = (const unsigned short *)B.scale[ct] + (cb >> 4); l.zp = nullptr;
+                l.out = o; l.qmin = -8.0f; l.qmax = 7.0f; l.zdt = CTB_I8;
+                lean_exact_chunk<0, QK_INT, F_PACK4, CTB_BF16>(l, c, c >> 4);
+                continue;
+            }
+            const uint32_t x4[4] = {w[u].x, w[u].y, w[u].z, w[u].w};
+            st_stream4(o + (size_t)c * 4, quant_int4_word_bf16(x4, rcp_approx(__uint_as_float(s[u] << 16)), false, u32_as_bf162(0u)));
+        }
+        unit = next;
+    }
+}
+
+}  // namespace ctb
+
+extern "C" int ctb_quantize_pack_int4_batch(const ctb_tensor_ref *tensors, int32_t count, void *stream) {
+    using namespace ctb;
+    if (!tensors && count > 0) return fail(CTB_EINVAL_NULL, "null tensor table");
+    static thread_local DQBatch B;
+    for (int32_t base = 0; base < count; base += kDQBatchMax) {
+        const int32_t n = count - base < kDQBatchMax ? count - base : kDQBatchMax;
+        int64_t g = 0;
+        for (int32_t i = 0; i < n; ++i) {
+            const ctb_tensor_ref &t = tensors[base + i];
+            if (!t.in || !t.out || !t.scale) return fail(CTB_EINVAL_NULL, "tensor %d has a null buffer", base + i);
+            if (t.rows < 0 || t.cols <= 0 || t.cols % 128) return fail(CTB_EINVAL_SHAPE, "tensor %d: columns %lld are not a multiple of 128", base + i, (long long)t.cols);
+            if (!aligned16(t.in) || (reinterpret_cast<uintptr_t>(t.out) & 3u) || (reinterpret_cast<uintptr_t>(t.scale) & 1u))
+                return fail(CTB_EINVAL_ALIGN, "tensor %d is misaligned", base + i);
+            B.ustart[i] = g;
+            B.nchunks[i] = t.rows * t.cols / 8;
+            B.in[i] = t.in;
+            B.scale[i] = t.scale;
+            B.out[i] = t.out;
+            g += cdiv(B.nchunks[i], kDQUnit);
+        }
+        B.count = n;
+        B.ustart[n] = g;
+        if (g == 0) continue;
+        int grid = grid_for(g, 1, 8);
+        quant_int4_batch_kernel<<<grid, kThreads, 0, as_stream(stream)>>>(B);
+        int rc = after_launch("quant_int4_batch_kernel");
+        if (rc) return rc;
+    }
+    return CTB_OK;
+}
+
 extern "C" int ctb_unpack_dequantize_int4_batch(const ctb_tensor_ref *tensors, int32_t count, void *stream) {
     using namespace ctb;
     if (!tensors && count > 0) return fail(CTB_EINVAL_NULL, "null tensor table");

@@ -21,6 +21,8 @@
 // roles drain and the kernel returns CTB_ETIMEOUT to the host through the status buffer.
 #include <cuda.h>
 
+#include <atomic>
+
 #include "ctb_codec.cuh"
 
 namespace ctb {
@@ -31,7 +33,7 @@ constexpr int kTcBatchMax = 256;
 constexpr uint32_t kTcHalfBytes = 128 * 64 * 2;      // one 128B-swizzled [128 rows x 64 cols] bf16 box
 constexpr uint32_t kTcTileBytes = 2 * kTcHalfBytes;  // 32 KiB: one A tile (or the B matrix)
 constexpr size_t kTcSmemBytes = 1024 /*alignment slack*/ + kTcTileBytes * (1 + kTcStages) + 256;
-constexpr long long kTcSpinCycles = 2000000000LL;    // bound of every wait, in SM clocks
+constexpr long long kTcSpinCycles = 2000000000LL;    // default bound of every wait, in SM clocks
 
 struct TCBatch {
     int count;
@@ -39,6 +41,8 @@ struct TCBatch {
     int64_t row0[kTcBatchMax];            // row of the tensor's first block in the tensor map's [rows, 128] view
     void *out[kTcBatchMax];
     void *scale[kTcBatchMax];
+    long long spin_cycles;                // bound of every device-side wait, in SM clocks
+    int skip_tile;                        // >= 0: the producer leaves this tile's copy out (test hook: makes a wait run out)
 };
 
 // ---------------------------------------------------------------- PTX wrappers
@@ -64,17 +68,22 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 // bounded wait: false when the budget ran out or another role already raised the error word
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *err) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *err, long long budget) {
     if (mbar_try(bar, parity)) return true;
     const long long t0 = clock64();
     while (!mbar_try(bar, parity)) {
         if (*err != 0) return false;
-        if (clock64() - t0 > kTcSpinCycles) {
+        if (clock64() - t0 > budget) {
             *err = 1;
             return false;
         }
     }
     return true;
+}
+// bounded wait that ignores the error word: used on the way out, for work this thread itself put in flight
+__device__ __forceinline__ void mbar_drain(uint32_t bar, uint32_t parity, long long budget) {
+    const long long t0 = clock64();
+    while (!mbar_try(bar, parity) && clock64() - t0 < budget) {}
 }
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int x, int y) {
@@ -188,11 +197,12 @@ rotquant128_tc_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
         // ------------------------------------------------ TMA producer
         if (lane == 0) {
             int t = 0;
-            int64_t it = 0;
+            int64_t it = 0, skipped = -1;
             for (int64_t tile = blockIdx.x; tile < total; tile += gridDim.x, ++it) {
                 const int s = (int)(it % kTcStages);
                 const uint32_t ph = (uint32_t)((it / kTcStages) & 1);
-                if (!mbar_wait(empty_bar(s), ph ^ 1u, err)) break;
+                if (!mbar_wait(empty_bar(s), ph ^ 1u, err, B.spin_cycles)) break;
+                if (tile == (int64_t)B.skip_tile) { skipped = it; continue; }  // nothing is issued, nothing is in flight for this stage
                 while (t + 1 < B.count && tile >= B.tile_start[t + 1]) ++t;
                 const int64_t row = B.row0[t] + (tile - B.tile_start[t]) * 128;
                 mbar_expect_tx(full_bar(s), kTcTileBytes);
@@ -201,10 +211,9 @@ rotquant128_tc_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
             }
             if (*err != 0) {
                 // let the copies still in flight land before the block gives its shared memory back
-                for (int64_t j = it > kTcStages ? it - kTcStages : 0; j < it; ++j) {
-                    const long long t0 = clock64();
-                    while (!mbar_try(full_bar((int)(j % kTcStages)), (uint32_t)((j / kTcStages) & 1)) && clock64() - t0 < kTcSpinCycles) {}
-                }
+                // (default budget: a copy that was issued does land; the short budget of a test must not cut this wait)
+                for (int64_t j = it > kTcStages ? it - kTcStages : 0; j < it; ++j)
+                    if (j != skipped) mbar_drain(full_bar((int)(j % kTcStages)), (uint32_t)((j / kTcStages) & 1), kTcSpinCycles);
             }
         }
     } else if (warp == 1) {
@@ -217,8 +226,8 @@ rotquant128_tc_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
                 const uint32_t ph = (uint32_t)((it / kTcStages) & 1);
                 const int b = (int)(it & 1);
                 const uint32_t bph = (uint32_t)((it >> 1) & 1);
-                if (!mbar_wait(acce_bar(b), bph ^ 1u, err)) break;
-                if (!mbar_wait(full_bar(s), ph, err)) break;
+                if (!mbar_wait(acce_bar(b), bph ^ 1u, err, B.spin_cycles)) break;
+                if (!mbar_wait(full_bar(s), ph, err, B.spin_cycles)) break;
                 tc_fence_after();
 #pragma unroll
                 for (int k = 0; k < 8; ++k) {
@@ -228,6 +237,9 @@ rotquant128_tc_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
                 umma_commit(empty_bar(s));  // the stage may be refilled once these MMAs have read it
                 umma_commit(accf_bar(b));   // ... and the accumulator is complete
             }
+            // On the error path nobody may be left to consume the last accumulator: wait here for the commit of
+            // the MMAs already issued, so that none is in flight when the block frees its TMEM and shared memory.
+            if (*err != 0 && it > 0) mbar_drain(accf_bar((int)((it - 1) & 1)), (uint32_t)(((it - 1) >> 1) & 1), kTcSpinCycles);
         }
     } else {
         // ------------------------------------------------ epilogue: two groups of four warps alternate tiles
@@ -239,7 +251,8 @@ rotquant128_tc_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
             if ((int)(it & 1) != e) continue;
             const int b = e;
             const uint32_t bph = (uint32_t)((it >> 1) & 1);
-            if (!mbar_wait(accf_bar(b), bph, err)) break;
+            // the decision to leave is taken by the whole warp: tcgen05.ld below is a warp-wide (.sync.aligned) instruction
+            if (!__all_sync(0xffffffffu, mbar_wait(accf_bar(b), bph, err, B.spin_cycles))) break;
             tc_fence_after();
             uint32_t acc[128];
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + b * 128;
@@ -319,18 +332,28 @@ static EncodeTiledFn encode_tiled() {
 // Tensor-core path for a table of tensors.  Every tensor must be a whole number of 128-block tiles and
 // sit a multiple of 256 bytes from the lowest one, so that ONE tensor map ([rows, 128] bf16 over the span
 // of the table) addresses them all; only rows that belong to a tensor are ever requested.
-int rotquant_tc_launch(const ctb_tensor_ref *tensors, int32_t count, const int8_t *signs, bool quant, int32_t *status, cudaStream_t st) {
+int rotquant_tc_launch(const ctb_tensor_ref *tensors, int32_t count, const int8_t *signs, bool quant, int32_t *status, cudaStream_t st,
+                       long long spin_cycles, int skip_tile) {
     if (count <= 0) return CTB_OK;
     EncodeTiledFn encode = encode_tiled();
     if (!encode) return fail(CTB_ECUDA, "cuTensorMapEncodeTiled is not available from this driver");
-    static bool attr_set[2] = {false, false};
-    if (!attr_set[quant]) {
-        cudaError_t e = quant ? cudaFuncSetAttribute(rotquant128_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBytes)
-                              : cudaFuncSetAttribute(rotquant128_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBytes);
-        if (e != cudaSuccess) return fail(CTB_ECUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-        attr_set[quant] = true;
+    {
+        // the opt-in to more than 48 KiB of dynamic shared memory is a per-device attribute of the function
+        static std::atomic<bool> attr_set[64][2];
+        int dev = 0;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess) return fail(CTB_ECUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+        const bool cacheable = dev >= 0 && dev < 64;
+        if (!cacheable || !attr_set[dev][quant].load(std::memory_order_acquire)) {
+            e = quant ? cudaFuncSetAttribute(rotquant128_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBytes)
+                      : cudaFuncSetAttribute(rotquant128_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBytes);
+            if (e != cudaSuccess) return fail(CTB_ECUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+            if (cacheable) attr_set[dev][quant].store(true, std::memory_order_release);
+        }
     }
     static thread_local TCBatch B;
+    B.spin_cycles = spin_cycles > 0 ? spin_cycles : kTcSpinCycles;
+    B.skip_tile = skip_tile;
     for (int32_t base_i = 0; base_i < count; base_i += kTcBatchMax) {
         const int32_t n = count - base_i < kTcBatchMax ? count - base_i : kTcBatchMax;
         uintptr_t lo = UINTPTR_MAX, hi = 0;

@@ -1105,14 +1105,18 @@ extern "C" int ctb_bitmask_decompress(const void *values, const uint8_t *bitmask
     return decompress_impl(values, bitmask, dtype, rows, cols, out, workspace, Gate{nullptr, 0}, stream, true);
 }
 
-extern "C" int ctb_sparse24_decompress(const void *values, const uint8_t *bitmask, int32_t dtype, int64_t rows, int64_t cols, void *out,
-                                       void *workspace, void *stream) {
+extern "C" int ctb_sparse24_decompress(const void *values, int64_t nvalues, const uint8_t *bitmask, int32_t dtype, int64_t rows,
+                                       int64_t cols, void *out, void *workspace, void *stream) {
     if (rows != 0 && cols != 0 && (!values || !bitmask || !out || !workspace)) return fail(CTB_EINVAL_NULL, "null buffer");
     ElemInfo e;
     if (!elem_info(dtype, &e)) return fail(CTB_EINVAL_DTYPE, "unsupported dtype for bitmask decompression");
     if (rows <= 0 || cols <= 0) return rows < 0 || cols < 0 ? fail(CTB_EINVAL_SHAPE, "negative shape") : CTB_OK;
-    if (cols % 8 != 0 || !aligned16(out) || (reinterpret_cast<uintptr_t>(values) & 15u))
-        return decompress_impl(values, bitmask, dtype, rows, cols, out, workspace, Gate{nullptr, 0}, stream);
+    if (nvalues < 0) return fail(CTB_EINVAL_SHAPE, "negative value count");
+    // The scan-free kernels read two values for every four columns whatever the bitmask says, so they may run only
+    // over a buffer that holds rows * cols / 2 elements: a shorter one (fewer bits set than two per four) goes to
+    // the generic kernels, which read exactly as many values as the bitmask has bits.
+    if (nvalues < rows * cols / 2 || cols % 8 != 0 || !aligned16(out) || (reinterpret_cast<uintptr_t>(values) & 15u))
+        return decompress_impl(values, bitmask, dtype, rows, cols, out, workspace, Gate{nullptr, 0}, stream, nvalues < rows * cols / 2);
     cudaStream_t st = as_stream(stream);
     int *flag = reinterpret_cast<int *>(static_cast<char *>(workspace) + flag_offset(rows));
     static std::atomic<int> s_ticket{1};
@@ -1144,18 +1148,20 @@ static __device__ __align__(256) int64_t g_row_offsets_static[kStaticMaxRows];
 // a stand-in for the symbol, so the address is asked of the runtime once per device, with that
 // device current, and cached.
 static int static_scratch(int64_t **out) {
-    static int64_t *cached[64] = {nullptr};
+    static std::atomic<int64_t *> cached[64];  // zero-initialised; two host threads may make their first call at once
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return fail(CTB_ECUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
     if (dev < 0 || dev >= 64) return fail(CTB_EUNSUPPORTED, "device index %d is outside the table of cached scratch addresses", dev);
-    if (cached[dev] == nullptr) {
+    int64_t *addr = cached[dev].load(std::memory_order_acquire);
+    if (addr == nullptr) {
         void *p = nullptr;
         e = cudaGetSymbolAddress(&p, g_row_offsets_static);
         if (e != cudaSuccess || p == nullptr) return fail(CTB_ECUDA, "cudaGetSymbolAddress(g_row_offsets_static): %s", cudaGetErrorString(e));
-        cached[dev] = static_cast<int64_t *>(p);
+        addr = static_cast<int64_t *>(p);
+        cached[dev].store(addr, std::memory_order_release);
     }
-    *out = cached[dev];
+    *out = addr;
     return CTB_OK;
 }
 

@@ -342,9 +342,11 @@ def sparse24_decompress(values, bitmask, shape):
     values, bitmask = _c(values.flatten()), _c(bitmask)
     rows, cols = int(shape[0]), int(shape[1])
     out = torch.empty((rows, cols), dtype=values.dtype, device=bitmask.device)
+    if values.numel() == 0:  # an all-zero tensor compresses to no values at all: nothing to read
+        return out.zero_()
     ws = _bitmask_workspace(rows, cols, bitmask.device)
-    check(lib().ctb_sparse24_decompress(ptr(values), ptr(bitmask), i32(DT[values.dtype]), i64(rows), i64(cols), ptr(out), ptr(ws),
-                                        stream_of(bitmask)))
+    check(lib().ctb_sparse24_decompress(ptr(values), i64(values.numel()), ptr(bitmask), i32(DT[values.dtype]), i64(rows), i64(cols),
+                                        ptr(out), ptr(ws), stream_of(bitmask)))
     return out
 
 

@@ -46,11 +46,12 @@ def _matches(name: str, module: torch.nn.Module, target: str) -> bool:
     return name == target or module.__class__.__name__ == target
 
 
-def match_named_modules(model: torch.nn.Module, targets: Iterable[str], ignore: Iterable[str] = ()) -> List[Tuple[str, torch.nn.Module]]:
-    """Modules whose name, class name or `re:` pattern matches a target and no ignore entry (utils/match.py:40)."""
+def match_named_modules(model, targets: Iterable[str], ignore: Iterable[str] = ()) -> List[Tuple[str, torch.nn.Module]]:
+    """Modules whose name, class name or `re:` pattern matches a target and no ignore entry (utils/match.py:40).
+    `model` is a module, or a list of (name, module) pairs from an earlier walk over one."""
     targets, ignore = list(targets or []), list(ignore or [])
     out = []
-    for name, module in model.named_modules():
+    for name, module in (model.named_modules() if isinstance(model, torch.nn.Module) else model):
         if any(_matches(name, module, t) for t in targets) and not any(_matches(name, module, i) for i in ignore):
             out.append((name, module))
     return out

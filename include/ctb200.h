@@ -197,10 +197,12 @@ int ctb_bitmask_decompress(const void *values, const uint8_t *bitmask, int32_t d
                            int64_t cols, void *out, void *workspace, void *stream);
 
 /* sparse_24_bitmask.py:206-224 sparse24_bitmask_decompress.  Same result as ctb_bitmask_decompress for any
- * bitmask; when the bitmask keeps exactly two of every four columns (what the 2:4 compressor writes) a
- * scan-free kernel does the work and the generic kernels return at once.  workspace: ctb_bitmask_workspace_bytes(). */
-int ctb_sparse24_decompress(const void *values, const uint8_t *bitmask, int32_t dtype, int64_t rows,
-                            int64_t cols, void *out, void *workspace, void *stream);
+ * bitmask.  `nvalues` is the number of elements `values` holds.  When it is at least rows * cols / 2 and the bitmask
+ * keeps exactly two of every four columns (what the 2:4 compressor writes) a scan-free kernel does the work and the
+ * generic kernels return at once; a shorter `values` is never read past its end: it takes the generic kernels
+ * directly.  workspace: ctb_bitmask_workspace_bytes(). */
+int ctb_sparse24_decompress(const void *values, int64_t nvalues, const uint8_t *bitmask, int32_t dtype,
+                            int64_t rows, int64_t cols, void *out, void *workspace, void *stream);
 
 /* No counterpart in the reference.  Same result as ctb_bitmask_decompress, for callers that cannot
  * allocate device memory where they decompress (a server whose memory went to a fixed arena at
@@ -281,6 +283,18 @@ typedef struct ctb_tensor_ref {
  * kernel gives up; it is left untouched otherwise. */
 int ctb_rotate_quantize_int4_batch(const ctb_tensor_ref *tensors, int32_t count, const int8_t *signs,
                                    int32_t precision, int32_t *device_status, void *stream);
+/* The CTB_ROT_TENSOR form of the call above with the bound of its device-side waits given by the caller
+ * (spin_cycles, in SM clocks; the default is about a second) and, for skip_tile >= 0, with the copy of that one
+ * tile left out, so that the wait for it runs out: the kernel then drains what it has in flight, frees its
+ * tensor memory, returns, and *device_status reads CTB_ETIMEOUT.  This is how the error path is exercised
+ * without a fault; the outputs of such a call are undefined.  No counterpart in the reference. */
+int ctb_rotate_quantize_int4_batch_bounded(const ctb_tensor_ref *tensors, int32_t count, const int8_t *signs,
+                                           int32_t *device_status, int64_t spin_cycles, int32_t skip_tile,
+                                           void *stream);
+/* ctb_quantize(codec PACK32, num_bits 4, group 128, bf16 scale GIVEN in t.scale, no zero point) for every tensor:
+ * the compress walk of a model that was calibrated beforehand (quantized_compressors/base.py:91-122 calling
+ * pack_quantized.py:88-145 per weight).  t.in = dense bf16 weight, t.out = int32 words, t.scale is read. */
+int ctb_quantize_pack_int4_batch(const ctb_tensor_ref *tensors, int32_t count, void *stream);
 /* ctb_dequantize(codec PACK32, num_bits 4, group 128, bf16 scale, no zero point) for every tensor. */
 int ctb_unpack_dequantize_int4_batch(const ctb_tensor_ref *tensors, int32_t count, void *stream);
 

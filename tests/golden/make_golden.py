@@ -542,11 +542,152 @@ def gen_fp4_pack_all():
     torch.save(out, os.path.join(OUT, "fp4_pack_all.pt"))
 
 
+TOY = dict(layers=2, hidden=128, intermediate=256, kv=128, vocab=64)
+
+
+def toy_llama(seed: int, dtype=torch.bfloat16):
+    """A two-layer module tree with Llama's Linear names and ratios (q/o hidden x hidden, k/v kv x hidden, gate/up
+    intermediate x hidden, down hidden x intermediate, lm_head), seeded N(0, 0.02) weights.  No forward is needed."""
+    from torch import nn
+
+    def lin(o, i):
+        return nn.Linear(i, o, bias=False, dtype=dtype)
+
+    class Attn(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.q_proj, self.k_proj = lin(TOY["hidden"], TOY["hidden"]), lin(TOY["kv"], TOY["hidden"])
+            self.v_proj, self.o_proj = lin(TOY["kv"], TOY["hidden"]), lin(TOY["hidden"], TOY["hidden"])
+
+    class MLP(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.gate_proj, self.up_proj = lin(TOY["intermediate"], TOY["hidden"]), lin(TOY["intermediate"], TOY["hidden"])
+            self.down_proj = lin(TOY["hidden"], TOY["intermediate"])
+
+    class Layer(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.self_attn, self.mlp = Attn(), MLP()
+            self.input_layernorm = nn.LayerNorm(TOY["hidden"], dtype=dtype)
+
+    class Inner(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.layers = nn.ModuleList([Layer() for _ in range(TOY["layers"])])
+
+    class Toy(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.model = Inner()
+            self.lm_head = lin(TOY["vocab"], TOY["hidden"])
+
+    m = Toy()
+    gen = torch.Generator().manual_seed(seed)
+    with torch.no_grad():
+        for name, p in m.named_parameters():
+            if name.endswith("layernorm.weight") or name.endswith("layernorm.bias"):
+                continue
+            p.copy_((torch.randn(p.shape, generator=gen) * 0.02).to(dtype))
+    return m
+
+
+def gen_model_compressor():
+    """ModelCompressor on the toy model, the way a calibrated checkpoint is made: apply_transform_config (random Hadamard,
+    block 128, weight_input) -> apply_quantization_config (W4A16 group 128) -> min-max scales through calculate_qparams ->
+    ModelCompressor.compress / compress_model / decompress_model.  Second case: FP8 per-channel weights (float-quantized)
+    stacked with sparse-24-bitmask on 2:4-pruned weights."""
+    import copy
+
+    from compressed_tensors.compressors import ModelCompressor
+    from compressed_tensors.config import Sparse24BitMaskConfig
+    from compressed_tensors.quantization import QuantizationConfig, QuantizationScheme, apply_quantization_config
+    from compressed_tensors.transform import TransformConfig, apply_transform_config
+    from compressed_tensors.utils import update_parameter_data
+
+    out = {}
+
+    def slim(original, compressed, compressed_inplace, decompressed):
+        """What the tests compare, without storing a tensor twice: the in-place result must equal the state-dict result
+        wherever both have a key (checked here), so only its key table is kept; of the decompressed model, the weights."""
+        for k, v in compressed_inplace.items():
+            if k in compressed:
+                assert v.dtype == compressed[k].dtype and torch.equal(v.view(torch.uint8), compressed[k].view(torch.uint8)), k
+        return {"original": original, "compressed": dict(compressed),
+                "inplace_keys": {k: (str(v.dtype), tuple(v.shape)) for k, v in compressed_inplace.items()},
+                "decompressed_keys": {k: (str(v.dtype), tuple(v.shape)) for k, v in decompressed.items()},
+                "decompressed": {k: v for k, v in decompressed.items() if k.endswith(".weight")}}
+
+    def calibrate(model):
+        for name, mod in model.named_modules():
+            scheme = getattr(mod, "quantization_scheme", None)
+            if scheme is None or scheme.weights is None:
+                continue
+            a, w = scheme.weights, mod.weight.data
+            g = a.group_size if a.strategy == "group" else w.shape[1]
+            mn, mx = group_minmax(w, g)
+            s, z = calculate_qparams(mn, mx, a)
+            update_parameter_data(mod, s.reshape(mod.weight_scale.shape).to(mod.weight_scale.dtype), "weight_scale")
+            if hasattr(mod, "weight_zero_point"):
+                update_parameter_data(mod, z.reshape(mod.weight_zero_point.shape).to(mod.weight_zero_point.dtype), "weight_zero_point")
+
+    # ---- case 1: rotation + W4A16 pack-quantized
+    model = toy_llama(31)
+    original = {k: v.clone() for k, v in model.state_dict().items()}
+    tcfg = TransformConfig(config_groups={"u": TransformScheme(type="random-hadamard", head_dim=128, apply=[
+        TransformArgs(targets=["Linear"], ignore=["lm_head"], location="weight_input")])})
+    apply_transform_config(model, tcfg)
+    rotated = {k: v.clone() for k, v in model.state_dict().items()}
+    qcfg = QuantizationConfig(config_groups={"group_0": QuantizationScheme(
+        targets=["Linear"], weights=QuantizationArgs(num_bits=4, symmetric=True, strategy="group", group_size=128))},
+        ignore=["lm_head"], format="pack-quantized")
+    apply_quantization_config(model, qcfg)
+    calibrate(model)
+    calibrated = {k: v.clone() for k, v in model.state_dict().items()}
+    mc = ModelCompressor(quantization_config=copy.deepcopy(qcfg))
+    compressed = mc.compress(model)
+    inplace = copy.deepcopy(model)
+    mc2 = ModelCompressor(quantization_config=copy.deepcopy(qcfg))
+    mc2.compress_model(inplace)
+    compressed_inplace = {k: v.clone() for k, v in inplace.state_dict().items()}
+    mc2.decompress_model(inplace)
+    decompressed = {k: v.clone() for k, v in inplace.state_dict().items()}
+    out["w4a16_rot"] = slim(original, compressed, compressed_inplace, decompressed)
+    out["w4a16_rot"]["rotated_q_proj"] = rotated["model.layers.0.self_attn.q_proj.weight"]
+
+    # ---- case 2: FP8 per-channel (float-quantized) stacked with 2:4 bitmask sparsity
+    model = toy_llama(32)
+    with torch.no_grad():
+        for name, mod in model.named_modules():
+            if isinstance(mod, torch.nn.Linear):
+                w = mod.weight.data
+                mask = get_24_bytemasks(w)
+                mod.weight.data = torch.where(mask, w, torch.zeros((), dtype=w.dtype))
+    original = {k: v.clone() for k, v in model.state_dict().items()}
+    qcfg = QuantizationConfig(config_groups={"group_0": QuantizationScheme(
+        targets=["Linear"], weights=QuantizationArgs(num_bits=8, type="float", symmetric=True, strategy="channel"))},
+        ignore=["lm_head"], format="float-quantized")
+    scfg = Sparse24BitMaskConfig(targets=["Linear"], ignore=["lm_head"], sparsity_structure="2:4")
+    apply_quantization_config(model, qcfg)
+    calibrate(model)
+    calibrated = {k: v.clone() for k, v in model.state_dict().items()}
+    mc = ModelCompressor(sparsity_config=scfg, quantization_config=copy.deepcopy(qcfg))
+    compressed = mc.compress(model)
+    inplace = copy.deepcopy(model)
+    mc2 = ModelCompressor(sparsity_config=scfg, quantization_config=copy.deepcopy(qcfg))
+    mc2.compress_model(inplace)
+    compressed_inplace = {k: v.clone() for k, v in inplace.state_dict().items()}
+    mc2.decompress_model(inplace)
+    decompressed = {k: v.clone() for k, v in inplace.state_dict().items()}
+    out["fp8_sparse24"] = slim(original, compressed, compressed_inplace, decompressed)
+    torch.save(out, os.path.join(OUT, "model_compressor.pt"))
+
+
 if __name__ == "__main__":
     only = sys.argv[2] if len(sys.argv) > 2 else None  # e.g. "mxfp4": regenerate one fixture
     for name, fn in (("int_quant", gen_int), ("fp8_quant", gen_fp8), ("nvfp4", gen_nvfp4), ("sparse", gen_sparse),
                      ("hadamard", gen_hadamard), ("hadamard_online", gen_hadamard_online), ("hadamard_randomize", gen_hadamard_randomize), ("hadamard_embedding", gen_hadamard_embedding), ("mxfp4", gen_mxfp4), ("marlin24", gen_marlin24),
-                     ("fp4_pack_all", gen_fp4_pack_all), ("hadamard_full", gen_hadamard_full), ("forward_quantize", gen_forward_quantize)):
+                     ("fp4_pack_all", gen_fp4_pack_all), ("hadamard_full", gen_hadamard_full), ("forward_quantize", gen_forward_quantize), ("model_compressor", gen_model_compressor)):
         if only is None or only == name:
             fn()
     for f in sorted(os.listdir(OUT)):
