@@ -21,7 +21,7 @@ from typing import Dict, List, Optional, Set, Tuple
 import torch
 from torch.nn import Module, Parameter
 
-from ... import ops
+from ... import torch_ops as ops
 from ...config import CompressionFormat, SparsityCompressionConfig
 from ...quantization.quant_config import QuantizationConfig, QuantizationStatus, apply_quantization_config, match_named_modules
 from ...quantization.quant_scheme import QuantizationScheme

@@ -6,7 +6,7 @@ from typing import Dict, Optional, Tuple
 import torch
 from torch import Tensor
 
-from ... import ops
+from ... import torch_ops as ops
 from ...config import CompressionFormat
 from ...quantization.lifecycle.forward import _geometry
 from ...quantization.quant_args import QuantizationArgs

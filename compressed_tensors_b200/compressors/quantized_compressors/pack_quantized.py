@@ -7,7 +7,7 @@ from typing import Dict, Literal, Optional, Tuple, Union
 import torch
 from torch import Tensor
 
-from ... import ops
+from ... import torch_ops as ops
 from ...config import CompressionFormat
 from ...quantization.lifecycle.forward import _geometry, dequantize, infer_dequant_args, quantize
 from ...quantization.quant_args import QuantizationArgs, QuantizationStrategy

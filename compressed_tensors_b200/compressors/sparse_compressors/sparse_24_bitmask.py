@@ -5,7 +5,7 @@ from typing import Dict, List, Tuple, Union
 import torch
 from torch import Tensor
 
-from ... import ops
+from ... import torch_ops as ops
 from ..._lib import on_gpu
 from ...config import CompressionFormat, SparsityStructure
 from ...utils.helpers import merge_names
@@ -28,11 +28,7 @@ def sparse24_bitmask_compress(tensor: Tensor, sparsity_structure: Union[Sparsity
     """sparse_24_bitmask.py:162-203 -> (values [R, C/2], bitmask uint8 [R, ceil(C/8)])."""
     assert len(tensor.shape) == 2, "Only 2D tensors are supported"
     assert SparsityStructure(sparsity_structure) == SparsityStructure.TWO_FOUR, "Only 2:4 sparsity is supported"
-    if tensor.is_meta:
-        rows, cols = tensor.shape
-        return (torch.empty((rows, cols // 2), dtype=tensor.dtype, device="meta"),
-                torch.empty((rows, (cols + 7) // 8), dtype=torch.uint8, device="meta"))
-    return ops.sparse24_compress(tensor)
+    return ops.sparse24_compress(tensor)  # a torch operator with a fake implementation: meta tensors give meta results
 
 
 def sparse24_bitmask_decompress(values: Tensor, bitmasks: Tensor, original_shape: torch.Size) -> Tensor:

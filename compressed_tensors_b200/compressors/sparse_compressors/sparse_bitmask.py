@@ -5,7 +5,7 @@ from typing import Dict, List, Tuple, Union
 import torch
 from torch import Tensor
 
-from ... import ops
+from ... import torch_ops as ops
 from ..._lib import on_gpu
 from ...config import CompressionFormat
 from ...utils.helpers import merge_names

@@ -8,7 +8,7 @@ from typing import Dict, Generator, Tuple
 import torch
 from torch import Tensor
 
-from ... import ops
+from ... import torch_ops as ops
 from ..._lib import on_gpu
 from ...config import CompressionFormat
 from ...quantization.lifecycle.forward import quantize

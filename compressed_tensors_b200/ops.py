@@ -15,7 +15,8 @@ __all__ = [
     "cutlass24_compress", "cutlass24_decompress", "marlin24_pack_weight", "marlin24_pack_scales",
     "pack_int32", "unpack_int32", "pack_fp4", "unpack_fp4", "pack_bitmasks", "unpack_bitmasks",
     "sparse24_mask", "sparse24_compress", "sparse24_decompress", "bitmask_compress", "bitmask_decompress", "hadamard",
-    "absmax_quantize", "rotate_quantize_int4_batch", "unpack_dequantize_int4_batch", "tensor_table", "QINT", "QFLOAT",
+    "absmax_quantize", "rotate_quantize_int4_batch", "rotate_quantize_int4_batch_bounded", "quantize_pack_int4_batch",
+    "unpack_dequantize_int4_batch", "tensor_table", "QINT", "QFLOAT",
 ]
 
 _CODEC = {"dtype": CODE_DTYPE, "pack32": CODE_PACK32, "fp4x2": CODE_FP4X2}
@@ -458,6 +459,21 @@ def rotate_quantize_int4_batch(table, signs, precision=torch.float64, device=Non
     s = None if signs is None else signs
     stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
     check(lib().ctb_rotate_quantize_int4_batch(table, i32(len(table)), ptr(s), i32(_precision_code(precision)), ptr(status), stream))
+
+
+def rotate_quantize_int4_batch_bounded(table, signs, status, spin_cycles, skip_tile=-1, device=None):
+    """The tensor-core form of rotate_quantize_int4_batch with the bound of its device-side waits given in SM clocks
+    and, for skip_tile >= 0, with that tile's copy left out so that the wait for it runs out.  Exercises the kernel's
+    error path: it returns, and `status` (device int32) then reads 5 (CTB_ETIMEOUT)."""
+    stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+    check(lib().ctb_rotate_quantize_int4_batch_bounded(table, i32(len(table)), ptr(signs), ptr(status), i64(spin_cycles), i32(skip_tile), stream))
+
+
+def quantize_pack_int4_batch(table, device=None):
+    """quantize with the GIVEN bf16 scales (symmetric int4, group 128) + pack_to_int32 of every tensor in `table`
+    (weights in, words out, scales read), as one launch."""
+    stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+    check(lib().ctb_quantize_pack_int4_batch(table, i32(len(table)), stream))
 
 
 def unpack_dequantize_int4_batch(table, device=None):

@@ -6,7 +6,7 @@ from typing import Optional, Tuple
 
 import torch
 
-from ... import ops
+from ... import torch_ops as ops
 from ..quant_args import QuantizationArgs, QuantizationStrategy
 from ..utils.helpers import qtype_code
 

@@ -33,7 +33,7 @@ class FP4_E2M1_DATA(FloatArgs):
     def cast_to_fp4(x: torch.Tensor) -> torch.Tensor:
         """Snap to the e2m1 grid with ties to the even code, keeping the dtype
         (quant_args.py:55-68).  Runs as a fake-quantize with unit scale on the device."""
-        from .. import ops
+        from .. import torch_ops as ops
 
         flat = x.reshape(1, -1) if x.ndim != 2 else x
         pad = (-flat.shape[-1]) % 16
@@ -214,7 +214,7 @@ class QuantizationArgs(BaseModel, use_enum_values=True):
 
 def round_to_quantized_type(tensor: torch.Tensor, args: QuantizationArgs) -> torch.Tensor:
     """Round to the nearest value of the quantized type, keeping the dtype (quant_args.py:384-408)."""
-    from .. import ops
+    from .. import torch_ops as ops
 
     if args.type == QuantizationType.FLOAT:
         if args.num_bits == 4:

@@ -69,7 +69,7 @@ def apply_quantization_config(model: torch.nn.Module, config: QuantizationConfig
 def calibrate_weight_qparams(module: torch.nn.Module) -> None:
     """Min-max calibration of a module's weight: registers `weight_scale`, `weight_zero_point` and, for
     NVFP4, `weight_global_scale`, shaped as lifecycle/initialize.py:155-280 shapes them."""
-    from .. import ops
+    from .. import torch_ops as ops
 
     args: QuantizationArgs = module.quantization_scheme.weights
     w = module.weight.data

@@ -5,7 +5,7 @@ from typing import Optional, Tuple
 
 import torch
 
-from ... import ops
+from ... import torch_ops as ops
 from ..quant_args import FP4_E2M1_DATA, FP8_E4M3_DATA, FloatArgs, QuantizationArgs, QuantizationStrategy, QuantizationType
 
 __all__ = ["calculate_qparams", "compute_dynamic_scales_and_zp", "calculate_range", "generate_gparam", "is_fp4", "strategy_cdiv", "qtype_code"]

@@ -3,7 +3,7 @@
 :75 generate_mxfp4_scales).  Scales are powers of two stored as uint8 exponents."""
 import torch
 
-from ... import ops
+from ... import torch_ops as ops
 
 __all__ = ["convert_mxfp4_exp_scale", "generate_mxfp4_scales", "round_to_power_2"]
 

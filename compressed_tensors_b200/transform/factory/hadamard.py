@@ -5,7 +5,7 @@ from typing import Optional
 import torch
 from torch.nn import Module, Parameter
 
-from ... import ops
+from ... import torch_ops as ops
 from ..transform_args import TransformArgs, TransformLocation
 from ..transform_scheme import TransformScheme
 from ..utils.hadamard import deterministic_hadamard_matrix

@@ -3,7 +3,7 @@ from typing import Optional, Tuple
 
 import torch
 
-from ... import ops
+from ... import torch_ops as ops
 from ..transform_args import TransformLocation
 from .hadamard import deterministic_hadamard_matrix, is_pow2
 

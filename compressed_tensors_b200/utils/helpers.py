@@ -3,7 +3,7 @@ from typing import List
 
 import torch
 
-from .. import ops
+from .. import torch_ops as ops
 
 __all__ = ["pack_bitmasks", "unpack_bitmasks", "merge_names", "tensor_follows_mask_structure"]
 

@@ -3,7 +3,7 @@
 sparse_semi_structured_to_dense_cutlass) for 16-bit dense dtypes (int16 metadata)."""
 import torch
 
-from .. import ops
+from .. import torch_ops as ops
 from .._lib import on_gpu
 
 __all__ = ["sparse_semi_structured_from_dense_cutlass", "sparse_semi_structured_to_dense_cutlass", "mask_creator"]

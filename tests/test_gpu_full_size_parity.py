@@ -1,0 +1,171 @@
+"""Bit-exact parity against the CPU oracle at the FULL tensor sizes of the benchmark configurations (the
+oracle is C + OpenMP and finishes each of these in about a second), so that anything that depends on the
+grid shape -- moving-window grids, tile-start tables, offsets beyond 2^31 bytes -- is compared and not
+only checked for self-consistency.  Outputs are allocated between canary pages: a kernel that writes one
+byte outside its output fails here even if the result is right."""
+import os
+
+import pytest
+import torch
+
+from tests.helpers import assert_bit_equal
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from compressed_tensors_b200 import ops as o
+    return o
+
+
+@pytest.fixture(scope="module")
+def orc():
+    from oracle import ref
+    ref.build()
+    ref.set_threads(os.cpu_count() or 1)
+    return ref
+
+
+def weights(rows, cols, seed, std=0.02):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(rows, cols, generator=g) * std).to(torch.bfloat16)
+
+
+def test_c1_w4a16_full(ops, orc, canary):
+    """BASELINE config 1 at 4096 x 4096: scales, packed words, dequantized values."""
+    w = weights(4096, 4096, 0)
+    mn, mx = orc.minmax(w, 1, 128)
+    scale, zp = orc.calculate_qparams(mn, mx, qtype=orc.QINT, bits=4, symmetric=True)
+    kw = dict(qtype=orc.QINT, bits=4, col_group=128, row_group=1, scale_row_stride=32)
+    words = orc.pack_int32(orc.quantize(w, scale, zp, out_dtype=torch.int8, **kw), 4)
+    deq = orc.dequantize(orc.unpack_int32(words, 4, w.shape), scale, None, out_dtype=torch.bfloat16, **kw)
+    with canary():
+        gw, gs = ops.absmax_quantize(w.cuda(), qtype=ops.QINT, bits=4, col_group=128, codec="pack32")
+        given = ops.quantize(w.cuda(), scale.cuda(), None, codec="pack32", **kw)
+        gd = ops.dequantize(gw, gs, None, out_dtype=torch.bfloat16, codec="pack32", cols=4096, **kw)
+    assert_bit_equal(gs.cpu(), scale, "scales")
+    assert_bit_equal(gw.cpu(), words, "words (fused calibrate)")
+    assert_bit_equal(given.cpu(), words, "words (given scales)")
+    assert_bit_equal(gd.cpu(), deq, "dequantized")
+
+
+def test_c2_fp8_full(ops, orc, canary):
+    """BASELINE config 2: 4096 x 4096 weight with static per-channel scales, and [1, 8192, 4096] activations with 41
+    outlier channels scaled x20, per-token dynamic scales; bf16 and fp32 scales."""
+    w = weights(4096, 4096, 1)
+    kw = dict(qtype=orc.QFLOAT, bits=8, col_group=4096, row_group=1, scale_row_stride=1)
+    mn, mx = orc.minmax(w, 1, 4096)
+    scale, zp = orc.calculate_qparams(mn, mx, qtype=orc.QFLOAT, bits=8, symmetric=True)
+    q = orc.quantize(w, scale, zp, out_dtype=torch.float8_e4m3fn, **kw)
+    with canary():
+        gq, gs = ops.absmax_quantize(w.cuda(), qtype=ops.QFLOAT, bits=8, col_group=4096, codec="dtype", out_dtype=torch.float8_e4m3fn)
+        gd = ops.dequantize(gq, gs, None, out_dtype=torch.bfloat16, **kw)
+    assert_bit_equal(gs.cpu(), scale.reshape(gs.shape), "weight scales")
+    assert_bit_equal(gq.cpu(), q, "weight codes")
+    assert_bit_equal(gd.cpu(), orc.dequantize(q, scale, None, out_dtype=torch.bfloat16, **kw), "weight dequantized")
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn(1, 8192, 4096, generator=g)
+    x[..., torch.randperm(4096, generator=g)[:41]] *= 20
+    x = x.to(torch.bfloat16)
+    x2 = x.reshape(8192, 4096)
+    mn, mx = orc.minmax(x2, 1, 4096)
+    s16, z16 = orc.calculate_qparams(mn, mx, qtype=orc.QFLOAT, bits=8, symmetric=True)
+    q16 = orc.quantize(x2, s16, z16, out_dtype=torch.float8_e4m3fn, **kw)
+    with canary():
+        gq, gs = ops.absmax_quantize(x.cuda(), qtype=ops.QFLOAT, bits=8, col_group=4096, codec="dtype", out_dtype=torch.float8_e4m3fn)
+        gd = ops.dequantize(gq, gs, None, out_dtype=torch.bfloat16, **kw)
+    assert_bit_equal(gs.cpu().reshape(-1), s16.reshape(-1), "token scales (bf16)")
+    assert_bit_equal(gq.cpu().reshape(8192, 4096), q16, "token codes (bf16 scales)")
+    assert_bit_equal(gd.cpu().reshape(8192, 4096), orc.dequantize(q16, s16, None, out_dtype=torch.bfloat16, **kw), "token dequantized")
+    mn, mx = orc.minmax(x2.float(), 1, 4096)
+    s32, z32 = orc.calculate_qparams(mn, mx, qtype=orc.QFLOAT, bits=8, symmetric=True)
+    q32 = orc.quantize(x2, s32, z32, out_dtype=torch.float8_e4m3fn, **kw)
+    with canary():
+        gq = ops.quantize(x2.cuda(), s32.cuda(), z32.cuda(), out_dtype=torch.float8_e4m3fn, **kw)
+        gd = ops.dequantize(gq, s32.cuda(), z32.cuda(), out_dtype=torch.float32, **kw)
+    assert_bit_equal(gq.cpu(), q32, "token codes (fp32 scales)")
+    assert_bit_equal(gd.cpu(), orc.dequantize(q32, s32, z32, out_dtype=torch.float32, **kw), "token dequantized (fp32)")
+
+
+@pytest.mark.parametrize("shape", [(14336, 4096), (4096, 14336)])
+def test_c3_nvfp4_full(ops, orc, canary, shape):
+    """BASELINE config 3 at the gate/up and down shapes: global scale, e4m3 group scales, packed e2m1 bytes, dequantized."""
+    rows, cols = shape
+    w = weights(rows, cols, 3 + rows % 7)
+    mn, mx = orc.minmax(w, rows, cols)
+    gs = orc.generate_gparam(mn, mx)
+    gmn, gmx = orc.minmax(w, 1, 16)
+    scale, _ = orc.calculate_qparams(gmn, gmx, qtype=orc.QFLOAT, bits=4, symmetric=True, global_scale=gs)
+    kw = dict(qtype=orc.QFLOAT, bits=4, col_group=16, row_group=1, scale_row_stride=cols // 16, global_scale=gs)
+    packed = orc.pack_fp4(orc.quantize(w, scale, None, out_dtype=torch.bfloat16, **kw))
+    deq = orc.dequantize(orc.unpack_fp4(packed, rows, cols), scale, None, out_dtype=torch.bfloat16, **kw)
+    with canary():
+        dmn, dmx = ops.minmax(w.cuda(), rows, cols)
+        dgs = ops.generate_gparam(dmn, dmx)
+        gp, gsc = ops.absmax_quantize(w.cuda(), qtype=ops.QFLOAT, bits=4, col_group=16, codec="fp4x2", global_scale=dgs)
+        gd = ops.dequantize(gp, gsc, None, out_dtype=torch.bfloat16, codec="fp4x2", **dict(kw, global_scale=dgs))
+    assert_bit_equal(dgs.cpu(), gs, "global scale")
+    assert_bit_equal(gsc.cpu(), scale, "group scales")
+    assert_bit_equal(gp.cpu(), packed, "packed bytes")
+    assert_bit_equal(gd.cpu(), deq, "dequantized")
+
+
+def test_c4a_sparse24_e4m3_full(ops, orc, canary):
+    """BASELINE config 4a at 4096 x 11008: bf16 weights pruned 2:4, FP8 per-channel, 2:4 bitmask codec on the e4m3 tensor."""
+    w = weights(4096, 11008, 4)
+    mask = orc.sparse24_mask(w)
+    pruned = torch.where(mask, w, torch.zeros((), dtype=w.dtype))
+    kw = dict(qtype=orc.QFLOAT, bits=8, col_group=11008, row_group=1, scale_row_stride=1)
+    mn, mx = orc.minmax(pruned, 1, 11008)
+    scale, zp = orc.calculate_qparams(mn, mx, qtype=orc.QFLOAT, bits=8, symmetric=True)
+    q = orc.quantize(pruned, scale, zp, out_dtype=torch.float8_e4m3fn, **kw)
+    v, b = orc.sparse24_compress(q)
+    with canary():
+        gmask = ops.sparse24_mask(w.cuda())
+        gq, _ = ops.absmax_quantize(pruned.cuda(), qtype=ops.QFLOAT, bits=8, col_group=11008, codec="dtype", out_dtype=torch.float8_e4m3fn)
+        gv, gb = ops.sparse24_compress(gq)
+        gd = ops.sparse24_decompress(gv, gb, q.shape)
+    assert_bit_equal(gmask.cpu(), mask, "keep mask")
+    assert_bit_equal(gq.cpu(), q, "e4m3 codes")
+    assert_bit_equal(gb.cpu(), b, "bitmask")
+    assert_bit_equal(gv.cpu(), v, "values")
+    assert_bit_equal(gd.cpu(), orc.bitmask_decompress(v, b, q.shape), "decompressed")
+
+
+def test_c4b_bitmask_full(ops, orc, canary):
+    """BASELINE config 4b at 4096 x 4096, Bernoulli(0.5) zero mask."""
+    g = torch.Generator().manual_seed(5)
+    w = weights(4096, 4096, 5)
+    w[torch.rand(4096, 4096, generator=g) < 0.5] = 0
+    values, bitmask, row_offsets = orc.bitmask_compress(w)
+    with canary():
+        gv, gb, gr = ops.bitmask_compress(w.cuda())
+        gd = ops.bitmask_decompress(gv, gb, w.shape)
+    assert_bit_equal(gb.cpu(), bitmask, "bitmask")
+    assert_bit_equal(gr.cpu(), row_offsets, "row offsets")
+    assert_bit_equal(gv.cpu(), values, "values")
+    assert_bit_equal(gd.cpu(), orc.bitmask_decompress(values, bitmask, w.shape), "decompressed")
+
+
+def test_quantize_pack_batch_equals_oracle(ops, orc, canary):
+    """The given-scale whole-shard entry point on a ragged table (tensors smaller than one unit, a partial last
+    unit, a scale outside the reciprocal form's range): every tensor's words against the oracle."""
+    shapes = [(8, 128), (4096, 4096), (1024, 4096), (33, 256), (4096, 14336)]
+    ws = [weights(r, c, 60 + i) for i, (r, c) in enumerate(shapes)]
+    want = []
+    for i, w in enumerate(ws):
+        mn, mx = orc.minmax(w, 1, 128)
+        scale, zp = orc.calculate_qparams(mn, mx, qtype=orc.QINT, bits=4, symmetric=True)
+        if i == 3:  # hand-made scales outside [2^-99, 2^99): the kernel's float routine takes these groups
+            scale[5, 0], scale[7, 1] = 2.0 ** -110, 2.0 ** 100
+        kw = dict(qtype=orc.QINT, bits=4, col_group=128, row_group=1, scale_row_stride=w.shape[1] // 128)
+        want.append((scale, orc.pack_int32(orc.quantize(w, scale, zp, out_dtype=torch.int8, **kw), 4)))
+    with canary():
+        dw = [w.cuda() for w in ws]
+        ds = [s.cuda() for s, _ in want]
+        out = [torch.empty((w.shape[0], w.shape[1] // 8), dtype=torch.int32, device="cuda") for w in ws]
+        ops.quantize_pack_int4_batch(ops.tensor_table(dw, out, ds, [tuple(w.shape) for w in ws]), torch.device("cuda", 0))
+        torch.cuda.synchronize()
+    for i, (o, (_, words)) in enumerate(zip(out, want)):
+        assert_bit_equal(o.cpu(), words, f"tensor {i} {shapes[i]}")

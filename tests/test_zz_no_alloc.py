@@ -37,6 +37,14 @@ def test_static_scratch_decompress_matches_twice():
             assert _call(lib.ctb_bitmask_decompress, values, bitmask, rows, cols, want, L.ptr(ws)) == 0
             assert _call(lib.ctb_bitmask_decompress_static, values, bitmask, rows, cols, got) == 0
             torch.cuda.synchronize()
+            # the point of the entry point: once its first call on the device is behind it, a call takes no device
+            # memory, neither from the driver nor from torch's allocator
+            free0, _ = torch.cuda.mem_get_info()
+            allocs0 = torch.cuda.memory_stats()["allocation.all.allocated"]
+            assert _call(lib.ctb_bitmask_decompress_static, values, bitmask, rows, cols, got) == 0
+            torch.cuda.synchronize()
+            assert torch.cuda.mem_get_info()[0] == free0
+            assert torch.cuda.memory_stats()["allocation.all.allocated"] == allocs0
             assert torch.equal(got.view(torch.uint8), want.view(torch.uint8))
             assert torch.equal(got, torch.where(x == 0, torch.zeros_like(x), x))
 
