@@ -32,7 +32,7 @@ from ...quantization.utils.helpers import calculate_qparams, generate_gparam, is
 __all__ = ["Job", "CodecEngine", "minmax_qparams", "is_w4a16_g128", "STEP_BYTES"]
 
 STEP_BYTES = 384 << 20   # host-resident work is streamed in steps of about this many input bytes
-MAX_INFLIGHT = 6         # steps whose device buffers may be alive at once
+INFLIGHT_FRACTION = 0.4  # of the device memory that is free when a pass starts: bound on the buffers of steps in flight
 _ALIGN = 256
 
 # parameters a quantization compressor reads next to the weight
@@ -370,6 +370,25 @@ class CodecEngine:
                 out["weight"] = st["weight"]
             j.out = out
 
+    # ------------------------------------------------------------------ replay of a recorded cycle
+    def replay_compress(self, table: np.ndarray, signs: Tensor, dev: torch.device) -> None:
+        """The fused rotate + calibrate + quantize + pack launch over a table recorded by an earlier pass."""
+        self._check_status(wait=False)
+        stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+        with self._timed("compress", dev):
+            L.check(L.lib().ctb_rotate_quantize_int4_batch(_table_ptr(table), L.i32(len(table)), L.ptr(signs),
+                                                           L.i32(ops._precision_code(self.rotation_precision)),
+                                                           L.ptr(self._status_word(dev)), stream))
+        self.launches += 1
+        if self.rotation_precision == ops.ROT_TENSOR:
+            self._watch_status(dev)
+
+    def replay_decompress(self, table: np.ndarray, dev: torch.device) -> None:
+        stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+        with self._timed("decompress", dev):
+            L.check(L.lib().ctb_unpack_dequantize_int4_batch(_table_ptr(table), L.i32(len(table)), stream))
+        self.launches += 1
+
     # ------------------------------------------------------------------ drivers
     def run(self, jobs: List[Job], direction: str, deliver: Optional[str] = None, sparsity_compressor=None,
             sparse_compress: Optional[Callable[[Job], None]] = None) -> None:
@@ -431,10 +450,17 @@ class CodecEngine:
                 acc = 0
             steps[-1].append(j)
             acc += nb
-        done: List[torch.cuda.Event] = []
+        # The host only enqueues; it waits for an old step when the device buffers of the steps still in flight would
+        # outgrow the budget (inputs plus outputs: outputs are at most the inputs when compressing, a few times when not).
+        budget = INFLIGHT_FRACTION * torch.cuda.mem_get_info(dev)[0]
+        inflight: List[Tuple[torch.cuda.Event, int]] = []
+        held = 0
         for k, step in enumerate(steps):
-            if k >= MAX_INFLIGHT:
-                done[k - MAX_INFLIGHT].synchronize()  # bounds the device memory in flight
+            need = (2 if direction == "compress" else 5) * sum(_nbytes(v) for j in step for v in self._inputs_of(j, direction).values())
+            while inflight and held + need > budget:
+                ev, nb = inflight.pop(0)
+                ev.synchronize()
+                held -= nb
             ev_in, ev_k, ev_out = torch.cuda.Event(), torch.cuda.Event(), torch.cuda.Event()
             originals = []
             with torch.cuda.stream(s_in):
@@ -475,7 +501,8 @@ class CodecEngine:
                     self._host_ready[host.buf.untyped_storage().data_ptr()] = ev_out
             for j, orig in zip(step, originals):
                 j.state = orig
-            done.append(ev_out)
+            inflight.append((ev_out, need))
+            held += need
             self._tail.append(ev_out)
 
     @staticmethod

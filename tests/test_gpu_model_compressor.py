@@ -96,7 +96,8 @@ def calibrate(model):
                 m.weight.data = w.cuda()
                 calibrate_weight_qparams(m)
                 for name, p in list(m._parameters.items()):
-                    p.data = p.data.cpu()
+                    if p is not None:
+                        p.data = p.data.cpu()
                 m.weight.data = w
 
 
@@ -217,6 +218,45 @@ def test_fused_flow_state_dict_path_and_pipelined(golden):
     for k, v in g["decompressed"].items():
         assert_bit_equal(got[k].cpu(), v, f"pipelined decompress: {k}")
     assert all(v.device.type == "cpu" for v in got.values())
+
+
+def test_reuse_buffers_cycles_equal_the_general_path(golden):
+    """Three compress_model + decompress_model cycles with `reuse_buffers`: the second and third run as two launches
+    over the first cycle's buffers and give the bits of a compressor that allocates afresh every time; a parameter
+    replaced behind the compressor's back sends the next call down the general path."""
+    from compressed_tensors_b200.compressors import ModelCompressor
+    from compressed_tensors_b200.quantization import apply_quantization_config
+
+    g = golden("model_compressor")["w4a16_rot"]
+    tcfg, qcfg = w4a16_configs()
+    models, mcs = [], []
+    for reuse in (True, False):
+        m = toy_llama(g["original"], device="cuda")
+        apply_quantization_config(m, qcfg)
+        models.append(m)
+        mcs.append(ModelCompressor(quantization_config=copy.deepcopy(qcfg), transform_config=tcfg, reuse_buffers=reuse))
+    for cycle in range(3):
+        states = []
+        for m, mc in zip(models, mcs):
+            if getattr(m, "transform_config", None) is not None:
+                del m.transform_config
+            n0 = mc.engine.launches
+            mc.compress_model(m)
+            comp = {k: v.detach().cpu().clone() for k, v in m.state_dict().items()}
+            mc.decompress_model(m)
+            states.append((comp, {k: v.detach().cpu().clone() for k, v in m.state_dict().items()}, mc.engine.launches - n0))
+        assert states[0][2] == 2 and states[1][2] == 2
+        check_state(states[0][0], states[1][0], f"cycle {cycle} compressed")
+        check_state(states[0][1], states[1][1], f"cycle {cycle} decompressed")
+        if cycle == 0:
+            check_state(states[0][0], g["compressed"], "first cycle against the reference")
+    assert mcs[0]._cycle is not None and mcs[0]._cycle.ready
+    lin = models[0].model.layers[0].mlp.down_proj
+    lin.weight = torch.nn.Parameter(lin.weight.data.clone(), requires_grad=False)  # not the tensor the record knows
+    del models[0].transform_config, models[1].transform_config
+    mcs[0].compress_model(models[0])
+    mcs[1].compress_model(models[1])
+    check_state(dict(models[0].state_dict()), {k: v.cpu() for k, v in models[1].state_dict().items()}, "after a foreign parameter")
 
 
 @pytest.mark.parametrize("where", ["cuda", "cpu"])
