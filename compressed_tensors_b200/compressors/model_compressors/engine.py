@@ -25,13 +25,14 @@ from torch import Tensor
 
 from ... import _lib as L
 from ... import ops
+from ...pinned import pool as pinned_pool
 from ...config import CompressionFormat
 from ...quantization.quant_args import QuantizationArgs, QuantizationStrategy, QuantizationType
 from ...quantization.utils.helpers import calculate_qparams, generate_gparam, is_fp4
 
 __all__ = ["Job", "CodecEngine", "minmax_qparams", "is_w4a16_g128", "STEP_BYTES"]
 
-STEP_BYTES = 384 << 20   # host-resident work is streamed in steps of about this many input bytes
+STEP_BYTES = 256 << 20   # host-resident work is streamed in steps of about this many bytes on the bus
 INFLIGHT_FRACTION = 0.4  # of the device memory that is free when a pass starts: bound on the buffers of steps in flight
 _ALIGN = 256
 
@@ -115,7 +116,7 @@ class _Arena:
 
     def __init__(self, nbytes: int, device=None, pinned: bool = False):
         if pinned:
-            self.buf = torch.empty(max(nbytes, 1), dtype=torch.uint8, pin_memory=True)
+            self.buf = pinned_pool().take(nbytes)
         else:
             self.buf = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=device)
         self.off = 0
@@ -156,6 +157,26 @@ def _table_ptr(t: np.ndarray):
     return ctypes.cast(t.ctypes.data, ctypes.POINTER(L.TensorRef))
 
 
+def _prod(shape) -> int:
+    n = 1
+    for d in shape:
+        n *= int(d)
+    return n
+
+
+class _Step:
+    """A few hundred megabytes of one pass over host-resident jobs: upload, kernels, download."""
+
+    def __init__(self, direction: str, jobs: List[Job], dev: torch.device, work, sparse_compress, need: int):
+        self.direction, self.jobs, self.dev, self.work, self.sparse_compress, self.need = direction, jobs, dev, work, sparse_compress, need
+        self.feeds: List[Dict[str, Tensor]] = []
+        self.reads: set = set()        # host storages the step uploads
+        self.writes: int = 0           # host storage its planned results live in
+        self.planned: list = []        # (job, in qparams?, name, host tensor) for results created ahead of the run
+        self.submitted = False
+        self.successor_submitted = False
+
+
 class CodecEngine:
     """Runs lists of jobs.  One engine per ModelCompressor; streams are created per device on first use."""
 
@@ -163,10 +184,16 @@ class CodecEngine:
         self.rotation_precision = rotation_precision
         self._streams: Dict[Tuple[int, str], Tuple[torch.cuda.Stream, ...]] = {}
         self._status: Dict[int, Tensor] = {}
-        self._status_reads: List[Tuple[torch.cuda.Event, Tensor, int]] = []  # (copy done, host copy of the word, device)
+        self._signs: Dict[Tuple[int, int], Tuple[object, Tensor]] = {}
         # host storage -> event after which its bytes are valid (results still on their way while `deferred`)
         self._host_ready: Dict[int, torch.cuda.Event] = {}
         self._tail: List[torch.cuda.Event] = []
+        self._queue: List[_Step] = []                 # planned, not yet submitted
+        self._producer: Dict[int, _Step] = {}         # host storage -> the planned step that fills it
+        self._last_submitted: Dict[str, _Step] = {}
+        self._eager_head: Dict[str, int] = {}         # steps of a pass submitted ahead of the drain (deferred mode)
+        self._inflight: Dict[int, List[Tuple[torch.cuda.Event, int]]] = {}
+        self._budget: Dict[int, float] = {}
         self.deferred = False
         self.launches = 0
         # measurement hook: with record_kernel_times set, every whole-shard launch is bracketed by two CUDA events
@@ -176,14 +203,27 @@ class CodecEngine:
 
     # ------------------------------------------------------------------ plumbing
     def _get_streams(self, dev: torch.device, role: str):
-        key = (dev.index, role)
+        import os
+        key = (dev.index, role if os.environ.get("CTB_SPLIT_STREAMS") else "")
         if key not in self._streams:
             self._streams[key] = tuple(torch.cuda.Stream(dev) for _ in range(3))
         return self._streams[key]
 
+    def _signs_on(self, transform, dev: torch.device) -> Tensor:
+        """The +-1 diagonal of a Hadamard transform on `dev`, copied over once: a copy from pageable host memory makes
+        the host wait for the stream, which would tie the enqueueing of every pipeline step to the GPU's pace."""
+        key = (id(transform), dev.index)
+        hit = self._signs.get(key)
+        if hit is None or hit[0] is not transform:
+            hit = self._signs[key] = (transform, transform._signs.to(dev))
+        return hit[1]
+
     def _status_word(self, dev: torch.device) -> Tensor:
+        """The word a kernel of `dev` writes when one of its bounded waits gives up.  It lives in page-locked host
+        memory that the device writes over the bus: reading it needs no copy, which on a busy pipeline would queue
+        behind the large transfers of its direction and hold up the stream it was issued on."""
         if dev.index not in self._status:
-            self._status[dev.index] = torch.zeros(1, dtype=torch.int32, device=dev)
+            self._status[dev.index] = torch.zeros(1, dtype=torch.int32).pin_memory()
         return self._status[dev.index]
 
     @contextlib.contextmanager
@@ -197,37 +237,33 @@ class CodecEngine:
         b.record(torch.cuda.current_stream(dev))
         self.kernel_times.append((kind, a, b))
 
-    def _watch_status(self, dev: torch.device) -> None:
-        """After a launch that may report a time-out: bring the status word to the host behind it, without a sync."""
-        host = torch.empty(1, dtype=torch.int32, pin_memory=True)
-        host.copy_(self._status_word(dev), non_blocking=True)
-        ev = torch.cuda.Event()
-        ev.record(torch.cuda.current_stream(dev))
-        self._status_reads.append((ev, host, dev.index))
-
-    def _check_status(self, wait: bool) -> None:
-        """Raise for a time-out that a finished launch reported (all launches when `wait`)."""
-        left = []
-        for ev, host, idx in self._status_reads:
-            if wait:
-                ev.synchronize()
-            elif not ev.query():
-                left.append((ev, host, idx))
-                continue
-            if int(host[0]) != 0:
-                self._status[idx].zero_()
-                self._status_reads = []
+    def _check_status(self, wait: bool = False) -> None:
+        """Raise for a time-out that a launch reported.  Without `wait` this sees what has been written so far; callers
+        that need the verdict of everything enqueued synchronise first."""
+        for idx, word in self._status.items():
+            if int(word[0]) != 0:
+                word.zero_()
                 raise TimeoutError(f"a bounded wait inside the tensor-core rotation kernel gave up on cuda:{idx}; "
                                    "the outputs of that compress pass are incomplete")
-        self._status_reads = left
 
     def finish(self) -> None:
         """Wait for everything this engine has put in flight, and turn a device-side time-out into an exception."""
+        self._drain()
         for ev in self._tail:
             ev.synchronize()
         self._tail.clear()
         self._host_ready.clear()
+        self._producer.clear()
+        self._last_submitted.clear()
+        self._eager_head.clear()
+        self._inflight.clear()
+        self._budget.clear()
         self._check_status(wait=True)
+        if pinned_pool().has_parked():
+            # Staging blocks whose tensors died may be handed out again once nothing queued can still touch them: the
+            # waits above cover this engine's own copies; a device-wide wait covers copies the caller issued itself.
+            torch.cuda.synchronize()
+            pinned_pool().settle()
 
     # ------------------------------------------------------------------ compress
     def classify_compress(self, job: Job) -> None:
@@ -277,15 +313,13 @@ class CodecEngine:
                 for i, j in enumerate(group):
                     by_signs.setdefault(id(j.transforms[0].weight), []).append(i)
                 for idxs in by_signs.values():
-                    signs = group[idxs[0]].transforms[0]._signs.to(dev)
+                    signs = self._signs_on(group[idxs[0]].transforms[0], dev)
                     sub = np.ascontiguousarray(table[idxs])
                     with self._timed("compress", dev):
                         L.check(L.lib().ctb_rotate_quantize_int4_batch(_table_ptr(sub), L.i32(len(idxs)), L.ptr(signs),
                                                                        L.i32(ops._precision_code(self.rotation_precision)),
                                                                        L.ptr(self._status_word(dev)), stream))
                     self.launches += 1
-                if self.rotation_precision == ops.ROT_TENSOR:
-                    self._watch_status(dev)
             else:
                 with self._timed("compress", dev):
                     L.check(L.lib().ctb_quantize_pack_int4_batch(_table_ptr(table), L.i32(len(group)), stream))
@@ -380,8 +414,6 @@ class CodecEngine:
                                                            L.i32(ops._precision_code(self.rotation_precision)),
                                                            L.ptr(self._status_word(dev)), stream))
         self.launches += 1
-        if self.rotation_precision == ops.ROT_TENSOR:
-            self._watch_status(dev)
 
     def replay_decompress(self, table: np.ndarray, dev: torch.device) -> None:
         stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
@@ -436,43 +468,143 @@ class CodecEngine:
         self._tail.append(ev)
 
     def _run_host(self, jobs: List[Job], work, direction: str, sparse_compress) -> None:
-        """Host-resident jobs: steps of about STEP_BYTES streamed over three streams of the current device."""
+        """Host-resident jobs: steps of about STEP_BYTES streamed over three streams of the current device.
+
+        A step whose outputs are known without running it (every job goes through a whole-shard entry point) is
+        *planned*: its page-locked output tensors exist at once, so the caller can hang them on the model, while its
+        copies and launches are *submitted* either right away or, when the caller deferred synchronisation, in an
+        order that interleaves the passes it has requested so far (`_drain`).  The order matters: copies of one
+        direction run in the order they were submitted, whatever stream they are on, so a decompress pass queued
+        wholesale behind a compress pass would see its small uploads wait behind every weight of the model."""
         if not torch.cuda.is_available():
             raise RuntimeError("compressed_tensors_b200 needs a CUDA device (no CPU fallback)")
         dev = torch.device("cuda", torch.cuda.current_device())
-        s_in, s_k, s_out = self._get_streams(dev, direction)
-        steps: List[List[Job]] = [[]]
+
+        # steps by the larger side of the job (what comes in when compressing, what goes out when decompressing), so
+        # that a step is a few hundred megabytes on the bus in its long direction whatever the compression ratio
+        def weight_of(j: Job) -> int:
+            nin = sum(_nbytes(v) for v in self._inputs_of(j, direction).values())
+            if direction == "compress":
+                return nin
+            if j.shape is not None:
+                return max(nin, 2 * j.shape[0] * j.shape[1])
+            return 4 * nin
+
+        groups: List[List[Job]] = [[]]
         acc = 0
         for j in jobs:
-            nb = sum(_nbytes(v) for v in self._inputs_of(j, direction).values())
-            if steps[-1] and acc + nb > STEP_BYTES:
-                steps.append([])
+            nb = weight_of(j)
+            if groups[-1] and acc + nb > STEP_BYTES:
+                groups.append([])
                 acc = 0
-            steps[-1].append(j)
+            groups[-1].append(j)
             acc += nb
+        for group in groups:
+            if not group:
+                continue
+            step = _Step(direction, group, dev, work, sparse_compress, need=2 * sum(weight_of(j) for j in group))
+            step.feeds = [self._inputs_of(j, direction) for j in group]
+            step.reads = {h.untyped_storage().data_ptr() for f in step.feeds for h in f.values()}
+            if all(j.kind in ("rotq4", "q4", "dq4") for j in group) and sparse_compress is None:
+                self._plan(step)
+                self._queue.append(step)
+                # Deferred: hold the step back so that a pass requested later can be interleaved with this one; the
+                # first two steps of a lone pass would lead any interleaving, so they go out at once and the GPU starts.
+                lone = all(q.direction == direction for q in self._queue)
+                if not self.deferred or (lone and sum(1 for q in self._queue) <= 2 and self._eager_head.get(direction, 0) < 2):
+                    if self.deferred:
+                        self._eager_head[direction] = self._eager_head.get(direction, 0) + 1
+                    self._drain()
+            else:
+                self._drain()  # whatever was planned before comes first
+                self._submit(step)
+
+    def _plan(self, step: "_Step") -> None:
+        """Create the host-side results of a step (views of one page-locked block) without running it."""
+        specs = []  # (job, dict, name, shape, dtype)
+        for j in step.jobs:
+            if step.direction == "compress":
+                r, c = j.state["weight"].shape
+                j.out = {"weight_shape": torch.tensor((r, c))}  # int64 [2], as torch.tensor(weight.shape)
+                specs.append((j, j.out, "weight_packed", (r, c // 8), torch.int32))
+                if j.kind == "rotq4":
+                    specs.append((j, j.qparams, "weight_scale", (r, c // 128), torch.bfloat16))
+                j.shape, j.quantized = (r, c), True
+            else:
+                specs.append((j, j.out, "weight", j.shape, torch.bfloat16))
+        host = _Arena(sum(_up(_prod(shape) * _ITEMSIZE[dt]) for _, _, _, shape, dt in specs), pinned=True)
+        for j, d, name, shape, dt in specs:
+            d[name] = host.take(shape, dt)
+            step.planned.append((j, d is j.qparams, name, d[name]))
+        step.writes = host.buf.untyped_storage().data_ptr()
+        self._producer[step.writes] = step
+
+    def _drain(self) -> None:
+        """Submit the planned steps.  Passes are interleaved: a step is submitted as soon as every step that produces
+        what it reads has been submitted and, so that the copy engine never has to wait for that round trip, one more
+        step of the producing pass behind them; steps of one pass keep their order."""
+        queue, self._queue = self._queue, []
+        passes: Dict[str, List[_Step]] = {}
+        for st in queue:
+            passes.setdefault(st.direction, []).append(st)
+        order = list(passes)  # the order in which the passes were requested
+        while any(passes.values()):
+            progressed = False
+            for d in reversed(order):  # the later pass first: its steps are the ones that wait on others
+                if not passes[d]:
+                    continue
+                st = passes[d][0]
+                producers = [self._producer[p] for p in st.reads if p in self._producer]
+                pending = [q for q in producers if not q.submitted]
+                if pending:
+                    continue
+                # keep the producing pass one step ahead
+                ahead_ok = True
+                for q in producers:
+                    rest = passes.get(q.direction, [])
+                    if rest and d != q.direction and not self._lead_ok(q, rest):
+                        ahead_ok = False
+                if not ahead_ok:
+                    continue
+                self._submit(passes[d].pop(0))
+                progressed = True
+                break
+            if not progressed:
+                # nothing of a later pass is ready: advance the earliest pass that has steps left
+                for d in order:
+                    if passes[d]:
+                        self._submit(passes[d].pop(0))
+                        break
+
+    @staticmethod
+    def _lead_ok(producer: "_Step", rest: List["_Step"]) -> bool:
+        """True when the pass of `producer` has submitted at least one step after it (or has none left)."""
+        return producer.successor_submitted or not rest
+
+    def _submit(self, step: "_Step") -> None:
+        dev, direction = step.dev, step.direction
+        s_in, s_k, s_out = self._get_streams(dev, direction)
         # The host only enqueues; it waits for an old step when the device buffers of the steps still in flight would
         # outgrow the budget (inputs plus outputs: outputs are at most the inputs when compressing, a few times when not).
-        budget = INFLIGHT_FRACTION * torch.cuda.mem_get_info(dev)[0]
-        inflight: List[Tuple[torch.cuda.Event, int]] = []
-        held = 0
-        for k, step in enumerate(steps):
-            need = (2 if direction == "compress" else 5) * sum(_nbytes(v) for j in step for v in self._inputs_of(j, direction).values())
-            while inflight and held + need > budget:
-                ev, nb = inflight.pop(0)
-                ev.synchronize()
-                held -= nb
-            ev_in, ev_k, ev_out = torch.cuda.Event(), torch.cuda.Event(), torch.cuda.Event()
-            originals = []
+        if self._budget.get(dev.index) is None:
+            self._budget[dev.index] = INFLIGHT_FRACTION * torch.cuda.mem_get_info(dev)[0]
+        inflight = self._inflight.setdefault(dev.index, [])
+        while inflight and sum(nb for _, nb in inflight) + step.need > self._budget[dev.index]:
+            ev, _ = inflight.pop(0)
+            ev.synchronize()
+        ev_in, ev_k, ev_out = torch.cuda.Event(), torch.cuda.Event(), torch.cuda.Event()
+        originals = []
+        planned_out = [(j, j.out, j.qparams) for j in step.jobs] if step.planned else None
+        with torch.cuda.device(dev):
             with torch.cuda.stream(s_in):
-                feeds = [self._inputs_of(j, direction) for j in step]
-                arena = _Arena(sum(_up(_nbytes(v)) for f in feeds for v in f.values()), dev)
-                for j, f in zip(step, feeds):
+                arena = _Arena(sum(_up(_nbytes(v)) for f in step.feeds for v in f.values()), dev)
+                for j, f in zip(step.jobs, step.feeds):
                     originals.append(j.state)
                     st = dict(j.state)
                     for name, h in f.items():
                         ready = self._host_ready.get(h.untyped_storage().data_ptr())
                         if ready is not None:
-                            s_in.wait_event(ready)  # bytes a deferred earlier pass is still delivering
+                            s_in.wait_event(ready)  # bytes an earlier step is still delivering
                         d = arena.take(h.shape, h.dtype)
                         d.copy_(h, non_blocking=True)
                         st[name] = d
@@ -481,29 +613,48 @@ class CodecEngine:
             arena.buf.record_stream(s_k)
             with torch.cuda.stream(s_k):
                 s_k.wait_event(ev_in)
-                work(step, dev)
-                if sparse_compress is not None:
-                    for j in step:
-                        sparse_compress(j)
+                if step.planned:
+                    for j in step.jobs:
+                        j.out, j.qparams = {}, {}
+                step.work(step.jobs, dev)
+                if step.sparse_compress is not None:
+                    for j in step.jobs:
+                        step.sparse_compress(j)
                 ev_k.record(s_k)
             with torch.cuda.stream(s_out):
                 s_out.wait_event(ev_k)
-                outs = [(d, name, v) for j in step for d, name, v in j.results() if v.is_cuda]  # small host tensors (shapes) stay
-                host = _Arena(sum(_up(_nbytes(v)) for _, _, v in outs), pinned=True)
-                for d, name, v in outs:
-                    v = v.contiguous()
-                    v.record_stream(s_out)
-                    h = host.take(v.shape, v.dtype)
-                    h.copy_(v, non_blocking=True)
-                    d[name] = h
-                ev_out.record(s_out)
-                if outs:
-                    self._host_ready[host.buf.untyped_storage().data_ptr()] = ev_out
-            for j, orig in zip(step, originals):
-                j.state = orig
-            inflight.append((ev_out, need))
-            held += need
-            self._tail.append(ev_out)
+                if step.planned:
+                    for j, in_qparams, name, h in step.planned:
+                        v = (j.qparams if in_qparams else j.out)[name]
+                        if tuple(v.shape) != tuple(h.shape) or v.dtype != h.dtype:
+                            raise RuntimeError(f"{j.prefix}.{name}: planned {tuple(h.shape)} {h.dtype}, produced {tuple(v.shape)} {v.dtype}")
+                        v = v.contiguous()
+                        v.record_stream(s_out)
+                        h.copy_(v, non_blocking=True)
+                    for (j, out, qparams) in planned_out:
+                        j.out, j.qparams = out, qparams  # the host tensors the caller already holds
+                    ev_out.record(s_out)
+                    self._host_ready[step.writes] = ev_out
+                else:
+                    outs = [(d, name, v) for j in step.jobs for d, name, v in j.results() if v.is_cuda]  # small host tensors (shapes) stay
+                    host = _Arena(sum(_up(_nbytes(v)) for _, _, v in outs), pinned=True)
+                    for d, name, v in outs:
+                        v = v.contiguous()
+                        v.record_stream(s_out)
+                        h = host.take(v.shape, v.dtype)
+                        h.copy_(v, non_blocking=True)
+                        d[name] = h
+                    ev_out.record(s_out)
+                    if outs:
+                        self._host_ready[host.buf.untyped_storage().data_ptr()] = ev_out
+        for j, orig in zip(step.jobs, originals):
+            j.state = orig
+        step.submitted = True
+        if step.direction in self._last_submitted:
+            self._last_submitted[step.direction].successor_submitted = True
+        self._last_submitted[step.direction] = step
+        inflight.append((ev_out, step.need))
+        self._tail.append(ev_out)
 
     @staticmethod
     def _inputs_of(j: Job, direction: str) -> Dict[str, Tensor]:

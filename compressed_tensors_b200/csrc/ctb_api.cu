@@ -52,3 +52,22 @@ int sm_count() {
 extern "C" const char *ctb_version(void) { return "ctb200 0.1.0 (sm_100a)"; }
 extern "C" const char *ctb_last_error_string(void) { return ctb::g_err; }
 extern "C" int64_t ctb_launch_count(void) { return ctb::g_launches.load(); }
+
+// ---- page-locked host memory for the staging buffers of the host <-> device pipeline ---------------------------
+// Plain wrappers over cudaHostAlloc / cudaFreeHost (portable: page-locked for every context of the process), so
+// that the host layer can keep its own pool of staging blocks and decide itself when one is reused.
+extern "C" int ctb_pinned_alloc(int64_t nbytes, void **out) {
+    if (!out || nbytes <= 0) return ctb::fail(CTB_EINVAL_NULL, "ctb_pinned_alloc needs a size and a place for the pointer");
+    void *p = nullptr;
+    cudaError_t e = cudaHostAlloc(&p, (size_t)nbytes, cudaHostAllocPortable);
+    if (e != cudaSuccess) return ctb::fail(CTB_ECUDA, "cudaHostAlloc(%lld): %s", (long long)nbytes, cudaGetErrorString(e));
+    *out = p;
+    return CTB_OK;
+}
+
+extern "C" int ctb_pinned_free(void *p) {
+    if (!p) return CTB_OK;
+    cudaError_t e = cudaFreeHost(p);
+    if (e != cudaSuccess) return ctb::fail(CTB_ECUDA, "cudaFreeHost: %s", cudaGetErrorString(e));
+    return CTB_OK;
+}

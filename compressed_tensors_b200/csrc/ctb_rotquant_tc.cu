@@ -305,7 +305,12 @@ rotquant128_tc_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256) : "memory");
     }
-    if (threadIdx.x == 0 && *err != 0 && status != nullptr) atomicExch(status, CTB_ETIMEOUT);
+    // a plain store: the status word may live in device memory or in page-locked host memory that the device reaches
+    // over the bus, where it can be read without a copy on any stream
+    if (threadIdx.x == 0 && *err != 0 && status != nullptr) {
+        *reinterpret_cast<volatile int *>(status) = CTB_ETIMEOUT;
+        __threadfence_system();
+    }
 }
 
 }  // namespace ctb

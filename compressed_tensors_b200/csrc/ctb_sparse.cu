@@ -7,6 +7,7 @@
 #include <atomic>
 
 #include "ctb_codec.cuh"
+#include "ctb_fastdiv.h"
 #include "ctb_sparse24_simd.cuh"
 
 namespace ctb {
@@ -558,47 +559,28 @@ __global__ void __launch_bounds__(kThreads) bm_expand_kernel(const void *values,
 }  // namespace ctb
 
 
-// ------------------------------------------------------------------ warp-tile bitmask codec (cols % 8 == 0)
+// ------------------------------------------------------------------ block-tile bitmask codec (cols % 8 == 0)
 //
-// The flat tensor is cut into tiles of 512 consecutive elements, one per warp and step (16 elements, i.e. two
-// bitmask bytes, per lane), and every warp of the grid owns a CONTIGUOUS range of tiles.
-//   kernel 1 streams over the tensor (compress: writes the bitmask) or over the bitmask (decompress) and leaves
-//            the kept count of every warp's range and of every block;
-//   kernel 2, launched with the same grid, sums the counts of the blocks before it (a few hundred words), then
-//            every warp walks its range with a running offset: kept values go through a per-warp shared-memory
-//            window that mirrors the 4-byte alignment of `values`, so that the global side is whole 32-bit words.
-// There is no block barrier inside the loops and nothing waits on another block; the second read of the dense
-// tensor comes from L2 when the tensor fits there.
+// The flat tensor is a sequence of units of 8 elements (one bitmask byte each).  Every block of the grid owns a
+// CONTIGUOUS range of units and walks it in tiles of kBmTile units (8192 elements), thread t taking units
+// t, t + 256, t + 512, t + 768 of a tile, so that each load or store instruction of a warp covers one contiguous span.
+//   kernel 1 streams over the tensor (compress: writes the bitmask) or over the bitmask (decompress) and leaves the
+//            kept count of every block;
+//   kernel 2, launched with the same grid, sums the counts of the blocks before it (at most 4096 words) and walks
+//            its range with a running offset.  Per tile: one block-wide exclusive scan of the per-unit counts
+//            (packed pairs through the warp shuffles, then 32 warp totals through one more warp scan), a
+//            data-dependent placement of single elements into (out of) a shared-memory window that mirrors the
+//            16-byte alignment of `values`, and the window is written (read) as whole 16-byte words; only the
+//            ragged head and tail of a tile move element by element.
+// Nothing waits on another block, and scratch is one count per block whatever the tensor size.  The second read
+// of the dense tensor comes from L2 when the tensor fits there.
 namespace ctb {
 
 constexpr int kWarps = kThreads / 32;
-constexpr int kWarpTile = 512;      // elements per warp and step
-constexpr int kTileMaxGrid = 4096;  // blocks per launch (bounds the scratch: nine words per block)
-
-// A warp's staging window is addressed plainly: with lane l owning units l and 32 + l, the lanes' runs start
-// about 8 bytes apart at 50 % density of 16-bit elements, i.e. two lanes per bank, and the index arithmetic that
-// padding would add to every element costs more than that conflict.
-__device__ __forceinline__ int pad_word(int w) { return w; }
-__device__ __forceinline__ int pad_byte(int o) { return o; }
-template <int ES>
-struct StageWords {
-    static constexpr int value = kWarpTile * ES / 4 + 2;
-};
-
-template <int ES>
-__device__ __forceinline__ uint32_t stage_load(const uint32_t *st, int o) {
-    const char *p = reinterpret_cast<const char *>(st) + pad_byte(o);
-    if constexpr (ES == 1) return *reinterpret_cast<const uint8_t *>(p);
-    else if constexpr (ES == 2) return *reinterpret_cast<const uint16_t *>(p);
-    else return *reinterpret_cast<const uint32_t *>(p);
-}
-template <int ES>
-__device__ __forceinline__ void stage_store(uint32_t *st, int o, uint32_t v) {
-    char *p = reinterpret_cast<char *>(st) + pad_byte(o);
-    if constexpr (ES == 1) *reinterpret_cast<uint8_t *>(p) = (uint8_t)v;
-    else if constexpr (ES == 2) *reinterpret_cast<uint16_t *>(p) = (uint16_t)v;
-    else *reinterpret_cast<uint32_t *>(p) = v;
-}
+constexpr int kBmRows = 4;                   // units per thread and tile
+constexpr int kBmTile = kThreads * kBmRows;  // units per block and step
+constexpr int kTileMaxGrid = 4096;           // blocks per launch (bounds the scratch: one count per block)
+static_assert(kWarps == 8 && kBmRows == 4, "tile_scan maps (row, warp) onto the 32 lanes of one warp");
 
 // The per-element placement, written as predicated instructions: `if (bit) { store; advance; }` in C++ becomes a
 // branch with its divergence bookkeeping per element, which is most of what these kernels would execute.
@@ -612,24 +594,36 @@ __device__ __forceinline__ void stage_put_if(uint32_t &saddr, uint32_t v, uint32
     else
         asm volatile("{ .reg .pred p; setp.ne.u32 p, %2, 0; @p st.shared.u32 [%0], %1; @p add.u32 %0, %0, 4; }" : "+r"(saddr) : "r"(v), "r"(bit) : "memory");
 }
-// tiles [first, last) of this warp when `ntiles` are dealt to all warps of the grid in contiguous ranges
-__device__ __forceinline__ void warp_range(int64_t ntiles, int64_t &first, int64_t &last) {
-    const int64_t nw = (int64_t)gridDim.x * kWarps;
-    const int64_t per = (ntiles + nw - 1) / nw;
-    const int64_t gw = (int64_t)blockIdx.x * kWarps + (threadIdx.x >> 5);
-    first = gw * per < ntiles ? gw * per : ntiles;
-    last = first + per < ntiles ? first + per : ntiles;
+// the mirror image: the element at `saddr` when the bit is set (and advance), zero otherwise
+template <int ES>
+__device__ __forceinline__ uint32_t stage_get_if(uint32_t &saddr, uint32_t bit) {
+    uint32_t v;
+    if constexpr (ES == 1)
+        asm volatile("{ .reg .pred p; setp.ne.u32 p, %2, 0; mov.u32 %0, 0; @p ld.shared.u8 %0, [%1]; @p add.u32 %1, %1, 1; }" : "=r"(v), "+r"(saddr) : "r"(bit) : "memory");
+    else if constexpr (ES == 2)
+        asm volatile("{ .reg .pred p; setp.ne.u32 p, %2, 0; mov.u32 %0, 0; @p ld.shared.u16 %0, [%1]; @p add.u32 %1, %1, 2; }" : "=r"(v), "+r"(saddr) : "r"(bit) : "memory");
+    else
+        asm volatile("{ .reg .pred p; setp.ne.u32 p, %2, 0; mov.u32 %0, 0; @p ld.shared.u32 %0, [%1]; @p add.u32 %1, %1, 4; }" : "=r"(v), "+r"(saddr) : "r"(bit) : "memory");
+    return v;
 }
 
-// kernel 1 epilogue: the kept count of this warp's range and of the block
-__device__ __forceinline__ void publish_counts(unsigned long long c, unsigned long long *block_tot, unsigned long long *warp_tot) {
+// units [first, last) of this block when the units are dealt to the blocks of the grid in contiguous ranges of
+// whole rows of kThreads units
+__device__ __forceinline__ void block_range(int64_t units, int64_t &first, int64_t &last) {
+    const int64_t rows = (units + kThreads - 1) / kThreads;
+    const int64_t per = (rows + gridDim.x - 1) / gridDim.x;
+    const int64_t r0 = min((int64_t)blockIdx.x * per, rows);
+    const int64_t r1 = min(r0 + per, rows);
+    first = r0 * kThreads;
+    last = min(r1 * kThreads, units);
+}
+
+// kernel 1 epilogue: the kept count of the block
+__device__ __forceinline__ void publish_count(unsigned long long c, unsigned long long *block_tot) {
     __shared__ unsigned long long wt[kWarps];
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xFFFFFFFFu, c, o);
-    if ((threadIdx.x & 31) == 0) {
-        wt[threadIdx.x >> 5] = c;
-        warp_tot[(int64_t)blockIdx.x * kWarps + (threadIdx.x >> 5)] = c;
-    }
+    if ((threadIdx.x & 31) == 0) wt[threadIdx.x >> 5] = c;
     __syncthreads();
     if (threadIdx.x == 0) {
         unsigned long long t = 0;
@@ -639,9 +633,8 @@ __device__ __forceinline__ void publish_counts(unsigned long long c, unsigned lo
     }
 }
 
-// kernel 2 prologue: index of the first kept value of this warp's range (uniform over the warp); the last block
-// also stores the grand total
-__device__ __forceinline__ unsigned long long warp_first_value(const unsigned long long *block_tot, const unsigned long long *warp_tot, int64_t *nnz) {
+// kernel 2 prologue: index of the first kept value of this block's range; the last block also stores the grand total
+__device__ __forceinline__ unsigned long long block_first_value(const unsigned long long *block_tot, int64_t *nnz) {
     __shared__ unsigned long long red[kWarps];
     unsigned long long s = 0;
     for (int i = threadIdx.x; i < (int)blockIdx.x; i += kThreads) s += block_tot[i];
@@ -653,30 +646,48 @@ __device__ __forceinline__ unsigned long long warp_first_value(const unsigned lo
 #pragma unroll
     for (int i = 0; i < kWarps; ++i) base += red[i];
     if (nnz != nullptr && blockIdx.x == gridDim.x - 1 && threadIdx.x == 0) *nnz = (int64_t)(base + block_tot[blockIdx.x]);
-    const int w = threadIdx.x >> 5;
-    for (int i = 0; i < w; ++i) base += warp_tot[(int64_t)blockIdx.x * kWarps + i];
     return base;
 }
 
-// Within a tile of 64 units (8 elements each) lane l owns unit l of the first half and unit 32 + l of the second,
-// so that each load or store instruction of the warp covers one contiguous span.  In tile order the lane's two
-// pieces are (half 0, lane l) and (half 1, lane l).
-
-// exclusive prefixes of this lane's two pieces within the tile, and the tile total: one scan on the packed pair
-// of counts (each at most 8 per lane, 256 per half)
-__device__ __forceinline__ void warp_excl_scan2(int c0, int c1, int &excl0, int &excl1, int &total) {
-    const int lane = threadIdx.x & 31;
-    uint32_t inc = (uint32_t)c0 | ((uint32_t)c1 << 16);
+// Exclusive prefixes, in tile order (row j of the tile before row j + 1, threads in order inside a row), of the
+// per-unit counts c[j] <= 8 of this thread, and the tile total.  Two barriers; `wt` and `pre` are block-shared.
+__device__ __forceinline__ void tile_scan(const uint32_t (&c)[kBmRows], uint32_t (&excl)[kBmRows], uint32_t &total, uint32_t (*wt)[2],
+                                          uint32_t *pre) {
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    uint32_t p01 = c[0] | (c[1] << 16), p23 = c[2] | (c[3] << 16);  // a warp's sums stay below 2^16
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
-        const uint32_t t = __shfl_up_sync(0xFFFFFFFFu, inc, o);
-        if (lane >= o) inc += t;
+        const uint32_t a = __shfl_up_sync(0xFFFFFFFFu, p01, o), b = __shfl_up_sync(0xFFFFFFFFu, p23, o);
+        if (lane >= o) {
+            p01 += a;
+            p23 += b;
+        }
     }
-    const uint32_t all = __shfl_sync(0xFFFFFFFFu, inc, 31);
-    const int tot0 = (int)(all & 0xFFFFu);
-    excl0 = (int)(inc & 0xFFFFu) - c0;
-    excl1 = tot0 + (int)(inc >> 16) - c1;
-    total = tot0 + (int)(all >> 16);
+    if (lane == 31) {
+        wt[w][0] = p01;
+        wt[w][1] = p23;
+    }
+    __syncthreads();
+    if (w == 0) {
+        // lane = row * kWarps + warp: the 32 (row, warp) totals in tile order
+        const int j = lane >> 3, ww = lane & 7;
+        const uint32_t packed = wt[ww][j >> 1];
+        const uint32_t v = (j & 1) ? (packed >> 16) : (packed & 0xFFFFu);
+        uint32_t inc = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t a = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+            if (lane >= o) inc += a;
+        }
+        pre[lane] = inc - v;
+        if (lane == 31) pre[32] = inc;
+    }
+    __syncthreads();
+    total = pre[32];
+    excl[0] = pre[0 * kWarps + w] + (p01 & 0xFFFFu) - c[0];
+    excl[1] = pre[1 * kWarps + w] + (p01 >> 16) - c[1];
+    excl[2] = pre[2 * kWarps + w] + (p23 & 0xFFFFu) - c[2];
+    excl[3] = pre[3 * kWarps + w] + (p23 >> 16) - c[3];
 }
 
 // raw 16-byte (ES = 2), 8-byte (ES = 1) or 32-byte (ES = 4) image of one 8-element unit; KEEP = the dense tensor is
@@ -714,214 +725,223 @@ __device__ __forceinline__ void unit_bits(const Raw8 &r, uint32_t (&b)[8]) {
     }
 }
 
-// 8-bit non-zero mask of one unit straight from its packed words (no per-element unpacking)
+// The top bits of the four bytes of t (bits 7, 15, 23, 31) as a nibble in bits 28..31: one multiply moves bit 7 + 8i
+// to bit 28 + i, and no two partial products share a bit, so nothing carries.
+__device__ __forceinline__ uint32_t top_bits_to_high_nibble(uint32_t t) { return (t & 0x80808080u) * 0x00204081u; }
+
+// 8-bit non-zero mask of one unit straight from its packed words.  16- and 8-bit elements: adding the magnitude mask
+// to the magnitude bits carries into the element's top bit exactly when one of them is set (an integer type's own
+// top bit is OR-ed in); the top bits are then gathered with a byte permute and a multiply.
 template <int ES>
 __device__ __forceinline__ uint32_t unit_nz_mask(const Raw8 &r, uint32_t nzm) {
-    uint32_t m = 0;
     if constexpr (ES == 2) {
-        const uint32_t w[4] = {r.a.x, r.a.y, r.a.z, r.a.w};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            m |= ((w[i] & nzm) != 0 ? 1u : 0u) << (2 * i);
-            m |= ((w[i] & (nzm << 16)) != 0 ? 1u : 0u) << (2 * i + 1);
-        }
+        const uint32_t k = 0x7FFF7FFFu;  // the 16-bit types here are floating point: sign excluded, -0.0 is a zero
+        const uint32_t t0 = (r.a.x & k) + k, t1 = (r.a.y & k) + k, t2 = (r.a.z & k) + k, t3 = (r.a.w & k) + k;
+        const uint32_t lo = top_bits_to_high_nibble(prmt_b32(t0, t1, 0x7531)), hi = top_bits_to_high_nibble(prmt_b32(t2, t3, 0x7531));
+        return (lo >> 28) | ((hi >> 24) & 0xF0u);
     } else if constexpr (ES == 1) {
-        const uint32_t w[2] = {r.a.x, r.a.y};
-#pragma unroll
-        for (int i = 0; i < 8; ++i) m |= ((w[i >> 2] & (nzm << (8 * (i & 3)))) != 0 ? 1u : 0u) << i;
+        const uint32_t k = 0x7F7F7F7Fu;
+        uint32_t t0 = (r.a.x & k) + k, t1 = (r.a.y & k) + k;
+        if (nzm & 0x80u) {
+            t0 |= r.a.x;
+            t1 |= r.a.y;
+        }
+        return (top_bits_to_high_nibble(t0) >> 28) | ((top_bits_to_high_nibble(t1) >> 24) & 0xF0u);
     } else {
+        uint32_t m = 0;
         const uint32_t w[8] = {r.a.x, r.a.y, r.a.z, r.a.w, r.b.x, r.b.y, r.b.z, r.b.w};
 #pragma unroll
         for (int i = 0; i < 8; ++i) m |= ((w[i] & nzm) != 0 ? 1u : 0u) << i;
+        return m;
     }
-    return m;
 }
 
-// compress, kernel 1: bitmask bytes and the kept counts
+// compress, kernel 1: bitmask bytes and the kept count of the block
 template <int ES>
-__global__ void __launch_bounds__(kThreads) bm_warp_count_kernel(const void *x, uint32_t nzm, int64_t units, uint8_t *bitmask,
-                                                                 unsigned long long *block_tot, unsigned long long *warp_tot) {
+__global__ void __launch_bounds__(kThreads) bm_block_count_kernel(const void *x, uint32_t nzm, int64_t units, uint8_t *bitmask,
+                                                                  unsigned long long *block_tot) {
     int64_t first, last;
-    warp_range((units + 63) / 64, first, last);
-    const int lane = threadIdx.x & 31;
-    int cnt = 0;
-    for (int64_t tile = first; tile < last; ++tile) {
+    block_range(units, first, last);
+    uint32_t cnt = 0;
+    for (int64_t base = first; base < last; base += kBmTile) {
+        Raw8 raw[kBmRows];
+        bool ok[kBmRows];
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            const int64_t u = tile * 64 + 32 * h + lane;
-            if (u < units) {
-                const uint32_t m = unit_nz_mask<ES>(load_unit_raw<ES, true>(x, u), nzm);
-                bitmask[u] = (uint8_t)m;
-                cnt += __popc(m);
-            }
+        for (int j = 0; j < kBmRows; ++j) {  // all loads of the tile first
+            const int64_t u = base + j * kThreads + threadIdx.x;
+            ok[j] = u < last;
+            if (ok[j]) raw[j] = load_unit_raw<ES, true>(x, u);
+        }
+#pragma unroll
+        for (int j = 0; j < kBmRows; ++j) {
+            if (!ok[j]) continue;
+            const uint32_t m = unit_nz_mask<ES>(raw[j], nzm);
+            bitmask[base + j * kThreads + threadIdx.x] = (uint8_t)m;
+            cnt += __popc(m);
         }
     }
-    publish_counts((unsigned long long)cnt, block_tot, warp_tot);
+    publish_count((unsigned long long)cnt, block_tot);
 }
 
-// decompress, kernel 1: the same counts from the bitmask (a tile is 64 bitmask bytes)
-__global__ void __launch_bounds__(kThreads) bm_warp_popcount_kernel(const uint8_t *bitmask, int64_t units, unsigned long long *block_tot,
-                                                                    unsigned long long *warp_tot, Gate gate) {
+// decompress, kernel 1: the same counts from the bitmask
+__global__ void __launch_bounds__(kThreads) bm_block_popcount_kernel(const uint8_t *bitmask, int64_t units, unsigned long long *block_tot,
+                                                                     Gate gate) {
     if (gate.flag != nullptr && *gate.flag != gate.value) return;  // the fast 2:4 expansion already produced the tensor
     int64_t first, last;
-    warp_range((units + 63) / 64, first, last);
-    const int lane = threadIdx.x & 31;
-    const int64_t b0 = first * 64, b1 = last * 64 < units ? last * 64 : units;
+    block_range(units, first, last);
     unsigned long long c = 0;
-    int64_t i = b0 + lane * 16;
+    int64_t i = first + (int64_t)threadIdx.x * 16;  // `first` is a multiple of 256: 16-byte steps keep the base's alignment
     if ((reinterpret_cast<uintptr_t>(bitmask) & 15u) == 0) {
-        for (; i + 16 <= b1; i += 512) {
+        for (; i + 16 <= last; i += kThreads * 16) {
             const uint4 v = *reinterpret_cast<const uint4 *>(bitmask + i);
             c += __popc(v.x) + __popc(v.y) + __popc(v.z) + __popc(v.w);
         }
     }
-    // ragged end (and unaligned bitmasks): a lane's first leftover chunk may be partial, later ones are whole
-    for (; i < b1; i += 512)
-        for (int64_t j = i; j < i + 16 && j < b1; ++j) c += __popc((uint32_t)bitmask[j]);
-    publish_counts(c, block_tot, warp_tot);
+    // ragged end (and unaligned bitmasks): a thread's first leftover piece may be partial, later ones are whole
+    for (; i < last; i += kThreads * 16)
+        for (int64_t j = i; j < i + 16 && j < last; ++j) c += __popc((uint32_t)bitmask[j]);
+    publish_count(c, block_tot);
 }
 
-// compress, kernel 2 (same grid as kernel 1): compact every tile of the warp's range into `values`, and the row offsets
 template <int ES>
-__global__ void __launch_bounds__(kThreads) bm_warp_scatter_kernel(const void *x, const uint8_t *bitmask, int64_t units, int64_t cols, int64_t rows,
-                                                                   const unsigned long long *block_tot, const unsigned long long *warp_tot, void *values,
-                                                                   int64_t *row_offsets, int64_t *nnz) {
-    __shared__ uint32_t stage_all[kWarps][StageWords<ES>::value];
-    uint32_t *st = stage_all[threadIdx.x >> 5];
-    const uint32_t st_addr = (uint32_t)__cvta_generic_to_shared(st);
+struct BmWindow {
+    static constexpr int kBytes = kBmTile * 8 * ES + 32;  // a tile's elements, shifted by up to 15 bytes
+};
+
+// compress, kernel 2 (same grid as kernel 1): compact every tile of the block's range into `values`, and the row offsets
+template <int ES>
+__global__ void __launch_bounds__(kThreads) bm_block_scatter_kernel(const void *x, const uint8_t *bitmask, int64_t units, FastDiv by_upr, uint32_t upr,
+                                                                    const unsigned long long *block_tot, void *values, int64_t *row_offsets,
+                                                                    int64_t *nnz) {
+    __shared__ __align__(16) unsigned char win[BmWindow<ES>::kBytes];
+    __shared__ uint32_t wt[kWarps][2], pre[kBmRows * kWarps + 1];
+    const uint32_t win_addr = (uint32_t)__cvta_generic_to_shared(win);
     int64_t first, last;
-    warp_range((units + 63) / 64, first, last);
-    const int lane = threadIdx.x & 31;
-    uint32_t mask[2] = {0, 0};
-    Raw8 raw[2];
-    // a tile's loads do not depend on the running offset: they are issued as soon as the registers of the tile
-    // before are free, i.e. before that tile's copy-out
-    const char *xw = (const char *)x + (first * 64 + lane) * (8 * ES);  // this lane's unit of the range's first tile
-    const uint8_t *mw = bitmask + first * 64 + lane;
-    auto fetch = [&](int64_t t) {
-        const uint32_t off = (uint32_t)(t - first) * 64u;  // units from the range's first tile (ranges are short)
+    block_range(units, first, last);
+    Raw8 raw[kBmRows];
+    uint32_t mask[kBmRows];
+    auto fetch = [&](int64_t base) {
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            mask[h] = 0;
-            raw[h].a = raw[h].b = make_uint4(0, 0, 0, 0);
-            if (t * 64 + 32 * h + lane < units) {
-                mask[h] = mw[off + 32 * h];
-                const char *p = xw + (size_t)(off + 32 * h) * (8 * ES);
-                if constexpr (ES == 2) raw[h].a = ld_stream(p);
-                else if constexpr (ES == 1) {
-                    const uint2 v = ld_stream8(p);
-                    raw[h].a.x = v.x;
-                    raw[h].a.y = v.y;
-                } else {
-                    raw[h].a = ld_stream(p);
-                    raw[h].b = ld_stream(p + 16);
-                }
+        for (int j = 0; j < kBmRows; ++j) {
+            const int64_t u = base + j * kThreads + threadIdx.x;
+            mask[j] = 0;
+            if (u < last) {
+                mask[j] = bitmask[u];
+                raw[j] = load_unit_raw<ES, false>(x, u);
             }
         }
     };
     if (first < last) fetch(first);  // in flight during the prologue
-    unsigned long long prefix = warp_first_value(block_tot, warp_tot, nnz);
-    // first row that starts inside this warp's range (32-bit division when the element index fits)
-    const int64_t e_first = first * kWarpTile + cols - 1;
-    int64_t r_next = (units < 0x10000000 && cols < 0x7FFFFFFF) ? (int64_t)((uint32_t)e_first / (uint32_t)cols) : e_first / cols;
-    int64_t e_next = r_next * cols;
-    for (int64_t tile = first; tile < last; ++tile) {
-        int excl[2], total;
-        warp_excl_scan2(__popc(mask[0]), __popc(mask[1]), excl[0], excl[1], total);
+    unsigned long long prefix = block_first_value(block_tot, nnz);
+    for (int64_t base = first; base < last; base += kBmTile) {
+        uint32_t c[kBmRows], excl[kBmRows], total;
+#pragma unroll
+        for (int j = 0; j < kBmRows; ++j) c[j] = __popc(mask[j]);
+        tile_scan(c, excl, total, wt, pre);
         char *dst = (char *)values + prefix * ES;
-        const int shift = (int)(reinterpret_cast<uintptr_t>(dst) & 3u);  // the window mirrors the destination's alignment
+        const uint32_t shift = (uint32_t)(reinterpret_cast<uintptr_t>(dst) & 15u);  // the window mirrors the destination's alignment
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
+        for (int j = 0; j < kBmRows; ++j) {
+            if (mask[j] == 0) continue;
             uint32_t b[8];
-            unit_bits<ES>(raw[h], b);
-            uint32_t sa = st_addr + (uint32_t)(shift + excl[h] * ES);
+            unit_bits<ES>(raw[j], b);
+            uint32_t sa = win_addr + shift + excl[j] * ES;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) stage_put_if<ES>(sa, b[j], mask[h] & (1u << j));
+            for (int e = 0; e < 8; ++e) stage_put_if<ES>(sa, b[e], mask[j] & (1u << e));
         }
-        if (tile + 1 < last) fetch(tile + 1);
-        // rows that begin inside this tile (cols is a multiple of 8: at the first element of one of its 64 units)
-        while (e_next < (tile + 1) * kWarpTile && r_next < rows) {  // uniform over the warp
-            const int unit = (int)(e_next - tile * kWarpTile) >> 3;
-            if (lane == (unit & 31)) row_offsets[r_next] = (int64_t)(prefix + ((unit >> 5) ? excl[1] : excl[0]));
-            ++r_next;
-            e_next += cols;
+        // rows that begin at one of this thread's units (cols is a multiple of 8, so a row starts on a unit)
+#pragma unroll
+        for (int j = 0; j < kBmRows; ++j) {
+            const int64_t u = base + j * kThreads + threadIdx.x;
+            if (u < last) {
+                const uint32_t r = fastdiv((uint32_t)u, by_upr);
+                if (r * upr == (uint32_t)u) row_offsets[r] = (int64_t)(prefix + excl[j]);
+            }
         }
-        __syncwarp();
-        const int nbytes = shift + total * ES;
-        const int first_full = shift ? 1 : 0, end_full = nbytes >> 2;  // words [first_full, end_full) are wholly this tile's
-        uint32_t *dw = reinterpret_cast<uint32_t *>(dst - shift) + first_full + lane;
-        const uint32_t *sw = st + first_full + lane;
-        for (int left = end_full - first_full; left > 0; left -= 32, dw += 32, sw += 32)  // uniform trip count
-            if (lane < left) *dw = *sw;
-        if (lane < 8) {  // the ragged head and tail share their words with the neighbouring tiles: element by element
-            const int head_end = first_full * 4 < nbytes ? first_full * 4 : nbytes;
-            const int tail0 = end_full * 4 > head_end ? end_full * 4 : head_end;
-            const int p = lane < 4 ? shift + lane * ES : tail0 + (lane - 4) * ES;
-            const int lim = lane < 4 ? head_end : nbytes;
-            if (p < lim) store_bits(values, ES, (int64_t)prefix + (p - shift) / ES, stage_load<ES>(st, p));
+        if (base + kBmTile < last) fetch(base + kBmTile);  // the next tile's loads fly while this one is copied out
+        __syncthreads();
+        // whole 16-byte words of the window that belong to this tile alone, then the ragged head and tail by element
+        const uint32_t nbytes = shift + total * ES;
+        const uint32_t first_full = shift ? 1u : 0u, end_full = nbytes >> 4;
+        char *dst0 = dst - shift;
+        for (uint32_t wv = first_full + threadIdx.x; wv < end_full; wv += kThreads)
+            *reinterpret_cast<uint4 *>(dst0 + 16 * wv) = *reinterpret_cast<const uint4 *>(win + 16 * wv);
+        {
+            const uint32_t head_end = min(16u * first_full, nbytes);
+            const uint32_t tail0 = max(16u * end_full, head_end);
+            const uint32_t per = 16 / ES;  // elements in one 16-byte word
+            if (threadIdx.x < per) {
+                const uint32_t p = shift + threadIdx.x * ES;
+                if (p < head_end) store_bits(values, ES, (int64_t)prefix + threadIdx.x, load_bits(win, ES, p / ES));
+            } else if (threadIdx.x >= 32 && threadIdx.x < 32 + per) {
+                const uint32_t p = tail0 + (threadIdx.x - 32) * ES;
+                if (p < nbytes) store_bits(values, ES, (int64_t)prefix + (p - shift) / ES, load_bits(win, ES, p / ES));
+            }
         }
-        prefix += (unsigned long long)total;
-        __syncwarp();  // the window is reused by the next tile
+        prefix += total;
+        __syncthreads();  // the window is reused by the next tile
     }
 }
 
-// decompress, kernel 2 (same grid as kernel 1): every tile's kept values are one contiguous run of `values`; bring
-// it in as whole 32-bit words, then every lane rebuilds its two units from the window
+// decompress, kernel 2 (same grid as kernel 1): every tile's kept values are one contiguous run of `values`: bring it
+// into the window (whole 16-byte words that lie inside the run, its ragged ends by element, so nothing outside
+// `values` is ever read), then every thread rebuilds its units from the window
 template <int ES>
-__global__ void __launch_bounds__(kThreads, ES == 4 ? 4 : 8) bm_warp_expand_kernel(const void *values, const uint8_t *bitmask, int64_t units, const unsigned long long *block_tot,
-                                                                  const unsigned long long *warp_tot, void *out, Gate gate) {
+__global__ void __launch_bounds__(kThreads) bm_block_expand_kernel(const void *values, const uint8_t *bitmask, int64_t units,
+                                                                   const unsigned long long *block_tot, void *out, Gate gate) {
     if (gate.flag != nullptr && *gate.flag != gate.value) return;
-    __shared__ uint32_t stage_all[kWarps][StageWords<ES>::value];
-    uint32_t *st = stage_all[threadIdx.x >> 5];
-    const int64_t ntiles = (units + 63) / 64;
+    __shared__ __align__(16) unsigned char win[BmWindow<ES>::kBytes];
+    __shared__ uint32_t wt[kWarps][2], pre[kBmRows * kWarps + 1];
+    const uint32_t win_addr = (uint32_t)__cvta_generic_to_shared(win);
     int64_t first, last;
-    warp_range(ntiles, first, last);
-    const int lane = threadIdx.x & 31;
-    uint32_t mask_n[2] = {0, 0};
-    auto fetch = [&](int64_t t) {
+    block_range(units, first, last);
+    uint32_t mask_n[kBmRows];
+    auto fetch = [&](int64_t base) {
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            const int64_t u = t * 64 + 32 * h + lane;
-            mask_n[h] = u < units ? (uint32_t)bitmask[u] : 0u;
+        for (int j = 0; j < kBmRows; ++j) {
+            const int64_t u = base + j * kThreads + threadIdx.x;
+            mask_n[j] = u < last ? (uint32_t)bitmask[u] : 0u;
         }
     };
-    if (first < last) fetch(first);  // in flight during the prologue
-    unsigned long long src = warp_first_value(block_tot, warp_tot, nullptr);
-    for (int64_t tile = first; tile < last; ++tile) {
-        const uint32_t mask[2] = {mask_n[0], mask_n[1]};
-        if (tile + 1 < last) fetch(tile + 1);  // one tile ahead
-        int excl[2], total;
-        warp_excl_scan2(__popc(mask[0]), __popc(mask[1]), excl[0], excl[1], total);
-        const char *a = (const char *)values + src * ES;
-        const int shift = (int)(reinterpret_cast<uintptr_t>(a) & 3u);
-        // Whole 32-bit words: the first may begin with the previous tile's bytes and the last may end with the next
-        // tile's, which are never used.  Only behind the very last tile is there no next tile: its ragged last word
-        // could run past the end of `values` and is fetched element by element.
-        const int nbytes = shift + total * ES;
-        const bool at_end = tile == ntiles - 1;
-        const int nwords = at_end ? nbytes >> 2 : (nbytes + 3) >> 2;
-        const uint32_t *a0 = reinterpret_cast<const uint32_t *>(a - shift);
-#pragma unroll 4
-        for (int w = lane; w < nwords; w += 32) st[pad_word(w)] = ld_stream4(a0 + w);
-        if (at_end && lane < 4) {
-            const int p = (nwords * 4 > shift ? nwords * 4 : shift) + lane * ES;
-            if (p < nbytes) stage_store<ES>(st, p, load_bits(values, ES, (int64_t)src + (p - shift) / ES));
-        }
-        __syncwarp();
+    if (first < last) fetch(first);
+    unsigned long long src = block_first_value(block_tot, nullptr);
+    for (int64_t base = first; base < last; base += kBmTile) {
+        uint32_t mask[kBmRows], c[kBmRows], excl[kBmRows], total;
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            const int64_t u = tile * 64 + 32 * h + lane;
-            if (u >= units) continue;
-            int o = shift + excl[h] * ES;
+        for (int j = 0; j < kBmRows; ++j) {
+            mask[j] = mask_n[j];
+            c[j] = __popc(mask[j]);
+        }
+        if (base + kBmTile < last) fetch(base + kBmTile);  // one tile ahead
+        tile_scan(c, excl, total, wt, pre);
+        const char *a = (const char *)values + src * ES;
+        const uint32_t shift = (uint32_t)(reinterpret_cast<uintptr_t>(a) & 15u);
+        const uint32_t nbytes = shift + total * ES;
+        const uint32_t first_full = shift ? 1u : 0u, end_full = nbytes >> 4;
+        const char *a0 = a - shift;
+        for (uint32_t wv = first_full + threadIdx.x; wv < end_full; wv += kThreads)
+            *reinterpret_cast<uint4 *>(win + 16 * wv) = ld_stream(a0 + 16 * wv);
+        {
+            const uint32_t head_end = min(16u * first_full, nbytes);
+            const uint32_t tail0 = max(16u * end_full, head_end);
+            const uint32_t per = 16 / ES;
+            if (threadIdx.x < per) {
+                const uint32_t p = shift + threadIdx.x * ES;
+                if (p < head_end) store_bits(win, ES, p / ES, load_bits(values, ES, (int64_t)src + threadIdx.x));
+            } else if (threadIdx.x >= 32 && threadIdx.x < 32 + per) {
+                const uint32_t p = tail0 + (threadIdx.x - 32) * ES;
+                if (p < nbytes) store_bits(win, ES, p / ES, load_bits(values, ES, (int64_t)src + (p - shift) / ES));
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int j = 0; j < kBmRows; ++j) {
+            const int64_t u = base + j * kThreads + threadIdx.x;
+            if (u >= last) continue;
+            uint32_t sa = win_addr + shift + excl[j] * ES;
             uint32_t b[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                b[j] = 0u;
-                if ((mask[h] >> j) & 1) {
-                    b[j] = stage_load<ES>(st, o);
-                    o += ES;
-                }
-            }
+            for (int e = 0; e < 8; ++e) b[e] = stage_get_if<ES>(sa, mask[j] & (1u << e));
             char *q = (char *)out + u * 8 * ES;
             if constexpr (ES == 2) st_stream(q, make_uint4(b[0] | (b[1] << 16), b[2] | (b[3] << 16), b[4] | (b[5] << 16), b[6] | (b[7] << 16)));
             else if constexpr (ES == 1) st_stream8(q, make_uint2(b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24), b[4] | (b[5] << 8) | (b[6] << 16) | (b[7] << 24)));
@@ -930,8 +950,8 @@ __global__ void __launch_bounds__(kThreads, ES == 4 ? 4 : 8) bm_warp_expand_kern
                 st_stream(q + 16, make_uint4(b[4], b[5], b[6], b[7]));
             }
         }
-        src += (unsigned long long)total;
-        __syncwarp();  // the window is reused by the next tile
+        src += total;
+        __syncthreads();  // the window is reused by the next tile
     }
 }
 
@@ -992,15 +1012,18 @@ extern "C" int ctb_sparse24_compress(const void *x, int32_t dtype, int64_t rows,
 }
 
 static int64_t tile_bytes() {
-    return 8 * (int64_t)kTileMaxGrid * (1 + kWarps);  // one count per block, then one per warp
+    return 8 * (int64_t)kTileMaxGrid;  // one count per block
 }
 // the 2:4 decompress keeps its "bitmask is irregular" flag behind whichever scratch layout is used
 static int64_t flag_offset(int64_t rows) {
     const int64_t a = tile_bytes(), b = rows * 8;
     return a > b ? a : b;
 }
-static int tile_grid(int64_t units, int blocks_per_sm = 8) {
-    const int g = grid_for(units * 8, (int64_t)kWarpTile * kWarps, blocks_per_sm);
+// Blocks of the two-kernel tile codec: both kernels must see the same grid, it defines the ranges.  A range is a whole
+// number of rows of kThreads units; a handful of resident blocks per SM keeps enough loads in flight for the
+// streaming kernel and enough warps for the placement kernel.
+static int tile_grid(int64_t units, int blocks_per_sm = 4) {
+    const int g = grid_for(units, kThreads, blocks_per_sm);
     return g < kTileMaxGrid ? g : kTileMaxGrid;
 }
 
@@ -1017,20 +1040,22 @@ static int compress_impl(const void *x, const uint8_t *pred, int32_t dtype, int6
         return CTB_OK;
     }
     const bool vec = !pred && cols % 8 == 0 && aligned16(x);
-    if (vec && workspace != nullptr && (reinterpret_cast<uintptr_t>(values) & 3u) == 0 && (reinterpret_cast<uintptr_t>(bitmask) & 1u) == 0) {
-        // warp tiles: count, then scatter (both kernels must see the same grid: it defines the tile ranges)
-        unsigned long long *block_tot = static_cast<unsigned long long *>(workspace), *warp_tot = block_tot + kTileMaxGrid;
+    if (vec && workspace != nullptr && (reinterpret_cast<uintptr_t>(values) & 3u) == 0 && rows * cols / 8 < (1LL << 31)) {
+        // block tiles: count, then scatter (both kernels must see the same grid: it defines the ranges)
+        unsigned long long *block_tot = static_cast<unsigned long long *>(workspace);
         const int64_t units = rows * cols / 8;
+        const uint32_t upr = (uint32_t)(cols / 8);  // units per row
+        const FastDiv by_upr = make_fastdiv(upr);
         const int g1 = tile_grid(units);
         int rc;
-        if (e.esize == 2) bm_warp_count_kernel<2><<<g1, kThreads, 0, st>>>(x, e.nz_mask, units, bitmask, block_tot, warp_tot);
-        else if (e.esize == 1) bm_warp_count_kernel<1><<<g1, kThreads, 0, st>>>(x, e.nz_mask, units, bitmask, block_tot, warp_tot);
-        else bm_warp_count_kernel<4><<<g1, kThreads, 0, st>>>(x, e.nz_mask, units, bitmask, block_tot, warp_tot);
-        if ((rc = after_launch("bm_warp_count_kernel"))) return rc;
-        if (e.esize == 2) bm_warp_scatter_kernel<2><<<g1, kThreads, 0, st>>>(x, bitmask, units, cols, rows, block_tot, warp_tot, values, row_offsets, nnz);
-        else if (e.esize == 1) bm_warp_scatter_kernel<1><<<g1, kThreads, 0, st>>>(x, bitmask, units, cols, rows, block_tot, warp_tot, values, row_offsets, nnz);
-        else bm_warp_scatter_kernel<4><<<g1, kThreads, 0, st>>>(x, bitmask, units, cols, rows, block_tot, warp_tot, values, row_offsets, nnz);
-        return after_launch("bm_warp_scatter_kernel");
+        if (e.esize == 2) bm_block_count_kernel<2><<<g1, kThreads, 0, st>>>(x, e.nz_mask, units, bitmask, block_tot);
+        else if (e.esize == 1) bm_block_count_kernel<1><<<g1, kThreads, 0, st>>>(x, e.nz_mask, units, bitmask, block_tot);
+        else bm_block_count_kernel<4><<<g1, kThreads, 0, st>>>(x, e.nz_mask, units, bitmask, block_tot);
+        if ((rc = after_launch("bm_block_count_kernel"))) return rc;
+        if (e.esize == 2) bm_block_scatter_kernel<2><<<g1, kThreads, 0, st>>>(x, bitmask, units, by_upr, upr, block_tot, values, row_offsets, nnz);
+        else if (e.esize == 1) bm_block_scatter_kernel<1><<<g1, kThreads, 0, st>>>(x, bitmask, units, by_upr, upr, block_tot, values, row_offsets, nnz);
+        else bm_block_scatter_kernel<4><<<g1, kThreads, 0, st>>>(x, bitmask, units, by_upr, upr, block_tot, values, row_offsets, nnz);
+        return after_launch("bm_block_scatter_kernel");
     }
     int grid = grid_for(rows, 1, 8);
     int rc;
@@ -1070,20 +1095,19 @@ static int decompress_impl(const void *values, const uint8_t *bitmask, int32_t d
     if (rows <= 0 || cols <= 0) return rows < 0 || cols < 0 ? fail(CTB_EINVAL_SHAPE, "negative shape") : CTB_OK;
     if (!values) return fail(CTB_EINVAL_NULL, "null values");
     cudaStream_t st = as_stream(stream);
-    if (tiles_ok && cols % 8 == 0 && aligned16(out) && (reinterpret_cast<uintptr_t>(values) & 3u) == 0 &&
-        (reinterpret_cast<uintptr_t>(bitmask) & 1u) == 0) {
-        unsigned long long *block_tot = static_cast<unsigned long long *>(workspace), *warp_tot = block_tot + kTileMaxGrid;
+    if (tiles_ok && cols % 8 == 0 && aligned16(out) && (reinterpret_cast<uintptr_t>(values) & 3u) == 0) {
+        unsigned long long *block_tot = static_cast<unsigned long long *>(workspace);
         const int64_t units = rows * cols / 8;
-        // both kernels must see the same grid: it defines the tile ranges.  As the gated fallback of the 2:4
+        // both kernels must see the same grid: it defines the ranges.  As the gated fallback of the 2:4
         // expansion the launches almost always return at once: keep them small.
-        const int g1 = tile_grid(units, gate.flag ? 1 : 8);
-        bm_warp_popcount_kernel<<<g1, kThreads, 0, st>>>(bitmask, units, block_tot, warp_tot, gate);
-        int rc0 = after_launch("bm_warp_popcount_kernel");
+        const int g1 = tile_grid(units, gate.flag ? 1 : 4);
+        bm_block_popcount_kernel<<<g1, kThreads, 0, st>>>(bitmask, units, block_tot, gate);
+        int rc0 = after_launch("bm_block_popcount_kernel");
         if (rc0) return rc0;
-        if (e.esize == 2) bm_warp_expand_kernel<2><<<g1, kThreads, 0, st>>>(values, bitmask, units, block_tot, warp_tot, out, gate);
-        else if (e.esize == 1) bm_warp_expand_kernel<1><<<g1, kThreads, 0, st>>>(values, bitmask, units, block_tot, warp_tot, out, gate);
-        else bm_warp_expand_kernel<4><<<g1, kThreads, 0, st>>>(values, bitmask, units, block_tot, warp_tot, out, gate);
-        return after_launch("bm_warp_expand_kernel");
+        if (e.esize == 2) bm_block_expand_kernel<2><<<g1, kThreads, 0, st>>>(values, bitmask, units, block_tot, out, gate);
+        else if (e.esize == 1) bm_block_expand_kernel<1><<<g1, kThreads, 0, st>>>(values, bitmask, units, block_tot, out, gate);
+        else bm_block_expand_kernel<4><<<g1, kThreads, 0, st>>>(values, bitmask, units, block_tot, out, gate);
+        return after_launch("bm_block_expand_kernel");
     }
     int64_t *offs = (int64_t *)workspace;
     int grid = grid_for(rows, 1, 8);

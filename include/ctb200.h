@@ -279,8 +279,9 @@ typedef struct ctb_tensor_ref {
 } ctb_tensor_ref;
 
 /* ctb_absmax_quantize(hadamard_n = 128, group 128, PACK32) for every tensor of the table. */
-/* device_status (device int32, may be NULL) receives CTB_ETIMEOUT if a bounded wait inside the tensor-core
- * kernel gives up; it is left untouched otherwise. */
+/* device_status (int32 the device can write: device memory, or page-locked host memory, which the host can then
+ * read without a copy; may be NULL) receives CTB_ETIMEOUT if a bounded wait inside the tensor-core kernel gives up;
+ * it is left untouched otherwise. */
 int ctb_rotate_quantize_int4_batch(const ctb_tensor_ref *tensors, int32_t count, const int8_t *signs,
                                    int32_t precision, int32_t *device_status, void *stream);
 /* The CTB_ROT_TENSOR form of the call above with the bound of its device-side waits given by the caller
@@ -297,6 +298,14 @@ int ctb_rotate_quantize_int4_batch_bounded(const ctb_tensor_ref *tensors, int32_
 int ctb_quantize_pack_int4_batch(const ctb_tensor_ref *tensors, int32_t count, void *stream);
 /* ctb_dequantize(codec PACK32, num_bits 4, group 128, bf16 scale, no zero point) for every tensor. */
 int ctb_unpack_dequantize_int4_batch(const ctb_tensor_ref *tensors, int32_t count, void *stream);
+
+/* ---- staging memory of the host <-> device pipeline ------------------------------------------------------
+ * The reference keeps a state dict in ordinary host memory and never leaves the CPU
+ * (compressors/quantized_compressors/base.py:74, :125 compression_device="cpu").  Here host-resident tensors are
+ * streamed through the GPU, which needs page-locked buffers on the host side; these two calls allocate and free
+ * them (cudaHostAlloc, portable) so that the caller can pool them.  No counterpart in the reference. */
+int ctb_pinned_alloc(int64_t nbytes, void **out);
+int ctb_pinned_free(void *ptr);
 
 #ifdef __cplusplus
 }

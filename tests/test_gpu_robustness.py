@@ -52,17 +52,27 @@ def test_tensor_core_kernel_wait_runs_out_and_returns():
 
 
 def test_engine_reports_a_device_timeout():
-    """CodecEngine turns the status word of a launch into TimeoutError at its next synchronisation point."""
+    """The engine hands the kernel a status word in page-locked host memory (no copy is needed to read it) and turns
+    CTB_ETIMEOUT into TimeoutError at its next synchronisation point.  Driven end to end: the kernel itself writes the
+    word when its wait runs out."""
+    from compressed_tensors_b200 import ops
     from compressed_tensors_b200.compressors.model_compressors.engine import CodecEngine
 
     eng = CodecEngine()
     dev = torch.device("cuda", 0)
-    eng._status_word(dev).fill_(5)
-    eng._watch_status(dev)
+    word = eng._status_word(dev)
+    assert word.is_pinned() and not word.is_cuda
+    sg = signs128(3).cuda()
+    w = weights(128, 128, 72).cuda()
+    packed = torch.empty((128, 16), dtype=torch.int32, device=dev)
+    scale = torch.empty((128, 1), dtype=torch.bfloat16, device=dev)
+    table = ops.tensor_table([w], [packed], [scale], [(128, 128)])
+    ops.rotate_quantize_int4_batch_bounded(table, sg, word, spin_cycles=2_000_000, skip_tile=0, device=dev)
+    torch.cuda.synchronize()
+    assert int(word[0]) == 5
     with pytest.raises(TimeoutError):
         eng.finish()
-    eng._watch_status(dev)  # the word was cleared
-    eng.finish()
+    eng.finish()  # the word was cleared
 
 
 def test_sparse24_decompress_short_values_take_the_generic_kernels():
