@@ -589,9 +589,10 @@ __device__ __forceinline__ float amax_of_pair(__nv_bfloat162 m) {
 // maximum stays in packed bf16 registers and the scale is computed once per 64 elements of a lane.
 __global__ void __launch_bounds__(kThreads) absmax_quant_g128_int4_kernel(const void *x, void *out, void *scale, int64_t ngroups) {
     const int h = threadIdx.x & 1;
-    const int64_t pairs = (int64_t)gridDim.x * (kThreads / 2);
+    const int ppb = blockDim.x >> 1;  // pairs per block
+    const int64_t pairs = (int64_t)gridDim.x * ppb;
     const int64_t padded = (ngroups + 15) & ~(int64_t)15;  // whole warps stay in the loop for the shuffles
-    for (int64_t g = (int64_t)blockIdx.x * (kThreads / 2) + (threadIdx.x >> 1); g < padded; g += pairs) {
+    for (int64_t g = (int64_t)blockIdx.x * ppb + (threadIdx.x >> 1); g < padded; g += pairs) {
         const bool live = g < ngroups;
         uint4 raw[8];
 #pragma unroll
@@ -785,8 +786,9 @@ __global__ void __launch_bounds__(kThreads) absmax_quant_warprow_kernel(const HA
     constexpr int M = XF == F_BF16 ? CTB_BF16 : XF == F_F16 ? CTB_F16 : CTB_F32;
     const int lane = threadIdx.x & 31;
     const float r_half = __frcp_rn(a.half_range);
-    const int64_t warps = (int64_t)gridDim.x * (kThreads / 32);
-    for (int64_t r = (int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5); r < rows; r += warps) {
+    const int wpb = blockDim.x >> 5;  // launched with 128 or 256 threads: the block is only a bundle of independent warps
+    const int64_t warps = (int64_t)gridDim.x * wpb;
+    for (int64_t r = (int64_t)blockIdx.x * wpb + (threadIdx.x >> 5); r < rows; r += warps) {
         Raw8 raw[CPL];
 #pragma unroll
         for (int k = 0; k < CPL; ++k) {
@@ -1092,7 +1094,10 @@ extern "C" int ctb_absmax_quantize(const ctb_qdesc *d, const void *x, const floa
     }
     if (fout == F_PACK4 && d->col_group == 128 && d->scale_row_stride == d->cols / 128) {
         const int64_t ngroups = d->rows * d->cols / 128;
-        absmax_quant_g128_int4_kernel<<<grid_for(ngroups, kThreads / 2, 16), kThreads, 0, st>>>(x, out, out_scale, ngroups);
+        // 128-thread blocks, eight per SM, striding over the groups: measured 8.9 us on 4096 x 4096 against 9.2 us for one
+        // wave and a partial second wave of 256-thread blocks
+        const int gthreads = 128;
+        absmax_quant_g128_int4_kernel<<<grid_for(ngroups, gthreads / 2, 8), gthreads, 0, st>>>(x, out, out_scale, ngroups);
         return after_launch("absmax_quant_g128_int4_kernel");
     }
     if (fout == F_FP4X2 && d->col_group == 16 && d->scale_row_stride == d->cols / 16) {
@@ -1119,12 +1124,15 @@ extern "C" int ctb_absmax_quantize(const ctb_qdesc *d, const void *x, const floa
     if (d->col_group == d->cols && d->scale_row_stride == 1 && qk != QK_FP4) {
         const int64_t cpr = d->cols / 8;
         if (cpr <= 32 * 32 && (fout == F_E4M3 || fout == F_I8 || fout == F_BF16)) {
-            int wgrid = grid_for(d->rows, kThreads / 32, cpr <= 512 ? 4 : 2);
+            // blocks of four warps: a block is only a bundle of independent rows, and small bundles spread a few thousand
+            // rows evenly over the SMs (4096 rows in blocks of eight left every seventh SM with an extra block: 11.9 -> 10.9 us)
+            const int wthreads = 128, wbps = cpr <= 512 ? 4 : 2;
+            int wgrid = grid_for(d->rows, wthreads / 32, wbps);
 #define CTB_WR(CPL_)                                                                                                              \
-    if (fout == F_E4M3) absmax_quant_warprow_kernel<CPL_, F_BF16, QK_FP8, F_E4M3><<<wgrid, kThreads, 0, st>>>(a, d->rows, (int)cpr); \
-    else if (fout == F_I8) absmax_quant_warprow_kernel<CPL_, F_BF16, QK_INT, F_I8><<<wgrid, kThreads, 0, st>>>(a, d->rows, (int)cpr); \
-    else if (qk == QK_FP8) absmax_quant_warprow_kernel<CPL_, F_BF16, QK_FP8, F_BF16><<<wgrid, kThreads, 0, st>>>(a, d->rows, (int)cpr); \
-    else absmax_quant_warprow_kernel<CPL_, F_BF16, QK_INT, F_BF16><<<wgrid, kThreads, 0, st>>>(a, d->rows, (int)cpr);
+    if (fout == F_E4M3) absmax_quant_warprow_kernel<CPL_, F_BF16, QK_FP8, F_E4M3><<<wgrid, wthreads, 0, st>>>(a, d->rows, (int)cpr); \
+    else if (fout == F_I8) absmax_quant_warprow_kernel<CPL_, F_BF16, QK_INT, F_I8><<<wgrid, wthreads, 0, st>>>(a, d->rows, (int)cpr); \
+    else if (qk == QK_FP8) absmax_quant_warprow_kernel<CPL_, F_BF16, QK_FP8, F_BF16><<<wgrid, wthreads, 0, st>>>(a, d->rows, (int)cpr); \
+    else absmax_quant_warprow_kernel<CPL_, F_BF16, QK_INT, F_BF16><<<wgrid, wthreads, 0, st>>>(a, d->rows, (int)cpr);
             if (cpr <= 128) { CTB_WR(4) } else if (cpr <= 256) { CTB_WR(8) } else if (cpr <= 512) { CTB_WR(16) } else { CTB_WR(32) }
             return after_launch("absmax_quant_warprow_kernel");
         }

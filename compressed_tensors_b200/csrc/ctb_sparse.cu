@@ -590,7 +590,7 @@ __device__ __forceinline__ void stage_put_if(uint32_t &saddr, uint32_t v, uint32
     if constexpr (ES == 1)
         asm volatile("{ .reg .pred p; setp.ne.u32 p, %2, 0; @p st.shared.u8 [%0], %1; @p add.u32 %0, %0, 1; }" : "+r"(saddr) : "r"(v), "r"(bit) : "memory");
     else if constexpr (ES == 2)
-        asm volatile("{ .reg .pred p; setp.ne.u32 p, %2, 0; @p st.shared.u16 [%0], %1; @p add.u32 %0, %0, 2; }" : "+r"(saddr) : "h"((unsigned short)v), "r"(bit) : "memory");
+        asm volatile("{ .reg .pred p; setp.ne.u32 p, %2, 0; @p st.shared.u16 [%0], %1; @p add.u32 %0, %0, 2; }" : "+r"(saddr) : "r"(v), "r"(bit) : "memory");  // the low half of v
     else
         asm volatile("{ .reg .pred p; setp.ne.u32 p, %2, 0; @p st.shared.u32 [%0], %1; @p add.u32 %0, %0, 4; }" : "+r"(saddr) : "r"(v), "r"(bit) : "memory");
 }
@@ -763,17 +763,18 @@ __global__ void __launch_bounds__(kThreads) bm_block_count_kernel(const void *x,
     int64_t first, last;
     block_range(units, first, last);
     uint32_t cnt = 0;
-    for (int64_t base = first; base < last; base += kBmTile) {
-        Raw8 raw[kBmRows];
-        bool ok[kBmRows];
+    constexpr int DEPTH = 4;  // units in flight per thread
+    for (int64_t base = first; base < last; base += DEPTH * kThreads) {
+        Raw8 raw[DEPTH];
+        bool ok[DEPTH];
 #pragma unroll
-        for (int j = 0; j < kBmRows; ++j) {  // all loads of the tile first
+        for (int j = 0; j < DEPTH; ++j) {  // all loads first
             const int64_t u = base + j * kThreads + threadIdx.x;
             ok[j] = u < last;
             if (ok[j]) raw[j] = load_unit_raw<ES, true>(x, u);
         }
 #pragma unroll
-        for (int j = 0; j < kBmRows; ++j) {
+        for (int j = 0; j < DEPTH; ++j) {
             if (!ok[j]) continue;
             const uint32_t m = unit_nz_mask<ES>(raw[j], nzm);
             bitmask[base + j * kThreads + threadIdx.x] = (uint8_t)m;
@@ -810,7 +811,7 @@ struct BmWindow {
 
 // compress, kernel 2 (same grid as kernel 1): compact every tile of the block's range into `values`, and the row offsets
 template <int ES>
-__global__ void __launch_bounds__(kThreads) bm_block_scatter_kernel(const void *x, const uint8_t *bitmask, int64_t units, FastDiv by_upr, uint32_t upr,
+__global__ void __launch_bounds__(kThreads, ES == 4 ? 4 : 6) bm_block_scatter_kernel(const void *x, const uint8_t *bitmask, int64_t units, FastDiv by_upr, uint32_t upr,
                                                                     const unsigned long long *block_tot, void *values, int64_t *row_offsets,
                                                                     int64_t *nnz) {
     __shared__ __align__(16) unsigned char win[BmWindow<ES>::kBytes];
@@ -887,7 +888,7 @@ __global__ void __launch_bounds__(kThreads) bm_block_scatter_kernel(const void *
 // into the window (whole 16-byte words that lie inside the run, its ragged ends by element, so nothing outside
 // `values` is ever read), then every thread rebuilds its units from the window
 template <int ES>
-__global__ void __launch_bounds__(kThreads) bm_block_expand_kernel(const void *values, const uint8_t *bitmask, int64_t units,
+__global__ void __launch_bounds__(kThreads, ES == 4 ? 4 : 6) bm_block_expand_kernel(const void *values, const uint8_t *bitmask, int64_t units,
                                                                    const unsigned long long *block_tot, void *out, Gate gate) {
     if (gate.flag != nullptr && *gate.flag != gate.value) return;
     __shared__ __align__(16) unsigned char win[BmWindow<ES>::kBytes];
@@ -955,6 +956,360 @@ __global__ void __launch_bounds__(kThreads) bm_block_expand_kernel(const void *v
     }
 }
 
+// ------------------------------------------------------------------ single-pass bitmask compress
+//
+// One cooperative kernel that reads the dense tensor from HBM exactly once.  The flat tensor is cut into tiles of
+// kFzThreads * ITEMS * 4 elements (16 KiB of 16-bit data); tile T belongs to block T % gridDim.x, so the tiles a
+// block works on at the same time as its neighbours (one "slab" of gridDim.x tiles) are adjacent in memory.
+//   * thread 0 of a block keeps kFzStages bulk copies (cp.async.bulk, completion on an mbarrier) in flight: the
+//     tiles after the current one stream into shared memory while it is worked on, and nothing is read twice;
+//   * every thread owns ITEMS runs of 4 elements of the tile (thread t the runs t, t + 256, ...: neighbouring
+//     lanes place their kept elements about 4 bytes apart, which keeps the placement free of bank conflicts);
+//     masks and counts come straight from shared memory, one block-wide scan orders them;
+//   * an iteration first COUNTS the block's next tile and publishes that count, then PLACES the current one, so a count
+//     is out a whole iteration before anyone needs it and no block runs in lockstep with another; the count goes out as (ticket, count) in one 64-bit word of the scratch (the 48-bit ticket of
+//     the call makes a stale or uninitialised word recognisable, so the scratch never needs clearing); the block then
+//     needs the counts of every tile before its own: all tiles of the slab before (read once per slab by the whole
+//     block) and the lower-numbered tiles of this slab.  Counts do not depend on anyone else's offsets, so
+//     there is no chain to wait along: a block only ever waits for other blocks to have COUNTED;
+//   * kept elements go through a shared-memory window that mirrors the 16-byte alignment of their place in
+//     `values` and leave as whole 16-byte words.
+// All blocks must be resident at once (a block waits for counts of higher-numbered blocks of the slab before),
+// hence the cooperative launch.  Every wait is bounded; on expiry the kernel stores -1 in *nnz and returns.
+constexpr int kFzThreads = 256;
+constexpr int kFzWarps = kFzThreads / 32;
+constexpr int kFzStages = 3;
+constexpr int kFzMaxTiles = 16384;  // count words in the scratch
+constexpr long long kFzSpinCycles = 2000000000LL;
+
+template <int ES>
+struct Fz {
+    static constexpr int kItems = ES == 4 ? 4 : 8;               // runs of 4 elements per thread and tile
+    static constexpr int kTileElems = kFzThreads * kItems * 4;   // 8192 (4096 for 32-bit elements)
+    static constexpr int kTileBytes = kTileElems * ES;           // 16 KiB (8 KiB for 8-bit elements)
+    static constexpr int kWindowBytes = kTileBytes + 32;
+    static constexpr int kSmemBytes = kFzStages * kTileBytes + kWindowBytes + 128 /*barriers*/ + 16 /*alignment*/;
+};
+
+__device__ __forceinline__ uint32_t fz_smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ bool fz_mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// bounded wait: false when the budget ran out
+__device__ __forceinline__ bool fz_mbar_wait(uint32_t bar, uint32_t parity) {
+    if (fz_mbar_try(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!fz_mbar_try(bar, parity))
+        if (clock64() - t0 > kFzSpinCycles) return false;
+    return true;
+}
+__device__ __forceinline__ void fz_bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void fz_publish(unsigned long long *flag, unsigned long long v) {
+    asm volatile("st.global.release.gpu.u64 [%0], %1;" ::"l"(flag), "l"(v) : "memory");
+}
+// the count another block published for this ticket; bounded, false on expiry
+__device__ __forceinline__ bool fz_await(const unsigned long long *flag, unsigned long long ticket, unsigned long long &count) {
+    const long long t0 = clock64();
+    for (;;) {
+        unsigned long long v;
+        asm volatile("ld.global.acquire.gpu.u64 %0, [%1];" : "=l"(v) : "l"(flag) : "memory");
+        if ((v >> 16) == ticket) {  // a tile keeps at most 8192 elements: 16 bits of count, 48 bits of ticket
+            count = v & 0xFFFFull;
+            return true;
+        }
+        if (clock64() - t0 > kFzSpinCycles) return false;
+        __nanosleep(32);
+    }
+}
+
+// 4-bit non-zero mask of a run of 4 elements at `p` in shared memory
+template <int ES>
+__device__ __forceinline__ uint32_t fz_run_mask(const unsigned char *p, uint32_t nzm) {
+    if constexpr (ES == 2) {
+        const uint2 v = *reinterpret_cast<const uint2 *>(p);
+        const uint32_t k = 0x7FFF7FFFu;
+        return top_bits_to_high_nibble(prmt_b32((v.x & k) + k, (v.y & k) + k, 0x7531)) >> 28;
+    } else if constexpr (ES == 1) {
+        const uint32_t v = *reinterpret_cast<const uint32_t *>(p);
+        uint32_t t0 = (v & 0x7F7F7F7Fu) + 0x7F7F7F7Fu;
+        if (nzm & 0x80u) t0 |= v;
+        return top_bits_to_high_nibble(t0) >> 28;
+    } else {
+        const uint4 v = *reinterpret_cast<const uint4 *>(p);
+        return ((v.x & nzm) != 0 ? 1u : 0u) | ((v.y & nzm) != 0 ? 2u : 0u) | ((v.z & nzm) != 0 ? 4u : 0u) | ((v.w & nzm) != 0 ? 8u : 0u);
+    }
+}
+
+template <int ES>
+__global__ void __launch_bounds__(kFzThreads, 3)
+bm_single_pass_compress_kernel(const void *x, uint32_t nzm, int64_t units, FastDiv by_upr, uint32_t upr, unsigned long long *flags,
+                               unsigned long long ticket, void *values, uint8_t *bitmask, int64_t *row_offsets, int64_t *nnz) {
+    using F = Fz<ES>;
+    constexpr int ITEMS = F::kItems;
+    extern __shared__ unsigned char fz_raw[];
+    unsigned char *base = fz_raw + ((16u - (fz_smem_u32(fz_raw) & 15u)) & 15u);
+    unsigned char *win = base + kFzStages * F::kTileBytes;
+    unsigned long long *bars = reinterpret_cast<unsigned long long *>(win + F::kWindowBytes + 8);
+    __shared__ uint32_t wt[kFzWarps][2], pre[ITEMS * kFzWarps + 1];
+    __shared__ unsigned long long red[kFzWarps][2];
+    __shared__ int failed;
+    const uint32_t win_addr = fz_smem_u32(win);
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int64_t elems = units * 8;
+    const int64_t ntiles = (elems + F::kTileElems - 1) / F::kTileElems;
+    const int64_t G = gridDim.x;
+
+    auto tile_bytes_of = [&](int64_t T) -> uint32_t {
+        const int64_t n = min((int64_t)F::kTileElems, elems - T * F::kTileElems);
+        return (uint32_t)(n * ES);
+    };
+    if (threadIdx.x == 0) {
+        failed = 0;
+        for (int i = 0; i < kFzStages; ++i)
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(fz_smem_u32(&bars[i])) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        for (int i = 0; i < kFzStages; ++i) {
+            const int64_t T = blockIdx.x + (int64_t)i * G;
+            if (T < ntiles) fz_bulk_load(fz_smem_u32(base + i * F::kTileBytes), (const char *)x + T * F::kTileBytes, tile_bytes_of(T), fz_smem_u32(&bars[i]));
+        }
+    }
+    __syncthreads();
+
+    // What the counting half of an iteration leaves for the placing half of the next one.
+    struct Counted {
+        uint32_t masks;        // the run masks of this thread, 4 bits per run
+        uint32_t excl[ITEMS];  // exclusive prefixes of its runs within the tile
+        uint32_t total;        // kept elements of the tile
+    };
+    // ---- count tile number `it` of this block (masks, bitmask bytes, block-wide scan) and publish its count
+    auto count_tile = [&](int64_t it, int64_t T, Counted &out) {
+        const int sidx = (int)(it % kFzStages);
+        if (!fz_mbar_wait(fz_smem_u32(&bars[sidx]), (uint32_t)((it / kFzStages) & 1))) failed = 1;  // benign race: every writer stores 1
+        const unsigned char *src = base + sidx * F::kTileBytes;
+        const uint32_t tile_elems = tile_bytes_of(T) / ES;
+        uint32_t c[ITEMS], mine = 0;
+#pragma unroll
+        for (int j = 0; j < ITEMS; ++j) {
+            const uint32_t r = j * kFzThreads + threadIdx.x;  // run index in tile order
+            // tiles are whole units of 8 elements: a run is inside or outside as a whole
+            const uint32_t m = r * 4 < tile_elems ? fz_run_mask<ES>(src + r * 4 * ES, nzm) : 0u;
+            c[j] = __popc(m);
+            mine |= m << (4 * j);
+        }
+        out.masks = mine;
+        // bitmask bytes: a unit is the pair of runs of an even lane and its odd neighbour; the even lane writes the bytes of
+        // the first half of the rows, the odd lane those of the second half
+        {
+            const uint32_t other = __shfl_xor_sync(0xFFFFFFFFu, mine, 1);
+            const uint32_t lo = (lane & 1) ? other : mine, hi = (lane & 1) ? mine : other;
+#pragma unroll
+            for (int jj = 0; jj < ITEMS / 2; ++jj) {
+                const int j = jj + ((lane & 1) ? ITEMS / 2 : 0);
+                const uint32_t r = j * kFzThreads + (threadIdx.x & ~1u);
+                if (r * 4 < tile_elems) bitmask[T * (F::kTileElems / 8) + (r >> 1)] = (uint8_t)(((lo >> (4 * j)) & 15u) | (((hi >> (4 * j)) & 15u) << 4));
+            }
+        }
+        // block-wide exclusive scan in tile order (row j before row j + 1, threads in order inside a row)
+        uint32_t p0 = 0, p1 = 0;  // byte fields: a warp's sum of one row is at most 128
+#pragma unroll
+        for (int j = 0; j < ITEMS && j < 4; ++j) p0 |= c[j] << (8 * j);
+#pragma unroll
+        for (int j = 4; j < ITEMS; ++j) p1 |= c[j] << (8 * (j - 4));
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t a = __shfl_up_sync(0xFFFFFFFFu, p0, o), b = __shfl_up_sync(0xFFFFFFFFu, p1, o);
+            if (lane >= o) {
+                p0 += a;
+                p1 += b;
+            }
+        }
+        if (lane == 31) {
+            wt[w][0] = p0;
+            wt[w][1] = p1;
+        }
+        __syncthreads();
+        if (w == 0) {
+            // ITEMS * kFzWarps (row, warp) totals in tile order, PER consecutive ones per lane
+            constexpr int PER = ITEMS * kFzWarps / 32;
+            static_assert(PER >= 1 && PER * 32 == ITEMS * kFzWarps, "one warp covers the (row, warp) totals");
+            uint32_t v[PER], sum = 0;
+#pragma unroll
+            for (int q = 0; q < PER; ++q) {
+                const int e = lane * PER + q, j = e / kFzWarps, ww = e % kFzWarps;
+                v[q] = (wt[ww][j >> 2] >> (8 * (j & 3))) & 0xFFu;
+                sum += v[q];
+            }
+            uint32_t inc = sum;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t a = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+                if (lane >= o) inc += a;
+            }
+            uint32_t run = inc - sum;
+#pragma unroll
+            for (int q = 0; q < PER; ++q) {
+                pre[lane * PER + q] = run;
+                run += v[q];
+            }
+            if (lane == 31) {
+                pre[ITEMS * kFzWarps] = inc;
+                // other blocks wait for counts only: out it goes, a whole iteration before this block places the tile
+                fz_publish(&flags[T], (ticket << 16) | (unsigned long long)inc);
+            }
+        }
+        __syncthreads();
+        out.total = pre[ITEMS * kFzWarps];
+#pragma unroll
+        for (int j = 0; j < ITEMS; ++j) {
+            const uint32_t incl = ((j < 4 ? p0 : p1) >> (8 * (j & 3))) & 0xFFu;
+            out.excl[j] = pre[j * kFzWarps + w] + incl - c[j];
+        }
+        __syncthreads();  // `pre` and `wt` are free again (the next scan may start before everyone has read them otherwise)
+    };
+
+    unsigned long long before_slab = 0;  // kept elements in all slabs before the current one (block-uniform)
+    Counted cur, nxt;
+    int64_t it = 0;
+    if ((int64_t)blockIdx.x < ntiles) count_tile(0, blockIdx.x, cur);
+    for (int64_t T = blockIdx.x; T < ntiles; T += G, ++it) {
+        const bool more = T + G < ntiles;
+        if (more) count_tile(it + 1, T + G, nxt);  // published one iteration ahead: nobody runs in lockstep
+        const int sidx = (int)(it % kFzStages);
+        const unsigned char *src = base + sidx * F::kTileBytes;
+        const uint32_t tile_elems = tile_bytes_of(T) / ES;
+        // ---- kept elements before this tile: every tile of the slab before (all blocks), lower tiles of this slab
+        {
+            const int64_t slab0 = T - blockIdx.x;  // first tile of this slab
+            unsigned long long prev = 0, here = 0;
+            bool ok = true;
+            if (slab0 > 0)
+                for (int64_t b = threadIdx.x; b < G; b += kFzThreads) {
+                    unsigned long long cnt = 0;
+                    ok = fz_await(&flags[slab0 - G + b], ticket, cnt) && ok;
+                    prev += cnt;
+                }
+            for (int64_t b = threadIdx.x; b < (int64_t)blockIdx.x; b += kFzThreads) {
+                unsigned long long cnt = 0;
+                ok = fz_await(&flags[slab0 + b], ticket, cnt) && ok;
+                here += cnt;
+            }
+            if (!ok) failed = 1;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                prev += __shfl_xor_sync(0xFFFFFFFFu, prev, o);
+                here += __shfl_xor_sync(0xFFFFFFFFu, here, o);
+            }
+            if (lane == 0) {
+                red[w][0] = prev;
+                red[w][1] = here;
+            }
+        }
+        __syncthreads();
+        unsigned long long slab_prev = 0, slab_here = 0;
+#pragma unroll
+        for (int i = 0; i < kFzWarps; ++i) {
+            slab_prev += red[i][0];
+            slab_here += red[i][1];
+        }
+        before_slab += slab_prev;
+        const unsigned long long prefix = before_slab + slab_here;
+        if (failed) break;  // block-uniform: every write to `failed` precedes the barrier above
+        // ---- place the kept elements in the window, which mirrors the 16-byte alignment of their place in `values`
+        char *dst = (char *)values + prefix * ES;
+        const uint32_t shift = (uint32_t)(reinterpret_cast<uintptr_t>(dst) & 15u);
+#pragma unroll
+        for (int j = 0; j < ITEMS; ++j) {
+            const uint32_t m = (cur.masks >> (4 * j)) & 15u;
+            if (m == 0) continue;
+            const unsigned char *p = src + (j * kFzThreads + threadIdx.x) * 4 * ES;
+            uint32_t sa = win_addr + shift + cur.excl[j] * ES;
+            if constexpr (ES == 2) {
+                const uint2 v = *reinterpret_cast<const uint2 *>(p);
+                stage_put_if<2>(sa, v.x, m & 1u);
+                stage_put_if<2>(sa, v.x >> 16, m & 2u);
+                stage_put_if<2>(sa, v.y, m & 4u);
+                stage_put_if<2>(sa, v.y >> 16, m & 8u);
+            } else if constexpr (ES == 1) {
+                const uint32_t v = *reinterpret_cast<const uint32_t *>(p);
+                stage_put_if<1>(sa, v, m & 1u);
+                stage_put_if<1>(sa, v >> 8, m & 2u);
+                stage_put_if<1>(sa, v >> 16, m & 4u);
+                stage_put_if<1>(sa, v >> 24, m & 8u);
+            } else {
+                const uint4 v = *reinterpret_cast<const uint4 *>(p);
+                stage_put_if<4>(sa, v.x, m & 1u);
+                stage_put_if<4>(sa, v.y, m & 2u);
+                stage_put_if<4>(sa, v.z, m & 4u);
+                stage_put_if<4>(sa, v.w, m & 8u);
+            }
+        }
+        // ---- rows that begin at one of this thread's units (cols is a multiple of 8: a row starts on a unit, i.e. at
+        //      the run of an even thread)
+        if ((threadIdx.x & 1) == 0) {
+#pragma unroll
+            for (int j = 0; j < ITEMS; ++j) {
+                const uint32_t r = j * kFzThreads + threadIdx.x;
+                if (r * 4 < tile_elems) {
+                    const uint32_t u = (uint32_t)(T * (F::kTileElems / 8)) + (r >> 1);
+                    const uint32_t row = fastdiv(u, by_upr);
+                    if (row * upr == u) row_offsets[row] = (int64_t)(prefix + cur.excl[j]);
+                }
+            }
+        }
+        __syncthreads();  // the stage buffer has been read by everyone, the window is complete
+        const uint32_t total = cur.total;
+        if (threadIdx.x == 0) {
+            const int64_t Tn = T + (int64_t)kFzStages * G;  // the tile that reuses this stage buffer
+            if (Tn < ntiles) {
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic reads above, async-proxy writes below
+                fz_bulk_load(fz_smem_u32(base + sidx * F::kTileBytes), (const char *)x + Tn * F::kTileBytes, tile_bytes_of(Tn), fz_smem_u32(&bars[sidx]));
+            }
+            if (T == ntiles - 1) *nnz = (int64_t)(prefix + total);
+        }
+        // ---- the window leaves as whole 16-byte words; its ragged head and tail by element
+        {
+            const uint32_t nbytes = shift + total * ES;
+            const uint32_t first_full = shift ? 1u : 0u, end_full = nbytes >> 4;
+            char *dst0 = dst - shift;
+            for (uint32_t wv = first_full + threadIdx.x; wv < end_full; wv += kFzThreads)
+                st_stream(dst0 + 16 * wv, *reinterpret_cast<const uint4 *>(win + 16 * wv));
+            const uint32_t head_end = min(16u * first_full, nbytes);
+            const uint32_t tail0 = max(16u * end_full, head_end);
+            constexpr uint32_t per = 16 / ES;
+            if (threadIdx.x < per) {
+                const uint32_t p = shift + threadIdx.x * ES;
+                if (p < head_end) store_bits(values, ES, (int64_t)prefix + threadIdx.x, load_bits(win, ES, p / ES));
+            } else if (threadIdx.x >= 32 && threadIdx.x < 32 + per) {
+                const uint32_t p = tail0 + (threadIdx.x - 32) * ES;
+                if (p < nbytes) store_bits(values, ES, (int64_t)prefix + (p - shift) / ES, load_bits(win, ES, p / ES));
+            }
+        }
+        __syncthreads();  // the window is reused by the next tile
+        cur = nxt;
+    }
+    if (failed) {
+        // let the copies still in flight land before the block gives its shared memory back, then report
+        if (threadIdx.x == 0) {
+            for (int64_t j = it; j < it + kFzStages; ++j) {
+                const int64_t Tj = blockIdx.x + j * G;
+                if (Tj < ntiles) fz_mbar_wait(fz_smem_u32(&bars[j % kFzStages]), (uint32_t)((j / kFzStages) & 1));
+            }
+            *nnz = -1;
+        }
+    }
+}
+
 }  // namespace ctb
 
 // ------------------------------------------------------------------ entry points
@@ -1011,8 +1366,13 @@ extern "C" int ctb_sparse24_compress(const void *x, int32_t dtype, int64_t rows,
     return after_launch("sparse24_compress_simd_kernel");
 }
 
+// 1 keeps ctb_bitmask_compress on the two-kernel path (the default: on the tensor sizes of a model's weights the pair
+// is the faster of the two; the single-pass kernel reads the tensor from HBM only once and is there for tensors that do
+// not fit the L2 cache).  ctb_bitmask_force_two_kernels(0) selects the single-pass kernel where it can run.
+static std::atomic<int> g_two_kernel_bitmask{1};
+
 static int64_t tile_bytes() {
-    return 8 * (int64_t)kTileMaxGrid;  // one count per block
+    return 8 * (int64_t)kFzMaxTiles;  // one count per block of the two-kernel codec (4096) or per tile of the single-pass kernel
 }
 // the 2:4 decompress keeps its "bitmask is irregular" flag behind whichever scratch layout is used
 static int64_t flag_offset(int64_t rows) {
@@ -1022,9 +1382,51 @@ static int64_t flag_offset(int64_t rows) {
 // Blocks of the two-kernel tile codec: both kernels must see the same grid, it defines the ranges.  A range is a whole
 // number of rows of kThreads units; a handful of resident blocks per SM keeps enough loads in flight for the
 // streaming kernel and enough warps for the placement kernel.
-static int tile_grid(int64_t units, int blocks_per_sm = 4) {
+static int tile_grid(int64_t units, int blocks_per_sm = 6) {
     const int g = grid_for(units, kThreads, blocks_per_sm);
     return g < kTileMaxGrid ? g : kTileMaxGrid;
+}
+
+// The single-pass kernel, when the device can hold the whole grid at once and one count word per tile fits the
+// scratch.  *launched = false leaves the call to the two-kernel path.
+template <int ES>
+static int launch_single_pass(const void *x, const ElemInfo &e, int64_t units, uint32_t upr, unsigned long long *flags, void *values,
+                              uint8_t *bitmask, int64_t *row_offsets, int64_t *nnz, cudaStream_t st, bool *launched) {
+    using F = Fz<ES>;
+    *launched = false;
+    const int64_t ntiles = cdiv(units * 8, F::kTileElems);
+    if (ntiles > kFzMaxTiles) return CTB_OK;
+    int dev = 0, coop = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return CTB_OK;
+    static std::atomic<int> per_sm[64];  // resident blocks per SM of this instantiation on each device (0: not asked yet, -1: cannot run)
+    int occ = per_sm[dev].load(std::memory_order_acquire);
+    auto *kernel = bm_single_pass_compress_kernel<ES>;
+    if (occ == 0) {
+        occ = -1;
+        if (cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev) == cudaSuccess && coop &&
+            cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, F::kSmemBytes) == cudaSuccess) {
+            int n = 0;
+            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, kFzThreads, F::kSmemBytes) == cudaSuccess && n > 0) occ = n;
+        }
+        cudaGetLastError();  // a refusal above is not an error of this call
+        per_sm[dev].store(occ, std::memory_order_release);
+    }
+    if (occ <= 0) return CTB_OK;
+    const int64_t cap = (int64_t)occ * sm_count();
+    const int grid = (int)(ntiles < cap ? ntiles : cap);
+    static std::atomic<unsigned long long> s_ticket{0x5DEECE66Dull};
+    unsigned long long ticket = s_ticket.fetch_add(0x9E3779B97F4Aull, std::memory_order_relaxed) & ((1ull << 48) - 1);
+    FastDiv by_upr = make_fastdiv(upr);
+    uint32_t nzm = e.nz_mask;
+    void *args[] = {(void *)&x, (void *)&nzm, (void *)&units, (void *)&by_upr, (void *)&upr, (void *)&flags, (void *)&ticket,
+                    (void *)&values, (void *)&bitmask, (void *)&row_offsets, (void *)&nnz};
+    cudaError_t err = cudaLaunchCooperativeKernel((const void *)kernel, dim3(grid), dim3(kFzThreads), args, F::kSmemBytes, st);
+    if (err != cudaSuccess) {
+        cudaGetLastError();
+        return CTB_OK;  // e.g. another context holds part of the device: the two-kernel path needs no co-residency
+    }
+    *launched = true;
+    return after_launch("bm_single_pass_compress_kernel");
 }
 
 static int compress_impl(const void *x, const uint8_t *pred, int32_t dtype, int64_t rows, int64_t cols, void *values, uint8_t *bitmask,
@@ -1046,8 +1448,15 @@ static int compress_impl(const void *x, const uint8_t *pred, int32_t dtype, int6
         const int64_t units = rows * cols / 8;
         const uint32_t upr = (uint32_t)(cols / 8);  // units per row
         const FastDiv by_upr = make_fastdiv(upr);
-        const int g1 = tile_grid(units);
         int rc;
+        if (aligned16(x) && (units * 8 * e.esize) % 16 == 0 && !g_two_kernel_bitmask.load(std::memory_order_relaxed)) {
+            bool launched = false;
+            if (e.esize == 2) rc = launch_single_pass<2>(x, e, units, upr, block_tot, values, bitmask, row_offsets, nnz, st, &launched);
+            else if (e.esize == 1) rc = launch_single_pass<1>(x, e, units, upr, block_tot, values, bitmask, row_offsets, nnz, st, &launched);
+            else rc = launch_single_pass<4>(x, e, units, upr, block_tot, values, bitmask, row_offsets, nnz, st, &launched);
+            if (rc || launched) return rc;
+        }
+        const int g1 = tile_grid(units);
         if (e.esize == 2) bm_block_count_kernel<2><<<g1, kThreads, 0, st>>>(x, e.nz_mask, units, bitmask, block_tot);
         else if (e.esize == 1) bm_block_count_kernel<1><<<g1, kThreads, 0, st>>>(x, e.nz_mask, units, bitmask, block_tot);
         else bm_block_count_kernel<4><<<g1, kThreads, 0, st>>>(x, e.nz_mask, units, bitmask, block_tot);
@@ -1071,6 +1480,8 @@ static int compress_impl(const void *x, const uint8_t *pred, int32_t dtype, int6
     CTB_BM(bm_scatter_kernel, x, pred, e.esize, e.nz_mask, rows, cols, row_offsets, values)
     return after_launch("bm_scatter_kernel");
 }
+
+extern "C" void ctb_bitmask_force_two_kernels(int32_t on) { g_two_kernel_bitmask.store(on ? 1 : 0, std::memory_order_relaxed); }
 
 extern "C" int64_t ctb_bitmask_workspace_bytes(int64_t rows, int64_t cols) {
     return flag_offset(rows) + 16;
@@ -1100,7 +1511,7 @@ static int decompress_impl(const void *values, const uint8_t *bitmask, int32_t d
         const int64_t units = rows * cols / 8;
         // both kernels must see the same grid: it defines the ranges.  As the gated fallback of the 2:4
         // expansion the launches almost always return at once: keep them small.
-        const int g1 = tile_grid(units, gate.flag ? 1 : 4);
+        const int g1 = tile_grid(units, gate.flag ? 1 : 6);
         bm_block_popcount_kernel<<<g1, kThreads, 0, st>>>(bitmask, units, block_tot, gate);
         int rc0 = after_launch("bm_block_popcount_kernel");
         if (rc0) return rc0;

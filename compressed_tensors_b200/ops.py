@@ -297,7 +297,10 @@ def _masked_compress(x, mask, sync=True):
                                         ptr(row_offsets), ptr(nnz), stream_of(x)))
     if not sync:  # full-capacity values buffer and the device-side count: no host round trip
         return values, bitmask, row_offsets, nnz
-    return values[: int(nnz.item())], bitmask, row_offsets
+    count = int(nnz.item())
+    if count < 0:
+        raise TimeoutError("a bounded wait inside the single-pass bitmask kernel gave up; its outputs are incomplete")
+    return values[:count], bitmask, row_offsets
 
 
 def sparse24_compress(x):

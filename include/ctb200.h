@@ -180,6 +180,12 @@ int ctb_sparse24_compress(const void *x, int32_t dtype, int64_t rows, int64_t co
  * contiguous range of tiles, then the compaction with a running offset); NULL selects the row-by-row
  * count / scan / scatter path. */
 int64_t ctb_bitmask_workspace_bytes(int64_t rows, int64_t cols);
+/* ctb_bitmask_force_two_kernels(0) lets ctb_bitmask_compress, given a `workspace`, run tensors of up to 16384 tiles of
+ * 8192 elements on a device with cooperative launches as ONE kernel that reads x from HBM once (bulk copies into shared
+ * memory, per-tile counts exchanged through the workspace, every wait bounded; if a wait gives up, *out_nnz reads -1 and
+ * the outputs are undefined).  The default (1) is the count + compaction pair of kernels, which is faster while the
+ * tensor fits the L2 cache.  Process-wide switch; no counterpart in the reference. */
+void ctb_bitmask_force_two_kernels(int32_t on);
 int ctb_bitmask_compress(const void *x, int32_t dtype, int64_t rows, int64_t cols, void *out_values,
                          uint8_t *out_bitmask, int64_t *out_row_offsets, int64_t *out_nnz,
                          void *workspace, void *stream);

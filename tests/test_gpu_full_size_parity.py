@@ -133,8 +133,14 @@ def test_c4a_sparse24_e4m3_full(ops, orc, canary):
     assert_bit_equal(gd.cpu(), orc.bitmask_decompress(v, b, q.shape), "decompressed")
 
 
-def test_c4b_bitmask_full(ops, orc, canary):
-    """BASELINE config 4b at 4096 x 4096, Bernoulli(0.5) zero mask."""
+@pytest.mark.parametrize("two_kernels", [False, True])
+def test_c4b_bitmask_full(ops, orc, canary, two_kernels, request):
+    """BASELINE config 4b at 4096 x 4096, Bernoulli(0.5) zero mask: the single-pass compress kernel (every block
+    waits for the counts of the others) and the count + compaction pair."""
+    from compressed_tensors_b200 import _lib as L
+
+    L.lib().ctb_bitmask_force_two_kernels(L.i32(1 if two_kernels else 0))
+    request.addfinalizer(lambda: L.lib().ctb_bitmask_force_two_kernels(L.i32(1)))
     g = torch.Generator().manual_seed(5)
     w = weights(4096, 4096, 5)
     w[torch.rand(4096, 4096, generator=g) < 0.5] = 0
@@ -146,6 +152,34 @@ def test_c4b_bitmask_full(ops, orc, canary):
     assert_bit_equal(gr.cpu(), row_offsets, "row offsets")
     assert_bit_equal(gv.cpu(), values, "values")
     assert_bit_equal(gd.cpu(), orc.bitmask_decompress(values, bitmask, w.shape), "decompressed")
+
+
+def test_bitmask_large_and_repeated(ops, orc, request):
+    """A tensor of many slabs (14336 x 4096: 3584 tiles, more than the grid holds at once) and twenty calls back to
+    back on one workspace-sized scratch: the per-call ticket keeps stale counts of earlier calls from being taken."""
+    from compressed_tensors_b200 import _lib as L
+
+    L.lib().ctb_bitmask_force_two_kernels(L.i32(0))  # the single-pass kernel
+    request.addfinalizer(lambda: L.lib().ctb_bitmask_force_two_kernels(L.i32(1)))
+    g = torch.Generator().manual_seed(6)
+    w = weights(14336, 4096, 6)
+    w[torch.rand(14336, 4096, generator=g) < 0.7] = 0
+    values, bitmask, row_offsets = orc.bitmask_compress(w)
+    wd = w.cuda()
+    for _ in range(3):
+        gv, gb, gr = ops.bitmask_compress(wd)
+        assert_bit_equal(gb.cpu(), bitmask, "bitmask")
+        assert_bit_equal(gr.cpu(), row_offsets, "row offsets")
+        assert_bit_equal(gv.cpu(), values, "values")
+    small = [weights(64, 512, 100 + i) for i in range(20)]
+    for i, t in enumerate(small):
+        t[torch.rand(64, 512, generator=g) < 0.1 * (i % 10)] = 0
+    outs = [ops._masked_compress(t.cuda(), None, sync=False) for t in small]
+    torch.cuda.synchronize()
+    for t, (v, b, r, n) in zip(small, outs):
+        ev, eb, er = orc.bitmask_compress(t)
+        assert int(n.item()) == ev.numel()
+        assert_bit_equal(v[: ev.numel()].cpu(), ev, "values"), assert_bit_equal(b.cpu(), eb, "bitmask"), assert_bit_equal(r.cpu(), er, "row offsets")
 
 
 def test_quantize_pack_batch_equals_oracle(ops, orc, canary):

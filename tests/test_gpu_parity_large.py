@@ -201,9 +201,15 @@ def test_sparse_codecs_match_oracle(ops, orc):
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32, torch.int8, torch.float8_e4m3fn])
 @pytest.mark.parametrize("shape", [(1, 8), (3, 8), (37, 24), (129, 1000), (5, 13), (700, 4096)])
 @pytest.mark.parametrize("density", [0.0, 0.03, 0.5, 1.0])
-def test_bitmask_codec_shapes_dtypes_densities(ops, orc, dtype, shape, density):
+@pytest.mark.parametrize("two_kernels", [False, True])
+def test_bitmask_codec_shapes_dtypes_densities(ops, orc, dtype, shape, density, two_kernels, request):
     """ragged tile counts, every element size, empty / sparse / dense tensors, and a row length that is not a
-    multiple of 8 (the row-by-row kernels), all bit-exact against the oracle"""
+    multiple of 8 (the row-by-row kernels), all bit-exact against the oracle; once through the single-pass compress
+    kernel and once through the count + compaction pair"""
+    from compressed_tensors_b200 import _lib as L
+
+    L.lib().ctb_bitmask_force_two_kernels(L.i32(1 if two_kernels else 0))
+    request.addfinalizer(lambda: L.lib().ctb_bitmask_force_two_kernels(L.i32(1)))
     g = torch.Generator().manual_seed(hash((shape, density)) % 1000)
     if dtype == torch.int8:
         w = torch.randint(1, 128, shape, generator=g).float()
