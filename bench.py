@@ -346,6 +346,15 @@ def per_config_table(dev, peak):
         q, _ = ops.absmax_quantize(w, qtype=ops.QFLOAT, bits=8, col_group=11008, codec="dtype", out_dtype=torch.float8_e4m3fn)
         return (q,)
     run("c4a_sparse24_compress_e4m3", s24, lambda q: ops.sparse24_compress(q), 2 * ns, 1.625 * ns, 1.7 * ns)
+    def s24_dense():
+        w = rnd(4096, 11008)
+        w = torch.where(ops.sparse24_mask(w), w, torch.zeros((), dtype=w.dtype, device=dev))
+        mn, mx = ops.minmax(w, 1, 11008)
+        scale, _ = ops.calculate_qparams(mn, mx, qtype=ops.QFLOAT, bits=8, symmetric=True)
+        return (w, scale.reshape(-1))
+    # the whole of configuration 4a in one pass: pruned bf16 weight + per-channel scale in, kept e4m3 values + bitmask out
+    run("c4a_fused_fp8_quantize_sparse24_compress", s24_dense, lambda w, sc: ops.quantize_fp8_sparse24(w, sc),
+        2 * ns, 2.625 * ns, 2.7 * ns)
     run("c4a_sparse24_decompress_e4m3", lambda: ops.sparse24_compress(s24()[0]),
         lambda v, b: ops.sparse24_decompress(v, b, (4096, 11008)), 2 * ns, 1.625 * ns, 1.7 * ns)
     def unstructured():
@@ -466,6 +475,8 @@ def per_config_cpu(ct):
         s, z = calculate_qparams(ws.amin(-1, keepdim=True), ws.amax(-1, keepdim=True), a8)
         q = quantize(ws, s, z, a8, dtype=torch.float8_e4m3fn)
         vals, bm = timed("c4a_sparse24_compress_e4m3", lambda: sparse24_bitmask_compress(q))
+        timed("c4a_fused_fp8_quantize_sparse24_compress",
+              lambda: sparse24_bitmask_compress(quantize(ws, s, z, a8, dtype=torch.float8_e4m3fn)))
         timed("c4a_sparse24_decompress_e4m3", lambda: sparse24_bitmask_decompress(vals, bm, q.shape))
         wu = rnd(4096, 4096)
         wu[torch.rand(4096, 4096, generator=g) < 0.5] = 0

@@ -196,6 +196,7 @@ class CodecEngine:
         self._budget: Dict[int, float] = {}
         self.deferred = False
         self.launches = 0
+        self.fuse_sparse24 = False  # set by the owner when its sparsity compressor is sparse-24-bitmask
         # measurement hook: with record_kernel_times set, every whole-shard launch is bracketed by two CUDA events
         # on its stream and (kind, start, end) is appended to kernel_times
         self.record_kernel_times = False
@@ -203,8 +204,9 @@ class CodecEngine:
 
     # ------------------------------------------------------------------ plumbing
     def _get_streams(self, dev: torch.device, role: str):
-        import os
-        key = (dev.index, role if os.environ.get("CTB_SPLIT_STREAMS") else "")
+        """Copy-in, kernel and copy-out stream of `dev`, shared by both directions: copies of one direction execute
+        in the order they were submitted whatever stream they are on, so more streams would buy nothing."""
+        key = (dev.index, "")
         if key not in self._streams:
             self._streams[key] = tuple(torch.cuda.Stream(dev) for _ in range(3))
         return self._streams[key]
@@ -347,6 +349,8 @@ class CodecEngine:
                 st.update(minmax_qparams(w, j.scheme.weights))
         if w is not None and j.transforms:
             j.qparams = {k: st[k] for k in _QPARAMS if k in st and st[k] is not j.state.get(k)}
+        if w is not None and self._fp8_sparse24(j, w, st):
+            return
         if w is not None and j.compressor is not None and j.scheme is not None and j.scheme.weights is not None \
                 and st.get("weight_scale") is not None:
             j.out = dict(j.compressor.compress_weight(weight=w, scale=st["weight_scale"], zero_point=st.get("weight_zero_point"),
@@ -355,6 +359,29 @@ class CodecEngine:
             j.shape, j.quantized = tuple(w.shape), True
         elif w is not None and j.transforms:
             j.out = {"weight": w}
+
+    def _fp8_sparse24(self, j: Job, w: Tensor, st: Dict[str, Tensor]) -> bool:
+        """A weight that the float-quantized compressor would turn into per-channel FP8 and the sparse-24-bitmask
+        compressor would then compact (model_compressor.py:498-519) goes through one kernel; the FP8 tensor between
+        the two is never materialised.  Fills the job as the two compressors would have."""
+        args = j.scheme.weights if j.scheme is not None else None
+        scale = st.get("weight_scale")
+        if (not self.fuse_sparse24 or not j.sparse or j.compressor is None or args is None or scale is None
+                or getattr(j.compressor, "_format_name", None) != CompressionFormat.float_quantized.value
+                or args.type != QuantizationType.FLOAT or args.num_bits != 8 or args.strategy != QuantizationStrategy.CHANNEL
+                or args.dynamic or w.ndim != 2 or w.dtype != torch.bfloat16 or not w.is_cuda or w.shape[1] % 8
+                or scale.dtype != torch.bfloat16 or scale.numel() != w.shape[0]
+                or st.get("weight_g_idx") is not None or st.get("weight_global_scale") is not None):
+            return False
+        zp = st.get("weight_zero_point")
+        if zp is not None and (zp.numel() != w.shape[0] or zp.dtype not in L.DT):
+            return False
+        with self._timed("compress", w.device):
+            values, bitmask = ops.quantize_fp8_sparse24(w, scale, zp)
+        self.launches += 1
+        j.out, j.shape, j.quantized = {}, tuple(w.shape), True
+        j.sparse_out = {"shape": torch.tensor(list(w.shape)).reshape(-1, 1), "compressed": values, "bitmask": bitmask}
+        return True
 
     # ------------------------------------------------------------------ decompress
     def classify_decompress(self, job: Job) -> None:

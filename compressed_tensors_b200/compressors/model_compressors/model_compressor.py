@@ -80,6 +80,8 @@ class ModelCompressor:
                 comp._format_name = f
                 self.quantization_compressor[f] = comp
         self.engine = CodecEngine(_PRECISIONS[rotation_precision])
+        self.engine.fuse_sparse24 = (self.sparsity_compressor is not None
+                                     and sparsity_config.format == CompressionFormat.sparse_24_bitmask.value)
         self._transforms: Dict[tuple, object] = {}  # transform objects of `transform_config`, made once
         self.reuse_buffers = reuse_buffers
         self._cycle: Optional[_Cycle] = None

@@ -14,7 +14,7 @@ __all__ = [
     "mxfp4_round_pow2", "mxfp4_generate_scales", "mxfp4_convert_scales",
     "cutlass24_compress", "cutlass24_decompress", "marlin24_pack_weight", "marlin24_pack_scales",
     "pack_int32", "unpack_int32", "pack_fp4", "unpack_fp4", "pack_bitmasks", "unpack_bitmasks",
-    "sparse24_mask", "sparse24_compress", "sparse24_decompress", "bitmask_compress", "bitmask_decompress", "hadamard",
+    "sparse24_mask", "sparse24_compress", "quantize_fp8_sparse24", "sparse24_decompress", "bitmask_compress", "bitmask_decompress", "hadamard",
     "absmax_quantize", "rotate_quantize_int4_batch", "rotate_quantize_int4_batch_bounded", "quantize_pack_int4_batch",
     "unpack_dequantize_int4_batch", "tensor_table", "QINT", "QFLOAT",
 ]
@@ -317,6 +317,30 @@ def sparse24_compress(x):
         return values, bitmask
     values, bitmask, _ = _masked_compress(x, sparse24_mask(x))
     return values.reshape(rows, cols // 2), bitmask
+
+
+def quantize_fp8_sparse24(x, scale, zero_point=None):
+    """Per-channel FP8 quantization (forward.py:462 _quantize to float8_e4m3fn) and sparse_24_bitmask.py:162
+    sparse24_bitmask_compress of the result in one pass -> (values e4m3 [rows, cols/2], bitmask).
+    x bf16 [rows, cols] with cols % 8 == 0, scale (bf16) and zero_point with one entry per row."""
+    require_cuda(x, scale)
+    x, scale = _c(x), _c(scale)
+    if zero_point is not None:
+        require_cuda(zero_point)
+        zero_point = _c(zero_point)
+        if zero_point.numel() != x.shape[0] or zero_point.dtype not in DT:
+            raise ValueError("zero_point needs one entry per row in a supported dtype")
+    if x.dtype != torch.bfloat16 or scale.dtype != torch.bfloat16 or x.dim() != 2:
+        raise TypeError("quantize_fp8_sparse24 takes a 2-D bf16 tensor and bf16 scales")
+    rows, cols = x.shape
+    if scale.numel() != rows:
+        raise ValueError(f"one scale per row expected, got {scale.numel()} for {rows} rows")
+    values = torch.empty((rows, cols // 2), dtype=torch.float8_e4m3fn, device=x.device)
+    bitmask = torch.empty((rows, cols // 8), dtype=torch.uint8, device=x.device)
+    check(lib().ctb_quantize_fp8_sparse24(ptr(x), ptr(scale), ptr(zero_point), i32(DT[zero_point.dtype] if zero_point is not None else 0),
+                                          i64(rows), i64(cols),
+                                          ptr(values), ptr(bitmask), stream_of(x)))
+    return values, bitmask
 
 
 def bitmask_compress(x):

@@ -8,7 +8,7 @@ operators; the host mirror of the reference interface calls these.
 
 Operators: quantize, dequantize, fake_quantize, absmax_quantize, minmax, calculate_qparams, generate_gparam,
 pack_int32, unpack_int32, pack_fp4, unpack_fp4, pack_bitmasks, unpack_bitmasks, sparse24_mask, sparse24_compress,
-sparse24_decompress, bitmask_compress, bitmask_decompress, hadamard.
+quantize_fp8_sparse24, sparse24_decompress, bitmask_compress, bitmask_decompress, hadamard.
 """
 from typing import List, Optional, Sequence, Tuple
 
@@ -307,6 +307,23 @@ def sparse24_compress(x):
     return torch.ops.ctb200.sparse24_compress(x)
 
 
+@custom_op(f"{NS}::quantize_fp8_sparse24", mutates_args=())
+def _quantize_fp8_sparse24(x: Tensor, scale: Tensor, zero_point: Optional[Tensor] = None) -> Tuple[Tensor, Tensor]:
+    return _o.quantize_fp8_sparse24(x, scale, zero_point)
+
+
+@_quantize_fp8_sparse24.register_fake
+def _(x, scale, zero_point=None):
+    rows, cols = x.shape
+    if cols % 8 != 0:
+        raise ValueError("fused FP8 + 2:4 compression needs cols % 8 == 0")
+    return x.new_empty((rows, cols // 2), dtype=torch.float8_e4m3fn), x.new_empty((rows, cols // 8), dtype=torch.uint8)
+
+
+def quantize_fp8_sparse24(x, scale, zero_point=None):
+    return torch.ops.ctb200.quantize_fp8_sparse24(x, scale, zero_point)
+
+
 @custom_op(f"{NS}::sparse24_decompress", mutates_args=())
 def _sparse24_decompress(values: Tensor, bitmask: Tensor, shape: List[int]) -> Tensor:
     return _o.sparse24_decompress(values, bitmask, shape)
@@ -370,5 +387,5 @@ def hadamard(x, n, signs=None, inverse=False, side=0, precision=torch.float64, n
 
 OPERATORS: Sequence[str] = ("quantize", "dequantize", "fake_quantize", "absmax_quantize", "minmax", "calculate_qparams",
                             "generate_gparam", "pack_int32", "unpack_int32", "pack_fp4", "unpack_fp4", "pack_bitmasks",
-                            "unpack_bitmasks", "sparse24_mask", "sparse24_compress", "sparse24_decompress", "bitmask_compress",
-                            "bitmask_decompress", "hadamard")
+                            "unpack_bitmasks", "sparse24_mask", "sparse24_compress", "quantize_fp8_sparse24", "sparse24_decompress",
+                            "bitmask_compress", "bitmask_decompress", "hadamard")

@@ -171,6 +171,16 @@ int ctb_sparse24_mask(const void *x, int32_t dtype, int64_t numel, uint8_t *out_
  * values [rows, cols/2] (same dtype as x) and bitmask uint8 [rows, ceil(cols/8)] in one pass. */
 int ctb_sparse24_compress(const void *x, int32_t dtype, int64_t rows, int64_t cols, void *out_values,
                           uint8_t *out_bitmask, void *stream);
+/* A stacked float-quantized + sparse-24-bitmask weight in one pass: per-channel static FP8 quantization
+ * (compressors/quantized_compressors/naive_quantized.py:124-140 compress_weight ->
+ * quantization/lifecycle/forward.py:462-489 _quantize to float8_e4m3fn) followed by
+ * sparse_24_bitmask.py:162-203 on the e4m3 result, which is never written to memory.
+ * x bf16 [rows, cols], cols % 8 == 0; scale bf16 [rows] (one per output channel); zero_point [rows] of
+ * zp_dtype or NULL (the reference adds it before rounding, so even an all-zero one turns -0.0 into +0.0).
+ * out_values e4m3 [rows, cols/2], out_bitmask uint8 [rows, cols/8]: bit-identical to ctb_quantize followed
+ * by ctb_sparse24_compress. */
+int ctb_quantize_fp8_sparse24(const void *x, const void *scale, const void *zero_point, int32_t zp_dtype,
+                              int64_t rows, int64_t cols, void *out_values, uint8_t *out_bitmask, void *stream);
 /* compressors/sparse_compressors/sparse_bitmask.py:131-149 bitmask_compress.
  * out_values needs room for rows*cols elements; the first *out_nnz (device int64) are valid,
  * row-major.  out_row_offsets is int64 [rows] (exclusive prefix of per-row counts).

@@ -133,6 +133,59 @@ def test_c4a_sparse24_e4m3_full(ops, orc, canary):
     assert_bit_equal(gd.cpu(), orc.bitmask_decompress(v, b, q.shape), "decompressed")
 
 
+def test_c4a_fused_quantize_sparse24_full(ops, orc, canary):
+    """The same configuration through the one-pass kernel: bf16 weight + per-channel scale in, kept e4m3 values and
+    bitmask out; with and without the (all-zero) zero point the calibrated module carries."""
+    w = weights(4096, 11008, 4)
+    pruned = torch.where(orc.sparse24_mask(w), w, torch.zeros((), dtype=w.dtype))
+    pruned[7, :64] = -0.0  # signed zeros: the zero point decides whether their code keeps the sign, and the sign the rank
+    kw = dict(qtype=orc.QFLOAT, bits=8, col_group=11008, row_group=1, scale_row_stride=1)
+    mn, mx = orc.minmax(pruned, 1, 11008)
+    scale, zp = orc.calculate_qparams(mn, mx, qtype=orc.QFLOAT, bits=8, symmetric=True)
+    for z in (zp, None):
+        v, b = orc.sparse24_compress(orc.quantize(pruned, scale, z, out_dtype=torch.float8_e4m3fn, **kw))
+        with canary():
+            gv, gb = ops.quantize_fp8_sparse24(pruned.cuda(), scale.cuda().reshape(-1), None if z is None else z.cuda().reshape(-1))
+        assert_bit_equal(gb.cpu(), b, f"bitmask (zero point: {z is not None})")
+        assert_bit_equal(gv.cpu(), v, f"values (zero point: {z is not None})")
+
+
+def test_fused_quantize_sparse24_edge_cases(ops, orc, canary):
+    """Dense (unpruned) rows so that ties and rank order matter, NaN / Inf / signed zeros, scales outside the range
+    of the reciprocal shortcut, a zero point other than zero, a unit count that fills neither a warp nor a pair."""
+    g = torch.Generator().manual_seed(17)
+    rows, cols = 37, 104
+    x = (torch.randn(rows, cols, generator=g) * 0.05).to(torch.bfloat16)
+    x[0, :8] = torch.tensor([0.5, -0.5, float("inf"), -float("inf"), 0.0, -0.0, 1.0, -1.0]).to(torch.bfloat16)
+    x.view(torch.int16)[0, 8:12] = torch.tensor([0x7FC0, -64, 0x7F81, -1], dtype=torch.int16)  # NaNs of both signs
+    x[1] = x[1, 0]            # every run a four-way tie
+    x[2, ::2] = -x[2, 1::2]   # magnitude ties between neighbours
+    x[3] = 0
+    x[4] = -0.0
+    scale = (x.float().abs().nan_to_num(0, 0, 0).amax(dim=1) / 448).clamp_min(1e-6).to(torch.bfloat16)
+    scale[5], scale[6], scale[8] = 2.0 ** -110, 2.0 ** 100, 2.0 ** -99
+    x[5] = (torch.randn(cols, generator=g) * 2.0 ** -105).to(torch.bfloat16)
+    x[6] = (torch.randn(cols, generator=g) * 2.0 ** 104).to(torch.bfloat16)
+    kw = dict(qtype=orc.QFLOAT, bits=8, col_group=cols, row_group=1, scale_row_stride=1)
+    zeros = torch.zeros(rows, dtype=torch.bfloat16)
+    shifted = zeros.clone()
+    shifted[9], shifted[10] = 3.0, -1.5
+    for name, z in (("none", None), ("zeros", zeros), ("shifted", shifted), ("e4m3 zeros", zeros.to(torch.float8_e4m3fn))):
+        want = orc.quantize(x, scale.reshape(-1, 1), None if z is None else z.reshape(-1, 1), out_dtype=torch.float8_e4m3fn, **kw)
+        v, b = orc.sparse24_compress(want)
+        with canary():
+            gv, gb = ops.quantize_fp8_sparse24(x.cuda(), scale.cuda(), None if z is None else z.cuda())
+            twice = ops.sparse24_compress(ops.quantize(x.cuda(), scale.cuda().reshape(-1, 1), None if z is None else z.cuda().reshape(-1, 1),
+                                                       out_dtype=torch.float8_e4m3fn, **{**kw, "qtype": ops.QFLOAT}))
+        assert_bit_equal(gb.cpu(), b, f"bitmask ({name})")
+        assert_bit_equal(gv.cpu(), v, f"values ({name})")
+        assert_bit_equal(gv.cpu(), twice[0].cpu(), f"values against the two-pass path ({name})")
+        assert_bit_equal(gb.cpu(), twice[1].cpu(), f"bitmask against the two-pass path ({name})")
+    assert ops.quantize_fp8_sparse24(x[:0].cuda(), scale[:0].cuda())[0].shape == (0, cols // 2)
+    with pytest.raises(ValueError):
+        ops.quantize_fp8_sparse24(x[:, :100].cuda(), scale.cuda())
+
+
 @pytest.mark.parametrize("two_kernels", [False, True])
 def test_c4b_bitmask_full(ops, orc, canary, two_kernels, request):
     """BASELINE config 4b at 4096 x 4096, Bernoulli(0.5) zero mask: the single-pass compress kernel (every block

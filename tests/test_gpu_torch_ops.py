@@ -37,6 +37,7 @@ def _inputs():
         "unpack_bitmasks": (bm, [64, 256]),
         "sparse24_mask": (x,),
         "sparse24_compress": (x,),
+        "quantize_fp8_sparse24": (x, (x.abs().amax(dim=1) / 448).to(torch.bfloat16), None),
         "sparse24_decompress": (v24, b24, [64, 256]),
         "bitmask_compress": (sparse,),
         "bitmask_decompress": (vals, bm, [64, 256]),
