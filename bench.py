@@ -230,6 +230,29 @@ def workload_config(layers, world, precision):
             "l2": "inputs larger than L2 (no flush needed)"}
 
 
+_RESULT_FD = None
+
+
+def quiet_stdout():
+    """Libraries write to file descriptor 1 on their own (NCCL prints its version there at the first
+    collective; progress bars of the reference).  The contract of this script is ONE JSON line on stdout, so
+    descriptor 1 is pointed at stderr for the run and the result line goes to the saved descriptor."""
+    global _RESULT_FD
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
+
+
+def emit(obj):
+    line = (json.dumps(obj) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(line.decode())
+        sys.stdout.flush()
+    else:
+        sys.stdout.flush()
+        os.write(_RESULT_FD, line)
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -240,7 +263,7 @@ def run_reference(args):
     cfg["sample"] = SAMPLE_TEXT
     cfg["path"] = ("reference package: apply_transform_config -> calculate_qparams -> ModelCompressor.compress_model -> decompress_model"
                    if arm.kind == "reference" else "C + OpenMP restatement of the same calls")
-    print(json.dumps({
+    emit(({
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic", "config": cfg,
@@ -587,10 +610,13 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-per-config", action="store_true", help="skip the C1-C4 per-scheme table")
     ap.add_argument("--no-other-modes", action="store_true", help="skip timing the other rotation arithmetics")
+    ap.add_argument("--per-config-only", action="store_true",
+                    help="time the C1-C4 per-scheme table alone, print it and exit (1 GPU; the small case for profiling one of its kernels)")
     ap.add_argument("--standalone-ops", action="store_true",
                     help="time the operators as separate calls on an 8192 x 8192 tensor, print that table alone and exit (1 GPU)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    quiet_stdout()
     if args.impl == "reference":
         return run_reference(args)
 
@@ -604,10 +630,17 @@ def main():
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+    if args.per_config_only:
+        if rank == 0:
+            emit({"per_config": per_config_table(dev, peaks()[0]), "peak_gbs": peaks()[0],
+                  "timing": "CUDA events over CUDA-graph replays, rotating inputs larger than 2x L2"})
+        if world > 1:
+            dist.destroy_process_group()
+        return
     if args.standalone_ops:
         if rank == 0:
-            print(json.dumps({"standalone_ops": standalone_ops_table(dev, peaks()[0]), "tensor": "8192x8192 bf16",
-                              "peak_gbs": peaks()[0], "timing": "CUDA events over CUDA-graph replays, rotating inputs larger than L2"}))
+            emit({"standalone_ops": standalone_ops_table(dev, peaks()[0]), "tensor": "8192x8192 bf16",
+                  "peak_gbs": peaks()[0], "timing": "CUDA events over CUDA-graph replays, rotating inputs larger than L2"})
         if world > 1:
             dist.destroy_process_group()
         return
@@ -791,7 +824,7 @@ def main():
         if arm is not None:
             dt, val = arm.time(2, 1)
             out["cpu_baseline"] = {"value": val, "unit": UNIT, "cores": arm.cores, "kind": arm.kind, "sample": SAMPLE_TEXT + ", 2 passes"}
-        print(json.dumps(out))
+        emit(out)
     if world > 1:
         dist.destroy_process_group()
 

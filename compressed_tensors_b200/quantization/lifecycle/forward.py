@@ -67,14 +67,32 @@ def infer_dequant_args(x_q: torch.Tensor, scale: torch.Tensor) -> QuantizationAr
     raise ValueError(f"Could not infer a quantization strategy from scale with {scale.ndim} dimmensions. Expected 0 or 2 dimmensions.")
 
 
+_G_IDX_UNSET = {}  # (data_ptr, version, numel) of a g_idx tensor -> whether it holds a -1 (one read-back per tensor state)
+
+
+def _resolve_g_idx(g_idx: torch.Tensor, col_group: int, cols: int):
+    """forward.py:286 `is_column_order = g_idx is None or -1 in g_idx`: a column map that still holds a -1 (the
+    value it is initialised with) is ignored.  The answer needs the tensor's contents, so it is read back once per
+    tensor state and remembered; while a CUDA graph is being captured nothing may be read back, and the choice is
+    made on the device instead (the map or the plain column order, selected by a 0-dim flag)."""
+    if g_idx.is_cuda and torch.cuda.is_current_stream_capturing():
+        plain = torch.arange(cols, device=g_idx.device, dtype=g_idx.dtype) // col_group
+        return torch.where((g_idx == -1).any(), plain, g_idx)
+    key = (g_idx.data_ptr(), g_idx._version, g_idx.numel(), g_idx.device)
+    unset = _G_IDX_UNSET.get(key)
+    if unset is None:
+        if len(_G_IDX_UNSET) > 4096:
+            _G_IDX_UNSET.clear()
+        unset = _G_IDX_UNSET[key] = bool((g_idx == -1).any())
+    return None if unset else g_idx
+
+
 def _common(x, scale, args, g_idx, global_scale):
     if x.dtype not in _FLOATS + (torch.int8, torch.float8_e4m3fn):
         raise TypeError(f"unsupported input dtype {x.dtype}")
     col_group, row_group, srs = _geometry(x, scale, args)
     grouped = args.strategy in (QuantizationStrategy.GROUP, QuantizationStrategy.TENSOR_GROUP)
-    use_gidx = None
-    if grouped and g_idx is not None and not bool((g_idx == -1).any()):  # forward.py:286 is_column_order
-        use_gidx = g_idx
+    use_gidx = _resolve_g_idx(g_idx, col_group, x.shape[-1]) if grouped and g_idx is not None else None
     kw = dict(qtype=qtype_code(args), bits=args.num_bits, col_group=col_group, row_group=row_group, scale_row_stride=srs,
               g_idx=use_gidx, global_scale=global_scale)
     sdt = torch.float32 if global_scale is not None else scale.dtype

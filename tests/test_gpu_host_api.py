@@ -68,6 +68,35 @@ def test_actorder(golden):
     # g_idx of all -1 means "column order" (forward.py:286)
     q_plain = quantize(x, scale, zp, args, dtype=torch.int8, g_idx=torch.full_like(g_idx, -1))
     assert_bit_equal(q_plain.cpu(), quantize(x, scale, zp, args, dtype=torch.int8).cpu())
+    # the same tensor filled in afterwards (in place) is a new state: the remembered answer must not stick
+    late = torch.full_like(g_idx, -1)
+    quantize(x, scale, zp, args, dtype=torch.int8, g_idx=late)
+    late.copy_(g_idx)
+    assert_bit_equal(quantize(x, scale, zp, args, dtype=torch.int8, g_idx=late).cpu(), d["q_int8"])
+
+
+def test_actorder_inside_graph_capture(golden):
+    """Nothing may be read back to the host while a CUDA graph is captured: whether the column map is in use
+    (forward.py:286) is then decided on the device."""
+    from compressed_tensors_b200.quantization import QuantizationArgs, fake_quantize
+
+    d = golden("int_quant")["w4_sym_g64_actorder"]
+    args = QuantizationArgs(num_bits=4, symmetric=True, strategy="group", group_size=64, actorder="group")
+    x, scale, zp, g_idx = dev(d["x"]), dev(d["scale"]), dev(d["zp"]), dev(d["g_idx"])
+    unset = torch.full_like(g_idx, -1)
+    plain = fake_quantize(x, scale, zp, args)
+    fake_quantize(x, scale, zp, args, g_idx=g_idx)  # warm-up outside the capture
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            mapped = fake_quantize(x, scale, zp, args, g_idx=g_idx)
+            ignored = fake_quantize(x, scale, zp, args, g_idx=unset)
+    graph.replay()
+    torch.cuda.synchronize()
+    assert_bit_equal(mapped.cpu(), d["fake"])
+    assert_bit_equal(ignored.cpu(), plain.cpu())
 
 
 def test_fp8_api(golden):
