@@ -120,7 +120,10 @@ __global__ void __launch_bounds__(kRQThreads, (sizeof(A) == 8 ? 2 : 4)) rotquant
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 A other = rq_shfl_xor<A>(v[a][j], 1);
-                v[a][j] = v[a][j] * sg + other;  // exact: one rounding, same as other -/+ v
+                // exact: one rounding, same as other -/+ v.  The fused form is asked for by name: left to the
+                // compiler, the float64 product by +-1 becomes a sign select per word in front of an add.
+                if constexpr (sizeof(A) == 8) v[a][j] = __fma_rn(v[a][j], sg, other);
+                else v[a][j] = __fmaf_rn(v[a][j], sg, other);
             }
         // normalise, apply the sign diagonal, round to bf16 (the rotated weight), group maximum
         uint32_t wq[8][4];  // rotated weights, packed bf16x2
