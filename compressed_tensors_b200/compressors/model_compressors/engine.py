@@ -276,6 +276,11 @@ class CodecEngine:
         args = job.scheme.weights
         fmt = getattr(job.compressor, "_format_name", None)
         rows, cols = w.shape
+        if self._is_fp8_channel(job, fmt, args, rows, cols) and w.dtype == torch.bfloat16 and not job.transforms:
+            zp = job.state.get("weight_zero_point")
+            if zp is None or (zp.numel() == rows and zp.dtype in L.DT):
+                job.kind = "q8c"
+            return
         if fmt != CompressionFormat.pack_quantized.value or not is_w4a16_g128(args) or w.dtype != torch.bfloat16 or cols % 128:
             return
         if job.sparse and "weight" in job.compressor.compression_param_names:
@@ -289,6 +294,16 @@ class CodecEngine:
         if (s is not None and s.dtype == torch.bfloat16 and tuple(s.shape) == (rows, cols // 128)
                 and job.state.get("weight_g_idx") is None):
             job.kind = "q4"
+
+    @staticmethod
+    def _is_fp8_channel(job: Job, fmt, args, rows: int, cols: int) -> bool:
+        """Static per-output-channel FP8 of a 2-D weight through the float-quantized compressor, not stacked with a
+        sparsity compressor: what the whole-shard FP8 entry points take."""
+        s = job.state.get("weight_scale")
+        return (fmt == CompressionFormat.float_quantized.value and args is not None and args.type == QuantizationType.FLOAT
+                and args.num_bits == 8 and args.strategy == QuantizationStrategy.CHANNEL and not args.dynamic
+                and not job.sparse and cols % 8 == 0 and s is not None and s.dtype == torch.bfloat16 and s.numel() == rows
+                and job.state.get("weight_g_idx") is None and job.state.get("weight_global_scale") is None)
 
     def _compress_on_device(self, jobs: List[Job], dev: torch.device) -> None:
         """All jobs hold device tensors of `dev`; the current stream is the one to launch on.  Fills job.out
@@ -332,9 +347,35 @@ class CodecEngine:
                 if fused:
                     j.qparams = {"weight_scale": s}
                 j.shape, j.quantized = shp, True
+        group = [j for j in jobs if j.kind == "q8c"]
+        if group:
+            shapes = [tuple(j.state["weight"].shape) for j in group]
+            codes = _Arena(sum(_up(r * c) for r, c in shapes), dev)
+            outs = [codes.take((r, c), torch.float8_e4m3fn) for r, c in shapes]
+            table = _table([j.state["weight"].contiguous() for j in group], outs,
+                           [j.state["weight_scale"].contiguous() for j in group], shapes)
+            zps = [j.state.get("weight_zero_point") for j in group]
+            zps = [None if z is None else z.contiguous() for z in zps]
+            with self._timed("compress", dev):
+                self._fp8_quantize(table, zps, dev)
+            self.launches += 1
+            for j, o, shp in zip(group, outs, shapes):
+                j.out = {"weight": o}
+                j.shape, j.quantized = shp, True
         for j in jobs:
             if j.kind == "generic":
                 self._compress_generic(j)
+
+    def _fp8_quantize(self, table: np.ndarray, zps, dev: torch.device) -> None:
+        stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+        arr, zdt = None, 0
+        if any(z is not None for z in zps):
+            dts = {z.dtype for z in zps if z is not None}
+            if len(dts) != 1:
+                raise TypeError("zero points of one shard must share one dtype")
+            zdt = L.DT[next(iter(dts))]
+            arr = (ctypes.c_void_p * len(zps))(*[None if z is None else z.data_ptr() for z in zps])
+        L.check(L.lib().ctb_quantize_fp8_channel_batch(_table_ptr(table), L.i32(len(table)), arr, L.i32(zdt), stream))
 
     def _compress_generic(self, j: Job) -> None:
         """The per-tensor walk on device tensors: fuse pending transforms, calibrate where a rotation invalidated
@@ -389,6 +430,11 @@ class CodecEngine:
         if job.compressor is None or job.scheme is None or job.sparse:
             return
         fmt = getattr(job.compressor, "_format_name", None)
+        q = job.state.get("weight")
+        if (q is not None and q.ndim == 2 and q.dtype == torch.float8_e4m3fn and job.state.get("weight_zero_point") is None
+                and self._is_fp8_channel(job, fmt, job.scheme.weights, q.shape[0], q.shape[1])):
+            job.kind, job.shape = "dq8c", tuple(q.shape)
+            return
         p, s = job.state.get("weight_packed"), job.state.get("weight_scale")
         if (fmt != CompressionFormat.pack_quantized.value or not is_w4a16_g128(job.scheme.weights) or p is None or s is None
                 or p.dtype != torch.int32 or s.dtype != torch.bfloat16 or p.ndim != 2 or s.ndim != 2):
@@ -411,6 +457,19 @@ class CodecEngine:
             stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
             with self._timed("decompress", dev):
                 L.check(L.lib().ctb_unpack_dequantize_int4_batch(_table_ptr(table), L.i32(len(group)), stream))
+            self.launches += 1
+            for j, o in zip(group, outs):
+                j.out = {"weight": o}
+        group = [j for j in jobs if j.kind == "dq8c"]
+        if group:
+            shapes = [j.shape for j in group]
+            dense = _Arena(sum(_up(r * c * 2) for r, c in shapes), dev)
+            outs = [dense.take((r, c), torch.bfloat16) for r, c in shapes]
+            table = _table([j.state["weight"].contiguous() for j in group], outs,
+                           [j.state["weight_scale"].contiguous() for j in group], shapes)
+            stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+            with self._timed("decompress", dev):
+                L.check(L.lib().ctb_dequantize_fp8_channel_batch(_table_ptr(table), L.i32(len(group)), stream))
             self.launches += 1
             for j, o in zip(group, outs):
                 j.out = {"weight": o}
@@ -532,7 +591,7 @@ class CodecEngine:
             step = _Step(direction, group, dev, work, sparse_compress, need=2 * sum(weight_of(j) for j in group))
             step.feeds = [self._inputs_of(j, direction) for j in group]
             step.reads = {h.untyped_storage().data_ptr() for f in step.feeds for h in f.values()}
-            if all(j.kind in ("rotq4", "q4", "dq4") for j in group) and sparse_compress is None:
+            if all(j.kind in ("rotq4", "q4", "dq4", "q8c", "dq8c") for j in group) and sparse_compress is None:
                 self._plan(step)
                 self._queue.append(step)
                 # Deferred: hold the step back so that a pass requested later can be interleaved with this one; the
@@ -550,7 +609,12 @@ class CodecEngine:
         """Create the host-side results of a step (views of one page-locked block) without running it."""
         specs = []  # (job, dict, name, shape, dtype)
         for j in step.jobs:
-            if step.direction == "compress":
+            if step.direction == "compress" and j.kind == "q8c":
+                r, c = j.state["weight"].shape
+                j.out = {}
+                specs.append((j, j.out, "weight", (r, c), torch.float8_e4m3fn))
+                j.shape, j.quantized = (r, c), True
+            elif step.direction == "compress":
                 r, c = j.state["weight"].shape
                 j.out = {"weight_shape": torch.tensor((r, c))}  # int64 [2], as torch.tensor(weight.shape)
                 specs.append((j, j.out, "weight_packed", (r, c // 8), torch.int32))

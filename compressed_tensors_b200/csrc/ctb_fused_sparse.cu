@@ -7,8 +7,8 @@
 // The arithmetic of each half is the arithmetic of the separate entry points (ctb_quantize and ctb_sparse24_compress),
 // so the outputs are those of running the two one after the other, bit for bit: the kept pair of each run of four is
 // chosen on the e4m3 codes (their int8 view, as the reference's topk on a float8 tensor does), not on the bf16 inputs.
-#include "ctb_codec.cuh"
 #include "ctb_fastdiv.h"
+#include "ctb_fp8_codes.cuh"
 #include "ctb_sparse24_simd.cuh"
 
 namespace ctb {
@@ -26,49 +26,6 @@ struct QuantSparse24Args {
     FastDiv by_upr;
 };
 
-// One unit by the float arithmetic of the generic quantize tier, an element at a time: the rare path (a scale outside
-// the range where the reciprocal product is proven to round like the quotient, a zero point other than zero, or a
-// NaN among the inputs, whose code must carry the input's sign).
-template <bool HAS_ZP>
-__device__ __noinline__ uint2 exact_codes8(const QuantSparse24Args &a, uint32_t u, uint32_t row) {
-    const QP q = load_qp(a.scale, CTB_BF16, a.zp, a.zdt, nullptr, row);
-    const uint16_t *x = reinterpret_cast<const uint16_t *>(a.in + u);
-    uint64_t acc = 0;
-#pragma unroll 1
-    for (int i = 0; i < 8; ++i) {
-        float t = scaled_div<CTB_BF16>(bf16_bits_to_f32(x[i]), q);  // forward.py:471
-        if (HAS_ZP) t = round_to<CTB_BF16>(t + q.zp);               // forward.py:474
-        t = clamp_nan(t, -448.0f, 448.0f);
-        uint32_t code = (uint32_t)__nv_cvt_float_to_fp8(t, __NV_SATFINITE, __NV_E4M3);
-        if (t != t) code = 0x7Fu | ((__float_as_uint(t) >> 24) & 0x80u);  // Tensor.to(float8_e4m3fn) keeps a NaN's sign
-        acc |= (uint64_t)code << (8 * i);
-    }
-    return make_uint2((uint32_t)acc, (uint32_t)(acc >> 32));
-}
-
-template <bool HAS_ZP>
-__device__ __forceinline__ uint2 codes8(const QuantSparse24Args &a, const uint4 &raw, uint32_t u) {
-    const uint32_t row = fastdiv(u, a.by_upr);
-    const uint32_t sbits = __ldg(a.scale + row);
-    bool exact = ((sbits >> 7) & 0xFFu) - 28u > 197u;  // biased exponent outside [28, 225]
-    if (HAS_ZP) exact = exact || load_f32(a.zp, a.zdt, row) != 0.0f;
-    if (exact) return exact_codes8<HAS_ZP>(a, u, row);
-    const float r = rcp_approx(__uint_as_float(sbits << 16));
-    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-    uint32_t c[4];
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-        const __nv_bfloat162 q = HAS_ZP ? scale_pair_plus_zero(w[k], r) : scale_pair(w[k], r);
-        const uint32_t b = bf162_as_u32(q);
-        c[k] = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(__uint_as_float(b << 16), __uint_as_float(b & 0xFFFF0000u)), __NV_SATFINITE,
-                                                  __NV_E4M3);
-    }
-    const uint32_t c0 = c[0] | (c[1] << 16), c1 = c[2] | (c[3] << 16);
-    if (((((c0 & 0x7F7F7F7Fu) + 0x01010101u) | ((c1 & 0x7F7F7F7Fu) + 0x01010101u)) & 0x80808080u) != 0)
-        return exact_codes8<HAS_ZP>(a, u, row);
-    return make_uint2(c0, c1);
-}
-
 // Lane l of a warp takes units 64 t + l and 64 t + 32 + l, so that every load and store instruction of the warp
 // covers one contiguous span; the four runs of four codes a thread then holds go through one 8-bit SIMD selection.
 template <bool HAS_ZP>
@@ -82,8 +39,8 @@ __global__ void __launch_bounds__(kFusedThreads) quant_fp8_sparse24_kernel(const
         if (la) ra = ld_stream(a.in + ua);
         if (lb) rb = ld_stream(a.in + ub);
         uint2 ca = make_uint2(0, 0), cb = make_uint2(0, 0);
-        if (la) ca = codes8<HAS_ZP>(a, ra, ua);
-        if (lb) cb = codes8<HAS_ZP>(a, rb, ub);
+        if (la) ca = fp8_codes8<HAS_ZP>(ra, a.in + ua, a.scale, a.zp, a.zdt, fastdiv(ua, a.by_upr));
+        if (lb) cb = fp8_codes8<HAS_ZP>(rb, a.in + ub, a.scale, a.zp, a.zdt, fastdiv(ub, a.by_upr));
         uint32_t v0, v1, m;
         sparse24_pack_u8x16(ca.x, ca.y, cb.x, cb.y, v0, v1, m);
         if (la) {

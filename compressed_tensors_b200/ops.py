@@ -16,7 +16,7 @@ __all__ = [
     "pack_int32", "unpack_int32", "pack_fp4", "unpack_fp4", "pack_bitmasks", "unpack_bitmasks",
     "sparse24_mask", "sparse24_compress", "quantize_fp8_sparse24", "sparse24_decompress", "bitmask_compress", "bitmask_decompress", "hadamard",
     "absmax_quantize", "rotate_quantize_int4_batch", "rotate_quantize_int4_batch_bounded", "quantize_pack_int4_batch",
-    "unpack_dequantize_int4_batch", "tensor_table", "QINT", "QFLOAT",
+    "unpack_dequantize_int4_batch", "quantize_fp8_channel_batch", "dequantize_fp8_channel_batch", "tensor_table", "QINT", "QFLOAT",
 ]
 
 _CODEC = {"dtype": CODE_DTYPE, "pack32": CODE_PACK32, "fp4x2": CODE_FP4X2}
@@ -501,6 +501,27 @@ def quantize_pack_int4_batch(table, device=None):
     (weights in, words out, scales read), as one launch."""
     stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
     check(lib().ctb_quantize_pack_int4_batch(table, i32(len(table)), stream))
+
+
+def quantize_fp8_channel_batch(table, zero_points=None, device=None):
+    """Per-channel FP8 quantize (static bf16 scale, one per row) of every tensor in `table` (bf16 weights in, e4m3 out,
+    scales read), as one launch.  zero_points: None, or one tensor / None per table entry."""
+    stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+    zps, zdt = None, 0
+    if zero_points is not None and any(z is not None for z in zero_points):
+        dts = {z.dtype for z in zero_points if z is not None}
+        if len(dts) != 1 or next(iter(dts)) not in DT:
+            raise TypeError("zero points of one call must share one supported dtype")
+        zdt = DT[next(iter(dts))]
+        zps = (ctypes.c_void_p * len(table))(*[None if z is None else z.data_ptr() for z in zero_points])
+    check(lib().ctb_quantize_fp8_channel_batch(table, i32(len(table)), zps, i32(zdt), stream))
+
+
+def dequantize_fp8_channel_batch(table, device=None):
+    """dequantize (e4m3 codes, static bf16 scale per row, no zero point) of every tensor in `table` (codes in, bf16
+    weights out), as one launch."""
+    stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+    check(lib().ctb_dequantize_fp8_channel_batch(table, i32(len(table)), stream))
 
 
 def unpack_dequantize_int4_batch(table, device=None):

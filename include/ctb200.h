@@ -315,6 +315,17 @@ int ctb_quantize_pack_int4_batch(const ctb_tensor_ref *tensors, int32_t count, v
 /* ctb_dequantize(codec PACK32, num_bits 4, group 128, bf16 scale, no zero point) for every tensor. */
 int ctb_unpack_dequantize_int4_batch(const ctb_tensor_ref *tensors, int32_t count, void *stream);
 
+/* Whole-shard FP8: ctb_quantize(q_dtype E4M3, CHANNEL strategy, static bf16 scale, one per row) for every tensor of
+ * the table: the compress walk of a calibrated FP8 model (quantized_compressors/base.py:91-122 calling
+ * naive_quantized.py:74-110 per weight).  t.in = dense bf16 weight [rows, cols], cols % 8 == 0, t.out = e4m3
+ * [rows, cols], t.scale = bf16 [rows] (read).  zero_points: NULL, or `count` device pointers ([rows] of zp_dtype each,
+ * NULL entries allowed) for modules that carry a zero point (the reference adds it before rounding). */
+int ctb_quantize_fp8_channel_batch(const ctb_tensor_ref *tensors, int32_t count, const void *const *zero_points,
+                                   int32_t zp_dtype, void *stream);
+/* ctb_dequantize(E4M3 codes, CHANNEL strategy, bf16 scale, no zero point) for every tensor (base.py:190-237 calling
+ * naive_quantized.py:113-140).  t.in = e4m3 [rows, cols], t.out = bf16 [rows, cols], t.scale = bf16 [rows]. */
+int ctb_dequantize_fp8_channel_batch(const ctb_tensor_ref *tensors, int32_t count, void *stream);
+
 /* ---- staging memory of the host <-> device pipeline ------------------------------------------------------
  * The reference keeps a state dict in ordinary host memory and never leaves the CPU
  * (compressors/quantized_compressors/base.py:74, :125 compression_device="cpu").  Here host-resident tensors are

@@ -680,6 +680,24 @@ def gen_model_compressor():
     mc2.decompress_model(inplace)
     decompressed = {k: v.clone() for k, v in inplace.state_dict().items()}
     out["fp8_sparse24"] = slim(original, compressed, compressed_inplace, decompressed)
+
+    # ---- case 3: the same weights and scales, FP8 per-channel alone (no sparsity config); `original` is case 2's
+    model = toy_llama(32)
+    model.load_state_dict(original)
+    apply_quantization_config(model, qcfg)
+    calibrate(model)
+    mc = ModelCompressor(quantization_config=copy.deepcopy(qcfg))
+    compressed = mc.compress(model)
+    inplace = copy.deepcopy(model)
+    mc2 = ModelCompressor(quantization_config=copy.deepcopy(qcfg))
+    mc2.compress_model(inplace)
+    compressed_inplace = {k: v.clone() for k, v in inplace.state_dict().items()}
+    mc2.decompress_model(inplace)
+    decompressed = {k: v.clone() for k, v in inplace.state_dict().items()}
+    out["fp8_channel"] = slim({}, compressed, compressed_inplace, decompressed)
+    # everything that is not a quantized weight (norms, embeddings, lm_head, scales) already sits in case 2
+    out["fp8_channel"]["compressed"] = {k: v for k, v in compressed.items() if v.dtype == torch.float8_e4m3fn}
+    out["fp8_channel"]["compressed_keys"] = {k: (str(v.dtype), tuple(v.shape)) for k, v in compressed.items()}
     torch.save(out, os.path.join(OUT, "model_compressor.pt"))
 
 

@@ -256,3 +256,45 @@ def test_quantize_pack_batch_equals_oracle(ops, orc, canary):
         torch.cuda.synchronize()
     for i, (o, (_, words)) in enumerate(zip(out, want)):
         assert_bit_equal(o.cpu(), words, f"tensor {i} {shapes[i]}")
+
+
+def test_fp8_channel_batch_equals_oracle(ops, orc, canary):
+    """The whole-shard FP8 entry points on a ragged table (a tensor smaller than one unit, a partial last unit, rows
+    whose scale is outside the reciprocal form's range, NaN / Inf / signed zeros, zero points of zero and not):
+    every tensor's codes and dequantized values against the oracle."""
+    shapes = [(8, 128), (4096, 4096), (1024, 4096), (33, 264), (4096, 14336)]
+    ws = [weights(r, c, 80 + i) for i, (r, c) in enumerate(shapes)]
+    ws[3][0, :8] = torch.tensor([0.5, -0.5, float("inf"), -float("inf"), 0.0, -0.0, 1.0, -1.0]).to(torch.bfloat16)
+    ws[3].view(torch.int16)[0, 8:12] = torch.tensor([0x7FC0, -64, 0x7F81, -1], dtype=torch.int16)
+    ws[3][4] = -0.0
+    scales, zps, want, deq = [], [], [], []
+    for i, w in enumerate(ws):
+        kw = dict(qtype=orc.QFLOAT, bits=8, col_group=w.shape[1], row_group=1, scale_row_stride=1)
+        mn, mx = orc.minmax(torch.nan_to_num(w.float(), 0, 0, 0).to(torch.bfloat16), 1, w.shape[1])
+        scale, zp = orc.calculate_qparams(mn, mx, qtype=orc.QFLOAT, bits=8, symmetric=True)
+        if i == 3:
+            scale[5, 0], scale[6, 0], scale[8, 0] = 2.0 ** -110, 2.0 ** 100, 2.0 ** -99
+            zp = zp.to(torch.bfloat16)
+            zp[9, 0], zp[10, 0] = 3.0, -1.5
+        z = zp if i in (1, 3) else None  # a table may mix modules with and without a zero point
+        q = orc.quantize(w, scale, z, out_dtype=torch.float8_e4m3fn, **kw)
+        scales.append(scale)
+        zps.append(None if z is None else z.to(torch.bfloat16))
+        want.append(q)
+        deq.append(orc.dequantize(q, scale, None, out_dtype=torch.bfloat16, **kw))
+    dev = torch.device("cuda", 0)
+    with canary():
+        dw = [w.cuda() for w in ws]
+        ds = [s.cuda().reshape(-1) for s in scales]
+        dz = [None if z is None else z.cuda().reshape(-1) for z in zps]
+        out = [torch.empty(w.shape, dtype=torch.float8_e4m3fn, device="cuda") for w in ws]
+        back = [torch.empty(w.shape, dtype=torch.bfloat16, device="cuda") for w in ws]
+        ops.quantize_fp8_channel_batch(ops.tensor_table(dw, out, ds, shapes), dz, dev)
+        ops.dequantize_fp8_channel_batch(ops.tensor_table(out, back, ds, shapes), dev)
+        torch.cuda.synchronize()
+    for i in range(len(ws)):
+        assert_bit_equal(out[i].cpu(), want[i], f"codes of tensor {i} {shapes[i]}")
+        got, ref = back[i].cpu(), deq[i]
+        nan = got.float().isnan() & ref.float().isnan()  # a NaN code decodes to a NaN; its payload is the platform's
+        assert_bit_equal(torch.where(nan, torch.zeros_like(got), got), torch.where(nan, torch.zeros_like(ref), ref),
+                         f"dequantized tensor {i} {shapes[i]}")

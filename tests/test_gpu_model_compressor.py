@@ -284,6 +284,42 @@ def test_stacked_fp8_and_sparse24_matches_reference(golden, where):
         assert_bit_equal(got[k].cpu(), v, f"stacked decompress_model ({where}): {k}")
 
 
+@pytest.mark.parametrize("where", ["cuda", "cpu", "cpu-pinned"])
+def test_fp8_channel_whole_shard_matches_reference(golden, where):
+    """FP8 per-channel weights alone (float-quantized): every quantized weight goes through the whole-shard FP8 entry
+    points, one launch per direction and device-resident call, and equals the reference's bit for bit."""
+    from compressed_tensors_b200.compressors import ModelCompressor
+    from compressed_tensors_b200.quantization import apply_quantization_config
+
+    both = golden("model_compressor")
+    g, original = both["fp8_channel"], both["fp8_sparse24"]["original"]
+    _, qcfg = fp8_sparse_configs()
+    model = toy_llama(original, device="cuda" if where == "cuda" else "cpu", pin=where == "cpu-pinned")
+    apply_quantization_config(model, qcfg)
+    calibrate(model)
+    mc = ModelCompressor(quantization_config=copy.deepcopy(qcfg))
+    sd = mc.compress(model)
+    assert {k: (str(v.dtype), tuple(v.shape)) for k, v in sd.items()} == g["compressed_keys"]
+    for k, v in g["compressed"].items():
+        assert_bit_equal(sd[k].cpu(), v, f"compress ({where}): {k}")
+    before = mc.engine.launches
+    mc.compress_model(model)
+    if where == "cuda":
+        assert mc.engine.launches - before == 1, "one launch for every quantized weight of the model"
+    got = dict(model.state_dict())
+    assert {k: (str(v.dtype), tuple(v.shape)) for k, v in got.items()} == g["inplace_keys"]
+    for k, v in g["compressed"].items():
+        assert_bit_equal(got[k].cpu(), v, f"compress_model ({where}): {k}")
+    before = mc.engine.launches
+    mc.decompress_model(model)
+    if where == "cuda":
+        assert mc.engine.launches - before == 1
+    got = dict(model.state_dict())
+    assert {k: (str(v.dtype), tuple(v.shape)) for k, v in got.items()} == g["decompressed_keys"]
+    for k, v in g["decompressed"].items():
+        assert_bit_equal(got[k].cpu(), v, f"decompress_model ({where}): {k}")
+
+
 def test_decompress_from_disk(golden, tmp_path):
     """ModelCompressor.decompress(model_path, model): the reference's compressed state dict saved as safetensors,
     decompressed into a fresh dense model."""
