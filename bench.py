@@ -130,6 +130,45 @@ def build_model(layers, shapes, weights):
     return root
 
 
+def fp8_shard_leg(ctb, ModelCompressor, weights, layers, shapes, dev, peak, use_layers=8):
+    """The same module tree (its first `use_layers` decoder layers) as an FP8 per-channel, float-quantized model with
+    calibrated static scales: ModelCompressor.compress_model / decompress_model, each ONE launch over the whole shard
+    (ctb_quantize_fp8_channel_batch / ctb_dequantize_fp8_channel_batch).  Algorithmic bytes: 3 per element each way."""
+    q = ctb.quantization
+    n = min(use_layers, len(layers))
+    per = len(shapes)
+    model = build_model(layers[:n], shapes, [w.clone() for w in weights[:n * per]])
+    qcfg = q.QuantizationConfig(config_groups={"group_0": q.QuantizationScheme(
+        targets=["Linear"], weights=q.QuantizationArgs(num_bits=8, type="float", symmetric=True, strategy="channel"))},
+        ignore=["lm_head"], format="float-quantized")
+    q.apply_quantization_config(model, qcfg)
+    for m in model.modules():
+        if getattr(m, "quantization_scheme", None) is not None and hasattr(m, "weight"):
+            q.calibrate_weight_qparams(m)
+    elems = sum(w.numel() for w in weights[:n * per])
+    mc = ModelCompressor(quantization_config=qcfg)
+    for _ in range(2):
+        mc.compress_model(model)
+        mc.decompress_model(model)
+    torch.cuda.synchronize()
+    mc.engine.record_kernel_times = True
+    mc.engine.kernel_times.clear()
+    launches0, reps = mc.engine.launches, 3
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        mc.compress_model(model)
+        mc.decompress_model(model)
+    torch.cuda.synchronize()
+    wall = (time.perf_counter() - t0) / reps
+    tc = sum(a.elapsed_time(b) for kind, a, b in mc.engine.kernel_times if kind == "compress") / 1e3 / reps
+    td = sum(a.elapsed_time(b) for kind, a, b in mc.engine.kernel_times if kind == "decompress") / 1e3 / reps
+    return {"layers": n, "elements": elems, "launches_per_cycle": (mc.engine.launches - launches0) / reps,
+            "compress_ms": round(tc * 1e3, 3), "compress_frac": round(3 * elems / tc / 1e9 / peak, 3),
+            "decompress_ms": round(td * 1e3, 3), "decompress_frac": round(3 * elems / td / 1e9 / peak, 3),
+            "cycle_wall_ms": round(wall * 1e3, 2),
+            "note": "kernel times from CUDA events around each launch; cycle_wall_ms includes the per-module host walk of the general path"}
+
+
 def configs(pkg):
     """(transform config, quantization config) of the workload, built from `pkg` (this package or the reference)."""
     q, t = pkg.quantization, pkg.transform
@@ -809,6 +848,7 @@ def main():
                 modes[tag] = {"compress_gbs": round(2 * total_elems / ta / 1e9, 1), "frac": round(ALG_BYTES_PER_ELEM * total_elems / ta / 1e9 / peak, 3)}
                 del alt
             out["other_rotation_modes"] = modes
+            out["other_schemes"] = {"fp8_channel_float_quantized": fp8_shard_leg(ctb, ModelCompressor, weights, my_layers, shapes, dev, peak)}
         arm = None
         if world == 1 and not args.no_cpu_baseline:
             arm = CpuArm()
