@@ -36,15 +36,15 @@ int after_launch(const char *what) {
 
 int sm_count() {
     // one cached value per device index
-    static int cached[64] = {0};
+    static std::atomic<int> cached[64];  // zero-initialised; two threads racing on a first call store the same value
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
-    if (cached[dev] == 0) {
-        int n = 0;
+    int n = cached[dev].load(std::memory_order_relaxed);
+    if (n == 0) {
         if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-        cached[dev] = n;
+        cached[dev].store(n, std::memory_order_relaxed);
     }
-    return cached[dev];
+    return n;
 }
 
 }  // namespace ctb
