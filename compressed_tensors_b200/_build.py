@@ -13,7 +13,7 @@ from concurrent.futures import ThreadPoolExecutor
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libctb200.so")
-SOURCES = ["ctb_api.cu", "ctb_quant.cu", "ctb_qparams.cu", "ctb_pack.cu", "ctb_sparse.cu", "ctb_fused_sparse.cu", "ctb_fp8_batch.cu", "ctb_hadamard.cu", "ctb_rotquant_tc.cu", "ctb_marlin24.cu"]
+SOURCES = ["ctb_api.cu", "ctb_quant.cu", "ctb_qparams.cu", "ctb_pack.cu", "ctb_sparse.cu", "ctb_fused_sparse.cu", "ctb_fp8_batch.cu", "ctb_fp4_batch.cu", "ctb_hadamard.cu", "ctb_rotquant_tc.cu", "ctb_marlin24.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     # IEEE semantics everywhere: no fast-math, exact division and square root, denormals kept

@@ -164,6 +164,9 @@ def _prod(shape) -> int:
     return n
 
 
+_PLANNED_KINDS = ("rotq4", "q4", "dq4", "q8c", "dq8c", "q4f", "dq4f")  # outputs known without running the step
+
+
 class _Step:
     """A few hundred megabytes of one pass over host-resident jobs: upload, kernels, download."""
 
@@ -281,6 +284,11 @@ class CodecEngine:
             if zp is None or (zp.numel() == rows and zp.dtype in L.DT):
                 job.kind = "q8c"
             return
+        if self._is_nvfp4(job, fmt, args, rows, cols) and w.dtype == torch.bfloat16 and not job.transforms:
+            zp, s = job.state.get("weight_zero_point"), job.state["weight_scale"]
+            if zp is None or (tuple(zp.shape) == tuple(s.shape) and zp.dtype in L.DT):
+                job.kind = "q4f"
+            return
         if fmt != CompressionFormat.pack_quantized.value or not is_w4a16_g128(args) or w.dtype != torch.bfloat16 or cols % 128:
             return
         if job.sparse and "weight" in job.compressor.compression_param_names:
@@ -304,6 +312,17 @@ class CodecEngine:
                 and args.num_bits == 8 and args.strategy == QuantizationStrategy.CHANNEL and not args.dynamic
                 and not job.sparse and cols % 8 == 0 and s is not None and s.dtype == torch.bfloat16 and s.numel() == rows
                 and job.state.get("weight_g_idx") is None and job.state.get("weight_global_scale") is None)
+
+    @staticmethod
+    def _is_nvfp4(job: Job, fmt, args, rows: int, cols: int) -> bool:
+        """NVFP4 (e2m1 codes, e4m3 group-16 scales, fp32 global scale) of a 2-D weight through the nvfp4-pack-quantized
+        compressor, not stacked with a sparsity compressor: what the whole-shard NVFP4 entry points take."""
+        s, gs = job.state.get("weight_scale"), job.state.get("weight_global_scale")
+        return (fmt == CompressionFormat.nvfp4_pack_quantized.value and args is not None and args.type == QuantizationType.FLOAT
+                and args.num_bits == 4 and args.strategy == QuantizationStrategy.TENSOR_GROUP and args.group_size == 16
+                and not args.dynamic and not job.sparse and cols % 16 == 0 and s is not None and s.dtype == torch.float8_e4m3fn
+                and tuple(s.shape) == (rows, cols // 16) and gs is not None and gs.dtype == torch.float32 and gs.numel() == 1
+                and job.state.get("weight_g_idx") is None)
 
     def _compress_on_device(self, jobs: List[Job], dev: torch.device) -> None:
         """All jobs hold device tensors of `dev`; the current stream is the one to launch on.  Fills job.out
@@ -361,6 +380,22 @@ class CodecEngine:
             self.launches += 1
             for j, o, shp in zip(group, outs, shapes):
                 j.out = {"weight": o}
+                j.shape, j.quantized = shp, True
+        group = [j for j in jobs if j.kind == "q4f"]
+        if group:
+            shapes = [tuple(j.state["weight"].shape) for j in group]
+            codes = _Arena(sum(_up(r * c // 2) for r, c in shapes), dev)
+            outs = [codes.take((r, c // 2), torch.uint8) for r, c in shapes]
+            table = _table([j.state["weight"].contiguous() for j in group], outs,
+                           [j.state["weight_scale"].contiguous() for j in group], shapes)
+            gss = [j.state["weight_global_scale"].contiguous() for j in group]
+            zps = [j.state.get("weight_zero_point") for j in group]
+            zps = [None if z is None else z.contiguous() for z in zps]
+            with self._timed("compress", dev):
+                ops.quantize_fp4_g16_batch(_table_ptr(table), gss, zps, device=dev)
+            self.launches += 1
+            for j, o, shp in zip(group, outs, shapes):
+                j.out = {"weight_packed": o}
                 j.shape, j.quantized = shp, True
         for j in jobs:
             if j.kind == "generic":
@@ -436,6 +471,10 @@ class CodecEngine:
             job.kind, job.shape = "dq8c", tuple(q.shape)
             return
         p, s = job.state.get("weight_packed"), job.state.get("weight_scale")
+        if (p is not None and p.ndim == 2 and p.dtype == torch.uint8 and job.state.get("weight_zero_point") is None
+                and self._is_nvfp4(job, fmt, job.scheme.weights, p.shape[0], 2 * p.shape[1])):
+            job.kind, job.shape = "dq4f", (p.shape[0], 2 * p.shape[1])
+            return
         if (fmt != CompressionFormat.pack_quantized.value or not is_w4a16_g128(job.scheme.weights) or p is None or s is None
                 or p.dtype != torch.int32 or s.dtype != torch.bfloat16 or p.ndim != 2 or s.ndim != 2):
             return
@@ -470,6 +509,19 @@ class CodecEngine:
             stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
             with self._timed("decompress", dev):
                 L.check(L.lib().ctb_dequantize_fp8_channel_batch(_table_ptr(table), L.i32(len(group)), stream))
+            self.launches += 1
+            for j, o in zip(group, outs):
+                j.out = {"weight": o}
+        group = [j for j in jobs if j.kind == "dq4f"]
+        if group:
+            shapes = [j.shape for j in group]
+            dense = _Arena(sum(_up(r * c * 2) for r, c in shapes), dev)
+            outs = [dense.take((r, c), torch.bfloat16) for r, c in shapes]
+            table = _table([j.state["weight_packed"].contiguous() for j in group], outs,
+                           [j.state["weight_scale"].contiguous() for j in group], shapes)
+            gss = [j.state["weight_global_scale"].contiguous() for j in group]
+            with self._timed("decompress", dev):
+                ops.dequantize_fp4_g16_batch(_table_ptr(table), gss, device=dev)
             self.launches += 1
             for j, o in zip(group, outs):
                 j.out = {"weight": o}
@@ -591,7 +643,7 @@ class CodecEngine:
             step = _Step(direction, group, dev, work, sparse_compress, need=2 * sum(weight_of(j) for j in group))
             step.feeds = [self._inputs_of(j, direction) for j in group]
             step.reads = {h.untyped_storage().data_ptr() for f in step.feeds for h in f.values()}
-            if all(j.kind in ("rotq4", "q4", "dq4", "q8c", "dq8c") for j in group) and sparse_compress is None:
+            if all(j.kind in _PLANNED_KINDS for j in group) and sparse_compress is None:
                 self._plan(step)
                 self._queue.append(step)
                 # Deferred: hold the step back so that a pass requested later can be interleaved with this one; the
@@ -613,6 +665,11 @@ class CodecEngine:
                 r, c = j.state["weight"].shape
                 j.out = {}
                 specs.append((j, j.out, "weight", (r, c), torch.float8_e4m3fn))
+                j.shape, j.quantized = (r, c), True
+            elif step.direction == "compress" and j.kind == "q4f":
+                r, c = j.state["weight"].shape
+                j.out = {}
+                specs.append((j, j.out, "weight_packed", (r, c // 2), torch.uint8))
                 j.shape, j.quantized = (r, c), True
             elif step.direction == "compress":
                 r, c = j.state["weight"].shape

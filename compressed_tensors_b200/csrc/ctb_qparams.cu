@@ -292,10 +292,12 @@ __global__ void __launch_bounds__(kThreads) qparams_kernel(const void *mins, con
     }
 }
 
-// helpers.py:414-434
+// helpers.py:414-434.  The reference writes `448 * 6 / amax` with a Python scalar on the left, which torch evaluates
+// as amax.reciprocal() * 2688 (Tensor.__rtruediv__): the reciprocal is rounded to the min/max dtype before the product is.
 __global__ void gparam_kernel(const void *mn_p, const void *mx_p, int M, float *out) {
     float mn = fminf(load_f32(mn_p, M, 0), 0.0f), mx = fmaxf(load_f32(mx_p, M, 0), 0.0f);
-    out[0] = round_to_rt(M, __fdiv_rn(2688.0f, fmaxf(fabsf(mn), fabsf(mx))));
+    const float r = round_to_rt(M, __frcp_rn(fmaxf(fabsf(mn), fabsf(mx))));
+    out[0] = round_to_rt(M, __fmul_rn(r, 2688.0f));
 }
 
 // quantization/utils/mxfp4_utils.py.  MODE 0: round_to_power_2 (bf16 bits in, bf16 bits out); MODE 1:

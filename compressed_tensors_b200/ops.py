@@ -16,7 +16,8 @@ __all__ = [
     "pack_int32", "unpack_int32", "pack_fp4", "unpack_fp4", "pack_bitmasks", "unpack_bitmasks",
     "sparse24_mask", "sparse24_compress", "quantize_fp8_sparse24", "sparse24_decompress", "bitmask_compress", "bitmask_decompress", "hadamard",
     "absmax_quantize", "rotate_quantize_int4_batch", "rotate_quantize_int4_batch_bounded", "quantize_pack_int4_batch",
-    "unpack_dequantize_int4_batch", "quantize_fp8_channel_batch", "dequantize_fp8_channel_batch", "tensor_table", "QINT", "QFLOAT",
+    "unpack_dequantize_int4_batch", "quantize_fp8_channel_batch", "dequantize_fp8_channel_batch",
+    "quantize_fp4_g16_batch", "dequantize_fp4_g16_batch", "tensor_table", "QINT", "QFLOAT",
 ]
 
 _CODEC = {"dtype": CODE_DTYPE, "pack32": CODE_PACK32, "fp4x2": CODE_FP4X2}
@@ -522,6 +523,30 @@ def dequantize_fp8_channel_batch(table, device=None):
     weights out), as one launch."""
     stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
     check(lib().ctb_dequantize_fp8_channel_batch(table, i32(len(table)), stream))
+
+
+def _pointer_array(tensors):
+    return (ctypes.c_void_p * len(tensors))(*[None if t is None else t.data_ptr() for t in tensors])
+
+
+def quantize_fp4_g16_batch(table, global_scales, zero_points=None, device=None):
+    """NVFP4 quantize + pack (e4m3 group-16 scales, fp32 global scale per tensor) of every tensor in `table` (bf16
+    weights in, uint8 pairs of e2m1 codes out, scales read), as one launch."""
+    stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+    zps, zdt = None, 0
+    if zero_points is not None and any(z is not None for z in zero_points):
+        dts = {z.dtype for z in zero_points if z is not None}
+        if len(dts) != 1 or next(iter(dts)) not in DT:
+            raise TypeError("zero points of one call must share one supported dtype")
+        zdt, zps = DT[next(iter(dts))], _pointer_array(zero_points)
+    check(lib().ctb_quantize_fp4_g16_batch(table, i32(len(global_scales)), _pointer_array(global_scales), zps, i32(zdt), stream))
+
+
+def dequantize_fp4_g16_batch(table, global_scales, device=None):
+    """unpack + dequantize NVFP4 (e4m3 group-16 scales, fp32 global scale, no zero point) of every tensor in `table`
+    (uint8 code pairs in, bf16 weights out), as one launch."""
+    stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+    check(lib().ctb_dequantize_fp4_g16_batch(table, i32(len(global_scales)), _pointer_array(global_scales), stream))
 
 
 def unpack_dequantize_int4_batch(table, device=None):

@@ -326,6 +326,18 @@ int ctb_quantize_fp8_channel_batch(const ctb_tensor_ref *tensors, int32_t count,
  * naive_quantized.py:113-140).  t.in = e4m3 [rows, cols], t.out = bf16 [rows, cols], t.scale = bf16 [rows]. */
 int ctb_dequantize_fp8_channel_batch(const ctb_tensor_ref *tensors, int32_t count, void *stream);
 
+/* Whole-shard NVFP4: ctb_quantize(codec FP4X2, num_bits 4, group 16, e4m3 scales, fp32 global scale) for every tensor
+ * of the table (quantized_compressors/base.py:91-122 calling fp4_quantized.py:84-105 per weight).  t.in = dense bf16
+ * weight [rows, cols], cols % 16 == 0, t.out = uint8 [rows, cols/2], t.scale = e4m3 [rows, cols/16] (read).
+ * global_scales: `count` device pointers to fp32 [1].  zero_points: NULL, or `count` device pointers
+ * ([rows, cols/16] of zp_dtype each, NULL entries allowed). */
+int ctb_quantize_fp4_g16_batch(const ctb_tensor_ref *tensors, int32_t count, const void *const *global_scales,
+                               const void *const *zero_points, int32_t zp_dtype, void *stream);
+/* ctb_dequantize(codec FP4X2, group 16, e4m3 scales, fp32 global scale, no zero point) for every tensor
+ * (base.py:190-237 calling fp4_quantized.py:108-132).  t.in = uint8 [rows, cols/2], t.out = bf16 [rows, cols]. */
+int ctb_dequantize_fp4_g16_batch(const ctb_tensor_ref *tensors, int32_t count, const void *const *global_scales,
+                                 void *stream);
+
 /* ---- staging memory of the host <-> device pipeline ------------------------------------------------------
  * The reference keeps a state dict in ordinary host memory and never leaves the CPU
  * (compressors/quantized_compressors/base.py:74, :125 compression_device="cpu").  Here host-resident tensors are

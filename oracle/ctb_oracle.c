@@ -312,13 +312,14 @@ int orc_calculate_qparams(const void *mins, const void *maxs, int M, int64_t n, 
     return 0;
 }
 
-/* helpers.py:414-434 generate_gparam: 448*6 / amax computed in the min/max dtype, then fp32 */
+/* helpers.py:414-434 generate_gparam: `448 * 6 / amax` with a Python scalar on the left, which torch evaluates as
+ * amax.reciprocal() * 2688 (Tensor.__rtruediv__): two roundings in the min/max dtype, then fp32 */
 float orc_generate_gparam(const void *mn_p, const void *mx_p, int M) {
     float mn = load_as_f32(mn_p, M, 0), mx = load_as_f32(mx_p, M, 0);
     mn = mn < 0.0f ? mn : 0.0f;
     mx = mx > 0.0f ? mx : 0.0f;
     float mvp = fmaxf(fabsf(mn), fabsf(mx));
-    return round_to(M, 2688.0f / mvp);
+    return round_to(M, round_to(M, 1.0f / mvp) * 2688.0f);
 }
 
 /* ------------------------------------------------------------ int32 packing */

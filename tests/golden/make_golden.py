@@ -592,6 +592,22 @@ def toy_llama(seed: int, dtype=torch.bfloat16):
     return m
 
 
+def gen_gparam_all():
+    """generate_gparam for every positive finite bf16 and fp16 maximum (min = 0) and a float32 sample: the expression
+    `FP8 max * FP4 max / amax` has a Python scalar on the left, and what torch does with that is part of the result."""
+    out = {}
+    bf = torch.arange(0, 0x7F80, dtype=torch.int32).to(torch.int16).view(torch.bfloat16)
+    fh = torch.arange(0, 0x7C00, dtype=torch.int32).to(torch.int16).view(torch.float16)
+    gen = torch.Generator().manual_seed(77)
+    f32 = torch.cat([torch.rand(2048, generator=gen) * 4 + 1e-4, torch.randn(2048, generator=gen).abs() * 0.02 + 1e-7])
+    for tag, mx in (("bf16", bf), ("f16", fh), ("f32", f32)):
+        res = torch.cat([generate_gparam(torch.zeros((), dtype=mx.dtype), m) for m in mx])
+        out[tag] = {"max": mx, "global_scale": res}
+    # a negative minimum that dominates
+    out["neg"] = {"min": -bf[1000:1100], "global_scale": torch.cat([generate_gparam(-m, m / 2) for m in bf[1000:1100]])}
+    torch.save(out, os.path.join(OUT, "gparam_all.pt"))
+
+
 def gen_model_compressor():
     """ModelCompressor on the toy model, the way a calibrated checkpoint is made: apply_transform_config (random Hadamard,
     block 128, weight_input) -> apply_quantization_config (W4A16 group 128) -> min-max scales through calculate_qparams ->
@@ -624,9 +640,13 @@ def gen_model_compressor():
             if scheme is None or scheme.weights is None:
                 continue
             a, w = scheme.weights, mod.weight.data
-            g = a.group_size if a.strategy == "group" else w.shape[1]
+            g = a.group_size if a.strategy in ("group", "tensor_group") else w.shape[1]
             mn, mx = group_minmax(w, g)
-            s, z = calculate_qparams(mn, mx, a)
+            gs = None
+            if a.strategy == "tensor_group":  # NVFP4: the fp32 global scale first, the e4m3 group scales under it
+                gs = generate_gparam(w.min().reshape(1), w.max().reshape(1))
+                update_parameter_data(mod, gs.reshape(mod.weight_global_scale.shape).to(mod.weight_global_scale.dtype), "weight_global_scale")
+            s, z = calculate_qparams(mn, mx, a, global_scale=gs)
             update_parameter_data(mod, s.reshape(mod.weight_scale.shape).to(mod.weight_scale.dtype), "weight_scale")
             if hasattr(mod, "weight_zero_point"):
                 update_parameter_data(mod, z.reshape(mod.weight_zero_point.shape).to(mod.weight_zero_point.dtype), "weight_zero_point")
@@ -698,6 +718,27 @@ def gen_model_compressor():
     # everything that is not a quantized weight (norms, embeddings, lm_head, scales) already sits in case 2
     out["fp8_channel"]["compressed"] = {k: v for k, v in compressed.items() if v.dtype == torch.float8_e4m3fn}
     out["fp8_channel"]["compressed_keys"] = {k: (str(v.dtype), tuple(v.shape)) for k, v in compressed.items()}
+
+    # ---- case 4: the same weights as NVFP4 (nvfp4-pack-quantized); `original` is case 2's
+    model = toy_llama(32)
+    model.load_state_dict(original)
+    qcfg4 = QuantizationConfig(config_groups={"group_0": QuantizationScheme(
+        targets=["Linear"], weights=QuantizationArgs(num_bits=4, type="float", symmetric=True, strategy="tensor_group", group_size=16))},
+        ignore=["lm_head"], format="nvfp4-pack-quantized")
+    apply_quantization_config(model, qcfg4)
+    calibrate(model)
+    mc = ModelCompressor(quantization_config=copy.deepcopy(qcfg4))
+    compressed = mc.compress(model)
+    inplace = copy.deepcopy(model)
+    mc2 = ModelCompressor(quantization_config=copy.deepcopy(qcfg4))
+    mc2.compress_model(inplace)
+    compressed_inplace = {k: v.clone() for k, v in inplace.state_dict().items()}
+    mc2.decompress_model(inplace)
+    decompressed = {k: v.clone() for k, v in inplace.state_dict().items()}
+    out["nvfp4"] = slim({}, compressed, compressed_inplace, decompressed)
+    out["nvfp4"]["compressed"] = {k: v for k, v in compressed.items()
+                                  if k.endswith(("weight_packed", "weight_scale", "weight_global_scale"))}
+    out["nvfp4"]["compressed_keys"] = {k: (str(v.dtype), tuple(v.shape)) for k, v in compressed.items()}
     torch.save(out, os.path.join(OUT, "model_compressor.pt"))
 
 
@@ -705,7 +746,7 @@ if __name__ == "__main__":
     only = sys.argv[2] if len(sys.argv) > 2 else None  # e.g. "mxfp4": regenerate one fixture
     for name, fn in (("int_quant", gen_int), ("fp8_quant", gen_fp8), ("nvfp4", gen_nvfp4), ("sparse", gen_sparse),
                      ("hadamard", gen_hadamard), ("hadamard_online", gen_hadamard_online), ("hadamard_randomize", gen_hadamard_randomize), ("hadamard_embedding", gen_hadamard_embedding), ("mxfp4", gen_mxfp4), ("marlin24", gen_marlin24),
-                     ("fp4_pack_all", gen_fp4_pack_all), ("hadamard_full", gen_hadamard_full), ("forward_quantize", gen_forward_quantize), ("model_compressor", gen_model_compressor)):
+                     ("fp4_pack_all", gen_fp4_pack_all), ("hadamard_full", gen_hadamard_full), ("forward_quantize", gen_forward_quantize), ("gparam_all", gen_gparam_all), ("model_compressor", gen_model_compressor)):
         if only is None or only == name:
             fn()
     for f in sorted(os.listdir(OUT)):

@@ -298,3 +298,19 @@ def test_empty_and_degenerate_tensors(ops):
     assert v.numel() == o.numel() and bool((b == 255).all()) and int(r[-1]) == 511 * 4096
     assert torch.equal(ops.bitmask_decompress(v, b, (512, 4096)), o)
 
+
+
+def test_generate_gparam_sweep(golden):
+    """The device kernel against the reference on every 5th positive bf16 / fp16 maximum, the float32 sample and
+    minima that dominate (the scalar-on-the-left division of the reference rounds twice)."""
+    from compressed_tensors_b200 import ops
+
+    g = golden("gparam_all")
+    for tag in ("bf16", "f16", "f32"):
+        mx, want = g[tag]["max"][::5].cuda(), g[tag]["global_scale"][::5]
+        zero = torch.zeros((), dtype=mx.dtype, device="cuda")
+        got = torch.cat([ops.generate_gparam(zero, m) for m in mx])
+        assert_bit_equal(got.cpu(), want, f"global scale, {tag} maxima")
+    mn, want = g["neg"]["min"].cuda(), g["neg"]["global_scale"]
+    got = torch.cat([ops.generate_gparam(m, -m / 2) for m in mn])
+    assert_bit_equal(got.cpu(), want, "global scale, dominated by the minimum")

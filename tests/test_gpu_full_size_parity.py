@@ -298,3 +298,41 @@ def test_fp8_channel_batch_equals_oracle(ops, orc, canary):
         nan = got.float().isnan() & ref.float().isnan()  # a NaN code decodes to a NaN; its payload is the platform's
         assert_bit_equal(torch.where(nan, torch.zeros_like(got), got), torch.where(nan, torch.zeros_like(ref), ref),
                          f"dequantized tensor {i} {shapes[i]}")
+
+
+def test_nvfp4_batch_equals_oracle(ops, orc, canary):
+    """The whole-shard NVFP4 entry points on a ragged table (a tensor smaller than one unit, partial last units, a
+    different global scale per tensor so that the decompress kernel's scale table is rebuilt, zero points present and
+    absent, signed zeros and values beyond the grid): codes and dequantized values against the oracle."""
+    shapes = [(8, 128), (4096, 4096), (1024, 4096), (33, 272), (14336, 4096)]
+    ws = [weights(r, c, 90 + i, std=0.02 * (1 + i)) for i, (r, c) in enumerate(shapes)]
+    ws[3][0, :8] = torch.tensor([0.5, -0.5, 3.0, -3.0, 0.0, -0.0, 1.0, -1.0]).to(torch.bfloat16)
+    ws[3][4] = -0.0
+    scales, gss, zps, want, deq = [], [], [], [], []
+    for i, w in enumerate(ws):
+        kw = dict(qtype=orc.QFLOAT, bits=4, col_group=16, row_group=1, scale_row_stride=w.shape[1] // 16)
+        tmn, tmx = orc.minmax(w, w.shape[0], w.shape[1])
+        gs = orc.generate_gparam(tmn, tmx)
+        mn, mx = orc.minmax(w, 1, 16)
+        scale, zp = orc.calculate_qparams(mn, mx, qtype=orc.QFLOAT, bits=4, symmetric=True, global_scale=gs)
+        z = zp if i in (1, 3) else None
+        packed = orc.pack_fp4(orc.quantize(w, scale, z, out_dtype=torch.bfloat16, global_scale=gs, **kw))
+        scales.append(scale)
+        gss.append(gs)
+        zps.append(z)
+        want.append(packed)
+        deq.append(orc.dequantize(orc.unpack_fp4(packed, *w.shape), scale, None, out_dtype=torch.bfloat16, global_scale=gs, **kw))
+    dev = torch.device("cuda", 0)
+    with canary():
+        dw = [w.cuda() for w in ws]
+        ds = [s.cuda() for s in scales]
+        dg = [g.cuda().reshape(1) for g in gss]
+        dz = [None if z is None else z.cuda() for z in zps]
+        out = [torch.empty((r, c // 2), dtype=torch.uint8, device="cuda") for r, c in shapes]
+        back = [torch.empty((r, c), dtype=torch.bfloat16, device="cuda") for r, c in shapes]
+        ops.quantize_fp4_g16_batch(ops.tensor_table(dw, out, ds, shapes), dg, dz, dev)
+        ops.dequantize_fp4_g16_batch(ops.tensor_table(out, back, ds, shapes), dg, dev)
+        torch.cuda.synchronize()
+    for i in range(len(ws)):
+        assert_bit_equal(out[i].cpu(), want[i], f"packed codes of tensor {i} {shapes[i]}")
+        assert_bit_equal(back[i].cpu(), deq[i], f"dequantized tensor {i} {shapes[i]}")

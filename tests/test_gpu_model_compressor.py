@@ -320,6 +320,44 @@ def test_fp8_channel_whole_shard_matches_reference(golden, where):
         assert_bit_equal(got[k].cpu(), v, f"decompress_model ({where}): {k}")
 
 
+@pytest.mark.parametrize("where", ["cuda", "cpu"])
+def test_nvfp4_whole_shard_matches_reference(golden, where):
+    """NVFP4 (nvfp4-pack-quantized: e2m1 codes, e4m3 group-16 scales under an fp32 global scale): every quantized
+    weight goes through the whole-shard NVFP4 entry points and equals the reference's bit for bit."""
+    from compressed_tensors_b200.compressors import ModelCompressor
+    from compressed_tensors_b200.quantization import QuantizationArgs, QuantizationConfig, QuantizationScheme, apply_quantization_config
+
+    both = golden("model_compressor")
+    g, original = both["nvfp4"], both["fp8_sparse24"]["original"]
+    qcfg = QuantizationConfig(config_groups={"group_0": QuantizationScheme(
+        targets=["Linear"], weights=QuantizationArgs(num_bits=4, type="float", symmetric=True, strategy="tensor_group", group_size=16))},
+        ignore=["lm_head"], format="nvfp4-pack-quantized")
+    model = toy_llama(original, device=where)
+    apply_quantization_config(model, qcfg)
+    calibrate(model)
+    mc = ModelCompressor(quantization_config=copy.deepcopy(qcfg))
+    sd = mc.compress(model)
+    assert {k: (str(v.dtype), tuple(v.shape)) for k, v in sd.items()} == g["compressed_keys"]
+    for k, v in g["compressed"].items():
+        assert_bit_equal(sd[k].cpu(), v, f"compress ({where}): {k}")
+    before = mc.engine.launches
+    mc.compress_model(model)
+    if where == "cuda":
+        assert mc.engine.launches - before == 1, "one launch for every quantized weight of the model"
+    got = dict(model.state_dict())
+    assert {k: (str(v.dtype), tuple(v.shape)) for k, v in got.items()} == g["inplace_keys"]
+    for k, v in g["compressed"].items():
+        assert_bit_equal(got[k].cpu(), v, f"compress_model ({where}): {k}")
+    before = mc.engine.launches
+    mc.decompress_model(model)
+    if where == "cuda":
+        assert mc.engine.launches - before == 1
+    got = dict(model.state_dict())
+    assert {k: (str(v.dtype), tuple(v.shape)) for k, v in got.items()} == g["decompressed_keys"]
+    for k, v in g["decompressed"].items():
+        assert_bit_equal(got[k].cpu(), v, f"decompress_model ({where}): {k}")
+
+
 def test_decompress_from_disk(golden, tmp_path):
     """ModelCompressor.decompress(model_path, model): the reference's compressed state dict saved as safetensors,
     decompressed into a fresh dense model."""

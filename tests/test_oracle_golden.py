@@ -274,3 +274,17 @@ def test_marlin24_steps(golden):
         assert_bit_equal(orc.marlin24_pack_scales(d["scale"], grouped), d["scale_packed"], name)
         assert torch.equal(meta.reshape(meta.shape[1] // 2, meta.shape[0] * 2), d["meta"]), name
 
+
+
+def test_generate_gparam_every_bf16_and_f16_maximum(golden):
+    """`448 * 6 / amax` with the scalar on the left is amax.reciprocal() * 2688 in torch: two roundings in the min/max
+    dtype.  Every positive finite bf16 and fp16 maximum and a float32 sample, against the reference's outputs."""
+    g = golden("gparam_all")
+    for tag in ("bf16", "f16", "f32"):
+        mx, want = g[tag]["max"], g[tag]["global_scale"]
+        zero = torch.zeros((), dtype=mx.dtype)
+        got = torch.cat([orc.generate_gparam(zero, m) for m in mx])
+        assert_bit_equal(got, want, f"global scale, {tag} maxima")
+    mn, want = g["neg"]["min"], g["neg"]["global_scale"]
+    got = torch.cat([orc.generate_gparam(m, -m / 2) for m in mn])
+    assert_bit_equal(got, want, "global scale, dominated by the minimum")
