@@ -130,17 +130,22 @@ def build_model(layers, shapes, weights):
     return root
 
 
-def fp8_shard_leg(ctb, ModelCompressor, weights, layers, shapes, dev, peak, use_layers=8):
-    """The same module tree (its first `use_layers` decoder layers) as an FP8 per-channel, float-quantized model with
-    calibrated static scales: ModelCompressor.compress_model / decompress_model, each ONE launch over the whole shard
-    (ctb_quantize_fp8_channel_batch / ctb_dequantize_fp8_channel_batch).  Algorithmic bytes: 3 per element each way."""
+def scheme_shard_leg(scheme, ctb, ModelCompressor, weights, layers, shapes, dev, peak, use_layers=8):
+    """The same module tree (its first `use_layers` decoder layers) as a calibrated model of another scheme:
+    "fp8" = FP8 per-channel float-quantized (3 algorithmic bytes per element each way), "nvfp4" = NVFP4
+    nvfp4-pack-quantized (2.5625).  ModelCompressor.compress_model / decompress_model are each ONE launch over the whole
+    shard (ctb_quantize_fp8_channel_batch / ctb_quantize_fp4_g16_batch and their inverses)."""
     q = ctb.quantization
     n = min(use_layers, len(layers))
     per = len(shapes)
     model = build_model(layers[:n], shapes, [w.clone() for w in weights[:n * per]])
-    qcfg = q.QuantizationConfig(config_groups={"group_0": q.QuantizationScheme(
-        targets=["Linear"], weights=q.QuantizationArgs(num_bits=8, type="float", symmetric=True, strategy="channel"))},
-        ignore=["lm_head"], format="float-quantized")
+    if scheme == "fp8":
+        wargs, fmt, alg = q.QuantizationArgs(num_bits=8, type="float", symmetric=True, strategy="channel"), "float-quantized", 3.0
+    else:
+        wargs = q.QuantizationArgs(num_bits=4, type="float", symmetric=True, strategy="tensor_group", group_size=16)
+        fmt, alg = "nvfp4-pack-quantized", 2.5625
+    qcfg = q.QuantizationConfig(config_groups={"group_0": q.QuantizationScheme(targets=["Linear"], weights=wargs)},
+                                ignore=["lm_head"], format=fmt)
     q.apply_quantization_config(model, qcfg)
     for m in model.modules():
         if getattr(m, "quantization_scheme", None) is not None and hasattr(m, "weight"):
@@ -163,8 +168,8 @@ def fp8_shard_leg(ctb, ModelCompressor, weights, layers, shapes, dev, peak, use_
     tc = sum(a.elapsed_time(b) for kind, a, b in mc.engine.kernel_times if kind == "compress") / 1e3 / reps
     td = sum(a.elapsed_time(b) for kind, a, b in mc.engine.kernel_times if kind == "decompress") / 1e3 / reps
     return {"layers": n, "elements": elems, "launches_per_cycle": (mc.engine.launches - launches0) / reps,
-            "compress_ms": round(tc * 1e3, 3), "compress_frac": round(3 * elems / tc / 1e9 / peak, 3),
-            "decompress_ms": round(td * 1e3, 3), "decompress_frac": round(3 * elems / td / 1e9 / peak, 3),
+            "compress_ms": round(tc * 1e3, 3), "compress_frac": round(alg * elems / tc / 1e9 / peak, 3),
+            "decompress_ms": round(td * 1e3, 3), "decompress_frac": round(alg * elems / td / 1e9 / peak, 3),
             "cycle_wall_ms": round(wall * 1e3, 2),
             "note": "kernel times from CUDA events around each launch; cycle_wall_ms includes the per-module host walk of the general path"}
 
@@ -848,7 +853,9 @@ def main():
                 modes[tag] = {"compress_gbs": round(2 * total_elems / ta / 1e9, 1), "frac": round(ALG_BYTES_PER_ELEM * total_elems / ta / 1e9 / peak, 3)}
                 del alt
             out["other_rotation_modes"] = modes
-            out["other_schemes"] = {"fp8_channel_float_quantized": fp8_shard_leg(ctb, ModelCompressor, weights, my_layers, shapes, dev, peak)}
+            out["other_schemes"] = {
+                "fp8_channel_float_quantized": scheme_shard_leg("fp8", ctb, ModelCompressor, weights, my_layers, shapes, dev, peak),
+                "nvfp4_pack_quantized": scheme_shard_leg("nvfp4", ctb, ModelCompressor, weights, my_layers, shapes, dev, peak)}
         arm = None
         if world == 1 and not args.no_cpu_baseline:
             arm = CpuArm()

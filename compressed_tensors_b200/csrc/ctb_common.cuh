@@ -45,6 +45,11 @@ inline int promote(int a, int b) { return a == b ? a : CTB_F32; }
 
 // grid for a grid-stride kernel: enough blocks to cover `work` units of `per_block`, capped at a
 // whole number of waves of resident blocks
+// ctb_fp4_batch.cu: NVFP4 quantize + pack of ONE tensor with given e4m3 group-16 scales (the whole-shard kernel on a
+// table of one entry); x 16-byte and out 8-byte aligned, cols % 16 == 0
+int quant_fp4_g16_one(const void *x, const void *scale, const float *gs, const void *zp, int zdt, int64_t rows, int64_t cols, void *out,
+                      cudaStream_t st);
+
 inline int grid_for(int64_t work, int64_t per_block, int blocks_per_sm) {
     int64_t need = cdiv(work, per_block);
     int64_t cap = (int64_t)sm_count() * blocks_per_sm;

@@ -1,8 +1,8 @@
 // Whole-shard NVFP4: every Linear weight of a shard in ONE grid per direction, the per-tensor loops of
 // compressors/quantized_compressors/base.py:91-134 (compress -> fp4_quantized.py:84-105 compress_weight: quantize with
 // e4m3 group-16 scales under an fp32 global scale, then pack_fp4_to_uint8) and base.py:190-237 (decompress_weight:
-// unpack_fp4_from_uint8, dequantize).  The arithmetic is the vec8 tier's of ctb_quantize / ctb_dequantize (same
-// templates), so the bytes are those of the per-tensor calls.
+// unpack_fp4_from_uint8, dequantize).  The arithmetic is that of ctb_quantize / ctb_dequantize and of the fused
+// calibrate kernel (same device functions), so the bytes are those of the per-tensor calls.
 #include "ctb_codec.cuh"
 
 namespace ctb {
@@ -23,46 +23,73 @@ struct F4Batch {
     void *out[kF4BatchMax];
 };
 
-// bf16 -> e2m1 codes, two per byte.  One chunk = 8 elements = half a group; the effective scale of a group is
-// float(e4m3 scale) / global_scale (forward.py:468-469), computed by load_qp exactly as the per-tensor kernel does.
+// bf16 -> e2m1 codes, two per byte.  A lane takes whole groups of 16 elements (32 contiguous bytes in, 8 out), so the
+// effective scale of a group, float(e4m3 scale) / global_scale (forward.py:468-469), is divided once per group.
+// Finite groups with a scale in the normal range and no zero point other than zero go through the reciprocal +
+// Markstein quotient and the saturating e2m1 convert (quant_fp4_codes_f32); everything else through the templates of
+// the per-tensor vec8 tier.
 __global__ void __launch_bounds__(kF4Threads) quant_fp4_g16_batch_kernel(const __grid_constant__ F4Batch B) {
+    constexpr int U = kF4Unroll / 2;  // groups per lane and unit
     const int64_t total = B.ustart[B.count];
     int t = 0;
-    Raw8 raw[kF4Unroll];
-    bool ok[kF4Unroll];
-    uint32_t cbase = 0;
+    uint4 raw[U][2];
+    bool ok[U];
+    uint32_t gbase = 0;
     auto fetch = [&](int64_t unit) {
         while (t + 1 < B.count && unit >= B.ustart[t + 1]) ++t;
-        cbase = (uint32_t)(unit - B.ustart[t]) * (uint32_t)kF4Unit;
+        gbase = (uint32_t)(unit - B.ustart[t]) * (uint32_t)(kF4Unit / 2);
+        const char *ip = (const char *)B.in[t];
+        const uint32_t ngroups = B.nchunks[t] >> 1;
 #pragma unroll
-        for (int u = 0; u < kF4Unroll; ++u) {
-            const uint32_t c = cbase + u * kF4Threads + threadIdx.x;
-            ok[u] = c < B.nchunks[t];
-            if (ok[u]) raw[u] = load_raw<F_BF16>(B.in[t], (int64_t)c);
+        for (int u = 0; u < U; ++u) {
+            const uint32_t g = gbase + u * kF4Threads + threadIdx.x;
+            ok[u] = g < ngroups;
+            if (ok[u]) {
+                // a lane's two halves share a 32-byte sector: let L1 keep it between the two instructions
+                raw[u][0] = __ldg(reinterpret_cast<const uint4 *>(ip + (size_t)g * 32));
+                raw[u][1] = __ldg(reinterpret_cast<const uint4 *>(ip + (size_t)g * 32 + 16));
+            }
         }
     };
     int64_t unit = blockIdx.x;
     if (unit < total) fetch(unit);
     while (unit < total) {
-        Raw8 w[kF4Unroll];
-        bool k[kF4Unroll];
+        uint4 w[U][2];
+        bool k[U];
         const int ct = t;
-        const uint32_t cb = cbase;
+        const uint32_t gb = gbase;
 #pragma unroll
-        for (int u = 0; u < kF4Unroll; ++u) { w[u] = raw[u]; k[u] = ok[u]; }
+        for (int u = 0; u < U; ++u) { w[u][0] = raw[u][0]; w[u][1] = raw[u][1]; k[u] = ok[u]; }
         const int64_t next = unit + gridDim.x;
         if (next < total) fetch(next);
         const void *zp = B.zp[ct];
         const bool has_zp = zp != nullptr;
 #pragma unroll
-        for (int u = 0; u < kF4Unroll; ++u) {
+        for (int u = 0; u < U; ++u) {
             if (!k[u]) continue;
-            const uint32_t c = cb + u * kF4Threads + threadIdx.x;
-            const QP q = load_qp(B.scale[ct], CTB_E4M3, zp, B.zdt, B.gs[ct], (int64_t)(c >> 1));
-            float v[8];
-            decode8<F_BF16>(w[u], v);
-            quant_prepare8<CTB_F32>(v, q, has_zp, q.zp, -6.0f, 6.0f);
-            encode_store8<QK_FP4, F_FP4X2>(B.out[ct], (int64_t)c, v);
+            const uint32_t g = gb + u * kF4Threads + threadIdx.x;
+            const QP q = load_qp(B.scale[ct], CTB_E4M3, zp, B.zdt, B.gs[ct], (int64_t)g);
+            const uint32_t w0[4] = {w[u][0].x, w[u][0].y, w[u][0].z, w[u][0].w};
+            const uint32_t w1[4] = {w[u][1].x, w[u][1].y, w[u][1].z, w[u][1].w};
+            // an element with all exponent bits set (inf, NaN): adding 0x0080 to its magnitude carries into bit 15
+            uint32_t nonfinite = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                nonfinite |= ((w0[i] & 0x7FFF7FFFu) + 0x00800080u) | ((w1[i] & 0x7FFF7FFFu) + 0x00800080u);
+            if (!q.slow && q.zp == 0.0f && (nonfinite & 0x80008000u) == 0) {
+                st_stream8((char *)B.out[ct] + (size_t)g * 8, make_uint2(quant_fp4_codes_f32(w0, q.s, q.r), quant_fp4_codes_f32(w1, q.s, q.r)));
+                continue;
+            }
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                Raw8 r8;
+                r8.a = w[u][h];
+                r8.b = make_uint4(0, 0, 0, 0);
+                float v[8];
+                decode8<F_BF16>(r8, v);
+                quant_prepare8<CTB_F32>(v, q, has_zp, q.zp, -6.0f, 6.0f);
+                encode_store8<QK_FP4, F_FP4X2>(B.out[ct], (int64_t)g * 2 + h, v);
+            }
         }
         unit = next;
     }
@@ -132,7 +159,7 @@ static int fill(F4Batch &B, const ctb_tensor_ref *tensors, const void *const *gl
         if (chunks > 0 && (!r.in || !r.out || !r.scale || !global_scales || !global_scales[base + i]))
             return fail(CTB_EINVAL_NULL, "tensor %d: null buffer", base + i);
         if ((reinterpret_cast<uintptr_t>(r.in) & (in_align - 1)) || (reinterpret_cast<uintptr_t>(r.out) & (out_align - 1)))
-            return fail(CTB_EINVAL_ALIGN, "tensor %d: the bf16 side must be 16-byte, the packed side 4-byte aligned", base + i);
+            return fail(CTB_EINVAL_ALIGN, "tensor %d: the bf16 side must be 16-byte aligned, the packed side 8-byte (quantize) / 4-byte (dequantize)", base + i);
         if (reinterpret_cast<uintptr_t>(global_scales ? global_scales[base + i] : nullptr) & 3u)
             return fail(CTB_EINVAL_ALIGN, "tensor %d: global scale must be 4-byte aligned", base + i);
         B.ustart[i] = units;
@@ -148,6 +175,23 @@ static int fill(F4Batch &B, const ctb_tensor_ref *tensors, const void *const *gl
     return CTB_OK;
 }
 
+int quant_fp4_g16_one(const void *x, const void *scale, const float *gs, const void *zp, int zdt, int64_t rows, int64_t cols, void *out,
+                      cudaStream_t st) {
+    static thread_local F4Batch B;
+    ctb_tensor_ref r;
+    r.in = x;
+    r.out = out;
+    r.scale = const_cast<void *>(scale);
+    r.rows = rows;
+    r.cols = cols;
+    const void *g = gs, *z = zp;
+    int rc = fill(B, &r, &g, zp ? &z : nullptr, zdt, 0, 1, kF4Unit, 16, 8);
+    if (rc) return rc;
+    if (B.ustart[1] == 0) return CTB_OK;
+    quant_fp4_g16_batch_kernel<<<grid_for(B.ustart[1], 1, 8), kF4Threads, 0, st>>>(B);
+    return after_launch("quant_fp4_g16_batch_kernel");
+}
+
 }  // namespace ctb
 
 using namespace ctb;
@@ -159,7 +203,7 @@ extern "C" int ctb_quantize_fp4_g16_batch(const ctb_tensor_ref *tensors, int32_t
     static thread_local F4Batch B;
     for (int32_t base = 0; base < count; base += kF4BatchMax) {
         const int32_t n = count - base < kF4BatchMax ? count - base : kF4BatchMax;
-        int rc = fill(B, tensors, global_scales, zero_points, zp_dtype, base, n, kF4Unit, 16, 4);
+        int rc = fill(B, tensors, global_scales, zero_points, zp_dtype, base, n, kF4Unit, 16, 8);
         if (rc) return rc;
         if (B.ustart[n] == 0) continue;
         quant_fp4_g16_batch_kernel<<<grid_for(B.ustart[n], 1, 8), kF4Threads, 0, as_stream(stream)>>>(B);

@@ -858,6 +858,12 @@ static int run(int mode, const ctb_qdesc *d, const void *in, const void *scale, 
             dequant_fp4_g16_bf16_kernel<<<grid_for(a.chunks, (int64_t)kThreads * 8, 32), kThreads, 0, st>>>(in, (const uint8_t *)scale, gs, a.chunks, out);
             return after_launch("dequant_fp4_g16_bf16_kernel");
         }
+        if (mode == 0 && a.qk == QK_FP4 && a.fin == F_BF16 && a.fout == F_FP4X2 && d->scale_dtype == CTB_E4M3 && gs && flat &&
+            d->col_group == 16 && a.idx32 && (!zp || dtype_size(d->zp_dtype) != 0)) {
+            // NVFP4 with given scales: the whole-shard kernel on a table of one (a lane per group of 16, the effective
+            // scale divided once per group)
+            return quant_fp4_g16_one(in, scale, gs, zp, d->zp_dtype, d->rows, d->cols, out, st);
+        }
         bool handled = false;
         rc = dispatch_lean(mode, a, st, &handled);
         if (handled) return rc;

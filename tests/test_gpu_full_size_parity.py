@@ -316,6 +316,10 @@ def test_nvfp4_batch_equals_oracle(ops, orc, canary):
         mn, mx = orc.minmax(w, 1, 16)
         scale, zp = orc.calculate_qparams(mn, mx, qtype=orc.QFLOAT, bits=4, symmetric=True, global_scale=gs)
         z = zp if i in (1, 3) else None
+        if i == 3:  # a zero point other than zero and infinite inputs take the kernel's general routine
+            z = z.clone()
+            z[9, 0], z[10, 3] = 1.0, -0.5
+            w[11, 5], w[11, 40] = float("inf"), -float("inf")
         packed = orc.pack_fp4(orc.quantize(w, scale, z, out_dtype=torch.bfloat16, global_scale=gs, **kw))
         scales.append(scale)
         gss.append(gs)
