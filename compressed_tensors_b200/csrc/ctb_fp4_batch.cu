@@ -23,75 +23,78 @@ struct F4Batch {
     void *out[kF4BatchMax];
 };
 
-// bf16 -> e2m1 codes, two per byte.  A lane takes whole groups of 16 elements (32 contiguous bytes in, 8 out), so the
-// effective scale of a group, float(e4m3 scale) / global_scale (forward.py:468-469), is divided once per group.
-// Finite groups with a scale in the normal range and no zero point other than zero go through the reciprocal +
+// One chunk by the templates of the per-tensor vec8 tier (any input, any scale, any zero point).  Out of line: it is
+// the rare path and its registers would otherwise set the occupancy of the whole kernel.
+__device__ __noinline__ void quant_fp4_chunk_general(const uint4 *chunk, const void *scale, const void *zp, int zdt, const float *gs, void *out,
+                                                     uint32_t c) {
+    const QP q = load_qp(scale, CTB_E4M3, zp, zdt, gs, (int64_t)(c >> 1));
+    Raw8 r8;
+    r8.a = __ldg(chunk);
+    r8.b = make_uint4(0, 0, 0, 0);
+    float v[8];
+    decode8<F_BF16>(r8, v);
+    quant_prepare8<CTB_F32>(v, q, zp != nullptr, q.zp, -6.0f, 6.0f);
+    encode_store8<QK_FP4, F_FP4X2>(out, (int64_t)c, v);
+}
+
+// bf16 -> e2m1 codes, two per byte.  A lane takes a chunk of 8 elements, half a group, so that every warp instruction
+// moves one contiguous span.  Finite chunks with a scale in the normal range and no zero point other than zero go through the reciprocal +
 // Markstein quotient and the saturating e2m1 convert (quant_fp4_codes_f32); everything else through the templates of
 // the per-tensor vec8 tier.
-__global__ void __launch_bounds__(kF4Threads) quant_fp4_g16_batch_kernel(const __grid_constant__ F4Batch B) {
-    constexpr int U = kF4Unroll / 2;  // groups per lane and unit
+__global__ void __launch_bounds__(kF4Threads, 6) quant_fp4_g16_batch_kernel(const __grid_constant__ F4Batch B) {
+    // (effective scale, its reciprocal) of every possible scale byte of the tensor the block is working on: 256 IEEE
+    // divisions per tensor instead of one per group.  A reciprocal of 0 marks a scale outside the range where the
+    // reciprocal + Markstein quotient is proven (or not finite): those chunks take the general routine.
+    __shared__ float2 tab[256];
+    static_assert(kF4Threads == 256, "one table entry per thread");
     const int64_t total = B.ustart[B.count];
-    int t = 0;
-    uint4 raw[U][2];
-    bool ok[U];
-    uint32_t gbase = 0;
-    auto fetch = [&](int64_t unit) {
+    int t = 0, table_of = -1;
+    for (int64_t unit = blockIdx.x; unit < total; unit += gridDim.x) {
         while (t + 1 < B.count && unit >= B.ustart[t + 1]) ++t;
-        gbase = (uint32_t)(unit - B.ustart[t]) * (uint32_t)(kF4Unit / 2);
-        const char *ip = (const char *)B.in[t];
-        const uint32_t ngroups = B.nchunks[t] >> 1;
+        if (t != table_of) {  // uniform across the block
+            __syncthreads();  // everyone is done with the previous tensor's table
+            const float se = __fdiv_rn(e4m3_to_f32((uint8_t)threadIdx.x), __ldg(B.gs[t]));  // forward.py:468-469
+            const bool fast = fabsf(se) >= 1.0e-30f && fabsf(se) <= 1.0e30f;
+            tab[threadIdx.x] = make_float2(se, fast ? __frcp_rn(se) : 0.0f);
+            __syncthreads();
+            table_of = t;
+        }
+        const uint32_t cbase = (uint32_t)(unit - B.ustart[t]) * (uint32_t)kF4Unit;
+        const uint4 *ip = (const uint4 *)B.in[t];
+        const uint32_t nchunks = B.nchunks[t];
+        const uint8_t *sp = (const uint8_t *)B.scale[t];
+        const void *zp = B.zp[t];
+        char *op = (char *)B.out[t];
+        uint4 w[kF4Unroll];
+        uint32_t sb[kF4Unroll];
+        float zv[kF4Unroll];
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const uint32_t g = gbase + u * kF4Threads + threadIdx.x;
-            ok[u] = g < ngroups;
-            if (ok[u]) {
-                // a lane's two halves share a 32-byte sector: let L1 keep it between the two instructions
-                raw[u][0] = __ldg(reinterpret_cast<const uint4 *>(ip + (size_t)g * 32));
-                raw[u][1] = __ldg(reinterpret_cast<const uint4 *>(ip + (size_t)g * 32 + 16));
+        for (int u = 0; u < kF4Unroll; ++u) {  // all loads first (data, scale byte, zero point): one memory latency per unit
+            const uint32_t c = cbase + u * kF4Threads + threadIdx.x;
+            zv[u] = 0.0f;
+            sb[u] = 0;
+            w[u] = make_uint4(0, 0, 0, 0);
+            if (c < nchunks) {
+                w[u] = ld_stream(ip + c);  // a warp instruction covers 512 contiguous bytes
+                sb[u] = __ldg(sp + (c >> 1));
+                if (zp) zv[u] = load_f32(zp, B.zdt, (int64_t)(c >> 1));
             }
         }
-    };
-    int64_t unit = blockIdx.x;
-    if (unit < total) fetch(unit);
-    while (unit < total) {
-        uint4 w[U][2];
-        bool k[U];
-        const int ct = t;
-        const uint32_t gb = gbase;
 #pragma unroll
-        for (int u = 0; u < U; ++u) { w[u][0] = raw[u][0]; w[u][1] = raw[u][1]; k[u] = ok[u]; }
-        const int64_t next = unit + gridDim.x;
-        if (next < total) fetch(next);
-        const void *zp = B.zp[ct];
-        const bool has_zp = zp != nullptr;
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            if (!k[u]) continue;
-            const uint32_t g = gb + u * kF4Threads + threadIdx.x;
-            const QP q = load_qp(B.scale[ct], CTB_E4M3, zp, B.zdt, B.gs[ct], (int64_t)g);
-            const uint32_t w0[4] = {w[u][0].x, w[u][0].y, w[u][0].z, w[u][0].w};
-            const uint32_t w1[4] = {w[u][1].x, w[u][1].y, w[u][1].z, w[u][1].w};
+        for (int u = 0; u < kF4Unroll; ++u) {
+            const uint32_t c = cbase + u * kF4Threads + threadIdx.x;
+            const float2 sr = tab[sb[u]];
+            const uint32_t x[4] = {w[u].x, w[u].y, w[u].z, w[u].w};
             // an element with all exponent bits set (inf, NaN): adding 0x0080 to its magnitude carries into bit 15
-            uint32_t nonfinite = 0;
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-                nonfinite |= ((w0[i] & 0x7FFF7FFFu) + 0x00800080u) | ((w1[i] & 0x7FFF7FFFu) + 0x00800080u);
-            if (!q.slow && q.zp == 0.0f && (nonfinite & 0x80008000u) == 0) {
-                st_stream8((char *)B.out[ct] + (size_t)g * 8, make_uint2(quant_fp4_codes_f32(w0, q.s, q.r), quant_fp4_codes_f32(w1, q.s, q.r)));
-                continue;
-            }
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                Raw8 r8;
-                r8.a = w[u][h];
-                r8.b = make_uint4(0, 0, 0, 0);
-                float v[8];
-                decode8<F_BF16>(r8, v);
-                quant_prepare8<CTB_F32>(v, q, has_zp, q.zp, -6.0f, 6.0f);
-                encode_store8<QK_FP4, F_FP4X2>(B.out[ct], (int64_t)g * 2 + h, v);
+            const uint32_t nonfinite = (((x[0] & 0x7FFF7FFFu) + 0x00800080u) | ((x[1] & 0x7FFF7FFFu) + 0x00800080u) |
+                                        ((x[2] & 0x7FFF7FFFu) + 0x00800080u) | ((x[3] & 0x7FFF7FFFu) + 0x00800080u)) & 0x80008000u;
+            const uint32_t codes = quant_fp4_codes_f32(x, sr.x, sr.y);
+            if (c < nchunks) {
+                st_stream4(op + (size_t)c * 4, codes);
+                // the rare cases redo the chunk with the per-tensor tier's templates and overwrite the word
+                if (sr.y == 0.0f || zv[u] != 0.0f || nonfinite != 0) quant_fp4_chunk_general(ip + c, B.scale[t], zp, B.zdt, B.gs[t], op, c);
             }
         }
-        unit = next;
     }
 }
 
@@ -159,7 +162,7 @@ static int fill(F4Batch &B, const ctb_tensor_ref *tensors, const void *const *gl
         if (chunks > 0 && (!r.in || !r.out || !r.scale || !global_scales || !global_scales[base + i]))
             return fail(CTB_EINVAL_NULL, "tensor %d: null buffer", base + i);
         if ((reinterpret_cast<uintptr_t>(r.in) & (in_align - 1)) || (reinterpret_cast<uintptr_t>(r.out) & (out_align - 1)))
-            return fail(CTB_EINVAL_ALIGN, "tensor %d: the bf16 side must be 16-byte aligned, the packed side 8-byte (quantize) / 4-byte (dequantize)", base + i);
+            return fail(CTB_EINVAL_ALIGN, "tensor %d: the bf16 side must be 16-byte, the packed side 4-byte aligned", base + i);
         if (reinterpret_cast<uintptr_t>(global_scales ? global_scales[base + i] : nullptr) & 3u)
             return fail(CTB_EINVAL_ALIGN, "tensor %d: global scale must be 4-byte aligned", base + i);
         B.ustart[i] = units;
@@ -185,10 +188,10 @@ int quant_fp4_g16_one(const void *x, const void *scale, const float *gs, const v
     r.rows = rows;
     r.cols = cols;
     const void *g = gs, *z = zp;
-    int rc = fill(B, &r, &g, zp ? &z : nullptr, zdt, 0, 1, kF4Unit, 16, 8);
+    int rc = fill(B, &r, &g, zp ? &z : nullptr, zdt, 0, 1, kF4Unit, 16, 4);
     if (rc) return rc;
     if (B.ustart[1] == 0) return CTB_OK;
-    quant_fp4_g16_batch_kernel<<<grid_for(B.ustart[1], 1, 8), kF4Threads, 0, st>>>(B);
+    quant_fp4_g16_batch_kernel<<<grid_for(B.ustart[1], 1, 6), kF4Threads, 0, st>>>(B);
     return after_launch("quant_fp4_g16_batch_kernel");
 }
 
@@ -203,10 +206,10 @@ extern "C" int ctb_quantize_fp4_g16_batch(const ctb_tensor_ref *tensors, int32_t
     static thread_local F4Batch B;
     for (int32_t base = 0; base < count; base += kF4BatchMax) {
         const int32_t n = count - base < kF4BatchMax ? count - base : kF4BatchMax;
-        int rc = fill(B, tensors, global_scales, zero_points, zp_dtype, base, n, kF4Unit, 16, 8);
+        int rc = fill(B, tensors, global_scales, zero_points, zp_dtype, base, n, kF4Unit, 16, 4);
         if (rc) return rc;
         if (B.ustart[n] == 0) continue;
-        quant_fp4_g16_batch_kernel<<<grid_for(B.ustart[n], 1, 8), kF4Threads, 0, as_stream(stream)>>>(B);
+        quant_fp4_g16_batch_kernel<<<grid_for(B.ustart[n], 1, 6), kF4Threads, 0, as_stream(stream)>>>(B);
         rc = after_launch("quant_fp4_g16_batch_kernel");
         if (rc) return rc;
     }
