@@ -796,7 +796,9 @@ def main():
         for _ in range(k):
             trip()
         te = torch.tensor([(time.perf_counter() - t0) / k], dtype=torch.float64, device=dev)
-        # the same trip without letting the two calls overlap (each call waits for its own results)
+        # the same trip without letting the two calls overlap (each call waits for its own results); all ranks start
+        # together, so that every rank sees the host-memory and PCIe contention of the others
+        barrier()
         t0 = time.perf_counter()
         if getattr(hmodel, "transform_config", None) is not None:
             del hmodel.transform_config
