@@ -422,6 +422,11 @@ def per_config_table(dev, peak):
     # the whole of configuration 4a in one pass: pruned bf16 weight + per-channel scale in, kept e4m3 values + bitmask out
     run("c4a_fused_fp8_quantize_sparse24_compress", s24_dense, lambda w, sc: ops.quantize_fp8_sparse24(w, sc),
         2 * ns, 2.625 * ns, 2.7 * ns)
+    def s24_packed():
+        w, sc = s24_dense()
+        return ops.quantize_fp8_sparse24(w, sc) + (sc,)
+    run("c4a_fused_sparse24_decompress_fp8_dequantize", s24_packed,
+        lambda v, b, sc: ops.sparse24_decompress_dequantize_fp8(v, b, sc, (4096, 11008)), 2 * ns, 2.625 * ns, 2.7 * ns)
     run("c4a_sparse24_decompress_e4m3", lambda: ops.sparse24_compress(s24()[0]),
         lambda v, b: ops.sparse24_decompress(v, b, (4096, 11008)), 2 * ns, 1.625 * ns, 1.7 * ns)
     def unstructured():
@@ -545,6 +550,8 @@ def per_config_cpu(ct):
         timed("c4a_fused_fp8_quantize_sparse24_compress",
               lambda: sparse24_bitmask_compress(quantize(ws, s, z, a8, dtype=torch.float8_e4m3fn)))
         timed("c4a_sparse24_decompress_e4m3", lambda: sparse24_bitmask_decompress(vals, bm, q.shape))
+        timed("c4a_fused_sparse24_decompress_fp8_dequantize",
+              lambda: dequantize(sparse24_bitmask_decompress(vals, bm, q.shape), s, None, a8, dtype=torch.bfloat16))
         wu = rnd(4096, 4096)
         wu[torch.rand(4096, 4096, generator=g) < 0.5] = 0
         v, b, _ = timed("c4b_bitmask_compress_bf16_50pct", lambda: bitmask_compress(wu))

@@ -529,6 +529,8 @@ class CodecEngine:
             if j.kind != "generic":
                 continue
             st = dict(j.state)
+            if j.sparse and sparsity_compressor is not None and self._sparse24_fp8(j, st):
+                continue
             if j.sparse and sparsity_compressor is not None:
                 names = sparsity_compressor.compression_param_names
                 data = {k: v for k, v in st.items() if k in names}
@@ -541,6 +543,26 @@ class CodecEngine:
             elif "weight" in st and st["weight"] is not j.state.get("weight"):
                 out["weight"] = st["weight"]
             j.out = out
+
+    def _sparse24_fp8(self, j: Job, st: Dict[str, Tensor]) -> bool:
+        """The inverse of _fp8_sparse24: kept e4m3 values + bitmask of a sparse-24-bitmask module whose scheme is FP8
+        per channel go to the bf16 weight in one kernel (model_compressor.py:580-611 does it in two walks)."""
+        args = j.scheme.weights if j.scheme is not None else None
+        vals, bm, shape, scale = st.get("compressed"), st.get("bitmask"), st.get("shape"), st.get("weight_scale")
+        if (not self.fuse_sparse24 or j.compressor is None or args is None or vals is None or bm is None or shape is None or scale is None
+                or getattr(j.compressor, "_format_name", None) != CompressionFormat.float_quantized.value
+                or args.type != QuantizationType.FLOAT or args.num_bits != 8 or args.strategy != QuantizationStrategy.CHANNEL
+                or args.dynamic or vals.dtype != torch.float8_e4m3fn or not vals.is_cuda or scale.dtype != torch.bfloat16
+                or st.get("weight_zero_point") is not None or st.get("weight_g_idx") is not None):
+            return False
+        rows, cols = (int(v) for v in shape.flatten().tolist())  # a small host tensor (the reference stores the shape as one)
+        if cols % 8 or scale.numel() != rows or tuple(bm.shape) != (rows, cols // 8):
+            return False
+        with self._timed("decompress", vals.device):
+            w = ops.sparse24_decompress_dequantize_fp8(vals, bm, scale, (rows, cols))
+        self.launches += 1
+        j.out = {"weight": w}
+        return True
 
     # ------------------------------------------------------------------ replay of a recorded cycle
     def replay_compress(self, table: np.ndarray, signs: Tensor, dev: torch.device) -> None:

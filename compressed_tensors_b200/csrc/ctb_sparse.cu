@@ -1569,6 +1569,123 @@ extern "C" int ctb_sparse24_decompress(const void *values, int64_t nvalues, cons
     return decompress_impl(values, bitmask, dtype, rows, cols, out, workspace, Gate{flag, ticket}, stream, true);
 }
 
+// ------------------------------------------------------------------ 2:4 decompress fused with the FP8 dequantize
+//
+// The decompress walk of a stacked sparse-24-bitmask + float-quantized module (model_compressor.py:580-611: the sparsity
+// compressor rebuilds the dense e4m3 weight, the quantization compressor dequantizes it) in one pass: kept e4m3 values
+// (0.5 B / element) and the bitmask (0.125) in, bf16 weight (2) out; the dense e4m3 tensor is never written.
+
+// One thread per 8 elements: the unit's two runs are rebuilt by byte permutes (selector table by mask nibble, as in
+// sparse24_expand_simd_kernel), decoded, multiplied by the row's scale and rounded once to bf16, which is
+// (x_q.to(bf16) * scale) of forward.py:504-512 for a bf16 scale and no zero point.
+__global__ void __launch_bounds__(kThreads) sparse24_expand_dequant_fp8_kernel(const void *values, const uint8_t *bitmask, const uint16_t *scale,
+                                                                               uint32_t units, FastDiv by_upr, void *out, int *irregular,
+                                                                               int irregular_value) {
+    __shared__ uint32_t lut[16];
+    if (threadIdx.x < 16) {
+        const uint32_t n = threadIdx.x;
+        uint32_t sel = 0;
+        int seen = 0;
+        for (int i = 0; i < 4; ++i) {
+            uint32_t src = 4;  // a zero byte (the second permute operand)
+            if ((n >> i) & 1) src = seen++ ? 1 : 0;
+            sel |= src << (4 * i);
+        }
+        lut[n] = sel;
+    }
+    __syncthreads();
+    bool bad = false;
+    constexpr int U = 4;  // units in flight per thread
+    const uint32_t stride = gridDim.x * (uint32_t)kThreads;
+    for (uint32_t u0 = blockIdx.x * (uint32_t)kThreads + threadIdx.x; u0 < units; u0 += U * stride) {
+        uint32_t m[U], v[U], sb[U];
+#pragma unroll
+        for (int k = 0; k < U; ++k) {  // all loads first; a warp instruction covers one contiguous span
+            const uint32_t u = u0 + k * stride;
+            m[k] = 0x33u;  // an absent unit counts as regular
+            v[k] = 0;
+            sb[k] = 0;
+            if (u < units) {
+                m[k] = bitmask[u];
+                v[k] = ld_stream4((const char *)values + (size_t)u * 4);
+                sb[k] = __ldg(scale + fastdiv(u, by_upr));
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < U; ++k) {
+            const uint32_t u = u0 + k * stride;
+            if (u >= units) break;
+            uint32_t c = m[k] - ((m[k] >> 1) & 0x55u);
+            c = (c & 0x33u) + ((c >> 2) & 0x33u);
+            bad |= c != 0x22u;  // each nibble must have exactly two bits set
+            Raw8 r;
+            r.a = make_uint4(prmt(v[k], 0, lut[m[k] & 0xFu]), prmt(v[k] >> 16, 0, lut[m[k] >> 4]), 0, 0);
+            r.b = make_uint4(0, 0, 0, 0);
+            float f[8];
+            decode8<F_E4M3>(r, f);
+            st_stream((char *)out + (size_t)u * 16, dequant8_to_bf16<false>(f, __uint_as_float(sb[k] << 16)));
+        }
+    }
+    if (__any_sync(0xFFFFFFFFu, bad) && (threadIdx.x & 31) == 0) atomicExch(irregular, irregular_value);
+}
+
+// dense e4m3 [rows, cols] -> bf16 with one bf16 scale per row; runs only if the gate is open (or absent)
+__global__ void __launch_bounds__(kThreads) dequant_fp8_rows_gated_kernel(const void *codes, const uint16_t *scale, uint32_t units, FastDiv by_upr,
+                                                                          void *out, Gate gate) {
+    if (gate.flag != nullptr && *gate.flag != gate.value) return;
+    for (uint32_t u = blockIdx.x * (uint32_t)kThreads + threadIdx.x; u < units; u += gridDim.x * (uint32_t)kThreads) {
+        const uint2 w = ld_stream8((const char *)codes + (size_t)u * 8);
+        Raw8 r;
+        r.a = make_uint4(w.x, w.y, 0, 0);
+        r.b = make_uint4(0, 0, 0, 0);
+        float f[8];
+        decode8<F_E4M3>(r, f);
+        st_stream((char *)out + (size_t)u * 16, dequant8_to_bf16<false>(f, __uint_as_float((uint32_t)__ldg(scale + fastdiv(u, by_upr)) << 16)));
+    }
+}
+
+static int64_t dense_scratch_offset(int64_t rows) { return (flag_offset(rows) + 16 + 255) & ~(int64_t)255; }
+
+extern "C" int64_t ctb_sparse24_dequantize_workspace_bytes(int64_t rows, int64_t cols) {
+    return dense_scratch_offset(rows) + rows * cols;  // the bitmask codec's scratch, then room for the dense e4m3 tensor
+}
+
+extern "C" int ctb_sparse24_decompress_dequantize_fp8(const void *values, int64_t nvalues, const uint8_t *bitmask, const void *scale, int64_t rows,
+                                                      int64_t cols, void *out, void *workspace, void *stream) {
+    if (rows != 0 && cols != 0 && (!values || !bitmask || !scale || !out || !workspace)) return fail(CTB_EINVAL_NULL, "null buffer");
+    if (rows <= 0 || cols <= 0) return rows < 0 || cols < 0 ? fail(CTB_EINVAL_SHAPE, "negative shape") : CTB_OK;
+    if (nvalues < 0) return fail(CTB_EINVAL_SHAPE, "negative value count");
+    if (cols % 8 != 0) return fail(CTB_EINVAL_SHAPE, "fused 2:4 decompress + dequantize needs cols %% 8 == 0, got %lld", (long long)cols);
+    if (!aligned16(out) || (reinterpret_cast<uintptr_t>(values) & 3u) || (reinterpret_cast<uintptr_t>(scale) & 1u))
+        return fail(CTB_EINVAL_ALIGN, "out must be 16-byte, values 4-byte, scale 2-byte aligned");
+    const int64_t units64 = rows * cols / 8;
+    if (units64 >= (1ll << 31) - 4 * 148 * 8 * kThreads) return fail(CTB_EUNSUPPORTED, "more than 2^34 elements in one call");
+    const uint32_t units = (uint32_t)units64;
+    const FastDiv by_upr = make_fastdiv((uint32_t)(cols / 8));
+    const uint16_t *sp = reinterpret_cast<const uint16_t *>(scale);
+    cudaStream_t st = as_stream(stream);
+    char *dense = static_cast<char *>(workspace) + dense_scratch_offset(rows);
+    const int dq_grid = grid_for(units64, kThreads, 16);
+    if (nvalues < rows * cols / 2) {
+        // fewer values than two per run of four: the bitmask decides where they go (generic codec), then a plain dequantize
+        int rc = decompress_impl(values, bitmask, CTB_E4M3, rows, cols, dense, workspace, Gate{nullptr, 0}, stream, true);
+        if (rc) return rc;
+        dequant_fp8_rows_gated_kernel<<<dq_grid, kThreads, 0, st>>>(dense, sp, units, by_upr, out, Gate{nullptr, 0});
+        return after_launch("dequant_fp8_rows_gated_kernel");
+    }
+    int *flag = reinterpret_cast<int *>(static_cast<char *>(workspace) + flag_offset(rows));
+    static std::atomic<int> s_ticket{0x40000001};
+    const int ticket = s_ticket.fetch_add(1, std::memory_order_relaxed);  // see Gate: no clearing of the flag word
+    sparse24_expand_dequant_fp8_kernel<<<grid_for(units64, (int64_t)kThreads * 4, 16), kThreads, 0, st>>>(values, bitmask, sp, units, by_upr, out, flag, ticket);
+    int rc = after_launch("sparse24_expand_dequant_fp8_kernel");
+    if (rc) return rc;
+    // a bitmask that is not two-per-run opened the gate: the generic codec and a plain dequantize redo the tensor
+    rc = decompress_impl(values, bitmask, CTB_E4M3, rows, cols, dense, workspace, Gate{flag, ticket}, stream, true);
+    if (rc) return rc;
+    dequant_fp8_rows_gated_kernel<<<tile_grid(units64, 1), kThreads, 0, st>>>(dense, sp, units, by_upr, out, Gate{flag, ticket});
+    return after_launch("dequant_fp8_rows_gated_kernel");
+}
+
 // ------------------------------------------------------------------ decompress without caller scratch
 //
 // Some hosts of this library may not allocate device memory at the point where they decompress:

@@ -14,7 +14,7 @@ __all__ = [
     "mxfp4_round_pow2", "mxfp4_generate_scales", "mxfp4_convert_scales",
     "cutlass24_compress", "cutlass24_decompress", "marlin24_pack_weight", "marlin24_pack_scales",
     "pack_int32", "unpack_int32", "pack_fp4", "unpack_fp4", "pack_bitmasks", "unpack_bitmasks",
-    "sparse24_mask", "sparse24_compress", "quantize_fp8_sparse24", "sparse24_decompress", "bitmask_compress", "bitmask_decompress", "hadamard",
+    "sparse24_mask", "sparse24_compress", "quantize_fp8_sparse24", "sparse24_decompress", "sparse24_decompress_dequantize_fp8", "bitmask_compress", "bitmask_decompress", "hadamard",
     "absmax_quantize", "rotate_quantize_int4_batch", "rotate_quantize_int4_batch_bounded", "quantize_pack_int4_batch",
     "unpack_dequantize_int4_batch", "quantize_fp8_channel_batch", "dequantize_fp8_channel_batch",
     "quantize_fp4_g16_batch", "dequantize_fp4_g16_batch", "tensor_table", "QINT", "QFLOAT",
@@ -376,6 +376,26 @@ def sparse24_decompress(values, bitmask, shape):
     ws = _bitmask_workspace(rows, cols, bitmask.device)
     check(lib().ctb_sparse24_decompress(ptr(values), i64(values.numel()), ptr(bitmask), i32(DT[values.dtype]), i64(rows), i64(cols),
                                         ptr(out), ptr(ws), stream_of(bitmask)))
+    return out
+
+
+def sparse24_decompress_dequantize_fp8(values, bitmask, scale, shape):
+    """sparse_24_bitmask.py:206 sparse24_bitmask_decompress of kept e4m3 values followed by the per-channel dequantize
+    of forward.py:504 (bf16 scale, one per row, no zero point), in one pass -> bf16 [rows, cols]."""
+    require_cuda(values, bitmask, scale)
+    values, bitmask, scale = _c(values.flatten()), _c(bitmask), _c(scale)
+    rows, cols = int(shape[0]), int(shape[1])
+    if values.dtype != torch.float8_e4m3fn or scale.dtype != torch.bfloat16:
+        raise TypeError("sparse24_decompress_dequantize_fp8 takes e4m3 values and bf16 scales")
+    if scale.numel() != rows:
+        raise ValueError(f"one scale per row expected, got {scale.numel()} for {rows} rows")
+    out = torch.empty((rows, cols), dtype=torch.bfloat16, device=bitmask.device)
+    if rows == 0 or cols == 0:
+        return out
+    lib().ctb_sparse24_dequantize_workspace_bytes.restype = ctypes.c_int64
+    ws = torch.empty(int(lib().ctb_sparse24_dequantize_workspace_bytes(i64(rows), i64(cols))), dtype=torch.uint8, device=bitmask.device)
+    check(lib().ctb_sparse24_decompress_dequantize_fp8(ptr(values), i64(values.numel()), ptr(bitmask), ptr(scale), i64(rows), i64(cols),
+                                                       ptr(out), ptr(ws), stream_of(bitmask)))
     return out
 
 

@@ -8,7 +8,7 @@ operators; the host mirror of the reference interface calls these.
 
 Operators: quantize, dequantize, fake_quantize, absmax_quantize, minmax, calculate_qparams, generate_gparam,
 pack_int32, unpack_int32, pack_fp4, unpack_fp4, pack_bitmasks, unpack_bitmasks, sparse24_mask, sparse24_compress,
-quantize_fp8_sparse24, sparse24_decompress, bitmask_compress, bitmask_decompress, hadamard.
+quantize_fp8_sparse24, sparse24_decompress, sparse24_decompress_dequantize_fp8, bitmask_compress, bitmask_decompress, hadamard.
 """
 from typing import List, Optional, Sequence, Tuple
 
@@ -338,6 +338,20 @@ def sparse24_decompress(values, bitmask, shape):
     return torch.ops.ctb200.sparse24_decompress(values, bitmask, [int(s) for s in shape])
 
 
+@custom_op(f"{NS}::sparse24_decompress_dequantize_fp8", mutates_args=())
+def _sparse24_decompress_dequantize_fp8(values: Tensor, bitmask: Tensor, scale: Tensor, shape: List[int]) -> Tensor:
+    return _o.sparse24_decompress_dequantize_fp8(values, bitmask, scale, shape)
+
+
+@_sparse24_decompress_dequantize_fp8.register_fake
+def _(values, bitmask, scale, shape):
+    return bitmask.new_empty((int(shape[0]), int(shape[1])), dtype=torch.bfloat16)
+
+
+def sparse24_decompress_dequantize_fp8(values, bitmask, scale, shape):
+    return torch.ops.ctb200.sparse24_decompress_dequantize_fp8(values, bitmask, scale, [int(s) for s in shape])
+
+
 @custom_op(f"{NS}::bitmask_compress", mutates_args=())
 def _bitmask_compress(x: Tensor) -> Tuple[Tensor, Tensor, Tensor]:
     values, bitmask, row_offsets = _o.bitmask_compress(x)
@@ -387,5 +401,5 @@ def hadamard(x, n, signs=None, inverse=False, side=0, precision=torch.float64, n
 
 OPERATORS: Sequence[str] = ("quantize", "dequantize", "fake_quantize", "absmax_quantize", "minmax", "calculate_qparams",
                             "generate_gparam", "pack_int32", "unpack_int32", "pack_fp4", "unpack_fp4", "pack_bitmasks",
-                            "unpack_bitmasks", "sparse24_mask", "sparse24_compress", "quantize_fp8_sparse24", "sparse24_decompress",
+                            "unpack_bitmasks", "sparse24_mask", "sparse24_compress", "quantize_fp8_sparse24", "sparse24_decompress", "sparse24_decompress_dequantize_fp8",
                             "bitmask_compress", "bitmask_decompress", "hadamard")

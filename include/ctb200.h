@@ -181,6 +181,14 @@ int ctb_sparse24_compress(const void *x, int32_t dtype, int64_t rows, int64_t co
  * by ctb_sparse24_compress. */
 int ctb_quantize_fp8_sparse24(const void *x, const void *scale, const void *zero_point, int32_t zp_dtype,
                               int64_t rows, int64_t cols, void *out_values, uint8_t *out_bitmask, void *stream);
+/* The inverse walk in one pass (model_compressor.py:580-611: sparse_24_bitmask.py:206-224 decompress, then
+ * naive_quantized.py:113-140 decompress_weight -> forward.py:504-512 dequantize): kept e4m3 values [nvalues]
+ * (rows*cols/2 for a two-per-four bitmask) + bitmask [rows, cols/8] + bf16 scale [rows] -> bf16 [rows, cols].
+ * Any bitmask gives the result of ctb_sparse24_decompress followed by ctb_dequantize (a bitmask that is not
+ * two-per-four takes the generic codec through the scratch).  workspace: ctb_sparse24_dequantize_workspace_bytes. */
+int64_t ctb_sparse24_dequantize_workspace_bytes(int64_t rows, int64_t cols);
+int ctb_sparse24_decompress_dequantize_fp8(const void *values, int64_t nvalues, const uint8_t *bitmask, const void *scale,
+                                           int64_t rows, int64_t cols, void *out, void *workspace, void *stream);
 /* compressors/sparse_compressors/sparse_bitmask.py:131-149 bitmask_compress.
  * out_values needs room for rows*cols elements; the first *out_nnz (device int64) are valid,
  * row-major.  out_row_offsets is int64 [rows] (exclusive prefix of per-row counts).

@@ -150,6 +150,46 @@ def test_c4a_fused_quantize_sparse24_full(ops, orc, canary):
         assert_bit_equal(gv.cpu(), v, f"values (zero point: {z is not None})")
 
 
+def test_c4a_fused_sparse24_decompress_dequantize_full(ops, orc, canary):
+    """The inverse of the one-pass compress at 4096 x 11008: kept e4m3 values + bitmask + per-channel scale in, bf16
+    weight out, against the oracle's bitmask decompress followed by its dequantize; then a bitmask that is not
+    two-per-four (the gated generic route) and a value buffer shorter than two per four (the ungated one)."""
+    w = weights(4096, 11008, 4)
+    pruned = torch.where(orc.sparse24_mask(w), w, torch.zeros((), dtype=w.dtype))
+    kw = dict(qtype=orc.QFLOAT, bits=8, col_group=11008, row_group=1, scale_row_stride=1)
+    mn, mx = orc.minmax(pruned, 1, 11008)
+    scale, zp = orc.calculate_qparams(mn, mx, qtype=orc.QFLOAT, bits=8, symmetric=True)
+    q = orc.quantize(pruned, scale, zp, out_dtype=torch.float8_e4m3fn, **kw)
+    v, b = orc.sparse24_compress(q)
+    want = orc.dequantize(orc.bitmask_decompress(v, b, q.shape), scale, None, out_dtype=torch.bfloat16, **kw)
+    with canary():
+        got = ops.sparse24_decompress_dequantize_fp8(v.cuda(), b.cuda(), scale.cuda().reshape(-1), q.shape)
+    assert_bit_equal(got.cpu(), want, "fused decompress + dequantize")
+    # irregular bitmasks on a smaller tensor: three-of-four and one-of-four runs, as the unstructured codec would write them
+    g = torch.Generator().manual_seed(23)
+    rows, cols = 257, 1032
+    x = (torch.randn(rows, cols, generator=g) * 0.05).to(torch.bfloat16)
+    x[torch.rand(rows, cols, generator=g) < 0.5] = 0
+    kw = dict(qtype=orc.QFLOAT, bits=8, col_group=cols, row_group=1, scale_row_stride=1)
+    mn, mx = orc.minmax(x, 1, cols)
+    scale, zp = orc.calculate_qparams(mn, mx, qtype=orc.QFLOAT, bits=8, symmetric=True)
+    q = orc.quantize(x, scale, None, out_dtype=torch.float8_e4m3fn, **kw)
+    values, bitmask, _ = orc.bitmask_compress(q)
+    want = orc.dequantize(orc.bitmask_decompress(values, bitmask, q.shape), scale, None, out_dtype=torch.bfloat16, **kw)
+    x2 = x.clone()
+    x2[::2] = 0  # every other row empty: far fewer values than two per run of four
+    q2 = orc.quantize(x2, scale, None, out_dtype=torch.float8_e4m3fn, **kw)
+    values2, bitmask2, _ = orc.bitmask_compress(q2)
+    assert values2.numel() < rows * cols // 2 <= values.numel() + 4096
+    want2 = orc.dequantize(orc.bitmask_decompress(values2, bitmask2, q.shape), scale, None, out_dtype=torch.bfloat16, **kw)
+    room = torch.zeros(max(values.numel(), rows * cols // 2), dtype=torch.float8_e4m3fn)
+    room[:values.numel()] = values  # a buffer with room for two per four, so the fast kernel runs first and opens the gate
+    for name, vals, bitmask, want in (("short value buffer", values2, bitmask2, want2), ("full-size buffer, irregular bitmask", room, bitmask, want)):
+        with canary():
+            got = ops.sparse24_decompress_dequantize_fp8(vals.cuda(), bitmask.cuda(), scale.cuda().reshape(-1), q.shape)
+        assert_bit_equal(got.cpu(), want, name)
+
+
 def test_fused_quantize_sparse24_edge_cases(ops, orc, canary):
     """Dense (unpruned) rows so that ties and rank order matter, NaN / Inf / signed zeros, scales outside the range
     of the reciprocal shortcut, a zero point other than zero, a unit count that fills neither a warp nor a pair."""
