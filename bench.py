@@ -751,10 +751,27 @@ def main():
     td = sum(a.elapsed_time(b) for kind, a, b in mc.engine.kernel_times if kind == "decompress") / 1e3
     mc.engine.record_kernel_times = False
     mc.engine.kernel_times.clear()
-    times = torch.tensor([t, tc, td], dtype=torch.float64, device=dev)
+    # the same steps through the general path of ModelCompressor (no recorded cycle: every call walks the module tree,
+    # allocates its outputs and re-installs the parameters), for the record
+    tg = 0.0
+    if not args.no_reuse_buffers:
+        mc_general = new_compressor()
+
+        def general_step():
+            if getattr(model, "transform_config", None) is not None:
+                del model.transform_config
+            mc_general.compress_model(model)
+            mc_general.decompress_model(model)
+
+        for _ in range(2):
+            general_step()
+        barrier()
+        tg = time_region(general_step, max(3, min(args.steps, 5)), stream) / max(3, min(args.steps, 5))
+        del mc_general
+    times = torch.tensor([t, tc, td, tg], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    t, tc, td = (float(v) for v in times.cpu())
+    t, tc, td, tg = (float(v) for v in times.cpu())
 
     # ---- end to end: the module tree lives in page-locked HOST memory; copies in both directions are inside the timed region
     e2e = None
@@ -840,6 +857,8 @@ def main():
             "metric": METRIC, "value": 2 * 2 * total_elems / (t / args.steps) / 1e9, "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": cfg,
+            "general_path": None if tg == 0.0 else {"value": 2 * 2 * total_elems / tg / 1e9, "ms_per_step": tg * 1e3,
+                                                    "note": "reuse_buffers=False: host-bound (one Python walk over the module tree per call)"},
             "kernel_compress_gbs": 2 * rank_elems * world / (tc / args.steps) / 1e9, "kernel_decompress_gbs": 2 * rank_elems * world / (td / args.steps) / 1e9,
             "kernel_ms_per_step": (tc + td) / args.steps * 1e3,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,

@@ -521,7 +521,8 @@ def _place_small(jobs: List[Job], owners: List[Module]) -> None:
             if name in ("weight_shape", "shape") and not v.is_cuda:
                 per_dev.setdefault(dev, []).append((d, name, v))
     for dev, items in per_dev.items():
-        flat = torch.cat([v.reshape(-1) for _, _, v in items]).to(dev)
+        # from page-locked memory and without waiting: a copy from pageable memory holds the host until it is staged
+        flat = torch.cat([v.reshape(-1) for _, _, v in items]).pin_memory().to(dev, non_blocking=True)
         off = 0
         for d, name, v in items:
             d[name] = flat[off:off + v.numel()].view(v.shape)
