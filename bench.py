@@ -318,8 +318,9 @@ def run_reference(args):
 
 def op_timer(out, peak):
     """Returns run(name, make_args, fn, dense_bytes, alg_bytes, per_set_bytes): times fn over a rotating set of
-    distinct argument sets whose total exceeds 2x the L2 size (every launch streams from HBM), replayed from a CUDA
-    graph, with CUDA events on the current stream, and records us / dense GB/s / fraction of `peak` under out[name]."""
+    distinct argument sets whose total exceeds 2x the L2 size, each call writing to output buffers of its own (every
+    launch streams from and to HBM), replayed from a CUDA graph, with CUDA events on the current stream, and records
+    us / dense GB/s / fraction of `peak` under out[name]."""
     l2 = 2 * 126 * 1024 * 1024
 
     def run(name, make_args, fn, dense_bytes, alg_bytes, per_set_bytes):
@@ -331,8 +332,10 @@ def op_timer(out, peak):
         reps = 3
 
         def sweep():
-            for a in sets:
-                fn(*a)
+            # the results of a sweep stay alive until its end, so every call writes to memory of its own: an output
+            # buffer handed back to the allocator and reused by the next call would be rewritten while still in L2
+            held = [fn(*a) for a in sets]
+            del held
 
         mode = "cuda graph"
         try:  # replay from a CUDA graph so that the host-side call overhead of these 5-50 us kernels is not what is timed

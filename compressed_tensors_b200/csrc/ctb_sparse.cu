@@ -804,6 +804,83 @@ __global__ void __launch_bounds__(kThreads) bm_block_popcount_kernel(const uint8
     publish_count(c, block_tot);
 }
 
+// Kept elements of the bitmask bytes [first, last) counted by the whole block (every thread returns the sum).
+// `first` is a multiple of 256 or 0: 16-byte steps keep the alignment of the bitmask's base.
+__device__ __forceinline__ unsigned long long block_popcount_range(const uint8_t *bitmask, int64_t first, int64_t last) {
+    __shared__ unsigned long long pc[kWarps];
+    unsigned long long c = 0;
+    int64_t i = first + (int64_t)threadIdx.x * 16;
+    if ((reinterpret_cast<uintptr_t>(bitmask) & 15u) == 0) {
+        for (; i + 16 <= last; i += kThreads * 16) {
+            const uint4 v = *reinterpret_cast<const uint4 *>(bitmask + i);
+            c += __popc(v.x) + __popc(v.y) + __popc(v.z) + __popc(v.w);
+        }
+    }
+    for (; i < last; i += kThreads * 16)
+        for (int64_t j = i; j < i + 16 && j < last; ++j) c += __popc((uint32_t)bitmask[j]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xFFFFFFFFu, c, o);
+    __syncthreads();  // `pc` may still be read by a previous call
+    if ((threadIdx.x & 31) == 0) pc[threadIdx.x >> 5] = c;
+    __syncthreads();
+    unsigned long long t = 0;
+#pragma unroll
+    for (int i2 = 0; i2 < kWarps; ++i2) t += pc[i2];
+    return t;
+}
+
+// The count exchange of the one-launch expand kernel: every block publishes the count of its own range as
+// (count, tag) and adds up what the blocks before it published.  The tag is a fresh 64-bit number per call, so the
+// scratch never has to be cleared.  Nothing waits for ever: a block that does not see a predecessor's count within
+// the budget (a device that runs the blocks of this grid one after the other, say) counts the bits before its range
+// itself, which needs nobody.
+constexpr long long kPubSpinCycles = 1ll << 21;  // about a millisecond
+__device__ __forceinline__ void publish_tagged(unsigned long long *slots, unsigned long long count, unsigned long long tag) {
+    if (threadIdx.x == 0) {
+        slots[2 * blockIdx.x] = count;
+        __threadfence();
+        asm volatile("st.global.release.gpu.u64 [%0], %1;" ::"l"(slots + 2 * blockIdx.x + 1), "l"(tag) : "memory");
+    }
+}
+__device__ __forceinline__ unsigned long long prefix_of_published(const unsigned long long *slots, unsigned long long tag, const uint8_t *bitmask,
+                                                                  int64_t first) {
+    __shared__ unsigned long long red[kWarps];
+    unsigned long long s = 0;
+    int missing = 0;
+    const long long t0 = clock64();
+    for (int i = threadIdx.x; i < (int)blockIdx.x && !missing; i += kThreads) {
+        for (;;) {
+            unsigned long long v;
+            asm volatile("ld.global.acquire.gpu.u64 %0, [%1];" : "=l"(v) : "l"(slots + 2 * i + 1) : "memory");
+            if (v == tag) {
+                s += *reinterpret_cast<const volatile unsigned long long *>(slots + 2 * i);
+                break;
+            }
+            if (clock64() - t0 > kPubSpinCycles) {
+                missing = 1;
+                break;
+            }
+            __nanosleep(64);
+        }
+    }
+    if (__syncthreads_or(missing)) return block_popcount_range(bitmask, 0, first);  // block-uniform
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+    __syncthreads();
+    unsigned long long base = 0;
+#pragma unroll
+    for (int i = 0; i < kWarps; ++i) base += red[i];
+    return base;
+}
+
+// what the one-launch form of the expand kernel needs besides the arguments of the two-launch form
+struct ExpandExtra {
+    unsigned long long tag;   // of this call's (count, tag) slots
+    const uint16_t *scale;    // DEQ: one bf16 scale per row
+    FastDiv by_upr;           // DEQ: unit -> row
+};
+
 template <int ES>
 struct BmWindow {
     static constexpr int kBytes = kBmTile * 8 * ES + 32;  // a tile's elements, shifted by up to 15 bytes
@@ -887,9 +964,16 @@ __global__ void __launch_bounds__(kThreads, ES == 4 ? 4 : 6) bm_block_scatter_ke
 // decompress, kernel 2 (same grid as kernel 1): every tile's kept values are one contiguous run of `values`: bring it
 // into the window (whole 16-byte words that lie inside the run, its ragged ends by element, so nothing outside
 // `values` is ever read), then every thread rebuilds its units from the window
-template <int ES>
+// ONEPASS: no count kernel runs in front: `block_tot` is the (count, tag) scratch of publish_tagged and the block counts
+// its own range first.  Used where the launch almost always returns at once (the gated fallback of the 2:4 kernels),
+// so that the common case pays for one empty launch and not two: as the main path it is slower than the pair, because no
+// block can start its walk before every block ahead of it has been dispatched and has published.
+// DEQ (8-bit elements): the rebuilt e4m3 codes are dequantized with the row's bf16 scale and `out` is bf16.
+template <int ES, bool ONEPASS = false, bool DEQ = false>
 __global__ void __launch_bounds__(kThreads, ES == 4 ? 4 : 6) bm_block_expand_kernel(const void *values, const uint8_t *bitmask, int64_t units,
-                                                                   const unsigned long long *block_tot, void *out, Gate gate) {
+                                                                   unsigned long long *block_tot, void *out, Gate gate,
+                                                                   ExpandExtra extra = ExpandExtra{}) {
+    static_assert(!DEQ || ES == 1, "the dequantizing form is for e4m3 codes");
     if (gate.flag != nullptr && *gate.flag != gate.value) return;
     __shared__ __align__(16) unsigned char win[BmWindow<ES>::kBytes];
     __shared__ uint32_t wt[kWarps][2], pre[kBmRows * kWarps + 1];
@@ -904,8 +988,15 @@ __global__ void __launch_bounds__(kThreads, ES == 4 ? 4 : 6) bm_block_expand_ker
             mask_n[j] = u < last ? (uint32_t)bitmask[u] : 0u;
         }
     };
-    if (first < last) fetch(first);
-    unsigned long long src = block_first_value(block_tot, nullptr);
+    unsigned long long src;
+    if constexpr (ONEPASS) {
+        publish_tagged(block_tot, block_popcount_range(bitmask, first, last), extra.tag);
+        if (first < last) fetch(first);
+        src = prefix_of_published(block_tot, extra.tag, bitmask, first);
+    } else {
+        if (first < last) fetch(first);
+        src = block_first_value(block_tot, nullptr);
+    }
     for (int64_t base = first; base < last; base += kBmTile) {
         uint32_t mask[kBmRows], c[kBmRows], excl[kBmRows], total;
 #pragma unroll
@@ -944,7 +1035,15 @@ __global__ void __launch_bounds__(kThreads, ES == 4 ? 4 : 6) bm_block_expand_ker
 #pragma unroll
             for (int e = 0; e < 8; ++e) b[e] = stage_get_if<ES>(sa, mask[j] & (1u << e));
             char *q = (char *)out + u * 8 * ES;
-            if constexpr (ES == 2) st_stream(q, make_uint4(b[0] | (b[1] << 16), b[2] | (b[3] << 16), b[4] | (b[5] << 16), b[6] | (b[7] << 16)));
+            if constexpr (DEQ) {
+                Raw8 r;
+                r.a = make_uint4(b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24), b[4] | (b[5] << 8) | (b[6] << 16) | (b[7] << 24), 0, 0);
+                r.b = make_uint4(0, 0, 0, 0);
+                float f[8];
+                decode8<F_E4M3>(r, f);
+                const uint32_t sb = __ldg(extra.scale + fastdiv((uint32_t)u, extra.by_upr));
+                st_stream((char *)out + u * 16, dequant8_to_bf16<false>(f, __uint_as_float(sb << 16)));
+            } else if constexpr (ES == 2) st_stream(q, make_uint4(b[0] | (b[1] << 16), b[2] | (b[3] << 16), b[4] | (b[5] << 16), b[6] | (b[7] << 16)));
             else if constexpr (ES == 1) st_stream8(q, make_uint2(b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24), b[4] | (b[5] << 8) | (b[6] << 16) | (b[7] << 24)));
             else {
                 st_stream(q, make_uint4(b[0], b[1], b[2], b[3]));
@@ -1499,7 +1598,7 @@ extern "C" int ctb_masked_compress(const void *x, const uint8_t *bytemask, int32
 }
 
 static int decompress_impl(const void *values, const uint8_t *bitmask, int32_t dtype, int64_t rows, int64_t cols, void *out, void *workspace,
-                           Gate gate, void *stream, bool tiles_ok = false) {
+                           Gate gate, void *stream, bool tiles_ok = false, const uint16_t *deq_scale = nullptr) {
     if (rows != 0 && cols != 0 && (!bitmask || !out || !workspace)) return fail(CTB_EINVAL_NULL, "null buffer");
     ElemInfo e;
     if (!elem_info(dtype, &e)) return fail(CTB_EINVAL_DTYPE, "unsupported dtype for bitmask decompression");
@@ -1512,6 +1611,22 @@ static int decompress_impl(const void *values, const uint8_t *bitmask, int32_t d
         // both kernels must see the same grid: it defines the ranges.  As the gated fallback of the 2:4
         // expansion the launches almost always return at once: keep them small.
         const int g1 = tile_grid(units, gate.flag ? 1 : 6);
+        if ((gate.flag != nullptr || deq_scale != nullptr) && 16ll * g1 <= tile_bytes() && units < (1ll << 31)) {
+            // the gated fallback (and the dequantizing form, which only exists in this shape): one launch
+            static std::atomic<unsigned long long> s_tag{0x9E3779B97F4A7C15ull};
+            ExpandExtra extra{};
+            extra.tag = s_tag.fetch_add(0xD1B54A32D192ED03ull, std::memory_order_relaxed);
+            extra.scale = deq_scale;
+            extra.by_upr = make_fastdiv((uint32_t)(cols / 8));
+            if (deq_scale != nullptr) {
+                if (e.esize != 1) return fail(CTB_EINVAL_DTYPE, "the dequantizing expansion takes e4m3 values");
+                bm_block_expand_kernel<1, true, true><<<g1, kThreads, 0, st>>>(values, bitmask, units, block_tot, out, gate, extra);
+            } else if (e.esize == 2) bm_block_expand_kernel<2, true><<<g1, kThreads, 0, st>>>(values, bitmask, units, block_tot, out, gate, extra);
+            else if (e.esize == 1) bm_block_expand_kernel<1, true><<<g1, kThreads, 0, st>>>(values, bitmask, units, block_tot, out, gate, extra);
+            else bm_block_expand_kernel<4, true><<<g1, kThreads, 0, st>>>(values, bitmask, units, block_tot, out, gate, extra);
+            return after_launch("bm_block_expand_kernel");
+        }
+        if (deq_scale != nullptr) return fail(CTB_EUNSUPPORTED, "tensor too large for the dequantizing expansion");
         bm_block_popcount_kernel<<<g1, kThreads, 0, st>>>(bitmask, units, block_tot, gate);
         int rc0 = after_launch("bm_block_popcount_kernel");
         if (rc0) return rc0;
@@ -1520,6 +1635,7 @@ static int decompress_impl(const void *values, const uint8_t *bitmask, int32_t d
         else bm_block_expand_kernel<4><<<g1, kThreads, 0, st>>>(values, bitmask, units, block_tot, out, gate);
         return after_launch("bm_block_expand_kernel");
     }
+    if (deq_scale != nullptr) return fail(CTB_EUNSUPPORTED, "the dequantizing expansion needs cols %% 8 == 0 and aligned buffers");
     int64_t *offs = (int64_t *)workspace;
     int grid = grid_for(rows, 1, 8);
     int rc;
@@ -1629,26 +1745,7 @@ __global__ void __launch_bounds__(kThreads) sparse24_expand_dequant_fp8_kernel(c
     if (__any_sync(0xFFFFFFFFu, bad) && (threadIdx.x & 31) == 0) atomicExch(irregular, irregular_value);
 }
 
-// dense e4m3 [rows, cols] -> bf16 with one bf16 scale per row; runs only if the gate is open (or absent)
-__global__ void __launch_bounds__(kThreads) dequant_fp8_rows_gated_kernel(const void *codes, const uint16_t *scale, uint32_t units, FastDiv by_upr,
-                                                                          void *out, Gate gate) {
-    if (gate.flag != nullptr && *gate.flag != gate.value) return;
-    for (uint32_t u = blockIdx.x * (uint32_t)kThreads + threadIdx.x; u < units; u += gridDim.x * (uint32_t)kThreads) {
-        const uint2 w = ld_stream8((const char *)codes + (size_t)u * 8);
-        Raw8 r;
-        r.a = make_uint4(w.x, w.y, 0, 0);
-        r.b = make_uint4(0, 0, 0, 0);
-        float f[8];
-        decode8<F_E4M3>(r, f);
-        st_stream((char *)out + (size_t)u * 16, dequant8_to_bf16<false>(f, __uint_as_float((uint32_t)__ldg(scale + fastdiv(u, by_upr)) << 16)));
-    }
-}
-
-static int64_t dense_scratch_offset(int64_t rows) { return (flag_offset(rows) + 16 + 255) & ~(int64_t)255; }
-
-extern "C" int64_t ctb_sparse24_dequantize_workspace_bytes(int64_t rows, int64_t cols) {
-    return dense_scratch_offset(rows) + rows * cols;  // the bitmask codec's scratch, then room for the dense e4m3 tensor
-}
+extern "C" int64_t ctb_sparse24_dequantize_workspace_bytes(int64_t rows, int64_t cols) { return ctb_bitmask_workspace_bytes(rows, cols); }
 
 extern "C" int ctb_sparse24_decompress_dequantize_fp8(const void *values, int64_t nvalues, const uint8_t *bitmask, const void *scale, int64_t rows,
                                                       int64_t cols, void *out, void *workspace, void *stream) {
@@ -1664,26 +1761,17 @@ extern "C" int ctb_sparse24_decompress_dequantize_fp8(const void *values, int64_
     const FastDiv by_upr = make_fastdiv((uint32_t)(cols / 8));
     const uint16_t *sp = reinterpret_cast<const uint16_t *>(scale);
     cudaStream_t st = as_stream(stream);
-    char *dense = static_cast<char *>(workspace) + dense_scratch_offset(rows);
-    const int dq_grid = grid_for(units64, kThreads, 16);
-    if (nvalues < rows * cols / 2) {
-        // fewer values than two per run of four: the bitmask decides where they go (generic codec), then a plain dequantize
-        int rc = decompress_impl(values, bitmask, CTB_E4M3, rows, cols, dense, workspace, Gate{nullptr, 0}, stream, true);
-        if (rc) return rc;
-        dequant_fp8_rows_gated_kernel<<<dq_grid, kThreads, 0, st>>>(dense, sp, units, by_upr, out, Gate{nullptr, 0});
-        return after_launch("dequant_fp8_rows_gated_kernel");
-    }
+    if (nvalues < rows * cols / 2)
+        // fewer values than two per run of four: the bitmask decides where they go (generic codec, dequantizing form)
+        return decompress_impl(values, bitmask, CTB_E4M3, rows, cols, out, workspace, Gate{nullptr, 0}, stream, true, sp);
     int *flag = reinterpret_cast<int *>(static_cast<char *>(workspace) + flag_offset(rows));
     static std::atomic<int> s_ticket{0x40000001};
     const int ticket = s_ticket.fetch_add(1, std::memory_order_relaxed);  // see Gate: no clearing of the flag word
     sparse24_expand_dequant_fp8_kernel<<<grid_for(units64, (int64_t)kThreads * 4, 16), kThreads, 0, st>>>(values, bitmask, sp, units, by_upr, out, flag, ticket);
     int rc = after_launch("sparse24_expand_dequant_fp8_kernel");
     if (rc) return rc;
-    // a bitmask that is not two-per-run opened the gate: the generic codec and a plain dequantize redo the tensor
-    rc = decompress_impl(values, bitmask, CTB_E4M3, rows, cols, dense, workspace, Gate{flag, ticket}, stream, true);
-    if (rc) return rc;
-    dequant_fp8_rows_gated_kernel<<<tile_grid(units64, 1), kThreads, 0, st>>>(dense, sp, units, by_upr, out, Gate{flag, ticket});
-    return after_launch("dequant_fp8_rows_gated_kernel");
+    // a bitmask that is not two-per-run opened the gate: the generic codec (dequantizing form) redoes the tensor
+    return decompress_impl(values, bitmask, CTB_E4M3, rows, cols, out, workspace, Gate{flag, ticket}, stream, true, sp);
 }
 
 // ------------------------------------------------------------------ decompress without caller scratch

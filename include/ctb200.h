@@ -185,7 +185,7 @@ int ctb_quantize_fp8_sparse24(const void *x, const void *scale, const void *zero
  * naive_quantized.py:113-140 decompress_weight -> forward.py:504-512 dequantize): kept e4m3 values [nvalues]
  * (rows*cols/2 for a two-per-four bitmask) + bitmask [rows, cols/8] + bf16 scale [rows] -> bf16 [rows, cols].
  * Any bitmask gives the result of ctb_sparse24_decompress followed by ctb_dequantize (a bitmask that is not
- * two-per-four takes the generic codec through the scratch).  workspace: ctb_sparse24_dequantize_workspace_bytes. */
+ * two-per-four takes the generic codec).  workspace: ctb_sparse24_dequantize_workspace_bytes. */
 int64_t ctb_sparse24_dequantize_workspace_bytes(int64_t rows, int64_t cols);
 int ctb_sparse24_decompress_dequantize_fp8(const void *values, int64_t nvalues, const uint8_t *bitmask, const void *scale,
                                            int64_t rows, int64_t cols, void *out, void *workspace, void *stream);
