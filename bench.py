@@ -376,6 +376,11 @@ def per_config_table(dev, peak):
 
     kw4 = dict(qtype=ops.QINT, bits=4, col_group=128)
     n = 4096 * 4096
+    # what a single launch can reach on this much data: a plain device copy (torch's kernel) moving the same number of
+    # bytes as the C1 / C2-weight kernels do (2.5 and 3 bytes per element of a 4096 x 4096 tensor, half read, half written)
+    for tag, nbytes in (("copy_42MB_single_launch_ceiling", int(2.515625 * n)), ("copy_50MB_single_launch_ceiling", 3 * n)):
+        run(tag, lambda nb=nbytes: (torch.empty(nb // 2, dtype=torch.uint8, device=dev).random_(0, 255),),
+            lambda src: torch.empty_like(src).copy_(src), nbytes, nbytes, nbytes)
     run("c1_w4a16_calibrate_quantize_pack", lambda: (rnd(4096, 4096),),
         lambda w: ops.absmax_quantize(w, codec="pack32", **kw4), 2 * n, 2.515625 * n, 2.6 * n)
     def c1_dq_args():
