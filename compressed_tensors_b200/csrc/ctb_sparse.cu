@@ -829,56 +829,10 @@ __device__ __forceinline__ unsigned long long block_popcount_range(const uint8_t
     return t;
 }
 
-// The count exchange of the one-launch expand kernel: every block publishes the count of its own range as
-// (count, tag) and adds up what the blocks before it published.  The tag is a fresh 64-bit number per call, so the
-// scratch never has to be cleared.  Nothing waits for ever: a block that does not see a predecessor's count within
-// the budget (a device that runs the blocks of this grid one after the other, say) counts the bits before its range
-// itself, which needs nobody.
-constexpr long long kPubSpinCycles = 1ll << 21;  // about a millisecond
-__device__ __forceinline__ void publish_tagged(unsigned long long *slots, unsigned long long count, unsigned long long tag) {
-    if (threadIdx.x == 0) {
-        slots[2 * blockIdx.x] = count;
-        __threadfence();
-        asm volatile("st.global.release.gpu.u64 [%0], %1;" ::"l"(slots + 2 * blockIdx.x + 1), "l"(tag) : "memory");
-    }
-}
-__device__ __forceinline__ unsigned long long prefix_of_published(const unsigned long long *slots, unsigned long long tag, const uint8_t *bitmask,
-                                                                  int64_t first) {
-    __shared__ unsigned long long red[kWarps];
-    unsigned long long s = 0;
-    int missing = 0;
-    const long long t0 = clock64();
-    for (int i = threadIdx.x; i < (int)blockIdx.x && !missing; i += kThreads) {
-        for (;;) {
-            unsigned long long v;
-            asm volatile("ld.global.acquire.gpu.u64 %0, [%1];" : "=l"(v) : "l"(slots + 2 * i + 1) : "memory");
-            if (v == tag) {
-                s += *reinterpret_cast<const volatile unsigned long long *>(slots + 2 * i);
-                break;
-            }
-            if (clock64() - t0 > kPubSpinCycles) {
-                missing = 1;
-                break;
-            }
-            __nanosleep(64);
-        }
-    }
-    if (__syncthreads_or(missing)) return block_popcount_range(bitmask, 0, first);  // block-uniform
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, o);
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
-    __syncthreads();
-    unsigned long long base = 0;
-#pragma unroll
-    for (int i = 0; i < kWarps; ++i) base += red[i];
-    return base;
-}
-
-// what the one-launch form of the expand kernel needs besides the arguments of the two-launch form
+// what the dequantizing form of the expand kernel needs besides the arguments of the plain form
 struct ExpandExtra {
-    unsigned long long tag;   // of this call's (count, tag) slots
-    const uint16_t *scale;    // DEQ: one bf16 scale per row
-    FastDiv by_upr;           // DEQ: unit -> row
+    const uint16_t *scale;  // one bf16 scale per row
+    FastDiv by_upr;         // unit -> row
 };
 
 template <int ES>
@@ -964,12 +918,12 @@ __global__ void __launch_bounds__(kThreads, ES == 4 ? 4 : 6) bm_block_scatter_ke
 // decompress, kernel 2 (same grid as kernel 1): every tile's kept values are one contiguous run of `values`: bring it
 // into the window (whole 16-byte words that lie inside the run, its ragged ends by element, so nothing outside
 // `values` is ever read), then every thread rebuilds its units from the window
-// ONEPASS: no count kernel runs in front: `block_tot` is the (count, tag) scratch of publish_tagged and the block counts
-// its own range first.  Used where the launch almost always returns at once (the gated fallback of the 2:4 kernels),
-// so that the common case pays for one empty launch and not two: as the main path it is slower than the pair, because no
-// block can start its walk before every block ahead of it has been dispatched and has published.
+// SELFCOUNT: no count kernel runs in front and nothing is exchanged between blocks: every block counts the bits before
+// its own range itself.  That reads half the bitmask per block on average, which is the price of a launch that needs
+// no scratch, no ticket and no other block; it is the form of the gated fallback of the 2:4 kernels, which returns at
+// once unless a bitmask is not two-per-four, so that the common case pays for one empty launch and not two.
 // DEQ (8-bit elements): the rebuilt e4m3 codes are dequantized with the row's bf16 scale and `out` is bf16.
-template <int ES, bool ONEPASS = false, bool DEQ = false>
+template <int ES, bool SELFCOUNT = false, bool DEQ = false>
 __global__ void __launch_bounds__(kThreads, ES == 4 ? 4 : 6) bm_block_expand_kernel(const void *values, const uint8_t *bitmask, int64_t units,
                                                                    unsigned long long *block_tot, void *out, Gate gate,
                                                                    ExpandExtra extra = ExpandExtra{}) {
@@ -989,10 +943,9 @@ __global__ void __launch_bounds__(kThreads, ES == 4 ? 4 : 6) bm_block_expand_ker
         }
     };
     unsigned long long src;
-    if constexpr (ONEPASS) {
-        publish_tagged(block_tot, block_popcount_range(bitmask, first, last), extra.tag);
+    if constexpr (SELFCOUNT) {
         if (first < last) fetch(first);
-        src = prefix_of_published(block_tot, extra.tag, bitmask, first);
+        src = block_popcount_range(bitmask, 0, first);
     } else {
         if (first < last) fetch(first);
         src = block_first_value(block_tot, nullptr);
@@ -1495,6 +1448,14 @@ static int launch_single_pass(const void *x, const ElemInfo &e, int64_t units, u
     *launched = false;
     const int64_t ntiles = cdiv(units * 8, F::kTileElems);
     if (ntiles > kFzMaxTiles) return CTB_OK;
+    // The per-tile counts are told apart from stale scratch by a ticket chosen per launch CALL.  A launch recorded into
+    // a CUDA graph would replay with the ticket it was recorded with and could take the counts of the replay before for
+    // its own: a capturing stream gets the two-kernel path, which exchanges nothing through tagged scratch.
+    cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &capturing) != cudaSuccess || capturing != cudaStreamCaptureStatusNone) {
+        cudaGetLastError();
+        return CTB_OK;
+    }
     int dev = 0, coop = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return CTB_OK;
     static std::atomic<int> per_sm[64];  // resident blocks per SM of this instantiation on each device (0: not asked yet, -1: cannot run)
@@ -1611,26 +1572,23 @@ static int decompress_impl(const void *values, const uint8_t *bitmask, int32_t d
         // both kernels must see the same grid: it defines the ranges.  As the gated fallback of the 2:4
         // expansion the launches almost always return at once: keep them small.
         const int g1 = tile_grid(units, gate.flag ? 1 : 6);
-        if ((gate.flag != nullptr || deq_scale != nullptr) && 16ll * g1 <= tile_bytes() && units < (1ll << 31)) {
-            // the gated fallback (and the dequantizing form, which only exists in this shape): one launch
-            static std::atomic<unsigned long long> s_tag{0x9E3779B97F4A7C15ull};
-            ExpandExtra extra{};
-            extra.tag = s_tag.fetch_add(0xD1B54A32D192ED03ull, std::memory_order_relaxed);
-            extra.scale = deq_scale;
-            extra.by_upr = make_fastdiv((uint32_t)(cols / 8));
-            if (deq_scale != nullptr) {
-                if (e.esize != 1) return fail(CTB_EINVAL_DTYPE, "the dequantizing expansion takes e4m3 values");
-                bm_block_expand_kernel<1, true, true><<<g1, kThreads, 0, st>>>(values, bitmask, units, block_tot, out, gate, extra);
-            } else if (e.esize == 2) bm_block_expand_kernel<2, true><<<g1, kThreads, 0, st>>>(values, bitmask, units, block_tot, out, gate, extra);
+        ExpandExtra extra{};
+        extra.scale = deq_scale;
+        extra.by_upr = make_fastdiv((uint32_t)(cols / 8));
+        if (deq_scale != nullptr && (e.esize != 1 || units >= (1ll << 31))) return fail(CTB_EUNSUPPORTED, "the dequantizing expansion takes at most 2^34 e4m3 values");
+        if (gate.flag != nullptr) {
+            // the gated fallback: one launch that needs no count kernel in front (see SELFCOUNT)
+            if (deq_scale != nullptr) bm_block_expand_kernel<1, true, true><<<g1, kThreads, 0, st>>>(values, bitmask, units, block_tot, out, gate, extra);
+            else if (e.esize == 2) bm_block_expand_kernel<2, true><<<g1, kThreads, 0, st>>>(values, bitmask, units, block_tot, out, gate, extra);
             else if (e.esize == 1) bm_block_expand_kernel<1, true><<<g1, kThreads, 0, st>>>(values, bitmask, units, block_tot, out, gate, extra);
             else bm_block_expand_kernel<4, true><<<g1, kThreads, 0, st>>>(values, bitmask, units, block_tot, out, gate, extra);
             return after_launch("bm_block_expand_kernel");
         }
-        if (deq_scale != nullptr) return fail(CTB_EUNSUPPORTED, "tensor too large for the dequantizing expansion");
         bm_block_popcount_kernel<<<g1, kThreads, 0, st>>>(bitmask, units, block_tot, gate);
         int rc0 = after_launch("bm_block_popcount_kernel");
         if (rc0) return rc0;
-        if (e.esize == 2) bm_block_expand_kernel<2><<<g1, kThreads, 0, st>>>(values, bitmask, units, block_tot, out, gate);
+        if (deq_scale != nullptr) bm_block_expand_kernel<1, false, true><<<g1, kThreads, 0, st>>>(values, bitmask, units, block_tot, out, gate, extra);
+        else if (e.esize == 2) bm_block_expand_kernel<2><<<g1, kThreads, 0, st>>>(values, bitmask, units, block_tot, out, gate);
         else if (e.esize == 1) bm_block_expand_kernel<1><<<g1, kThreads, 0, st>>>(values, bitmask, units, block_tot, out, gate);
         else bm_block_expand_kernel<4><<<g1, kThreads, 0, st>>>(values, bitmask, units, block_tot, out, gate);
         return after_launch("bm_block_expand_kernel");

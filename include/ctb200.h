@@ -202,7 +202,9 @@ int64_t ctb_bitmask_workspace_bytes(int64_t rows, int64_t cols);
  * 8192 elements on a device with cooperative launches as ONE kernel that reads x from HBM once (bulk copies into shared
  * memory, per-tile counts exchanged through the workspace, every wait bounded; if a wait gives up, *out_nnz reads -1 and
  * the outputs are undefined).  The default (1) is the count + compaction pair of kernels, which is faster while the
- * tensor fits the L2 cache.  Process-wide switch; no counterpart in the reference. */
+ * tensor fits the L2 cache, and it is what a stream that is being captured into a CUDA graph always gets (the single
+ * kernel tells its per-tile counts from stale scratch by a ticket chosen per launch call, which a replay would repeat).
+ * Process-wide switch; no counterpart in the reference. */
 void ctb_bitmask_force_two_kernels(int32_t on);
 int ctb_bitmask_compress(const void *x, int32_t dtype, int64_t rows, int64_t cols, void *out_values,
                          uint8_t *out_bitmask, int64_t *out_row_offsets, int64_t *out_nnz,
