@@ -928,6 +928,9 @@ __global__ void __launch_bounds__(kThreads, ES == 4 ? 4 : 6) bm_block_expand_ker
                                                                    unsigned long long *block_tot, void *out, Gate gate,
                                                                    ExpandExtra extra = ExpandExtra{}) {
     static_assert(!DEQ || ES == 1, "the dequantizing form is for e4m3 codes");
+    // launched as a programmatic dependent of the kernel that may raise the flag: its blocks may be resident before that
+    // kernel has finished, and wait here for its completion (and the visibility of its writes)
+    if constexpr (SELFCOUNT) asm volatile("griddepcontrol.wait;" ::: "memory");
     if (gate.flag != nullptr && *gate.flag != gate.value) return;
     __shared__ __align__(16) unsigned char win[BmWindow<ES>::kBytes];
     __shared__ uint32_t wt[kWarps][2], pre[kBmRows * kWarps + 1];
@@ -1577,11 +1580,24 @@ static int decompress_impl(const void *values, const uint8_t *bitmask, int32_t d
         extra.by_upr = make_fastdiv((uint32_t)(cols / 8));
         if (deq_scale != nullptr && (e.esize != 1 || units >= (1ll << 31))) return fail(CTB_EUNSUPPORTED, "the dequantizing expansion takes at most 2^34 e4m3 values");
         if (gate.flag != nullptr) {
-            // the gated fallback: one launch that needs no count kernel in front (see SELFCOUNT)
-            if (deq_scale != nullptr) bm_block_expand_kernel<1, true, true><<<g1, kThreads, 0, st>>>(values, bitmask, units, block_tot, out, gate, extra);
-            else if (e.esize == 2) bm_block_expand_kernel<2, true><<<g1, kThreads, 0, st>>>(values, bitmask, units, block_tot, out, gate, extra);
-            else if (e.esize == 1) bm_block_expand_kernel<1, true><<<g1, kThreads, 0, st>>>(values, bitmask, units, block_tot, out, gate, extra);
-            else bm_block_expand_kernel<4, true><<<g1, kThreads, 0, st>>>(values, bitmask, units, block_tot, out, gate, extra);
+            // the gated fallback: one launch that needs no count kernel in front (see SELFCOUNT), queued as a programmatic
+            // dependent of the kernel before it, so that its launch latency is spent while that kernel still runs
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3((unsigned)g1);
+            cfg.blockDim = dim3(kThreads);
+            cfg.dynamicSmemBytes = 0;
+            cfg.stream = st;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[0].val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            cudaError_t le;
+            if (deq_scale != nullptr) le = cudaLaunchKernelEx(&cfg, bm_block_expand_kernel<1, true, true>, values, bitmask, units, block_tot, out, gate, extra);
+            else if (e.esize == 2) le = cudaLaunchKernelEx(&cfg, bm_block_expand_kernel<2, true, false>, values, bitmask, units, block_tot, out, gate, extra);
+            else if (e.esize == 1) le = cudaLaunchKernelEx(&cfg, bm_block_expand_kernel<1, true, false>, values, bitmask, units, block_tot, out, gate, extra);
+            else le = cudaLaunchKernelEx(&cfg, bm_block_expand_kernel<4, true, false>, values, bitmask, units, block_tot, out, gate, extra);
+            if (le != cudaSuccess) return fail(CTB_ECUDA, "bm_block_expand_kernel: %s", cudaGetErrorString(le));
             return after_launch("bm_block_expand_kernel");
         }
         bm_block_popcount_kernel<<<g1, kThreads, 0, st>>>(bitmask, units, block_tot, gate);
