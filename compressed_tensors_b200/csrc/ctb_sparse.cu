@@ -847,6 +847,7 @@ __global__ void __launch_bounds__(kThreads, ES == 4 ? 4 : 6) bm_block_scatter_ke
                                                                     int64_t *nnz) {
     __shared__ __align__(16) unsigned char win[BmWindow<ES>::kBytes];
     __shared__ uint32_t wt[kWarps][2], pre[kBmRows * kWarps + 1];
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // a programmatic dependent of the count kernel (see launch_dependent)
     const uint32_t win_addr = (uint32_t)__cvta_generic_to_shared(win);
     int64_t first, last;
     block_range(units, first, last);
@@ -928,9 +929,10 @@ __global__ void __launch_bounds__(kThreads, ES == 4 ? 4 : 6) bm_block_expand_ker
                                                                    unsigned long long *block_tot, void *out, Gate gate,
                                                                    ExpandExtra extra = ExpandExtra{}) {
     static_assert(!DEQ || ES == 1, "the dequantizing form is for e4m3 codes");
-    // launched as a programmatic dependent of the kernel that may raise the flag: its blocks may be resident before that
-    // kernel has finished, and wait here for its completion (and the visibility of its writes)
-    if constexpr (SELFCOUNT) asm volatile("griddepcontrol.wait;" ::: "memory");
+    // launched as a programmatic dependent of the kernel in front (the count kernel, or the 2:4 kernel that may raise the
+    // flag): its blocks may be resident before that kernel has finished, and wait here for its completion and the
+    // visibility of its writes (without the launch attribute this returns at once)
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     if (gate.flag != nullptr && *gate.flag != gate.value) return;
     __shared__ __align__(16) unsigned char win[BmWindow<ES>::kBytes];
     __shared__ uint32_t wt[kWarps][2], pre[kBmRows * kWarps + 1];
@@ -1421,6 +1423,23 @@ extern "C" int ctb_sparse24_compress(const void *x, int32_t dtype, int64_t rows,
     return after_launch("sparse24_compress_simd_kernel");
 }
 
+// Launch `kernel` as a programmatic dependent of the kernel before it on the stream: its launch latency is spent while
+// that kernel still runs, and its blocks wait at their `griddepcontrol.wait` for that kernel to have completed.
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_dependent(void (*kernel)(KArgs...), int grid, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 // 1 keeps ctb_bitmask_compress on the two-kernel path (the default: on the tensor sizes of a model's weights the pair
 // is the faster of the two; the single-pass kernel reads the tensor from HBM only once and is there for tensors that do
 // not fit the L2 cache).  ctb_bitmask_force_two_kernels(0) selects the single-pass kernel where it can run.
@@ -1524,9 +1543,11 @@ static int compress_impl(const void *x, const uint8_t *pred, int32_t dtype, int6
         else if (e.esize == 1) bm_block_count_kernel<1><<<g1, kThreads, 0, st>>>(x, e.nz_mask, units, bitmask, block_tot);
         else bm_block_count_kernel<4><<<g1, kThreads, 0, st>>>(x, e.nz_mask, units, bitmask, block_tot);
         if ((rc = after_launch("bm_block_count_kernel"))) return rc;
-        if (e.esize == 2) bm_block_scatter_kernel<2><<<g1, kThreads, 0, st>>>(x, bitmask, units, by_upr, upr, block_tot, values, row_offsets, nnz);
-        else if (e.esize == 1) bm_block_scatter_kernel<1><<<g1, kThreads, 0, st>>>(x, bitmask, units, by_upr, upr, block_tot, values, row_offsets, nnz);
-        else bm_block_scatter_kernel<4><<<g1, kThreads, 0, st>>>(x, bitmask, units, by_upr, upr, block_tot, values, row_offsets, nnz);
+        cudaError_t le;
+        if (e.esize == 2) le = launch_dependent(bm_block_scatter_kernel<2>, g1, st, x, bitmask, units, by_upr, upr, block_tot, values, row_offsets, nnz);
+        else if (e.esize == 1) le = launch_dependent(bm_block_scatter_kernel<1>, g1, st, x, bitmask, units, by_upr, upr, block_tot, values, row_offsets, nnz);
+        else le = launch_dependent(bm_block_scatter_kernel<4>, g1, st, x, bitmask, units, by_upr, upr, block_tot, values, row_offsets, nnz);
+        if (le != cudaSuccess) return fail(CTB_ECUDA, "bm_block_scatter_kernel: %s", cudaGetErrorString(le));
         return after_launch("bm_block_scatter_kernel");
     }
     int grid = grid_for(rows, 1, 8);
@@ -1582,31 +1603,23 @@ static int decompress_impl(const void *values, const uint8_t *bitmask, int32_t d
         if (gate.flag != nullptr) {
             // the gated fallback: one launch that needs no count kernel in front (see SELFCOUNT), queued as a programmatic
             // dependent of the kernel before it, so that its launch latency is spent while that kernel still runs
-            cudaLaunchConfig_t cfg = {};
-            cfg.gridDim = dim3((unsigned)g1);
-            cfg.blockDim = dim3(kThreads);
-            cfg.dynamicSmemBytes = 0;
-            cfg.stream = st;
-            cudaLaunchAttribute attr[1];
-            attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-            attr[0].val.programmaticStreamSerializationAllowed = 1;
-            cfg.attrs = attr;
-            cfg.numAttrs = 1;
             cudaError_t le;
-            if (deq_scale != nullptr) le = cudaLaunchKernelEx(&cfg, bm_block_expand_kernel<1, true, true>, values, bitmask, units, block_tot, out, gate, extra);
-            else if (e.esize == 2) le = cudaLaunchKernelEx(&cfg, bm_block_expand_kernel<2, true, false>, values, bitmask, units, block_tot, out, gate, extra);
-            else if (e.esize == 1) le = cudaLaunchKernelEx(&cfg, bm_block_expand_kernel<1, true, false>, values, bitmask, units, block_tot, out, gate, extra);
-            else le = cudaLaunchKernelEx(&cfg, bm_block_expand_kernel<4, true, false>, values, bitmask, units, block_tot, out, gate, extra);
+            if (deq_scale != nullptr) le = launch_dependent(bm_block_expand_kernel<1, true, true>, g1, st, values, bitmask, units, block_tot, out, gate, extra);
+            else if (e.esize == 2) le = launch_dependent(bm_block_expand_kernel<2, true, false>, g1, st, values, bitmask, units, block_tot, out, gate, extra);
+            else if (e.esize == 1) le = launch_dependent(bm_block_expand_kernel<1, true, false>, g1, st, values, bitmask, units, block_tot, out, gate, extra);
+            else le = launch_dependent(bm_block_expand_kernel<4, true, false>, g1, st, values, bitmask, units, block_tot, out, gate, extra);
             if (le != cudaSuccess) return fail(CTB_ECUDA, "bm_block_expand_kernel: %s", cudaGetErrorString(le));
             return after_launch("bm_block_expand_kernel");
         }
         bm_block_popcount_kernel<<<g1, kThreads, 0, st>>>(bitmask, units, block_tot, gate);
         int rc0 = after_launch("bm_block_popcount_kernel");
         if (rc0) return rc0;
-        if (deq_scale != nullptr) bm_block_expand_kernel<1, false, true><<<g1, kThreads, 0, st>>>(values, bitmask, units, block_tot, out, gate, extra);
-        else if (e.esize == 2) bm_block_expand_kernel<2><<<g1, kThreads, 0, st>>>(values, bitmask, units, block_tot, out, gate);
-        else if (e.esize == 1) bm_block_expand_kernel<1><<<g1, kThreads, 0, st>>>(values, bitmask, units, block_tot, out, gate);
-        else bm_block_expand_kernel<4><<<g1, kThreads, 0, st>>>(values, bitmask, units, block_tot, out, gate);
+        cudaError_t le;
+        if (deq_scale != nullptr) le = launch_dependent(bm_block_expand_kernel<1, false, true>, g1, st, values, bitmask, units, block_tot, out, gate, extra);
+        else if (e.esize == 2) le = launch_dependent(bm_block_expand_kernel<2, false, false>, g1, st, values, bitmask, units, block_tot, out, gate, extra);
+        else if (e.esize == 1) le = launch_dependent(bm_block_expand_kernel<1, false, false>, g1, st, values, bitmask, units, block_tot, out, gate, extra);
+        else le = launch_dependent(bm_block_expand_kernel<4, false, false>, g1, st, values, bitmask, units, block_tot, out, gate, extra);
+        if (le != cudaSuccess) return fail(CTB_ECUDA, "bm_block_expand_kernel: %s", cudaGetErrorString(le));
         return after_launch("bm_block_expand_kernel");
     }
     if (deq_scale != nullptr) return fail(CTB_EUNSUPPORTED, "the dequantizing expansion needs cols %% 8 == 0 and aligned buffers");
