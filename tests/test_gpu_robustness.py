@@ -103,6 +103,49 @@ def test_sparse24_decompress_short_values_take_the_generic_kernels():
     assert L.launch_count() - n0 == 2
 
 
+def test_sparse24_decompress_replayed_from_a_graph_with_changing_bitmasks():
+    """One captured launch sequence, replayed over buffers whose contents change between replays: a two-per-four
+    bitmask, then an irregular one (the gated fallback must run and give the generic codec's result), then a regular
+    one again.  Nothing in the sequence may depend on state that a replay repeats (tickets, tags) for its result."""
+    from compressed_tensors_b200 import ops
+    from oracle import ref as orc
+
+    orc.build()
+    rows, cols = 96, 1024
+    g = torch.Generator().manual_seed(5)
+
+    def regular(seed):
+        t = weights(rows, cols, seed)
+        v, b = orc.sparse24_compress(t)
+        return v.flatten(), b, orc.bitmask_decompress(v, b, t.shape)
+
+    def irregular():
+        t = weights(rows, cols, 77)
+        t[torch.rand(rows, cols, generator=g) < 0.6] = 0  # fewer than two kept per four on average, unevenly spread
+        v, b, _ = orc.bitmask_compress(t)
+        room = torch.zeros(rows * cols // 2, dtype=t.dtype)  # a buffer of two per four, so the scan-free kernel runs first
+        assert v.numel() <= room.numel()
+        room[:v.numel()] = v
+        return room, b, orc.bitmask_decompress(v, b, t.shape)
+
+    cases = [regular(1), irregular(), regular(2), irregular(), regular(3)]
+    values = torch.empty(rows * cols // 2, dtype=torch.bfloat16, device="cuda")
+    bitmask = torch.empty((rows, cols // 8), dtype=torch.uint8, device="cuda")
+    values.copy_(cases[0][0]), bitmask.copy_(cases[0][1])
+    ops.sparse24_decompress(values, bitmask, (rows, cols))  # warm-up outside the capture
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            out = ops.sparse24_decompress(values, bitmask, (rows, cols))
+    for i, (v, b, want) in enumerate(cases):
+        values.copy_(v), bitmask.copy_(b)
+        graph.replay()
+        torch.cuda.synchronize()
+        assert_bit_equal(out.cpu(), want, f"replay {i}")
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs in one process")
 def test_one_process_two_devices():
     """The tensor-core entry point opts into its large dynamic shared memory per device: a process that drives a second
