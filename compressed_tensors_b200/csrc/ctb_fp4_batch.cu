@@ -38,9 +38,9 @@ __device__ __noinline__ void quant_fp4_chunk_general(const uint4 *chunk, const v
 }
 
 // bf16 -> e2m1 codes, two per byte.  A lane takes a chunk of 8 elements, half a group, so that every warp instruction
-// moves one contiguous span.  Finite chunks with a scale in the normal range and no zero point other than zero go through the reciprocal +
-// Markstein quotient and the saturating e2m1 convert (quant_fp4_codes_f32); everything else through the templates of
-// the per-tensor vec8 tier.
+// moves one contiguous span.  Finite chunks with a scale in the normal range and no zero point other than zero go
+// through the reciprocal + Markstein quotient and the saturating e2m1 convert (quant_fp4_codes_f32); everything else
+// through the templates of the per-tensor vec8 tier.
 __global__ void __launch_bounds__(kF4Threads, 6) quant_fp4_g16_batch_kernel(const __grid_constant__ F4Batch B) {
     // (effective scale, its reciprocal) of every possible scale byte of the tensor the block is working on: 256 IEEE
     // divisions per tensor instead of one per group.  A reciprocal of 0 marks a scale outside the range where the
